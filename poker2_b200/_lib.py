@@ -1,0 +1,82 @@
+"""ctypes binding of libpoker2_b200.so (the C ABI declared in include/poker2_b200.h).
+
+There is no CPU fallback: if the shared library is missing or a call fails, an exception
+is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+_PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG_DIR, "libpoker2_b200.so")
+TABLE_BYTES = 18592
+NUM_HANDS = 1326
+
+_lib = None
+
+_vp = ctypes.c_void_p
+_i64 = ctypes.c_int64
+_i32 = ctypes.c_int
+_f32 = ctypes.c_float
+
+# name -> argtypes; every function returns int
+_SIGNATURES = {
+    "p2b_rank7_cards": [_vp, _i64, _vp, _vp],
+    "p2b_compare7_cards": [_vp, _i64, _vp, _vp],
+    "p2b_compare7_planes": [_vp, _i64, _vp, _vp],
+    "p2b_rank_hands": [_vp, _i64, _vp, _vp, _vp, _vp],
+    "p2b_showdown_values": [_vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _i64, _vp],
+}
+
+
+def library_available() -> bool:
+    return os.path.exists(LIB_PATH)
+
+
+def lib():
+    """Loads the shared library once; raises RuntimeError if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m poker2_b200.build` "
+                "(poker2_b200 has no CPU or PyTorch fallback)"
+            )
+        handle = ctypes.CDLL(LIB_PATH)
+        handle.p2b_last_error.restype = ctypes.c_char_p
+        handle.p2b_last_error.argtypes = []
+        handle.p2b_version.restype = ctypes.c_int
+        for name, argtypes in _SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.argtypes = argtypes
+            fn.restype = ctypes.c_int
+        _lib = handle
+    return _lib
+
+
+def exported_symbols():
+    return ["p2b_last_error", "p2b_version", *_SIGNATURES.keys()]
+
+
+def call(name: str, *args) -> None:
+    handle = lib()
+    rc = getattr(handle, name)(*args)
+    if rc != 0:
+        msg = handle.p2b_last_error().decode("utf-8", "replace")
+        raise RuntimeError(f"{name} failed ({rc}): {msg}")
+
+
+def ptr(t: torch.Tensor | None):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def stream_ptr(device: torch.device):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def require_cuda(t: torch.Tensor, what: str) -> None:
+    if t.device.type != "cuda":
+        raise ValueError(f"{what} requires a CUDA tensor.")

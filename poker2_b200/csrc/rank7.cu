@@ -1,0 +1,116 @@
+// Hand-ranking kernels: packed score of [N,7] card ids, pairwise comparison of card-id
+// and one-hot-plane hands.  HBM-bound by design: 14 B in + 4 B out per hand, staged
+// through shared memory so that global loads are 128-bit and coalesced although a hand
+// row (14 B) is not a power of two.
+#include "common.cuh"
+#include "rank7.cuh"
+
+namespace p2b {
+
+constexpr int kRankThreads = 256;
+constexpr int kHandsPerThread = 4;
+constexpr int kTileHands = kRankThreads * kHandsPerThread;  // 1024 hands = 14336 B per tile
+constexpr int kTileVec = kTileHands * 14 / 16;              // 896 x 16 B
+
+// cards: [n,7] int16; out: [n] int32.  VEC = base pointer is 16-byte aligned.
+template <bool VEC>
+__global__ void __launch_bounds__(kRankThreads) rank7_cards_kernel(const int16_t* __restrict__ cards,
+                                                                   int32_t* __restrict__ out, int64_t n) {
+    __shared__ __align__(16) int16_t tile[kTileHands * 7];
+    const int64_t num_tiles = (n + kTileHands - 1) / kTileHands;
+    for (int64_t t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+        const int64_t hand0 = t * kTileHands;
+        const int64_t remaining = n - hand0;
+        const int hands = remaining < kTileHands ? (int)remaining : kTileHands;
+        const int16_t* src = cards + hand0 * 7;
+        if (VEC && hands == kTileHands) {
+            const uint4* src4 = reinterpret_cast<const uint4*>(src);
+            uint4* dst4 = reinterpret_cast<uint4*>(tile);
+#pragma unroll
+            for (int i = threadIdx.x; i < kTileVec; i += kRankThreads) dst4[i] = __ldcs(src4 + i);
+        } else {
+            for (int i = threadIdx.x; i < hands * 7; i += kRankThreads) tile[i] = src[i];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < kHandsPerThread; ++j) {
+            const int h = threadIdx.x + j * kRankThreads;
+            if (h < hands) {
+                int c[7];
+#pragma unroll
+                for (int i = 0; i < 7; ++i) c[i] = tile[h * 7 + i];
+                __stcs(out + hand0 + h, score_cards<7>(c));
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// cards: [n,2,7] int16 -> {1,-1,0}
+__global__ void __launch_bounds__(256) compare7_cards_kernel(const int16_t* __restrict__ cards,
+                                                            int32_t* __restrict__ out, int64_t n) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        int a[7], b[7];
+#pragma unroll
+        for (int k = 0; k < 7; ++k) {
+            a[k] = cards[i * 14 + k];
+            b[k] = cards[i * 14 + 7 + k];
+        }
+        const int32_t sa = score_cards<7>(a), sb = score_cards<7>(b);
+        out[i] = (sa > sb) - (sa < sb);
+    }
+}
+
+// planes: [n,2,4,13] bytes (non-zero = card present) -> {1,-1,0}.  A plane set is a set of
+// cards, so a rank's count is the number of suits holding it (p2/env/rules.py:157).
+__device__ __forceinline__ int32_t score_planes(const int8_t* __restrict__ p) {
+    uint32_t m[4];
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+        uint32_t bits = 0;
+#pragma unroll
+        for (int r = 0; r < 13; ++r) bits |= (p[s * 13 + r] != 0 ? 1u : 0u) << r;
+        m[s] = bits;
+    }
+    return score_from_masks(m[0], m[1], m[2], m[3], classes_from_suits(m[0], m[1], m[2], m[3]));
+}
+
+__global__ void __launch_bounds__(256) compare7_planes_kernel(const int8_t* __restrict__ planes,
+                                                             int32_t* __restrict__ out, int64_t n) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int32_t sa = score_planes(planes + i * 104), sb = score_planes(planes + i * 104 + 52);
+        out[i] = (sa > sb) - (sa < sb);
+    }
+}
+
+static int grid_for(int64_t work_items, int per_block, int max_blocks) {
+    int64_t g = (work_items + per_block - 1) / per_block;
+    if (g < 1) g = 1;
+    if (g > max_blocks) g = max_blocks;
+    return (int)g;
+}
+
+int sm_count();
+
+int launch_rank7_cards(const int16_t* cards, int64_t n, int32_t* out, cudaStream_t stream) {
+    if (n == 0) return P2B_OK;
+    const int grid = grid_for(n, kTileHands, sm_count() * 8);
+    const bool vec = (reinterpret_cast<uintptr_t>(cards) & 15) == 0;
+    if (vec) rank7_cards_kernel<true><<<grid, kRankThreads, 0, stream>>>(cards, out, n);
+    else rank7_cards_kernel<false><<<grid, kRankThreads, 0, stream>>>(cards, out, n);
+    return check_cuda(cudaGetLastError(), "rank7_cards_kernel");
+}
+
+int launch_compare7_cards(const int16_t* cards, int64_t n, int32_t* out, cudaStream_t stream) {
+    if (n == 0) return P2B_OK;
+    compare7_cards_kernel<<<grid_for(n, 256, sm_count() * 8), 256, 0, stream>>>(cards, out, n);
+    return check_cuda(cudaGetLastError(), "compare7_cards_kernel");
+}
+
+int launch_compare7_planes(const int8_t* planes, int64_t n, int32_t* out, cudaStream_t stream) {
+    if (n == 0) return P2B_OK;
+    compare7_planes_kernel<<<grid_for(n, 256, sm_count() * 8), 256, 0, stream>>>(planes, out, n);
+    return check_cuda(cudaGetLastError(), "compare7_planes_kernel");
+}
+
+}  // namespace p2b

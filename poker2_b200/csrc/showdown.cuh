@@ -1,0 +1,112 @@
+// Blocker-aware river showdown: per-board strength tables and the per-range evaluation.
+//
+// What is computed (p2/search/cfr_evaluator.py:406-601): for a hero hand h=(c1,c2) against
+// an opponent range x over the 1326 combos, with hands sorted by strength and tie groups
+// [L,R) in sorted positions,
+//   win  = P[L] - PC[c1][<L] - PC[c2][<L]
+//   tie  = (P[R]-P[L]) - (PC[c1][<R]-PC[c1][<L]) - (PC[c2][<R]-PC[c2][<L]) + x[h]
+//   den  = max(1 - PC[c1][all] - PC[c2][all] + x[h], 1e-8)
+//   EV   = win/den - (1 - win/den - tie/den),   0 for hands that use a board card
+// where P is the prefix sum of x in strength order and PC[c] the prefix sum restricted to
+// hands holding card c.  The upstream code materialises PC as an [1327,52] table per
+// node; here each card keeps its own list of 51 hands in strength order, and a hand
+// stores how many entries of its two lists lie before L and before R, so PC is a
+// 52x52 table in shared memory.  Prefix sums are accumulated in fp64 and rounded to
+// fp32 per element, which is what the upstream CPU cumsum does; the remaining
+// arithmetic is fp32 in the upstream operation order.
+#pragma once
+
+#include "common.cuh"
+#include "rank7.cuh"
+
+namespace p2b {
+
+// ---- per-board table blob (global memory and shared memory use the same layout) ----
+struct HandRec {          // 8 bytes per hand, natural combo order
+    uint16_t lpos, rpos;  // tie group [lpos, rpos) in sorted positions
+    uint8_t nb0, ne0;     // entries of card c1's list before lpos / before rpos
+    uint8_t nb1, ne1;     // same for card c2
+};
+constexpr int kTabHeaderBytes = 16;                 // uint64 board-card mask + padding
+constexpr int kTabRecBytes = P2B_NUM_HANDS * 8;     // 10608
+constexpr int kTabSortedBytes = P2B_HPAD * 2;       // 2656 (1326 used)
+constexpr int kTabCardListBytes = 5312;             // uint16 [51][52] = 5304 used
+constexpr int kTabBytes = kTabHeaderBytes + kTabRecBytes + kTabSortedBytes + kTabCardListBytes;  // 18592
+static_assert(kTabBytes % 16 == 0, "table blob must be a whole number of 16-byte vectors");
+
+struct BoardTabView {
+    const unsigned long long* board_mask;
+    const HandRec* rec;
+    const uint16_t* sorted;     // [1326] combo at sorted position k
+    const uint16_t* cardlist;   // [51][52]: t-th weakest hand holding card c at [t*52+c]
+};
+__host__ __device__ __forceinline__ BoardTabView view_tables(const unsigned char* blob) {
+    BoardTabView v;
+    v.board_mask = reinterpret_cast<const unsigned long long*>(blob);
+    v.rec = reinterpret_cast<const HandRec*>(blob + kTabHeaderBytes);
+    v.sorted = reinterpret_cast<const uint16_t*>(blob + kTabHeaderBytes + kTabRecBytes);
+    v.cardlist = reinterpret_cast<const uint16_t*>(blob + kTabHeaderBytes + kTabRecBytes + kTabSortedBytes);
+    return v;
+}
+
+// Inclusive block-wide prefix sum in fp64 over `n` values fetched by `fetch(k)`, four
+// consecutive positions per thread; writes fl32(prefix through k) to out[k+1] and 0 to
+// out[0].  `warp_tot` is shared scratch of at least blockDim.x/32 doubles.  All threads of
+// the block must call it; it ends with a barrier.
+template <typename Fetch>
+__device__ __forceinline__ void block_prefix_f64(Fetch fetch, int n, float* __restrict__ out, double* warp_tot) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    for (int base = 0; base < n; base += 4 * blockDim.x) {
+        const int k0 = base + 4 * tid;
+        double v[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] = (k0 + i < n) ? (double)fetch(k0 + i) : 0.0;
+        v[1] += v[0];
+        v[2] += v[1];
+        v[3] += v[2];
+        double incl = v[3];
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const double up = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += up;
+        }
+        // carry of earlier chunks lives in warp_tot[nwarps]
+        if (lane == 31) warp_tot[warp] = incl;
+        __syncthreads();
+        double offset = (base == 0) ? 0.0 : warp_tot[nwarps];
+        for (int w = 0; w < warp; ++w) offset += warp_tot[w];
+        const double excl = offset + (incl - v[3]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            if (k0 + i < n) out[k0 + i + 1] = (float)(excl + v[i]);
+        __syncthreads();
+        if (tid == blockDim.x - 1) warp_tot[nwarps] = excl + v[3];
+        __syncthreads();
+    }
+    if (tid == 0) out[0] = 0.0f;
+    __syncthreads();
+}
+
+// One hero hand of the showdown formula.  P: [1327] prefix in strength order; PC: [52][52]
+// per-card prefix (PC[c*52+t] = mass of the t weakest hands holding c); x: opponent range.
+__device__ __forceinline__ float showdown_hand_ev(const HandRec r, int c1, int c2, float xh, bool allowed,
+                                                  const float* __restrict__ P, const float* __restrict__ PC) {
+    const float PL = P[r.lpos], PR = P[r.rpos];
+    const float* pc1 = PC + c1 * 52;
+    const float* pc2 = PC + c2 * 52;
+    const float a0 = pc1[r.nb0], a1 = pc1[r.ne0], b0 = pc2[r.nb1], b1 = pc2[r.ne1];
+    const float win = __fsub_rn(__fsub_rn(PL, a0), b0);
+    const float seg = __fsub_rn(PR, PL);
+    const float tie = __fadd_rn(__fsub_rn(__fsub_rn(seg, __fsub_rn(a1, a0)), __fsub_rn(b1, b0)), xh);
+    float den = __fadd_rn(__fsub_rn(__fsub_rn(1.0f, pc1[51]), pc2[51]), xh);
+    den = fmaxf(den, 1e-8f);
+    float ev = 0.0f;
+    if (den > 1e-8f) {
+        const float wp = __fdiv_rn(win, den), tp = __fdiv_rn(tie, den);
+        const float lp = __fsub_rn(__fsub_rn(1.0f, wp), tp);
+        ev = __fsub_rn(wp, lp);
+    }
+    return allowed ? ev : 0.0f;
+}
+
+}  // namespace p2b

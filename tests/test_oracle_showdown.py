@@ -1,0 +1,39 @@
+"""The showdown and unblocked-mass oracles against values computed by the upstream code."""
+import os
+
+import numpy as np
+import torch
+
+from oracle import cards, showdown, unblocked
+
+
+def test_showdown_oracle_bit_exact(golden_dir):
+    z = np.load(os.path.join(golden_dir, "showdown.npz"))
+    got = showdown.showdown_values(z["boards"], z["beliefs"], z["potential"], z["scale"])
+    assert torch.equal(got, torch.from_numpy(z["values"]))
+
+
+def test_showdown_oracle_against_enumeration(golden_dir):
+    """Independent check: enumerate opponent hands for a handful of hero hands."""
+    from oracle import rank7
+
+    z = np.load(os.path.join(golden_dir, "showdown.npz"))
+    b = 0
+    board = z["boards"][b : b + 1]
+    bel = torch.from_numpy(z["beliefs"][b : b + 1])
+    vals = showdown.showdown_values(board, bel, np.ones((1, 2), dtype=np.int64), np.ones(1, dtype=np.float32))
+    scores = rank7.rank_boards(board, rank7.MODE_PLANES)[0]
+    ok = cards.allowed_mask(board.astype(np.int64))[0]
+    compat = cards.compatible()
+    opp = z["beliefs"][b, 1].astype(np.float64)
+    for h in np.flatnonzero(ok)[::97]:
+        w = opp * compat[h] * ok
+        tot = w.sum()
+        ev = ((w * (scores < scores[h])).sum() - (w * (scores > scores[h])).sum()) / tot
+        assert abs(vals[0, 0, h].item() - ev) < 1e-5
+
+
+def test_unblocked_oracle_bit_exact(golden_dir):
+    z = np.load(os.path.join(golden_dir, "unblocked.npz"))
+    got = unblocked.unblocked_mass(torch.from_numpy(z["x"]))
+    assert torch.equal(got, torch.from_numpy(z["y"]))
