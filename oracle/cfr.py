@@ -1,0 +1,353 @@
+"""CPU oracle of the subgame CFR loop on a ragged public tree.  Test infrastructure only.
+
+Restates, with torch CPU tensors and the same fp32 operations in the same order, the
+upstream sparse evaluator for trees whose leaves are all terminal (fold or showdown):
+p2/search/cfr_evaluator.py (`initialize_policy_and_beliefs` :830-886, `cfr_iteration`
+:1331-1381, `compute_instantaneous_regrets` :1117-1165, `update_policy` :1168-1193,
+`update_average_policy` :1195-1258, `compute_expected_values` :1049-1115,
+`update_average_values_final` :1276-1292, `_best_response_values` /
+`_compute_exploitability` :603-764) with the tree primitives of
+p2/search/sparse_cfr_evaluator.py (:428-538).
+
+The tree comes in the upstream node order: level-major over the whole batch, children of a
+parent contiguous in action order.  Required keys of `tree` (numpy arrays):
+  depth_offsets [D+2] int, parent_index [M], action_from_parent [M], to_act [M],
+  child_count [M], leaf_mask [M] bool, done [M] bool, street [M] (4 = showdown reached),
+  fold_value [M] fp32 (value for player 0 at fold leaves, 0 elsewhere),
+  showdown_potential [M,2] int64, scale [M] fp32, boards [N,5], num_actions int.
+The initial policy is uniform over the legal children, which is what the upstream code
+obtains from a model that returns zero logits (:306-330).
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from . import cards, showdown, unblocked
+
+H = cards.NUM_HANDS
+
+
+class SubgameOracle:
+    def __init__(self, tree: dict, root_beliefs: torch.Tensor, *, iterations: int,
+                 alpha: float = 1.5, beta: float = 0.0, gamma: float = 2.0,
+                 dcfr_delay: int = 0, cfr_type: str = "discounted", cfr_plus: bool = False):
+        t = {k: (torch.from_numpy(np.ascontiguousarray(v)) if isinstance(v, np.ndarray) else v)
+             for k, v in tree.items()}
+        self.offs = [int(x) for x in tree["depth_offsets"]]
+        self.N = self.offs[1]
+        self.M = self.offs[-1]
+        self.depth = len(self.offs) - 2
+        self.top = self.offs[-2]
+        self.A = int(tree["num_actions"])
+        self.parent = t["parent_index"].long()
+        self.action = t["action_from_parent"].long()
+        self.to_act = t["to_act"].long()
+        self.child_count = t["child_count"].long()
+        self.leaf = t["leaf_mask"].bool()
+        self.done = t["done"].bool()
+        self.fold_value = t["fold_value"].float()
+        self.scale = t["scale"].float()
+        self.iterations = iterations
+        self.alpha, self.beta, self.gamma = alpha, beta, gamma
+        self.dcfr_delay = dcfr_delay
+        self.cfr_type = cfr_type
+        self.cfr_plus = cfr_plus
+        N, M = self.N, self.M
+
+        self.prev_actor = torch.full((M,), -1, dtype=torch.long)
+        self.prev_actor[N:] = self.to_act[self.parent[N:]]
+        sd = torch.where(t["street"].long() == 4)[0]
+        self.sd_idx = sd
+        self.sd_potential = t["showdown_potential"].long()[sd]
+        root_of = torch.arange(M)
+        for d in range(self.depth):
+            a, b = self.offs[d + 1], self.offs[d + 2]
+            root_of[a:b] = root_of[self.parent[a:b]]
+        self.root_of = root_of
+        self.boards = np.asarray(tree["boards"])
+        self.sd_boards = self.boards[root_of[sd].numpy()]
+
+        allowed_root = torch.from_numpy(cards.allowed_mask(self.boards))
+        prob_root = allowed_root.float()
+        prob_root = prob_root / prob_root.sum(-1, keepdim=True).clamp(min=1.0)
+        self.allowed = allowed_root[root_of]
+        self.allowed_prob = prob_root[root_of]
+
+        z = lambda *s: torch.zeros(*s, dtype=torch.float32)  # noqa: E731
+        self.policy = z(M, H)
+        self.policy_avg = z(M, H)
+        self.regrets = z(M, H)
+        self.weight_sums = z(M, H)
+        self.uniform = z(M, H)
+        self.uniform[N:] = (1.0 / self._fan_out(self.child_count))[:, None].expand(-1, H)
+        self.beliefs = z(M, 2, H)
+        self.beliefs[:N] = root_beliefs.float()
+        self.beliefs_avg = self.beliefs.clone()
+        self.reach = z(M, 2, H)
+        self.reach[:N] = 1.0
+        self.reach_avg = self.reach.clone()
+        self.values = z(M, 2, H)
+        fold = (self.action == 0) & self.done
+        self.values[fold, 0] = self.fold_value[fold][:, None]
+        self.values[fold, 1] = -self.fold_value[fold][:, None]
+        self.values_avg = self.values.clone()
+
+    # ---- tree primitives (sparse_cfr_evaluator.py:428-538) ----
+    def _fan_out(self, x, level=None):
+        if level is None:
+            a, b, size = 0, self.top, self.M - self.N
+        else:
+            a, b = self.offs[level], self.offs[level + 1]
+            size = self.offs[level + 2] - b
+        return x[a:b].repeat_interleave(self.child_count[a:b], dim=0, output_size=size)
+
+    def _pull_back_sum(self, x, out, level=None):
+        a, b = (self.N, self.M) if level is None else (self.offs[level + 1], self.offs[level + 2])
+        src = x[a:b] if x.shape[0] == self.M else x
+        idx = self.parent[a:b][(...,) + (None,) * (src.dim() - 1)].expand(-1, *src.shape[1:])
+        out.scatter_reduce_(0, idx, src, reduce="sum", include_self=True)
+
+    def _pull_back(self, x, level=None):
+        if level is None:
+            pa, pb, ca, cb = 0, self.top, self.N, self.M
+        else:
+            pa, pb = self.offs[level], self.offs[level + 1]
+            ca, cb = self.offs[level + 1], self.offs[level + 2]
+        out = torch.zeros((pb - pa, self.A, *x.shape[1:]), dtype=x.dtype)
+        out[self.parent[ca:cb] - pa, self.action[ca:cb]] = x[ca:cb]
+        return out
+
+    def _fan_out_deep(self, x):
+        out = torch.zeros((self.M, *x.shape[1:]), dtype=x.dtype)
+        out[: self.N] = x
+        for d in range(self.depth):
+            out[self.offs[d + 1]: self.offs[d + 2]] = self._fan_out(out, d)
+        return out
+
+    # ---- beliefs and reach (cfr_evaluator.py:248-273, 332-380) ----
+    def _block(self, target):
+        target.masked_fill_((~self.allowed)[:, None, :], 0.0)
+
+    def _normalize(self, target):
+        denom = target.sum(dim=-1, keepdim=True)
+        torch.where(denom > 1e-5, target / denom, self.allowed_prob[:, None, :], out=target)
+
+    def _reach_weights(self, target, policy):
+        for d in range(self.depth):
+            a, b = self.offs[d + 1], self.offs[d + 2]
+            dest = target[a:b]
+            dest[:] = self._fan_out(target, level=d)
+            idx = self.prev_actor[a:b][:, None, None].expand(-1, -1, H)
+            dest.scatter_reduce_(1, idx, policy[a:b][:, None], reduce="prod", include_self=True)
+        self._block(target)
+
+    def _propagate_beliefs(self, target, reach):
+        target[:] = self._fan_out_deep(target[: self.N]) * reach
+        self._normalize(target)
+
+    # ---- start of evaluate_cfr (cfr_evaluator.py:1503-1513) ----
+    def initialize(self):
+        self.policy.zero_()
+        for d in range(self.depth):
+            a, b, c = self.offs[d], self.offs[d + 1], self.offs[d + 2]
+            self.policy[b:c] = self.uniform[b:c]
+            self.beliefs[b:c] = self._fan_out(self.beliefs, level=d)
+            rows = torch.arange(b, c)
+            self.beliefs[rows, self.prev_actor[b:c]] *= self.policy[b:c]
+            self._block(self.beliefs)
+            self._normalize(self.beliefs)
+        if self.depth == 0:
+            self._block(self.beliefs)
+            self._normalize(self.beliefs)
+        self._reach_weights(self.reach, self.policy)
+        self.policy_avg[:] = self.policy
+        self.reach_avg[:] = self.reach
+        self.beliefs_avg[:] = self.beliefs
+        self.set_leaf_values()
+        self.expected_values()
+        self.values_avg[:] = self.values
+
+    # ---- leaves and backup ----
+    def set_leaf_values(self, beliefs=None):
+        beliefs = self.beliefs if beliefs is None else beliefs
+        if self.sd_idx.numel():
+            vals = showdown.showdown_values(self.sd_boards, beliefs[self.sd_idx], self.sd_potential,
+                                            self.scale[self.sd_idx])
+            self.values[self.sd_idx] = vals
+
+    def expected_values(self, policy=None, beliefs=None, leaf_values=None, values=None):
+        policy = self.policy if policy is None else policy
+        beliefs = self.beliefs if beliefs is None else beliefs
+        leaf_values = self.values if leaf_values is None else leaf_values
+        values = leaf_values if values is None else values
+        if leaf_values is values:
+            values.masked_fill_((~self.leaf)[:, None, None], 0.0)
+        else:
+            torch.where(self.leaf[:, None, None], leaf_values, torch.zeros_like(values), out=values)
+        N, top = self.N, self.top
+        actor = self.to_act[:top, None, None].expand(-1, -1, H)
+        actor_beliefs = beliefs[:top].gather(1, actor).squeeze(1)
+        dest = self._fan_out(actor_beliefs)
+        marginal = dest * policy[N:]
+        blocked = unblocked.unblocked_mass(marginal)
+        matchup = unblocked.unblocked_mass(dest)
+        opp_policy = torch.zeros_like(policy)
+        torch.where(matchup > 1e-5, blocked / matchup, torch.zeros_like(blocked), out=opp_policy[N:])
+        for d in range(self.depth - 1, -1, -1):
+            b, c = self.offs[d + 1], self.offs[d + 2]
+            rows = torch.arange(c - b)
+            pa = self.prev_actor[b:c]
+            weighted = values[b:c].clone()
+            weighted[rows, pa, :] *= policy[b:c]
+            weighted[rows, 1 - pa, :] *= opp_policy[b:c]
+            self._pull_back_sum(weighted, values, level=d)
+
+    # ---- one iteration (cfr_evaluator.py:1331-1381) ----
+    def instantaneous_regrets(self):
+        N = self.N
+        out = torch.zeros_like(self.policy)
+        actor = self.to_act[:, None, None].expand(-1, -1, H)
+        pa = self.prev_actor[N:, None, None].expand(-1, -1, H)
+        opp_reach = unblocked.unblocked_mass(self.beliefs.flip(dims=[1]))
+        weights = self._fan_out(opp_reach.gather(1, actor).squeeze(1))
+        expected = self._fan_out(self.values.gather(1, actor).squeeze(1))
+        achieved = self.values[N:].gather(1, pa).squeeze(1)
+        out[N:] = weights * (achieved - expected)
+        return out
+
+    def mixing_weights(self, t):
+        if self.cfr_type == "standard":
+            return t, 1
+        if self.cfr_type == "linear":
+            return t, 2
+        if self.cfr_type == "discounted":
+            return t ** self.gamma, (t + 1) ** self.gamma
+        if t > self.dcfr_delay:  # discounted_plus
+            return t - self.dcfr_delay, 2
+        return 0, 1
+
+    def update_average_policy(self, t):
+        if self.cfr_type in ("discounted", "discounted_plus") and t <= self.dcfr_delay:
+            self.policy_avg[:] = self.policy
+            return
+        if t == 0:
+            self.policy_avg[:] = self.policy
+            return
+        N, top = self.N, self.top
+        old, new = self.mixing_weights(t)
+        actor = self.to_act[:top, None, None].expand(-1, -1, H)
+        r_new = self.reach[:top].gather(1, actor).squeeze(1)
+        r_old = self.reach_avg[:top].gather(1, actor).squeeze(1)
+        r_old *= old
+        r_new *= new
+        r_new_c = self._fan_out(r_new)
+        r_old_c = self._fan_out(r_old)
+        numer = r_old_c * self.policy_avg[N:] + r_new_c * self.policy[N:]
+        denom = r_old_c + r_new_c
+        plain = (old * self.policy_avg[N:] + new * self.policy[N:]) / (old + new)
+        torch.where(denom > 1e-5, numer / denom, plain, out=self.policy_avg[N:])
+        sums = torch.zeros(top, H)
+        self._pull_back_sum(self.policy_avg, sums)
+        pd = self._fan_out(sums)
+        torch.where(pd > 1e-5, self.policy_avg[N:] / pd, self.policy_avg[N:], out=self.policy_avg[N:])
+        self.policy_avg[:N] = 0.0
+
+    def update_policy(self, t):
+        N = self.N
+        pos = self.regrets.clamp(min=0.0)
+        sums = torch.zeros_like(self.policy)
+        self._pull_back_sum(pos, sums)
+        denom = self._fan_out(sums)
+        torch.where(denom > 1e-8, pos[N:] / denom.clamp(min=1e-8), self.uniform[N:], out=self.policy[N:])
+        self._reach_weights(self.reach, self.policy)
+        self._propagate_beliefs(self.beliefs, self.reach)
+        self.update_average_policy(t)
+        self._reach_weights(self.reach_avg, self.policy_avg)
+        self._propagate_beliefs(self.beliefs_avg, self.reach_avg)
+
+    def iteration(self, t):
+        inst = self.instantaneous_regrets()
+        if self.cfr_type == "linear":
+            inst.masked_fill_(self.prev_actor[:, None] == t % 2, 0.0)
+        elif self.cfr_type in ("discounted", "discounted_plus"):
+            pos = self.regrets > 0
+            num = torch.where(pos, t ** self.alpha, t ** self.beta)
+            den = torch.where(pos, t ** self.alpha + 1, t ** self.beta + 1)
+            self.regrets *= num
+            self.regrets /= den
+            self.weight_sums *= num
+            self.weight_sums /= den
+        self.weight_sums += 1
+        self.regrets += inst
+        if self.cfr_plus:
+            self.regrets.clamp_(min=0)
+        self.update_policy(t)
+        self.set_leaf_values()
+        self.expected_values()
+
+    def finalize(self):
+        """update_average_values_final (cfr_evaluator.py:1276-1292), no zero-sum shift."""
+        self.set_leaf_values(beliefs=self.beliefs_avg)
+        self.expected_values(self.policy_avg, self.beliefs_avg, self.values, self.values_avg)
+
+    def solve(self):
+        self.initialize()
+        for t in range(self.iterations):
+            self.iteration(t)
+        self.finalize()
+        return self
+
+    # ---- local exploitability of the average policy (cfr_evaluator.py:603-764) ----
+    def _best_response(self, policy, beliefs, base_values, deviator):
+        top, A = self.top, self.A
+        vbr = torch.where(self.leaf[:, None, None], base_values, torch.zeros(()))
+        minv = torch.finfo(torch.float32).min
+        pol_src = self._pull_back(policy)
+        actor_all = self.to_act[:, None, None].expand(-1, -1, H)
+        actor_beliefs = beliefs.gather(1, actor_all).squeeze(1)[:top]
+        matchup = unblocked.unblocked_mass(actor_beliefs)
+        pol_blocked = unblocked.unblocked_mass(pol_src * actor_beliefs[:, None, :])
+        opp_pol = torch.where(matchup[:, None, :] > 1e-5, pol_blocked / matchup[:, None, :], torch.zeros(()))
+        child_mask = pol_src.new_zeros((top, A), dtype=torch.bool)
+        child_mask[self.parent[self.N:], self.action[self.N:]] = True
+        for d in range(self.depth - 1, -1, -1):
+            a, b = self.offs[d], self.offs[d + 1]
+            rows = torch.arange(b - a)
+            actor = self.to_act[a:b]
+            dev = deviator[a:b]
+            vsrc = self._pull_back(vbr, level=d)  # [K,A,2,H]
+            ai = actor[:, None, None, None].expand(-1, A, 1, H)
+            av = vsrc.gather(2, ai).squeeze(2)
+            ov = vsrc.gather(2, 1 - ai).squeeze(2)
+            best = av.masked_fill(~child_mask[a:b][:, :, None], minv).argmax(dim=1)
+            best_v = av.gather(1, best[:, None, :]).squeeze(1)
+            db = actor_beliefs[a:b]
+            mass = torch.zeros(b - a, A, H)
+            mass.scatter_add_(1, best[:, None, :], db[:, None, :])
+            mb = unblocked.unblocked_mass(mass)
+            dm = matchup[a:b][:, None, :]
+            p_dev = torch.where(dm > 1e-5, mb / dm, torch.zeros(()))
+            v_opp = (p_dev * ov).sum(dim=1)
+            is_dev = (dev == actor)[:, None]
+            actor_values = torch.where(is_dev, best_v, (av * pol_src[a:b]).sum(dim=1))
+            opp_values = torch.where(is_dev, v_opp, (ov * opp_pol[a:b]).sum(dim=1))
+            vbr[rows + a, actor] = actor_values
+            vbr[rows + a, 1 - actor] = opp_values
+            torch.where(self.leaf[a:b, None, None], base_values[a:b], vbr[a:b], out=vbr[a:b])
+        return vbr
+
+    def exploitability(self):
+        N = self.N
+        leaf_values = self.values_avg.clamp(-1.0, 1.0)
+        base = torch.zeros_like(leaf_values)
+        self.expected_values(self.policy_avg, self.beliefs_avg, leaf_values, base)
+        gains, br_vals = [], []
+        for player in range(2):
+            dev = torch.full((self.M,), player, dtype=torch.long)
+            br = self._best_response(self.policy_avg, self.beliefs_avg, leaf_values, dev)
+            rb = self.beliefs_avg[:N, player]
+            gains.append(((br[:N, player] - base[:N, player]) * rb).sum(dim=-1))
+            br_vals.append((br[:N, player] * rb).sum(dim=-1))
+        total = gains[0] + gains[1]
+        return total, torch.stack(br_vals, dim=-1)

@@ -1,0 +1,220 @@
+"""Tree and CFR sections of the golden-vector generator (runs the upstream evaluator).
+
+Imported by make_golden.py.  River subgames are set up the way the upstream tests do it
+(tests/test_rebel_cfr_evaluator.py:1185-1217): force the deck, check down to the river,
+then overwrite pot / stacks / starting stacks / scale.
+"""
+from __future__ import annotations
+
+import os
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+SB, BB = 1, 2
+BET_BINS = [0.5, 1.0]
+
+
+def save(name: str, **arrays) -> None:
+    path = os.path.join(HERE, name)
+    np.savez_compressed(path, **arrays)
+    print(f"wrote {path} ({os.path.getsize(path) / 1024:.1f} KiB)")
+
+
+class ZeroModel:
+    """Leaf/policy model stand-in: zero logits (uniform initial policy), zero values."""
+
+    enforce_zero_sum = False
+    hidden_dim = 1
+
+    def __init__(self, num_actions: int):
+        self.num_actions = num_actions
+
+    def eval(self):
+        pass
+
+    def create_feature_encoder(self, env, device=None, dtype=None):
+        from p2.models.mlp.rebel_feature_encoder import RebelFeatureEncoder
+
+        return RebelFeatureEncoder(env=env, device=device, dtype=dtype)
+
+    def __call__(self, features, include_policy=True, **kw):
+        from p2.models.model_output import ModelOutput
+
+        n = len(features)
+        return ModelOutput(policy_logits=torch.zeros(n, 1326, self.num_actions), value=torch.zeros(n),
+                           hand_values=torch.zeros(n, 2, 1326))
+
+
+def install_raise_cap(cap):
+    """Adds a per-street cap on bets/raises/all-ins to the upstream environment by
+    wrapping its methods (the upstream code has no such option).  cap=None removes it."""
+    from p2.env.hunl_tensor_env import HUNLTensorEnv as Env
+
+    if not hasattr(Env, "_orig"):
+        Env._orig = dict(init=Env.__init__, copy=Env.copy_state_from, rep=Env.repeat_interleave,
+                         step=Env.step_bins, legal=Env.legal_bins_amounts_and_mask)
+    o = Env._orig
+
+    def init(self, *a, **k):
+        o["init"](self, *a, **k)
+        self.raises = torch.zeros(self.N, dtype=torch.long)
+
+    def copy(self, src_env, src_select, dest_select, copy_deck=True):
+        o["copy"](self, src_env, src_select, dest_select, copy_deck)
+        self.raises[dest_select] = src_env.raises[src_select]
+
+    def rep(self, repeats, output_size):
+        dst = o["rep"](self, repeats, output_size)
+        dst.raises[:] = self.raises.repeat_interleave(repeats, dim=0, output_size=output_size)
+        return dst
+
+    def step(self, bin_indices, *a, **k):
+        out = o["step"](self, bin_indices, *a, **k)
+        self.raises += (bin_indices >= 2).long()
+        self.raises[self.actions_this_round == 0] = 0
+        return out
+
+    def legal(self, bet_bins=None):
+        amounts, mask = o["legal"](self, bet_bins)
+        if Env._cap is not None:
+            mask[:, 2:] &= (self.raises < Env._cap)[:, None]
+        return amounts, mask
+
+    Env._cap = cap
+    Env.__init__, Env.copy_state_from, Env.repeat_interleave = init, copy, rep
+    Env.step_bins, Env.legal_bins_amounts_and_mask = step, legal
+
+
+def river_env(boards: torch.Tensor, pot: torch.Tensor, stack: torch.Tensor):
+    from p2.env.hunl_tensor_env import HUNLTensorEnv
+
+    n = boards.shape[0]
+    env = HUNLTensorEnv(num_envs=n, starting_stack=1000, sb=SB, bb=BB, default_bet_bins=BET_BINS,
+                        device=torch.device("cpu"), rng=torch.Generator().manual_seed(0))
+    decks = []
+    for b in boards.tolist():
+        unused = [c for c in range(52) if c not in b]
+        decks.append(unused[:4] + b)
+    env.reset(force_deck=torch.tensor(decks), force_button=torch.zeros(n, dtype=torch.long))
+    for _ in range(6):
+        env.step_bins(torch.ones(n, dtype=torch.long))
+    assert (env.street == 3).all() and (env.actions_this_round == 0).all()
+    env.pot[:] = pot
+    env.stacks[:] = stack[:, None]
+    env.starting_stacks[:] = (stack + pot // 2)[:, None]
+    env.scale[:] = (stack + pot // 2).float()
+    if hasattr(env, "raises"):
+        env.raises[:] = 0
+    return env
+
+
+def make_evaluator(n, iterations, depth=8):
+    from p2.core.structured_config import CFRType, Config
+    from p2.search.sparse_cfr_evaluator import SparseCFREvaluator
+
+    cfg = Config()
+    cfg.device = "cpu"
+    cfg.seed = 0
+    cfg.num_envs = n
+    cfg.env.bet_bins = BET_BINS
+    cfg.env.sb, cfg.env.bb = SB, BB
+    cfg.search.depth = depth
+    cfg.search.iterations = iterations
+    cfg.search.warm_start_iterations = 0
+    cfg.search.cfr_type = CFRType.discounted
+    cfg.search.cfr_plus = False
+    cfg.search.cfr_avg = False
+    cfg.search.dcfr_alpha, cfg.search.dcfr_beta, cfg.search.dcfr_gamma = 1.5, 0.0, 2.0
+    cfg.search.dcfr_plus_delay = 0
+    cfg.search.value_targets_from_final_policy = True
+    ev = SparseCFREvaluator(ZeroModel(len(BET_BINS) + 3), torch.device("cpu"), cfg,
+                            generator=torch.Generator().manual_seed(0))
+    ev.sample_leaves = lambda training_mode: None
+    return ev
+
+
+def tree_arrays(ev) -> dict:
+    fold = (ev.action_from_parent == 0) & ev.env.done
+    potential = ev.env.stacks + ev.env.pot[:, None] - ev.env.starting_stacks
+    return dict(
+        depth_offsets=np.asarray(ev.depth_offsets, dtype=np.int64),
+        parent_index=ev.parent_index.numpy(), action_from_parent=ev.action_from_parent.numpy(),
+        to_act=ev.env.to_act.numpy(), legal_mask=ev.legal_mask.numpy(), leaf_mask=ev.leaf_mask.numpy(),
+        child_count=ev.child_count.numpy(), child_offsets=ev.child_offsets.numpy(), done=ev.env.done.numpy(),
+        street=ev.env.street.numpy(), pot=ev.env.pot.numpy(), stacks=ev.env.stacks.numpy(),
+        fold_value=torch.where(fold, ev.latest_values[:, 0, 0], torch.zeros(())).numpy(),
+        showdown_potential=potential.numpy(), scale=ev.env.scale.numpy(), prev_actor=ev.prev_actor.numpy(),
+    )
+
+
+def seeded_inputs(seed, n, pot_range=None, stack_range=None):
+    import make_golden
+
+    g = torch.Generator().manual_seed(seed)
+    boards = torch.stack([torch.randperm(52, generator=g)[:5] for _ in range(n)])
+    ranges = make_golden.dirichlet_ranges(boards, g)
+    if pot_range is None:
+        pot = torch.full((n,), 100, dtype=torch.long)
+        stack = torch.full((n,), 400, dtype=torch.long)
+    else:
+        pot = torch.randint(pot_range[0], pot_range[1] + 1, (n,), generator=g)
+        stack = torch.randint(stack_range[0], stack_range[1] + 1, (n,), generator=g)
+    return boards, ranges, pot, stack
+
+
+def gen_tree() -> None:
+    """Tree indices and legal masks for a spread of pot/stack ratios, capped and uncapped."""
+    pots = torch.tensor([100, 20, 200, 37, 150, 20, 199, 64, 90, 120])
+    stacks = torch.tensor([400, 1000, 100, 333, 75, 100, 1000, 32, 45, 60])
+    g = torch.Generator().manual_seed(5)
+    boards = torch.stack([torch.randperm(52, generator=g)[:5] for _ in range(len(pots))])
+    out = {}
+    for tag, cap, depth in (("cap2", 2, 8), ("nocap", None, 5)):
+        install_raise_cap(cap)
+        ev = make_evaluator(len(pots), 1, depth=depth)
+        ev.initialize_subgame(river_env(boards, pots, stacks), torch.arange(len(pots)), None)
+        for k, v in tree_arrays(ev).items():
+            out[f"{tag}_{k}"] = v
+        out[f"{tag}_max_depth"] = np.int64(depth)
+        print(tag, "nodes", ev.total_nodes, "depth", ev.tree_depth)
+    install_raise_cap(None)
+    save("tree.npz", pots=pots.numpy(), stacks=stacks.numpy(), **out)
+
+
+def run_cfr(tag, boards, ranges, pot, stack, iterations, cap, depth=8, keep_all=False):
+    install_raise_cap(cap)
+    n = boards.shape[0]
+    ev = make_evaluator(n, iterations, depth=depth)
+    ev.initialize_subgame(river_env(boards, pot, stack), torch.arange(n), ranges)
+    ev.evaluate_cfr()
+    ex = ev._compute_exploitability()
+    install_raise_cap(None)
+    print(tag, "nodes", ev.total_nodes, "exploitability", ex.local_exploitability.tolist()[:4])
+    out = dict(
+        boards=boards.to(torch.int16).numpy(), ranges=ranges.numpy(), pot=pot.numpy(), stack=stack.numpy(),
+        iterations=np.int64(iterations), cap=np.int64(-1 if cap is None else cap), max_depth=np.int64(depth),
+        total_nodes=np.int64(ev.total_nodes),
+        policy_avg=ev.policy_probs_avg.numpy(), root_values=ev.values_avg[:n].numpy(),
+        exploitability=ex.local_exploitability.numpy(), br_values=ex.local_best_response_values.numpy(),
+    )
+    if keep_all:
+        out.update(regrets=ev.cumulative_regrets.numpy(), weight_sums=ev.regret_weight_sums.numpy(),
+                   policy=ev.policy_probs.numpy(), values_avg=ev.values_avg.numpy(),
+                   latest_values=ev.latest_values.numpy(), beliefs=ev.beliefs.numpy())
+    save(f"cfr_{tag}.npz", **out)
+
+
+def gen_cfr() -> None:
+    # config 0: one seeded river subgame, pot 100 / stack 400, DCFR(1.5, 0, 2), 256 iterations
+    b, r, p, s = seeded_inputs(0, 1)
+    run_cfr("single_cap2_t256", b, r, p, s, 256, cap=2)
+    run_cfr("single_cap2_t8", b, r, p, s, 8, cap=2, keep_all=True)
+    run_cfr("single_nocap_t32", b, r, p, s, 32, cap=None)
+    # ragged batch: pots in [20,200], stacks in [100,1000]
+    b, r, p, s = seeded_inputs(2, 4, (20, 200), (100, 1000))
+    run_cfr("batch_cap2_t24", b, r, p, s, 24, cap=2)
+
+
+SECTIONS = {"tree": gen_tree, "cfr": gen_cfr}

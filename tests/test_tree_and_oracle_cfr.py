@@ -1,0 +1,64 @@
+"""Host tree builder and the CFR oracle against arrays produced by the upstream evaluator."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import cfr as ocfr
+from poker2_b200 import tree as ptree
+
+BET_BINS = [0.5, 1.0]
+
+
+def _build(pot, stack, cap, depth):
+    roots = ptree.root_states(pot, stack, min_raise=2)
+    return ptree.build_trees(roots, BET_BINS, depth, bb=2, max_raises=cap)
+
+
+@pytest.mark.parametrize("tag,cap", [("cap2", 2), ("nocap", None)])
+def test_tree_indices_and_legal_masks_bit_exact(golden_dir, tag, cap):
+    z = np.load(os.path.join(golden_dir, "tree.npz"))
+    t = _build(z["pots"], z["stacks"], cap, int(z[f"{tag}_max_depth"]))
+    assert t.depth_offsets == z[f"{tag}_depth_offsets"].tolist()
+    for name, mine in [
+        ("parent_index", t.parent_index), ("action_from_parent", t.action_from_parent), ("to_act", t.state.to_act),
+        ("legal_mask", t.legal_mask), ("leaf_mask", t.leaf_mask), ("child_count", t.child_count),
+        ("child_offsets", t.child_offsets), ("done", t.state.done), ("street", t.state.street),
+        ("pot", t.state.pot), ("stacks", t.state.stacks), ("showdown_potential", t.showdown_potential),
+        ("scale", t.state.scale), ("prev_actor", t.prev_actor), ("fold_value", t.fold_value),
+    ]:
+        assert np.array_equal(mine, z[f"{tag}_{name}"]), name
+
+
+def _oracle_from_golden(z):
+    cap = int(z["cap"])
+    t = _build(z["pot"], z["stack"], None if cap < 0 else cap, int(z["max_depth"]))
+    assert t.total_nodes == int(z["total_nodes"])
+    o = ocfr.SubgameOracle(t.oracle_dict(z["boards"].astype(np.int64)), torch.from_numpy(z["ranges"]),
+                           iterations=int(z["iterations"]))
+    return o.solve()
+
+
+def test_cfr_oracle_bit_exact_short_run(golden_dir):
+    z = np.load(os.path.join(golden_dir, "cfr_single_cap2_t8.npz"))
+    o = _oracle_from_golden(z)
+    assert torch.equal(o.policy, torch.from_numpy(z["policy"]))
+    assert torch.equal(o.regrets, torch.from_numpy(z["regrets"]))
+    assert torch.equal(o.weight_sums, torch.from_numpy(z["weight_sums"]))
+    assert torch.equal(o.beliefs, torch.from_numpy(z["beliefs"]))
+    assert torch.equal(o.policy_avg, torch.from_numpy(z["policy_avg"]))
+    assert torch.equal(o.values_avg, torch.from_numpy(z["values_avg"]))
+    ex, br = o.exploitability()
+    assert torch.equal(ex, torch.from_numpy(z["exploitability"]))
+    assert torch.equal(br, torch.from_numpy(z["br_values"]))
+
+
+@pytest.mark.parametrize("name", ["cfr_single_nocap_t32", "cfr_batch_cap2_t24"])
+def test_cfr_oracle_bit_exact_other_trees(golden_dir, name):
+    z = np.load(os.path.join(golden_dir, name + ".npz"))
+    o = _oracle_from_golden(z)
+    assert torch.equal(o.policy_avg, torch.from_numpy(z["policy_avg"]))
+    assert torch.equal(o.values_avg[: o.N], torch.from_numpy(z["root_values"]))
+    ex, _ = o.exploitability()
+    assert torch.equal(ex, torch.from_numpy(z["exploitability"]))
