@@ -58,6 +58,38 @@ int p2b_showdown_values(const unsigned char* tables, const int32_t* table_of_row
                         const int64_t* potential, const float* scale, float* values,
                         int64_t value_row_stride, int64_t rows, void* stream);
 
+/* ---- fused subgame CFR (src/p2/search/cfr_evaluator.py:1497-1528 evaluate_cfr with
+ * cfr_iteration :1331-1381, on the ragged tree of sparse_cfr_evaluator.py:141-306) ----
+ * One persistent kernel runs the start pass, `iterations` DCFR iterations and the final
+ * average-policy evaluation for `num_subgames` independent subgames whose leaves are all
+ * terminal (fold or showdown).  Rows are 1328 floats (1326 combos + 2 padding floats) so
+ * that every row is 16-byte aligned; all row arrays must be 16-byte aligned.
+ *
+ *  subgames   [num_subgames] 32-byte records {int32 node_begin, n_nodes, n_internal,
+ *             table_index; float scale, allowed_prob; uint64 board_mask}
+ *  nodes      [rows] 16-byte records {uint8 parent, first_child, n_children, to_act, kind
+ *             (0 internal, 1 fold leaf, 2 showdown leaf, 3 other leaf), action, depth,
+ *             internal_idx; float v0, v1}, breadth-first per subgame, local indices
+ *  tables     showdown tables from p2b_rank_hands, indexed by table_index
+ *  root_beliefs [num_subgames,2,1328] input ranges
+ *  regrets, weight_sums (may be NULL), policy_avg, policy (may be NULL): [rows,1328] out
+ *  root_values [num_subgames,2,1328] out; values_avg, beliefs_avg [rows,2,1328] out (may be NULL)
+ *  scratch    p2b_cfr_scratch_floats(max_internal, num_blocks) floats of work space
+ *  scalars    [iterations] 32-byte records {float t^alpha, t^alpha+1, t^beta, t^beta+1,
+ *             mix_old, mix_new, fl(mix_old+mix_new); int32 do_mix}
+ *  init_depth depth of the deepest tree of the batch (the upstream start pass re-normalises
+ *             every belief row once per level of the batch-wide tree)
+ *  work_counter one int32 (zeroed by the call)
+ *  num_blocks 0 = one block per SM. */
+int p2b_cfr_solve(const void* subgames, const void* nodes, int32_t num_subgames, int32_t max_children,
+                  int32_t max_internal, const unsigned char* tables, const float* root_beliefs,
+                  float* regrets, float* weight_sums, float* policy_avg, float* policy,
+                  float* root_values, float* values_avg, float* beliefs_avg, float* scratch,
+                  int64_t scratch_floats, const void* scalars, int32_t iterations, int32_t cfr_plus,
+                  int32_t init_depth, int32_t* work_counter, int32_t num_blocks, void* stream);
+int64_t p2b_cfr_scratch_floats(int32_t max_internal, int32_t num_blocks);
+int p2b_cfr_default_blocks(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -29,7 +29,11 @@ _SIGNATURES = {
     "p2b_compare7_planes": [_vp, _i64, _vp, _vp],
     "p2b_rank_hands": [_vp, _i64, _vp, _vp, _vp, _vp],
     "p2b_showdown_values": [_vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _i64, _vp],
+    "p2b_cfr_solve": [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp,
+                      _i32, _i32, _i32, _vp, _i32, _vp],
 }
+# functions whose return value is a quantity, not a status code
+_VALUE_FUNCS = {"p2b_cfr_scratch_floats": ([_i32, _i32], _i64), "p2b_cfr_default_blocks": ([], _i32)}
 
 
 def library_available() -> bool:
@@ -53,12 +57,16 @@ def lib():
             fn = getattr(handle, name)
             fn.argtypes = argtypes
             fn.restype = ctypes.c_int
+        for name, (argtypes, restype) in _VALUE_FUNCS.items():
+            fn = getattr(handle, name)
+            fn.argtypes = argtypes
+            fn.restype = restype
         _lib = handle
     return _lib
 
 
 def exported_symbols():
-    return ["p2b_last_error", "p2b_version", *_SIGNATURES.keys()]
+    return ["p2b_last_error", "p2b_version", *_SIGNATURES.keys(), *_VALUE_FUNCS.keys()]
 
 
 def call(name: str, *args) -> None:

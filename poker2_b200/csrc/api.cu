@@ -1,6 +1,7 @@
 // extern "C" surface of the library (declared in include/poker2_b200.h).
 #include "../../include/poker2_b200.h"
 
+#include "cfr.cuh"
 #include "common.cuh"
 
 namespace p2b {
@@ -63,6 +64,58 @@ int p2b_showdown_values(const unsigned char* tables, const int32_t* table_of_row
     return launch_showdown_eval(tables, table_of_row, beliefs, belief_row_stride,
                                 reinterpret_cast<const long long*>(potential), scale, values, value_row_stride, rows,
                                 (cudaStream_t)stream);
+}
+
+int p2b_cfr_default_blocks(void) { return cfr_default_blocks(); }
+
+int64_t p2b_cfr_scratch_floats(int32_t max_internal, int32_t num_blocks) {
+    if (num_blocks <= 0) num_blocks = cfr_default_blocks();
+    return cfr_scratch_floats(max_internal) * num_blocks;
+}
+
+int p2b_cfr_solve(const void* subgames, const void* nodes, int32_t num_subgames, int32_t max_children,
+                  int32_t max_internal, const unsigned char* tables, const float* root_beliefs, float* regrets,
+                  float* weight_sums, float* policy_avg, float* policy, float* root_values, float* values_avg,
+                  float* beliefs_avg, float* scratch, int64_t scratch_floats, const void* scalars, int32_t iterations,
+                  int32_t cfr_plus, int32_t init_depth, int32_t* work_counter, int32_t num_blocks, void* stream) {
+    P2B_REQUIRE(num_subgames >= 0 && iterations >= 0, "negative count");
+    if (num_subgames == 0) return P2B_OK;
+    P2B_REQUIRE(subgames && nodes && root_beliefs && regrets && policy_avg && root_values && scratch && work_counter,
+                "null pointer");
+    P2B_REQUIRE(iterations == 0 || scalars, "null scalars");
+    P2B_REQUIRE(max_internal >= 1, "max_internal must be positive");
+    if (num_blocks <= 0) num_blocks = cfr_default_blocks();
+    if (num_blocks > num_subgames) num_blocks = num_subgames;
+    P2B_REQUIRE(scratch_floats >= cfr_scratch_floats(max_internal) * num_blocks, "scratch too small");
+    const uintptr_t align = reinterpret_cast<uintptr_t>(subgames) | reinterpret_cast<uintptr_t>(nodes) |
+                            reinterpret_cast<uintptr_t>(tables) | reinterpret_cast<uintptr_t>(root_beliefs) |
+                            reinterpret_cast<uintptr_t>(regrets) | reinterpret_cast<uintptr_t>(weight_sums) |
+                            reinterpret_cast<uintptr_t>(policy_avg) | reinterpret_cast<uintptr_t>(policy) |
+                            reinterpret_cast<uintptr_t>(root_values) | reinterpret_cast<uintptr_t>(values_avg) |
+                            reinterpret_cast<uintptr_t>(beliefs_avg) | reinterpret_cast<uintptr_t>(scratch);
+    P2B_REQUIRE((align & 15) == 0, "all arrays must be 16-byte aligned");
+    CfrParams p{};
+    p.subgames = static_cast<const SubgameRec*>(subgames);
+    p.nodes = static_cast<const NodeRec*>(nodes);
+    p.num_subgames = num_subgames;
+    p.tables = tables;
+    p.root_beliefs = root_beliefs;
+    p.regrets = regrets;
+    p.weight_sums = weight_sums;
+    p.policy_avg = policy_avg;
+    p.policy = policy;
+    p.root_values = root_values;
+    p.values_avg = values_avg;
+    p.beliefs_avg = beliefs_avg;
+    p.scratch = scratch;
+    p.scratch_stride = cfr_scratch_floats(max_internal);
+    p.max_internal = max_internal;
+    p.scalars = static_cast<const IterScalars*>(scalars);
+    p.iterations = iterations;
+    p.cfr_plus = cfr_plus;
+    p.init_depth = init_depth;
+    p.work_counter = work_counter;
+    return launch_cfr_solve(p, num_blocks, max_children, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -1,0 +1,83 @@
+// Data structures of the fused subgame-CFR kernel (shared by cfr.cu and api.cu).
+#pragma once
+
+#include "common.cuh"
+
+namespace p2b {
+
+enum NodeKind : uint8_t { kInternal = 0, kFoldLeaf = 1, kShowdownLeaf = 2, kModelLeaf = 3 };
+
+// One public-tree node, 16 bytes.  Nodes of a subgame are stored breadth-first (parents
+// before children, children of a node contiguous in action order); indices are local to
+// the subgame.
+struct NodeRec {
+    uint8_t parent;
+    uint8_t first_child;
+    uint8_t n_children;
+    uint8_t to_act;
+    uint8_t kind;
+    uint8_t action;
+    uint8_t depth;
+    uint8_t internal_idx;  // rank of this node among the internal nodes of its subgame
+    float v0;              // fold leaf: value of player 0; showdown leaf: chips player 0 can win
+    float v1;              // showdown leaf: chips player 1 can win
+};
+static_assert(sizeof(NodeRec) == 16, "NodeRec must be 16 bytes");
+
+struct SubgameRec {  // 32 bytes
+    int32_t node_begin;   // first row of the subgame in the [rows][HPAD] state arrays
+    int32_t n_nodes;
+    int32_t n_internal;
+    int32_t table_index;  // board-table blob of this subgame, -1 if it has no showdown leaf
+    float scale;
+    float allowed_prob;   // 1 / (number of combos not blocked by the board)
+    unsigned long long board_mask;
+};
+static_assert(sizeof(SubgameRec) == 32, "SubgameRec must be 32 bytes");
+
+// Per-iteration scalars, computed on the host in fp64 and rounded to fp32 the way the
+// upstream Python code does (p2/search/cfr_evaluator.py:1346-1360, 285-303).
+struct IterScalars {  // 32 bytes
+    float num_pos, den_pos;  // t^alpha, t^alpha + 1      (regret discount, positive regrets)
+    float num_neg, den_neg;  // t^beta,  t^beta + 1       (non-positive regrets)
+    float mix_old, mix_new, mix_total;  // average-policy mixing weights and fl(old+new)
+    int32_t do_mix;          // 0: average policy := current policy at this iteration
+};
+
+constexpr int kCfrThreads = 352;  // 332 threads x 4 hands cover the 1328-float padded row
+constexpr int kCfrMaxNodes = 160;
+constexpr int kCfrMaxChildren = 6;
+
+struct CfrParams {
+    const SubgameRec* subgames;
+    const NodeRec* nodes;        // indexed by node_begin + local index
+    int32_t num_subgames;
+    const unsigned char* tables; // [*, kTabBytes] board tables
+    const ComboTable* combos;    // filled in by the launcher
+    const float* root_beliefs;   // [B][2][HPAD] input ranges (read-only)
+    float* regrets;              // [rows][HPAD] cumulative regrets (out)
+    float* weight_sums;          // [rows][HPAD] regret weight sums (out, may be null)
+    float* policy_avg;           // [rows][HPAD] average policy (out)
+    float* policy;               // [rows][HPAD] last current policy (out, may be null)
+    float* root_values;          // [B][2][HPAD] values of the final average policy at the roots (out)
+    float* values_avg;           // [rows][2][HPAD] the same for every node (out, may be null)
+    float* beliefs_avg;          // [rows][2][HPAD] beliefs under the average policy (out, may be null)
+    float* scratch;              // per-block work rows
+    long long scratch_stride;    // floats per block
+    int32_t max_internal;        // largest n_internal over the batch
+    const IterScalars* scalars;  // [iterations]
+    int32_t iterations;
+    int32_t cfr_plus;
+    int32_t init_depth;          // depth of the deepest tree of the batch the subgames were built in
+    int32_t* work_counter;       // dynamic subgame queue (zeroed by the launcher)
+};
+
+// floats of scratch one block needs: per internal node reach[2], average reach[2], values[2]
+__host__ __device__ inline long long cfr_scratch_floats(int max_internal) {
+    return (long long)max_internal * 6 * P2B_HPAD;
+}
+
+int launch_cfr_solve(const CfrParams& p, int num_blocks, int max_children, cudaStream_t stream);
+int cfr_default_blocks();
+
+}  // namespace p2b

@@ -1,0 +1,238 @@
+"""Batched subgame solving on the GPU: host-side preparation and the call into the fused
+CFR kernel (`p2b_cfr_solve`).
+
+`solve_subgames` does, for a batch of independent river subgames, what the upstream
+`initialize_subgame` + `evaluate_cfr` do (p2/search/cfr_evaluator.py:770-828, 1497-1528,
+with `value_targets_from_final_policy`), and returns the arrays `training_data` reads
+(:1384-1495): average policy per node, values of the average policy at the roots, plus the
+cumulative regrets and weight sums.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from . import _lib, tree as ptree
+from .showdown import BoardTables
+
+HPAD = 1328
+NUM_HANDS = 1326
+MAX_NODES = 160
+MAX_CHILDREN = 6
+
+NODE_DTYPE = np.dtype([("parent", "u1"), ("first_child", "u1"), ("n_children", "u1"), ("to_act", "u1"),
+                       ("kind", "u1"), ("action", "u1"), ("depth", "u1"), ("internal_idx", "u1"),
+                       ("v0", "<f4"), ("v1", "<f4")])
+SUBGAME_DTYPE = np.dtype([("node_begin", "<i4"), ("n_nodes", "<i4"), ("n_internal", "<i4"), ("table_index", "<i4"),
+                          ("scale", "<f4"), ("allowed_prob", "<f4"), ("board_mask", "<u8")])
+SCALAR_DTYPE = np.dtype([("num_pos", "<f4"), ("den_pos", "<f4"), ("num_neg", "<f4"), ("den_neg", "<f4"),
+                         ("mix_old", "<f4"), ("mix_new", "<f4"), ("mix_total", "<f4"), ("do_mix", "<i4")])
+assert NODE_DTYPE.itemsize == 16 and SUBGAME_DTYPE.itemsize == 32 and SCALAR_DTYPE.itemsize == 32
+
+
+def iteration_scalars(iterations: int, *, cfr_type: str = "discounted", alpha: float = 1.5, beta: float = 0.0,
+                      gamma: float = 2.0, dcfr_delay: int = 0) -> np.ndarray:
+    """Per-iteration discount and mixing scalars, evaluated in Python floats and rounded to
+    fp32 exactly as the upstream loop does (cfr_evaluator.py:1346-1360, 285-303, 1197-1205).
+    t is 0-based: 0**0.0 == 1 and 0**1.5 == 0."""
+    out = np.zeros(iterations, dtype=SCALAR_DTYPE)
+    discounted = cfr_type in ("discounted", "discounted_plus")
+    for t in range(iterations):
+        if discounted:
+            ta, tb = float(t) ** alpha, float(t) ** beta
+            out[t]["num_pos"], out[t]["den_pos"] = ta, ta + 1
+            out[t]["num_neg"], out[t]["den_neg"] = tb, tb + 1
+        else:
+            out[t]["num_pos"] = out[t]["den_pos"] = out[t]["num_neg"] = out[t]["den_neg"] = 1.0
+        if cfr_type == "standard":
+            old, new = t, 1
+        elif cfr_type == "linear":
+            raise ValueError("linear CFR (alternating updates) is not supported by the fused kernel")
+        elif cfr_type == "discounted":
+            old, new = float(t) ** gamma, float(t + 1) ** gamma
+        elif cfr_type == "discounted_plus":
+            old, new = (t - dcfr_delay, 2) if t > dcfr_delay else (0, 1)
+        else:
+            raise ValueError(f"unknown cfr_type {cfr_type!r}")
+        out[t]["mix_old"], out[t]["mix_new"], out[t]["mix_total"] = old, new, old + new
+        out[t]["do_mix"] = 0 if (t == 0 or (discounted and t <= dcfr_delay)) else 1
+    return out
+
+
+@dataclass
+class DeviceTreeLayout:
+    """Subgame-major node order and the packed records the kernel reads."""
+
+    subgames: np.ndarray  # [B] SUBGAME_DTYPE
+    nodes: np.ndarray  # [rows] NODE_DTYPE
+    to_level_major: np.ndarray  # [rows] level-major (upstream) index of each row
+    from_level_major: np.ndarray  # [rows] row of each level-major node
+    max_internal: int
+    max_children: int
+    tree_depth: int  # depth of the deepest tree of the batch
+
+    @property
+    def rows(self) -> int:
+        return self.nodes.shape[0]
+
+
+def device_layout(trees: ptree.PublicTrees, boards: np.ndarray) -> DeviceTreeLayout:
+    M, B = trees.total_nodes, trees.num_roots
+    order = np.lexsort((np.arange(M), trees.root_of))  # by subgame, then upstream order (breadth-first)
+    pos = np.empty(M, dtype=np.int64)
+    pos[order] = np.arange(M)
+    n_nodes = np.bincount(trees.root_of, minlength=B)
+    node_begin = np.concatenate([[0], np.cumsum(n_nodes)])[:-1]
+    if n_nodes.max() > MAX_NODES:
+        raise ValueError(f"a subgame has {n_nodes.max()} nodes; the kernel supports up to {MAX_NODES}")
+    if trees.child_count.max() > MAX_CHILDREN:
+        raise ValueError(f"at most {MAX_CHILDREN} actions per node are supported")
+    local = pos - node_begin[trees.root_of]
+    st = trees.state
+    internal = trees.child_count > 0
+    fold = (trees.action_from_parent == 0) & st.done
+    showdown = (st.street == 4) & ~internal
+    kind = np.full(M, ptree.KIND_MODEL, dtype=np.uint8)
+    kind[showdown] = ptree.KIND_SHOWDOWN
+    kind[fold] = ptree.KIND_FOLD
+    kind[internal] = ptree.KIND_INTERNAL
+    rec = np.zeros(M, dtype=NODE_DTYPE)
+    parent_local = np.where(trees.parent_index >= 0, local[np.maximum(trees.parent_index, 0)], 0)
+    first_child = np.where(internal, local[np.minimum(trees.child_offsets, M - 1)], 0)
+    rec["parent"], rec["first_child"] = parent_local, first_child
+    rec["n_children"], rec["to_act"], rec["kind"] = trees.child_count, st.to_act, kind
+    rec["action"] = np.maximum(trees.action_from_parent, 0)
+    rec["depth"] = trees.depth_of
+    rec["v0"] = np.where(fold, trees.fold_value, trees.showdown_potential[:, 0].astype(np.float32))
+    rec["v1"] = trees.showdown_potential[:, 1].astype(np.float32)
+    rec = rec[order]
+    # rank among the internal nodes of the same subgame
+    int_sorted = internal[order].astype(np.int64)
+    csum = np.cumsum(int_sorted) - int_sorted
+    root_sorted = trees.root_of[order]
+    rec["internal_idx"] = csum - csum[node_begin[root_sorted]]
+    n_internal = np.bincount(trees.root_of, weights=internal, minlength=B).astype(np.int64)
+
+    boards = np.asarray(boards, dtype=np.int64)
+    sub = np.zeros(B, dtype=SUBGAME_DTYPE)
+    sub["node_begin"], sub["n_nodes"], sub["n_internal"] = node_begin, n_nodes, n_internal
+    has_sd = np.bincount(trees.root_of, weights=showdown, minlength=B) > 0
+    sub["table_index"] = np.where(has_sd, np.arange(B), -1)
+    sub["scale"] = st.scale[:B]
+    mask = np.zeros(B, dtype=np.uint64)
+    n_blocked_cards = np.zeros(B, dtype=np.int64)
+    for j in range(boards.shape[1]):
+        valid = boards[:, j] >= 0
+        mask[valid] |= np.uint64(1) << boards[valid, j].astype(np.uint64)
+        n_blocked_cards += valid
+    sub["board_mask"] = mask
+    n_allowed = (52 - n_blocked_cards) * (51 - n_blocked_cards) // 2
+    sub["allowed_prob"] = (np.float32(1.0) / np.maximum(n_allowed, 1).astype(np.float32)).astype(np.float32)
+    return DeviceTreeLayout(subgames=sub, nodes=rec, to_level_major=order, from_level_major=pos,
+                            max_internal=int(n_internal.max()), max_children=int(trees.child_count.max()),
+                            tree_depth=trees.tree_depth)
+
+
+def pad_rows(x: torch.Tensor) -> torch.Tensor:
+    """[..., 1326] -> [..., 1328] zero padded (rows of the kernel are 16-byte aligned)."""
+    out = x.new_zeros(*x.shape[:-1], HPAD)
+    out[..., :NUM_HANDS] = x
+    return out
+
+
+@dataclass
+class SolveResult:
+    """Arrays in the kernel's subgame-major row order, padded to 1328 columns.  Use
+    `level_major(x)` to obtain the upstream node order with 1326 columns."""
+
+    layout: DeviceTreeLayout
+    policy_avg: torch.Tensor  # [rows,1328]
+    regrets: torch.Tensor  # [rows,1328]
+    weight_sums: torch.Tensor | None
+    policy: torch.Tensor | None
+    root_values: torch.Tensor  # [B,2,1328]
+    values_avg: torch.Tensor | None  # [rows,2,1328]
+    beliefs_avg: torch.Tensor | None
+
+    def level_major(self, x: torch.Tensor) -> torch.Tensor:
+        idx = torch.from_numpy(self.layout.from_level_major).to(x.device)
+        return x.index_select(0, idx)[..., :NUM_HANDS]
+
+
+class SubgameSolver:
+    """Holds the device buffers of one batch shape and runs the fused kernel on them."""
+
+    def __init__(self, layout: DeviceTreeLayout, boards: torch.Tensor, device: torch.device, *,
+                 track_weight_sums: bool = True, keep_policy: bool = False, keep_node_values: bool = False,
+                 num_blocks: int = 0):
+        if device.type != "cuda":
+            raise ValueError("SubgameSolver requires a CUDA device.")
+        self.layout, self.device = layout, device
+        rows, B = layout.rows, layout.subgames.shape[0]
+        self.B = B
+        with torch.cuda.device(device):
+            blocks = num_blocks if num_blocks > 0 else int(_lib.lib().p2b_cfr_default_blocks())
+        self.num_blocks = min(blocks, B)
+        f32 = dict(device=device, dtype=torch.float32)
+        self.subgames = torch.from_numpy(layout.subgames.view(np.uint8).reshape(B, 32)).to(device)
+        self.nodes = torch.from_numpy(layout.nodes.view(np.uint8).reshape(rows, 16)).to(device)
+        self.tables = BoardTables(boards.to(device)) if (layout.subgames["table_index"] >= 0).any() else None
+        self.regrets = torch.empty(rows, HPAD, **f32)
+        self.policy_avg = torch.empty(rows, HPAD, **f32)
+        self.weight_sums = torch.empty(rows, HPAD, **f32) if track_weight_sums else None
+        self.policy = torch.zeros(rows, HPAD, **f32) if keep_policy else None
+        self.root_values = torch.empty(B, 2, HPAD, **f32)
+        self.values_avg = torch.zeros(rows, 2, HPAD, **f32) if keep_node_values else None
+        self.beliefs_avg = torch.zeros(rows, 2, HPAD, **f32) if keep_node_values else None
+        n_scratch = int(_lib.lib().p2b_cfr_scratch_floats(layout.max_internal, self.num_blocks))
+        self.scratch = torch.empty(n_scratch, **f32)
+        self.work_counter = torch.zeros(4, device=device, dtype=torch.int32)
+        self.launches = 0
+
+    def solve(self, root_beliefs: torch.Tensor, scalars: np.ndarray, *, cfr_plus: bool = False) -> SolveResult:
+        """root_beliefs: [B,2,1328] fp32 on the device (padded).  Enqueues one kernel."""
+        assert root_beliefs.shape == (self.B, 2, HPAD) and root_beliefs.dtype == torch.float32
+        assert root_beliefs.is_contiguous() and root_beliefs.device == self.device
+        iterations = int(scalars.shape[0])
+        sc = torch.from_numpy(scalars.view(np.uint8).reshape(max(iterations, 0), 32).copy()).to(self.device)
+        self._scalars = sc
+        p = _lib.ptr
+        with torch.cuda.device(self.device):
+            # rows of leaf-only bookkeeping (roots have no regrets) must not hold garbage
+            self.regrets.zero_()
+            self.policy_avg.zero_()
+            if self.weight_sums is not None:
+                self.weight_sums.zero_()
+            _lib.call(
+                "p2b_cfr_solve", p(self.subgames), p(self.nodes), self.B, self.layout.max_children,
+                self.layout.max_internal, p(self.tables.blob) if self.tables is not None else None, p(root_beliefs),
+                p(self.regrets), p(self.weight_sums), p(self.policy_avg), p(self.policy), p(self.root_values),
+                p(self.values_avg), p(self.beliefs_avg), p(self.scratch), self.scratch.numel(),
+                p(sc) if iterations else None, iterations, int(cfr_plus), self.layout.tree_depth, p(self.work_counter),
+                self.num_blocks,
+                _lib.stream_ptr(self.device))
+        self.launches += 1
+        return SolveResult(self.layout, self.policy_avg, self.regrets, self.weight_sums, self.policy,
+                           self.root_values, self.values_avg, self.beliefs_avg)
+
+
+def solve_subgames(boards, ranges, pot, stacks, *, iterations: int, bet_bins=(0.5, 1.0), max_depth: int = 8,
+                   max_raises=None, bb: int = 2, cfr_type: str = "discounted", alpha: float = 1.5, beta: float = 0.0,
+                   gamma: float = 2.0, dcfr_delay: int = 0, cfr_plus: bool = False, device=None,
+                   keep_policy: bool = False, keep_node_values: bool = False, track_weight_sums: bool = True):
+    """Solves a batch of river subgames: boards [B,5] card ids, ranges [B,2,1326] fp32,
+    pot [B] and stacks [B] or [B,2] in chips.  Returns (SolveResult, PublicTrees)."""
+    device = torch.device(device if device is not None else "cuda:0")
+    boards_np = np.asarray(boards.cpu() if torch.is_tensor(boards) else boards, dtype=np.int64)
+    pot_np = np.asarray(pot.cpu() if torch.is_tensor(pot) else pot, dtype=np.int64)
+    stacks_np = np.asarray(stacks.cpu() if torch.is_tensor(stacks) else stacks, dtype=np.int64)
+    roots = ptree.root_states(pot_np, stacks_np, min_raise=bb)
+    trees = ptree.build_trees(roots, list(bet_bins), max_depth, bb=bb, max_raises=max_raises)
+    layout = device_layout(trees, boards_np)
+    solver = SubgameSolver(layout, torch.from_numpy(boards_np), device, track_weight_sums=track_weight_sums,
+                           keep_policy=keep_policy, keep_node_values=keep_node_values)
+    rb = pad_rows(torch.as_tensor(ranges, dtype=torch.float32).to(device)).contiguous()
+    scal = iteration_scalars(iterations, cfr_type=cfr_type, alpha=alpha, beta=beta, gamma=gamma, dcfr_delay=dcfr_delay)
+    return solver.solve(rb, scal, cfr_plus=cfr_plus), trees
