@@ -156,6 +156,17 @@ class SolveResult:
     values_avg: torch.Tensor | None  # [rows,2,1328]
     beliefs_avg: torch.Tensor | None
 
+    def to_host(self, pinned: dict | None = None) -> dict:
+        """Copies the training targets (root values, average policy) to pinned host memory
+        and waits for the copy."""
+        pinned = {} if pinned is None else pinned
+        for name, src in (("root_values", self.root_values), ("policy_avg", self.policy_avg)):
+            if name not in pinned or pinned[name].shape != src.shape:
+                pinned[name] = torch.empty(src.shape, dtype=src.dtype, pin_memory=True)
+            pinned[name].copy_(src, non_blocking=True)
+        torch.cuda.current_stream(self.root_values.device).synchronize()
+        return pinned
+
     def level_major(self, x: torch.Tensor) -> torch.Tensor:
         idx = torch.from_numpy(self.layout.from_level_major).to(x.device)
         return x.index_select(0, idx)[..., :NUM_HANDS]
@@ -179,9 +190,11 @@ class SubgameSolver:
         self.subgames = torch.from_numpy(layout.subgames.view(np.uint8).reshape(B, 32)).to(device)
         self.nodes = torch.from_numpy(layout.nodes.view(np.uint8).reshape(rows, 16)).to(device)
         self.tables = BoardTables(boards.to(device)) if (layout.subgames["table_index"] >= 0).any() else None
-        self.regrets = torch.empty(rows, HPAD, **f32)
-        self.policy_avg = torch.empty(rows, HPAD, **f32)
-        self.weight_sums = torch.empty(rows, HPAD, **f32) if track_weight_sums else None
+        # zeroed once: the kernel rewrites every non-root row on each solve and never touches
+        # the root rows (a root is reached by no action)
+        self.regrets = torch.zeros(rows, HPAD, **f32)
+        self.policy_avg = torch.zeros(rows, HPAD, **f32)
+        self.weight_sums = torch.zeros(rows, HPAD, **f32) if track_weight_sums else None
         self.policy = torch.zeros(rows, HPAD, **f32) if keep_policy else None
         self.root_values = torch.empty(B, 2, HPAD, **f32)
         self.values_avg = torch.zeros(rows, 2, HPAD, **f32) if keep_node_values else None
@@ -190,6 +203,12 @@ class SubgameSolver:
         self.scratch = torch.empty(n_scratch, **f32)
         self.work_counter = torch.zeros(4, device=device, dtype=torch.int32)
         self.launches = 0
+
+    def release(self) -> None:
+        """Drops the device buffers (they return to the caching allocator)."""
+        for name in ("regrets", "policy_avg", "weight_sums", "policy", "root_values", "values_avg", "beliefs_avg",
+                     "scratch", "tables"):
+            setattr(self, name, None)
 
     def solve(self, root_beliefs: torch.Tensor, scalars: np.ndarray, *, cfr_plus: bool = False) -> SolveResult:
         """root_beliefs: [B,2,1328] fp32 on the device (padded).  Enqueues one kernel."""
@@ -200,11 +219,6 @@ class SubgameSolver:
         self._scalars = sc
         p = _lib.ptr
         with torch.cuda.device(self.device):
-            # rows of leaf-only bookkeeping (roots have no regrets) must not hold garbage
-            self.regrets.zero_()
-            self.policy_avg.zero_()
-            if self.weight_sums is not None:
-                self.weight_sums.zero_()
             _lib.call(
                 "p2b_cfr_solve", p(self.subgames), p(self.nodes), self.B, self.layout.max_children,
                 self.layout.max_internal, p(self.tables.blob) if self.tables is not None else None, p(root_beliefs),
