@@ -166,7 +166,7 @@ def workload_config():
 def run_gpu_arm(args, rank: int, world: int, local_rank: int):
     import torch.distributed as dist
 
-    from poker2_b200 import build, solver
+    from poker2_b200 import build, sharding, solver
     from poker2_b200 import tree as ptree
 
     build.build()
@@ -183,12 +183,12 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
     sv = solver.SubgameSolver(layout, boards, device)
     rb = solver.pad_rows(ranges.to(device)).contiguous()
     scal = solver.iteration_scalars(ITERATIONS)
-    gathered = torch.empty(world * BATCH, 2, solver.HPAD, device=device) if distributed else None
+    gathered = None
 
     def step():
         res = sv.solve(rb, scal)
         if distributed:  # the one exchange of the path: value targets of all shards
-            dist.all_gather_into_tensor(gathered, res.root_values)
+            sharding.gather_rows(res.root_values)
         return res
 
     for _ in range(args.warmup):
@@ -238,7 +238,9 @@ def run_e2e(args, solver, sv, boards, ranges, pot, stack, layout, scal, gathered
         res, _ = solver.solve_subgames(h_boards, h_ranges, pot, stack, iterations=ITERATIONS, bet_bins=BET_BINS,
                                        max_depth=MAX_DEPTH, max_raises=MAX_RAISES, device=device)
         if distributed:
-            dist.all_gather_into_tensor(gathered, res.root_values)
+            from poker2_b200 import sharding
+
+            sharding.gather_rows(res.root_values)
         return res.to_host(pinned)
 
     sv.release()
