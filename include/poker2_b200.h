@@ -90,6 +90,37 @@ int p2b_cfr_solve(const void* subgames, const void* nodes, int32_t num_subgames,
 int64_t p2b_cfr_scratch_floats(int32_t max_internal, int32_t num_blocks);
 int p2b_cfr_default_blocks(void);
 
+/* p2b_cfr_solve_noalloc -- the same solve without any allocation.  (No counterpart in the
+ * upstream project: it exists for hosts of this library that cannot allocate.)
+ *
+ * Who needs it: a data-generation worker that was handed a fixed slice of GPU memory by
+ * its trainer and must not take more; a caller in a latency-sensitive loop, for which a
+ * cudaMalloc would stall the whole device; a process whose framework allocator already
+ * owns all free memory, so that a driver allocation could simply fail.  Such a caller
+ * cannot provide the work rows and the queue counter that p2b_cfr_solve asks for, and
+ * must not trigger the one-time table allocation that the other entry points perform.
+ *
+ * This variant keeps its work rows, queue counter and combo table in a fixed area that is
+ * part of the library image: 32 MiB (p2b_cfr_noalloc_scratch_floats() floats) on every
+ * GPU that loads the library, held until the process exits.  Limits that follow:
+ *   - a subgame needs max_internal * 6 * 1328 floats of work rows per thread block; if
+ *     that exceeds the area the call fails with a message and nothing is launched;
+ *   - the number of thread blocks is what fits in the area (at most one per SM), so large
+ *     trees run on fewer SMs than with p2b_cfr_solve.
+ * The first call on a device resolves the area's addresses and uploads a 2.6 KB table
+ * with a blocking copy; make that first call before any stream capture.  Every call uses
+ * the same area: it zeroes the queue counter itself and needs no other clearing, but two
+ * calls that overlap on the GPU (different streams or threads) race on it -- serialise them.
+ * It calls no cudaMalloc / cudaFree and no allocating library routine; inputs and outputs
+ * are the caller's, with the meaning they have in p2b_cfr_solve. */
+int p2b_cfr_solve_noalloc(const void* subgames, const void* nodes, int32_t num_subgames,
+                          int32_t max_children, int32_t max_internal, const unsigned char* tables,
+                          const float* root_beliefs, float* regrets, float* weight_sums,
+                          float* policy_avg, float* policy, float* root_values, float* values_avg,
+                          float* beliefs_avg, const void* scalars, int32_t iterations,
+                          int32_t cfr_plus, int32_t init_depth, void* stream);
+int64_t p2b_cfr_noalloc_scratch_floats(void);
+
 #ifdef __cplusplus
 }
 #endif

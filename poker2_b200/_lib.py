@@ -31,9 +31,12 @@ _SIGNATURES = {
     "p2b_showdown_values": [_vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _i64, _vp],
     "p2b_cfr_solve": [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp,
                       _i32, _i32, _i32, _vp, _i32, _vp],
+    "p2b_cfr_solve_noalloc": [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32,
+                              _i32, _vp],
 }
 # functions whose return value is a quantity, not a status code
-_VALUE_FUNCS = {"p2b_cfr_scratch_floats": ([_i32, _i32], _i64), "p2b_cfr_default_blocks": ([], _i32)}
+_VALUE_FUNCS = {"p2b_cfr_scratch_floats": ([_i32, _i32], _i64), "p2b_cfr_default_blocks": ([], _i32),
+                "p2b_cfr_noalloc_scratch_floats": ([], _i64)}
 
 
 def library_available() -> bool:

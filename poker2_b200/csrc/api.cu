@@ -118,4 +118,45 @@ int p2b_cfr_solve(const void* subgames, const void* nodes, int32_t num_subgames,
     return launch_cfr_solve(p, num_blocks, max_children, (cudaStream_t)stream);
 }
 
+int64_t p2b_cfr_noalloc_scratch_floats(void) { return cfr_static_scratch_floats(); }
+
+// Allocation-free twin of p2b_cfr_solve: work rows, queue counter and combo table come from
+// a fixed device area inside the library (see launch_cfr_solve_static).
+int p2b_cfr_solve_noalloc(const void* subgames, const void* nodes, int32_t num_subgames, int32_t max_children,
+                          int32_t max_internal, const unsigned char* tables, const float* root_beliefs, float* regrets,
+                          float* weight_sums, float* policy_avg, float* policy, float* root_values, float* values_avg,
+                          float* beliefs_avg, const void* scalars, int32_t iterations, int32_t cfr_plus,
+                          int32_t init_depth, void* stream) {
+    P2B_REQUIRE(num_subgames >= 0 && iterations >= 0, "negative count");
+    if (num_subgames == 0) return P2B_OK;
+    P2B_REQUIRE(subgames && nodes && root_beliefs && regrets && policy_avg && root_values && scalars, "null pointer");
+    P2B_REQUIRE(max_internal >= 1, "max_internal must be positive");
+    const uintptr_t align = reinterpret_cast<uintptr_t>(subgames) | reinterpret_cast<uintptr_t>(nodes) |
+                            reinterpret_cast<uintptr_t>(tables) | reinterpret_cast<uintptr_t>(root_beliefs) |
+                            reinterpret_cast<uintptr_t>(regrets) | reinterpret_cast<uintptr_t>(weight_sums) |
+                            reinterpret_cast<uintptr_t>(policy_avg) | reinterpret_cast<uintptr_t>(policy) |
+                            reinterpret_cast<uintptr_t>(root_values) | reinterpret_cast<uintptr_t>(values_avg) |
+                            reinterpret_cast<uintptr_t>(beliefs_avg);
+    P2B_REQUIRE((align & 15) == 0, "all arrays must be 16-byte aligned");
+    CfrParams p{};
+    p.subgames = static_cast<const SubgameRec*>(subgames);
+    p.nodes = static_cast<const NodeRec*>(nodes);
+    p.num_subgames = num_subgames;
+    p.tables = tables;
+    p.root_beliefs = root_beliefs;
+    p.regrets = regrets;
+    p.weight_sums = weight_sums;
+    p.policy_avg = policy_avg;
+    p.policy = policy;
+    p.root_values = root_values;
+    p.values_avg = values_avg;
+    p.beliefs_avg = beliefs_avg;
+    p.max_internal = max_internal;
+    p.scalars = static_cast<const IterScalars*>(scalars);
+    p.iterations = iterations;
+    p.cfr_plus = cfr_plus;
+    p.init_depth = init_depth;
+    return launch_cfr_solve_static(p, max_children, (cudaStream_t)stream);
+}
+
 }  // extern "C"

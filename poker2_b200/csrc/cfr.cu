@@ -773,6 +773,12 @@ int sm_count();
 
 int cfr_default_blocks() { return sm_count(); }
 
+static int dispatch_cfr(const CfrParams& p, int num_blocks, int max_children, cudaStream_t stream) {
+    if (max_children <= 5) return launch_variant<2, 5>(p, num_blocks, stream);
+    if (max_children <= kCfrMaxChildren) return launch_variant<2, kCfrMaxChildren>(p, num_blocks, stream);
+    return set_error(P2B_ERR_ARG, "at most %d actions per node are supported, got %d", kCfrMaxChildren, max_children);
+}
+
 int launch_cfr_solve(const CfrParams& params, int num_blocks, int max_children, cudaStream_t stream) {
     if (params.num_subgames == 0) return P2B_OK;
     if (params.iterations < 1) return set_error(P2B_ERR_ARG, "at least one iteration is required");
@@ -782,9 +788,80 @@ int launch_cfr_solve(const CfrParams& params, int num_blocks, int max_children, 
     p.combos = device_combo_table();
     rc = check_cuda(cudaMemsetAsync(p.work_counter, 0, sizeof(int32_t), stream), "cudaMemsetAsync(work counter)");
     if (rc) return rc;
-    if (max_children <= 5) return launch_variant<2, 5>(p, num_blocks, stream);
-    if (max_children <= kCfrMaxChildren) return launch_variant<2, kCfrMaxChildren>(p, num_blocks, stream);
-    return set_error(P2B_ERR_ARG, "at most %d actions per node are supported, got %d", kCfrMaxChildren, max_children);
+    return dispatch_cfr(p, num_blocks, max_children, stream);
+}
+
+// ---- variant that allocates nothing --------------------------------------------------
+// Work rows, the subgame queue counter and the combo table live in file-scope device
+// arrays, so every GPU that loads this library holds them (about 32 MiB) until the process
+// exits.  In host code these names are only stand-ins: the device addresses are obtained
+// once per device with cudaGetSymbolAddress and handed to the kernel.
+constexpr long long kStaticScratchFloats = 8ll << 20;  // 32 MiB of work rows
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+static __device__ __align__(256) int32_t g_static_counter[64];
+static __device__ __align__(256) ComboTable g_static_combos;
+
+namespace {
+struct StaticPointers {
+    float* scratch = nullptr;
+    int32_t* counter = nullptr;
+    ComboTable* combos = nullptr;
+    bool ready = false;
+};
+constexpr int kStaticMaxDevices = 64;
+StaticPointers g_static[kStaticMaxDevices];
+}  // namespace
+
+long long cfr_static_scratch_floats() { return kStaticScratchFloats; }
+
+// First call on a device: resolves the three symbols and uploads the combo table with a
+// synchronous copy.  Later calls only enqueue a 4-byte memset and the kernel.
+int launch_cfr_solve_static(const CfrParams& params, int max_children, cudaStream_t stream) {
+    if (params.num_subgames == 0) return P2B_OK;
+    if (params.iterations < 1) return set_error(P2B_ERR_ARG, "at least one iteration is required");
+    int dev = 0;
+    int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+    if (rc) return rc;
+    if (dev < 0 || dev >= kStaticMaxDevices) return set_error(P2B_ERR_STATE, "device ordinal %d out of range", dev);
+    StaticPointers& sp = g_static[dev];
+    if (!sp.ready) {
+        rc = check_cuda(cudaGetSymbolAddress((void**)&sp.scratch, g_static_scratch), "cudaGetSymbolAddress(scratch)");
+        if (rc) return rc;
+        rc = check_cuda(cudaGetSymbolAddress((void**)&sp.counter, g_static_counter), "cudaGetSymbolAddress(counter)");
+        if (rc) return rc;
+        rc = check_cuda(cudaGetSymbolAddress((void**)&sp.combos, g_static_combos), "cudaGetSymbolAddress(combos)");
+        if (rc) return rc;
+        ComboTable host;
+        int h = 0;
+        for (int a = 0; a < P2B_NUM_CARDS; ++a)
+            for (int b = a + 1; b < P2B_NUM_CARDS; ++b, ++h) {
+                host.c1[h] = (uint8_t)a;
+                host.c2[h] = (uint8_t)b;
+            }
+        rc = check_cuda(cudaMemcpy(sp.combos, &host, sizeof(ComboTable), cudaMemcpyHostToDevice),
+                        "cudaMemcpy(static combo table)");
+        if (rc) return rc;
+        sp.ready = true;
+    }
+    const long long per_block = cfr_scratch_floats(params.max_internal);
+    if (per_block > kStaticScratchFloats)
+        return set_error(P2B_ERR_ARG,
+                         "a subgame with %d internal nodes needs %lld floats of work rows per block; the built-in "
+                         "work area holds %lld floats (use p2b_cfr_solve with caller-provided scratch instead)",
+                         params.max_internal, per_block, kStaticScratchFloats);
+    long long blocks = kStaticScratchFloats / per_block;
+    if (blocks > sm_count()) blocks = sm_count();
+    if (blocks > params.num_subgames) blocks = params.num_subgames;
+    CfrParams p = params;
+    p.combos = sp.combos;
+    p.scratch = sp.scratch;
+    p.scratch_stride = per_block;
+    p.work_counter = sp.counter;
+    // the queue counter must start at zero; the work rows need no clearing (every row is
+    // written before it is read within a solve)
+    rc = check_cuda(cudaMemsetAsync(sp.counter, 0, sizeof(int32_t), stream), "cudaMemsetAsync(static counter)");
+    if (rc) return rc;
+    return dispatch_cfr(p, (int)blocks, max_children, stream);
 }
 
 }  // namespace p2b

@@ -79,5 +79,7 @@ __host__ __device__ inline long long cfr_scratch_floats(int max_internal) {
 
 int launch_cfr_solve(const CfrParams& p, int num_blocks, int max_children, cudaStream_t stream);
 int cfr_default_blocks();
+int launch_cfr_solve_static(const CfrParams& p, int max_children, cudaStream_t stream);
+long long cfr_static_scratch_floats();
 
 }  // namespace p2b

@@ -232,6 +232,28 @@ class SubgameSolver:
                            self.root_values, self.values_avg, self.beliefs_avg)
 
 
+def solve_noalloc(sv: SubgameSolver, root_beliefs: torch.Tensor, scalars_dev: torch.Tensor, *,
+                  cfr_plus: bool = False) -> SolveResult:
+    """Runs the same solve as `SubgameSolver.solve` through `p2b_cfr_solve_noalloc`, the entry
+    point for hosts that cannot allocate GPU memory (a worker confined to a fixed memory
+    slice, a latency-critical loop, a process whose framework pool owns all free memory).
+    The library's built-in 32 MiB work area replaces `sv.scratch` and `sv.work_counter`;
+    nothing is allocated here either: `scalars_dev` is the caller's device copy of the
+    per-iteration scalars ([T,32] uint8) and outputs go to the buffers `sv` already owns.
+    Calls share that work area, so do not overlap two of them on one GPU."""
+    assert root_beliefs.shape == (sv.B, 2, HPAD) and root_beliefs.is_contiguous()
+    p = _lib.ptr
+    with torch.cuda.device(sv.device):
+        _lib.call(
+            "p2b_cfr_solve_noalloc", p(sv.subgames), p(sv.nodes), sv.B, sv.layout.max_children,
+            sv.layout.max_internal, p(sv.tables.blob) if sv.tables is not None else None, p(root_beliefs),
+            p(sv.regrets), p(sv.weight_sums), p(sv.policy_avg), p(sv.policy), p(sv.root_values), p(sv.values_avg),
+            p(sv.beliefs_avg), p(scalars_dev), int(scalars_dev.shape[0]), int(cfr_plus), sv.layout.tree_depth,
+            _lib.stream_ptr(sv.device))
+    return SolveResult(sv.layout, sv.policy_avg, sv.regrets, sv.weight_sums, sv.policy, sv.root_values,
+                       sv.values_avg, sv.beliefs_avg)
+
+
 def solve_subgames(boards, ranges, pot, stacks, *, iterations: int, bet_bins=(0.5, 1.0), max_depth: int = 8,
                    max_raises=None, bb: int = 2, cfr_type: str = "discounted", alpha: float = 1.5, beta: float = 0.0,
                    gamma: float = 2.0, dcfr_delay: int = 0, cfr_plus: bool = False, device=None,
