@@ -34,7 +34,9 @@ namespace {
 
 constexpr int kNatEntries = 52 * 51;
 constexpr int kBankRows = kCfrMaxChildren;  // child rows staged per node in the top-down sweep
-constexpr int kStageRows = 2 * kBankRows;   // two banks, alternated between consecutive nodes
+constexpr int kStageRows = 2 + 2 * kBankRows;  // top-down: two banks of child rows; bottom-up: 2 belief rows,
+                                               // one marginal row and one leaf-belief row per child
+constexpr int kCsRows = 2 + kBankRows;       // rows whose per-card sums are needed at one node
 
 // ---- shared memory carve-up (bytes) ----
 constexpr int kOffTab = 0;
@@ -43,9 +45,9 @@ constexpr int kOffXs = kOffNodes + kCfrMaxNodes * 16;
 constexpr int kOffPref = kOffXs + kStageRows * P2B_HPAD * 4;
 constexpr int kOffPc = kOffPref + 2 * P2B_HPAD * 4;
 constexpr int kOffCs = kOffPc + 2 * 52 * 52 * 4;
-constexpr int kOffWarpTot = kOffCs + 2 * 52 * 8;
+constexpr int kOffWarpTot = kOffCs + kCsRows * 52 * 8;
 constexpr int kOffS = kOffWarpTot + 32 * 8;
-constexpr int kOffSig = kOffS + 4 * 8;
+constexpr int kOffSig = kOffS + kCsRows * 8;
 constexpr int kOffNat = kOffSig + kCfrMaxNodes * 2 * 4;
 constexpr int kOffMisc = kOffNat + ((kNatEntries * 2 + 15) / 16) * 16;
 constexpr int kCfrSmem = kOffMisc + 64;
@@ -95,40 +97,6 @@ __device__ __forceinline__ double warp_sum(double v) {
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
     return v;
-}
-
-// Per-card sums of `nrows` (1 or 2) ranges staged in xs[row][HPAD]: cs[row][c] = mass of the
-// hands holding card c, S[row] = total mass.  Four threads share one card.  Ends with a
-// barrier; the caller must have made xs visible with a barrier before the call.
-__device__ __forceinline__ void block_cardsums(const float* xs, int nrows, const uint16_t* nat, double* cs, double* S) {
-    const int tid = threadIdx.x;
-    const int ntasks = nrows * 208;
-    for (int base = 0; base < ntasks; base += blockDim.x) {
-        const int t = base + tid;
-        const bool valid = t < ntasks;
-        const int row = t / 208, rem = t % 208, c = rem >> 2, q = rem & 3;
-        double s = 0.0;
-        if (valid) {
-            const float* x = xs + row * P2B_HPAD;
-            const uint16_t* list = nat + c * 51;
-#pragma unroll
-            for (int i = 0; i < 13; ++i) {
-                const int e = q + 4 * i;
-                if (e < 51) s += (double)x[list[e]];
-            }
-        }
-        s += __shfl_xor_sync(0xffffffffu, s, 1);
-        s += __shfl_xor_sync(0xffffffffu, s, 2);
-        if (valid && q == 0) cs[row * 52 + c] = s;
-    }
-    __syncthreads();
-    const int lane = tid & 31, warp = tid >> 5;
-    if (warp < nrows) {
-        double v = cs[warp * 52 + lane] + (lane + 32 < 52 ? cs[warp * 52 + lane + 32] : 0.0);
-        v = warp_sum(v);
-        if (lane == 0) S[warp] = 0.5 * v;  // every hand was counted under both of its cards
-    }
-    __syncthreads();
 }
 
 // Mass of the hands that share no card with (c1,c2): total - card sums + own mass,
@@ -230,10 +198,13 @@ __device__ __forceinline__ void children_policy(int mode, const CfrParams& p, co
     FV<VPT> sum;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) sum.v[i] = 0.0f;
+    // all loads first: the rows are independent, so their latencies overlap
+#pragma unroll
+    for (int c = 0; c < MAXC; ++c)
+        if (c < k) Rc[c] = ldv<VPT>(B.row1(p.regrets, fc + c), tid);
 #pragma unroll
     for (int c = 0; c < MAXC; ++c)
         if (c < k) {
-            Rc[c] = ldv<VPT>(B.row1(p.regrets, fc + c), tid);
 #pragma unroll
             for (int i = 0; i < VPT; ++i) sum.v[i] = __fadd_rn(sum.v[i], fmaxf(Rc[c].v[i], 0.0f));
         }
@@ -274,37 +245,112 @@ __device__ __forceinline__ void normalize2(Block& B, const HandInfo<VPT>& hi, FV
     apply_norm<VPT>(B, hi, x[1], B.fsum[1]);
 }
 
-// Strength-order prefix sums (pref[0..1326]) and per-card prefix sums (pc[52][52]) of the
-// range staged in x, for the showdown formula.  Contains block barriers; pref and pc are
-// valid on return.
-__device__ __forceinline__ void showdown_tables(Block& B, const float* __restrict__ x, float* __restrict__ pref,
-                                                float* __restrict__ pc) {
+// One block-wide round of the cross-hand work of a node.  For each of the `n_cs` staged rows
+// cs_row0 .. cs_row0+n_cs-1: per-card sums (cs[i][52]) and total (S[i]).  For each of the
+// `n_pc` rows listed in pc_rows: strength-order prefix sums (pref slot i) and per-card
+// prefix sums (pc slot i) for the showdown formula.  Threads work in groups of four on one
+// (row, card) list; whole warps take the row totals and the strength-order scans.  The
+// staged rows must be visible (barrier) before the call; it ends with a barrier.
+__device__ __forceinline__ void node_tables(Block& B, int cs_row0, int n_cs, const int (&pc_rows)[2], int n_pc) {
     const BoardTabView tv = view_tables(B.tab);
-    const int tid = threadIdx.x;
-    if (tid < 224) {  // warps 0..6: four threads per card, a quarter of its list each
-        const bool valid = tid < 208;
-        const int c = valid ? tid >> 2 : 0, q = tid & 3, k0 = 13 * q;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    const int quads_cs = n_cs * 208, quads = quads_cs + n_pc * 208;
+    for (int base = 0; base < quads; base += blockDim.x) {
+        const int t = base + tid;
+        const bool valid = t < quads, is_cs = t < quads_cs;
+        const int u = is_cs ? t : t - quads_cs;
+        const int slot = u / 208, rem = u % 208, c = rem >> 2, q = rem & 3;
+        const float* x = B.stage_row(is_cs ? cs_row0 + slot : pc_rows[slot > 1 ? 1 : slot]);
         double tot = 0.0;
-#pragma unroll
-        for (int i = 0; i < 13; ++i)
-            if (valid && k0 + i < 51) tot += (double)x[tv.cardlist[(k0 + i) * 52 + c]];
-        const int base = (tid & 31) & ~3;
-        const double t0 = __shfl_sync(0xffffffffu, tot, base);
-        const double t1 = __shfl_sync(0xffffffffu, tot, base + 1);
-        const double t2 = __shfl_sync(0xffffffffu, tot, base + 2);
-        double acc = q == 0 ? 0.0 : (q == 1 ? t0 : (q == 2 ? t0 + t1 : (t0 + t1) + t2));
         if (valid) {
-            float* row = pc + c * 52;
-            if (q == 0) row[0] = 0.0f;
+            if (is_cs) {
+                const uint16_t* list = B.nat + c * 51;
 #pragma unroll
-            for (int i = 0; i < 13; ++i)
-                if (k0 + i < 51) {
-                    acc += (double)x[tv.cardlist[(k0 + i) * 52 + c]];
-                    row[k0 + i + 1] = (float)acc;
+                for (int i = 0; i < 13; ++i) {
+                    const int e = q + 4 * i;
+                    if (e < 51) tot += (double)x[list[e]];
                 }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 13; ++i)
+                    if (13 * q + i < 51) tot += (double)x[tv.cardlist[(13 * q + i) * 52 + c]];
+            }
+        }
+        const int g = lane & ~3;
+        const double t0 = __shfl_sync(0xffffffffu, tot, g), t1 = __shfl_sync(0xffffffffu, tot, g + 1);
+        const double t2 = __shfl_sync(0xffffffffu, tot, g + 2), t3 = __shfl_sync(0xffffffffu, tot, g + 3);
+        if (valid) {
+            if (is_cs) {
+                if (q == 0) B.cs[slot * 52 + c] = ((t0 + t1) + t2) + t3;
+            } else {
+                double acc = q == 0 ? 0.0 : (q == 1 ? t0 : (q == 2 ? t0 + t1 : (t0 + t1) + t2));
+                float* row = B.pc + slot * 52 * 52 + c * 52;
+                if (q == 0) row[0] = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 13; ++i)
+                    if (13 * q + i < 51) {
+                        acc += (double)x[tv.cardlist[(13 * q + i) * 52 + c]];
+                        row[13 * q + i + 1] = (float)acc;
+                    }
+            }
         }
     }
-    block_prefix_f64([&](int k) { return x[tv.sorted[k]]; }, P2B_NUM_HANDS, pref, B.warp_tot);
+    // Whole-warp tasks go to the highest-numbered warps first: those have the fewest list
+    // tasks above.  Sums run on several independent accumulators to shorten the fp64
+    // dependency chains.
+    for (int wt = nwarps - 1 - warp; wt < n_cs + n_pc; wt += nwarps) {
+        if (wt < n_cs) {  // total mass of a row
+            const float* x = B.stage_row(cs_row0 + wt);
+            double v[6] = {0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
+#pragma unroll
+            for (int i = 0; i < 42; ++i) {
+                const int h = lane + 32 * i;
+                if (h < P2B_NUM_HANDS) v[i % 6] += (double)x[h];
+            }
+            const double tot = warp_sum(((v[0] + v[1]) + (v[2] + v[3])) + (v[4] + v[5]));
+            if (lane == 0) B.S[wt] = tot;
+        } else {  // strength-order prefix sums of a row: 42 consecutive positions per lane,
+                  // as six runs of seven so that the runs accumulate independently
+            const int slot = wt - n_cs;
+            const float* x = B.stage_row(pc_rows[slot]);
+            float* pref = B.pref + slot * P2B_HPAD;
+            const int k0 = 42 * lane;
+            double part[6];
+#pragma unroll
+            for (int b = 0; b < 6; ++b) {
+                double acc = 0.0;
+#pragma unroll
+                for (int i = 0; i < 7; ++i) {
+                    const int k = k0 + 7 * b + i;
+                    if (k < P2B_NUM_HANDS) acc += (double)x[tv.sorted[k]];
+                }
+                part[b] = acc;
+            }
+            const double local = ((part[0] + part[1]) + (part[2] + part[3])) + (part[4] + part[5]);
+            double incl = local;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const double up = __shfl_up_sync(0xffffffffu, incl, d);
+                if (lane >= d) incl += up;
+            }
+            double start = incl - local;
+            if (lane == 0) pref[0] = 0.0f;
+#pragma unroll
+            for (int b = 0; b < 6; ++b) {
+                double run = start;
+#pragma unroll
+                for (int i = 0; i < 7; ++i) {
+                    const int k = k0 + 7 * b + i;
+                    if (k < P2B_NUM_HANDS) {
+                        run += (double)x[tv.sorted[k]];
+                        pref[k + 1] = (float)run;
+                    }
+                }
+                start += part[b];
+            }
+        }
+    }
+    __syncthreads();
 }
 
 // Showdown EV (before the pot scaling) of the hero's hands against the range x.
@@ -398,10 +444,14 @@ __device__ __forceinline__ void sweep_down(int mode, int pass, const CfrParams& 
                     rn.v[i] = __fmul_rn(ra.v[i], sc.mix_new);
                     sum.v[i] = 0.0f;
                 }
+                FV<VPT> Pbs[MAXC];
+#pragma unroll
+                for (int c = 0; c < MAXC; ++c)
+                    if (c < k) Pbs[c] = ldv<VPT>(B.row1(p.policy_avg, fc + c), tid);
 #pragma unroll
                 for (int c = 0; c < MAXC; ++c)
                     if (c < k) {
-                        const FV<VPT> Pb = ldv<VPT>(B.row1(p.policy_avg, fc + c), tid);
+                        const FV<VPT> Pb = Pbs[c];
                         const NodeRec ch = B.nodes[fc + c];
                         if (ch.kind == kInternal) {  // average reach under the OLD average policy
                             FV<VPT> t;
@@ -483,11 +533,16 @@ __device__ __forceinline__ void sweep_down(int mode, int pass, const CfrParams& 
 }
 
 // ---- bottom-up sweep of one pass ------------------------------------------------------
-// Suffix _a: the player acting at the node, _o: the other player.
+// Suffix _a: the player acting at the node, _o: the other player.  Per node: stage every
+// row that needs cross-hand work, one block-wide round of that work (node_tables), then
+// the per-hand arithmetic with no further barrier.  Staging rows: 0 = beliefs of the
+// acting player, 1 = of the other player, 2+c = marginal policy of child c, 8+c = beliefs
+// of the acting player at showdown child c.
 template <int VPT, int MAXC>
 __device__ __forceinline__ void sweep_up(int mode, int pass, const CfrParams& p, Block& B, const HandInfo<VPT>& hi,
                                          const FV<VPT> (&prior)[2], const FV<VPT> (&root_b)[2], int s, int tid) {
     const bool update = (mode != kPassFinal) && (pass + 1 < p.iterations);
+    constexpr int kRowM = 2, kRowLeaf = 2 + kBankRows;
     FV<VPT> mask;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) mask.v[i] = hi.allowed[i] ? 1.0f : 0.0f;
@@ -519,68 +574,84 @@ __device__ __forceinline__ void sweep_up(int mode, int pass, const CfrParams& p,
                 apply_norm<VPT>(B, hi, b_o, B.sig[j * 2 + o]);
             }
         }
-        bool has_showdown = false;
-        for (int c = 0; c < k; ++c) has_showdown |= B.nodes[fc + c].kind == kShowdownLeaf;
+        FV<VPT> P[MAXC], Rc[MAXC], Va[MAXC], acc_a, acc_o;
+        children_policy<VPT, MAXC>(mode, p, B, fc, k, tid, P, Rc);
 
-        stv<VPT>(B.stage_row(a), tid, b_a);
-        stv<VPT>(B.stage_row(o), tid, b_o);
-        __syncthreads();
-        block_cardsums(B.xs, 2, B.nat, B.cs, B.S);
-        FV<VPT> wgt, denm, eva;
+        // ---- stage ----
+        int first_sd = -1;
 #pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-            wgt.v[i] = unblocked(B.cs + o * 52, B.S[o], hi.c1[i], hi.c2[i], b_o.v[i]);
-            denm.v[i] = unblocked(B.cs + a * 52, B.S[a], hi.c1[i], hi.c2[i], b_a.v[i]);
-            eva.v[i] = 0.0f;
+        for (int c = 0; c < MAXC; ++c) {
+            if (c >= k) continue;
+            const NodeRec ch = B.nodes[fc + c];
+            if (ch.kind != kShowdownLeaf) continue;
+            if (first_sd < 0) first_sd = c;
+            FV<VPT> bca;  // beliefs of the acting player at the leaf
+            if (mode == kPassInit) {
+                FV<VPT> x[2];
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) {
+                    const float xa = __fmul_rn(r_a.v[i], P[c].v[i]);
+                    x[0].v[i] = a == 0 ? xa : r_o.v[i];
+                    x[1].v[i] = a == 0 ? r_o.v[i] : xa;
+                }
+                for (int rep = ch.depth; rep <= p.init_depth; ++rep) normalize2<VPT>(B, hi, x);
+                bca = pick<VPT>(x, a);
+            } else {
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) bca.v[i] = __fmul_rn(prior_a.v[i], __fmul_rn(r_a.v[i], P[c].v[i]));
+                apply_norm<VPT>(B, hi, bca, B.sig[(fc + c) * 2 + a]);
+            }
+            stv<VPT>(B.stage_row(kRowLeaf + c), tid, bca);
+            if (mode == kPassFinal && p.beliefs_avg) {
+                stv<VPT>(B.row2(p.beliefs_avg, fc + c, a), tid, bca);
+                stv<VPT>(B.row2(p.beliefs_avg, fc + c, o), tid, b_o);
+            }
         }
-        if (has_showdown) {
-            // The acting player's showdown EV only depends on the other player's beliefs, which
-            // every child shares with this node: one set of tables serves all showdown children.
-            showdown_tables(B, B.stage_row(o), B.pref, B.pc);
-            showdown_ev<VPT>(B, hi, tid, B.stage_row(o), B.pref, B.pc, eva);
-        }
+        stv<VPT>(B.stage_row(0), tid, b_a);
+        stv<VPT>(B.stage_row(1), tid, b_o);
+#pragma unroll
+        for (int c = 0; c < MAXC; ++c)
+            if (c < k) {
+                FV<VPT> m;
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) m.v[i] = __fmul_rn(b_a.v[i], P[c].v[i]);
+                stv<VPT>(B.stage_row(kRowM + c), tid, m);
+            }
         if (mode == kPassFinal && p.beliefs_avg) {
             stv<VPT>(B.row2(p.beliefs_avg, j, a), tid, b_a);
             stv<VPT>(B.row2(p.beliefs_avg, j, o), tid, b_o);
         }
-        FV<VPT> P[MAXC], Rc[MAXC], Va[MAXC], acc_a, acc_o;
-        children_policy<VPT, MAXC>(mode, p, B, fc, k, tid, P, Rc);
+        __syncthreads();
+
+        // ---- cross-hand work: per-card sums of every row, showdown tables of the other
+        // player's beliefs (they serve the acting player at every showdown child) and of the
+        // first showdown child ----
+        {
+            int pc_rows[2] = {1, first_sd >= 0 ? kRowLeaf + first_sd : 1};
+            node_tables(B, 0, 2 + k, pc_rows, first_sd >= 0 ? 2 : 0);
+        }
+
+        // ---- per-hand arithmetic ----
+        FV<VPT> wgt, denm, eva;
 #pragma unroll
-        for (int i = 0; i < VPT; ++i) acc_a.v[i] = acc_o.v[i] = 0.0f;
+        for (int i = 0; i < VPT; ++i) {
+            wgt.v[i] = unblocked(B.cs + 52, B.S[1], hi.c1[i], hi.c2[i], b_o.v[i]);
+            denm.v[i] = unblocked(B.cs, B.S[0], hi.c1[i], hi.c2[i], b_a.v[i]);
+            eva.v[i] = 0.0f;
+            acc_a.v[i] = acc_o.v[i] = 0.0f;
+        }
+        if (first_sd >= 0) showdown_ev<VPT>(B, hi, tid, B.stage_row(1), B.pref, B.pc, eva);
 
 #pragma unroll
         for (int c = 0; c < MAXC; ++c) {
             if (c >= k) continue;  // uniform across the block
             const NodeRec ch = B.nodes[fc + c];
-            FV<VPT> m, pio, bca;
-#pragma unroll
-            for (int i = 0; i < VPT; ++i) m.v[i] = __fmul_rn(b_a.v[i], P[c].v[i]);
-            if (ch.kind == kShowdownLeaf) {
-                // beliefs of the acting player at the leaf
-                if (mode == kPassInit) {
-                    FV<VPT> x[2];
-#pragma unroll
-                    for (int i = 0; i < VPT; ++i) {
-                        const float xa = __fmul_rn(r_a.v[i], P[c].v[i]);
-                        x[0].v[i] = a == 0 ? xa : r_o.v[i];
-                        x[1].v[i] = a == 0 ? r_o.v[i] : xa;
-                    }
-                    for (int rep = ch.depth; rep <= p.init_depth; ++rep) normalize2<VPT>(B, hi, x);
-                    bca = pick<VPT>(x, a);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < VPT; ++i) bca.v[i] = __fmul_rn(prior_a.v[i], __fmul_rn(r_a.v[i], P[c].v[i]));
-                    apply_norm<VPT>(B, hi, bca, B.sig[(fc + c) * 2 + a]);
-                }
-                stv<VPT>(B.stage_row(3), tid, bca);
-            }
             // policy of this child as seen by each opponent hand (cfr_evaluator.py:1083-1093)
-            stv<VPT>(B.stage_row(2), tid, m);
-            __syncthreads();
-            block_cardsums(B.stage_row(2), 1, B.nat, B.cs, B.S);
+            FV<VPT> pio;
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
-                const float blk = unblocked(B.cs, B.S[0], hi.c1[i], hi.c2[i], m.v[i]);
+                const float m = __fmul_rn(b_a.v[i], P[c].v[i]);
+                const float blk = unblocked(B.cs + (kRowM + c) * 52, B.S[kRowM + c], hi.c1[i], hi.c2[i], m);
                 pio.v[i] = denm.v[i] > 1e-5f ? __fdiv_rn(blk, denm.v[i]) : 0.0f;
             }
             FV<VPT> V_a, V_o;
@@ -596,17 +667,21 @@ __device__ __forceinline__ void sweep_up(int mode, int pass, const CfrParams& p,
                 V_o = ldv<VPT>(B.val(ch.internal_idx, o), tid);
             } else if (ch.kind == kShowdownLeaf) {
                 FV<VPT> evo;
-                showdown_tables(B, B.stage_row(3), B.pref + P2B_HPAD, B.pc + 52 * 52);
-                showdown_ev<VPT>(B, hi, tid, B.stage_row(3), B.pref + P2B_HPAD, B.pc + 52 * 52, evo);
+                if (c == first_sd) {
+                    showdown_ev<VPT>(B, hi, tid, B.stage_row(kRowLeaf + c), B.pref + P2B_HPAD, B.pc + 52 * 52, evo);
+                } else {
+                    // a further showdown child: another round builds its tables in slot 0 (the
+                    // acting player's EV, the only user of slot 0, is already in registers)
+                    __syncthreads();
+                    int pc_rows[2] = {kRowLeaf + c, kRowLeaf + c};
+                    node_tables(B, 0, 0, pc_rows, 1);
+                    showdown_ev<VPT>(B, hi, tid, B.stage_row(kRowLeaf + c), B.pref, B.pc, evo);
+                }
                 const float pot_a = a == 0 ? ch.v0 : ch.v1, pot_o = a == 0 ? ch.v1 : ch.v0;
 #pragma unroll
                 for (int i = 0; i < VPT; ++i) {
                     V_a.v[i] = __fdiv_rn(__fmul_rn(eva.v[i], pot_a), B.sg.scale);
                     V_o.v[i] = __fdiv_rn(__fmul_rn(evo.v[i], pot_o), B.sg.scale);
-                }
-                if (mode == kPassFinal && p.beliefs_avg) {
-                    stv<VPT>(B.row2(p.beliefs_avg, fc + c, a), tid, bca);
-                    stv<VPT>(B.row2(p.beliefs_avg, fc + c, o), tid, b_o);
                 }
             } else {
 #pragma unroll
@@ -640,13 +715,17 @@ __device__ __forceinline__ void sweep_up(int mode, int pass, const CfrParams& p,
         if (update) {
             // instantaneous regrets of this pass folded into the discounted update of the next
             const IterScalars sc = p.scalars[pass + 1];
+            FV<VPT> ws[MAXC];
+#pragma unroll
+            for (int c = 0; c < MAXC; ++c) {
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) ws[c].v[i] = 0.0f;
+                if (c < k && p.weight_sums && mode != kPassInit) ws[c] = ldv<VPT>(B.row1(p.weight_sums, fc + c), tid);
+            }
 #pragma unroll
             for (int c = 0; c < MAXC; ++c)
                 if (c < k) {
-                    FV<VPT> w;
-#pragma unroll
-                    for (int i = 0; i < VPT; ++i) w.v[i] = 0.0f;
-                    if (p.weight_sums && mode != kPassInit) w = ldv<VPT>(B.row1(p.weight_sums, fc + c), tid);
+                    FV<VPT> w = ws[c];
 #pragma unroll
                     for (int i = 0; i < VPT; ++i) {
                         const float reg = __fmul_rn(wgt.v[i], __fsub_rn(Va[c].v[i], acc_a.v[i]));
