@@ -271,6 +271,9 @@ def finish_gpu_arm(args, rank, world, layout, ms_step, value, clocks, e2e, distr
         alg_bytes = 16.0 * 1326 * nonroot * ITERATIONS  # regrets + average policy, read + write, per iteration
         peak, peak_kind = measured_peak_gbs()
         achieved = alg_bytes / (ms_step / 1e3) / 1e9
+        # DRAM bytes per subgame-pass from the ncu capture of a small case (profiles/), scaled
+        # to this launch by the number of subgame-passes (traffic grows in proportion)
+        traffic = 2.532e6 * BATCH * (ITERATIONS + 2)
         line = {
             "metric": "subgame-CFR-iterations/sec", "value": value, "unit": "subgame-iterations/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
@@ -280,7 +283,7 @@ def finish_gpu_arm(args, rank, world, layout, ms_step, value, clocks, e2e, distr
             "clocks": clocks, "gpu_launches": args.steps,
             "e2e": e2e,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": None, "peak_source": peak_kind,
+                         "frac": achieved / peak, "traffic": traffic, "peak_source": peak_kind,
                          "kernel": "cfr_solve_kernel", "algorithmic_bytes_per_launch": alg_bytes},
         }
         if world == 1 and not args.no_cpu_baseline:
