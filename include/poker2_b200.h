@@ -121,6 +121,68 @@ int p2b_cfr_solve_noalloc(const void* subgames, const void* nodes, int32_t num_s
                           int32_t cfr_plus, int32_t init_depth, void* stream);
 int64_t p2b_cfr_noalloc_scratch_floats(void);
 
+/* ---- step-level kernels (src/p2/search/fused_cfr_triton.py) ----------------------------
+ * One entry point per fused kernel of the upstream module, on caller-owned contiguous fp32
+ * tensors in the upstream node order; index tensors are int64, masks one byte per entry.
+ * Iteration-dependent scalars are read from device memory.  H is the row length (1326). */
+/* fused_dcfr_update_with_tensors_ (:200-235); scalars4 = {t^a, t^b, t^a+1, t^b+1} */
+int p2b_step_dcfr_update(const float* regrets, float* cumulative, float* weight_sums, float* positive_out,
+                         const float* scalars4, int64_t n, int apply_dcfr, int cfr_plus, void* stream);
+/* fused_block_and_normalize_beliefs_ (:286-335) */
+int p2b_step_block_normalize(float* target, const uint8_t* allowed, const float* allowed_prob, int64_t rows,
+                             int32_t rows_per_outer, int32_t H, float eps, void* stream);
+/* fused_regret_matching_divide_ (:369-399) */
+int p2b_step_regret_matching_divide(const float* positive, const float* denom, const float* uniform, float* out,
+                                    int64_t n, float eps, void* stream);
+/* fused_weight_child_values (:438-477) */
+int p2b_step_weight_child_values(const float* values, const int64_t* prev_actor, const float* policy_hero,
+                                 const float* policy_opp, float* out, int64_t M, int32_t H, void* stream);
+/* fused_update_average_values_with_tensors_ (:538-560) */
+int p2b_step_update_average_values(float* values_avg, const float* latest, const float* old_w, const float* new_w,
+                                   const float* inv_total, int64_t n, void* stream);
+/* fused_avg_values_zero_sum_ (:623-668) with subtract_b=0, scale=1/(old+new);
+ * fused_model_values_mix_zero_sum (:1739-1775) with subtract_b=1, scale=NULL:
+ * out = (a*coef_a +/- b*coef_b) [*scale] - 0.5*sum_p sum_h out*beliefs (rows of [2,H]) */
+int p2b_step_mix_zero_sum(const float* a, const float* b, const float* beliefs, const uint8_t* ignore,
+                          const float* coef_a, const float* coef_b, const float* scale, float* out, int64_t rows,
+                          int32_t H, int subtract_b, int enforce_zero_sum, void* stream);
+/* fused_model_values_mix_with_tensors (:1658-1680): out = coef_a*a - coef_b*b */
+int p2b_step_scaled_difference(const float* a, const float* b, const float* coef_a, const float* coef_b, float* out,
+                               int64_t n, void* stream);
+/* fused_regret_tail_ (:712-766) */
+int p2b_step_regret_tail(const float* values_achieved, const float* actor_values, const float* src_weights,
+                         const int64_t* parent_index, const int64_t* prev_actor, float* regrets, int64_t bottom,
+                         int64_t total, int32_t H, void* stream);
+/* fused_average_policy_mix_with_tensors_ (:879-914) */
+int p2b_step_average_policy_mix(const float* reach, const float* reach_avg, const float* policy, float* policy_avg,
+                                const int64_t* to_act, const int64_t* parent_index, const float* old_w,
+                                const float* new_w, const float* total_w, int64_t bottom, int64_t total, int32_t H,
+                                float eps, void* stream);
+/* fused_parent_sum (:1279-1313) and fused_sibling_sum (:1355-1398, broadcast_to_children=1) */
+int p2b_step_parent_sum(const float* values, const int64_t* child_offsets, const int64_t* child_count, float* out,
+                        int64_t num_parents, int32_t H, int broadcast_to_children, int64_t out_offset, void* stream);
+/* fused_divide_by_parent_sum_ (:1316-1352) */
+int p2b_step_divide_by_parent_sum(const float* pos, const float* fallback, const float* parent_sum,
+                                  const int64_t* parent_index, float* out, int64_t num_children, int32_t H, float eps,
+                                  void* stream);
+/* unblocked_mass_triton (:1110-1157) and unblocked_mass_opp_at_parents_triton (:1067-1107):
+ * out[r] = unblocked mass of the 1326-float row src + row_index[r]*1326 (row_index NULL = r) */
+int p2b_step_unblocked_mass(const float* src, const int64_t* row_index, float* out, int64_t rows, void* stream);
+/* unblocked_mass_ratio_triton (:1559-1602) and unblocked_mass_ratio_indirect_triton (:1499-1556) */
+int p2b_step_unblocked_mass_ratio(const float* numer, const float* denom, const int64_t* parent_index, float* out,
+                                  int64_t rows, float eps, void* stream);
+/* fused_weighted_parent_sum (:1838-1889) */
+int p2b_step_weighted_parent_sum(float* values, const int64_t* prev_actor, const float* policy_hero,
+                                 const float* policy_opp, const int64_t* child_offsets, const int64_t* child_count,
+                                 int64_t parent_base, int64_t num_parents, int32_t H, void* stream);
+/* fused_reach_weights_depth_ (:1944-1986) */
+int p2b_step_reach_weights(float* reach, const float* policy, const uint8_t* allowed, const int64_t* parent_index,
+                           const int64_t* prev_actor, int64_t start, int64_t end, int32_t H, void* stream);
+/* fused_deep_beliefs_ (:2039-2092) */
+int p2b_step_deep_beliefs(float* out, const float* root_beliefs, const float* reach, const float* allowed_prob,
+                          const int64_t* root_index, int64_t num_roots, int64_t total, int32_t H, float eps,
+                          void* stream);
+
 #ifdef __cplusplus
 }
 #endif

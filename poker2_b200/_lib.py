@@ -33,6 +33,22 @@ _SIGNATURES = {
                       _i32, _i32, _i32, _vp, _i32, _vp],
     "p2b_cfr_solve_noalloc": [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32,
                               _i32, _vp],
+    "p2b_step_dcfr_update": [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _vp],
+    "p2b_step_block_normalize": [_vp, _vp, _vp, _i64, _i32, _i32, _f32, _vp],
+    "p2b_step_regret_matching_divide": [_vp, _vp, _vp, _vp, _i64, _f32, _vp],
+    "p2b_step_weight_child_values": [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _vp],
+    "p2b_step_update_average_values": [_vp, _vp, _vp, _vp, _vp, _i64, _vp],
+    "p2b_step_mix_zero_sum": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _vp],
+    "p2b_step_scaled_difference": [_vp, _vp, _vp, _vp, _vp, _i64, _vp],
+    "p2b_step_regret_tail": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _vp],
+    "p2b_step_average_policy_mix": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _f32, _vp],
+    "p2b_step_parent_sum": [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _i64, _vp],
+    "p2b_step_divide_by_parent_sum": [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _f32, _vp],
+    "p2b_step_unblocked_mass": [_vp, _vp, _vp, _i64, _vp],
+    "p2b_step_unblocked_mass_ratio": [_vp, _vp, _vp, _vp, _i64, _f32, _vp],
+    "p2b_step_weighted_parent_sum": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _vp],
+    "p2b_step_reach_weights": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _vp],
+    "p2b_step_deep_beliefs": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _f32, _vp],
 }
 # functions whose return value is a quantity, not a status code
 _VALUE_FUNCS = {"p2b_cfr_scratch_floats": ([_i32, _i32], _i64), "p2b_cfr_default_blocks": ([], _i32),

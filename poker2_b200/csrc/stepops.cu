@@ -1,0 +1,496 @@
+// Step-level kernels: one kernel per step of the CFR iteration, on caller-owned tensors in
+// the upstream node order.  They mirror, one for one, the fused kernels of
+// p2/search/fused_cfr_triton.py (cited per kernel) so that an evaluator written against
+// that module can switch to this library step by step.  The whole-subgame kernel in
+// cfr.cu is the fast path; these exist for drop-in compatibility.  Scalars that depend on
+// the iteration number are read from device memory (as upstream's TScalars do).
+#include "common.cuh"
+
+namespace p2b {
+
+namespace {
+
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ double block_sum(double v, double* red) {
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    double s = 0.0;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) s += red[w];
+    return s;
+}
+
+inline int blocks_for(long long n, int cap) {
+    long long g = (n + kThreads - 1) / kThreads;
+    if (g < 1) g = 1;
+    if (g > cap) g = cap;
+    return (int)g;
+}
+
+// fused_cfr_triton.py:72-121 (_fused_dcfr_update_kernel)
+__global__ void dcfr_update_kernel(const float* __restrict__ regrets, float* __restrict__ cumul,
+                                   float* __restrict__ weights, float* __restrict__ pos_out,
+                                   const float* __restrict__ scal /* a_num,b_num,a_den,b_den */, long long n,
+                                   int apply_dcfr, int cfr_plus) {
+    const float an = scal[0], bn = scal[1], ad = scal[2], bd = scal[3];
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        float c = cumul[i], w = weights[i];
+        if (apply_dcfr) {
+            const bool pos = c > 0.0f;
+            const float num = pos ? an : bn, den = pos ? ad : bd;
+            c = __fdiv_rn(__fmul_rn(c, num), den);
+            w = __fdiv_rn(__fmul_rn(w, num), den);
+        }
+        w = __fadd_rn(w, 1.0f);
+        c = __fadd_rn(c, regrets[i]);
+        if (cfr_plus) c = fmaxf(c, 0.0f);
+        cumul[i] = c;
+        weights[i] = w;
+        if (pos_out) pos_out[i] = fmaxf(c, 0.0f);
+    }
+}
+
+// fused_cfr_triton.py:246-284 (_fused_block_normalize_kernel): one block per row
+__global__ void block_normalize_kernel(float* __restrict__ target, const unsigned char* __restrict__ allowed,
+                                       const float* __restrict__ allowed_prob, long long rows, int outer_stride, int H,
+                                       float eps) {
+    __shared__ double red[kThreads / 32];
+    for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+        const long long outer = row / outer_stride;
+        float* t = target + row * H;
+        const unsigned char* m = allowed + outer * H;
+        double s = 0.0;
+        for (int h = threadIdx.x; h < H; h += blockDim.x) {
+            const float v = m[h] ? t[h] : 0.0f;
+            t[h] = v;
+            s += (double)v;
+        }
+        const float total = (float)block_sum(s, red);
+        for (int h = threadIdx.x; h < H; h += blockDim.x)
+            t[h] = total > eps ? __fdiv_rn(t[h], total) : allowed_prob[outer * H + h];
+    }
+}
+
+// fused_cfr_triton.py:346-367 (_fused_regret_matching_divide_kernel)
+__global__ void regret_matching_divide_kernel(const float* __restrict__ pos, const float* __restrict__ den,
+                                              const float* __restrict__ uniform, float* __restrict__ out, long long n,
+                                              float eps) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const float d = den[i];
+        out[i] = d > eps ? __fdiv_rn(pos[i], fmaxf(d, eps)) : uniform[i];
+    }
+}
+
+// fused_cfr_triton.py:410-436 (_fused_weight_child_values_kernel)
+__global__ void weight_child_values_kernel(const float* __restrict__ values, const long long* __restrict__ prev_actor,
+                                           const float* __restrict__ pol_hero, const float* __restrict__ pol_opp,
+                                           float* __restrict__ out, long long M, int H) {
+    const long long n = M * 2 * H;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long m = i / (2 * H);
+        const int p = (int)((i / H) & 1), h = (int)(i % H);
+        const float pol = (p == (int)prev_actor[m]) ? pol_hero[m * H + h] : pol_opp[m * H + h];
+        out[i] = __fmul_rn(values[i], pol);
+    }
+}
+
+// fused_cfr_triton.py:488-507 (_fused_update_average_values_kernel)
+__global__ void update_average_values_kernel(float* __restrict__ avg, const float* __restrict__ latest,
+                                             const float* __restrict__ old_p, const float* __restrict__ new_p,
+                                             const float* __restrict__ inv_p, long long n) {
+    const float o = *old_p, w = *new_p, inv = *inv_p;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        avg[i] = __fmul_rn(__fadd_rn(__fmul_rn(avg[i], o), __fmul_rn(latest[i], w)), inv);
+}
+
+// fused_cfr_triton.py:572-621 (_fused_avg_values_zs_kernel) and :1692-1737
+// (_fused_model_values_mix_zs_kernel): out = a*ca (+|-) b*cb [* scale], then the zero-sum shift
+// 0.5 * sum_p sum_h out_p * belief_p.  One block per row of [2,H].
+__global__ void mix_zero_sum_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                                    const float* __restrict__ beliefs, const unsigned char* __restrict__ ignore,
+                                    const float* __restrict__ ca_p, const float* __restrict__ cb_p,
+                                    const float* __restrict__ scale_p, float* __restrict__ out, long long rows, int H,
+                                    int subtract_b, int enforce_zs) {
+    __shared__ double red[kThreads / 32];
+    const float ca = *ca_p, cb = *cb_p, sc = scale_p ? *scale_p : 1.0f;
+    for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+        const long long base = row * 2 * H;
+        double s = 0.0;
+        for (int i = threadIdx.x; i < 2 * H; i += blockDim.x) {
+            const float x = __fmul_rn(a[base + i], ca), y = __fmul_rn(b[base + i], cb);
+            float v = subtract_b ? __fsub_rn(x, y) : __fadd_rn(x, y);
+            if (scale_p) v = __fmul_rn(v, sc);
+            out[base + i] = v;
+            if (enforce_zs) s += (double)__fmul_rn(v, beliefs[base + i]);
+        }
+        if (enforce_zs) {  // uniform branch: all threads take it
+            float shift = 0.5f * (float)block_sum(s, red);
+            if (ignore && ignore[row]) shift = 0.0f;
+            for (int i = threadIdx.x; i < 2 * H; i += blockDim.x) out[base + i] = __fsub_rn(out[base + i], shift);
+        }
+    }
+}
+
+// fused_cfr_triton.py:679-710 (_fused_regret_tail_kernel)
+__global__ void regret_tail_kernel(const float* __restrict__ achieved, const float* __restrict__ actor_values,
+                                   const float* __restrict__ src_weights, const long long* __restrict__ parent_index,
+                                   const long long* __restrict__ prev_actor, float* __restrict__ regrets,
+                                   long long bottom, long long total, int H) {
+    const long long n = (total - bottom) * H;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long c = bottom + i / H;
+        const int h = (int)(i % H);
+        const long long par = parent_index[c];
+        const float ach = achieved[(c * 2 + prev_actor[c]) * H + h];
+        regrets[c * H + h] = __fmul_rn(src_weights[par * H + h], __fsub_rn(ach, actor_values[par * H + h]));
+    }
+}
+
+// fused_cfr_triton.py:777-821 (_fused_average_policy_mix_kernel)
+__global__ void average_policy_mix_kernel(const float* __restrict__ reach, const float* __restrict__ reach_avg,
+                                          const float* __restrict__ policy, float* __restrict__ policy_avg,
+                                          const long long* __restrict__ to_act, const long long* __restrict__ parent_index,
+                                          const float* __restrict__ old_p, const float* __restrict__ new_p,
+                                          const float* __restrict__ tot_p, long long bottom, long long total, int H,
+                                          float eps) {
+    const float o = *old_p, w = *new_p, tot = *tot_p;
+    const long long n = (total - bottom) * H;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long c = bottom + i / H;
+        const int h = (int)(i % H);
+        const long long par = parent_index[c], row = (par * 2 + to_act[par]) * H + h;
+        const float ra = __fmul_rn(reach_avg[row], o), rn = __fmul_rn(reach[row], w);
+        const float avg = policy_avg[c * H + h], cur = policy[c * H + h];
+        const float den = __fadd_rn(ra, rn);
+        policy_avg[c * H + h] = den > eps ? __fdiv_rn(__fadd_rn(__fmul_rn(ra, avg), __fmul_rn(rn, cur)), den)
+                                          : __fdiv_rn(__fadd_rn(__fmul_rn(o, avg), __fmul_rn(w, cur)), tot);
+    }
+}
+
+// fused_cfr_triton.py:1210-1239 (_parent_sum_kernel) and :1168-1205 (_sibling_sum_kernel):
+// broadcast = 0 writes one row per parent, = 1 one row per child (relative to out_offset).
+__global__ void parent_sum_kernel(const float* __restrict__ values, const long long* __restrict__ child_offsets,
+                                  const long long* __restrict__ child_count, float* __restrict__ out,
+                                  long long num_parents, int H, int broadcast, long long out_offset) {
+    const long long n = num_parents * H;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long p = i / H;
+        const int h = (int)(i % H);
+        const long long first = child_offsets[p], cnt = child_count[p];
+        float acc = 0.0f;
+        for (long long k = 0; k < cnt; ++k) acc = __fadd_rn(acc, values[(first + k) * H + h]);
+        if (!broadcast) out[p * H + h] = acc;
+        else
+            for (long long k = 0; k < cnt; ++k) out[(first + k - out_offset) * H + h] = acc;
+    }
+}
+
+// fused_cfr_triton.py:1241-1277 (_fused_divide_by_parent_sum_kernel)
+__global__ void divide_by_parent_sum_kernel(const float* __restrict__ pos, const float* __restrict__ fallback,
+                                            const float* __restrict__ parent_sum, const long long* __restrict__ parent_index,
+                                            float* __restrict__ out, long long num_children, int H, float eps) {
+    const long long n = num_children * H;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long c = i / H;
+        const int h = (int)(i % H);
+        const float d = parent_sum[parent_index[c] * H + h];
+        const float f = fallback[i], pv = pos[i];
+        out[i] = d > eps ? __fdiv_rn(pv, fmaxf(d, eps)) : f;
+    }
+}
+
+// out = a*ca - b*cb (fused_cfr_triton.py:1613-1631, _fused_model_values_mix_kernel)
+__global__ void scaled_difference_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                                         const float* __restrict__ ca_p, const float* __restrict__ cb_p,
+                                         float* __restrict__ out, long long n) {
+    const float ca = *ca_p, cb = *cb_p;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        out[i] = __fsub_rn(__fmul_rn(ca, a[i]), __fmul_rn(cb, b[i]));
+}
+
+// Per-card sums and total of one 1326-combo row in fp64; cs must hold 52 doubles.
+__device__ __forceinline__ double row_card_sums(const float* __restrict__ x, const ComboTable* __restrict__ combos,
+                                                double* cs, double* red) {
+    __syncthreads();  // previous users of cs are done
+    // four threads per card, each a quarter of the 51 hands holding it (warps 0..6)
+    if (threadIdx.x < 224) {
+        const int t = threadIdx.x, c = t >> 2, q = t & 3;
+        const bool valid = t < 208;
+        double s = 0.0;
+        if (valid)
+            for (int i = q; i < 51; i += 4) {
+                const int d = i < c ? i : i + 1;
+                s += (double)x[c < d ? combo_index(c, d) : combo_index(d, c)];
+            }
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        if (valid && q == 0) cs[c] = s;
+    }
+    double tot = 0.0;
+    for (int h = threadIdx.x; h < P2B_NUM_HANDS; h += blockDim.x) tot += (double)x[h];
+    (void)combos;
+    return block_sum(tot, red);
+}
+
+__device__ __forceinline__ float unblocked_value(const double* cs, double S, int c1, int c2, float x) {
+    return fmaxf((float)(S - cs[c1] - cs[c2] + (double)x), 0.0f);
+}
+
+// unblocked mass of gathered rows: out[r] = U(src + row_index[r]*1326) (row_index null = r).
+// fused_cfr_triton.py:929-960 with the S/card-sum preprocessing of :1008-1026 done in-kernel.
+__global__ void unblocked_mass_kernel(const float* __restrict__ src, const long long* __restrict__ row_index,
+                                      const ComboTable* __restrict__ combos, float* __restrict__ out, long long rows) {
+    __shared__ double cs[P2B_NUM_CARDS];
+    __shared__ double red[kThreads / 32];
+    for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+        const float* x = src + (row_index ? row_index[r] : r) * P2B_NUM_HANDS;
+        const double S = row_card_sums(x, combos, cs, red);
+        for (int h = threadIdx.x; h < P2B_NUM_HANDS; h += blockDim.x)
+            out[r * P2B_NUM_HANDS + h] = unblocked_value(cs, S, combos->c1[h], combos->c2[h], x[h]);
+        __syncthreads();
+    }
+}
+
+// ratio U(numer[c]) / U(denom[parent(c)]), 0 where the denominator is <= eps
+// (fused_cfr_triton.py:1409-1497; parent_index null = denominator row c)
+__global__ void unblocked_ratio_kernel(const float* __restrict__ numer, const float* __restrict__ denom,
+                                       const long long* __restrict__ parent_index,
+                                       const ComboTable* __restrict__ combos, float* __restrict__ out,
+                                       long long rows, float eps) {
+    __shared__ double cs_n[P2B_NUM_CARDS], cs_d[P2B_NUM_CARDS];
+    __shared__ double red[kThreads / 32];
+    for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+        const float* xn = numer + r * P2B_NUM_HANDS;
+        const float* xd = denom + (parent_index ? parent_index[r] : r) * P2B_NUM_HANDS;
+        const double Sn = row_card_sums(xn, combos, cs_n, red);
+        const double Sd = row_card_sums(xd, combos, cs_d, red);
+        for (int h = threadIdx.x; h < P2B_NUM_HANDS; h += blockDim.x) {
+            const int c1 = combos->c1[h], c2 = combos->c2[h];
+            const float n = unblocked_value(cs_n, Sn, c1, c2, xn[h]), d = unblocked_value(cs_d, Sd, c1, c2, xd[h]);
+            out[r * P2B_NUM_HANDS + h] = d > eps ? __fdiv_rn(n, d) : 0.0f;
+        }
+        __syncthreads();
+    }
+}
+
+// fused_cfr_triton.py:1788-1836 (_fused_weighted_parent_sum_kernel)
+__global__ void weighted_parent_sum_kernel(float* __restrict__ values, const long long* __restrict__ prev_actor,
+                                           const float* __restrict__ pol_hero, const float* __restrict__ pol_opp,
+                                           const long long* __restrict__ child_offsets,
+                                           const long long* __restrict__ child_count, long long parent_base,
+                                           long long num_parents, int H) {
+    const long long n = num_parents * 2 * H;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long p = i / (2 * H);
+        const int player = (int)((i / H) & 1), h = (int)(i % H);
+        const long long first = child_offsets[p], cnt = child_count[p];
+        if (cnt == 0) continue;
+        float acc = 0.0f;
+        for (long long k = 0; k < cnt; ++k) {
+            const long long ch = first + k;
+            const float pol = ((int)prev_actor[ch] == player) ? pol_hero[ch * H + h] : pol_opp[ch * H + h];
+            acc = __fadd_rn(acc, __fmul_rn(values[(ch * 2 + player) * H + h], pol));
+        }
+        values[((parent_base + p) * 2 + player) * H + h] = acc;
+    }
+}
+
+// fused_cfr_triton.py:1901-1942 (_fused_reach_weights_kernel)
+__global__ void reach_weights_kernel(float* __restrict__ reach, const float* __restrict__ policy,
+                                     const unsigned char* __restrict__ allowed, const long long* __restrict__ parent_index,
+                                     const long long* __restrict__ prev_actor, long long start, long long end, int H) {
+    const long long n = (end - start) * H;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long c = start + i / H;
+        const int h = (int)(i % H);
+        const long long par = parent_index[c];
+        float v0 = reach[(par * 2 + 0) * H + h], v1 = reach[(par * 2 + 1) * H + h];
+        const float pol = policy[c * H + h];
+        if (prev_actor[c] == 0) v0 = __fmul_rn(v0, pol);
+        else v1 = __fmul_rn(v1, pol);
+        const bool ok = allowed[c * H + h] != 0;
+        reach[(c * 2 + 0) * H + h] = ok ? v0 : 0.0f;
+        reach[(c * 2 + 1) * H + h] = ok ? v1 : 0.0f;
+    }
+}
+
+// fused_cfr_triton.py:1997-2037 (_fused_deep_beliefs_kernel): one block per (node, player)
+__global__ void deep_beliefs_kernel(float* __restrict__ out, const float* __restrict__ root_beliefs,
+                                    const float* __restrict__ reach, const float* __restrict__ allowed_prob,
+                                    const long long* __restrict__ root_index, long long num_roots, long long total,
+                                    int H, float eps) {
+    __shared__ double red[kThreads / 32];
+    const long long rows = (total - num_roots) * 2;
+    for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+        const long long node = num_roots + r / 2;
+        const int p = (int)(r & 1);
+        const float* rb = root_beliefs + (root_index[node] * 2 + p) * H;
+        const float* rw = reach + (node * 2 + p) * H;
+        float* o = out + (node * 2 + p) * H;
+        double s = 0.0;
+        for (int h = threadIdx.x; h < H; h += blockDim.x) s += (double)__fmul_rn(rb[h], rw[h]);
+        const float tot = (float)block_sum(s, red);
+        for (int h = threadIdx.x; h < H; h += blockDim.x)
+            o[h] = tot > eps ? __fdiv_rn(__fmul_rn(rb[h], rw[h]), tot) : allowed_prob[node * H + h];
+    }
+}
+
+}  // namespace
+
+int sm_count();
+
+}  // namespace p2b
+
+using namespace p2b;
+
+#define STEP_CHECK(name) return check_cuda(cudaGetLastError(), name)
+#define GRID_ELEMS(n) blocks_for((n), sm_count() * 16)
+#define GRID_ROWS(r) ((int)((r) < (long long)sm_count() * 8 ? ((r) > 0 ? (r) : 1) : (long long)sm_count() * 8))
+
+extern "C" {
+
+int p2b_step_dcfr_update(const float* regrets, float* cumulative, float* weight_sums, float* positive_out,
+                         const float* scalars4, int64_t n, int apply_dcfr, int cfr_plus, void* stream) {
+    if (n <= 0) return P2B_OK;
+    dcfr_update_kernel<<<GRID_ELEMS(n), kThreads, 0, (cudaStream_t)stream>>>(regrets, cumulative, weight_sums,
+                                                                            positive_out, scalars4, n, apply_dcfr, cfr_plus);
+    STEP_CHECK("dcfr_update_kernel");
+}
+
+int p2b_step_block_normalize(float* target, const uint8_t* allowed, const float* allowed_prob, int64_t rows,
+                             int32_t rows_per_outer, int32_t H, float eps, void* stream) {
+    if (rows <= 0) return P2B_OK;
+    block_normalize_kernel<<<GRID_ROWS(rows), kThreads, 0, (cudaStream_t)stream>>>(target, allowed, allowed_prob, rows,
+                                                                                  rows_per_outer, H, eps);
+    STEP_CHECK("block_normalize_kernel");
+}
+
+int p2b_step_regret_matching_divide(const float* positive, const float* denom, const float* uniform, float* out,
+                                    int64_t n, float eps, void* stream) {
+    if (n <= 0) return P2B_OK;
+    regret_matching_divide_kernel<<<GRID_ELEMS(n), kThreads, 0, (cudaStream_t)stream>>>(positive, denom, uniform, out, n, eps);
+    STEP_CHECK("regret_matching_divide_kernel");
+}
+
+int p2b_step_weight_child_values(const float* values, const int64_t* prev_actor, const float* policy_hero,
+                                 const float* policy_opp, float* out, int64_t M, int32_t H, void* stream) {
+    if (M <= 0) return P2B_OK;
+    weight_child_values_kernel<<<GRID_ELEMS(M * 2 * H), kThreads, 0, (cudaStream_t)stream>>>(
+        values, (const long long*)prev_actor, policy_hero, policy_opp, out, M, H);
+    STEP_CHECK("weight_child_values_kernel");
+}
+
+int p2b_step_update_average_values(float* values_avg, const float* latest, const float* old_w, const float* new_w,
+                                   const float* inv_total, int64_t n, void* stream) {
+    if (n <= 0) return P2B_OK;
+    update_average_values_kernel<<<GRID_ELEMS(n), kThreads, 0, (cudaStream_t)stream>>>(values_avg, latest, old_w, new_w,
+                                                                                      inv_total, n);
+    STEP_CHECK("update_average_values_kernel");
+}
+
+int p2b_step_mix_zero_sum(const float* a, const float* b, const float* beliefs, const uint8_t* ignore,
+                          const float* coef_a, const float* coef_b, const float* scale, float* out, int64_t rows,
+                          int32_t H, int subtract_b, int enforce_zero_sum, void* stream) {
+    if (rows <= 0) return P2B_OK;
+    mix_zero_sum_kernel<<<GRID_ROWS(rows), kThreads, 0, (cudaStream_t)stream>>>(a, b, beliefs, ignore, coef_a, coef_b, scale,
+                                                                               out, rows, H, subtract_b, enforce_zero_sum);
+    STEP_CHECK("mix_zero_sum_kernel");
+}
+
+int p2b_step_scaled_difference(const float* a, const float* b, const float* coef_a, const float* coef_b, float* out,
+                               int64_t n, void* stream) {
+    if (n <= 0) return P2B_OK;
+    scaled_difference_kernel<<<GRID_ELEMS(n), kThreads, 0, (cudaStream_t)stream>>>(a, b, coef_a, coef_b, out, n);
+    STEP_CHECK("scaled_difference_kernel");
+}
+
+int p2b_step_regret_tail(const float* values_achieved, const float* actor_values, const float* src_weights,
+                         const int64_t* parent_index, const int64_t* prev_actor, float* regrets, int64_t bottom,
+                         int64_t total, int32_t H, void* stream) {
+    if (total <= bottom) return P2B_OK;
+    regret_tail_kernel<<<GRID_ELEMS((total - bottom) * H), kThreads, 0, (cudaStream_t)stream>>>(
+        values_achieved, actor_values, src_weights, (const long long*)parent_index, (const long long*)prev_actor, regrets,
+        bottom, total, H);
+    STEP_CHECK("regret_tail_kernel");
+}
+
+int p2b_step_average_policy_mix(const float* reach, const float* reach_avg, const float* policy, float* policy_avg,
+                                const int64_t* to_act, const int64_t* parent_index, const float* old_w,
+                                const float* new_w, const float* total_w, int64_t bottom, int64_t total, int32_t H,
+                                float eps, void* stream) {
+    if (total <= bottom) return P2B_OK;
+    average_policy_mix_kernel<<<GRID_ELEMS((total - bottom) * H), kThreads, 0, (cudaStream_t)stream>>>(
+        reach, reach_avg, policy, policy_avg, (const long long*)to_act, (const long long*)parent_index, old_w, new_w,
+        total_w, bottom, total, H, eps);
+    STEP_CHECK("average_policy_mix_kernel");
+}
+
+int p2b_step_parent_sum(const float* values, const int64_t* child_offsets, const int64_t* child_count, float* out,
+                        int64_t num_parents, int32_t H, int broadcast_to_children, int64_t out_offset, void* stream) {
+    if (num_parents <= 0) return P2B_OK;
+    parent_sum_kernel<<<GRID_ELEMS(num_parents * H), kThreads, 0, (cudaStream_t)stream>>>(
+        values, (const long long*)child_offsets, (const long long*)child_count, out, num_parents, H, broadcast_to_children,
+        out_offset);
+    STEP_CHECK("parent_sum_kernel");
+}
+
+int p2b_step_divide_by_parent_sum(const float* pos, const float* fallback, const float* parent_sum,
+                                  const int64_t* parent_index, float* out, int64_t num_children, int32_t H, float eps,
+                                  void* stream) {
+    if (num_children <= 0) return P2B_OK;
+    divide_by_parent_sum_kernel<<<GRID_ELEMS(num_children * H), kThreads, 0, (cudaStream_t)stream>>>(
+        pos, fallback, parent_sum, (const long long*)parent_index, out, num_children, H, eps);
+    STEP_CHECK("divide_by_parent_sum_kernel");
+}
+
+int p2b_step_unblocked_mass(const float* src, const int64_t* row_index, float* out, int64_t rows, void* stream) {
+    if (rows <= 0) return P2B_OK;
+    int rc = ensure_tables();
+    if (rc) return rc;
+    unblocked_mass_kernel<<<GRID_ROWS(rows), kThreads, 0, (cudaStream_t)stream>>>(src, (const long long*)row_index,
+                                                                                 device_combo_table(), out, rows);
+    STEP_CHECK("unblocked_mass_kernel");
+}
+
+int p2b_step_unblocked_mass_ratio(const float* numer, const float* denom, const int64_t* parent_index, float* out,
+                                  int64_t rows, float eps, void* stream) {
+    if (rows <= 0) return P2B_OK;
+    int rc = ensure_tables();
+    if (rc) return rc;
+    unblocked_ratio_kernel<<<GRID_ROWS(rows), kThreads, 0, (cudaStream_t)stream>>>(numer, denom, (const long long*)parent_index,
+                                                                                  device_combo_table(), out, rows, eps);
+    STEP_CHECK("unblocked_ratio_kernel");
+}
+
+int p2b_step_weighted_parent_sum(float* values, const int64_t* prev_actor, const float* policy_hero,
+                                 const float* policy_opp, const int64_t* child_offsets, const int64_t* child_count,
+                                 int64_t parent_base, int64_t num_parents, int32_t H, void* stream) {
+    if (num_parents <= 0) return P2B_OK;
+    weighted_parent_sum_kernel<<<GRID_ELEMS(num_parents * 2 * H), kThreads, 0, (cudaStream_t)stream>>>(
+        values, (const long long*)prev_actor, policy_hero, policy_opp, (const long long*)child_offsets,
+        (const long long*)child_count, parent_base, num_parents, H);
+    STEP_CHECK("weighted_parent_sum_kernel");
+}
+
+int p2b_step_reach_weights(float* reach, const float* policy, const uint8_t* allowed, const int64_t* parent_index,
+                           const int64_t* prev_actor, int64_t start, int64_t end, int32_t H, void* stream) {
+    if (end <= start) return P2B_OK;
+    reach_weights_kernel<<<GRID_ELEMS((end - start) * H), kThreads, 0, (cudaStream_t)stream>>>(
+        reach, policy, allowed, (const long long*)parent_index, (const long long*)prev_actor, start, end, H);
+    STEP_CHECK("reach_weights_kernel");
+}
+
+int p2b_step_deep_beliefs(float* out, const float* root_beliefs, const float* reach, const float* allowed_prob,
+                          const int64_t* root_index, int64_t num_roots, int64_t total, int32_t H, float eps,
+                          void* stream) {
+    if (total <= num_roots) return P2B_OK;
+    deep_beliefs_kernel<<<GRID_ROWS((total - num_roots) * 2), kThreads, 0, (cudaStream_t)stream>>>(
+        out, root_beliefs, reach, allowed_prob, (const long long*)root_index, num_roots, total, H, eps);
+    STEP_CHECK("deep_beliefs_kernel");
+}
+
+}  // extern "C"
