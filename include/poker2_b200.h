@@ -183,6 +183,22 @@ int p2b_step_deep_beliefs(float* out, const float* root_beliefs, const float* re
                           const int64_t* root_index, int64_t num_roots, int64_t total, int32_t H, float eps,
                           void* stream);
 
+/* ---- chance nodes (src/p2/search/chance_node_helper.py:359-479, single_card_chance_values) --
+ * p2b_chance_expand: for each root b, one sample per card not on its board (ascending card
+ * id; samples grouped by root).  boards [num_roots, board_len] int64 with -1 for empty
+ * slots; sample_offsets [num_roots+1] int64 = exclusive prefix of the number of free cards;
+ * pre_beliefs [num_roots,2,1326].  Outputs per sample: post_beliefs [S,2,1326] (combos
+ * touching the extended board zeroed, rows renormalised, uniform fallback at mass <= 1e-12,
+ * :434-444), root_lookup [S] int64 and board_samples [S, board_len] int64 (:402-418). */
+int p2b_chance_expand(const float* pre_beliefs, const int64_t* boards, int32_t board_len, const int64_t* sample_offsets,
+                      int64_t num_roots, int64_t num_samples, float* post_beliefs, int64_t* root_lookup,
+                      int64_t* board_samples, void* stream);
+/* p2b_indexed_add_rows: out[index[i], :] (+)= src[i, :] in ascending i, for a sorted int64
+ * index (the index_add_ of :468-475); mean != 0 divides by max(count,1) (:476-477);
+ * accumulate == 0 overwrites out instead of adding to it. */
+int p2b_indexed_add_rows(float* out, const int64_t* index, const float* src, int64_t num_src, int64_t num_out,
+                         int64_t width, int mean, int accumulate, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

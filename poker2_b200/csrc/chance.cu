@@ -1,0 +1,166 @@
+// Chance-node helpers: belief expansion over the next public card and the ordered
+// indexed add that averages the leaf-model values back per root
+// (p2/search/chance_node_helper.py:359-479, `single_card_chance_values`).
+#include "common.cuh"
+
+namespace p2b {
+namespace {
+
+constexpr int kThreads = 256;
+
+// One block per (root, next card) sample.  boards: [B, board_len] int64, -1 = empty slot.
+// Sample s of root b is the s-th card (ascending id) not on b's board; sample rows are
+// grouped by root in root order, which is the order upstream's nonzero() produces
+// (:402-414).  Writes, per sample: the root index, the board with the new card in the first
+// empty slot (:416-418), and both players' beliefs with every combo touching the extended
+// board zeroed and the row renormalised; a row whose mass is <= 1e-12 becomes uniform over
+// the allowed combos (:434-444).
+__global__ void chance_expand_kernel(const float* __restrict__ pre_beliefs, const long long* __restrict__ boards,
+                                     int board_len, const long long* __restrict__ sample_offsets, long long num_roots,
+                                     const ComboTable* __restrict__ combos, float* __restrict__ post_beliefs,
+                                     long long* __restrict__ root_lookup, long long* __restrict__ board_samples) {
+    __shared__ double red[kThreads / 32];
+    __shared__ int s_root;
+    __shared__ int s_card;
+    __shared__ unsigned long long s_mask;
+    const long long total = sample_offsets[num_roots];
+    for (long long smp = blockIdx.x; smp < total; smp += gridDim.x) {
+        if (threadIdx.x == 0) {
+            // root of this sample: last b with sample_offsets[b] <= smp
+            long long lo = 0, hi = num_roots - 1;
+            while (lo < hi) {
+                const long long mid = (lo + hi + 1) >> 1;
+                if (sample_offsets[mid] <= smp) lo = mid;
+                else hi = mid - 1;
+            }
+            unsigned long long mask = 0;
+            int ncards = 0;
+            for (int j = 0; j < board_len; ++j) {
+                const long long c = boards[lo * board_len + j];
+                if (c >= 0) {
+                    mask |= 1ull << c;
+                    ++ncards;
+                }
+            }
+            // the k-th free card, k = smp - offset
+            int k = (int)(smp - sample_offsets[lo]), card = 0;
+            for (;; ++card)
+                if (!((mask >> card) & 1ull) && k-- == 0) break;
+            s_root = (int)lo;
+            s_card = card;
+            s_mask = mask | (1ull << card);
+            root_lookup[smp] = lo;
+            for (int j = 0; j < board_len; ++j) {
+                long long c = boards[lo * board_len + j];
+                if (j == ncards) c = card;
+                board_samples[smp * board_len + j] = c;
+            }
+        }
+        __syncthreads();
+        const unsigned long long mask = s_mask;
+        const long long b = s_root;
+        for (int p = 0; p < 2; ++p) {
+            const float* src = pre_beliefs + (b * 2 + p) * P2B_NUM_HANDS;
+            float* dst = post_beliefs + (smp * 2 + p) * P2B_NUM_HANDS;
+            double s = 0.0;
+            int n_allowed = 0;
+            for (int h = threadIdx.x; h < P2B_NUM_HANDS; h += blockDim.x) {
+                const bool ok = (((mask >> combos->c1[h]) | (mask >> combos->c2[h])) & 1ull) == 0;
+                const float v = ok ? src[h] : 0.0f;
+                dst[h] = v;
+                s += (double)v;
+                n_allowed += ok;
+            }
+            // block sums (mass and number of allowed combos)
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) {
+                s += __shfl_xor_sync(0xffffffffu, s, d);
+                n_allowed += __shfl_xor_sync(0xffffffffu, n_allowed, d);
+            }
+            __shared__ int cnt[kThreads / 32];
+            __syncthreads();
+            if ((threadIdx.x & 31) == 0) {
+                red[threadIdx.x >> 5] = s;
+                cnt[threadIdx.x >> 5] = n_allowed;
+            }
+            __syncthreads();
+            double tot = 0.0;
+            int nall = 0;
+            for (int w = 0; w < kThreads / 32; ++w) {
+                tot += red[w];
+                nall += cnt[w];
+            }
+            const float sum = (float)tot;
+            const float uni = __fdiv_rn(1.0f, fmaxf((float)nall, 1.0f));
+            for (int h = threadIdx.x; h < P2B_NUM_HANDS; h += blockDim.x) {
+                const bool ok = (((mask >> combos->c1[h]) | (mask >> combos->c2[h])) & 1ull) == 0;
+                dst[h] = sum > 1e-12f ? __fdiv_rn(dst[h], fmaxf(sum, 1e-12f)) : (ok ? uni : 0.0f);
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// out[index[i], :] += src[i, :] for i in ascending order; `index` must be sorted
+// (non-decreasing), as the chance helper's root_lookup is.  Each output element is owned
+// by one thread, so the additions happen in index order: deterministic, no atomics.  With
+// `mean` the sum is divided by max(count, 1) (:468-477).
+__global__ void indexed_add_rows_kernel(float* __restrict__ out, const long long* __restrict__ index,
+                                        const float* __restrict__ src, long long num_src, long long num_out,
+                                        long long width, int mean, int accumulate) {
+    const long long n = num_out * width;
+    for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < n; e += (long long)gridDim.x * blockDim.x) {
+        const long long row = e / width, col = e % width;
+        // first i with index[i] >= row
+        long long lo = 0, hi = num_src;
+        while (lo < hi) {
+            const long long mid = (lo + hi) >> 1;
+            if (index[mid] < row) lo = mid + 1;
+            else hi = mid;
+        }
+        float acc = accumulate ? out[e] : 0.0f;
+        long long i = lo;
+        for (; i < num_src && index[i] == row; ++i) acc = __fadd_rn(acc, src[i * width + col]);
+        if (mean) acc = __fdiv_rn(acc, fmaxf((float)(i - lo), 1.0f));
+        out[e] = acc;
+    }
+}
+
+}  // namespace
+
+int sm_count();
+
+}  // namespace p2b
+
+using namespace p2b;
+
+extern "C" {
+
+int p2b_chance_expand(const float* pre_beliefs, const int64_t* boards, int32_t board_len, const int64_t* sample_offsets,
+                      int64_t num_roots, int64_t num_samples, float* post_beliefs, int64_t* root_lookup,
+                      int64_t* board_samples, void* stream) {
+    if (num_roots <= 0 || num_samples <= 0) return P2B_OK;
+    if (!pre_beliefs || !boards || !sample_offsets || !post_beliefs || !root_lookup || !board_samples)
+        return set_error(P2B_ERR_ARG, "p2b_chance_expand: null pointer");
+    int rc = ensure_tables();
+    if (rc) return rc;
+    long long grid = num_samples;
+    if (grid > (long long)sm_count() * 16) grid = (long long)sm_count() * 16;
+    chance_expand_kernel<<<(unsigned)grid, kThreads, 0, (cudaStream_t)stream>>>(
+        pre_beliefs, (const long long*)boards, board_len, (const long long*)sample_offsets, num_roots,
+        device_combo_table(), post_beliefs, (long long*)root_lookup, (long long*)board_samples);
+    return check_cuda(cudaGetLastError(), "chance_expand_kernel");
+}
+
+int p2b_indexed_add_rows(float* out, const int64_t* index, const float* src, int64_t num_src, int64_t num_out,
+                         int64_t width, int mean, int accumulate, void* stream) {
+    if (num_out <= 0 || width <= 0) return P2B_OK;
+    if (!out || (num_src > 0 && (!index || !src))) return set_error(P2B_ERR_ARG, "p2b_indexed_add_rows: null pointer");
+    long long blocks = (num_out * width + kThreads - 1) / kThreads;
+    if (blocks > (long long)sm_count() * 16) blocks = (long long)sm_count() * 16;
+    indexed_add_rows_kernel<<<(unsigned)blocks, kThreads, 0, (cudaStream_t)stream>>>(
+        out, (const long long*)index, src, num_src, num_out, width, mean, accumulate);
+    return check_cuda(cudaGetLastError(), "indexed_add_rows_kernel");
+}
+
+}  // extern "C"

@@ -218,3 +218,53 @@ def gen_cfr() -> None:
 
 
 SECTIONS = {"tree": gen_tree, "cfr": gen_cfr}
+
+
+class _BeliefEchoModel:
+    """Deterministic stand-in for the leaf model of the chance helper: values are a fixed
+    function of the sample's beliefs and newest board card."""
+
+    def __init__(self, weights):
+        self.w = weights
+
+    def eval(self):
+        pass
+
+    def __call__(self, features, **kw):
+        from p2.models.model_output import ModelOutput
+
+        n = len(features)
+        bel = features.beliefs.view(n, 2, 1326).float()
+        newest = features.board.gather(1, ((features.board >= 0).sum(dim=1) - 1).view(-1, 1)).squeeze(1)
+        scale = self.w[newest].view(-1, 1, 1)
+        hv = torch.stack([bel[:, 1], -bel[:, 0]], dim=1) * scale + 0.25 * scale
+        return ModelOutput(policy_logits=None, value=torch.zeros(n), hand_values=hv)
+
+
+def gen_chance() -> None:
+    """single_card_chance_values (chance_node_helper.py:359-479) on turn roots."""
+    import warnings
+
+    from p2.models.mlp.mlp_features import MLPFeatures
+    from p2.search.chance_node_helper import ChanceNodeHelper
+
+    g = torch.Generator().manual_seed(9)
+    B, n_board = 4, 4
+    boards = torch.full((B, 5), -1, dtype=torch.long)
+    for b in range(B):
+        boards[b, :n_board] = torch.randperm(52, generator=g)[:n_board]
+    bel = torch.empty(B, 2, 1326).exponential_(generator=g)
+    bel = bel / bel.sum(-1, keepdim=True)
+    bel[0, 1] = 0
+    w = torch.randn(52, generator=torch.Generator().manual_seed(2))
+    helper = ChanceNodeHelper(device=torch.device("cpu"), float_dtype=torch.float32, num_players=2,
+                              model=_BeliefEchoModel(w), generator=g)
+    feats = MLPFeatures(context=torch.zeros(B, 4), street=torch.full((B,), 2), to_act=torch.zeros(B, dtype=torch.long),
+                        board=boards, beliefs=bel.reshape(B, -1))
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        out = helper.single_card_chance_values(torch.arange(B), feats, bel, boards)
+    save("chance.npz", boards=boards.numpy(), beliefs=bel.numpy(), weights=w.numpy(), expected=out.numpy())
+
+
+SECTIONS["chance"] = gen_chance

@@ -37,3 +37,19 @@ def test_unblocked_oracle_bit_exact(golden_dir):
     z = np.load(os.path.join(golden_dir, "unblocked.npz"))
     got = unblocked.unblocked_mass(torch.from_numpy(z["x"]))
     assert torch.equal(got, torch.from_numpy(z["y"]))
+
+
+def test_chance_oracle_matches_upstream_helper(golden_dir):
+    """oracle/chance.py against ChanceNodeHelper.single_card_chance_values run upstream."""
+    from oracle import chance as ochance
+
+    z = np.load(os.path.join(golden_dir, "chance.npz"))
+    w = torch.from_numpy(z["weights"])
+
+    def value_fn(post, samples, lookup):
+        newest = samples.gather(1, ((samples >= 0).sum(dim=1) - 1).view(-1, 1)).squeeze(1)
+        scale = w[newest].view(-1, 1, 1)
+        return torch.stack([post[:, 1], -post[:, 0]], dim=1) * scale + 0.25 * scale
+
+    got = ochance.single_card_chance_values(torch.from_numpy(z["beliefs"]), torch.from_numpy(z["boards"]), value_fn)
+    assert torch.equal(got, torch.from_numpy(z["expected"]))
