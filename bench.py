@@ -180,15 +180,16 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
     trees = ptree.build_trees(ptree.root_states(pot.numpy(), stack.numpy()), list(BET_BINS), MAX_DEPTH,
                               max_raises=MAX_RAISES)
     layout = solver.device_layout(trees, boards.numpy())
-    sv = solver.SubgameSolver(layout, boards, device)
+    sv = solver.SubgameSolver(layout, boards, device, exploitability=True)
     rb = solver.pad_rows(ranges.to(device)).contiguous()
     scal = solver.iteration_scalars(ITERATIONS)
     gathered = None
 
     def step():
         res = sv.solve(rb, scal)
-        if distributed:  # the one exchange of the path: value targets of all shards
+        if distributed:  # the one exchange of the path: value targets and exploitability statistics
             sharding.gather_rows(res.root_values)
+            sharding.reduce_exploitability(res.exploitability)
         return res
 
     for _ in range(args.warmup):
@@ -236,12 +237,14 @@ def run_e2e(args, solver, sv, boards, ranges, pot, stack, layout, scal, gathered
 
     def e2e_step():
         res, _ = solver.solve_subgames(h_boards, h_ranges, pot, stack, iterations=ITERATIONS, bet_bins=BET_BINS,
-                                       max_depth=MAX_DEPTH, max_raises=MAX_RAISES, device=device)
-        if distributed:
-            from poker2_b200 import sharding
+                                       max_depth=MAX_DEPTH, max_raises=MAX_RAISES, device=device, exploitability=True)
+        from poker2_b200 import sharding
 
+        if distributed:
             sharding.gather_rows(res.root_values)
-        return res.to_host(pinned)
+        out = res.to_host(pinned)
+        out["stats"] = sharding.reduce_exploitability(res.exploitability)  # one small D2H read
+        return out
 
     sv.release()
     torch.cuda.empty_cache()
@@ -258,7 +261,7 @@ def run_e2e(args, solver, sv, boards, ranges, pot, stack, layout, scal, gathered
         dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
     e2e_value = units_per_step * e2e_steps / float(e2e_s.item())
     h2d = h_boards.numel() * 2 + h_ranges.numel() * 4 + layout.nodes.nbytes + layout.subgames.nbytes + scal.nbytes
-    d2h = sum(t.numel() * 4 for t in out.values())
+    d2h = sum(t.numel() * 4 for t in out.values() if torch.is_tensor(t)) + 4 * 8
     return {"value": e2e_value, "unit": "subgame-iterations/s", "h2d_bytes_per_step": int(h2d),
             "d2h_bytes_per_step": int(d2h), "steps": e2e_steps}
 

@@ -74,6 +74,9 @@ int p2b_showdown_values(const unsigned char* tables, const int32_t* table_of_row
  *  root_beliefs [num_subgames,2,1328] input ranges
  *  regrets, weight_sums (may be NULL), policy_avg, policy (may be NULL): [rows,1328] out
  *  root_values [num_subgames,2,1328] out; values_avg, beliefs_avg [rows,2,1328] out (may be NULL)
+ *  exploitability [num_subgames], br_values [num_subgames,2] out (may be NULL; need values_avg):
+ *             local exploitability of the average policy and the best-response value of each
+ *             player at the root (cfr_evaluator.py:718-764)
  *  scratch    p2b_cfr_scratch_floats(max_internal, num_blocks) floats of work space
  *  scalars    [iterations] 32-byte records {float t^alpha, t^alpha+1, t^beta, t^beta+1,
  *             mix_old, mix_new, fl(mix_old+mix_new); int32 do_mix}
@@ -84,8 +87,8 @@ int p2b_showdown_values(const unsigned char* tables, const int32_t* table_of_row
 int p2b_cfr_solve(const void* subgames, const void* nodes, int32_t num_subgames, int32_t max_children,
                   int32_t max_internal, const unsigned char* tables, const float* root_beliefs,
                   float* regrets, float* weight_sums, float* policy_avg, float* policy,
-                  float* root_values, float* values_avg, float* beliefs_avg, float* scratch,
-                  int64_t scratch_floats, const void* scalars, int32_t iterations, int32_t cfr_plus,
+                  float* root_values, float* values_avg, float* beliefs_avg, float* exploitability,
+                  float* br_values, float* scratch, int64_t scratch_floats, const void* scalars, int32_t iterations, int32_t cfr_plus,
                   int32_t init_depth, int32_t* work_counter, int32_t num_blocks, void* stream);
 int64_t p2b_cfr_scratch_floats(int32_t max_internal, int32_t num_blocks);
 int p2b_cfr_default_blocks(void);
@@ -117,8 +120,8 @@ int p2b_cfr_solve_noalloc(const void* subgames, const void* nodes, int32_t num_s
                           int32_t max_children, int32_t max_internal, const unsigned char* tables,
                           const float* root_beliefs, float* regrets, float* weight_sums,
                           float* policy_avg, float* policy, float* root_values, float* values_avg,
-                          float* beliefs_avg, const void* scalars, int32_t iterations,
-                          int32_t cfr_plus, int32_t init_depth, void* stream);
+                          float* beliefs_avg, float* exploitability, float* br_values, const void* scalars,
+                          int32_t iterations, int32_t cfr_plus, int32_t init_depth, void* stream);
 int64_t p2b_cfr_noalloc_scratch_floats(void);
 
 /* ---- step-level kernels (src/p2/search/fused_cfr_triton.py) ----------------------------

@@ -29,10 +29,10 @@ _SIGNATURES = {
     "p2b_compare7_planes": [_vp, _i64, _vp, _vp],
     "p2b_rank_hands": [_vp, _i64, _vp, _vp, _vp, _vp],
     "p2b_showdown_values": [_vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _i64, _vp],
-    "p2b_cfr_solve": [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp,
-                      _i32, _i32, _i32, _vp, _i32, _vp],
-    "p2b_cfr_solve_noalloc": [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32,
-                              _i32, _vp],
+    "p2b_cfr_solve": [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64,
+                      _vp, _i32, _i32, _i32, _vp, _i32, _vp],
+    "p2b_cfr_solve_noalloc": [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                              _i32, _i32, _i32, _vp],
     "p2b_step_dcfr_update": [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _vp],
     "p2b_step_block_normalize": [_vp, _vp, _vp, _i64, _i32, _i32, _f32, _vp],
     "p2b_step_regret_matching_divide": [_vp, _vp, _vp, _vp, _i64, _f32, _vp],

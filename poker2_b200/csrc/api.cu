@@ -76,14 +76,16 @@ int64_t p2b_cfr_scratch_floats(int32_t max_internal, int32_t num_blocks) {
 int p2b_cfr_solve(const void* subgames, const void* nodes, int32_t num_subgames, int32_t max_children,
                   int32_t max_internal, const unsigned char* tables, const float* root_beliefs, float* regrets,
                   float* weight_sums, float* policy_avg, float* policy, float* root_values, float* values_avg,
-                  float* beliefs_avg, float* scratch, int64_t scratch_floats, const void* scalars, int32_t iterations,
-                  int32_t cfr_plus, int32_t init_depth, int32_t* work_counter, int32_t num_blocks, void* stream) {
+                  float* beliefs_avg, float* exploitability, float* br_values, float* scratch, int64_t scratch_floats,
+                  const void* scalars, int32_t iterations, int32_t cfr_plus, int32_t init_depth, int32_t* work_counter,
+                  int32_t num_blocks, void* stream) {
     P2B_REQUIRE(num_subgames >= 0 && iterations >= 0, "negative count");
     if (num_subgames == 0) return P2B_OK;
     P2B_REQUIRE(subgames && nodes && root_beliefs && regrets && policy_avg && root_values && scratch && work_counter,
                 "null pointer");
     P2B_REQUIRE(iterations == 0 || scalars, "null scalars");
     P2B_REQUIRE(max_internal >= 1, "max_internal must be positive");
+    P2B_REQUIRE(!exploitability || values_avg, "exploitability needs values_avg");
     if (num_blocks <= 0) num_blocks = cfr_default_blocks();
     if (num_blocks > num_subgames) num_blocks = num_subgames;
     P2B_REQUIRE(scratch_floats >= cfr_scratch_floats(max_internal) * num_blocks, "scratch too small");
@@ -107,6 +109,8 @@ int p2b_cfr_solve(const void* subgames, const void* nodes, int32_t num_subgames,
     p.root_values = root_values;
     p.values_avg = values_avg;
     p.beliefs_avg = beliefs_avg;
+    p.exploitability = exploitability;
+    p.br_values = br_values;
     p.scratch = scratch;
     p.scratch_stride = cfr_scratch_floats(max_internal);
     p.max_internal = max_internal;
@@ -125,12 +129,13 @@ int64_t p2b_cfr_noalloc_scratch_floats(void) { return cfr_static_scratch_floats(
 int p2b_cfr_solve_noalloc(const void* subgames, const void* nodes, int32_t num_subgames, int32_t max_children,
                           int32_t max_internal, const unsigned char* tables, const float* root_beliefs, float* regrets,
                           float* weight_sums, float* policy_avg, float* policy, float* root_values, float* values_avg,
-                          float* beliefs_avg, const void* scalars, int32_t iterations, int32_t cfr_plus,
-                          int32_t init_depth, void* stream) {
+                          float* beliefs_avg, float* exploitability, float* br_values, const void* scalars,
+                          int32_t iterations, int32_t cfr_plus, int32_t init_depth, void* stream) {
     P2B_REQUIRE(num_subgames >= 0 && iterations >= 0, "negative count");
     if (num_subgames == 0) return P2B_OK;
     P2B_REQUIRE(subgames && nodes && root_beliefs && regrets && policy_avg && root_values && scalars, "null pointer");
     P2B_REQUIRE(max_internal >= 1, "max_internal must be positive");
+    P2B_REQUIRE(!exploitability || values_avg, "exploitability needs values_avg");
     const uintptr_t align = reinterpret_cast<uintptr_t>(subgames) | reinterpret_cast<uintptr_t>(nodes) |
                             reinterpret_cast<uintptr_t>(tables) | reinterpret_cast<uintptr_t>(root_beliefs) |
                             reinterpret_cast<uintptr_t>(regrets) | reinterpret_cast<uintptr_t>(weight_sums) |
@@ -151,6 +156,8 @@ int p2b_cfr_solve_noalloc(const void* subgames, const void* nodes, int32_t num_s
     p.root_values = root_values;
     p.values_avg = values_avg;
     p.beliefs_avg = beliefs_avg;
+    p.exploitability = exploitability;
+    p.br_values = br_values;
     p.max_internal = max_internal;
     p.scalars = static_cast<const IterScalars*>(scalars);
     p.iterations = iterations;

@@ -744,6 +744,140 @@ __device__ __forceinline__ void sweep_up(int mode, int pass, const CfrParams& p,
     }
 }
 
+// ---- best-response sweeps (local exploitability of the average policy) -------------------
+// Upstream: `_compute_exploitability` / `_best_response_values`
+// (p2/search/cfr_evaluator.py:603-764).  Runs after the final pass, whose reach rows and
+// normalisation sums are still in place.  Leaf values are the final-pass values clamped to
+// [-1,1] (:730), read back from p.values_avg.  deviator < 0: plain expectation under the
+// average policy (`base_values`, :732-735); deviator = d: player d plays a best response.
+// Returns the root values of both players in root_v (index = player).
+template <int VPT, int MAXC>
+__device__ __forceinline__ void sweep_br(int deviator, const CfrParams& p, Block& B, const HandInfo<VPT>& hi,
+                                         const FV<VPT> (&prior)[2], const FV<VPT> (&root_b)[2], int tid,
+                                         FV<VPT> (&root_v)[2]) {
+    constexpr int kRowM = 2;
+    FV<VPT> mask;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) mask.v[i] = hi.allowed[i] ? 1.0f : 0.0f;
+    for (int j = B.sg.n_nodes - 1; j >= 0; --j) {
+        const NodeRec nd = B.nodes[j];
+        if (nd.kind != kInternal) continue;
+        const int a = nd.to_act, o = 1 - a, k = nd.n_children, fc = nd.first_child, ii = nd.internal_idx;
+        const bool deviates = deviator == a;
+        FV<VPT> b_a;  // beliefs of the acting player under the average policy
+        if (j == 0) {
+            b_a = pick<VPT>(root_b, a);
+        } else {
+            const FV<VPT> prior_a = pick<VPT>(prior, a);
+            const FV<VPT> r_a = ldv<VPT>(B.reach(ii, a), tid);
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) b_a.v[i] = __fmul_rn(prior_a.v[i], r_a.v[i]);
+            apply_norm<VPT>(B, hi, b_a, B.sig[j * 2 + a]);
+        }
+        // child values of both players (leaves: clamped final values; internal: this sweep)
+        FV<VPT> Va[MAXC], Vo[MAXC], P[MAXC];
+#pragma unroll
+        for (int c = 0; c < MAXC; ++c) {
+            if (c >= k) continue;
+            const NodeRec ch = B.nodes[fc + c];
+            if (ch.kind == kInternal) {
+                Va[c] = ldv<VPT>(B.val(ch.internal_idx, a), tid);
+                Vo[c] = ldv<VPT>(B.val(ch.internal_idx, o), tid);
+            } else {
+                Va[c] = ldv<VPT>(B.row2(p.values_avg, fc + c, a), tid);
+                Vo[c] = ldv<VPT>(B.row2(p.values_avg, fc + c, o), tid);
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) {
+                    Va[c].v[i] = fminf(fmaxf(Va[c].v[i], -1.0f), 1.0f);
+                    Vo[c].v[i] = fminf(fmaxf(Vo[c].v[i], -1.0f), 1.0f);
+                }
+            }
+            P[c] = ldv<VPT>(B.row1(p.policy_avg, fc + c), tid);
+        }
+        // best action of the deviating player per hand: first maximum (argmax, :653-660)
+        FV<VPT> best_v;
+        int best_c[VPT];
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            best_v.v[i] = Va[0].v[i];
+            best_c[i] = 0;
+        }
+#pragma unroll
+        for (int c = 1; c < MAXC; ++c)
+            if (c < k) {
+#pragma unroll
+                for (int i = 0; i < VPT; ++i)
+                    if (Va[c].v[i] > best_v.v[i]) {
+                        best_v.v[i] = Va[c].v[i];
+                        best_c[i] = c;
+                    }
+            }
+        // rows whose unblocked mass is needed: the acting player's beliefs (matchup mass) and,
+        // per child, either the belief mass that picks it (deviator) or belief x policy
+        stv<VPT>(B.stage_row(0), tid, b_a);
+        stv<VPT>(B.stage_row(1), tid, b_a);
+#pragma unroll
+        for (int c = 0; c < MAXC; ++c)
+            if (c < k) {
+                FV<VPT> m;
+#pragma unroll
+                for (int i = 0; i < VPT; ++i)
+                    m.v[i] = deviates ? (best_c[i] == c ? b_a.v[i] : 0.0f) : __fmul_rn(P[c].v[i], b_a.v[i]);
+                stv<VPT>(B.stage_row(kRowM + c), tid, m);
+            }
+        __syncthreads();
+        {
+            int pc_rows[2] = {0, 0};
+            node_tables(B, 0, 2 + k, pc_rows, 0);
+        }
+        FV<VPT> acc_a, acc_o;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) acc_a.v[i] = acc_o.v[i] = 0.0f;
+#pragma unroll
+        for (int c = 0; c < MAXC; ++c)
+            if (c < k) {
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) {
+                    const float m = deviates ? (best_c[i] == c ? b_a.v[i] : 0.0f) : __fmul_rn(P[c].v[i], b_a.v[i]);
+                    const float blk = unblocked(B.cs + (kRowM + c) * 52, B.S[kRowM + c], hi.c1[i], hi.c2[i], m);
+                    const float den = unblocked(B.cs, B.S[0], hi.c1[i], hi.c2[i], b_a.v[i]);
+                    const float w = den > 1e-5f ? __fdiv_rn(blk, den) : 0.0f;
+                    acc_o.v[i] = __fadd_rn(acc_o.v[i], __fmul_rn(w, Vo[c].v[i]));
+                    acc_a.v[i] = __fadd_rn(acc_a.v[i], __fmul_rn(Va[c].v[i], P[c].v[i]));
+                }
+            }
+        if (deviates) acc_a = best_v;
+        if (j != 0) {
+            stv<VPT>(B.val(ii, a), tid, acc_a);
+            stv<VPT>(B.val(ii, o), tid, acc_o);
+        } else {
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) {
+                root_v[0].v[i] = a == 0 ? acc_a.v[i] : acc_o.v[i];
+                root_v[1].v[i] = a == 0 ? acc_o.v[i] : acc_a.v[i];
+            }
+        }
+    }
+}
+
+// sum over hands of x*y in the reference row-reduction order; stage rows 0/1 must be free.
+template <int VPT>
+__device__ __forceinline__ void dot2_reference_order(Block& B, const FV<VPT>& x0, const FV<VPT>& x1, float (&out)[2]) {
+    const int tid = threadIdx.x;
+    __syncthreads();
+    stv<VPT>(B.stage_row(0), tid, x0);
+    stv<VPT>(B.stage_row(1), tid, x1);
+    __syncthreads();
+    const int warp = tid >> 5;
+    if (warp < 2) {
+        const float sum = row_sum_reference_order(B.stage_row(warp));
+        if ((tid & 31) == 0) B.fsum[warp] = sum;
+    }
+    __syncthreads();
+    out[0] = B.fsum[0];
+    out[1] = B.fsum[1];
+}
+
 template <int VPT>
 struct CfrThreads {
     static constexpr int value = ((P2B_HPAD / VPT + 31) / 32) * 32;  // 352 for four hands per thread, 672 for two
@@ -832,6 +966,33 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
             }
             sweep_down<VPT, MAXC>(mode, pass, p, B, hi, prior, tid);
             sweep_up<VPT, MAXC>(mode, pass, p, B, hi, prior, root_b, s, tid);
+        }
+        if (p.exploitability && p.values_avg) {
+            // local exploitability of the average policy (cfr_evaluator.py:718-764)
+            __syncthreads();
+            FV<VPT> base[2], br[2];
+            float total = 0.0f;
+            for (int d = -1; d < 2; ++d) {
+                __syncthreads();
+                sweep_br<VPT, MAXC>(d, p, B, hi, prior, root_b, tid, br);
+                if (d < 0) {
+                    base[0] = br[0];
+                    base[1] = br[1];
+                    continue;
+                }
+                const FV<VPT> rb = pick<VPT>(root_b, d), bv = pick<VPT>(br, d), sv = pick<VPT>(base, d);
+                FV<VPT> gain, val;
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) {
+                    gain.v[i] = __fmul_rn(__fsub_rn(bv.v[i], sv.v[i]), rb.v[i]);
+                    val.v[i] = __fmul_rn(bv.v[i], rb.v[i]);
+                }
+                float sums[2];
+                dot2_reference_order<VPT>(B, gain, val, sums);
+                total = d == 0 ? sums[0] : __fadd_rn(total, sums[0]);
+                if (tid == 0 && p.br_values) p.br_values[(long long)s * 2 + d] = sums[1];
+            }
+            if (tid == 0) p.exploitability[s] = total;
         }
     }
 }

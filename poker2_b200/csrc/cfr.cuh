@@ -62,6 +62,9 @@ struct CfrParams {
     float* root_values;          // [B][2][HPAD] values of the final average policy at the roots (out)
     float* values_avg;           // [rows][2][HPAD] the same for every node (out, may be null)
     float* beliefs_avg;          // [rows][2][HPAD] beliefs under the average policy (out, may be null)
+    float* exploitability;       // [B] local exploitability of the average policy (out, may be null;
+                                 // needs values_avg)
+    float* br_values;            // [B][2] best-response value of each player at the root (out, may be null)
     float* scratch;              // per-block work rows
     long long scratch_stride;    // floats per block
     int32_t max_internal;        // largest n_internal over the batch

@@ -155,6 +155,8 @@ class SolveResult:
     root_values: torch.Tensor  # [B,2,1328]
     values_avg: torch.Tensor | None  # [rows,2,1328]
     beliefs_avg: torch.Tensor | None
+    exploitability: torch.Tensor | None = None  # [B] local exploitability of the average policy
+    br_values: torch.Tensor | None = None  # [B,2] best-response values at the roots
 
     def to_host(self, pinned: dict | None = None) -> dict:
         """Copies the training targets (root values, average policy) to pinned host memory
@@ -177,7 +179,8 @@ class SubgameSolver:
 
     def __init__(self, layout: DeviceTreeLayout, boards: torch.Tensor, device: torch.device, *,
                  track_weight_sums: bool = True, keep_policy: bool = False, keep_node_values: bool = False,
-                 num_blocks: int = 0):
+                 exploitability: bool = False, num_blocks: int = 0):
+        keep_node_values = keep_node_values or exploitability  # best responses read the node values
         if device.type != "cuda":
             raise ValueError("SubgameSolver requires a CUDA device.")
         self.layout, self.device = layout, device
@@ -199,6 +202,8 @@ class SubgameSolver:
         self.root_values = torch.empty(B, 2, HPAD, **f32)
         self.values_avg = torch.zeros(rows, 2, HPAD, **f32) if keep_node_values else None
         self.beliefs_avg = torch.zeros(rows, 2, HPAD, **f32) if keep_node_values else None
+        self.exploitability = torch.zeros(B, **f32) if (exploitability and keep_node_values) else None
+        self.br_values = torch.zeros(B, 2, **f32) if (exploitability and keep_node_values) else None
         n_scratch = int(_lib.lib().p2b_cfr_scratch_floats(layout.max_internal, self.num_blocks))
         self.scratch = torch.empty(n_scratch, **f32)
         self.work_counter = torch.zeros(4, device=device, dtype=torch.int32)
@@ -207,7 +212,7 @@ class SubgameSolver:
     def release(self) -> None:
         """Drops the device buffers (they return to the caching allocator)."""
         for name in ("regrets", "policy_avg", "weight_sums", "policy", "root_values", "values_avg", "beliefs_avg",
-                     "scratch", "tables"):
+                     "exploitability", "br_values", "scratch", "tables"):
             setattr(self, name, None)
 
     def solve(self, root_beliefs: torch.Tensor, scalars: np.ndarray, *, cfr_plus: bool = False) -> SolveResult:
@@ -223,13 +228,14 @@ class SubgameSolver:
                 "p2b_cfr_solve", p(self.subgames), p(self.nodes), self.B, self.layout.max_children,
                 self.layout.max_internal, p(self.tables.blob) if self.tables is not None else None, p(root_beliefs),
                 p(self.regrets), p(self.weight_sums), p(self.policy_avg), p(self.policy), p(self.root_values),
-                p(self.values_avg), p(self.beliefs_avg), p(self.scratch), self.scratch.numel(),
+                p(self.values_avg), p(self.beliefs_avg), p(self.exploitability), p(self.br_values), p(self.scratch),
+                self.scratch.numel(),
                 p(sc) if iterations else None, iterations, int(cfr_plus), self.layout.tree_depth, p(self.work_counter),
                 self.num_blocks,
                 _lib.stream_ptr(self.device))
         self.launches += 1
         return SolveResult(self.layout, self.policy_avg, self.regrets, self.weight_sums, self.policy,
-                           self.root_values, self.values_avg, self.beliefs_avg)
+                           self.root_values, self.values_avg, self.beliefs_avg, self.exploitability, self.br_values)
 
 
 def solve_noalloc(sv: SubgameSolver, root_beliefs: torch.Tensor, scalars_dev: torch.Tensor, *,
@@ -248,16 +254,18 @@ def solve_noalloc(sv: SubgameSolver, root_beliefs: torch.Tensor, scalars_dev: to
             "p2b_cfr_solve_noalloc", p(sv.subgames), p(sv.nodes), sv.B, sv.layout.max_children,
             sv.layout.max_internal, p(sv.tables.blob) if sv.tables is not None else None, p(root_beliefs),
             p(sv.regrets), p(sv.weight_sums), p(sv.policy_avg), p(sv.policy), p(sv.root_values), p(sv.values_avg),
-            p(sv.beliefs_avg), p(scalars_dev), int(scalars_dev.shape[0]), int(cfr_plus), sv.layout.tree_depth,
+            p(sv.beliefs_avg), p(sv.exploitability), p(sv.br_values), p(scalars_dev), int(scalars_dev.shape[0]),
+            int(cfr_plus), sv.layout.tree_depth,
             _lib.stream_ptr(sv.device))
     return SolveResult(sv.layout, sv.policy_avg, sv.regrets, sv.weight_sums, sv.policy, sv.root_values,
-                       sv.values_avg, sv.beliefs_avg)
+                       sv.values_avg, sv.beliefs_avg, sv.exploitability, sv.br_values)
 
 
 def solve_subgames(boards, ranges, pot, stacks, *, iterations: int, bet_bins=(0.5, 1.0), max_depth: int = 8,
                    max_raises=None, bb: int = 2, cfr_type: str = "discounted", alpha: float = 1.5, beta: float = 0.0,
                    gamma: float = 2.0, dcfr_delay: int = 0, cfr_plus: bool = False, device=None,
-                   keep_policy: bool = False, keep_node_values: bool = False, track_weight_sums: bool = True):
+                   keep_policy: bool = False, keep_node_values: bool = False, track_weight_sums: bool = True,
+                   exploitability: bool = False):
     """Solves a batch of river subgames: boards [B,5] card ids, ranges [B,2,1326] fp32,
     pot [B] and stacks [B] or [B,2] in chips.  Returns (SolveResult, PublicTrees)."""
     device = torch.device(device if device is not None else "cuda:0")
@@ -268,7 +276,7 @@ def solve_subgames(boards, ranges, pot, stacks, *, iterations: int, bet_bins=(0.
     trees = ptree.build_trees(roots, list(bet_bins), max_depth, bb=bb, max_raises=max_raises)
     layout = device_layout(trees, boards_np)
     solver = SubgameSolver(layout, torch.from_numpy(boards_np), device, track_weight_sums=track_weight_sums,
-                           keep_policy=keep_policy, keep_node_values=keep_node_values)
+                           keep_policy=keep_policy, keep_node_values=keep_node_values, exploitability=exploitability)
     rb = pad_rows(torch.as_tensor(ranges, dtype=torch.float32).to(device)).contiguous()
     scal = iteration_scalars(iterations, cfr_type=cfr_type, alpha=alpha, beta=beta, gamma=gamma, dcfr_delay=dcfr_delay)
     return solver.solve(rb, scal, cfr_plus=cfr_plus), trees

@@ -60,3 +60,18 @@ def test_golden_strategies_and_values(cuda_device, golden_dir, name):
     _report(name + " root_values", vals, want_vals)
     torch.testing.assert_close(pol, want_pol, rtol=RTOL, atol=ATOL)
     torch.testing.assert_close(vals, want_vals, rtol=RTOL, atol=ATOL)
+
+
+@pytest.mark.parametrize("name", ["cfr_single_cap2_t8", "cfr_single_cap2_t256", "cfr_single_nocap_t32",
+                                  "cfr_batch_cap2_t24"])
+def test_local_exploitability_matches_upstream(cuda_device, golden_dir, name):
+    """Best-response sweeps in the kernel against `_compute_exploitability` run upstream."""
+    z = np.load(os.path.join(golden_dir, name + ".npz"))
+    res, _ = _solve_golden(z, cuda_device, exploitability=True)
+    got, want = res.exploitability.cpu(), torch.from_numpy(z["exploitability"])
+    _report(name + " exploitability", got, want)
+    torch.testing.assert_close(got, want, rtol=RTOL, atol=ATOL)
+    torch.testing.assert_close(res.br_values.cpu(), torch.from_numpy(z["br_values"]), rtol=RTOL, atol=ATOL)
+    # asking for exploitability must not change the solution
+    torch.testing.assert_close(res.root_values[..., :1326].cpu(), torch.from_numpy(z["root_values"]),
+                               rtol=RTOL, atol=ATOL)
