@@ -84,6 +84,12 @@ __device__ __forceinline__ void stv(float* row, int tid, const FV<VPT>& r) {
     }
 }
 
+// Hint that this thread's slice of a row will be read soon: pulls the line into L2.
+template <int VPT>
+__device__ __forceinline__ void prefetch_row(const float* row, int tid) {
+    if (tid < P2B_HPAD / VPT) asm volatile("prefetch.global.L2 [%0];" ::"l"(row + VPT * tid));
+}
+
 // x[which] without indexing a register array by a run-time value
 template <int VPT>
 __device__ __forceinline__ FV<VPT> pick(const FV<VPT> (&x)[2], int which) {
@@ -255,27 +261,32 @@ __device__ __forceinline__ void node_tables(Block& B, int cs_row0, int n_cs, con
     const BoardTabView tv = view_tables(B.tab);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     const int quads_cs = n_cs * 208, quads = quads_cs + n_pc * 208;
+    const uint16_t* __restrict__ nat = B.nat;
+    const uint16_t* __restrict__ cardlist = tv.cardlist;
+    const uint16_t* __restrict__ sorted = tv.sorted;
     for (int base = 0; base < quads; base += blockDim.x) {
         const int t = base + tid;
         const bool valid = t < quads, is_cs = t < quads_cs;
         const int u = is_cs ? t : t - quads_cs;
         const int slot = u / 208, rem = u % 208, c = rem >> 2, q = rem & 3;
-        const float* x = B.stage_row(is_cs ? cs_row0 + slot : pc_rows[slot > 1 ? 1 : slot]);
-        double tot = 0.0;
-        if (valid) {
-            if (is_cs) {
-                const uint16_t* list = B.nat + c * 51;
+        const float* __restrict__ x = B.stage_row(is_cs ? cs_row0 + slot : pc_rows[slot > 1 ? 1 : slot]);
+        // the (up to) 13 values of this quarter list, loaded before any arithmetic so that the
+        // shared-memory latencies overlap
+        float v[13];
 #pragma unroll
-                for (int i = 0; i < 13; ++i) {
-                    const int e = q + 4 * i;
-                    if (e < 51) tot += (double)x[list[e]];
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < 13; ++i)
-                    if (13 * q + i < 51) tot += (double)x[tv.cardlist[(13 * q + i) * 52 + c]];
-            }
+        for (int i = 0; i < 13; ++i) {
+            const int e = is_cs ? q + 4 * i : 13 * q + i;  // interleaved for sums, contiguous for prefixes
+            int idx = 0;
+            if (valid && e < 51) idx = is_cs ? nat[c * 51 + e] : cardlist[e * 52 + c];
+            v[i] = (valid && e < 51) ? x[idx] : 0.0f;
         }
+        double t_even = 0.0, t_odd = 0.0;
+#pragma unroll
+        for (int i = 0; i < 13; ++i) {
+            if (i & 1) t_odd += (double)v[i];
+            else t_even += (double)v[i];
+        }
+        const double tot = t_even + t_odd;
         const int g = lane & ~3;
         const double t0 = __shfl_sync(0xffffffffu, tot, g), t1 = __shfl_sync(0xffffffffu, tot, g + 1);
         const double t2 = __shfl_sync(0xffffffffu, tot, g + 2), t3 = __shfl_sync(0xffffffffu, tot, g + 3);
@@ -284,12 +295,12 @@ __device__ __forceinline__ void node_tables(Block& B, int cs_row0, int n_cs, con
                 if (q == 0) B.cs[slot * 52 + c] = ((t0 + t1) + t2) + t3;
             } else {
                 double acc = q == 0 ? 0.0 : (q == 1 ? t0 : (q == 2 ? t0 + t1 : (t0 + t1) + t2));
-                float* row = B.pc + slot * 52 * 52 + c * 52;
+                float* __restrict__ row = B.pc + slot * 52 * 52 + c * 52;
                 if (q == 0) row[0] = 0.0f;
 #pragma unroll
                 for (int i = 0; i < 13; ++i)
                     if (13 * q + i < 51) {
-                        acc += (double)x[tv.cardlist[(13 * q + i) * 52 + c]];
+                        acc += (double)v[i];
                         row[13 * q + i + 1] = (float)acc;
                     }
             }
@@ -297,34 +308,43 @@ __device__ __forceinline__ void node_tables(Block& B, int cs_row0, int n_cs, con
     }
     // Whole-warp tasks go to the highest-numbered warps first: those have the fewest list
     // tasks above.  Sums run on several independent accumulators to shorten the fp64
-    // dependency chains.
+    // dependency chains; loads are grouped ahead of the arithmetic.
     for (int wt = nwarps - 1 - warp; wt < n_cs + n_pc; wt += nwarps) {
         if (wt < n_cs) {  // total mass of a row
-            const float* x = B.stage_row(cs_row0 + wt);
-            double v[6] = {0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
+            const float* __restrict__ x = B.stage_row(cs_row0 + wt);
+            double acc[6] = {0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
 #pragma unroll
-            for (int i = 0; i < 42; ++i) {
-                const int h = lane + 32 * i;
-                if (h < P2B_NUM_HANDS) v[i % 6] += (double)x[h];
+            for (int b = 0; b < 7; ++b) {
+                float v[6];
+#pragma unroll
+                for (int i = 0; i < 6; ++i) {
+                    const int h = lane + 32 * (6 * b + i);
+                    v[i] = h < P2B_NUM_HANDS ? x[h] : 0.0f;
+                }
+#pragma unroll
+                for (int i = 0; i < 6; ++i) acc[i] += (double)v[i];
             }
-            const double tot = warp_sum(((v[0] + v[1]) + (v[2] + v[3])) + (v[4] + v[5]));
+            const double tot = warp_sum(((acc[0] + acc[1]) + (acc[2] + acc[3])) + (acc[4] + acc[5]));
             if (lane == 0) B.S[wt] = tot;
         } else {  // strength-order prefix sums of a row: 42 consecutive positions per lane,
                   // as six runs of seven so that the runs accumulate independently
             const int slot = wt - n_cs;
-            const float* x = B.stage_row(pc_rows[slot]);
-            float* pref = B.pref + slot * P2B_HPAD;
+            const float* __restrict__ x = B.stage_row(pc_rows[slot]);
+            float* __restrict__ pref = B.pref + slot * P2B_HPAD;
             const int k0 = 42 * lane;
             double part[6];
 #pragma unroll
             for (int b = 0; b < 6; ++b) {
-                double acc = 0.0;
+                float v[7];
 #pragma unroll
                 for (int i = 0; i < 7; ++i) {
                     const int k = k0 + 7 * b + i;
-                    if (k < P2B_NUM_HANDS) acc += (double)x[tv.sorted[k]];
+                    v[i] = k < P2B_NUM_HANDS ? x[sorted[k]] : 0.0f;
                 }
-                part[b] = acc;
+                double a = 0.0;
+#pragma unroll
+                for (int i = 0; i < 7; ++i) a += (double)v[i];
+                part[b] = a;
             }
             const double local = ((part[0] + part[1]) + (part[2] + part[3])) + (part[4] + part[5]);
             double incl = local;
@@ -337,14 +357,18 @@ __device__ __forceinline__ void node_tables(Block& B, int cs_row0, int n_cs, con
             if (lane == 0) pref[0] = 0.0f;
 #pragma unroll
             for (int b = 0; b < 6; ++b) {
+                float v[7];
+#pragma unroll
+                for (int i = 0; i < 7; ++i) {
+                    const int k = k0 + 7 * b + i;
+                    v[i] = k < P2B_NUM_HANDS ? x[sorted[k]] : 0.0f;
+                }
                 double run = start;
 #pragma unroll
                 for (int i = 0; i < 7; ++i) {
                     const int k = k0 + 7 * b + i;
-                    if (k < P2B_NUM_HANDS) {
-                        run += (double)x[tv.sorted[k]];
-                        pref[k + 1] = (float)run;
-                    }
+                    run += (double)v[i];
+                    if (k < P2B_NUM_HANDS) pref[k + 1] = (float)run;
                 }
                 start += part[b];
             }
@@ -392,7 +416,24 @@ __device__ __forceinline__ void sweep_down(int mode, int pass, const CfrParams& 
                 rbna = ldv<VPT>(B.rbar(ii, 1 - a), tid);
             }
         }
-        FV<VPT> P[MAXC], Rc[MAXC];
+        if (mode != kPassInit) {
+            // the next internal node's state rows are streamed from HBM: start them now
+            int jn = j + 1;
+            while (jn < B.sg.n_nodes && B.nodes[jn].kind != kInternal) ++jn;
+            if (jn < B.sg.n_nodes) {
+                const NodeRec nn = B.nodes[jn];
+                for (int c = 0; c < nn.n_children; ++c) {
+                    prefetch_row<VPT>(B.row1(mode == kPassFinal ? p.policy_avg : p.regrets, nn.first_child + c), tid);
+                    if (mix) prefetch_row<VPT>(B.row1(p.policy_avg, nn.first_child + c), tid);
+                }
+            }
+        }
+        FV<VPT> P[MAXC], Rc[MAXC], Pbs[MAXC];
+        if (mix) {
+#pragma unroll
+            for (int c = 0; c < MAXC; ++c)
+                if (c < k) Pbs[c] = ldv<VPT>(B.row1(p.policy_avg, fc + c), tid);
+        }
         children_policy<VPT, MAXC>(mode, p, B, fc, k, tid, P, Rc);
 
         if (mode == kPassInit) {
@@ -444,10 +485,6 @@ __device__ __forceinline__ void sweep_down(int mode, int pass, const CfrParams& 
                     rn.v[i] = __fmul_rn(ra.v[i], sc.mix_new);
                     sum.v[i] = 0.0f;
                 }
-                FV<VPT> Pbs[MAXC];
-#pragma unroll
-                for (int c = 0; c < MAXC; ++c)
-                    if (c < k) Pbs[c] = ldv<VPT>(B.row1(p.policy_avg, fc + c), tid);
 #pragma unroll
                 for (int c = 0; c < MAXC; ++c)
                     if (c < k) {
@@ -574,6 +611,17 @@ __device__ __forceinline__ void sweep_up(int mode, int pass, const CfrParams& p,
                 apply_norm<VPT>(B, hi, b_o, B.sig[j * 2 + o]);
             }
         }
+        {
+            int jn = j - 1;
+            while (jn >= 0 && B.nodes[jn].kind != kInternal) --jn;
+            if (jn >= 0) {
+                const NodeRec nn = B.nodes[jn];
+                for (int c = 0; c < nn.n_children; ++c) {
+                    prefetch_row<VPT>(B.row1(mode == kPassFinal ? p.policy_avg : p.regrets, nn.first_child + c), tid);
+                    if (update && p.weight_sums) prefetch_row<VPT>(B.row1(p.weight_sums, nn.first_child + c), tid);
+                }
+            }
+        }
         FV<VPT> P[MAXC], Rc[MAXC], Va[MAXC], acc_a, acc_o;
         children_policy<VPT, MAXC>(mode, p, B, fc, k, tid, P, Rc);
 
@@ -630,7 +678,6 @@ __device__ __forceinline__ void sweep_up(int mode, int pass, const CfrParams& p,
             int pc_rows[2] = {1, first_sd >= 0 ? kRowLeaf + first_sd : 1};
             node_tables(B, 0, 2 + k, pc_rows, first_sd >= 0 ? 2 : 0);
         }
-
         // ---- per-hand arithmetic ----
         FV<VPT> wgt, denm, eva;
 #pragma unroll
