@@ -62,7 +62,7 @@ int p2b_showdown_values(const unsigned char* tables, const int32_t* table_of_row
  * cfr_iteration :1331-1381, on the ragged tree of sparse_cfr_evaluator.py:141-306) ----
  * One persistent kernel runs the start pass, `iterations` DCFR iterations and the final
  * average-policy evaluation for `num_subgames` independent subgames whose leaves are all
- * terminal (fold or showdown).  Rows are 1328 floats (1326 combos + 2 padding floats) so
+ * terminal (fold or showdown).  Rows are 1344 floats (1326 combos + 18 padding floats) so
  * that every row is 16-byte aligned; all row arrays must be 16-byte aligned.
  *
  *  subgames   [num_subgames] 32-byte records {int32 node_begin, n_nodes, n_internal,
@@ -71,9 +71,9 @@ int p2b_showdown_values(const unsigned char* tables, const int32_t* table_of_row
  *             (0 internal, 1 fold leaf, 2 showdown leaf, 3 other leaf), action, depth,
  *             internal_idx; float v0, v1}, breadth-first per subgame, local indices
  *  tables     showdown tables from p2b_rank_hands, indexed by table_index
- *  root_beliefs [num_subgames,2,1328] input ranges
- *  regrets, weight_sums (may be NULL), policy_avg, policy (may be NULL): [rows,1328] out
- *  root_values [num_subgames,2,1328] out; values_avg, beliefs_avg [rows,2,1328] out (may be NULL)
+ *  root_beliefs [num_subgames,2,1344] input ranges
+ *  regrets, weight_sums (may be NULL), policy_avg, policy (may be NULL): [rows,1344] out
+ *  root_values [num_subgames,2,1344] out; values_avg, beliefs_avg [rows,2,1344] out (may be NULL)
  *  exploitability [num_subgames], br_values [num_subgames,2] out (may be NULL; need values_avg):
  *             local exploitability of the average policy and the best-response value of each
  *             player at the root (cfr_evaluator.py:718-764)
@@ -106,7 +106,7 @@ int p2b_cfr_default_blocks(void);
  * This variant keeps its work rows, queue counter and combo table in a fixed area that is
  * part of the library image: 32 MiB (p2b_cfr_noalloc_scratch_floats() floats) on every
  * GPU that loads the library, held until the process exits.  Limits that follow:
- *   - a subgame needs max_internal * 6 * 1328 floats of work rows per thread block; if
+ *   - a subgame needs max_internal * 6 * 1344 floats of work rows per thread block; if
  *     that exceeds the area the call fails with a message and nothing is launched;
  *   - the number of thread blocks is what fits in the area (at most one per SM), so large
  *     trees run on fewer SMs than with p2b_cfr_solve.

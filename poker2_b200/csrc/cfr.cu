@@ -59,35 +59,30 @@ struct FV {
     float v[VPT];
 };
 
+static_assert(P2B_HPAD == 1344, "rows are covered exactly by 672 x 2 or 336 x 4 hands");
+
 template <int VPT>
 __device__ __forceinline__ FV<VPT> ldv(const float* row, int tid) {
     FV<VPT> r;
-    if (tid < P2B_HPAD / VPT) {
-        if (VPT == 4) {
-            const float4 t = *reinterpret_cast<const float4*>(row + 4 * tid);
-            r.v[0] = t.x; r.v[1] = t.y; r.v[VPT - 2] = t.z; r.v[VPT - 1] = t.w;
-        } else {
-            const float2 t = *reinterpret_cast<const float2*>(row + 2 * tid);
-            r.v[0] = t.x; r.v[1] = t.y;
-        }
+    if (VPT == 4) {
+        const float4 t = *reinterpret_cast<const float4*>(row + 4 * tid);
+        r.v[0] = t.x; r.v[1] = t.y; r.v[VPT - 2] = t.z; r.v[VPT - 1] = t.w;
     } else {
-#pragma unroll
-        for (int i = 0; i < VPT; ++i) r.v[i] = 0.0f;
+        const float2 t = *reinterpret_cast<const float2*>(row + 2 * tid);
+        r.v[0] = t.x; r.v[1] = t.y;
     }
     return r;
 }
 template <int VPT>
 __device__ __forceinline__ void stv(float* row, int tid, const FV<VPT>& r) {
-    if (tid < P2B_HPAD / VPT) {
-        if (VPT == 4) *reinterpret_cast<float4*>(row + 4 * tid) = make_float4(r.v[0], r.v[1], r.v[VPT - 2], r.v[VPT - 1]);
-        else *reinterpret_cast<float2*>(row + 2 * tid) = make_float2(r.v[0], r.v[1]);
-    }
+    if (VPT == 4) *reinterpret_cast<float4*>(row + 4 * tid) = make_float4(r.v[0], r.v[1], r.v[VPT - 2], r.v[VPT - 1]);
+    else *reinterpret_cast<float2*>(row + 2 * tid) = make_float2(r.v[0], r.v[1]);
 }
 
 // Hint that this thread's slice of a row will be read soon: pulls the line into L2.
 template <int VPT>
 __device__ __forceinline__ void prefetch_row(const float* row, int tid) {
-    if (tid < P2B_HPAD / VPT) asm volatile("prefetch.global.L2 [%0];" ::"l"(row + VPT * tid));
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(row + VPT * tid));
 }
 
 // x[which] without indexing a register array by a run-time value
@@ -179,15 +174,15 @@ struct Block {
     __device__ __forceinline__ float* stage_row(int r) const { return xs + r * P2B_HPAD; }
 };
 
-// Policy of the k children of one node: uniform (start pass), the stored average policy
+// Policy of the K (== k) children of one node: uniform (start pass), the stored average policy
 // (final pass) or regret matching on the cumulative regrets, which are returned in Rc.
-template <int VPT, int MAXC>
+template <int VPT, int K>
 __device__ __forceinline__ void children_policy(int mode, const CfrParams& p, const Block& B, int fc, int k, int tid,
-                                                FV<VPT> (&P)[MAXC], FV<VPT> (&Rc)[MAXC]) {
+                                                FV<VPT> (&P)[K], FV<VPT> (&Rc)[K]) {
     const float invk = __fdiv_rn(1.0f, (float)k);
     if (mode == kPassInit) {
 #pragma unroll
-        for (int c = 0; c < MAXC; ++c)
+        for (int c = 0; c < K; ++c)
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
                 P[c].v[i] = invk;
@@ -197,8 +192,8 @@ __device__ __forceinline__ void children_policy(int mode, const CfrParams& p, co
     }
     if (mode == kPassFinal) {
 #pragma unroll
-        for (int c = 0; c < MAXC; ++c)
-            if (c < k) P[c] = ldv<VPT>(B.row1(p.policy_avg, fc + c), tid);
+        for (int c = 0; c < K; ++c)
+            P[c] = ldv<VPT>(B.row1(p.policy_avg, fc + c), tid);
         return;
     }
     FV<VPT> sum;
@@ -206,17 +201,17 @@ __device__ __forceinline__ void children_policy(int mode, const CfrParams& p, co
     for (int i = 0; i < VPT; ++i) sum.v[i] = 0.0f;
     // all loads first: the rows are independent, so their latencies overlap
 #pragma unroll
-    for (int c = 0; c < MAXC; ++c)
-        if (c < k) Rc[c] = ldv<VPT>(B.row1(p.regrets, fc + c), tid);
+    for (int c = 0; c < K; ++c)
+        Rc[c] = ldv<VPT>(B.row1(p.regrets, fc + c), tid);
 #pragma unroll
-    for (int c = 0; c < MAXC; ++c)
-        if (c < k) {
+    for (int c = 0; c < K; ++c)
+        {
 #pragma unroll
             for (int i = 0; i < VPT; ++i) sum.v[i] = __fadd_rn(sum.v[i], fmaxf(Rc[c].v[i], 0.0f));
         }
 #pragma unroll
-    for (int c = 0; c < MAXC; ++c)
-        if (c < k) {
+    for (int c = 0; c < K; ++c)
+        {
 #pragma unroll
             for (int i = 0; i < VPT; ++i)
                 P[c].v[i] = sum.v[i] > 1e-8f ? __fdiv_rn(fmaxf(Rc[c].v[i], 0.0f), fmaxf(sum.v[i], 1e-8f)) : invk;
@@ -394,6 +389,25 @@ __device__ __forceinline__ void showdown_ev(const Block& B, const HandInfo<VPT>&
     }
 }
 
+// Runs body(ChildCount<k>) for the run-time child count k (uniform over the
+// block): each instantiation is unrolled for exactly k children, so no instruction is spent
+// on absent child slots.
+template <int N>
+struct ChildCount {
+    static constexpr int value = N;
+};
+template <typename Body>
+__device__ __forceinline__ void dispatch_children(int k, Body&& body) {
+    switch (k) {
+        case 1: body(ChildCount<1>{}); break;
+        case 2: body(ChildCount<2>{}); break;
+        case 3: body(ChildCount<3>{}); break;
+        case 4: body(ChildCount<4>{}); break;
+        case 5: body(ChildCount<5>{}); break;
+        default: body(ChildCount<kCfrMaxChildren>{}); break;
+    }
+}
+
 // ---- top-down sweep of one pass -------------------------------------------------------
 template <int VPT, int MAXC>
 __device__ __forceinline__ void sweep_down(int mode, int pass, const CfrParams& p, Block& B, const HandInfo<VPT>& hi,
@@ -407,6 +421,8 @@ __device__ __forceinline__ void sweep_down(int mode, int pass, const CfrParams& 
         const NodeRec nd = B.nodes[j];
         if (nd.kind != kInternal) continue;
         const int a = nd.to_act, k = nd.n_children, fc = nd.first_child, ii = nd.internal_idx;
+        auto node_body = [&](auto kc) {
+        constexpr int K = decltype(kc)::value;
         FV<VPT> ra = mask, rna = mask, rba = mask, rbna = mask;
         if (j != 0) {
             ra = ldv<VPT>(B.reach(ii, a), tid);
@@ -428,13 +444,13 @@ __device__ __forceinline__ void sweep_down(int mode, int pass, const CfrParams& 
                 }
             }
         }
-        FV<VPT> P[MAXC], Rc[MAXC], Pbs[MAXC];
+        FV<VPT> P[K], Rc[K], Pbs[K];
         if (mix) {
 #pragma unroll
-            for (int c = 0; c < MAXC; ++c)
-                if (c < k) Pbs[c] = ldv<VPT>(B.row1(p.policy_avg, fc + c), tid);
+            for (int c = 0; c < K; ++c)
+                Pbs[c] = ldv<VPT>(B.row1(p.policy_avg, fc + c), tid);
         }
-        children_policy<VPT, MAXC>(mode, p, B, fc, k, tid, P, Rc);
+        children_policy<VPT, K>(mode, p, B, fc, k, tid, P, Rc);
 
         if (mode == kPassInit) {
             // Start beliefs.  Upstream pushes beliefs down one level at a time and re-normalises
@@ -451,8 +467,7 @@ __device__ __forceinline__ void sweep_down(int mode, int pass, const CfrParams& 
                 b1o = ldv<VPT>(B.reach(ii, 1 - a), tid);
             }
 #pragma unroll
-            for (int c = 0; c < MAXC; ++c) {
-                if (c >= k) continue;
+            for (int c = 0; c < K; ++c) {
                 const NodeRec ch = B.nodes[fc + c];
                 stv<VPT>(B.row1(p.policy_avg, fc + c), tid, P[c]);
                 if (ch.kind != kInternal) continue;
@@ -470,12 +485,12 @@ __device__ __forceinline__ void sweep_down(int mode, int pass, const CfrParams& 
                 stv<VPT>(B.rbar(ch.internal_idx, 0), tid, x[0]);
                 stv<VPT>(B.rbar(ch.internal_idx, 1), tid, x[1]);
             }
-            continue;
+            return;
         }
 
         if (mode == kPassIter) {
             // average policy of the children
-            FV<VPT> Pn[MAXC];
+            FV<VPT> Pn[K];
             if (mix) {
                 const IterScalars sc = p.scalars[pass];
                 FV<VPT> ro, rn, sum;
@@ -486,8 +501,8 @@ __device__ __forceinline__ void sweep_down(int mode, int pass, const CfrParams& 
                     sum.v[i] = 0.0f;
                 }
 #pragma unroll
-                for (int c = 0; c < MAXC; ++c)
-                    if (c < k) {
+                for (int c = 0; c < K; ++c)
+                    {
                         const FV<VPT> Pb = Pbs[c];
                         const NodeRec ch = B.nodes[fc + c];
                         if (ch.kind == kInternal) {  // average reach under the OLD average policy
@@ -512,8 +527,8 @@ __device__ __forceinline__ void sweep_down(int mode, int pass, const CfrParams& 
                         }
                     }
 #pragma unroll
-                for (int c = 0; c < MAXC; ++c)
-                    if (c < k) {
+                for (int c = 0; c < K; ++c)
+                    {
 #pragma unroll
                         for (int i = 0; i < VPT; ++i)
                             if (sum.v[i] > 1e-5f) Pn[c].v[i] = __fdiv_rn(Pn[c].v[i], sum.v[i]);
@@ -521,13 +536,13 @@ __device__ __forceinline__ void sweep_down(int mode, int pass, const CfrParams& 
                     }
             } else {
 #pragma unroll
-                for (int c = 0; c < MAXC; ++c)
-                    if (c < k) stv<VPT>(B.row1(p.policy_avg, fc + c), tid, P[c]);
+                for (int c = 0; c < K; ++c)
+                    stv<VPT>(B.row1(p.policy_avg, fc + c), tid, P[c]);
             }
             if (p.policy && pass == p.iterations - 1) {
 #pragma unroll
-                for (int c = 0; c < MAXC; ++c)
-                    if (c < k) stv<VPT>(B.row1(p.policy, fc + c), tid, P[c]);
+                for (int c = 0; c < K; ++c)
+                    stv<VPT>(B.row1(p.policy, fc + c), tid, P[c]);
             }
         }
         // reach of the children under the policy of this pass, and the rows whose sums
@@ -537,8 +552,8 @@ __device__ __forceinline__ void sweep_down(int mode, int pass, const CfrParams& 
         parity ^= 1;
         const FV<VPT> prior_a = pick<VPT>(prior, a);
 #pragma unroll
-        for (int c = 0; c < MAXC; ++c)
-            if (c < k) {
+        for (int c = 0; c < K; ++c)
+            {
                 const NodeRec ch = B.nodes[fc + c];
                 if (ch.kind == kFoldLeaf || ch.kind == kModelLeaf) continue;
                 FV<VPT> t, u;
@@ -565,6 +580,8 @@ __device__ __forceinline__ void sweep_down(int mode, int pass, const CfrParams& 
                 }
             }
         }
+        };
+        dispatch_children(k, node_body);
     }
     __syncthreads();
 }
@@ -587,6 +604,8 @@ __device__ __forceinline__ void sweep_up(int mode, int pass, const CfrParams& p,
         const NodeRec nd = B.nodes[j];
         if (nd.kind != kInternal) continue;
         const int a = nd.to_act, o = 1 - a, k = nd.n_children, fc = nd.first_child, ii = nd.internal_idx;
+        auto node_body = [&](auto kc) {
+        constexpr int K = decltype(kc)::value;
         const FV<VPT> prior_a = pick<VPT>(prior, a), prior_o = pick<VPT>(prior, o);
         // r: reach of both players (start pass: once-normalised start beliefs, see sweep_down)
         FV<VPT> r_a, r_o, b_a, b_o;
@@ -622,14 +641,13 @@ __device__ __forceinline__ void sweep_up(int mode, int pass, const CfrParams& p,
                 }
             }
         }
-        FV<VPT> P[MAXC], Rc[MAXC], Va[MAXC], acc_a, acc_o;
-        children_policy<VPT, MAXC>(mode, p, B, fc, k, tid, P, Rc);
+        FV<VPT> P[K], Rc[K], Va[K], acc_a, acc_o;
+        children_policy<VPT, K>(mode, p, B, fc, k, tid, P, Rc);
 
         // ---- stage ----
         int first_sd = -1;
 #pragma unroll
-        for (int c = 0; c < MAXC; ++c) {
-            if (c >= k) continue;
+        for (int c = 0; c < K; ++c) {
             const NodeRec ch = B.nodes[fc + c];
             if (ch.kind != kShowdownLeaf) continue;
             if (first_sd < 0) first_sd = c;
@@ -658,8 +676,8 @@ __device__ __forceinline__ void sweep_up(int mode, int pass, const CfrParams& p,
         stv<VPT>(B.stage_row(0), tid, b_a);
         stv<VPT>(B.stage_row(1), tid, b_o);
 #pragma unroll
-        for (int c = 0; c < MAXC; ++c)
-            if (c < k) {
+        for (int c = 0; c < K; ++c)
+            {
                 FV<VPT> m;
 #pragma unroll
                 for (int i = 0; i < VPT; ++i) m.v[i] = __fmul_rn(b_a.v[i], P[c].v[i]);
@@ -690,8 +708,7 @@ __device__ __forceinline__ void sweep_up(int mode, int pass, const CfrParams& p,
         if (first_sd >= 0) showdown_ev<VPT>(B, hi, tid, B.stage_row(1), B.pref, B.pc, eva);
 
 #pragma unroll
-        for (int c = 0; c < MAXC; ++c) {
-            if (c >= k) continue;  // uniform across the block
+        for (int c = 0; c < K; ++c) {
             const NodeRec ch = B.nodes[fc + c];
             // policy of this child as seen by each opponent hand (cfr_evaluator.py:1083-1093)
             FV<VPT> pio;
@@ -762,16 +779,16 @@ __device__ __forceinline__ void sweep_up(int mode, int pass, const CfrParams& p,
         if (update) {
             // instantaneous regrets of this pass folded into the discounted update of the next
             const IterScalars sc = p.scalars[pass + 1];
-            FV<VPT> ws[MAXC];
+            FV<VPT> ws[K];
 #pragma unroll
-            for (int c = 0; c < MAXC; ++c) {
+            for (int c = 0; c < K; ++c) {
 #pragma unroll
                 for (int i = 0; i < VPT; ++i) ws[c].v[i] = 0.0f;
-                if (c < k && p.weight_sums && mode != kPassInit) ws[c] = ldv<VPT>(B.row1(p.weight_sums, fc + c), tid);
+                if (p.weight_sums && mode != kPassInit) ws[c] = ldv<VPT>(B.row1(p.weight_sums, fc + c), tid);
             }
 #pragma unroll
-            for (int c = 0; c < MAXC; ++c)
-                if (c < k) {
+            for (int c = 0; c < K; ++c)
+                {
                     FV<VPT> w = ws[c];
 #pragma unroll
                     for (int i = 0; i < VPT; ++i) {
@@ -788,6 +805,8 @@ __device__ __forceinline__ void sweep_up(int mode, int pass, const CfrParams& p,
                     if (p.weight_sums) stv<VPT>(B.row1(p.weight_sums, fc + c), tid, w);
                 }
         }
+        };
+        dispatch_children(k, node_body);
     }
 }
 
@@ -810,6 +829,8 @@ __device__ __forceinline__ void sweep_br(int deviator, const CfrParams& p, Block
         const NodeRec nd = B.nodes[j];
         if (nd.kind != kInternal) continue;
         const int a = nd.to_act, o = 1 - a, k = nd.n_children, fc = nd.first_child, ii = nd.internal_idx;
+        auto node_body = [&](auto kc) {
+        constexpr int K = decltype(kc)::value;
         const bool deviates = deviator == a;
         FV<VPT> b_a;  // beliefs of the acting player under the average policy
         if (j == 0) {
@@ -822,10 +843,9 @@ __device__ __forceinline__ void sweep_br(int deviator, const CfrParams& p, Block
             apply_norm<VPT>(B, hi, b_a, B.sig[j * 2 + a]);
         }
         // child values of both players (leaves: clamped final values; internal: this sweep)
-        FV<VPT> Va[MAXC], Vo[MAXC], P[MAXC];
+        FV<VPT> Va[K], Vo[K], P[K];
 #pragma unroll
-        for (int c = 0; c < MAXC; ++c) {
-            if (c >= k) continue;
+        for (int c = 0; c < K; ++c) {
             const NodeRec ch = B.nodes[fc + c];
             if (ch.kind == kInternal) {
                 Va[c] = ldv<VPT>(B.val(ch.internal_idx, a), tid);
@@ -850,8 +870,8 @@ __device__ __forceinline__ void sweep_br(int deviator, const CfrParams& p, Block
             best_c[i] = 0;
         }
 #pragma unroll
-        for (int c = 1; c < MAXC; ++c)
-            if (c < k) {
+        for (int c = 1; c < K; ++c)
+            {
 #pragma unroll
                 for (int i = 0; i < VPT; ++i)
                     if (Va[c].v[i] > best_v.v[i]) {
@@ -864,8 +884,8 @@ __device__ __forceinline__ void sweep_br(int deviator, const CfrParams& p, Block
         stv<VPT>(B.stage_row(0), tid, b_a);
         stv<VPT>(B.stage_row(1), tid, b_a);
 #pragma unroll
-        for (int c = 0; c < MAXC; ++c)
-            if (c < k) {
+        for (int c = 0; c < K; ++c)
+            {
                 FV<VPT> m;
 #pragma unroll
                 for (int i = 0; i < VPT; ++i)
@@ -881,8 +901,8 @@ __device__ __forceinline__ void sweep_br(int deviator, const CfrParams& p, Block
 #pragma unroll
         for (int i = 0; i < VPT; ++i) acc_a.v[i] = acc_o.v[i] = 0.0f;
 #pragma unroll
-        for (int c = 0; c < MAXC; ++c)
-            if (c < k) {
+        for (int c = 0; c < K; ++c)
+            {
 #pragma unroll
                 for (int i = 0; i < VPT; ++i) {
                     const float m = deviates ? (best_c[i] == c ? b_a.v[i] : 0.0f) : __fmul_rn(P[c].v[i], b_a.v[i]);
@@ -904,6 +924,8 @@ __device__ __forceinline__ void sweep_br(int deviator, const CfrParams& p, Block
                 root_v[1].v[i] = a == 0 ? acc_o.v[i] : acc_a.v[i];
             }
         }
+        };
+        dispatch_children(k, node_body);
     }
 }
 
@@ -927,7 +949,7 @@ __device__ __forceinline__ void dot2_reference_order(Block& B, const FV<VPT>& x0
 
 template <int VPT>
 struct CfrThreads {
-    static constexpr int value = ((P2B_HPAD / VPT + 31) / 32) * 32;  // 352 for four hands per thread, 672 for two
+    static constexpr int value = P2B_HPAD / VPT;  // 672 threads for two hands per thread, 336 for four
 };
 
 template <int VPT, int MAXC>
@@ -1061,7 +1083,7 @@ int sm_count();
 int cfr_default_blocks() { return sm_count(); }
 
 static int dispatch_cfr(const CfrParams& p, int num_blocks, int max_children, cudaStream_t stream) {
-    if (max_children <= 5) return launch_variant<2, 5>(p, num_blocks, stream);
+    // one kernel serves every child count: node bodies are specialised per count inside it
     if (max_children <= kCfrMaxChildren) return launch_variant<2, kCfrMaxChildren>(p, num_blocks, stream);
     return set_error(P2B_ERR_ARG, "at most %d actions per node are supported, got %d", kCfrMaxChildren, max_children);
 }

@@ -44,7 +44,7 @@ struct IterScalars {  // 32 bytes
     int32_t do_mix;          // 0: average policy := current policy at this iteration
 };
 
-constexpr int kCfrThreads = 352;  // 332 threads x 4 hands cover the 1328-float padded row
+constexpr int kCfrThreads = 672;  // 672 threads x 2 hands cover the 1344-float padded row
 constexpr int kCfrMaxNodes = 160;
 constexpr int kCfrMaxChildren = 6;
 

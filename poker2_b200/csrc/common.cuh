@@ -6,9 +6,10 @@
 
 #define P2B_NUM_HANDS 1326
 #define P2B_NUM_CARDS 52
-// Hand rows are padded to a multiple of four floats so that every row of a
-// [node][combo] array starts on a 16-byte boundary (128-bit loads and stores).
-#define P2B_HPAD 1328
+// Hand rows are padded to 1344 floats: every row of a [node][combo] array starts on a
+// 16-byte boundary (128-bit loads and stores), and 672 threads x 2 hands (or 336 x 4) cover a
+// row exactly, so the solver's row accesses need no bounds check.
+#define P2B_HPAD 1344
 
 namespace p2b {
 

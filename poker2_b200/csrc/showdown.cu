@@ -95,7 +95,7 @@ __global__ void __launch_bounds__(kSetupThreads) board_setup_kernel(const int16_
         reinterpret_cast<unsigned long long*>(blob)[0] = mask;
         reinterpret_cast<unsigned long long*>(blob)[1] = 0ull;
     }
-    for (int k = tid; k < P2B_HPAD; k += kSetupThreads) sorted[k] = k < P2B_NUM_HANDS ? (uint16_t)(keys[k] & 2047ull) : 0;
+    for (int k = tid; k < kTabSortedPad; k += kSetupThreads) sorted[k] = k < P2B_NUM_HANDS ? (uint16_t)(keys[k] & 2047ull) : 0;
 
     // 4. per-card lists in strength order, 5. per-hand counts before L and before R.
     // Task (c, i): the i-th other card d of card c names the hand g = {c,d}.

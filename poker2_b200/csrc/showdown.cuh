@@ -29,10 +29,12 @@ struct HandRec {          // 8 bytes per hand, natural combo order
 };
 constexpr int kTabHeaderBytes = 16;                 // uint64 board-card mask + padding
 constexpr int kTabRecBytes = P2B_NUM_HANDS * 8;     // 10608
-constexpr int kTabSortedBytes = P2B_HPAD * 2;       // 2656 (1326 used)
+constexpr int kTabSortedPad = 1328;                 // entries reserved for the strength order (1326 used)
+constexpr int kTabSortedBytes = kTabSortedPad * 2;  // 2656
 constexpr int kTabCardListBytes = 5312;             // uint16 [51][52] = 5304 used
 constexpr int kTabBytes = kTabHeaderBytes + kTabRecBytes + kTabSortedBytes + kTabCardListBytes;  // 18592
 static_assert(kTabBytes % 16 == 0, "table blob must be a whole number of 16-byte vectors");
+static_assert(kTabBytes == 18592, "the table size is part of the C ABI (P2B_TABLE_BYTES)");
 
 struct BoardTabView {
     const unsigned long long* board_mask;

@@ -17,7 +17,7 @@ import torch
 from . import _lib, tree as ptree
 from .showdown import BoardTables
 
-HPAD = 1328
+HPAD = 1344
 NUM_HANDS = 1326
 MAX_NODES = 160
 MAX_CHILDREN = 6
@@ -136,7 +136,7 @@ def device_layout(trees: ptree.PublicTrees, boards: np.ndarray) -> DeviceTreeLay
 
 
 def pad_rows(x: torch.Tensor) -> torch.Tensor:
-    """[..., 1326] -> [..., 1328] zero padded (rows of the kernel are 16-byte aligned)."""
+    """[..., 1326] -> [..., 1344] zero padded (rows of the kernel are 16-byte aligned)."""
     out = x.new_zeros(*x.shape[:-1], HPAD)
     out[..., :NUM_HANDS] = x
     return out
@@ -144,16 +144,16 @@ def pad_rows(x: torch.Tensor) -> torch.Tensor:
 
 @dataclass
 class SolveResult:
-    """Arrays in the kernel's subgame-major row order, padded to 1328 columns.  Use
+    """Arrays in the kernel's subgame-major row order, padded to 1344 columns.  Use
     `level_major(x)` to obtain the upstream node order with 1326 columns."""
 
     layout: DeviceTreeLayout
-    policy_avg: torch.Tensor  # [rows,1328]
-    regrets: torch.Tensor  # [rows,1328]
+    policy_avg: torch.Tensor  # [rows,1344]
+    regrets: torch.Tensor  # [rows,1344]
     weight_sums: torch.Tensor | None
     policy: torch.Tensor | None
-    root_values: torch.Tensor  # [B,2,1328]
-    values_avg: torch.Tensor | None  # [rows,2,1328]
+    root_values: torch.Tensor  # [B,2,1344]
+    values_avg: torch.Tensor | None  # [rows,2,1344]
     beliefs_avg: torch.Tensor | None
     exploitability: torch.Tensor | None = None  # [B] local exploitability of the average policy
     br_values: torch.Tensor | None = None  # [B,2] best-response values at the roots
@@ -216,7 +216,7 @@ class SubgameSolver:
             setattr(self, name, None)
 
     def solve(self, root_beliefs: torch.Tensor, scalars: np.ndarray, *, cfr_plus: bool = False) -> SolveResult:
-        """root_beliefs: [B,2,1328] fp32 on the device (padded).  Enqueues one kernel."""
+        """root_beliefs: [B,2,1344] fp32 on the device (padded).  Enqueues one kernel."""
         assert root_beliefs.shape == (self.B, 2, HPAD) and root_beliefs.dtype == torch.float32
         assert root_beliefs.is_contiguous() and root_beliefs.device == self.device
         iterations = int(scalars.shape[0])

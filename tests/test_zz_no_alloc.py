@@ -69,7 +69,7 @@ def test_noalloc_entry_rejects_oversized_trees(cuda_device):
     trees = ptree.build_trees(ptree.root_states(pot.numpy(), stack.numpy()), [0.5, 1.0], 8, max_raises=2)
     layout = solver.device_layout(trees, boards.numpy())
     sv = solver.SubgameSolver(layout, boards, cuda_device)
-    per_block = 6 * 1328
+    per_block = 6 * 1344
     layout.max_internal = int(_lib.lib().p2b_cfr_noalloc_scratch_floats()) // per_block + 1  # one too many
     scal = solver.iteration_scalars(2)
     scal_dev = torch.from_numpy(scal.view(np.uint8).reshape(2, 32).copy()).to(cuda_device)
