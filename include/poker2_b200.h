@@ -202,6 +202,15 @@ int p2b_chance_expand(const float* pre_beliefs, const int64_t* boards, int32_t b
 int p2b_indexed_add_rows(float* out, const int64_t* index, const float* src, int64_t num_src, int64_t num_out,
                          int64_t width, int mean, int accumulate, void* stream);
 
+/* ---- self-test (no counterpart in the reference) ------------------------------------------
+ * The solver's divisions share divisors and run through a short correctly rounded sequence
+ * (csrc/exactdiv.cuh).  p2b_selftest_division compares it with the compiler's IEEE division
+ * on at least num_pairs generated (x, y) pairs of stream `seed` and ADDS the number of
+ * results that differ in any bit to *mismatches and the number of pairs served by the short
+ * sequence to *short_path (device pointers, cleared by the caller). */
+int p2b_selftest_division(uint64_t num_pairs, uint32_t seed, unsigned long long* mismatches,
+                          unsigned long long* short_path, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

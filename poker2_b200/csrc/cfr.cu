@@ -26,6 +26,7 @@
 // accumulated in fp64 here too, in a different order, which changes the rounded fp32
 // result only when the fp64 value lies within ~1e-16 of a rounding boundary.
 #include "cfr.cuh"
+#include "exactdiv.cuh"
 #include "showdown.cuh"
 
 namespace p2b {
@@ -209,12 +210,15 @@ __device__ __forceinline__ void children_policy(int mode, const CfrParams& p, co
 #pragma unroll
             for (int i = 0; i < VPT; ++i) sum.v[i] = __fadd_rn(sum.v[i], fmaxf(Rc[c].v[i], 0.0f));
         }
+    Divisor ds[VPT];  // the siblings share the divisor
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) ds[i] = make_divisor(fmaxf(sum.v[i], 1e-8f));
 #pragma unroll
     for (int c = 0; c < K; ++c)
         {
 #pragma unroll
             for (int i = 0; i < VPT; ++i)
-                P[c].v[i] = sum.v[i] > 1e-8f ? __fdiv_rn(fmaxf(Rc[c].v[i], 0.0f), fmaxf(sum.v[i], 1e-8f)) : invk;
+                P[c].v[i] = sum.v[i] > 1e-8f ? div_exact(fmaxf(Rc[c].v[i], 0.0f), ds[i]) : invk;
         }
 }
 
@@ -222,9 +226,10 @@ __device__ __forceinline__ void children_policy(int mode, const CfrParams& p, co
 // (numerically) empty (cfr_evaluator.py:263-273).
 template <int VPT>
 __device__ __forceinline__ void apply_norm(const Block& B, const HandInfo<VPT>& hi, FV<VPT>& x, float sum) {
+    const Divisor d = make_divisor(sum);
 #pragma unroll
     for (int i = 0; i < VPT; ++i)
-        x.v[i] = sum > 1e-5f ? __fdiv_rn(x.v[i], sum) : (hi.allowed[i] ? B.sg.allowed_prob : 0.0f);
+        x.v[i] = sum > 1e-5f ? div_exact(x.v[i], d) : (hi.allowed[i] ? B.sg.allowed_prob : 0.0f);
 }
 
 // Normalises the two rows x[0], x[1] (one per player) over hands.  Uses staging rows 0 and
@@ -493,11 +498,19 @@ __device__ __forceinline__ void sweep_down(int mode, int pass, const CfrParams& 
             FV<VPT> Pn[K];
             if (mix) {
                 const IterScalars sc = p.scalars[pass];
+                // weights of the old average and of the new policy: reach-weighted, or the plain
+                // iteration weights where the hand has (numerically) no reach (:1231-1239)
                 FV<VPT> ro, rn, sum;
+                Divisor dmix[VPT];
 #pragma unroll
                 for (int i = 0; i < VPT; ++i) {
                     ro.v[i] = __fmul_rn(rba.v[i], sc.mix_old);
                     rn.v[i] = __fmul_rn(ra.v[i], sc.mix_new);
+                    const float den = __fadd_rn(ro.v[i], rn.v[i]);
+                    const bool weighted = den > 1e-5f;
+                    ro.v[i] = weighted ? ro.v[i] : sc.mix_old;
+                    rn.v[i] = weighted ? rn.v[i] : sc.mix_new;
+                    dmix[i] = make_divisor(weighted ? den : sc.mix_total);
                     sum.v[i] = 0.0f;
                 }
 #pragma unroll
@@ -514,24 +527,21 @@ __device__ __forceinline__ void sweep_down(int mode, int pass, const CfrParams& 
                         }
 #pragma unroll
                         for (int i = 0; i < VPT; ++i) {
-                            const float den = __fadd_rn(ro.v[i], rn.v[i]);
-                            float v;
-                            if (den > 1e-5f) {
-                                v = __fdiv_rn(__fadd_rn(__fmul_rn(ro.v[i], Pb.v[i]), __fmul_rn(rn.v[i], P[c].v[i])), den);
-                            } else {
-                                v = __fdiv_rn(__fadd_rn(__fmul_rn(sc.mix_old, Pb.v[i]), __fmul_rn(sc.mix_new, P[c].v[i])),
-                                              sc.mix_total);
-                            }
+                            const float v =
+                                div_exact(__fadd_rn(__fmul_rn(ro.v[i], Pb.v[i]), __fmul_rn(rn.v[i], P[c].v[i])), dmix[i]);
                             Pn[c].v[i] = v;
                             sum.v[i] = __fadd_rn(sum.v[i], v);
                         }
                     }
+                Divisor dsum[VPT];
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) dsum[i] = make_divisor(sum.v[i]);
 #pragma unroll
                 for (int c = 0; c < K; ++c)
                     {
 #pragma unroll
                         for (int i = 0; i < VPT; ++i)
-                            if (sum.v[i] > 1e-5f) Pn[c].v[i] = __fdiv_rn(Pn[c].v[i], sum.v[i]);
+                            if (sum.v[i] > 1e-5f) Pn[c].v[i] = div_exact(Pn[c].v[i], dsum[i]);
                         stv<VPT>(B.row1(p.policy_avg, fc + c), tid, Pn[c]);
                     }
             } else {
@@ -698,10 +708,12 @@ __device__ __forceinline__ void sweep_up(int mode, int pass, const CfrParams& p,
         }
         // ---- per-hand arithmetic ----
         FV<VPT> wgt, denm, eva;
+        Divisor ddenm[VPT];
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             wgt.v[i] = unblocked(B.cs + 52, B.S[1], hi.c1[i], hi.c2[i], b_o.v[i]);
             denm.v[i] = unblocked(B.cs, B.S[0], hi.c1[i], hi.c2[i], b_a.v[i]);
+            ddenm[i] = make_divisor(denm.v[i]);
             eva.v[i] = 0.0f;
             acc_a.v[i] = acc_o.v[i] = 0.0f;
         }
@@ -716,7 +728,7 @@ __device__ __forceinline__ void sweep_up(int mode, int pass, const CfrParams& p,
             for (int i = 0; i < VPT; ++i) {
                 const float m = __fmul_rn(b_a.v[i], P[c].v[i]);
                 const float blk = unblocked(B.cs + (kRowM + c) * 52, B.S[kRowM + c], hi.c1[i], hi.c2[i], m);
-                pio.v[i] = denm.v[i] > 1e-5f ? __fdiv_rn(blk, denm.v[i]) : 0.0f;
+                pio.v[i] = denm.v[i] > 1e-5f ? div_exact(blk, ddenm[i]) : 0.0f;
             }
             FV<VPT> V_a, V_o;
             if (ch.kind == kFoldLeaf) {
@@ -742,10 +754,11 @@ __device__ __forceinline__ void sweep_up(int mode, int pass, const CfrParams& p,
                     showdown_ev<VPT>(B, hi, tid, B.stage_row(kRowLeaf + c), B.pref, B.pc, evo);
                 }
                 const float pot_a = a == 0 ? ch.v0 : ch.v1, pot_o = a == 0 ? ch.v1 : ch.v0;
+                const Divisor dscale = make_divisor(B.sg.scale);
 #pragma unroll
                 for (int i = 0; i < VPT; ++i) {
-                    V_a.v[i] = __fdiv_rn(__fmul_rn(eva.v[i], pot_a), B.sg.scale);
-                    V_o.v[i] = __fdiv_rn(__fmul_rn(evo.v[i], pot_o), B.sg.scale);
+                    V_a.v[i] = div_exact(__fmul_rn(eva.v[i], pot_a), dscale);
+                    V_o.v[i] = div_exact(__fmul_rn(evo.v[i], pot_o), dscale);
                 }
             } else {
 #pragma unroll
@@ -779,6 +792,7 @@ __device__ __forceinline__ void sweep_up(int mode, int pass, const CfrParams& p,
         if (update) {
             // instantaneous regrets of this pass folded into the discounted update of the next
             const IterScalars sc = p.scalars[pass + 1];
+            const Divisor d_pos = make_divisor(sc.den_pos), d_neg = make_divisor(sc.den_neg);
             FV<VPT> ws[K];
 #pragma unroll
             for (int c = 0; c < K; ++c) {
@@ -794,12 +808,16 @@ __device__ __forceinline__ void sweep_up(int mode, int pass, const CfrParams& p,
                     for (int i = 0; i < VPT; ++i) {
                         const float reg = __fmul_rn(wgt.v[i], __fsub_rn(Va[c].v[i], acc_a.v[i]));
                         const bool pos = Rc[c].v[i] > 0.0f;
-                        const float num = pos ? sc.num_pos : sc.num_neg, den = pos ? sc.den_pos : sc.den_neg;
-                        float rr = __fdiv_rn(__fmul_rn(Rc[c].v[i], num), den);
+                        const float num = pos ? sc.num_pos : sc.num_neg;
+                        Divisor d;
+                        d.y = pos ? d_pos.y : d_neg.y;
+                        d.r = pos ? d_pos.r : d_neg.r;
+                        d.ok = d_pos.ok && d_neg.ok;
+                        float rr = div_exact(__fmul_rn(Rc[c].v[i], num), d);
                         rr = __fadd_rn(rr, reg);
                         if (p.cfr_plus) rr = fmaxf(rr, 0.0f);
                         Rc[c].v[i] = rr;
-                        w.v[i] = __fadd_rn(__fdiv_rn(__fmul_rn(w.v[i], num), den), 1.0f);
+                        w.v[i] = __fadd_rn(div_exact(__fmul_rn(w.v[i], num), d), 1.0f);
                     }
                     stv<VPT>(B.row1(p.regrets, fc + c), tid, Rc[c]);
                     if (p.weight_sums) stv<VPT>(B.row1(p.weight_sums, fc + c), tid, w);

@@ -17,6 +17,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "exactdiv.cuh"
 #include "rank7.cuh"
 
 namespace p2b {
@@ -104,7 +105,8 @@ __device__ __forceinline__ float showdown_hand_ev(const HandRec r, int c1, int c
     den = fmaxf(den, 1e-8f);
     float ev = 0.0f;
     if (den > 1e-8f) {
-        const float wp = __fdiv_rn(win, den), tp = __fdiv_rn(tie, den);
+        const Divisor d = make_divisor(den);
+        const float wp = div_exact(win, d), tp = div_exact(tie, d);
         const float lp = __fsub_rn(__fsub_rn(1.0f, wp), tp);
         ev = __fsub_rn(wp, lp);
     }
