@@ -93,6 +93,34 @@ int p2b_cfr_solve(const void* subgames, const void* nodes, int32_t num_subgames,
 int64_t p2b_cfr_scratch_floats(int32_t max_internal, int32_t num_blocks);
 int p2b_cfr_default_blocks(void);
 
+/* p2b_cfr_step -- part of a solve, for subgames whose non-terminal leaves (start of the next
+ * street, depth limit) are valued by the caller's model (set_leaf_values,
+ * src/p2/search/cfr_evaluator.py:1025-1047): the model runs between the top-down sweep of a
+ * pass (policy, reach, beliefs) and its bottom-up sweep (values, regrets).  Passes are
+ * numbered -1 (start pass), 0..iterations-1 (DCFR iterations), iterations (final evaluation
+ * of the average policy).  A call runs the passes pass_begin..pass_end; `phases` selects the
+ * top-down sweep (1), the bottom-up sweep (2) or both (3); with 1 or 2 the range is one pass.
+ * The caller's loop is: for every pass { step(pass, 1); leaf_values = model(leaf_beliefs);
+ * step(pass, 2); }.  Arrays as in p2b_cfr_solve, plus state carried between calls:
+ *  scratch      p2b_cfr_scratch_floats(max_internal, 1) * num_subgames floats (one set of
+ *               work rows per subgame instead of per block)
+ *  carry_sums   [rows,2] floats, carry_roots [num_subgames,4,1344] floats (opaque)
+ *  leaf_begin   [num_subgames] int32: first leaf slot of each subgame; a node of kind 3 uses
+ *               slot leaf_begin[subgame] + its internal_idx field
+ *  leaf_beliefs [slots,2,1344] out (top-down sweep): both players' beliefs at each such leaf
+ *  leaf_values  [slots,2,1344] in (bottom-up sweep): both players' values there, in the units
+ *               of the other leaf values (chips / scale)
+ * With leaf_beliefs == NULL / leaf_values == NULL such leaves are skipped / valued 0. */
+int p2b_cfr_step(const void* subgames, const void* nodes, int32_t num_subgames, int32_t max_children,
+                 int32_t max_internal, const unsigned char* tables, const float* root_beliefs,
+                 float* regrets, float* weight_sums, float* policy_avg, float* policy,
+                 float* root_values, float* values_avg, float* beliefs_avg, float* exploitability,
+                 float* br_values, float* scratch, int64_t scratch_floats, const void* scalars,
+                 int32_t iterations, int32_t cfr_plus, int32_t init_depth, int32_t* work_counter,
+                 int32_t num_blocks, int32_t pass_begin, int32_t pass_end, int32_t phases,
+                 float* carry_sums, float* carry_roots, const int32_t* leaf_begin, float* leaf_beliefs,
+                 const float* leaf_values, void* stream);
+
 /* p2b_cfr_solve_noalloc -- the same solve without any allocation.  (No counterpart in the
  * upstream project: it exists for hosts of this library that cannot allocate.)
  *

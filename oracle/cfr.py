@@ -1,7 +1,8 @@
 """CPU oracle of the subgame CFR loop on a ragged public tree.  Test infrastructure only.
 
 Restates, with torch CPU tensors and the same fp32 operations in the same order, the
-upstream sparse evaluator for trees whose leaves are all terminal (fold or showdown):
+upstream sparse evaluator (leaves: fold, showdown, or valued by a caller-supplied
+`leaf_fn`, the stand-in for the value network of `set_leaf_values` :1025-1047):
 p2/search/cfr_evaluator.py (`initialize_policy_and_beliefs` :830-886, `cfr_iteration`
 :1331-1381, `compute_instantaneous_regrets` :1117-1165, `update_policy` :1168-1193,
 `update_average_policy` :1195-1258, `compute_expected_values` :1049-1115,
@@ -31,7 +32,7 @@ H = cards.NUM_HANDS
 class SubgameOracle:
     def __init__(self, tree: dict, root_beliefs: torch.Tensor, *, iterations: int,
                  alpha: float = 1.5, beta: float = 0.0, gamma: float = 2.0,
-                 dcfr_delay: int = 0, cfr_type: str = "discounted", cfr_plus: bool = False):
+                 dcfr_delay: int = 0, cfr_type: str = "discounted", cfr_plus: bool = False, leaf_fn=None):
         t = {k: (torch.from_numpy(np.ascontiguousarray(v)) if isinstance(v, np.ndarray) else v)
              for k, v in tree.items()}
         self.offs = [int(x) for x in tree["depth_offsets"]]
@@ -53,6 +54,9 @@ class SubgameOracle:
         self.dcfr_delay = dcfr_delay
         self.cfr_type = cfr_type
         self.cfr_plus = cfr_plus
+        # leaves that are not terminal are valued by leaf_fn(beliefs[idx] [L,2,1326], idx) -> [L,2,1326]
+        self.leaf_fn = leaf_fn
+        self.model_idx = torch.where(self.leaf & ~self.done)[0]
         N, M = self.N, self.M
 
         self.prev_actor = torch.full((M,), -1, dtype=torch.long)
@@ -171,6 +175,8 @@ class SubgameOracle:
     # ---- leaves and backup ----
     def set_leaf_values(self, beliefs=None):
         beliefs = self.beliefs if beliefs is None else beliefs
+        if self.model_idx.numel() and self.leaf_fn is not None:
+            self.values[self.model_idx] = self.leaf_fn(beliefs[self.model_idx], self.model_idx).float()
         if self.sd_idx.numel():
             vals = showdown.showdown_values(self.sd_boards, beliefs[self.sd_idx], self.sd_potential,
                                             self.scale[self.sd_idx])

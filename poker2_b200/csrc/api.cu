@@ -122,6 +122,74 @@ int p2b_cfr_solve(const void* subgames, const void* nodes, int32_t num_subgames,
     return launch_cfr_solve(p, num_blocks, max_children, (cudaStream_t)stream);
 }
 
+// Part of a solve: the passes pass_begin..pass_end, top-down and/or bottom-up sweeps.
+int p2b_cfr_step(const void* subgames, const void* nodes, int32_t num_subgames, int32_t max_children,
+                 int32_t max_internal, const unsigned char* tables, const float* root_beliefs, float* regrets,
+                 float* weight_sums, float* policy_avg, float* policy, float* root_values, float* values_avg,
+                 float* beliefs_avg, float* exploitability, float* br_values, float* scratch, int64_t scratch_floats,
+                 const void* scalars, int32_t iterations, int32_t cfr_plus, int32_t init_depth, int32_t* work_counter,
+                 int32_t num_blocks, int32_t pass_begin, int32_t pass_end, int32_t phases, float* carry_sums,
+                 float* carry_roots, const int32_t* leaf_begin, float* leaf_beliefs, const float* leaf_values,
+                 void* stream) {
+    P2B_REQUIRE(num_subgames >= 0 && iterations >= 1, "bad count");
+    if (num_subgames == 0) return P2B_OK;
+    P2B_REQUIRE(subgames && nodes && root_beliefs && regrets && policy_avg && root_values && scratch && work_counter &&
+                    scalars && carry_sums && carry_roots,
+                "null pointer");
+    P2B_REQUIRE(max_internal >= 1, "max_internal must be positive");
+    P2B_REQUIRE(!exploitability || values_avg, "exploitability needs values_avg");
+    P2B_REQUIRE(pass_begin >= -1 && pass_begin <= pass_end && pass_end <= iterations, "pass range outside [-1, iterations]");
+    P2B_REQUIRE(phases >= 1 && phases <= 3, "phases must be 1 (top-down), 2 (bottom-up) or 3 (both)");
+    P2B_REQUIRE(phases == 3 || pass_begin == pass_end, "a single sweep direction covers exactly one pass");
+    P2B_REQUIRE((!leaf_beliefs && !leaf_values) || leaf_begin, "leaf arrays need leaf_begin");
+    if (num_blocks <= 0) num_blocks = cfr_default_blocks();
+    if (num_blocks > num_subgames) num_blocks = num_subgames;
+    P2B_REQUIRE(scratch_floats >= cfr_scratch_floats(max_internal) * num_subgames,
+                "scratch too small (stepped solves keep one set of work rows per subgame)");
+    const uintptr_t align = reinterpret_cast<uintptr_t>(subgames) | reinterpret_cast<uintptr_t>(nodes) |
+                            reinterpret_cast<uintptr_t>(tables) | reinterpret_cast<uintptr_t>(root_beliefs) |
+                            reinterpret_cast<uintptr_t>(regrets) | reinterpret_cast<uintptr_t>(weight_sums) |
+                            reinterpret_cast<uintptr_t>(policy_avg) | reinterpret_cast<uintptr_t>(policy) |
+                            reinterpret_cast<uintptr_t>(root_values) | reinterpret_cast<uintptr_t>(values_avg) |
+                            reinterpret_cast<uintptr_t>(beliefs_avg) | reinterpret_cast<uintptr_t>(scratch) |
+                            reinterpret_cast<uintptr_t>(carry_roots) | reinterpret_cast<uintptr_t>(leaf_beliefs) |
+                            reinterpret_cast<uintptr_t>(leaf_values);
+    P2B_REQUIRE((align & 15) == 0, "all row arrays must be 16-byte aligned");
+    CfrParams p{};
+    p.subgames = static_cast<const SubgameRec*>(subgames);
+    p.nodes = static_cast<const NodeRec*>(nodes);
+    p.num_subgames = num_subgames;
+    p.tables = tables;
+    p.root_beliefs = root_beliefs;
+    p.regrets = regrets;
+    p.weight_sums = weight_sums;
+    p.policy_avg = policy_avg;
+    p.policy = policy;
+    p.root_values = root_values;
+    p.values_avg = values_avg;
+    p.beliefs_avg = beliefs_avg;
+    p.exploitability = exploitability;
+    p.br_values = br_values;
+    p.scratch = scratch;
+    p.scratch_stride = cfr_scratch_floats(max_internal);
+    p.max_internal = max_internal;
+    p.scalars = static_cast<const IterScalars*>(scalars);
+    p.iterations = iterations;
+    p.cfr_plus = cfr_plus;
+    p.init_depth = init_depth;
+    p.work_counter = work_counter;
+    p.stepped = 1;
+    p.pass_begin = pass_begin;
+    p.pass_end = pass_end;
+    p.phases = phases;
+    p.carry_sums = carry_sums;
+    p.carry_roots = carry_roots;
+    p.leaf_begin = leaf_begin;
+    p.leaf_beliefs = leaf_beliefs;
+    p.leaf_values = leaf_values;
+    return launch_cfr_solve(p, num_blocks, max_children, (cudaStream_t)stream);
+}
+
 int64_t p2b_cfr_noalloc_scratch_floats(void) { return cfr_static_scratch_floats(); }
 
 // Allocation-free twin of p2b_cfr_solve: work rows, queue counter and combo table come from

@@ -173,6 +173,10 @@ struct Block {
         return base + ((long long)(sg.node_begin + node) * 2 + pl) * P2B_HPAD;
     }
     __device__ __forceinline__ float* stage_row(int r) const { return xs + r * P2B_HPAD; }
+    int leaf0;  // first model-leaf slot of the current subgame
+    __device__ __forceinline__ long long leaf_row(int leaf_rank, int pl) const {
+        return ((long long)(leaf0 + leaf_rank) * 2 + pl) * P2B_HPAD;
+    }
 };
 
 // Policy of the K (== k) children of one node: uniform (start pass), the stored average policy
@@ -475,13 +479,19 @@ __device__ __forceinline__ void sweep_down(int mode, int pass, const CfrParams& 
             for (int c = 0; c < K; ++c) {
                 const NodeRec ch = B.nodes[fc + c];
                 stv<VPT>(B.row1(p.policy_avg, fc + c), tid, P[c]);
-                if (ch.kind != kInternal) continue;
+                if (ch.kind != kInternal && !(ch.kind == kModelLeaf && p.leaf_beliefs)) continue;
                 FV<VPT> x[2];
 #pragma unroll
                 for (int i = 0; i < VPT; ++i) {
                     const float xa = __fmul_rn(b1a.v[i], P[c].v[i]);
                     x[0].v[i] = a == 0 ? xa : b1o.v[i];
                     x[1].v[i] = a == 0 ? b1o.v[i] : xa;
+                }
+                if (ch.kind == kModelLeaf) {  // a leaf row is normalised once per level from its own down
+                    for (int rep = ch.depth; rep <= p.init_depth; ++rep) normalize2<VPT>(B, hi, x);
+                    stv<VPT>(p.leaf_beliefs + B.leaf_row(ch.internal_idx, 0), tid, x[0]);
+                    stv<VPT>(p.leaf_beliefs + B.leaf_row(ch.internal_idx, 1), tid, x[1]);
+                    continue;
                 }
                 normalize2<VPT>(B, hi, x);
                 stv<VPT>(B.reach(ch.internal_idx, 0), tid, x[0]);
@@ -565,7 +575,7 @@ __device__ __forceinline__ void sweep_down(int mode, int pass, const CfrParams& 
         for (int c = 0; c < K; ++c)
             {
                 const NodeRec ch = B.nodes[fc + c];
-                if (ch.kind == kFoldLeaf || ch.kind == kModelLeaf) continue;
+                if (ch.kind == kFoldLeaf || (ch.kind == kModelLeaf && !p.leaf_beliefs)) continue;
                 FV<VPT> t, u;
 #pragma unroll
                 for (int i = 0; i < VPT; ++i) {
@@ -573,6 +583,16 @@ __device__ __forceinline__ void sweep_down(int mode, int pass, const CfrParams& 
                     u.v[i] = __fmul_rn(prior_a.v[i], t.v[i]);
                 }
                 stv<VPT>(B.stage_row(bank + c), tid, u);
+                if (ch.kind == kModelLeaf) {
+                    // unnormalised rows now; normalised in place at the end of the sweep, when
+                    // the sums are known
+                    const FV<VPT> prior_o = pick<VPT>(prior, 1 - a);
+                    FV<VPT> w;
+#pragma unroll
+                    for (int i = 0; i < VPT; ++i) w.v[i] = __fmul_rn(prior_o.v[i], rna.v[i]);
+                    stv<VPT>(p.leaf_beliefs + B.leaf_row(ch.internal_idx, a), tid, u);
+                    stv<VPT>(p.leaf_beliefs + B.leaf_row(ch.internal_idx, 1 - a), tid, w);
+                }
                 if (ch.kind == kInternal) {
                     stv<VPT>(B.reach(ch.internal_idx, a), tid, t);
                     stv<VPT>(B.reach(ch.internal_idx, 1 - a), tid, rna);
@@ -582,7 +602,7 @@ __device__ __forceinline__ void sweep_down(int mode, int pass, const CfrParams& 
         const int warp = tid >> 5;
         if (warp < k) {
             const NodeRec ch = B.nodes[fc + warp];
-            if (ch.kind == kInternal || ch.kind == kShowdownLeaf) {
+            if (ch.kind == kInternal || ch.kind == kShowdownLeaf || (ch.kind == kModelLeaf && p.leaf_beliefs)) {
                 const float sum = row_sum_reference_order(B.stage_row(bank + warp));
                 if ((tid & 31) == 0) {
                     B.sig[(fc + warp) * 2 + a] = sum;
@@ -594,6 +614,20 @@ __device__ __forceinline__ void sweep_down(int mode, int pass, const CfrParams& 
         dispatch_children(k, node_body);
     }
     __syncthreads();
+    if (p.leaf_beliefs && mode != kPassInit) {
+        // beliefs at the model leaves: divide the rows written above by their sums
+        for (int j = 1; j < B.sg.n_nodes; ++j) {
+            const NodeRec nd = B.nodes[j];
+            if (nd.kind != kModelLeaf) continue;
+#pragma unroll
+            for (int pl = 0; pl < 2; ++pl) {
+                float* row = p.leaf_beliefs + B.leaf_row(nd.internal_idx, pl);
+                FV<VPT> x = ldv<VPT>(row, tid);
+                apply_norm<VPT>(B, hi, x, B.sig[j * 2 + pl]);
+                stv<VPT>(row, tid, x);
+            }
+        }
+    }
 }
 
 // ---- bottom-up sweep of one pass ------------------------------------------------------
@@ -760,6 +794,9 @@ __device__ __forceinline__ void sweep_up(int mode, int pass, const CfrParams& p,
                     V_a.v[i] = div_exact(__fmul_rn(eva.v[i], pot_a), dscale);
                     V_o.v[i] = div_exact(__fmul_rn(evo.v[i], pot_o), dscale);
                 }
+            } else if (p.leaf_values) {  // valued by the caller's model between the sweeps
+                V_a = ldv<VPT>(p.leaf_values + B.leaf_row(ch.internal_idx, a), tid);
+                V_o = ldv<VPT>(p.leaf_values + B.leaf_row(ch.internal_idx, o), tid);
             } else {
 #pragma unroll
                 for (int i = 0; i < VPT; ++i) V_a.v[i] = V_o.v[i] = 0.0f;
@@ -987,7 +1024,6 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
     B.nat = reinterpret_cast<uint16_t*>(smem + kOffNat);
     B.misc = reinterpret_cast<int*>(smem + kOffMisc);
     B.fsum = reinterpret_cast<float*>(smem + kOffMisc + 16);
-    B.scr = p.scratch + (long long)blockIdx.x * p.scratch_stride;
     const int tid = threadIdx.x;
 
     // hands holding each card, in combo order (used by the per-card sums)
@@ -1012,6 +1048,9 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
         const int s = B.misc[0];
         if (s >= p.num_subgames) break;
         B.sg = p.subgames[s];
+        // work rows: one set per block, or one per subgame when state is carried between launches
+        B.scr = p.scratch + (long long)(p.stepped ? s : (int)blockIdx.x) * p.scratch_stride;
+        B.leaf0 = p.leaf_begin ? p.leaf_begin[s] : 0;
         {
             const uint4* src = reinterpret_cast<const uint4*>(p.nodes + B.sg.node_begin);
             for (int i = tid; i < B.sg.n_nodes; i += NT) reinterpret_cast<uint4*>(B.nodes)[i] = src[i];
@@ -1026,13 +1065,27 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
         // prior = root beliefs the node beliefs of a pass are derived from; root_b = the
         // root's own row, renormalised once per pass like every other row upstream.
         FV<VPT> prior[2], root_b[2];
-        root_b[0] = ldv<VPT>(p.root_beliefs + ((long long)s * 2 + 0) * P2B_HPAD, tid);
-        root_b[1] = ldv<VPT>(p.root_beliefs + ((long long)s * 2 + 1) * P2B_HPAD, tid);
+        const int pass_first = p.stepped ? p.pass_begin : -1, pass_last = p.stepped ? p.pass_end : p.iterations;
+        const bool run_down = !p.stepped || (p.phases & 1), run_up = !p.stepped || (p.phases & 2);
+        const bool resume = p.stepped && !(pass_first < 0 && run_down);  // continue from carried state
+        if (resume) {
+            const float* cr = p.carry_roots + (long long)s * 4 * P2B_HPAD;
+            prior[0] = ldv<VPT>(cr, tid);
+            prior[1] = ldv<VPT>(cr + P2B_HPAD, tid);
+            root_b[0] = ldv<VPT>(cr + 2 * P2B_HPAD, tid);
+            root_b[1] = ldv<VPT>(cr + 3 * P2B_HPAD, tid);
+            for (int i = tid; i < 2 * B.sg.n_nodes; i += NT) B.sig[i] = p.carry_sums[(long long)B.sg.node_begin * 2 + i];
+        } else {
+            root_b[0] = ldv<VPT>(p.root_beliefs + ((long long)s * 2 + 0) * P2B_HPAD, tid);
+            root_b[1] = ldv<VPT>(p.root_beliefs + ((long long)s * 2 + 1) * P2B_HPAD, tid);
+        }
         __syncthreads();
 
-        for (int pass = -1; pass <= p.iterations; ++pass) {
+        for (int pass = pass_first; pass <= pass_last; ++pass) {
             const int mode = pass < 0 ? kPassInit : (pass == p.iterations ? kPassFinal : kPassIter);
-            if (mode == kPassInit) {
+            if (!run_down) {
+                // the top-down sweep of this pass ran in an earlier launch
+            } else if (mode == kPassInit) {
                 // prior = the given ranges restricted to the allowed hands; the root's own row is
                 // normalised once per tree level during the start pass (see sweep_down)
 #pragma unroll
@@ -1051,10 +1104,19 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
                 // a child's row of the player who did not act is the root's row; so is its sum
                 if (tid < 2) B.sig[tid] = B.fsum[tid];
             }
-            sweep_down<VPT, MAXC>(mode, pass, p, B, hi, prior, tid);
-            sweep_up<VPT, MAXC>(mode, pass, p, B, hi, prior, root_b, s, tid);
+            if (run_down) sweep_down<VPT, MAXC>(mode, pass, p, B, hi, prior, tid);
+            if (run_up) sweep_up<VPT, MAXC>(mode, pass, p, B, hi, prior, root_b, s, tid);
         }
-        if (p.exploitability && p.values_avg) {
+        if (p.stepped) {
+            __syncthreads();
+            float* cr = p.carry_roots + (long long)s * 4 * P2B_HPAD;
+            stv<VPT>(cr, tid, prior[0]);
+            stv<VPT>(cr + P2B_HPAD, tid, prior[1]);
+            stv<VPT>(cr + 2 * P2B_HPAD, tid, root_b[0]);
+            stv<VPT>(cr + 3 * P2B_HPAD, tid, root_b[1]);
+            for (int i = tid; i < 2 * B.sg.n_nodes; i += NT) p.carry_sums[(long long)B.sg.node_begin * 2 + i] = B.sig[i];
+        }
+        if (p.exploitability && p.values_avg && run_up && pass_last == p.iterations) {
             // local exploitability of the average policy (cfr_evaluator.py:718-764)
             __syncthreads();
             FV<VPT> base[2], br[2];

@@ -18,7 +18,8 @@ struct NodeRec {
     uint8_t kind;
     uint8_t action;
     uint8_t depth;
-    uint8_t internal_idx;  // rank of this node among the internal nodes of its subgame
+    uint8_t internal_idx;  // rank of this node among the internal nodes of its subgame (model leaf: rank
+                           // among the model leaves of its subgame)
     float v0;              // fold leaf: value of player 0; showdown leaf: chips player 0 can win
     float v1;              // showdown leaf: chips player 1 can win
 };
@@ -73,6 +74,20 @@ struct CfrParams {
     int32_t cfr_plus;
     int32_t init_depth;          // depth of the deepest tree of the batch the subgames were built in
     int32_t* work_counter;       // dynamic subgame queue (zeroed by the launcher)
+    // ---- stepped mode: a launch runs part of the pass sequence and the state that a whole
+    // solve keeps on chip is carried between launches in global memory.  Used when leaves are
+    // valued by a caller-side model between the two sweeps of a pass.  All zero / null in
+    // the one-launch mode.
+    int32_t stepped;             // 0: one launch runs every pass
+    int32_t pass_begin;          // first pass of this launch (-1 = start pass, iterations = final pass)
+    int32_t pass_end;            // last pass of this launch (inclusive)
+    int32_t phases;              // bit 0: top-down sweep, bit 1: bottom-up sweep (+ best responses after
+                                 // the final pass)
+    float* carry_sums;           // [rows][2] normalisation sums of the node beliefs
+    float* carry_roots;          // [B][4][HPAD] prior (2 rows) and root beliefs (2 rows) of the pass
+    const int32_t* leaf_begin;   // [B] first model-leaf slot of each subgame
+    float* leaf_beliefs;         // [slots][2][HPAD] beliefs at the model leaves (out, top-down sweep)
+    const float* leaf_values;    // [slots][2][HPAD] values at the model leaves (in, bottom-up sweep)
 };
 
 // floats of scratch one block needs: per internal node reach[2], average reach[2], values[2]

@@ -72,10 +72,18 @@ class DeviceTreeLayout:
     max_internal: int
     max_children: int
     tree_depth: int  # depth of the deepest tree of the batch
+    # leaves valued by a model (start of the next street, depth limit), in slot order
+    leaf_begin: np.ndarray = None  # [B] int32 first slot of each subgame
+    model_rows: np.ndarray = None  # [slots] row of each model leaf
+    model_nodes: np.ndarray = None  # [slots] level-major (upstream) node index of each model leaf
 
     @property
     def rows(self) -> int:
         return self.nodes.shape[0]
+
+    @property
+    def num_model_leaves(self) -> int:
+        return 0 if self.model_rows is None else int(self.model_rows.shape[0])
 
 
 def device_layout(trees: ptree.PublicTrees, boards: np.ndarray) -> DeviceTreeLayout:
@@ -114,6 +122,14 @@ def device_layout(trees: ptree.PublicTrees, boards: np.ndarray) -> DeviceTreeLay
     root_sorted = trees.root_of[order]
     rec["internal_idx"] = csum - csum[node_begin[root_sorted]]
     n_internal = np.bincount(trees.root_of, weights=internal, minlength=B).astype(np.int64)
+    # model leaves: rank among the model leaves of the subgame, slots in row order
+    is_model = rec["kind"] == ptree.KIND_MODEL
+    mdl = is_model.astype(np.int64)
+    msum = np.cumsum(mdl) - mdl
+    rec["internal_idx"] = np.where(is_model, msum - msum[node_begin[root_sorted]], rec["internal_idx"])
+    n_model = np.bincount(root_sorted, weights=mdl, minlength=B).astype(np.int64)
+    leaf_begin = (np.cumsum(n_model) - n_model).astype(np.int32)
+    model_rows = np.nonzero(is_model)[0]
 
     boards = np.asarray(boards, dtype=np.int64)
     sub = np.zeros(B, dtype=SUBGAME_DTYPE)
@@ -132,7 +148,8 @@ def device_layout(trees: ptree.PublicTrees, boards: np.ndarray) -> DeviceTreeLay
     sub["allowed_prob"] = (np.float32(1.0) / np.maximum(n_allowed, 1).astype(np.float32)).astype(np.float32)
     return DeviceTreeLayout(subgames=sub, nodes=rec, to_level_major=order, from_level_major=pos,
                             max_internal=int(n_internal.max()), max_children=int(trees.child_count.max()),
-                            tree_depth=trees.tree_depth)
+                            tree_depth=trees.tree_depth, leaf_begin=leaf_begin, model_rows=model_rows,
+                            model_nodes=order[model_rows])
 
 
 def pad_rows(x: torch.Tensor) -> torch.Tensor:
@@ -234,6 +251,65 @@ class SubgameSolver:
                 self.num_blocks,
                 _lib.stream_ptr(self.device))
         self.launches += 1
+        return SolveResult(self.layout, self.policy_avg, self.regrets, self.weight_sums, self.policy,
+                           self.root_values, self.values_avg, self.beliefs_avg, self.exploitability, self.br_values)
+
+
+class SteppedSolver(SubgameSolver):
+    """Solves subgames whose non-terminal leaves are valued by a caller-side model
+    (`set_leaf_values`, p2/search/cfr_evaluator.py:1025-1047): every pass is two launches
+    (`p2b_cfr_step`) with the model call in between.
+
+    `leaf_fn(beliefs)` receives the beliefs at the model leaves, [slots,2,1344] fp32 on the
+    device (columns 1326.. are padding; slot order = `layout.model_rows`), and returns their
+    values for both players in the same shape (or [slots,2,1326]), in chips / scale."""
+
+    def __init__(self, layout: DeviceTreeLayout, boards: torch.Tensor, device: torch.device, **kw):
+        super().__init__(layout, boards, device, **kw)
+        f32 = dict(device=device, dtype=torch.float32)
+        n_scratch = int(_lib.lib().p2b_cfr_scratch_floats(layout.max_internal, 1)) * self.B
+        self.scratch = torch.empty(n_scratch, **f32)
+        self.carry_sums = torch.zeros(layout.rows, 2, **f32)
+        self.carry_roots = torch.zeros(self.B, 4, HPAD, **f32)
+        slots = max(layout.num_model_leaves, 1)
+        self.leaf_begin = torch.from_numpy(np.ascontiguousarray(layout.leaf_begin, dtype=np.int32)).to(device)
+        self.leaf_beliefs = torch.zeros(slots, 2, HPAD, **f32)
+        self.leaf_values = torch.zeros(slots, 2, HPAD, **f32)
+
+    def _step(self, root_beliefs, sc, iterations, cfr_plus, pass_begin, pass_end, phases) -> None:
+        p = _lib.ptr
+        with torch.cuda.device(self.device):
+            _lib.call(
+                "p2b_cfr_step", p(self.subgames), p(self.nodes), self.B, self.layout.max_children,
+                self.layout.max_internal, p(self.tables.blob) if self.tables is not None else None, p(root_beliefs),
+                p(self.regrets), p(self.weight_sums), p(self.policy_avg), p(self.policy), p(self.root_values),
+                p(self.values_avg), p(self.beliefs_avg), p(self.exploitability), p(self.br_values), p(self.scratch),
+                self.scratch.numel(), p(sc), iterations, int(cfr_plus), self.layout.tree_depth, p(self.work_counter),
+                self.num_blocks, pass_begin, pass_end, phases, p(self.carry_sums), p(self.carry_roots),
+                p(self.leaf_begin), p(self.leaf_beliefs), p(self.leaf_values), _lib.stream_ptr(self.device))
+        self.launches += 1
+
+    def solve(self, root_beliefs: torch.Tensor, scalars: np.ndarray, leaf_fn=None, *,
+              cfr_plus: bool = False) -> SolveResult:
+        assert root_beliefs.shape == (self.B, 2, HPAD) and root_beliefs.dtype == torch.float32
+        assert root_beliefs.is_contiguous() and root_beliefs.device == self.device
+        iterations = int(scalars.shape[0])
+        sc = torch.from_numpy(scalars.view(np.uint8).reshape(iterations, 32).copy()).to(self.device)
+        self._scalars = sc
+        n_leaves = self.layout.num_model_leaves
+        if n_leaves and leaf_fn is None:
+            raise ValueError("the trees have model-valued leaves: a leaf_fn is required")
+        for pas in range(-1, iterations + 1):
+            if n_leaves == 0:
+                self._step(root_beliefs, sc, iterations, cfr_plus, pas, pas, 3)
+                continue
+            self._step(root_beliefs, sc, iterations, cfr_plus, pas, pas, 1)
+            vals = leaf_fn(self.leaf_beliefs[:n_leaves])
+            if vals.shape[-1] == NUM_HANDS:
+                self.leaf_values[:n_leaves, :, :NUM_HANDS].copy_(vals)
+            else:
+                self.leaf_values[:n_leaves].copy_(vals)
+            self._step(root_beliefs, sc, iterations, cfr_plus, pas, pas, 2)
         return SolveResult(self.layout, self.policy_avg, self.regrets, self.weight_sums, self.policy,
                            self.root_values, self.values_avg, self.beliefs_avg, self.exploitability, self.br_values)
 

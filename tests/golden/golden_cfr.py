@@ -217,7 +217,85 @@ def gen_cfr() -> None:
     run_cfr("batch_cap2_t24", b, r, p, s, 24, cap=2)
 
 
-SECTIONS = {"tree": gen_tree, "cfr": gen_cfr}
+def hand_weights() -> torch.Tensor:
+    """Fixed per-hand weights in [-1, 1] used by PotEchoModel."""
+    return torch.rand(1326, generator=torch.Generator().manual_seed(77)) * 2 - 1
+
+
+class PotEchoModel(ZeroModel):
+    """Deterministic stand-in for the value network at non-terminal leaves: the values of a
+    leaf are an elementwise function of its beliefs, of a fixed per-hand weight w and of the
+    pot fraction the upstream feature encoder puts into context[:, 2]
+    (rebel_feature_encoder.py:104-108): s = 0.5 + pot_fraction;
+    v0 = s*w + b1; v1 = (s*w)*(-0.5) + b0."""
+
+    def __call__(self, features, include_policy=True, **kw):
+        from p2.models.model_output import ModelOutput
+
+        n = len(features)
+        bel = features.beliefs.view(n, 2, 1326).float()
+        s = (0.5 + features.context[:, 2].float()).view(n, 1)
+        sw = s * hand_weights().view(1, 1326)
+        hv = torch.stack([sw + bel[:, 1], sw * (-0.5) + bel[:, 0]], dim=1)
+        return ModelOutput(policy_logits=torch.zeros(n, 1326, self.num_actions), value=torch.zeros(n), hand_values=hv)
+
+
+def turn_env(boards: torch.Tensor, pot: torch.Tensor, stack: torch.Tensor):
+    """Environments at the start of the turn betting round with the given 4-card boards."""
+    from p2.env.hunl_tensor_env import HUNLTensorEnv
+
+    n = boards.shape[0]
+    env = HUNLTensorEnv(num_envs=n, starting_stack=1000, sb=SB, bb=BB, default_bet_bins=BET_BINS,
+                        device=torch.device("cpu"), rng=torch.Generator().manual_seed(0))
+    decks = []
+    for b in boards.tolist():
+        unused = [c for c in range(52) if c not in b]
+        decks.append(unused[:4] + b + unused[4:5])
+    env.reset(force_deck=torch.tensor(decks), force_button=torch.zeros(n, dtype=torch.long))
+    for _ in range(4):
+        env.step_bins(torch.ones(n, dtype=torch.long))
+    assert (env.street == 2).all() and (env.actions_this_round == 0).all()
+    env.pot[:] = pot
+    env.stacks[:] = stack[:, None]
+    env.starting_stacks[:] = (stack + pot // 2)[:, None]
+    env.scale[:] = (stack + pot // 2).float()
+    if hasattr(env, "raises"):
+        env.raises[:] = 0
+    return env
+
+
+def gen_turn() -> None:
+    """Turn subgames: every non-fold leaf is the start of the river, valued by the model."""
+    import make_golden
+    from p2.search.sparse_cfr_evaluator import SparseCFREvaluator
+
+    g = torch.Generator().manual_seed(11)
+    n, iterations, cap, depth = 3, 16, 2, 8
+    boards = torch.stack([torch.randperm(52, generator=g)[:4] for _ in range(n)])
+    ranges = make_golden.dirichlet_ranges(boards, g)
+    pot = torch.randint(20, 201, (n,), generator=g)
+    stack = torch.randint(100, 1001, (n,), generator=g)
+    install_raise_cap(cap)
+    ev = make_evaluator(n, iterations, depth=depth)
+    ev.model = PotEchoModel(len(BET_BINS) + 3)
+    ev.initialize_subgame(turn_env(boards, pot, stack), torch.arange(n), ranges)
+    ev.evaluate_cfr()
+    ex = ev._compute_exploitability()
+    install_raise_cap(None)
+    model_mask = ev.leaf_mask & ~ev.env.done
+    print("turn nodes", ev.total_nodes, "model leaves", int(model_mask.sum()), "showdown", int((ev.env.street == 4).sum()),
+          "exploitability", ex.local_exploitability.tolist())
+    save("cfr_turn_cap2_t16.npz",
+         boards=boards.to(torch.int16).numpy(), ranges=ranges.numpy(), pot=pot.numpy(), stack=stack.numpy(),
+         iterations=np.int64(iterations), cap=np.int64(cap), max_depth=np.int64(depth),
+         total_nodes=np.int64(ev.total_nodes), model_mask=model_mask.numpy(), hand_weights=hand_weights().numpy(),
+         policy_avg=ev.policy_probs_avg.numpy(), root_values=ev.values_avg[:n].numpy(),
+         regrets=ev.cumulative_regrets.numpy(), leaf_mask=ev.leaf_mask.numpy(),
+         parent_index=ev.parent_index.numpy(), street=ev.env.street.numpy(),
+         exploitability=ex.local_exploitability.numpy(), br_values=ex.local_best_response_values.numpy())
+
+
+SECTIONS = {"tree": gen_tree, "cfr": gen_cfr, "turn": gen_turn}
 
 
 class _BeliefEchoModel:

@@ -75,3 +75,57 @@ def test_local_exploitability_matches_upstream(cuda_device, golden_dir, name):
     # asking for exploitability must not change the solution
     torch.testing.assert_close(res.root_values[..., :1326].cpu(), torch.from_numpy(z["root_values"]),
                                rtol=RTOL, atol=ATOL)
+
+
+def _stepped_turn(z, device, **kw):
+    from leaf_models import pot_echo_leaf_fn
+    from poker2_b200 import solver, tree as ptree
+
+    roots = ptree.root_states(z["pot"], z["stack"], min_raise=2, street=2)
+    trees = ptree.build_trees(roots, [0.5, 1.0], int(z["max_depth"]), bb=2, max_raises=int(z["cap"]))
+    boards = np.concatenate([z["boards"].astype(np.int64), np.full((z["boards"].shape[0], 1), -1)], axis=1)
+    layout = solver.device_layout(trees, boards)
+    assert layout.num_model_leaves == int(z["model_mask"].sum())
+    sv = solver.SteppedSolver(layout, torch.from_numpy(boards), device, **kw)
+    leaf_fn = pot_echo_leaf_fn(trees, layout.model_nodes, torch.from_numpy(z["hand_weights"]))
+    rb = solver.pad_rows(torch.from_numpy(z["ranges"]).to(device)).contiguous()
+    res = sv.solve(rb, solver.iteration_scalars(int(z["iterations"])), leaf_fn)
+    return res, trees, sv
+
+
+def test_model_valued_leaves_match_upstream(cuda_device, golden_dir):
+    """Turn subgames, leaves at the start of the river valued by a stand-in model between
+    the two sweeps of every pass (p2b_cfr_step), against the upstream evaluator run with the
+    same model."""
+    z = np.load(os.path.join(golden_dir, "cfr_turn_cap2_t16.npz"))
+    res, trees, sv = _stepped_turn(z, cuda_device, exploitability=True)
+    n = trees.num_roots
+    assert sv.launches == 2 * (int(z["iterations"]) + 2)
+    for name, got, want in [("regrets", res.regrets, z["regrets"]), ("policy_avg", res.policy_avg, z["policy_avg"])]:
+        got = res.level_major(got).cpu()[n:]
+        want = torch.from_numpy(want)[n:]
+        _report(name, got, want)
+        torch.testing.assert_close(got, want, rtol=RTOL, atol=ATOL)
+    vals = res.root_values[..., :1326].cpu()
+    _report("root_values", vals, torch.from_numpy(z["root_values"]))
+    torch.testing.assert_close(vals, torch.from_numpy(z["root_values"]), rtol=RTOL, atol=ATOL)
+    torch.testing.assert_close(res.exploitability.cpu(), torch.from_numpy(z["exploitability"]), rtol=1e-4, atol=1e-6)
+    torch.testing.assert_close(res.br_values.cpu(), torch.from_numpy(z["br_values"]), rtol=1e-4, atol=1e-6)
+
+
+@pytest.mark.parametrize("name", ["cfr_single_cap2_t8", "cfr_batch_cap2_t24"])
+def test_stepped_solve_equals_one_launch_solve(cuda_device, golden_dir, name):
+    """River subgames (no model leaves) solved pass by pass through p2b_cfr_step give the
+    bits of the one-launch solve."""
+    from poker2_b200 import solver, tree as ptree
+
+    z = np.load(os.path.join(golden_dir, name + ".npz"))
+    res, trees = _solve_golden(z, cuda_device, exploitability=True)
+    cap = int(z["cap"])
+    layout = solver.device_layout(trees, z["boards"].astype(np.int64))
+    sv = solver.SteppedSolver(layout, torch.from_numpy(z["boards"].astype(np.int64)), cuda_device, exploitability=True)
+    rb = solver.pad_rows(torch.from_numpy(z["ranges"]).to(cuda_device)).contiguous()
+    res2 = sv.solve(rb, solver.iteration_scalars(int(z["iterations"])))
+    for a, b in [(res.regrets, res2.regrets), (res.policy_avg, res2.policy_avg), (res.root_values, res2.root_values),
+                 (res.weight_sums, res2.weight_sums), (res.exploitability, res2.exploitability)]:
+        assert torch.equal(a, b)

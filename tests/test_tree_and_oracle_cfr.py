@@ -5,6 +5,7 @@ import numpy as np
 import pytest
 import torch
 
+from leaf_models import pot_echo_leaf_fn
 from oracle import cfr as ocfr
 from poker2_b200 import tree as ptree
 
@@ -62,3 +63,39 @@ def test_cfr_oracle_bit_exact_other_trees(golden_dir, name):
     assert torch.equal(o.values_avg[: o.N], torch.from_numpy(z["root_values"]))
     ex, _ = o.exploitability()
     assert torch.equal(ex, torch.from_numpy(z["exploitability"]))
+
+
+def _turn_trees(z):
+    roots = ptree.root_states(z["pot"], z["stack"], min_raise=2, street=2)
+    return ptree.build_trees(roots, BET_BINS, int(z["max_depth"]), bb=2, max_raises=int(z["cap"]))
+
+
+def test_turn_tree_matches_upstream(golden_dir):
+    z = np.load(os.path.join(golden_dir, "cfr_turn_cap2_t16.npz"))
+    t = _turn_trees(z)
+    assert t.total_nodes == int(z["total_nodes"])
+    assert np.array_equal(t.parent_index, z["parent_index"])
+    assert np.array_equal(t.leaf_mask, z["leaf_mask"])
+    assert np.array_equal(t.state.street, z["street"])
+    assert np.array_equal(t.leaf_mask & ~t.state.done, z["model_mask"])
+
+
+def test_cfr_oracle_with_model_leaves_bit_exact(golden_dir):
+    """Turn subgames whose non-fold leaves are valued by a stand-in model, against the
+    upstream evaluator run with the same model."""
+    z = np.load(os.path.join(golden_dir, "cfr_turn_cap2_t16.npz"))
+    t = _turn_trees(z)
+    boards = np.concatenate([z["boards"].astype(np.int64), np.full((z["boards"].shape[0], 1), -1)], axis=1)
+    w = torch.from_numpy(z["hand_weights"])
+
+    def leaf_fn(beliefs, idx):
+        return pot_echo_leaf_fn(t, idx, w)(beliefs)
+
+    o = ocfr.SubgameOracle(t.oracle_dict(boards), torch.from_numpy(z["ranges"]), iterations=int(z["iterations"]),
+                           leaf_fn=leaf_fn).solve()
+    assert torch.equal(o.regrets, torch.from_numpy(z["regrets"]))
+    assert torch.equal(o.policy_avg, torch.from_numpy(z["policy_avg"]))
+    assert torch.equal(o.values_avg[: o.N], torch.from_numpy(z["root_values"]))
+    ex, br = o.exploitability()
+    assert torch.equal(ex, torch.from_numpy(z["exploitability"]))
+    assert torch.equal(br, torch.from_numpy(z["br_values"]))
