@@ -356,3 +356,37 @@ def solve_subgames(boards, ranges, pot, stacks, *, iterations: int, bet_bins=(0.
     rb = pad_rows(torch.as_tensor(ranges, dtype=torch.float32).to(device)).contiguous()
     scal = iteration_scalars(iterations, cfr_type=cfr_type, alpha=alpha, beta=beta, gamma=gamma, dcfr_delay=dcfr_delay)
     return solver.solve(rb, scal, cfr_plus=cfr_plus), trees
+
+
+def solve_subgames_with_model(boards, ranges, pot, stacks, model, *, street: int, iterations: int,
+                              bet_bins=(0.5, 1.0), max_depth: int = 8, max_raises=None, bb: int = 2,
+                              cfr_type: str = "discounted", alpha: float = 1.5, beta: float = 0.0, gamma: float = 2.0,
+                              dcfr_delay: int = 0, cfr_plus: bool = False, device=None, chance_average: bool = True,
+                              chunk: int = 2048, exploitability: bool = False, keep_node_values: bool = False):
+    """Solves a batch of flop (street=1, 3 board cards) or turn (street=2, 4 cards) subgames
+    whose leaves at the start of the next street are valued by `model(beliefs, boards,
+    context)`, averaged over the next public card when `chance_average` (the
+    `single_card_chance_values` semantics).  Returns (SolveResult, PublicTrees, SteppedSolver)."""
+    from . import leaf_eval
+
+    device = torch.device(device if device is not None else "cuda:0")
+    boards_np = np.asarray(boards.cpu() if torch.is_tensor(boards) else boards, dtype=np.int64)
+    if boards_np.shape[1] < 5:
+        boards_np = np.concatenate([boards_np, np.full((boards_np.shape[0], 5 - boards_np.shape[1]), -1)], axis=1)
+    pot_np = np.asarray(pot.cpu() if torch.is_tensor(pot) else pot, dtype=np.int64)
+    stacks_np = np.asarray(stacks.cpu() if torch.is_tensor(stacks) else stacks, dtype=np.int64)
+    roots = ptree.root_states(pot_np, stacks_np, min_raise=bb, street=street)
+    trees = ptree.build_trees(roots, list(bet_bins), max_depth, bb=bb, max_raises=max_raises)
+    layout = device_layout(trees, boards_np)
+    sv = SteppedSolver(layout, torch.from_numpy(boards_np), device, exploitability=exploitability,
+                       keep_node_values=keep_node_values)
+    leaf_boards = torch.from_numpy(boards_np[trees.root_of[layout.model_nodes]])
+    ctx = leaf_eval.leaf_context(trees, layout.model_nodes)
+    if chance_average:
+        evaluator = leaf_eval.ChanceLeafEvaluator(model, leaf_boards, ctx, device, chunk=chunk)
+    else:
+        evaluator = leaf_eval.DirectLeafEvaluator(model, leaf_boards, ctx, device)
+    rb = pad_rows(torch.as_tensor(ranges, dtype=torch.float32).to(device)).contiguous()
+    scal = iteration_scalars(iterations, cfr_type=cfr_type, alpha=alpha, beta=beta, gamma=gamma, dcfr_delay=dcfr_delay)
+    res = sv.solve(rb, scal, evaluator if layout.num_model_leaves else None, cfr_plus=cfr_plus)
+    return res, trees, sv
