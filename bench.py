@@ -299,6 +299,178 @@ def finish_gpu_arm(args, rank, world, layout, ms_step, value, clocks, e2e, distr
         dist.destroy_process_group()
 
 
+def _time_ms(fn, steps: int, warmup: int) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def run_micro(args):
+    """Rules / showdown micro-benchmark: 2^26 seven-card hands ranked to int32; 4096 river
+    boards (x `--micro-board-factor` so that the working set exceeds L2) with two Dirichlet(1)
+    ranges each, fp32 showdown values for both players."""
+    from poker2_b200 import _lib, build, rules, showdown
+
+    build.build()
+    device = torch.device("cuda:0")
+    torch.cuda.set_device(device)
+    g = torch.Generator(device=device).manual_seed(1)
+    n_hands = 1 << args.micro_log2_hands
+    chunks = []
+    for _ in range(16):
+        r = torch.rand((n_hands // 16, 52), device=device, generator=g)
+        chunks.append(r.argsort(dim=1)[:, :7].to(torch.int16))
+    cards = torch.cat(chunks)
+    del chunks
+    out = torch.empty(n_hands, dtype=torch.int32, device=device)
+    sampler = ClockSampler(0)
+    sampler.start()
+    ms_rank = _time_ms(lambda: _lib.call("p2b_rank7_cards", _lib.ptr(cards), n_hands, _lib.ptr(out),
+                                         _lib.stream_ptr(device)), max(args.steps, 5), max(args.warmup, 3))
+    del cards, out
+    m = 4096 * args.micro_board_factor
+    boards = torch.rand((m, 52), device=device, generator=g).argsort(dim=1)[:, :5].contiguous()
+    hit = torch.zeros(m, 52, dtype=torch.bool, device=device)
+    hit.scatter_(1, boards, True)
+    c1, c2 = np.triu_indices(52, k=1)
+    blocked = hit[:, torch.from_numpy(c1).to(device)] | hit[:, torch.from_numpy(c2).to(device)]
+    bel = torch.empty(m, 2, 1326, device=device).exponential_(generator=g) * (~blocked)[:, None, :]
+    bel = (bel / bel.sum(-1, keepdim=True)).contiguous()
+    pot = torch.ones((m, 2), dtype=torch.int64, device=device)
+    scale = torch.ones(m, device=device)
+    vals = torch.empty_like(bel)
+    holder = {}
+
+    def both():
+        holder["t"] = showdown.BoardTables(boards)
+        showdown.showdown_values(holder["t"], bel, pot, scale, out=vals)
+
+    ms_both = _time_ms(both, max(args.steps, 5), max(args.warmup, 3))
+    tabs = showdown.BoardTables(boards)
+    ms_eval = _time_ms(lambda: showdown.showdown_values(tabs, bel, pot, scale, out=vals), max(args.steps, 5),
+                       max(args.warmup, 3))
+    clocks = sampler.stop()
+    peak, peak_kind = measured_peak_gbs()
+    rank_gbs = n_hands * 18 / ms_rank * 1e-6
+    both_gbs = m * 26520 / ms_both * 1e-6
+    eval_gbs = m * 21216 / ms_eval * 1e-6
+    line = {
+        "metric": "showdown evals/sec", "value": 2 * m / (ms_both / 1e3), "unit": "evals/s", "n_gpus": 1,
+        "steps": max(args.steps, 5), "warmup": max(args.warmup, 3), "ms_per_step": ms_both, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"rules/showdown microbench: {m} river boards x 2 Dirichlet(1) ranges, tables built "
+                               f"per board then evaluated; 2^{args.micro_log2_hands} 7-card hands ranked",
+                   "l2": "inputs larger than L2"},
+        "clocks": clocks, "gpu_launches": 2 * max(args.steps, 5),
+        "roofline": {"bound": "hbm", "achieved": both_gbs, "peak": peak, "unit": "GB/s", "frac": both_gbs / peak,
+                     "traffic": None, "peak_source": peak_kind, "kernel": "board_setup_kernel + showdown_eval_kernel",
+                     "algorithmic_bytes_per_board": 26520},
+        "showdown_eval_only": {"evals_per_s": 2 * m / (ms_eval / 1e3), "ms": ms_eval, "achieved_gbs": eval_gbs,
+                               "frac": eval_gbs / peak, "algorithmic_bytes_per_board": 21216},
+        "rank7": {"hands_per_s": n_hands / (ms_rank / 1e3), "ms": ms_rank, "achieved_gbs": rank_gbs,
+                  "frac": rank_gbs / peak, "algorithmic_bytes_per_hand": 18},
+    }
+    print(json.dumps(line))
+
+
+def make_street_inputs(batch: int, n_board: int, seed: int, alpha: float):
+    g = torch.Generator().manual_seed(seed)
+    boards = torch.rand(batch, 52, generator=g).argsort(dim=1)[:, :n_board]
+    hit = torch.zeros(batch, 52, dtype=torch.bool)
+    hit.scatter_(1, boards, True)
+    c1, c2 = np.triu_indices(52, k=1)
+    blocked = hit[:, torch.from_numpy(c1)] | hit[:, torch.from_numpy(c2)]
+    if alpha == 1.0:
+        gam = torch.empty(batch, 2, 1326).exponential_(generator=g)
+    else:
+        gam = torch._standard_gamma(torch.full((batch, 2, 1326), alpha), generator=g)
+    ranges = gam * (~blocked)[:, None, :]
+    ranges = ranges / ranges.sum(-1, keepdim=True)
+    pot = torch.randint(20, 201, (batch,), generator=g)
+    stack = torch.randint(100, 1001, (batch,), generator=g)
+    return boards, ranges, pot, stack
+
+
+def run_street(args, rank: int, world: int, local_rank: int):
+    """Turn (B=1024, 128 iterations, leaves averaged over the 48 river cards) or flop
+    (B=2048 per GPU, Dirichlet(0.5) ranges, 64 iterations, 49 turn cards) subgames whose
+    leaves are valued by a random-init bf16 MLP (2x1326 + 52 + 3 -> 4 x 1536 GELU -> 2x1326)."""
+    import torch.distributed as dist
+
+    from poker2_b200 import build, leaf_eval, sharding, solver
+
+    build.build()
+    device = torch.device(f"cuda:{local_rank}")
+    torch.cuda.set_device(device)
+    distributed = world > 1
+    if distributed:
+        dist.init_process_group("nccl", device_id=device)
+    turn = args.workload == "turn"
+    street, n_board = (2, 4) if turn else (1, 3)
+    batch = args.batch if args.batch != 4096 else (1024 if turn else 2048)
+    iterations = args.iterations if args.iterations != 256 else (128 if turn else 64)
+    boards, ranges, pot, stack = make_street_inputs(batch, n_board, (3 if turn else 4) + rank, 1.0 if turn else 0.5)
+    model = leaf_eval.ValueMLP(1536, 4, dtype=torch.bfloat16, seed=0).to(device)
+    info = {}
+
+    def step():
+        res, trees, sv = solver.solve_subgames_with_model(
+            boards, ranges, pot, stack, model, street=street, iterations=iterations, bet_bins=BET_BINS,
+            max_depth=MAX_DEPTH, max_raises=MAX_RAISES, device=device, exploitability=True, chunk=args.leaf_chunk)
+        if distributed:
+            sharding.gather_rows(res.root_values)
+            sharding.reduce_exploitability(res.exploitability)
+        info.update(launches=sv.launches, leaves=sv.layout.num_model_leaves, rows=sv.layout.rows)
+        return res
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    if distributed:
+        dist.barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    if distributed:
+        dist.barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms = torch.tensor([e0.elapsed_time(e1)], device=device)
+    if distributed:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_step = float(ms.item()) / args.steps
+    if rank == 0:
+        cards_next = 52 - n_board
+        print(json.dumps({
+            "metric": "subgame-CFR-iterations/sec", "value": world * batch * iterations / (ms_step / 1e3),
+            "unit": "subgame-iterations/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32 solver state, bf16 leaf network", "data": "synthetic",
+            "config": {"workload": f"batched {'turn' if turn else 'flop'} subgames, B={batch} per GPU, {iterations} "
+                                   f"DCFR(1.5,0,2) iterations, leaves at the start of the next street valued by a "
+                                   f"random-init bf16 MLP (2707 -> 4 x 1536 GELU -> 2652) averaged over the "
+                                   f"{cards_next} next cards; tree build, host->device copies and the final "
+                                   "exploitability pass inside the timed region",
+                       "batch_per_gpu": batch, "iterations": iterations, "model_leaves_per_gpu": info["leaves"],
+                       "network_samples_per_pass": info["leaves"] * cards_next, "nodes_per_gpu": info["rows"]},
+            "clocks": clocks, "gpu_launches": info["launches"] * args.steps,
+        }))
+    if distributed:
+        dist.destroy_process_group()
+
+
 def main():
     global BATCH, ITERATIONS
     ap = argparse.ArgumentParser()
@@ -310,6 +482,12 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
     ap.add_argument("--batch", type=int, default=BATCH, help="subgames per GPU (default: the headline 4096)")
     ap.add_argument("--iterations", type=int, default=ITERATIONS, help="DCFR iterations (default: 256)")
+    ap.add_argument("--workload", default="river", choices=["river", "micro", "turn", "flop"],
+                    help="river = the headline batched river solve; micro = rules/showdown micro-benchmark; "
+                         "turn / flop = subgames with network-valued leaves")
+    ap.add_argument("--micro-log2-hands", type=int, default=26)
+    ap.add_argument("--micro-board-factor", type=int, default=4, help="boards = 4096 x this")
+    ap.add_argument("--leaf-chunk", type=int, default=2048, help="leaves per network batch (x ~48 samples)")
     args = ap.parse_args()
     BATCH, ITERATIONS = args.batch, args.iterations
     rank = int(os.environ.get("RANK", "0"))
@@ -320,6 +498,13 @@ def main():
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (poker2_b200 has no CPU path)")
+    if args.workload == "micro":
+        if rank == 0:
+            run_micro(args)
+        return
+    if args.workload in ("turn", "flop"):
+        run_street(args, rank, world, local_rank)
+        return
     run_gpu_arm(args, rank, world, local_rank)
 
 
