@@ -5,188 +5,440 @@
 
 namespace p2b {
 
-constexpr int kSetupThreads = 1024;
-constexpr int kSortN = 2048;
+// ---------------------------------------------------------------------------------------
+// Board set-up.  One block per board, 352 threads, four keys per thread.
+//   1. strength of every combo (board cards + two hole cards; combos that overlap the board
+//      are scored with repeated card ids, as p2/env/rules_triton.py:139-146 does);
+//   2. stable LSD radix sort of the 24-bit strengths, four passes of six bits.  A warp ranks
+//      32 consecutive keys with a match instruction; counts per (digit, chunk of 32) are
+//      bytes, scanned in digit-major order to give every key its destination;
+//   3. tie groups [L,R) from the sorted strengths (one block-wide max scan);
+//   4. per-card hand lists in strength order: the 2652 (card, hand) incidences, walked in
+//      strength order, are counting-sorted by card with the same rank/scan machinery;
+//   5. per hand, how many entries of its two cards' lists lie before L and before R.
+// The table blob is assembled in shared memory and written out with 16-byte stores.
+// ---------------------------------------------------------------------------------------
+constexpr int kSetupThreads = 352;
+constexpr int kSetupWarps = kSetupThreads / 32;         // 11
+constexpr int kSortChunks = 44;                         // chunks of 32 keys
+constexpr int kSortN = kSortChunks * 32;                // 1408 >= 1326
+constexpr int kSortRounds = kSortChunks / kSetupWarps;  // 4 chunks per warp
+constexpr int kDigitBits = 6, kDigits = 1 << kDigitBits, kSortPasses = 4;
+constexpr int kIncidences = 2 * P2B_NUM_HANDS;          // 2652
+constexpr int kIncChunks = 84;                          // chunks of 32 incidences (83 used), multiple of 4
+constexpr int kIncRounds = (kIncChunks + kSetupWarps - 1) / kSetupWarps;  // 8
+static_assert(kSortChunks % 4 == 0 && kIncChunks % 4 == 0, "count bytes are scanned four at a time");
+static_assert(kSortChunks == kSortRounds * kSetupWarps, "every warp sorts the same number of chunks");
 
-// One block per board.  boards: [m,5] int16.  Any of tabs / scores / order may be null.
+constexpr int kCntWords = (52 * kIncChunks) / 4;        // 1092 words of four byte counters (>= 64*44/4)
+constexpr int kOffEntries = 52 * kIncChunks;            // 4368 uint16 offsets (>= 64*44)
+
+// shared-memory carve-up (bytes)
+constexpr int kSuKey = 0;                                // uint32 [2][kSortN]
+constexpr int kSuVal = kSuKey + 2 * kSortN * 4;          // uint16 [2][kSortN]
+constexpr int kSuCnt = kSuVal + 2 * kSortN * 2;          // uint32 [kCntWords]
+constexpr int kSuOff = kSuCnt + kCntWords * 4;           // uint16 [kOffEntries]
+constexpr int kSuLg = kSuOff + kOffEntries * 2;          // uint16 [kSortN]   tie-group start per sorted position
+constexpr int kSuRt = kSuLg + kSortN * 2;                // uint16 [kSortN]   tie-group end, indexed by group start
+constexpr int kSuLp = kSuRt + kSortN * 2;                // uint16 [52][52]   sorted position of list entries
+constexpr int kSuBlob = (kSuLp + 52 * 52 * 2 + 15) / 16 * 16;  // the table blob
+constexpr int kSuWarp = kSuBlob + kTabBytes;             // uint32 [16] warp totals of the block scan
+constexpr int kSetupSmem = kSuWarp + 64;
+static_assert(kSuCnt % 4 == 0 && kSuBlob % 16 == 0 && kSuWarp % 4 == 0, "alignment");
+
+// Exclusive prefix over `words*4` byte counters (in memory order) -> uint16 offsets.  Every
+// thread takes `words_per_thread` consecutive words.  Ends with a barrier.
+template <int WPT>
+__device__ __forceinline__ void scan_byte_counts(const uint32_t* __restrict__ cnt, int words, uint16_t* __restrict__ off,
+                                                 uint32_t* warp_tot) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    uint32_t w[WPT];
+    uint32_t local = 0;
+#pragma unroll
+    for (int i = 0; i < WPT; ++i) {
+        const int idx = tid * WPT + i;
+        w[i] = idx < words ? cnt[idx] : 0u;
+        local += (w[i] & 0xffu) + ((w[i] >> 8) & 0xffu) + ((w[i] >> 16) & 0xffu) + (w[i] >> 24);
+    }
+    uint32_t incl = local;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const uint32_t up = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += up;
+    }
+    if (lane == 31) warp_tot[warp] = incl;
+    __syncthreads();
+    uint32_t base = incl - local;
+    for (int k = 0; k < warp; ++k) base += warp_tot[k];
+#pragma unroll
+    for (int i = 0; i < WPT; ++i) {
+        const int idx = tid * WPT + i;
+        if (idx < words) {
+            uint32_t run = base;
+            ushort4 o;
+            o.x = (uint16_t)run; run += w[i] & 0xffu;
+            o.y = (uint16_t)run; run += (w[i] >> 8) & 0xffu;
+            o.z = (uint16_t)run; run += (w[i] >> 16) & 0xffu;
+            o.w = (uint16_t)run; run += w[i] >> 24;
+            *reinterpret_cast<ushort4*>(off + 4 * idx) = o;
+            base = run;
+        }
+    }
+    __syncthreads();
+}
+
+// boards: [m,5] int16.  Any of tabs / scores / order may be null.
 //   tabs   : [m, kTabBytes] table blobs used by the showdown evaluation
-//   scores : [m,1326] int32 packed strength of every combo (combos that overlap the board
-//            are scored with repeated card ids, as p2/env/rules_triton.py:139-146 does)
+//   scores : [m,1326] int32 packed strength of every combo
 //   order  : [m,1326] int64 stable ascending argsort of scores
-__global__ void __launch_bounds__(kSetupThreads) board_setup_kernel(const int16_t* __restrict__ boards, int64_t m,
-                                                                    const ComboTable* __restrict__ combos,
-                                                                    unsigned char* __restrict__ tabs,
-                                                                    int32_t* __restrict__ scores,
-                                                                    long long* __restrict__ order) {
-    __shared__ unsigned long long keys[kSortN];
-    __shared__ uint16_t pos[P2B_NUM_HANDS];   // sorted position of combo h
-    __shared__ uint16_t lgrp[kSortN];         // tie-group start per sorted position
-    __shared__ uint16_t rgrp[kSortN];         // tie-group end (exclusive) per sorted position
-    __shared__ uint16_t tmp16[kSortN];
-    __shared__ int bcard[5];
-    const int tid = threadIdx.x;
+__global__ void __launch_bounds__(kSetupThreads, 3) board_setup_kernel(const int16_t* __restrict__ boards, int64_t m,
+                                                                       const ComboTable* __restrict__ combos,
+                                                                       unsigned char* __restrict__ tabs,
+                                                                       int32_t* __restrict__ scores,
+                                                                       long long* __restrict__ order) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    uint32_t* key = reinterpret_cast<uint32_t*>(smem + kSuKey);
+    uint16_t* val = reinterpret_cast<uint16_t*>(smem + kSuVal);
+    uint32_t* cnt = reinterpret_cast<uint32_t*>(smem + kSuCnt);
+    unsigned char* cnt8 = smem + kSuCnt;
+    uint16_t* off = reinterpret_cast<uint16_t*>(smem + kSuOff);
+    uint16_t* lg = reinterpret_cast<uint16_t*>(smem + kSuLg);
+    uint16_t* rt = reinterpret_cast<uint16_t*>(smem + kSuRt);
+    uint16_t* lp = reinterpret_cast<uint16_t*>(smem + kSuLp);
+    unsigned char* blob = smem + kSuBlob;
+    uint32_t* warp_tot = reinterpret_cast<uint32_t*>(smem + kSuWarp);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t lt_mask = (1u << lane) - 1u;
     const int64_t b = blockIdx.x;
-    if (tid < 5) bcard[tid] = boards[b * 5 + tid];
-    __syncthreads();
 
-    // 1. strength of every combo
+    // ---- 1. strengths.  The board's share of the suit masks and rank counts is common ----
+    int bc[5];
+#pragma unroll
+    for (int i = 0; i < 5; ++i) bc[i] = boards[b * 5 + i];
+    uint64_t bsuits = 0;
+    RankChain bchain;
+#pragma unroll
+    for (int i = 0; i < 5; ++i) {
+        const int bit = card_bit(bc[i]);
+        bsuits |= 1ull << bit;
+        bchain.add(1u << (bit & 15));
+    }
     for (int h = tid; h < kSortN; h += kSetupThreads) {
+        uint32_t k = 0xffffffffu;
         if (h < P2B_NUM_HANDS) {
-            int c[7] = {combos->c1[h], combos->c2[h], bcard[0], bcard[1], bcard[2], bcard[3], bcard[4]};
-            const int32_t s = score_cards<7>(c);
+            const int b1 = card_bit(combos->c1[h]), b2 = card_bit(combos->c2[h]);
+            const uint64_t suits = bsuits | (1ull << b1) | (1ull << b2);
+            RankChain ch = bchain;
+            ch.add(1u << (b1 & 15));
+            ch.add(1u << (b2 & 15));
+            const uint32_t lo = (uint32_t)suits, hi = (uint32_t)(suits >> 32);
+            const int32_t s = score_from_masks(lo & 0x1fffu, (lo >> 16) & 0x1fffu, hi & 0x1fffu, (hi >> 16) & 0x1fffu,
+                                               ch.classes());
             if (scores) scores[b * P2B_NUM_HANDS + h] = s;
-            keys[h] = ((unsigned long long)(uint32_t)s << 11) | (unsigned long long)h;
-        } else {
-            keys[h] = ~0ull;
+            k = (uint32_t)s;
+        }
+        key[h] = k;
+        val[h] = (uint16_t)h;
+    }
+    for (int i = tid; i < kCntWords; i += kSetupThreads) cnt[i] = 0u;
+    __syncthreads();
+
+    // ---- 2. stable radix sort; buffers alternate, the result ends in buffer 0 ----
+#pragma unroll 1
+    for (int pass = 0; pass < kSortPasses; ++pass) {
+        const uint32_t* ksrc = key + (pass & 1) * kSortN;
+        const uint16_t* vsrc = val + (pass & 1) * kSortN;
+        uint32_t* kdst = key + ((pass & 1) ^ 1) * kSortN;
+        uint16_t* vdst = val + ((pass & 1) ^ 1) * kSortN;
+        const int shift = kDigitBits * pass;
+        uint32_t kk[kSortRounds];
+        uint16_t vv[kSortRounds];
+        int slot[kSortRounds], rnk[kSortRounds];
+#pragma unroll
+        for (int i = 0; i < kSortRounds; ++i) {
+            const int chunk = warp + kSetupWarps * i, p = 32 * chunk + lane;
+            kk[i] = ksrc[p];
+            vv[i] = vsrc[p];
+            const int d = (int)((kk[i] >> shift) & (kDigits - 1));
+            const uint32_t peers = __match_any_sync(0xffffffffu, d);
+            rnk[i] = __popc(peers & lt_mask);
+            slot[i] = d * kSortChunks + chunk;
+            if (rnk[i] == 0) cnt8[slot[i]] = (unsigned char)__popc(peers);
+        }
+        __syncthreads();
+        scan_byte_counts<2>(cnt, kDigits * kSortChunks / 4, off, warp_tot);
+#pragma unroll
+        for (int i = 0; i < kSortRounds; ++i) {
+            const int dest = off[slot[i]] + rnk[i];
+            kdst[dest] = kk[i];
+            vdst[dest] = vv[i];
+        }
+        for (int i = tid; i < kCntWords; i += kSetupThreads) cnt[i] = 0u;
+        __syncthreads();
+    }
+
+    // ---- 3. tie groups: lg[k] = first position of the run of equal strengths holding k ----
+    {
+        const int k0 = 4 * tid;
+        uint32_t kprev = k0 > 0 ? key[k0 - 1] : ~key[0];
+        int run[4];
+        int best = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t kc = key[k0 + i];
+            if (kc != kprev) best = k0 + i;
+            run[i] = best;
+            kprev = kc;
+        }
+        int incl = best;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl = max(incl, up);
+        }
+        if (lane == 31) warp_tot[warp] = (uint32_t)incl;
+        __syncthreads();
+        int base = __shfl_up_sync(0xffffffffu, incl, 1);
+        if (lane == 0) base = 0;
+        for (int w = 0; w < warp; ++w) base = max(base, (int)warp_tot[w]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) lg[k0 + i] = (uint16_t)max(run[i], base);
+        __syncthreads();
+        // the end of a group is the start of the next one; position 1326 (first pad) closes the last
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int k = k0 + i;
+            if (k > 0 && k <= P2B_NUM_HANDS && lg[k] == k) rt[lg[k - 1]] = (uint16_t)k;
         }
     }
     __syncthreads();
 
-    // 2. bitonic sort, ascending; the combo index in the low bits makes it stable
-    for (int k = 2; k <= kSortN; k <<= 1) {
-        for (int j = k >> 1; j > 0; j >>= 1) {
-            const int i = ((tid & ~(j - 1)) << 1) | (tid & (j - 1));  // lower index of the pair
-            const int p = i | j;
-            const unsigned long long a = keys[i], c = keys[p];
-            const bool up = (i & k) == 0;
-            if ((a > c) == up) {
-                keys[i] = c;
-                keys[p] = a;
-            }
-            __syncthreads();
+    // ---- 4. per-card lists: incidence i = (sorted position i/2, lower or upper card) ----
+#pragma unroll 1
+    for (int r = 0; r < kIncRounds; ++r) {
+        const int chunk = warp + kSetupWarps * r;
+        if (chunk >= kIncChunks) break;  // uniform per warp
+        const int i = 32 * chunk + lane;
+        int card = 63;
+        if (i < kIncidences) {
+            const int h = val[i >> 1];
+            card = (i & 1) ? combos->c2[h] : combos->c1[h];
         }
-    }
-
-    // 3. positions and tie groups
-    for (int k = tid; k < kSortN; k += kSetupThreads) {
-        if (k < P2B_NUM_HANDS) {
-            const int h = (int)(keys[k] & 2047ull);
-            pos[h] = (uint16_t)k;
-            if (order) order[b * P2B_NUM_HANDS + k] = h;
-            const bool start = (k == 0) || ((keys[k] >> 11) != (keys[k - 1] >> 11));
-            const bool last = (k == P2B_NUM_HANDS - 1) || ((keys[k] >> 11) != (keys[k + 1] >> 11));
-            lgrp[k] = start ? (uint16_t)k : 0;            // max-scan from the left
-            rgrp[k] = last ? (uint16_t)(k + 1) : 0xFFFF;  // min-scan from the right
-        } else {
-            lgrp[k] = 0;
-            rgrp[k] = 0xFFFF;
-        }
+        const uint32_t peers = __match_any_sync(0xffffffffu, card);
+        if (card < 52 && __popc(peers & lt_mask) == 0) cnt8[card * kIncChunks + chunk] = (unsigned char)__popc(peers);
     }
     __syncthreads();
-    for (int d = 1; d < kSortN; d <<= 1) {
-        for (int k = tid; k < kSortN; k += kSetupThreads) tmp16[k] = (k >= d) ? max(lgrp[k], lgrp[k - d]) : lgrp[k];
-        __syncthreads();
-        for (int k = tid; k < kSortN; k += kSetupThreads) lgrp[k] = tmp16[k];
-        __syncthreads();
-        for (int k = tid; k < kSortN; k += kSetupThreads) tmp16[k] = (k + d < kSortN) ? min(rgrp[k], rgrp[k + d]) : rgrp[k];
-        __syncthreads();
-        for (int k = tid; k < kSortN; k += kSetupThreads) rgrp[k] = tmp16[k];
-        __syncthreads();
+    scan_byte_counts<4>(cnt, kCntWords, off, warp_tot);
+    BoardTabView tv = view_tables(blob);
+    uint16_t* sorted_s = const_cast<uint16_t*>(tv.sorted);
+    uint16_t* cardlist_s = const_cast<uint16_t*>(tv.cardlist);
+    HandRec* rec_s = const_cast<HandRec*>(tv.rec);
+#pragma unroll 1
+    for (int r = 0; r < kIncRounds; ++r) {
+        const int chunk = warp + kSetupWarps * r;
+        if (chunk >= kIncChunks) break;
+        const int i = 32 * chunk + lane;
+        int card = 63, h = 0;
+        if (i < kIncidences) {
+            h = val[i >> 1];
+            card = (i & 1) ? combos->c2[h] : combos->c1[h];
+        }
+        const uint32_t peers = __match_any_sync(0xffffffffu, card);
+        if (card < 52) {
+            // every card has 51 incidences, so its list starts at 51*card in the card-major scan
+            const int t = off[card * kIncChunks + chunk] - 51 * card + __popc(peers & lt_mask);
+            cardlist_s[t * 52 + card] = (uint16_t)h;
+            lp[card * 52 + t] = (uint16_t)(i >> 1);
+        }
     }
-    if (!tabs) return;
-
-    unsigned char* blob = tabs + b * (int64_t)kTabBytes;
-    HandRec* rec = reinterpret_cast<HandRec*>(blob + kTabHeaderBytes);
-    uint16_t* sorted = reinterpret_cast<uint16_t*>(blob + kTabHeaderBytes + kTabRecBytes);
-    uint16_t* cardlist = reinterpret_cast<uint16_t*>(blob + kTabHeaderBytes + kTabRecBytes + kTabSortedBytes);
+    if (tid < (kTabCardListBytes - 51 * 52 * 2) / 2) cardlist_s[51 * 52 + tid] = 0;
+    for (int k = tid; k < kTabSortedPad; k += kSetupThreads) {
+        const uint16_t h = k < P2B_NUM_HANDS ? val[k] : (uint16_t)0;
+        sorted_s[k] = h;
+        if (order && k < P2B_NUM_HANDS) order[b * P2B_NUM_HANDS + k] = h;
+    }
     if (tid == 0) {
         unsigned long long mask = 0;
-        for (int i = 0; i < 5; ++i) mask |= 1ull << bcard[i];
+        for (int i = 0; i < 5; ++i) mask |= 1ull << bc[i];
         reinterpret_cast<unsigned long long*>(blob)[0] = mask;
         reinterpret_cast<unsigned long long*>(blob)[1] = 0ull;
     }
-    for (int k = tid; k < kTabSortedPad; k += kSetupThreads) sorted[k] = k < P2B_NUM_HANDS ? (uint16_t)(keys[k] & 2047ull) : 0;
+    __syncthreads();
 
-    // 4. per-card lists in strength order, 5. per-hand counts before L and before R.
-    // Task (c, i): the i-th other card d of card c names the hand g = {c,d}.
-    for (int task = tid; task < P2B_NUM_CARDS * 51; task += kSetupThreads) {
-        const int c = task / 51, i = task % 51;
-        const int d = i < c ? i : i + 1;
-        const int g = c < d ? combo_index(c, d) : combo_index(d, c);
-        const int pg = pos[g];
-        const int L = lgrp[pg], R = rgrp[pg];
-        int before = 0, nb = 0, ne = 0;
-        for (int j = 0; j < 51; ++j) {
-            const int e = j < c ? j : j + 1;
-            const int q = pos[c < e ? combo_index(c, e) : combo_index(e, c)];
-            before += q < pg;
-            nb += q < L;
-            ne += q < R;
-        }
-        cardlist[before * 52 + c] = (uint16_t)g;
-        HandRec* r = rec + g;
-        if (c < d) {  // c is the hand's lower card
-            r->lpos = (uint16_t)L;
-            r->rpos = (uint16_t)R;
-            r->nb0 = (uint8_t)nb;
-            r->ne0 = (uint8_t)ne;
+    // ---- 5. list entries before the tie group and before its end, per hand and card ----
+    for (int idx = tid; idx < 52 * 51; idx += kSetupThreads) {
+        const int card = idx / 51, t = idx - 51 * card;
+        const uint16_t* list = lp + card * 52;
+        const int k = list[t];
+        const int L = lg[k], R = rt[L];
+        int nb = t, ne = t + 1;
+        while (nb > 0 && list[nb - 1] >= L) --nb;
+        while (ne < 51 && list[ne] < R) ++ne;
+        const int h = val[k];
+        HandRec* rr = rec_s + h;
+        if (card == combos->c1[h]) {  // the hand's lower card
+            rr->lpos = (uint16_t)L;
+            rr->rpos = (uint16_t)R;
+            rr->nb0 = (uint8_t)nb;
+            rr->ne0 = (uint8_t)ne;
         } else {
-            r->nb1 = (uint8_t)nb;
-            r->ne1 = (uint8_t)ne;
+            rr->nb1 = (uint8_t)nb;
+            rr->ne1 = (uint8_t)ne;
         }
     }
-    if (tid < (kTabCardListBytes - 51 * 52 * 2) / 2) cardlist[51 * 52 + tid] = 0;
+    __syncthreads();
+    if (tabs) {
+        uint4* dst = reinterpret_cast<uint4*>(tabs + b * (int64_t)kTabBytes);
+        const uint4* src = reinterpret_cast<const uint4*>(blob);
+        for (int i = tid; i < kTabBytes / 16; i += kSetupThreads) dst[i] = src[i];
+    }
 }
 
-constexpr int kEvalThreads = 384;
-constexpr int kEvalSmem = kTabBytes + 2 * P2B_HPAD * 4 /*x*/ + 2 * P2B_HPAD * 4 /*P*/ + 2 * 52 * 52 * 4 /*PC*/ + 32 * 8;
+// ---------------------------------------------------------------------------------------
+// Stand-alone showdown evaluation.  One block (448 threads) per showdown row at a time.
+// beliefs: [rows,2,1326] fp32 (row stride given in floats so that padded layouts work);
+// values: same shape.  tab_of_row: which table blob a row uses (null = row index).
+// potential: [rows,2] int64 chips won by each player at showdown, scale: [rows] fp32;
+// value = EV * potential / scale (cfr_evaluator.py:597-601).
+//
+// Per row: (A) the 2 x 52 per-card prefix lists, four threads per list, and the totals of
+// the four quarters of both strength-order scans; (B) the eight quarter scans, one warp
+// each; (C) the per-hand formula.  All sums are fp64, rounded to fp32 per element.
+// ---------------------------------------------------------------------------------------
+constexpr int kEvalThreads = 448;
+constexpr int kEvalWarps = kEvalThreads / 32;
+constexpr int kQuarter = 352;  // sorted positions per quarter scan: 32 lanes x 11
+constexpr int kEvX = kTabBytes;                         // float [2*1326 (+pad)]
+constexpr int kEvP = kEvX + 2 * P2B_HPAD * 4;           // float [2][HPAD]
+constexpr int kEvPC = kEvP + 2 * P2B_HPAD * 4;          // float [2][52*52]
+constexpr int kEvQ = kEvPC + 2 * 52 * 52 * 4;           // double [8]
+constexpr int kEvCombo = kEvQ + 64;                     // uint8 [2][1326 (+pad)]
+constexpr int kEvalSmem = kEvCombo + 2 * 1328;
+static_assert(kEvQ % 8 == 0, "alignment");
 
-// One block per showdown row.  beliefs: [rows,2,1326] fp32 (row stride given in floats so
-// that padded layouts work); values: same shape.  tab_of_row: which table blob a row uses
-// (null = row index).  potential: [rows,2] int64 chips won by each player at showdown,
-// scale: [rows] fp32; value = EV * potential / scale (cfr_evaluator.py:597-601).
-__global__ void __launch_bounds__(kEvalThreads) showdown_eval_kernel(
+__global__ void __launch_bounds__(kEvalThreads, 3) showdown_eval_kernel(
     const unsigned char* __restrict__ tabs, const int32_t* __restrict__ tab_of_row, const ComboTable* __restrict__ combos,
     const float* __restrict__ beliefs, int64_t belief_row_stride, const long long* __restrict__ potential,
     const float* __restrict__ scale, float* __restrict__ values, int64_t value_row_stride, int64_t rows) {
     extern __shared__ __align__(16) unsigned char smem[];
     unsigned char* tab_s = smem;
-    float* x = reinterpret_cast<float*>(smem + kTabBytes);  // [2][HPAD]: x[p] = range of player p
-    float* P = x + 2 * P2B_HPAD;                            // [2][HPAD]: prefix of the range of player p
-    float* PC = P + 2 * P2B_HPAD;                           // [2][52*52]
-    double* warp_tot = reinterpret_cast<double*>(PC + 2 * 52 * 52);
-    const int tid = threadIdx.x;
+    float* x = reinterpret_cast<float*>(smem + kEvX);   // x[p*1326 + h] = range of player p
+    float* P = reinterpret_cast<float*>(smem + kEvP);   // P[p*HPAD + k] = prefix of player p's range, strength order
+    float* PC = reinterpret_cast<float*>(smem + kEvPC);
+    double* qtot = reinterpret_cast<double*>(smem + kEvQ);
+    uint8_t* c1s = smem + kEvCombo;
+    uint8_t* c2s = c1s + 1328;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int h = tid; h < P2B_NUM_HANDS; h += kEvalThreads) {
+        c1s[h] = combos->c1[h];
+        c2s[h] = combos->c2[h];
+    }
+    const bool vec_in = ((reinterpret_cast<uintptr_t>(beliefs) | (uintptr_t)(belief_row_stride * 4)) & 15) == 0;
 
     for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
         const int64_t t = tab_of_row ? tab_of_row[row] : row;
         const uint4* src = reinterpret_cast<const uint4*>(tabs + t * (int64_t)kTabBytes);
         for (int i = tid; i < kTabBytes / 16; i += kEvalThreads) reinterpret_cast<uint4*>(tab_s)[i] = src[i];
         const float* brow = beliefs + row * belief_row_stride;
-        for (int i = tid; i < 2 * P2B_NUM_HANDS; i += kEvalThreads) {
-            const int p = i >= P2B_NUM_HANDS;
-            x[p * P2B_HPAD + (i - p * P2B_NUM_HANDS)] = __ldcs(brow + i);
+        if (vec_in) {
+            const float4* b4 = reinterpret_cast<const float4*>(brow);
+            for (int i = tid; i < 2 * P2B_NUM_HANDS / 4; i += kEvalThreads) reinterpret_cast<float4*>(x)[i] = __ldcs(b4 + i);
+        } else {
+            for (int i = tid; i < 2 * P2B_NUM_HANDS; i += kEvalThreads) x[i] = __ldcs(brow + i);
         }
         __syncthreads();
         const BoardTabView tv = view_tables(tab_s);
 
-        // per-card prefix sums: thread (p,c) walks card c's list in strength order
-        if (tid < 2 * 52) {
-            const int p = tid / 52, c = tid % 52;
-            const float* xp = x + p * P2B_HPAD;
-            float* pc = PC + p * 52 * 52 + c * 52;
-            double acc = 0.0;
-            pc[0] = 0.0f;
-#pragma unroll 3
-            for (int k = 0; k < 51; ++k) {
-                acc += (double)xp[tv.cardlist[k * 52 + c]];
-                pc[k + 1] = (float)acc;
+        // ---- A. per-card prefix lists (threads 0..415: player, card, quarter of the list) ----
+        {
+            const bool valid = tid < 2 * 52 * 4;
+            const int p = tid / 208, rem = tid % 208, c = rem >> 2, q = rem & 3;
+            const float* xp = x + (valid ? p : 0) * P2B_NUM_HANDS;
+            float v[13];
+#pragma unroll
+            for (int i = 0; i < 13; ++i) {
+                const int e = 13 * q + i;
+                v[i] = (valid && e < 51) ? xp[tv.cardlist[e * 52 + c]] : 0.0f;
+            }
+            double t_even = 0.0, t_odd = 0.0;
+#pragma unroll
+            for (int i = 0; i < 13; ++i) {
+                if (i & 1) t_odd += (double)v[i];
+                else t_even += (double)v[i];
+            }
+            const double tot = t_even + t_odd;
+            const int g = lane & ~3;
+            const double t0 = __shfl_sync(0xffffffffu, tot, g), t1 = __shfl_sync(0xffffffffu, tot, g + 1);
+            const double t2 = __shfl_sync(0xffffffffu, tot, g + 2);
+            if (valid) {
+                double acc = q == 0 ? 0.0 : (q == 1 ? t0 : (q == 2 ? t0 + t1 : (t0 + t1) + t2));
+                float* out = PC + p * 52 * 52 + c * 52;
+                if (q == 0) out[0] = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 13; ++i)
+                    if (13 * q + i < 51) {
+                        acc += (double)v[i];
+                        out[13 * q + i + 1] = (float)acc;
+                    }
             }
         }
-        // strength-order prefix sums of both ranges
-        for (int p = 0; p < 2; ++p) {
-            const float* xp = x + p * P2B_HPAD;
-            block_prefix_f64([&](int k) { return xp[tv.sorted[k]]; }, P2B_NUM_HANDS, P + p * P2B_HPAD, warp_tot);
+        // quarter totals of the strength-order scans: task = player*4 + quarter, last warps first
+        for (int wt = kEvalWarps - 1 - warp; wt < 8; wt += kEvalWarps) {
+            const int p = wt >> 2, k0 = (wt & 3) * kQuarter + 11 * lane;
+            const float* xp = x + p * P2B_NUM_HANDS;
+            float v[11];
+#pragma unroll
+            for (int i = 0; i < 11; ++i) v[i] = (k0 + i < P2B_NUM_HANDS) ? xp[tv.sorted[k0 + i]] : 0.0f;
+            double a = 0.0;
+#pragma unroll
+            for (int i = 0; i < 11; ++i) a += (double)v[i];
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) a += __shfl_xor_sync(0xffffffffu, a, d);
+            if (lane == 0) qtot[wt] = a;
         }
+        __syncthreads();
+
+        // ---- B. the eight quarter scans ----
+        for (int wt = warp; wt < 8; wt += kEvalWarps) {
+            const int p = wt >> 2, qi = wt & 3, k0 = qi * kQuarter + 11 * lane;
+            const float* xp = x + p * P2B_NUM_HANDS;
+            float* pref = P + p * P2B_HPAD;
+            double start = 0.0;
+            for (int r = 0; r < qi; ++r) start += qtot[p * 4 + r];
+            float v[11];
+#pragma unroll
+            for (int i = 0; i < 11; ++i) v[i] = (k0 + i < P2B_NUM_HANDS) ? xp[tv.sorted[k0 + i]] : 0.0f;
+            double local = 0.0;
+#pragma unroll
+            for (int i = 0; i < 11; ++i) local += (double)v[i];
+            double incl = local;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const double up = __shfl_up_sync(0xffffffffu, incl, d);
+                if (lane >= d) incl += up;
+            }
+            double run = start + (incl - local);
+            if (wt == p * 4 && lane == 0) pref[0] = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 11; ++i) {
+                run += (double)v[i];
+                if (k0 + i < P2B_NUM_HANDS) pref[k0 + i + 1] = (float)run;
+            }
+        }
+        __syncthreads();
+
+        // ---- C. per-hand formula ----
         const unsigned long long bmask = *tv.board_mask;
         float* vrow = values + row * value_row_stride;
+        const float pot0 = (float)potential[row * 2], pot1 = (float)potential[row * 2 + 1];
+        const Divisor dscale = make_divisor(scale[row]);
         for (int i = tid; i < 2 * P2B_NUM_HANDS; i += kEvalThreads) {
             const int hero = i >= P2B_NUM_HANDS, h = i - hero * P2B_NUM_HANDS, opp = 1 - hero;
-            const int c1 = combos->c1[h], c2 = combos->c2[h];
+            const int c1 = c1s[h], c2 = c2s[h];
             const bool allowed = (((bmask >> c1) | (bmask >> c2)) & 1ull) == 0;
-            const float ev = showdown_hand_ev(tv.rec[h], c1, c2, x[opp * P2B_HPAD + h], allowed, P + opp * P2B_HPAD,
+            const float ev = showdown_hand_ev(tv.rec[h], c1, c2, x[opp * P2B_NUM_HANDS + h], allowed, P + opp * P2B_HPAD,
                                               PC + opp * 52 * 52);
-            const float pot = (float)potential[row * 2 + hero];
-            __stcs(vrow + i, __fdiv_rn(__fmul_rn(ev, pot), scale[row]));
+            __stcs(vrow + i, div_exact(__fmul_rn(ev, hero ? pot1 : pot0), dscale));
         }
         __syncthreads();
     }
@@ -199,7 +451,11 @@ int launch_board_setup(const int16_t* boards, int64_t m, unsigned char* tabs, in
     if (m == 0) return P2B_OK;
     int rc = ensure_tables();
     if (rc) return rc;
-    board_setup_kernel<<<(unsigned)m, kSetupThreads, 0, stream>>>(boards, m, device_combo_table(), tabs, scores, order);
+    rc = check_cuda(cudaFuncSetAttribute(board_setup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSetupSmem),
+                    "board_setup_kernel smem attribute");
+    if (rc) return rc;
+    board_setup_kernel<<<(unsigned)m, kSetupThreads, kSetupSmem, stream>>>(boards, m, device_combo_table(), tabs, scores,
+                                                                         order);
     return check_cuda(cudaGetLastError(), "board_setup_kernel");
 }
 

@@ -52,44 +52,6 @@ __host__ __device__ __forceinline__ BoardTabView view_tables(const unsigned char
     return v;
 }
 
-// Inclusive block-wide prefix sum in fp64 over `n` values fetched by `fetch(k)`, four
-// consecutive positions per thread; writes fl32(prefix through k) to out[k+1] and 0 to
-// out[0].  `warp_tot` is shared scratch of at least blockDim.x/32 doubles.  All threads of
-// the block must call it; it ends with a barrier.
-template <typename Fetch>
-__device__ __forceinline__ void block_prefix_f64(Fetch fetch, int n, float* __restrict__ out, double* warp_tot) {
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
-    for (int base = 0; base < n; base += 4 * blockDim.x) {
-        const int k0 = base + 4 * tid;
-        double v[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) v[i] = (k0 + i < n) ? (double)fetch(k0 + i) : 0.0;
-        v[1] += v[0];
-        v[2] += v[1];
-        v[3] += v[2];
-        double incl = v[3];
-#pragma unroll
-        for (int d = 1; d < 32; d <<= 1) {
-            const double up = __shfl_up_sync(0xffffffffu, incl, d);
-            if (lane >= d) incl += up;
-        }
-        // carry of earlier chunks lives in warp_tot[nwarps]
-        if (lane == 31) warp_tot[warp] = incl;
-        __syncthreads();
-        double offset = (base == 0) ? 0.0 : warp_tot[nwarps];
-        for (int w = 0; w < warp; ++w) offset += warp_tot[w];
-        const double excl = offset + (incl - v[3]);
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-            if (k0 + i < n) out[k0 + i + 1] = (float)(excl + v[i]);
-        __syncthreads();
-        if (tid == blockDim.x - 1) warp_tot[nwarps] = excl + v[3];
-        __syncthreads();
-    }
-    if (tid == 0) out[0] = 0.0f;
-    __syncthreads();
-}
-
 // One hero hand of the showdown formula.  P: [1327] prefix in strength order; PC: [52][52]
 // per-card prefix (PC[c*52+t] = mass of the t weakest hands holding c); x: opponent range.
 __device__ __forceinline__ float showdown_hand_ev(const HandRec r, int c1, int c2, float xh, bool allowed,

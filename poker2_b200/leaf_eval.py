@@ -25,15 +25,21 @@ class ValueMLP(torch.nn.Module):
     1326-combo ranges + 52-d board one-hot + 3 pot/stack scalars, `depth` hidden layers of
     `width` GELU units, output = 2 x 1326 hand values.  Random initialisation."""
 
+    IN_FEATURES = 2 * NUM_HANDS + 52 + 3  # 2707
+    IN_PADDED = 2720  # GEMM operands want rows that are multiples of 16 bytes; the extra columns are zero
+    OUT_PADDED = 2656
+
     def __init__(self, width: int = 1536, depth: int = 4, *, dtype=torch.bfloat16, seed: int = 0):
         super().__init__()
         g = torch.Generator().manual_seed(seed)
-        dims = [2 * NUM_HANDS + 52 + 3] + [width] * depth + [2 * NUM_HANDS]
+        dims = [self.IN_FEATURES] + [width] * depth + [2 * NUM_HANDS]
+        padded = [self.IN_PADDED] + [width] * depth + [self.OUT_PADDED]
         layers = []
         for i in range(len(dims) - 1):
-            lin = torch.nn.Linear(dims[i], dims[i + 1])
+            lin = torch.nn.Linear(padded[i], padded[i + 1])
             with torch.no_grad():
-                lin.weight.copy_(torch.randn(dims[i + 1], dims[i], generator=g) / dims[i] ** 0.5)
+                lin.weight.zero_()
+                lin.weight[: dims[i + 1], : dims[i]] = torch.randn(dims[i + 1], dims[i], generator=g) / dims[i] ** 0.5
                 lin.bias.zero_()
             layers.append(lin)
             if i < len(dims) - 2:
@@ -46,13 +52,14 @@ class ValueMLP(torch.nn.Module):
         """beliefs [S,2,1326] fp32, boards [S,L] int64 (-1 = empty), context [S,3] fp32
         -> values [S,2,1326] fp32."""
         S = beliefs.shape[0]
-        x = torch.empty(S, 2 * NUM_HANDS + 55, device=beliefs.device, dtype=self.dtype)
+        x = torch.zeros(S, self.IN_PADDED, device=beliefs.device, dtype=self.dtype)
         x[:, : 2 * NUM_HANDS] = beliefs.reshape(S, 2 * NUM_HANDS)
         onehot = torch.zeros(S, 53, device=beliefs.device, dtype=self.dtype)
         onehot.scatter_(1, torch.where(boards >= 0, boards, torch.full_like(boards, 52)), 1.0)
         x[:, 2 * NUM_HANDS: 2 * NUM_HANDS + 52] = onehot[:, :52]
-        x[:, 2 * NUM_HANDS + 52:] = context
-        return self.net(x).to(torch.float32).view(S, 2, NUM_HANDS)
+        x[:, 2 * NUM_HANDS + 52: self.IN_FEATURES] = context
+        y = self.net(x)[:, : 2 * NUM_HANDS]
+        return y.to(torch.float32).view(S, 2, NUM_HANDS)
 
 
 def leaf_context(trees, node_index) -> torch.Tensor:
