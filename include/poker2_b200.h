@@ -83,13 +83,21 @@ int p2b_showdown_values(const unsigned char* tables, const int32_t* table_of_row
  *  init_depth depth of the deepest tree of the batch (the upstream start pass re-normalises
  *             every belief row once per level of the batch-wide tree)
  *  work_counter one int32 (zeroed by the call)
- *  num_blocks 0 = one block per SM. */
+ *  num_blocks 0 = one block per SM
+ *  sample_pass [num_subgames] int32 (may be NULL), policy_sample [rows,1344] out (may be NULL):
+ *             the current policy of pass sample_pass[s] is kept for subgame s -- the
+ *             policy_probs_sample snapshot of cfr_evaluator.py:1336-1341 (taken at the start of
+ *             iteration t_sample, i.e. the policy of pass t_sample-1); rows of subgames whose
+ *             sample_pass is outside 0..iterations-1 are left untouched
+ *  beliefs_last [rows,2,1344] out (may be NULL): beliefs of the last iteration at the internal
+ *             nodes (what sample_leaves returns for the sampled nodes). */
 int p2b_cfr_solve(const void* subgames, const void* nodes, int32_t num_subgames, int32_t max_children,
                   int32_t max_internal, const unsigned char* tables, const float* root_beliefs,
                   float* regrets, float* weight_sums, float* policy_avg, float* policy,
                   float* root_values, float* values_avg, float* beliefs_avg, float* exploitability,
                   float* br_values, float* scratch, int64_t scratch_floats, const void* scalars, int32_t iterations, int32_t cfr_plus,
-                  int32_t init_depth, int32_t* work_counter, int32_t num_blocks, void* stream);
+                  int32_t init_depth, int32_t* work_counter, int32_t num_blocks, const int32_t* sample_pass,
+                  float* policy_sample, float* beliefs_last, void* stream);
 int64_t p2b_cfr_scratch_floats(int32_t max_internal, int32_t num_blocks);
 int p2b_cfr_default_blocks(void);
 
@@ -119,7 +127,8 @@ int p2b_cfr_step(const void* subgames, const void* nodes, int32_t num_subgames, 
                  int32_t iterations, int32_t cfr_plus, int32_t init_depth, int32_t* work_counter,
                  int32_t num_blocks, int32_t pass_begin, int32_t pass_end, int32_t phases,
                  float* carry_sums, float* carry_roots, const int32_t* leaf_begin, float* leaf_beliefs,
-                 const float* leaf_values, void* stream);
+                 const float* leaf_values, const int32_t* sample_pass, float* policy_sample,
+                 float* beliefs_last, void* stream);
 
 /* p2b_cfr_solve_noalloc -- the same solve without any allocation.  (No counterpart in the
  * upstream project: it exists for hosts of this library that cannot allocate.)

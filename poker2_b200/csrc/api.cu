@@ -78,8 +78,12 @@ int p2b_cfr_solve(const void* subgames, const void* nodes, int32_t num_subgames,
                   float* weight_sums, float* policy_avg, float* policy, float* root_values, float* values_avg,
                   float* beliefs_avg, float* exploitability, float* br_values, float* scratch, int64_t scratch_floats,
                   const void* scalars, int32_t iterations, int32_t cfr_plus, int32_t init_depth, int32_t* work_counter,
-                  int32_t num_blocks, void* stream) {
+                  int32_t num_blocks, const int32_t* sample_pass, float* policy_sample, float* beliefs_last,
+                  void* stream) {
     P2B_REQUIRE(num_subgames >= 0 && iterations >= 0, "negative count");
+    P2B_REQUIRE(!policy_sample || sample_pass, "policy_sample needs sample_pass");
+    P2B_REQUIRE(((reinterpret_cast<uintptr_t>(policy_sample) | reinterpret_cast<uintptr_t>(beliefs_last)) & 15) == 0,
+                "all arrays must be 16-byte aligned");
     if (num_subgames == 0) return P2B_OK;
     P2B_REQUIRE(subgames && nodes && root_beliefs && regrets && policy_avg && root_values && scratch && work_counter,
                 "null pointer");
@@ -119,6 +123,9 @@ int p2b_cfr_solve(const void* subgames, const void* nodes, int32_t num_subgames,
     p.cfr_plus = cfr_plus;
     p.init_depth = init_depth;
     p.work_counter = work_counter;
+    p.sample_pass = sample_pass;
+    p.policy_sample = policy_sample;
+    p.beliefs_last = beliefs_last;
     return launch_cfr_solve(p, num_blocks, max_children, (cudaStream_t)stream);
 }
 
@@ -130,8 +137,11 @@ int p2b_cfr_step(const void* subgames, const void* nodes, int32_t num_subgames, 
                  const void* scalars, int32_t iterations, int32_t cfr_plus, int32_t init_depth, int32_t* work_counter,
                  int32_t num_blocks, int32_t pass_begin, int32_t pass_end, int32_t phases, float* carry_sums,
                  float* carry_roots, const int32_t* leaf_begin, float* leaf_beliefs, const float* leaf_values,
-                 void* stream) {
+                 const int32_t* sample_pass, float* policy_sample, float* beliefs_last, void* stream) {
     P2B_REQUIRE(num_subgames >= 0 && iterations >= 1, "bad count");
+    P2B_REQUIRE(!policy_sample || sample_pass, "policy_sample needs sample_pass");
+    P2B_REQUIRE(((reinterpret_cast<uintptr_t>(policy_sample) | reinterpret_cast<uintptr_t>(beliefs_last)) & 15) == 0,
+                "all row arrays must be 16-byte aligned");
     if (num_subgames == 0) return P2B_OK;
     P2B_REQUIRE(subgames && nodes && root_beliefs && regrets && policy_avg && root_values && scratch && work_counter &&
                     scalars && carry_sums && carry_roots,
@@ -187,6 +197,9 @@ int p2b_cfr_step(const void* subgames, const void* nodes, int32_t num_subgames, 
     p.leaf_begin = leaf_begin;
     p.leaf_beliefs = leaf_beliefs;
     p.leaf_values = leaf_values;
+    p.sample_pass = sample_pass;
+    p.policy_sample = policy_sample;
+    p.beliefs_last = beliefs_last;
     return launch_cfr_solve(p, num_blocks, max_children, (cudaStream_t)stream);
 }
 

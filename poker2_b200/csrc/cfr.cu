@@ -173,6 +173,7 @@ struct Block {
         return base + ((long long)(sg.node_begin + node) * 2 + pl) * P2B_HPAD;
     }
     __device__ __forceinline__ float* stage_row(int r) const { return xs + r * P2B_HPAD; }
+    int sample_pass;  // pass whose policy is the sampling policy of the current subgame (-2: none)
     int leaf0;  // first model-leaf slot of the current subgame
     __device__ __forceinline__ long long leaf_row(int leaf_rank, int pl) const {
         return ((long long)(leaf0 + leaf_rank) * 2 + pl) * P2B_HPAD;
@@ -564,6 +565,11 @@ __device__ __forceinline__ void sweep_down(int mode, int pass, const CfrParams& 
                 for (int c = 0; c < K; ++c)
                     stv<VPT>(B.row1(p.policy, fc + c), tid, P[c]);
             }
+            if (p.policy_sample && pass == B.sample_pass) {
+#pragma unroll
+                for (int c = 0; c < K; ++c)
+                    stv<VPT>(B.row1(p.policy_sample, fc + c), tid, P[c]);
+            }
         }
         // reach of the children under the policy of this pass, and the rows whose sums
         // normalise the children's beliefs (only the acting player's row is new: the other
@@ -730,6 +736,10 @@ __device__ __forceinline__ void sweep_up(int mode, int pass, const CfrParams& p,
         if (mode == kPassFinal && p.beliefs_avg) {
             stv<VPT>(B.row2(p.beliefs_avg, j, a), tid, b_a);
             stv<VPT>(B.row2(p.beliefs_avg, j, o), tid, b_o);
+        }
+        if (p.beliefs_last && mode == kPassIter && pass == p.iterations - 1) {
+            stv<VPT>(B.row2(p.beliefs_last, j, a), tid, b_a);
+            stv<VPT>(B.row2(p.beliefs_last, j, o), tid, b_o);
         }
         __syncthreads();
 
@@ -1051,6 +1061,7 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
         // work rows: one set per block, or one per subgame when state is carried between launches
         B.scr = p.scratch + (long long)(p.stepped ? s : (int)blockIdx.x) * p.scratch_stride;
         B.leaf0 = p.leaf_begin ? p.leaf_begin[s] : 0;
+        B.sample_pass = p.sample_pass ? p.sample_pass[s] : -2;
         {
             const uint4* src = reinterpret_cast<const uint4*>(p.nodes + B.sg.node_begin);
             for (int i = tid; i < B.sg.n_nodes; i += NT) reinterpret_cast<uint4*>(B.nodes)[i] = src[i];

@@ -88,6 +88,10 @@ struct CfrParams {
     const int32_t* leaf_begin;   // [B] first model-leaf slot of each subgame
     float* leaf_beliefs;         // [slots][2][HPAD] beliefs at the model leaves (out, top-down sweep)
     const float* leaf_values;    // [slots][2][HPAD] values at the model leaves (in, bottom-up sweep)
+    // ---- inputs of leaf sampling (p2/search/cfr_evaluator.py:1336-1341, sparse_cfr_evaluator.py:325-426)
+    const int32_t* sample_pass;  // [B] pass whose current policy is kept in policy_sample (may be null)
+    float* policy_sample;        // [rows][HPAD] (out, may be null)
+    float* beliefs_last;         // [rows][2][HPAD] beliefs of the last iteration at internal nodes (out, may be null)
 };
 
 // floats of scratch one block needs: per internal node reach[2], average reach[2], values[2]

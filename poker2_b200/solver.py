@@ -174,6 +174,8 @@ class SolveResult:
     beliefs_avg: torch.Tensor | None
     exploitability: torch.Tensor | None = None  # [B] local exploitability of the average policy
     br_values: torch.Tensor | None = None  # [B,2] best-response values at the roots
+    policy_sample: torch.Tensor | None = None  # [rows,1344] policy of each subgame's sampling iteration
+    beliefs_last: torch.Tensor | None = None  # [rows,2,1344] beliefs of the last iteration (internal nodes)
 
     def to_host(self, pinned: dict | None = None) -> dict:
         """Copies the training targets (root values, average policy) to pinned host memory
@@ -196,7 +198,7 @@ class SubgameSolver:
 
     def __init__(self, layout: DeviceTreeLayout, boards: torch.Tensor, device: torch.device, *,
                  track_weight_sums: bool = True, keep_policy: bool = False, keep_node_values: bool = False,
-                 exploitability: bool = False, num_blocks: int = 0):
+                 exploitability: bool = False, num_blocks: int = 0, sampling: bool = False):
         keep_node_values = keep_node_values or exploitability  # best responses read the node values
         if device.type != "cuda":
             raise ValueError("SubgameSolver requires a CUDA device.")
@@ -224,12 +226,29 @@ class SubgameSolver:
         n_scratch = int(_lib.lib().p2b_cfr_scratch_floats(layout.max_internal, self.num_blocks))
         self.scratch = torch.empty(n_scratch, **f32)
         self.work_counter = torch.zeros(4, device=device, dtype=torch.int32)
+        # leaf sampling: the policy of one scheduled iteration per subgame, beliefs of the last one
+        self.policy_sample = torch.zeros(rows, HPAD, **f32) if sampling else None
+        self.beliefs_last = torch.zeros(rows, 2, HPAD, **f32) if sampling else None
+        self.sample_pass = torch.full((B,), -2, device=device, dtype=torch.int32) if sampling else None
         self.launches = 0
+
+    def set_sampling_schedule(self, t_sample: torch.Tensor) -> None:
+        """t_sample [B]: iteration at whose start each subgame's current policy is kept
+        (`sampling.sampling_schedule`)."""
+        if self.sample_pass is None:
+            raise ValueError("the solver was built without sampling=True")
+        self.sample_pass.copy_((t_sample.to(torch.int64) - 1).to(torch.int32))
+        self.policy_sample.zero_()
+
+    def _result(self) -> "SolveResult":
+        return SolveResult(self.layout, self.policy_avg, self.regrets, self.weight_sums, self.policy,
+                           self.root_values, self.values_avg, self.beliefs_avg, self.exploitability, self.br_values,
+                           self.policy_sample, self.beliefs_last)
 
     def release(self) -> None:
         """Drops the device buffers (they return to the caching allocator)."""
         for name in ("regrets", "policy_avg", "weight_sums", "policy", "root_values", "values_avg", "beliefs_avg",
-                     "exploitability", "br_values", "scratch", "tables"):
+                     "exploitability", "br_values", "scratch", "tables", "policy_sample", "beliefs_last"):
             setattr(self, name, None)
 
     def solve(self, root_beliefs: torch.Tensor, scalars: np.ndarray, *, cfr_plus: bool = False) -> SolveResult:
@@ -248,11 +267,10 @@ class SubgameSolver:
                 p(self.values_avg), p(self.beliefs_avg), p(self.exploitability), p(self.br_values), p(self.scratch),
                 self.scratch.numel(),
                 p(sc) if iterations else None, iterations, int(cfr_plus), self.layout.tree_depth, p(self.work_counter),
-                self.num_blocks,
+                self.num_blocks, p(self.sample_pass), p(self.policy_sample), p(self.beliefs_last),
                 _lib.stream_ptr(self.device))
         self.launches += 1
-        return SolveResult(self.layout, self.policy_avg, self.regrets, self.weight_sums, self.policy,
-                           self.root_values, self.values_avg, self.beliefs_avg, self.exploitability, self.br_values)
+        return self._result()
 
 
 class SteppedSolver(SubgameSolver):
@@ -286,7 +304,8 @@ class SteppedSolver(SubgameSolver):
                 p(self.values_avg), p(self.beliefs_avg), p(self.exploitability), p(self.br_values), p(self.scratch),
                 self.scratch.numel(), p(sc), iterations, int(cfr_plus), self.layout.tree_depth, p(self.work_counter),
                 self.num_blocks, pass_begin, pass_end, phases, p(self.carry_sums), p(self.carry_roots),
-                p(self.leaf_begin), p(self.leaf_beliefs), p(self.leaf_values), _lib.stream_ptr(self.device))
+                p(self.leaf_begin), p(self.leaf_beliefs), p(self.leaf_values), p(self.sample_pass),
+                p(self.policy_sample), p(self.beliefs_last), _lib.stream_ptr(self.device))
         self.launches += 1
 
     def solve(self, root_beliefs: torch.Tensor, scalars: np.ndarray, leaf_fn=None, *,
@@ -309,9 +328,11 @@ class SteppedSolver(SubgameSolver):
                 self.leaf_values[:n_leaves, :, :NUM_HANDS].copy_(vals)
             else:
                 self.leaf_values[:n_leaves].copy_(vals)
+            if self.beliefs_last is not None and pas == iterations - 1:
+                # beliefs of the last iteration at the model leaves (the states sampling continues from)
+                self.beliefs_last[torch.from_numpy(self.layout.model_rows).to(self.device)] = self.leaf_beliefs[:n_leaves]
             self._step(root_beliefs, sc, iterations, cfr_plus, pas, pas, 2)
-        return SolveResult(self.layout, self.policy_avg, self.regrets, self.weight_sums, self.policy,
-                           self.root_values, self.values_avg, self.beliefs_avg, self.exploitability, self.br_values)
+        return self._result()
 
 
 def solve_noalloc(sv: SubgameSolver, root_beliefs: torch.Tensor, scalars_dev: torch.Tensor, *,

@@ -279,8 +279,14 @@ def gen_turn() -> None:
     ev = make_evaluator(n, iterations, depth=depth)
     ev.model = PotEchoModel(len(BET_BINS) + 3)
     ev.initialize_subgame(turn_env(boards, pot, stack), torch.arange(n), ranges)
+    ev.generator = torch.Generator().manual_seed(123)  # consumed by the sampling schedule only
     ev.evaluate_cfr()
     ex = ev._compute_exploitability()
+    # leaf sampling (sparse_cfr_evaluator.py:325-426) with a freshly seeded generator
+    ev.generator = torch.Generator().manual_seed(321)
+    pbs = SparseCFREvaluator.sample_leaves(ev, True)
+    ev.generator = torch.Generator().manual_seed(99)
+    schedule = ev._get_sampling_schedule()[:n]
     install_raise_cap(None)
     model_mask = ev.leaf_mask & ~ev.env.done
     print("turn nodes", ev.total_nodes, "model leaves", int(model_mask.sum()), "showdown", int((ev.env.street == 4).sum()),
@@ -292,6 +298,10 @@ def gen_turn() -> None:
          policy_avg=ev.policy_probs_avg.numpy(), root_values=ev.values_avg[:n].numpy(),
          regrets=ev.cumulative_regrets.numpy(), leaf_mask=ev.leaf_mask.numpy(),
          parent_index=ev.parent_index.numpy(), street=ev.env.street.numpy(),
+         t_sample=ev.t_sample[:n].numpy(), policy_sample=ev.policy_probs_sample.numpy(),
+         beliefs_last=ev.beliefs.numpy(), sample_epsilon=np.float64(ev.sample_epsilon),
+         sampled_beliefs=pbs.beliefs.numpy(), sampled_pot=pbs.env.pot.numpy(),
+         sampled_stacks=pbs.env.stacks.numpy(), schedule_seed99=schedule.numpy(),
          exploitability=ex.local_exploitability.numpy(), br_values=ex.local_best_response_values.numpy())
 
 

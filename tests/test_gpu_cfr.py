@@ -129,3 +129,31 @@ def test_stepped_solve_equals_one_launch_solve(cuda_device, golden_dir, name):
     for a, b in [(res.regrets, res2.regrets), (res.policy_avg, res2.policy_avg), (res.root_values, res2.root_values),
                  (res.weight_sums, res2.weight_sums), (res.exploitability, res2.exploitability)]:
         assert torch.equal(a, b)
+
+
+def test_sampling_policy_and_last_beliefs_match_upstream(cuda_device, golden_dir):
+    """policy_probs_sample (the policy at the start of iteration t_sample) and the beliefs of
+    the last iteration, the inputs of leaf sampling, against the upstream run."""
+    z = np.load(os.path.join(golden_dir, "cfr_turn_cap2_t16.npz"))
+    from leaf_models import pot_echo_leaf_fn
+    from poker2_b200 import solver, tree as ptree
+
+    roots = ptree.root_states(z["pot"], z["stack"], min_raise=2, street=2)
+    trees = ptree.build_trees(roots, [0.5, 1.0], int(z["max_depth"]), bb=2, max_raises=int(z["cap"]))
+    boards = np.concatenate([z["boards"].astype(np.int64), np.full((z["boards"].shape[0], 1), -1)], axis=1)
+    layout = solver.device_layout(trees, boards)
+    sv = solver.SteppedSolver(layout, torch.from_numpy(boards), cuda_device, sampling=True)
+    sv.set_sampling_schedule(torch.from_numpy(z["t_sample"]))
+    leaf_fn = pot_echo_leaf_fn(trees, layout.model_nodes, torch.from_numpy(z["hand_weights"]))
+    rb = solver.pad_rows(torch.from_numpy(z["ranges"]).to(cuda_device)).contiguous()
+    res = sv.solve(rb, solver.iteration_scalars(int(z["iterations"])), leaf_fn)
+    n = trees.num_roots
+    got = res.level_major(res.policy_sample).cpu()[n:]
+    want = torch.from_numpy(z["policy_sample"])[n:]
+    _report("policy_sample", got, want)
+    torch.testing.assert_close(got, want, rtol=RTOL, atol=ATOL)
+    keep = torch.from_numpy((trees.child_count > 0) | (trees.leaf_mask & ~trees.state.done))  # internal + model leaves
+    got_b = res.level_major(res.beliefs_last).cpu()[keep]
+    want_b = torch.from_numpy(z["beliefs_last"])[keep]
+    _report("beliefs_last", got_b, want_b)
+    torch.testing.assert_close(got_b, want_b, rtol=RTOL, atol=ATOL)

@@ -99,3 +99,26 @@ def test_cfr_oracle_with_model_leaves_bit_exact(golden_dir):
     ex, br = o.exploitability()
     assert torch.equal(ex, torch.from_numpy(z["exploitability"]))
     assert torch.equal(br, torch.from_numpy(z["br_values"]))
+
+
+def test_sampling_schedule_matches_upstream(golden_dir):
+    from poker2_b200 import sampling
+
+    z = np.load(os.path.join(golden_dir, "cfr_turn_cap2_t16.npz"))
+    got = sampling.sampling_schedule(3, int(z["iterations"]), torch.Generator().manual_seed(99))
+    assert np.array_equal(got.numpy(), z["schedule_seed99"])
+
+
+def test_sample_leaves_matches_upstream(golden_dir):
+    """The walk from the roots to the next public states, with the upstream run's sampling
+    policy and beliefs and the same generator seed, lands on the same states."""
+    from poker2_b200 import sampling
+
+    z = np.load(os.path.join(golden_dir, "cfr_turn_cap2_t16.npz"))
+    t = _turn_trees(z)
+    nodes, cont, bel = sampling.sample_leaves(
+        t, torch.from_numpy(z["policy_sample"]), torch.from_numpy(z["beliefs_last"]),
+        torch.Generator().manual_seed(321), sample_epsilon=float(z["sample_epsilon"]), training_mode=True)
+    assert torch.equal(bel, torch.from_numpy(z["sampled_beliefs"]))
+    assert np.array_equal(t.state.pot[cont.numpy()], z["sampled_pot"])
+    assert np.array_equal(t.state.stacks[cont.numpy()], z["sampled_stacks"])
