@@ -1,5 +1,6 @@
 // Error plumbing and per-device constant tables.
 #include "common.cuh"
+#include "rank7.cuh"
 
 #include <cstdarg>
 #include <cstdio>
@@ -26,6 +27,7 @@ int check_cuda(cudaError_t e, const char* what) {
 
 constexpr int kMaxDevices = 64;
 static ComboTable* g_combo[kMaxDevices] = {nullptr};
+static RankLut* g_rank_lut[kMaxDevices] = {nullptr};
 static int g_sms[kMaxDevices] = {0};
 static std::mutex g_mu;
 
@@ -55,11 +57,25 @@ int ensure_tables() {
         cudaFree(d);
         return rc;
     }
+    static RankLut lut;  // 33 KB, filled once
+    for (uint32_t m = 0; m < (uint32_t)kRankLutEntries; ++m) lut.mask_entry[m] = rank_lut_mask_entry(m);
+    for (int i = 0; i < kTypeLutEntries; ++i) lut.type_entry[i] = rank_lut_type_entry(i / 12, (i / 4) % 3, i % 4);
+    for (int i = 0; i < 8; ++i) lut.pad[i] = 0;
+    RankLut* dl = nullptr;
+    rc = check_cuda(cudaMalloc(&dl, sizeof(RankLut)), "cudaMalloc(rank table)");
+    if (!rc) rc = check_cuda(cudaMemcpy(dl, &lut, sizeof(RankLut), cudaMemcpyHostToDevice), "cudaMemcpy(rank table)");
+    if (rc) {
+        cudaFree(d);
+        if (dl) cudaFree(dl);
+        return rc;
+    }
+    g_rank_lut[dev] = dl;
     g_combo[dev] = d;
     return P2B_OK;
 }
 
 const ComboTable* device_combo_table() { return g_combo[current_device()]; }
+const RankLut* device_rank_lut() { return g_rank_lut[current_device()]; }
 
 int sm_count() {
     const int dev = current_device();

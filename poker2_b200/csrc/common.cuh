@@ -30,6 +30,8 @@ struct ComboTable {
 };
 int ensure_tables();  // uploads the constant tables of the current device (idempotent)
 const ComboTable* device_combo_table();
+struct RankLut;
+const RankLut* device_rank_lut();  // tables of the hand-ranking table walk (rank7.cuh)
 
 }  // namespace p2b
 

@@ -13,10 +13,21 @@ constexpr int kTileHands = kRankThreads * kHandsPerThread;  // 1024 hands = 1433
 constexpr int kTileVec = kTileHands * 14 / 16;              // 896 x 16 B
 
 // cards: [n,7] int16; out: [n] int32.  VEC = base pointer is 16-byte aligned.
+// A block keeps the 32 KB rank table, the type table and a card -> suit-lane-bit table in
+// shared memory; a hand of distinct cards is scored by the table walk of rank7.cuh
+// (score_distinct_lut), a hand with repeated ids by the general bit-mask scorer.
 template <bool VEC>
 __global__ void __launch_bounds__(kRankThreads) rank7_cards_kernel(const int16_t* __restrict__ cards,
-                                                                   int32_t* __restrict__ out, int64_t n) {
+                                                                   int32_t* __restrict__ out, int64_t n,
+                                                                   const RankLut* __restrict__ lut) {
+    __shared__ __align__(16) uint32_t T[kRankLutEntries];
+    __shared__ uint32_t TT[32];
     __shared__ __align__(16) int16_t tile[kTileHands * 7];
+    {
+        const uint4* src = reinterpret_cast<const uint4*>(lut->mask_entry);
+        for (int i = threadIdx.x; i < kRankLutEntries / 4; i += kRankThreads) reinterpret_cast<uint4*>(T)[i] = __ldg(src + i);
+        if (threadIdx.x < 32) TT[threadIdx.x] = threadIdx.x < kTypeLutEntries ? lut->type_entry[threadIdx.x] : 0u;
+    }
     const int64_t num_tiles = (n + kTileHands - 1) / kTileHands;
     for (int64_t t = blockIdx.x; t < num_tiles; t += gridDim.x) {
         const int64_t hand0 = t * kTileHands;
@@ -30,17 +41,49 @@ __global__ void __launch_bounds__(kRankThreads) rank7_cards_kernel(const int16_t
             for (int i = threadIdx.x; i < kTileVec; i += kRankThreads) dst4[i] = __ldcs(src4 + i);
         } else {
             for (int i = threadIdx.x; i < hands * 7; i += kRankThreads) tile[i] = src[i];
+            for (int i = hands * 7 + threadIdx.x; i < kTileHands * 7; i += kRankThreads) tile[i] = 0;
         }
         __syncthreads();
+        // a thread takes four consecutive hands: 56 bytes = seven 8-byte words of the tile
+        uint32_t w[14];
+        {
+            const uint2* mine = reinterpret_cast<const uint2*>(tile) + 7 * threadIdx.x;
+#pragma unroll
+            for (int i = 0; i < 7; ++i) {
+                const uint2 v = mine[i];
+                w[2 * i] = v.x;
+                w[2 * i + 1] = v.y;
+            }
+        }
+        int32_t score[kHandsPerThread];
 #pragma unroll
         for (int j = 0; j < kHandsPerThread; ++j) {
-            const int h = threadIdx.x + j * kRankThreads;
-            if (h < hands) {
-                int c[7];
+            int c[7];
+            uint32_t lo = 0, hi = 0;
 #pragma unroll
-                for (int i = 0; i < 7; ++i) c[i] = tile[h * 7 + i];
-                __stcs(out + hand0 + h, score_cards<7>(c));
+            for (int i = 0; i < 7; ++i) {
+                const int e = 7 * j + i;  // 16-bit element of the thread's 28
+                c[i] = (int)(int16_t)((e & 1) ? (w[e >> 1] >> 16) : (w[e >> 1] & 0xffffu));
+                const uint32_t bit = (uint32_t)card_bit(c[i]);
+                uint32_t blo, bhi;  // 1 << bit as two words: shl.b32 gives 0 for shift counts above 31
+                asm("shl.b32 %0, 1, %1;" : "=r"(blo) : "r"(bit));
+                asm("shl.b32 %0, 1, %1;" : "=r"(bhi) : "r"(bit - 32u));
+                lo |= blo;
+                hi |= bhi;
             }
+            if (__popc(lo) + __popc(hi) == 7) {
+                score[j] = score_distinct_lut(lo & 0x1fffu, (lo >> 16) & 0x1fffu, hi & 0x1fffu, (hi >> 16) & 0x1fffu, T, TT);
+            } else {
+                score[j] = score_cards<7>(c);
+            }
+        }
+        const int h0 = kHandsPerThread * threadIdx.x;
+        if (h0 + kHandsPerThread <= hands && ((reinterpret_cast<uintptr_t>(out + hand0) & 15) == 0)) {
+            __stcs(reinterpret_cast<int4*>(out + hand0 + h0), make_int4(score[0], score[1], score[2], score[3]));
+        } else {
+#pragma unroll
+            for (int j = 0; j < kHandsPerThread; ++j)
+                if (h0 + j < hands) out[hand0 + h0 + j] = score[j];
         }
         __syncthreads();
     }
@@ -94,10 +137,12 @@ int sm_count();
 
 int launch_rank7_cards(const int16_t* cards, int64_t n, int32_t* out, cudaStream_t stream) {
     if (n == 0) return P2B_OK;
-    const int grid = grid_for(n, kTileHands, sm_count() * 8);
+    int rc = ensure_tables();
+    if (rc) return rc;
+    const int grid = grid_for(n, kTileHands, sm_count() * 4);  // 4 blocks of 46.6 KB shared memory per SM
     const bool vec = (reinterpret_cast<uintptr_t>(cards) & 15) == 0;
-    if (vec) rank7_cards_kernel<true><<<grid, kRankThreads, 0, stream>>>(cards, out, n);
-    else rank7_cards_kernel<false><<<grid, kRankThreads, 0, stream>>>(cards, out, n);
+    if (vec) rank7_cards_kernel<true><<<grid, kRankThreads, 0, stream>>>(cards, out, n, device_rank_lut());
+    else rank7_cards_kernel<false><<<grid, kRankThreads, 0, stream>>>(cards, out, n, device_rank_lut());
     return check_cuda(cudaGetLastError(), "rank7_cards_kernel");
 }
 

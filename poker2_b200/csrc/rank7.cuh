@@ -114,6 +114,81 @@ __device__ __forceinline__ int32_t score_from_masks(uint32_t m0, uint32_t m1, ui
     return best;
 }
 
+// ---- table walk for hands of distinct cards --------------------------------------------
+// One 32-bit entry per 13-bit rank mask:
+//   bits 19:0   the (up to) five highest ranks of the mask as 4-bit fields, highest first,
+//               left-aligned, zero-filled;
+//   bits 27:24  1 + the LOWEST complete straight window of the mask (0 = no straight);
+//   bits 31:28  1 + the HIGHEST complete straight window.
+// With the four multiplicity masks of a hand, the kicker fields (ranks by count desc, rank
+// desc) are the concatenation of the entries of quads, trips, pairs and singles, each
+// shifted right by four bits per rank already placed; the hand type and the number of
+// fields it keeps follow from the three counts (quads, trips, pairs) through a 24-entry
+// table.  Straight and flush candidates come from the entries of the rank union and of the
+// flush suit.
+constexpr int kRankLutEntries = 8192;
+constexpr int kTypeLutEntries = 24;
+struct RankLut {
+    uint32_t mask_entry[kRankLutEntries];
+    uint32_t type_entry[kTypeLutEntries];  // index quads*12 + trips*4 + pairs: type << 24 | kept-field mask
+    uint32_t pad[8];
+};
+
+inline uint32_t rank_lut_mask_entry(uint32_t mask) {  // host side, plain loops
+    uint32_t fields = 0;
+    int placed = 0;
+    for (int r = 12; r >= 0 && placed < 5; --r)
+        if (mask & (1u << r)) {
+            fields |= (uint32_t)r << (16 - 4 * placed);
+            ++placed;
+        }
+    const uint32_t ext = (mask << 1) | ((mask >> 12) & 1u);
+    int lowest = -1, highest = -1;
+    for (int w = 0; w <= 9; ++w)
+        if (((ext >> w) & 0x1fu) == 0x1fu) {
+            if (lowest < 0) lowest = w;
+            highest = w;
+        }
+    return fields | ((uint32_t)(lowest + 1) << 24) | ((uint32_t)(highest + 1) << 28);
+}
+
+inline uint32_t rank_lut_type_entry(int quads, int trips, int pairs) {
+    int type, nf;
+    if (quads) { type = 8; nf = 2; }
+    else if (trips && (trips >= 2 || pairs)) { type = 7; nf = 2; }
+    else if (trips) { type = 4; nf = 3; }
+    else if (pairs >= 2) { type = 3; nf = 3; }
+    else if (pairs) { type = 2; nf = 4; }
+    else { type = 1; nf = 5; }
+    const uint32_t keep = (0xFFFFFu << (4 * (5 - nf))) & 0xFFFFFu;
+    return ((uint32_t)type << 24) | keep;
+}
+
+// Score of a hand of DISTINCT cards given as four suit masks; T / TT are the two tables
+// (shared or global memory).  Bit-identical to score_from_masks for such hands.
+__device__ __forceinline__ int32_t score_distinct_lut(uint32_t m0, uint32_t m1, uint32_t m2, uint32_t m3,
+                                                      const uint32_t* __restrict__ T, const uint32_t* __restrict__ TT) {
+    const RankClasses rc = classes_from_suits(m0, m1, m2, m3);
+    const uint32_t seen = m0 | m1 | m2 | m3;
+    const uint32_t eq = T[rc.quads] & 0xFFFFFu, et = T[rc.trips] & 0xFFFFFu, ep = T[rc.pairs] & 0xFFFFFu;
+    const uint32_t es = T[rc.singles] & 0xFFFFFu, en = T[seen];
+    const int nq = __popc(rc.quads), nt = __popc(rc.trips), np = __popc(rc.pairs);
+    const uint32_t kick = eq | (et >> (4 * nq)) | (ep >> (4 * (nq + nt))) | (es >> (4 * (nq + nt + np)));
+    const uint32_t tt = TT[nq * 12 + nt * 4 + np];
+    int32_t best = (int32_t)(((tt >> 24) << 20) | (kick & tt & 0xFFFFFu));
+    const uint32_t sw = (en >> 24) & 15u;
+    if (sw) best = max(best, (int32_t)((5u << 20) | ((sw - 1u) << 16)));
+    const int c0 = __popc(m0), c1 = __popc(m1), c2 = __popc(m2), c3 = __popc(m3);
+    if (max(max(c0, c1), max(c2, c3)) >= 5) {
+        const uint32_t fm = c0 >= 5 ? m0 : (c1 >= 5 ? m1 : (c2 >= 5 ? m2 : m3));
+        const uint32_t ef = T[fm];
+        best = max(best, (int32_t)((6u << 20) | (ef & 0xFFFFFu)));
+        const uint32_t sf = ef >> 28;
+        if (sf) best = max(best, (int32_t)((9u << 20) | ((sf - 1u) << 16)));
+    }
+    return best;
+}
+
 // Position of card id c (0..51) in a 64-bit word made of four 16-bit suit lanes.
 __device__ __forceinline__ int card_bit(int c) {
     const int s = (c * 79) >> 10;  // c / 13 for 0 <= c < 52

@@ -93,6 +93,7 @@ __device__ __forceinline__ void scan_byte_counts(const uint32_t* __restrict__ cn
 //   order  : [m,1326] int64 stable ascending argsort of scores
 __global__ void __launch_bounds__(kSetupThreads, 3) board_setup_kernel(const int16_t* __restrict__ boards, int64_t m,
                                                                        const ComboTable* __restrict__ combos,
+                                                                       const RankLut* __restrict__ lut,
                                                                        unsigned char* __restrict__ tabs,
                                                                        int32_t* __restrict__ scores,
                                                                        long long* __restrict__ order) {
@@ -132,8 +133,13 @@ __global__ void __launch_bounds__(kSetupThreads, 3) board_setup_kernel(const int
             ch.add(1u << (b1 & 15));
             ch.add(1u << (b2 & 15));
             const uint32_t lo = (uint32_t)suits, hi = (uint32_t)(suits >> 32);
-            const int32_t s = score_from_masks(lo & 0x1fffu, (lo >> 16) & 0x1fffu, hi & 0x1fffu, (hi >> 16) & 0x1fffu,
-                                               ch.classes());
+            int32_t s;
+            if (__popcll(suits) == 7)  // seven distinct cards: table walk (tables read through L1)
+                s = score_distinct_lut(lo & 0x1fffu, (lo >> 16) & 0x1fffu, hi & 0x1fffu, (hi >> 16) & 0x1fffu,
+                                       lut->mask_entry, lut->type_entry);
+            else
+                s = score_from_masks(lo & 0x1fffu, (lo >> 16) & 0x1fffu, hi & 0x1fffu, (hi >> 16) & 0x1fffu,
+                                     ch.classes());
             if (scores) scores[b * P2B_NUM_HANDS + h] = s;
             k = (uint32_t)s;
         }
@@ -266,24 +272,67 @@ __global__ void __launch_bounds__(kSetupThreads, 3) board_setup_kernel(const int
     __syncthreads();
 
     // ---- 5. list entries before the tie group and before its end, per hand and card ----
-    for (int idx = tid; idx < 52 * 51; idx += kSetupThreads) {
-        const int card = idx / 51, t = idx - 51 * card;
+    // Entries of one tie group are consecutive in a card's list.  A warp takes a list (51
+    // entries: lane and lane+32): nb = index of the first entry of the run, ne = index after
+    // its last one, by a max scan and a reverse min scan over run starts.
+    for (int card = warp; card < 52; card += kSetupWarps) {
         const uint16_t* list = lp + card * 52;
-        const int k = list[t];
-        const int L = lg[k], R = rt[L];
-        int nb = t, ne = t + 1;
-        while (nb > 0 && list[nb - 1] >= L) --nb;
-        while (ne < 51 && list[ne] < R) ++ne;
-        const int h = val[k];
-        HandRec* rr = rec_s + h;
-        if (card == combos->c1[h]) {  // the hand's lower card
-            rr->lpos = (uint16_t)L;
-            rr->rpos = (uint16_t)R;
-            rr->nb0 = (uint8_t)nb;
-            rr->ne0 = (uint8_t)ne;
-        } else {
-            rr->nb1 = (uint8_t)nb;
-            rr->ne1 = (uint8_t)ne;
+        const int tA = lane, tB = lane + 32;
+        const bool hasB = tB < 51;
+        const int kA = list[tA], kB = hasB ? list[tB] : 0;
+        const int LA = lg[kA], LB = hasB ? (int)lg[kB] : -1;
+        int prevA = __shfl_up_sync(0xffffffffu, LA, 1);
+        int prevB = __shfl_up_sync(0xffffffffu, LB, 1);
+        const int lastA = __shfl_sync(0xffffffffu, LA, 31);
+        if (lane == 0) {
+            prevA = -2;
+            prevB = lastA;
+        }
+        const bool startA = LA != prevA, startB = hasB && LB != prevB;
+        // latest run start at or before each entry
+        int nbA = startA ? tA : -1, nbB = startB ? tB : -1;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int ua = __shfl_up_sync(0xffffffffu, nbA, d), ub = __shfl_up_sync(0xffffffffu, nbB, d);
+            if (lane >= d) {
+                nbA = max(nbA, ua);
+                nbB = max(nbB, ub);
+            }
+        }
+        nbB = max(nbB, __shfl_sync(0xffffffffu, nbA, 31));
+        // first run start after each entry (51 if none)
+        int neA = startA ? tA : 51, neB = startB ? tB : 51;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int da = __shfl_down_sync(0xffffffffu, neA, d), db = __shfl_down_sync(0xffffffffu, neB, d);
+            if (lane + d < 32) {
+                neA = min(neA, da);
+                neB = min(neB, db);
+            }
+        }
+        // neA/neB now hold the first start at or after the entry; shift by one entry
+        const int firstB = __shfl_sync(0xffffffffu, neB, 0);
+        int afterA = __shfl_down_sync(0xffffffffu, neA, 1), afterB = __shfl_down_sync(0xffffffffu, neB, 1);
+        if (lane == 31) {
+            afterA = firstB;
+            afterB = 51;
+        }
+        afterA = min(afterA, firstB);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            if (half == 1 && !hasB) break;
+            const int k = half ? kB : kA, L = half ? LB : LA, nb = half ? nbB : nbA, ne = half ? afterB : afterA;
+            const int h = val[k];
+            HandRec* rr = rec_s + h;
+            if (card == combos->c1[h]) {  // the hand's lower card
+                rr->lpos = (uint16_t)L;
+                rr->rpos = rt[L];
+                rr->nb0 = (uint8_t)nb;
+                rr->ne0 = (uint8_t)ne;
+            } else {
+                rr->nb1 = (uint8_t)nb;
+                rr->ne1 = (uint8_t)ne;
+            }
         }
     }
     __syncthreads();
@@ -454,8 +503,8 @@ int launch_board_setup(const int16_t* boards, int64_t m, unsigned char* tabs, in
     rc = check_cuda(cudaFuncSetAttribute(board_setup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSetupSmem),
                     "board_setup_kernel smem attribute");
     if (rc) return rc;
-    board_setup_kernel<<<(unsigned)m, kSetupThreads, kSetupSmem, stream>>>(boards, m, device_combo_table(), tabs, scores,
-                                                                         order);
+    board_setup_kernel<<<(unsigned)m, kSetupThreads, kSetupSmem, stream>>>(boards, m, device_combo_table(),
+                                                                         device_rank_lut(), tabs, scores, order);
     return check_cuda(cudaGetLastError(), "board_setup_kernel");
 }
 

@@ -131,3 +131,25 @@ def test_argument_errors(cuda_device):
         rules.rank_hands(torch.zeros(4, 4, dtype=torch.int64, device=cuda_device))
     with pytest.raises(ValueError):
         rules.compare_7_batches(torch.zeros(2, 4, 13), torch.zeros(3, 4, 13))
+
+
+def test_rank7_every_count_pattern(cuda_device):
+    """Hands drawn per rank-multiplicity pattern (4+3, 4+2+1, 3+3+1, 3+2+2, 2+2+2+1, ...),
+    so that the rare hand types are as frequent as the common ones."""
+    from poker2_b200 import rules
+
+    g = np.random.default_rng(11)
+    patterns = [(4, 3), (4, 2, 1), (4, 1, 1, 1), (3, 3, 1), (3, 2, 2), (3, 2, 1, 1), (3, 1, 1, 1, 1), (2, 2, 2, 1),
+                (2, 2, 1, 1, 1), (2, 1, 1, 1, 1, 1), (1, 1, 1, 1, 1, 1, 1)]
+    hands = []
+    for pat in patterns:
+        for _ in range(4000):
+            ranks = g.choice(13, size=len(pat), replace=False)
+            hand = []
+            for r, cnt in zip(ranks, pat):
+                hand += [int(s) * 13 + int(r) for s in g.choice(4, size=cnt, replace=False)]
+            g.shuffle(hand)
+            hands.append(hand)
+    hands = np.asarray(hands, dtype=np.int16)
+    got = rules.rank_7_cards_single_batch(torch.from_numpy(hands).to(cuda_device)).cpu().numpy()
+    assert np.array_equal(got, rank7.rank7(hands, rank7.MODE_IDS))
