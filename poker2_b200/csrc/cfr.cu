@@ -259,63 +259,77 @@ __device__ __forceinline__ void normalize2(Block& B, const HandInfo<VPT>& hi, FV
 // One block-wide round of the cross-hand work of a node.  For each of the `n_cs` staged rows
 // cs_row0 .. cs_row0+n_cs-1: per-card sums (cs[i][52]) and total (S[i]).  For each of the
 // `n_pc` rows listed in pc_rows: strength-order prefix sums (pref slot i) and per-card
-// prefix sums (pc slot i) for the showdown formula.  Threads work in groups of four on one
-// (row, card) list; whole warps take the row totals and the strength-order scans.  The
-// staged rows must be visible (barrier) before the call; it ends with a barrier.
+// prefix sums (pc slot i) for the showdown formula.
+//
+// The work is cut into warp-sized units that the warps of the block take from a shared
+// counter, largest first, so that all warps finish together whatever the mix:
+//   * quarter scans: a warp produces the strength-order prefix of 352 consecutive sorted
+//     positions; its starting offset is the sum of the earlier quarters, which it adds up
+//     itself (no dependency on another warp);
+//   * row totals: a warp adds up one row;
+//   * list rounds: 32 threads = 8 groups of four threads, a group takes one (row, card) list
+//     of 51 hands (13 entries per thread).
+// Every unit's arithmetic is fixed, so the results do not depend on which warp ran it.
+// The staged rows must be visible (barrier) before the call; it ends with a barrier.
+constexpr int kScanQuarter = 352;  // 32 lanes x 11 sorted positions
+
 __device__ __forceinline__ void node_tables(Block& B, int cs_row0, int n_cs, const int (&pc_rows)[2], int n_pc) {
     const BoardTabView tv = view_tables(B.tab);
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    const int tid = threadIdx.x, lane = tid & 31;
     const int quads_cs = n_cs * 208, quads = quads_cs + n_pc * 208;
     const uint16_t* __restrict__ nat = B.nat;
     const uint16_t* __restrict__ cardlist = tv.cardlist;
     const uint16_t* __restrict__ sorted = tv.sorted;
-    for (int base = 0; base < quads; base += blockDim.x) {
-        const int t = base + tid;
-        const bool valid = t < quads, is_cs = t < quads_cs;
-        const int u = is_cs ? t : t - quads_cs;
-        const int slot = u / 208, rem = u % 208, c = rem >> 2, q = rem & 3;
-        const float* __restrict__ x = B.stage_row(is_cs ? cs_row0 + slot : pc_rows[slot > 1 ? 1 : slot]);
-        // the (up to) 13 values of this quarter list, loaded before any arithmetic so that the
-        // shared-memory latencies overlap
-        float v[13];
+    const int n_scan = 4 * n_pc, n_units = n_scan + n_cs + (quads + 31) / 32;
+    int* queue = B.misc + 2;
+    while (true) {
+        int unit = 0;
+        if (lane == 0) unit = atomicAdd(queue, 1);
+        unit = __shfl_sync(0xffffffffu, unit, 0);
+        if (unit >= n_units) break;
+        if (unit < n_scan) {
+            // quarter scan; the last quarters (most preceding positions to add up) go first
+            const int slot = unit % n_pc, qi = 3 - unit / n_pc;
+            const float* __restrict__ x = B.stage_row(pc_rows[slot]);
+            float* __restrict__ pref = B.pref + slot * P2B_HPAD;
+            double before = 0.0;
+            for (int r = 0; r < qi; ++r) {
+                const int k0 = r * kScanQuarter + 11 * lane;  // all inside the row: r < 3
+                float v[11];
 #pragma unroll
-        for (int i = 0; i < 13; ++i) {
-            const int e = is_cs ? q + 4 * i : 13 * q + i;  // interleaved for sums, contiguous for prefixes
-            int idx = 0;
-            if (valid && e < 51) idx = is_cs ? nat[c * 51 + e] : cardlist[e * 52 + c];
-            v[i] = (valid && e < 51) ? x[idx] : 0.0f;
-        }
-        double t_even = 0.0, t_odd = 0.0;
+                for (int i = 0; i < 11; ++i) v[i] = x[sorted[k0 + i]];
+                double a0 = 0.0, a1 = 0.0;
 #pragma unroll
-        for (int i = 0; i < 13; ++i) {
-            if (i & 1) t_odd += (double)v[i];
-            else t_even += (double)v[i];
-        }
-        const double tot = t_even + t_odd;
-        const int g = lane & ~3;
-        const double t0 = __shfl_sync(0xffffffffu, tot, g), t1 = __shfl_sync(0xffffffffu, tot, g + 1);
-        const double t2 = __shfl_sync(0xffffffffu, tot, g + 2), t3 = __shfl_sync(0xffffffffu, tot, g + 3);
-        if (valid) {
-            if (is_cs) {
-                if (q == 0) B.cs[slot * 52 + c] = ((t0 + t1) + t2) + t3;
-            } else {
-                double acc = q == 0 ? 0.0 : (q == 1 ? t0 : (q == 2 ? t0 + t1 : (t0 + t1) + t2));
-                float* __restrict__ row = B.pc + slot * 52 * 52 + c * 52;
-                if (q == 0) row[0] = 0.0f;
-#pragma unroll
-                for (int i = 0; i < 13; ++i)
-                    if (13 * q + i < 51) {
-                        acc += (double)v[i];
-                        row[13 * q + i + 1] = (float)acc;
-                    }
+                for (int i = 0; i < 11; ++i) {
+                    if (i & 1) a1 += (double)v[i];
+                    else a0 += (double)v[i];
+                }
+                before += a0 + a1;
             }
-        }
-    }
-    // Whole-warp tasks go to the highest-numbered warps first: those have the fewest list
-    // tasks above.  Sums run on several independent accumulators to shorten the fp64
-    // dependency chains; loads are grouped ahead of the arithmetic.
-    for (int wt = nwarps - 1 - warp; wt < n_cs + n_pc; wt += nwarps) {
-        if (wt < n_cs) {  // total mass of a row
+            before = warp_sum(before);
+            const int k0 = qi * kScanQuarter + 11 * lane;
+            float v[11];
+#pragma unroll
+            for (int i = 0; i < 11; ++i) v[i] = (k0 + i < P2B_NUM_HANDS) ? x[sorted[k0 + i]] : 0.0f;
+            double local = 0.0;
+#pragma unroll
+            for (int i = 0; i < 11; ++i) local += (double)v[i];
+            double incl = local;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const double up = __shfl_up_sync(0xffffffffu, incl, d);
+                if (lane >= d) incl += up;
+            }
+            double run = before + (incl - local);
+            if (qi == 0 && lane == 0) pref[0] = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 11; ++i) {
+                run += (double)v[i];
+                if (k0 + i < P2B_NUM_HANDS) pref[k0 + i + 1] = (float)run;
+            }
+        } else if (unit < n_scan + n_cs) {
+            // total mass of a row, on several independent accumulators
+            const int wt = unit - n_scan;
             const float* __restrict__ x = B.stage_row(cs_row0 + wt);
             double acc[6] = {0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
 #pragma unroll
@@ -331,55 +345,52 @@ __device__ __forceinline__ void node_tables(Block& B, int cs_row0, int n_cs, con
             }
             const double tot = warp_sum(((acc[0] + acc[1]) + (acc[2] + acc[3])) + (acc[4] + acc[5]));
             if (lane == 0) B.S[wt] = tot;
-        } else {  // strength-order prefix sums of a row: 42 consecutive positions per lane,
-                  // as six runs of seven so that the runs accumulate independently
-            const int slot = wt - n_cs;
-            const float* __restrict__ x = B.stage_row(pc_rows[slot]);
-            float* __restrict__ pref = B.pref + slot * P2B_HPAD;
-            const int k0 = 42 * lane;
-            double part[6];
+        } else {
+            // list round: thread t of the round works on quarter q of list (row, card)
+            const int t = (unit - n_scan - n_cs) * 32 + lane;
+            const bool valid = t < quads, is_cs = t < quads_cs;
+            const int u = is_cs ? t : t - quads_cs;
+            const int slot = u / 208, rem = u % 208, c = rem >> 2, q = rem & 3;
+            const float* __restrict__ x = B.stage_row(is_cs ? cs_row0 + slot : pc_rows[slot > 1 ? 1 : slot]);
+            // the (up to) 13 values of this quarter list, loaded before any arithmetic so that the
+            // shared-memory latencies overlap
+            float v[13];
 #pragma unroll
-            for (int b = 0; b < 6; ++b) {
-                float v[7];
-#pragma unroll
-                for (int i = 0; i < 7; ++i) {
-                    const int k = k0 + 7 * b + i;
-                    v[i] = k < P2B_NUM_HANDS ? x[sorted[k]] : 0.0f;
-                }
-                double a = 0.0;
-#pragma unroll
-                for (int i = 0; i < 7; ++i) a += (double)v[i];
-                part[b] = a;
+            for (int i = 0; i < 13; ++i) {
+                const int e = is_cs ? q + 4 * i : 13 * q + i;  // interleaved for sums, contiguous for prefixes
+                int idx = 0;
+                if (valid && e < 51) idx = is_cs ? nat[c * 51 + e] : cardlist[e * 52 + c];
+                v[i] = (valid && e < 51) ? x[idx] : 0.0f;
             }
-            const double local = ((part[0] + part[1]) + (part[2] + part[3])) + (part[4] + part[5]);
-            double incl = local;
+            double t_even = 0.0, t_odd = 0.0;
 #pragma unroll
-            for (int d = 1; d < 32; d <<= 1) {
-                const double up = __shfl_up_sync(0xffffffffu, incl, d);
-                if (lane >= d) incl += up;
+            for (int i = 0; i < 13; ++i) {
+                if (i & 1) t_odd += (double)v[i];
+                else t_even += (double)v[i];
             }
-            double start = incl - local;
-            if (lane == 0) pref[0] = 0.0f;
+            const double tot = t_even + t_odd;
+            const int g = lane & ~3;
+            const double t0 = __shfl_sync(0xffffffffu, tot, g), t1 = __shfl_sync(0xffffffffu, tot, g + 1);
+            const double t2 = __shfl_sync(0xffffffffu, tot, g + 2), t3 = __shfl_sync(0xffffffffu, tot, g + 3);
+            if (valid) {
+                if (is_cs) {
+                    if (q == 0) B.cs[slot * 52 + c] = ((t0 + t1) + t2) + t3;
+                } else {
+                    double acc = q == 0 ? 0.0 : (q == 1 ? t0 : (q == 2 ? t0 + t1 : (t0 + t1) + t2));
+                    float* __restrict__ row = B.pc + slot * 52 * 52 + c * 52;
+                    if (q == 0) row[0] = 0.0f;
 #pragma unroll
-            for (int b = 0; b < 6; ++b) {
-                float v[7];
-#pragma unroll
-                for (int i = 0; i < 7; ++i) {
-                    const int k = k0 + 7 * b + i;
-                    v[i] = k < P2B_NUM_HANDS ? x[sorted[k]] : 0.0f;
+                    for (int i = 0; i < 13; ++i)
+                        if (13 * q + i < 51) {
+                            acc += (double)v[i];
+                            row[13 * q + i + 1] = (float)acc;
+                        }
                 }
-                double run = start;
-#pragma unroll
-                for (int i = 0; i < 7; ++i) {
-                    const int k = k0 + 7 * b + i;
-                    run += (double)v[i];
-                    if (k < P2B_NUM_HANDS) pref[k + 1] = (float)run;
-                }
-                start += part[b];
             }
         }
     }
     __syncthreads();
+    if (tid == 0) *queue = 0;  // for the next round; the barrier that precedes it publishes the reset
 }
 
 // Showdown EV (before the pot scaling) of the hero's hands against the range x.
@@ -1034,6 +1045,7 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
     B.nat = reinterpret_cast<uint16_t*>(smem + kOffNat);
     B.misc = reinterpret_cast<int*>(smem + kOffMisc);
     B.fsum = reinterpret_cast<float*>(smem + kOffMisc + 16);
+    if (threadIdx.x == 0) B.misc[2] = 0;  // unit counter of node_tables
     const int tid = threadIdx.x;
 
     // hands holding each card, in combo order (used by the per-card sums)
