@@ -1,0 +1,194 @@
+"""Evaluator facade with the method names the upstream data generator calls
+(`RebelDataGenerator.generate_data`, p2/search/rebel_data_generator.py:52-96):
+`initialize_subgame(src_env, src_indices, initial_beliefs)`, `evaluate_cfr(training_mode)`,
+`training_data(exclude_start)`; attributes `root_nodes`, `num_players`, `device`, `stats`,
+`cfr_iterations` (the trainer's schedule may change it between subgames).
+
+`src_env` is read by attribute, as the upstream `HUNLTensorEnv` exposes them (tensors or
+arrays indexed by environment): board_indices [E,5] (-1 = not dealt), pot, stacks [E,2],
+starting_stacks [E,2], committed [E,2], to_act, button, street, actions_this_round,
+min_raise, is_allin [E,2], done, scale.  Upstream classes are not imported: the returned
+batches are plain dataclasses with the fields of `RebelBatch` that do not depend on a
+feature encoder (the `beliefs` member is what `features.beliefs` holds upstream).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from types import SimpleNamespace
+
+import numpy as np
+import torch
+
+from . import leaf_eval, sampling, solver as psolver, tree as ptree
+
+NUM_HANDS = 1326
+
+
+def _np(x, dtype=None) -> np.ndarray:
+    a = x.detach().cpu().numpy() if torch.is_tensor(x) else np.asarray(x)
+    return a.astype(dtype) if dtype is not None else a
+
+
+@dataclass
+class Batch:
+    """Counterpart of the upstream `RebelBatch` (p2/models/mlp/rebel_replay.py)."""
+
+    beliefs: torch.Tensor  # [n, 2*1326] beliefs under the average policy (features.beliefs upstream)
+    legal_masks: torch.Tensor  # [n, A] bool
+    statistics: dict
+    value_targets: torch.Tensor | None = None  # [n, 2, 1326]
+    policy_targets: torch.Tensor | None = None  # [n, 1326, A]
+
+    def __len__(self) -> int:
+        return int(self.beliefs.shape[0])
+
+    def __getitem__(self, index) -> "Batch":
+        pick = lambda t: None if t is None else t[index]  # noqa: E731
+        return Batch(self.beliefs[index], self.legal_masks[index], {k: v[index] for k, v in self.statistics.items()},
+                     pick(self.value_targets), pick(self.policy_targets))
+
+
+@dataclass
+class SampledStates:
+    """What `evaluate_cfr` returns: the public states the next subgames start from (upstream:
+    a `PublicBeliefState`), as tree node indices, their beliefs and their betting state."""
+
+    nodes: torch.Tensor  # [n] upstream node indices inside the solved trees
+    beliefs: torch.Tensor  # [n, 2, 1326]
+    state: ptree.RoundState
+    boards: np.ndarray  # [n, 5]
+    all_nodes: torch.Tensor = field(default=None)  # [N] the node every root's walk ended at
+
+
+class SubgameEvaluator:
+    num_players = 2
+
+    def __init__(self, device, *, iterations: int, bet_bins=(0.5, 1.0), max_depth: int = 8, bb: int = 2,
+                 cfr_type: str = "discounted", alpha: float = 1.5, beta: float = 0.0, gamma: float = 2.0,
+                 dcfr_delay: int = 0, cfr_plus: bool = False, max_raises=None, model=None,
+                 chance_average: bool = True, leaf_chunk: int = 2048, sample_epsilon: float = 0.25,
+                 generator: torch.Generator | None = None):
+        self.device = torch.device(device)
+        self.cfr_iterations = int(iterations)
+        self.bet_bins, self.max_depth, self.bb, self.max_raises = list(bet_bins), max_depth, bb, max_raises
+        self.cfr_type, self.alpha, self.beta, self.gamma = cfr_type, alpha, beta, gamma
+        self.dcfr_delay, self.cfr_plus = dcfr_delay, cfr_plus
+        self.model, self.chance_average, self.leaf_chunk = model, chance_average, leaf_chunk
+        self.sample_epsilon = sample_epsilon
+        self.generator = generator
+        self.stats: dict = {}
+        self.root_nodes = 0
+        self._result = None
+
+    # ------------------------------------------------------------------ initialize_subgame
+    def initialize_subgame(self, src_env, src_indices, initial_beliefs=None) -> None:
+        """Builds the public trees below the given root states and the device buffers of the
+        solve (cfr_evaluator.py:770-828, sparse_cfr_evaluator.py:141-306)."""
+        idx = _np(src_indices, np.int64)
+        take = lambda name, dt: _np(getattr(src_env, name))[idx].astype(dt)  # noqa: E731
+        n = idx.shape[0]
+        raises = take("raises", np.int64) if hasattr(src_env, "raises") else np.zeros(n, dtype=np.int64)
+        roots = ptree.RoundState(
+            to_act=take("to_act", np.int64), pot=take("pot", np.int64), stacks=take("stacks", np.int64),
+            committed=take("committed", np.int64), min_raise=take("min_raise", np.int64),
+            actions_this_round=take("actions_this_round", np.int64), is_allin=take("is_allin", bool),
+            done=take("done", bool), street=take("street", np.int64), button=take("button", np.int64),
+            starting_stacks=take("starting_stacks", np.int64), scale=take("scale", np.float32), raises=raises)
+        self.boards = take("board_indices", np.int64)
+        self.trees = ptree.build_trees(roots, self.bet_bins, self.max_depth, bb=self.bb, max_raises=self.max_raises)
+        self.layout = psolver.device_layout(self.trees, self.boards)
+        self.root_nodes = n
+        boards_t = torch.from_numpy(self.boards)
+        kw = dict(exploitability=True, keep_node_values=True, sampling=True)
+        if self.layout.num_model_leaves:
+            if self.model is None:
+                raise ValueError("the subgames have non-terminal leaves: a leaf model is required")
+            self.solver = psolver.SteppedSolver(self.layout, boards_t, self.device, **kw)
+            leaf_boards = torch.from_numpy(self.boards[self.trees.root_of[self.layout.model_nodes]])
+            ctx = leaf_eval.leaf_context(self.trees, self.layout.model_nodes)
+            cls = leaf_eval.ChanceLeafEvaluator if self.chance_average else leaf_eval.DirectLeafEvaluator
+            extra = dict(chunk=self.leaf_chunk) if self.chance_average else {}
+            self.leaf_fn = cls(self.model, leaf_boards, ctx, self.device, **extra)
+        else:
+            self.solver = psolver.SubgameSolver(self.layout, boards_t, self.device, **kw)
+            self.leaf_fn = None
+        if initial_beliefs is None:
+            initial_beliefs = torch.full((n, 2, NUM_HANDS), 1.0 / NUM_HANDS, dtype=torch.float32)
+        self.root_beliefs = psolver.pad_rows(initial_beliefs.to(device=self.device, dtype=torch.float32)).contiguous()
+        self._result = None
+        self.stats["evaluator_street"] = float(roots.street.mean())
+        self.stats["evaluator_total_nodes"] = float(self.trees.total_nodes)
+        self.stats["evaluator_root_nodes"] = float(n)
+        self.stats["evaluator_tree_depth"] = float(self.trees.tree_depth)
+
+    # ------------------------------------------------------------------ evaluate_cfr
+    def evaluate_cfr(self, training_mode: bool = True) -> SampledStates:
+        """Runs the solve (cfr_evaluator.py:1497-1528) and samples the next public states."""
+        T = self.cfr_iterations
+        gen_device = self.generator.device if self.generator is not None else torch.device("cpu")
+        t_sample = sampling.sampling_schedule(self.root_nodes, T, self.generator, cfr_type=self.cfr_type,
+                                              dcfr_delay=self.dcfr_delay, device=gen_device)
+        self.t_sample = t_sample
+        self.solver.set_sampling_schedule(t_sample.to(self.device))
+        scal = psolver.iteration_scalars(T, cfr_type=self.cfr_type, alpha=self.alpha, beta=self.beta,
+                                         gamma=self.gamma, dcfr_delay=self.dcfr_delay)
+        if self.leaf_fn is not None:
+            res = self.solver.solve(self.root_beliefs, scal, self.leaf_fn, cfr_plus=self.cfr_plus)
+        else:
+            res = self.solver.solve(self.root_beliefs, scal, cfr_plus=self.cfr_plus)
+        self._result = res
+        # the walk draws from the generator: run it where the generator lives
+        pol = res.level_major(res.policy_sample).to(gen_device)
+        bel = res.level_major(res.beliefs_last).to(gen_device)
+        nodes, cont, cont_beliefs = sampling.sample_leaves(self.trees, pol, bel, self.generator,
+                                                           sample_epsilon=self.sample_epsilon,
+                                                           training_mode=training_mode)
+        cont_np = cont.cpu().numpy()
+        return SampledStates(nodes=cont, beliefs=cont_beliefs, state=self.trees.state.take(cont_np),
+                             boards=self.boards[self.trees.root_of[cont_np]], all_nodes=nodes)
+
+    # ------------------------------------------------------------------ training_data
+    def training_data(self, exclude_start: bool = True):
+        """(value batch, pre-chance value batch, policy batch) as upstream
+        (cfr_evaluator.py:1384-1495).  The pre-chance batch (targets averaged over the card that
+        opened the street, which needs the value network on the previous street's beliefs) is
+        not produced here: None."""
+        if self._result is None:
+            raise RuntimeError("training_data() needs evaluate_cfr() first")
+        res, t = self._result, self.trees
+        N, top, A = t.num_roots, t.depth_offsets[-2], t.num_actions
+        dev = self.device
+        pol = res.level_major(res.policy_avg)  # [M,1326]
+        parent = torch.from_numpy(t.parent_index[N:]).to(dev)
+        action = torch.from_numpy(t.action_from_parent[N:]).to(dev)
+        by_src = torch.zeros((top, A, NUM_HANDS), dtype=torch.float32, device=dev)
+        by_src[parent, action] = pol[N:]
+        policy_targets = by_src.permute(0, 2, 1)
+        value_targets = res.root_values[..., :NUM_HANDS].clamp(-1.0, 1.0)
+        beliefs_avg = res.level_major(res.beliefs_avg)[:top].reshape(top, 2 * NUM_HANDS)
+        amounts, legal = ptree.legal_bins(t.state, self.bet_bins, self.max_raises)
+        st = t.state
+        as_t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)  # noqa: E731
+        statistics = {"to_act": as_t(st.to_act), "street": as_t(st.street), "stage": as_t(2 * st.street),
+                      "board": as_t(self.boards[t.root_of]), "pot": as_t(st.pot), "bet_amounts": as_t(amounts)}
+        legal_t = as_t(legal)
+        value_stats = {k: v[:N] for k, v in statistics.items()}
+        value_stats["local_exploitability"] = res.exploitability
+        value_stats["local_best_response_values"] = res.br_values
+        value_batch = Batch(beliefs_avg[:N], legal_t[:N], value_stats, value_targets=value_targets)
+        if exclude_start:
+            start = as_t((st.street[:N] == 0) & (st.actions_this_round[:N] == 0))
+            value_batch = value_batch[~start]
+        valid_top = as_t(~t.leaf_mask[:top])
+        policy_batch = Batch(beliefs_avg[valid_top], legal_t[:top][valid_top],
+                             {k: v[:top][valid_top] for k, v in statistics.items()},
+                             policy_targets=policy_targets[valid_top])
+        return value_batch, None, policy_batch
+
+
+def env_view(roots: ptree.RoundState, boards) -> SimpleNamespace:
+    """An object with the attributes `initialize_subgame` reads, from a `RoundState` and the
+    boards of the same rows (for callers that do not hold an upstream environment)."""
+    ns = SimpleNamespace(**{k: v for k, v in roots.__dict__.items()})
+    ns.board_indices = np.asarray(boards, dtype=np.int64)
+    return ns

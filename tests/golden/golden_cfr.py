@@ -305,7 +305,38 @@ def gen_turn() -> None:
          exploitability=ex.local_exploitability.numpy(), br_values=ex.local_best_response_values.numpy())
 
 
-SECTIONS = {"tree": gen_tree, "cfr": gen_cfr, "turn": gen_turn}
+def gen_training_data() -> None:
+    """`training_data()` of the upstream evaluator (cfr_evaluator.py:1384-1495) after a short
+    river solve: value targets, policy targets, legal masks and statistics."""
+    import warnings
+
+    b, r, p, s = seeded_inputs(7, 2, (20, 200), (100, 1000))
+    iterations, cap, depth = 12, 2, 8
+    install_raise_cap(cap)
+    ev = make_evaluator(2, iterations, depth=depth)
+    ev.initialize_subgame(river_env(b, p, s), torch.arange(2), r)
+    ev.evaluate_cfr()
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        vb, pre, pol = ev.training_data(exclude_start=True)
+    install_raise_cap(None)
+    print("training_data: value", len(vb), "pre", len(pre), "policy", len(pol))
+    save("training_data_cap2_t12.npz",
+         boards=b.to(torch.int16).numpy(), ranges=r.numpy(), pot=p.numpy(), stack=s.numpy(),
+         iterations=np.int64(iterations), cap=np.int64(cap), max_depth=np.int64(depth),
+         value_targets=vb.value_targets.numpy(), value_legal_masks=vb.legal_masks.numpy(),
+         value_beliefs=vb.features.beliefs.numpy(),
+         value_pot=vb.statistics["pot"].numpy(), value_to_act=vb.statistics["to_act"].numpy(),
+         value_bet_amounts=vb.statistics["bet_amounts"].numpy(),
+         value_exploitability=vb.statistics["local_exploitability"].numpy(),
+         value_br=vb.statistics["local_best_response_values"].numpy(),
+         policy_targets=pol.policy_targets.numpy(), policy_legal_masks=pol.legal_masks.numpy(),
+         policy_beliefs=pol.features.beliefs.numpy(), policy_pot=pol.statistics["pot"].numpy(),
+         policy_to_act=pol.statistics["to_act"].numpy(), policy_bet_amounts=pol.statistics["bet_amounts"].numpy(),
+         pre_count=np.int64(len(pre)))
+
+
+SECTIONS = {"tree": gen_tree, "cfr": gen_cfr, "turn": gen_turn, "training_data": gen_training_data}
 
 
 class _BeliefEchoModel:

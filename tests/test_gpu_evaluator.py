@@ -1,0 +1,39 @@
+"""The evaluator facade (initialize_subgame / evaluate_cfr / training_data) against the
+batches the upstream evaluator returned for the same river subgames."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_training_data_matches_upstream(cuda_device, golden_dir):
+    from poker2_b200 import evaluator, tree as ptree
+
+    z = np.load(os.path.join(golden_dir, "training_data_cap2_t12.npz"))
+    roots = ptree.root_states(z["pot"], z["stack"], min_raise=2)
+    env = evaluator.env_view(roots, z["boards"].astype(np.int64))
+    ev = evaluator.SubgameEvaluator(cuda_device, iterations=int(z["iterations"]), max_depth=int(z["max_depth"]),
+                                    max_raises=int(z["cap"]), generator=torch.Generator().manual_seed(0))
+    ev.initialize_subgame(env, torch.arange(2), torch.from_numpy(z["ranges"]))
+    assert ev.root_nodes == 2 and ev.stats["evaluator_root_nodes"] == 2.0
+    sampled = ev.evaluate_cfr(training_mode=True)
+    assert sampled.beliefs.shape[1:] == (2, 1326) and len(sampled.nodes) == sampled.beliefs.shape[0]
+    value_batch, pre_batch, policy_batch = ev.training_data(exclude_start=True)
+    assert pre_batch is None
+    close = lambda a, b: torch.testing.assert_close(a.cpu(), torch.from_numpy(b), rtol=1e-5, atol=1e-6)  # noqa: E731
+    close(value_batch.value_targets, z["value_targets"])
+    close(value_batch.beliefs, z["value_beliefs"])
+    close(policy_batch.policy_targets, z["policy_targets"])
+    close(policy_batch.beliefs, z["policy_beliefs"])
+    close(value_batch.statistics["local_exploitability"], z["value_exploitability"])
+    close(value_batch.statistics["local_best_response_values"], z["value_br"])
+    for got, want in [(value_batch.legal_masks, "value_legal_masks"), (policy_batch.legal_masks, "policy_legal_masks"),
+                      (value_batch.statistics["pot"], "value_pot"), (policy_batch.statistics["pot"], "policy_pot"),
+                      (value_batch.statistics["to_act"], "value_to_act"),
+                      (policy_batch.statistics["to_act"], "policy_to_act"),
+                      (value_batch.statistics["bet_amounts"], "value_bet_amounts"),
+                      (policy_batch.statistics["bet_amounts"], "policy_bet_amounts")]:
+        assert np.array_equal(got.cpu().numpy(), z[want]), want
