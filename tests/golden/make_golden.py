@@ -1,11 +1,12 @@
 """Generates the golden vectors under tests/golden/ by RUNNING THE UPSTREAM P2 CODE.
 
-Run it on a machine where the upstream checkout is mounted (default /root/reference, or
-set P2_REFERENCE_SRC to its `src` directory and P2_REFERENCE_TESTS to its `tests`):
+Run it on a machine where the upstream checkout is mounted, with P2_REFERENCE_SRC set to
+its `src` directory and P2_REFERENCE_TESTS to its `tests` directory:
 
-    python tests/golden/make_golden.py [section ...]
+    P2_REFERENCE_SRC=<checkout>/src P2_REFERENCE_TESTS=<checkout>/tests \
+        python tests/golden/make_golden.py [section ...]
 
-Sections: rules, showdown, unblocked, tree, cfr (default: all).  The outputs are small
+Sections: rules, showdown, unblocked, tree, cfr, chance, turn, training_data (default: all).  The outputs are small
 .npz files that travel with the repository; the test-suite reads only those files, never
 the upstream checkout.
 """
@@ -26,7 +27,8 @@ refshim.install()
 import numpy as np  # noqa: E402
 import torch  # noqa: E402
 
-REF_TESTS = os.environ.get("P2_REFERENCE_TESTS", "/root/reference/tests")
+REF_TESTS = os.environ.get("P2_REFERENCE_TESTS") or os.path.join(
+    os.path.dirname(os.environ.get("P2_REFERENCE_SRC", "").rstrip("/")), "tests")
 
 
 def save(name: str, **arrays) -> None:

@@ -14,7 +14,9 @@ import types
 
 def install(reference_src: str | None = None) -> None:
     os.environ.setdefault("TORCHDYNAMO_DISABLE", "1")
-    src = reference_src or os.environ.get("P2_REFERENCE_SRC", "/root/reference/src")
+    src = reference_src or os.environ.get("P2_REFERENCE_SRC")
+    if not src or not os.path.isdir(src):
+        raise SystemExit("set P2_REFERENCE_SRC to the `src` directory of the upstream checkout")
     if src not in sys.path:
         sys.path.insert(0, src)
     if "hydra" not in sys.modules:
