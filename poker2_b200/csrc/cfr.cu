@@ -347,21 +347,23 @@ __device__ __forceinline__ void node_tables(Block& B, int cs_row0, int n_cs, con
             if (lane == 0) B.S[wt] = tot;
         } else {
             // list round: thread t of the round works on quarter q of list (row, card)
-            const int t = (unit - n_scan - n_cs) * 32 + lane;
-            const bool valid = t < quads, is_cs = t < quads_cs;
+            const int t_raw = (unit - n_scan - n_cs) * 32 + lane;
+            const bool valid = t_raw < quads;
+            const int t = valid ? t_raw : quads - 1;  // idle threads of the last round redo the last task, unstored
+            const bool is_cs = t < quads_cs;
             const int u = is_cs ? t : t - quads_cs;
             const int slot = u / 208, rem = u % 208, c = rem >> 2, q = rem & 3;
             const float* __restrict__ x = B.stage_row(is_cs ? cs_row0 + slot : pc_rows[slot > 1 ? 1 : slot]);
-            // the (up to) 13 values of this quarter list, loaded before any arithmetic so that the
-            // shared-memory latencies overlap
+            // The (up to) 13 values of this quarter list, loaded before any arithmetic so that the
+            // shared-memory latencies overlap.  Entry e = q + 4i (sums: interleaved) or 13q + i
+            // (prefixes: contiguous); in both cases only i = 12 can fall outside the 51 entries,
+            // and it does exactly when q = 3.
             float v[13];
+            const uint16_t* __restrict__ idx_base = is_cs ? nat + c * 51 + q : cardlist + 13 * q * 52 + c;
+            const int idx_step = is_cs ? 4 : 52;
 #pragma unroll
-            for (int i = 0; i < 13; ++i) {
-                const int e = is_cs ? q + 4 * i : 13 * q + i;  // interleaved for sums, contiguous for prefixes
-                int idx = 0;
-                if (valid && e < 51) idx = is_cs ? nat[c * 51 + e] : cardlist[e * 52 + c];
-                v[i] = (valid && e < 51) ? x[idx] : 0.0f;
-            }
+            for (int i = 0; i < 12; ++i) v[i] = x[idx_base[i * idx_step]];
+            v[12] = q < 3 ? x[idx_base[12 * idx_step]] : 0.0f;
             double t_even = 0.0, t_odd = 0.0;
 #pragma unroll
             for (int i = 0; i < 13; ++i) {

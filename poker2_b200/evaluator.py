@@ -95,6 +95,13 @@ class SubgameEvaluator:
             done=take("done", bool), street=take("street", np.int64), button=take("button", np.int64),
             starting_stacks=take("starting_stacks", np.int64), scale=take("scale", np.float32), raises=raises)
         self.boards = take("board_indices", np.int64)
+        if hasattr(src_env, "last_board_indices"):
+            self.last_boards = take("last_board_indices", np.int64)
+        else:  # the board before the newest card was dealt
+            self.last_boards = self.boards.copy()
+            n_cards = (self.boards >= 0).sum(axis=1)
+            has = n_cards > 0
+            self.last_boards[np.nonzero(has)[0], n_cards[has] - 1] = -1
         self.trees = ptree.build_trees(roots, self.bet_bins, self.max_depth, bb=self.bb, max_raises=self.max_raises)
         self.layout = psolver.device_layout(self.trees, self.boards)
         self.root_nodes = n
@@ -150,9 +157,11 @@ class SubgameEvaluator:
     # ------------------------------------------------------------------ training_data
     def training_data(self, exclude_start: bool = True):
         """(value batch, pre-chance value batch, policy batch) as upstream
-        (cfr_evaluator.py:1384-1495).  The pre-chance batch (targets averaged over the card that
-        opened the street, which needs the value network on the previous street's beliefs) is
-        not produced here: None."""
+        (cfr_evaluator.py:1384-1495).  The pre-chance batch holds, for roots at the start of the
+        turn or river betting round, the expectation of the value network over the card that
+        opened the street, on the beliefs held before it (:1446-1493); it needs the leaf model
+        (None without one).  Roots at the start of the flop round (canonical-flop sampling,
+        chance_node_helper.py:218-357) are not covered and are left out of that batch."""
         if self._result is None:
             raise RuntimeError("training_data() needs evaluate_cfr() first")
         res, t = self._result, self.trees
@@ -183,7 +192,33 @@ class SubgameEvaluator:
         policy_batch = Batch(beliefs_avg[valid_top], legal_t[:top][valid_top],
                              {k: v[:top][valid_top] for k, v in statistics.items()},
                              policy_targets=policy_targets[valid_top])
-        return value_batch, None, policy_batch
+        return value_batch, self._pre_chance_batch(value_targets, legal_t[:N], value_stats), policy_batch
+
+    def _pre_chance_batch(self, value_targets, legal_root, value_stats):
+        from . import chance
+
+        t = self.trees
+        N, st = t.num_roots, t.state
+        start = (st.actions_this_round[:N] == 0) & ((st.street[:N] == 2) | (st.street[:N] == 3))
+        if self.model is None or not start.any():
+            return None
+        dev = self.device
+        rows = torch.from_numpy(np.nonzero(start)[0]).to(dev)
+        pre = self.root_beliefs[rows][..., :NUM_HANDS].contiguous()
+        boards_pre = torch.from_numpy(self.last_boards[np.nonzero(start)[0]]).to(dev)
+        ctx = leaf_eval.leaf_context(t, np.nonzero(start)[0]).to(dev)
+        expected = chance.single_card_chance_values(
+            pre, boards_pre, lambda post, samples, lookup: self.model(post, samples, ctx[lookup]))
+        targets = value_targets.clone()
+        targets[rows] = expected
+        stats = {k: v.clone() for k, v in value_stats.items()}
+        stats["board"] = torch.from_numpy(self.last_boards[:N]).to(dev)
+        street = torch.from_numpy(st.street[:N]).to(dev)
+        prev = torch.where((street > 0) & (street < 4) & torch.from_numpy(st.actions_this_round[:N] == 0).to(dev),
+                           street - 1, street)
+        stats["street"], stats["stage"] = prev, 2 * prev + 1
+        batch = Batch(self.root_beliefs[..., :NUM_HANDS].reshape(N, -1), legal_root, stats, value_targets=targets)
+        return batch[torch.from_numpy(start).to(dev)]
 
 
 def env_view(roots: ptree.RoundState, boards) -> SimpleNamespace:

@@ -67,9 +67,10 @@ def leaf_context(trees, node_index) -> torch.Tensor:
     stacks as fractions of the two starting stacks together."""
     st = trees.state
     idx = np.asarray(node_index, dtype=np.int64)
-    total = np.maximum(st.starting_stacks[idx].sum(axis=1), 1).astype(np.float32)
-    ctx = np.stack([st.pot[idx] / total, st.stacks[idx, 0] / total, st.stacks[idx, 1] / total], axis=1)
-    return torch.from_numpy(ctx.astype(np.float32))
+    total = np.maximum(st.starting_stacks[idx].astype(np.float32).sum(axis=1), np.float32(1.0))
+    f32 = lambda a: a.astype(np.float32)  # noqa: E731  (fp32 division, as the upstream encoder does)
+    ctx = np.stack([f32(st.pot[idx]) / total, f32(st.stacks[idx, 0]) / total, f32(st.stacks[idx, 1]) / total], axis=1)
+    return torch.from_numpy(np.ascontiguousarray(ctx, dtype=np.float32))
 
 
 class ChanceLeafEvaluator:

@@ -314,6 +314,8 @@ def gen_training_data() -> None:
     iterations, cap, depth = 12, 2, 8
     install_raise_cap(cap)
     ev = make_evaluator(2, iterations, depth=depth)
+    ev.model = PotEchoModel(len(BET_BINS) + 3)  # only the pre-chance batch calls it (no model leaves on the river)
+    ev.chance_helper.model = ev.model
     ev.initialize_subgame(river_env(b, p, s), torch.arange(2), r)
     ev.evaluate_cfr()
     with warnings.catch_warnings():
@@ -333,7 +335,10 @@ def gen_training_data() -> None:
          policy_targets=pol.policy_targets.numpy(), policy_legal_masks=pol.legal_masks.numpy(),
          policy_beliefs=pol.features.beliefs.numpy(), policy_pot=pol.statistics["pot"].numpy(),
          policy_to_act=pol.statistics["to_act"].numpy(), policy_bet_amounts=pol.statistics["bet_amounts"].numpy(),
-         pre_count=np.int64(len(pre)))
+         pre_count=np.int64(len(pre)), pre_value_targets=pre.value_targets.numpy(),
+         pre_beliefs=pre.features.beliefs.numpy(), pre_board=pre.statistics["board"].numpy(),
+         pre_street=pre.statistics["street"].numpy(), pre_stage=pre.statistics["stage"].numpy(),
+         hand_weights=hand_weights().numpy())
 
 
 SECTIONS = {"tree": gen_tree, "cfr": gen_cfr, "turn": gen_turn, "training_data": gen_training_data}

@@ -15,19 +15,31 @@ def test_training_data_matches_upstream(cuda_device, golden_dir):
     z = np.load(os.path.join(golden_dir, "training_data_cap2_t12.npz"))
     roots = ptree.root_states(z["pot"], z["stack"], min_raise=2)
     env = evaluator.env_view(roots, z["boards"].astype(np.int64))
+    w = torch.from_numpy(z["hand_weights"]).to(cuda_device)
+
+    def model(beliefs, boards, context):
+        # the stand-in network of the golden run (tests/golden/golden_cfr.py, PotEchoModel)
+        sw = (0.5 + context[:, 0].clamp(0.0, 10.0)).view(-1, 1) * w.view(1, 1326)
+        return torch.stack([sw + beliefs[:, 1], sw * (-0.5) + beliefs[:, 0]], dim=1)
+
     ev = evaluator.SubgameEvaluator(cuda_device, iterations=int(z["iterations"]), max_depth=int(z["max_depth"]),
-                                    max_raises=int(z["cap"]), generator=torch.Generator().manual_seed(0))
+                                    max_raises=int(z["cap"]), generator=torch.Generator().manual_seed(0), model=model)
     ev.initialize_subgame(env, torch.arange(2), torch.from_numpy(z["ranges"]))
     assert ev.root_nodes == 2 and ev.stats["evaluator_root_nodes"] == 2.0
     sampled = ev.evaluate_cfr(training_mode=True)
     assert sampled.beliefs.shape[1:] == (2, 1326) and len(sampled.nodes) == sampled.beliefs.shape[0]
     value_batch, pre_batch, policy_batch = ev.training_data(exclude_start=True)
-    assert pre_batch is None
+    # roots at the start of the river round: targets averaged over the 48 possible river cards
+    assert len(pre_batch) == int(z["pre_count"])
     close = lambda a, b: torch.testing.assert_close(a.cpu(), torch.from_numpy(b), rtol=1e-5, atol=1e-6)  # noqa: E731
     close(value_batch.value_targets, z["value_targets"])
     close(value_batch.beliefs, z["value_beliefs"])
     close(policy_batch.policy_targets, z["policy_targets"])
     close(policy_batch.beliefs, z["policy_beliefs"])
+    close(pre_batch.value_targets, z["pre_value_targets"])
+    close(pre_batch.beliefs, z["pre_beliefs"])
+    for key in ("board", "street", "stage"):
+        assert np.array_equal(pre_batch.statistics[key].cpu().numpy(), z["pre_" + key]), key
     close(value_batch.statistics["local_exploitability"], z["value_exploitability"])
     close(value_batch.statistics["local_best_response_values"], z["value_br"])
     for got, want in [(value_batch.legal_masks, "value_legal_masks"), (policy_batch.legal_masks, "policy_legal_masks"),
