@@ -283,7 +283,7 @@ def finish_gpu_arm(args, rank, world, layout, ms_step, value, clocks, e2e, distr
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": dict(workload_config(), nodes_per_gpu=int(layout.rows),
                            mean_nodes_per_subgame=layout.rows / BATCH),
-            "clocks": clocks, "gpu_launches": args.steps,
+            "clocks": clocks, "gpu_launches": 2 * args.steps,  # per step: record check + solver kernel
             "e2e": e2e,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": traffic, "peak_source": peak_kind,

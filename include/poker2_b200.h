@@ -82,7 +82,13 @@ int p2b_showdown_values(const unsigned char* tables, const int32_t* table_of_row
  *             mix_old, mix_new, fl(mix_old+mix_new); int32 do_mix}
  *  init_depth depth of the deepest tree of the batch (the upstream start pass re-normalises
  *             every belief row once per level of the batch-wide tree)
- *  work_counter one int32 (zeroed by the call)
+ *  work_counter two int32, zeroed by the call: [0] the queue the thread blocks take subgames
+ *             from; [1] status.  Before solving, a checking kernel compares every subgame's
+ *             records with the solver's limits (1..160 nodes per subgame, 1..6 children per
+ *             internal node, children stored after their parent and inside the subgame,
+ *             internal_idx < max_internal, root internal, a table for every showdown leaf).
+ *             On a violation status = 1 + the index of an offending subgame and NOTHING is
+ *             solved (outputs untouched); otherwise status stays 0
  *  num_blocks 0 = one block per SM
  *  sample_pass [num_subgames] int32 (may be NULL), policy_sample [rows,1344] out (may be NULL):
  *             the current policy of pass sample_pass[s] is kept for subgame s -- the

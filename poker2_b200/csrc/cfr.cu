@@ -1171,12 +1171,41 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
     }
 }
 
+// Checks every subgame's records against the solver kernel's limits before it runs: a
+// malformed tree would make it index shared memory out of range.  One block per subgame, one
+// thread per node.  On a violation the status word (work_counter[1]) receives 1 + the
+// subgame index and the subgame queue (work_counter[0]) is set past its end, so that the
+// solver kernel launched next on the stream finds no work at all.
+__global__ void __launch_bounds__(kCfrMaxNodes) cfr_validate_kernel(const CfrParams p) {
+    const int s = blockIdx.x, i = threadIdx.x;
+    const SubgameRec sg = p.subgames[s];
+    int bad = sg.n_nodes < 1 || sg.n_nodes > kCfrMaxNodes || sg.n_internal > p.max_internal || sg.node_begin < 0;
+    if (!bad && i < sg.n_nodes) {
+        const NodeRec nd = p.nodes[sg.node_begin + i];
+        if (nd.kind > kModelLeaf || (nd.kind == kShowdownLeaf && (sg.table_index < 0 || p.tables == nullptr))) bad = 1;
+        if (i == 0 && nd.kind != kInternal) bad = 1;
+        if (nd.kind == kInternal &&
+            (nd.n_children < 1 || nd.n_children > kCfrMaxChildren || nd.first_child <= i ||
+             nd.first_child + nd.n_children > sg.n_nodes || nd.internal_idx >= p.max_internal))
+            bad = 1;
+    }
+    if (__syncthreads_or(bad) && i == 0) {
+        atomicMax(p.work_counter + 1, s + 1);
+        atomicMax(p.work_counter, p.num_subgames);
+    }
+}
+
 template <int VPT, int MAXC>
 int launch_variant(const CfrParams& p, int num_blocks, cudaStream_t stream) {
     int rc = check_cuda(cudaFuncSetAttribute(cfr_solve_kernel<VPT, MAXC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              kCfrSmem),
                         "cfr_solve_kernel shared-memory attribute");
     if (rc) return rc;
+    if (!p.stepped || (p.pass_begin < 0 && (p.phases & 1))) {  // a stepped solve is checked at its first step
+        cfr_validate_kernel<<<p.num_subgames, kCfrMaxNodes, 0, stream>>>(p);
+        rc = check_cuda(cudaGetLastError(), "cfr_validate_kernel");
+        if (rc) return rc;
+    }
     cfr_solve_kernel<VPT, MAXC><<<num_blocks, CfrThreads<VPT>::value, kCfrSmem, stream>>>(p);
     return check_cuda(cudaGetLastError(), "cfr_solve_kernel");
 }
@@ -1200,7 +1229,7 @@ int launch_cfr_solve(const CfrParams& params, int num_blocks, int max_children, 
     if (rc) return rc;
     CfrParams p = params;
     p.combos = device_combo_table();
-    rc = check_cuda(cudaMemsetAsync(p.work_counter, 0, sizeof(int32_t), stream), "cudaMemsetAsync(work counter)");
+    rc = check_cuda(cudaMemsetAsync(p.work_counter, 0, 2 * sizeof(int32_t), stream), "cudaMemsetAsync(work counter)");
     if (rc) return rc;
     return dispatch_cfr(p, num_blocks, max_children, stream);
 }
@@ -1273,7 +1302,7 @@ int launch_cfr_solve_static(const CfrParams& params, int max_children, cudaStrea
     p.work_counter = sp.counter;
     // the queue counter must start at zero; the work rows need no clearing (every row is
     // written before it is read within a solve)
-    rc = check_cuda(cudaMemsetAsync(sp.counter, 0, sizeof(int32_t), stream), "cudaMemsetAsync(static counter)");
+    rc = check_cuda(cudaMemsetAsync(sp.counter, 0, 2 * sizeof(int32_t), stream), "cudaMemsetAsync(static counter)");
     if (rc) return rc;
     return dispatch_cfr(p, (int)blocks, max_children, stream);
 }

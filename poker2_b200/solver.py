@@ -245,6 +245,11 @@ class SubgameSolver:
                            self.root_values, self.values_avg, self.beliefs_avg, self.exploitability, self.br_values,
                            self.policy_sample, self.beliefs_last)
 
+    def status(self) -> int:
+        """0, or 1 + the index of a subgame whose records exceed the kernel's limits, in which
+        case the last solve did nothing.  Reads one word from the device (synchronises)."""
+        return int(self.work_counter[1].item())
+
     def release(self) -> None:
         """Drops the device buffers (they return to the caching allocator)."""
         for name in ("regrets", "policy_avg", "weight_sums", "policy", "root_values", "values_avg", "beliefs_avg",

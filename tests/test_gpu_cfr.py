@@ -157,3 +157,27 @@ def test_sampling_policy_and_last_beliefs_match_upstream(cuda_device, golden_dir
     want_b = torch.from_numpy(z["beliefs_last"])[keep]
     _report("beliefs_last", got_b, want_b)
     torch.testing.assert_close(got_b, want_b, rtol=RTOL, atol=ATOL)
+
+
+def test_malformed_subgame_is_reported_and_nothing_runs(cuda_device, golden_dir):
+    """A node record beyond the kernel's limits must not be followed: the checking kernel names
+    the subgame in the status word and the solver finds an empty queue."""
+    from poker2_b200 import solver
+
+    z = np.load(os.path.join(golden_dir, "cfr_batch_cap2_t24.npz"))
+    clean, trees = _solve_golden(z, cuda_device)
+    boards = torch.from_numpy(z["boards"].astype(np.int64))
+    layout = solver.device_layout(trees, z["boards"].astype(np.int64))
+    victim = 2
+    first = int(layout.subgames[victim]["node_begin"])
+    layout.nodes[first]["n_children"] = 9  # the root of subgame 2 claims nine children
+    sv = solver.SubgameSolver(layout, boards, cuda_device)
+    rb = solver.pad_rows(torch.from_numpy(z["ranges"]).to(cuda_device)).contiguous()
+    sv.root_values.fill_(-7.0)
+    res = sv.solve(rb, solver.iteration_scalars(int(z["iterations"])))
+    assert sv.status() == victim + 1
+    assert bool((res.root_values == -7.0).all())  # nothing was solved
+    # a well-formed batch reports nothing and is solved
+    ok = solver.SubgameSolver(clean.layout, boards, cuda_device)
+    res2 = ok.solve(rb, solver.iteration_scalars(int(z["iterations"])))
+    assert ok.status() == 0 and torch.equal(res2.root_values, clean.root_values)
