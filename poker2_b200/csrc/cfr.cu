@@ -328,7 +328,8 @@ __device__ __forceinline__ void node_tables(Block& B, int cs_row0, int n_cs, con
                 if (k0 + i < P2B_NUM_HANDS) pref[k0 + i + 1] = (float)run;
             }
         } else if (unit < n_scan + n_cs) {
-            // total mass of a row, on several independent accumulators
+            // total mass of a row, on several independent accumulators (the 18 padding entries
+            // of a staged row are zero, so all 1344 are added)
             const int wt = unit - n_scan;
             const float* __restrict__ x = B.stage_row(cs_row0 + wt);
             double acc[6] = {0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
@@ -336,10 +337,7 @@ __device__ __forceinline__ void node_tables(Block& B, int cs_row0, int n_cs, con
             for (int b = 0; b < 7; ++b) {
                 float v[6];
 #pragma unroll
-                for (int i = 0; i < 6; ++i) {
-                    const int h = lane + 32 * (6 * b + i);
-                    v[i] = h < P2B_NUM_HANDS ? x[h] : 0.0f;
-                }
+                for (int i = 0; i < 6; ++i) v[i] = x[lane + 32 * (6 * b + i)];
 #pragma unroll
                 for (int i = 0; i < 6; ++i) acc[i] += (double)v[i];
             }
@@ -381,12 +379,13 @@ __device__ __forceinline__ void node_tables(Block& B, int cs_row0, int n_cs, con
                     double acc = q == 0 ? 0.0 : (q == 1 ? t0 : (q == 2 ? t0 + t1 : (t0 + t1) + t2));
                     float* __restrict__ row = B.pc + slot * 52 * 52 + c * 52;
                     if (q == 0) row[0] = 0.0f;
+                    float* __restrict__ out = row + 13 * q + 1;
 #pragma unroll
-                    for (int i = 0; i < 13; ++i)
-                        if (13 * q + i < 51) {
-                            acc += (double)v[i];
-                            row[13 * q + i + 1] = (float)acc;
-                        }
+                    for (int i = 0; i < 12; ++i) {
+                        acc += (double)v[i];
+                        out[i] = (float)acc;
+                    }
+                    if (q < 3) out[12] = (float)(acc + (double)v[12]);
                 }
             }
         }
