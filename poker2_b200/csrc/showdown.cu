@@ -358,20 +358,19 @@ constexpr int kEvalThreads = 448;
 constexpr int kEvalWarps = kEvalThreads / 32;
 constexpr int kQuarter = 352;  // sorted positions per quarter scan: 32 lanes x 11
 constexpr int kEvX = kTabBytes;                         // float [2*1326 (+pad)]
-constexpr int kEvP = kEvX + 2 * P2B_HPAD * 4;           // float [2][HPAD]
+constexpr int kEvStage = kTabBytes + 2 * P2B_HPAD * 4;  // one staging buffer: table blob + both ranges
+constexpr int kEvP = 2 * kEvStage;                      // float [2][HPAD]   (two staging buffers come first)
 constexpr int kEvPC = kEvP + 2 * P2B_HPAD * 4;          // float [2][52*52]
 constexpr int kEvQ = kEvPC + 2 * 52 * 52 * 4;           // double [8]
 constexpr int kEvCombo = kEvQ + 64;                     // uint8 [2][1326 (+pad)]
 constexpr int kEvalSmem = kEvCombo + 2 * 1328;
 static_assert(kEvQ % 8 == 0, "alignment");
 
-__global__ void __launch_bounds__(kEvalThreads, 3) showdown_eval_kernel(
+__global__ void __launch_bounds__(kEvalThreads, 2) showdown_eval_kernel(
     const unsigned char* __restrict__ tabs, const int32_t* __restrict__ tab_of_row, const ComboTable* __restrict__ combos,
     const float* __restrict__ beliefs, int64_t belief_row_stride, const long long* __restrict__ potential,
     const float* __restrict__ scale, float* __restrict__ values, int64_t value_row_stride, int64_t rows) {
     extern __shared__ __align__(16) unsigned char smem[];
-    unsigned char* tab_s = smem;
-    float* x = reinterpret_cast<float*>(smem + kEvX);   // x[p*1326 + h] = range of player p
     float* P = reinterpret_cast<float*>(smem + kEvP);   // P[p*HPAD + k] = prefix of player p's range, strength order
     float* PC = reinterpret_cast<float*>(smem + kEvPC);
     double* qtot = reinterpret_cast<double*>(smem + kEvQ);
@@ -384,18 +383,41 @@ __global__ void __launch_bounds__(kEvalThreads, 3) showdown_eval_kernel(
     }
     const bool vec_in = ((reinterpret_cast<uintptr_t>(beliefs) | (uintptr_t)(belief_row_stride * 4)) & 15) == 0;
 
-    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
-        const int64_t t = tab_of_row ? tab_of_row[row] : row;
-        const uint4* src = reinterpret_cast<const uint4*>(tabs + t * (int64_t)kTabBytes);
-        for (int i = tid; i < kTabBytes / 16; i += kEvalThreads) reinterpret_cast<uint4*>(tab_s)[i] = src[i];
-        const float* brow = beliefs + row * belief_row_stride;
-        if (vec_in) {
-            const float4* b4 = reinterpret_cast<const float4*>(brow);
-            for (int i = tid; i < 2 * P2B_NUM_HANDS / 4; i += kEvalThreads) reinterpret_cast<float4*>(x)[i] = __ldcs(b4 + i);
-        } else {
-            for (int i = tid; i < 2 * P2B_NUM_HANDS; i += kEvalThreads) x[i] = __ldcs(brow + i);
+    // The table blob and the two ranges of a row are copied into one of two staging buffers
+    // asynchronously, one row ahead of the row being evaluated.
+    auto stage_row = [&](int64_t row, int buf) {
+        if (row < rows) {
+            unsigned char* dst = smem + buf * kEvStage;
+            const int64_t t = tab_of_row ? tab_of_row[row] : row;
+            const unsigned char* src = tabs + t * (int64_t)kTabBytes;
+            for (int i = tid; i < kTabBytes / 16; i += kEvalThreads) {
+                const unsigned d = (unsigned)__cvta_generic_to_shared(dst + 16 * i);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src + 16 * i) : "memory");
+            }
+            const float* brow = beliefs + row * belief_row_stride;
+            float* xd = reinterpret_cast<float*>(dst + kEvX);
+            if (vec_in) {
+                for (int i = tid; i < 2 * P2B_NUM_HANDS / 4; i += kEvalThreads) {
+                    const unsigned d = (unsigned)__cvta_generic_to_shared(xd + 4 * i);
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(brow + 4 * i) : "memory");
+                }
+            } else {
+                for (int i = tid; i < 2 * P2B_NUM_HANDS; i += kEvalThreads) {
+                    const unsigned d = (unsigned)__cvta_generic_to_shared(xd + i);
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(brow + i) : "memory");
+                }
+            }
         }
-        __syncthreads();
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    int buf = 0;
+    stage_row(blockIdx.x, 0);
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, buf ^= 1) {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();  // every thread's share of this row has landed; the other buffer is free
+        stage_row(row + gridDim.x, buf ^ 1);
+        unsigned char* tab_s = smem + buf * kEvStage;
+        float* x = reinterpret_cast<float*>(tab_s + kEvX);  // x[p*1326 + h] = range of player p
         const BoardTabView tv = view_tables(tab_s);
 
         // ---- A. per-card prefix lists (threads 0..415: player, card, quarter of the list) ----
@@ -489,8 +511,8 @@ __global__ void __launch_bounds__(kEvalThreads, 3) showdown_eval_kernel(
                                               PC + opp * 52 * 52);
             __stcs(vrow + i, div_exact(__fmul_rn(ev, hero ? pot1 : pot0), dscale));
         }
-        __syncthreads();
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
 int sm_count();
@@ -518,7 +540,7 @@ int launch_showdown_eval(const unsigned char* tabs, const int32_t* tab_of_row, c
                     "showdown_eval_kernel smem attribute");
     if (rc) return rc;
     int64_t grid = rows;
-    const int64_t cap = (int64_t)sm_count() * 3;
+    const int64_t cap = (int64_t)sm_count() * 2;
     if (grid > cap) grid = cap;
     showdown_eval_kernel<<<(unsigned)grid, kEvalThreads, kEvalSmem, stream>>>(
         tabs, tab_of_row, device_combo_table(), beliefs, belief_row_stride, potential, scale, values, value_row_stride,
