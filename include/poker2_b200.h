@@ -239,6 +239,21 @@ int p2b_step_deep_beliefs(float* out, const float* root_beliefs, const float* re
 int p2b_chance_expand(const float* pre_beliefs, const int64_t* boards, int32_t board_len, const int64_t* sample_offsets,
                       int64_t num_roots, int64_t num_samples, float* post_beliefs, int64_t* root_lookup,
                       int64_t* board_samples, void* stream);
+/* Fused forms for a bf16 value network (same arithmetic as the two calls around them, no
+ * fp32 copy of the expanded beliefs).  p2b_chance_expand_features writes the network's input
+ * rows: features [num_samples, feature_stride] bf16 = both players' post-card beliefs (2 x 1326),
+ * the 52-d one-hot of the extended board, the root's 3 context scalars (context [num_roots,3]
+ * fp32), zeros up to feature_stride (>= 2707).  The two belief rows of a root are player_stride
+ * floats apart (1326 packed, 1344 for the solver's padded rows).  root_lookup may be NULL.
+ * p2b_indexed_mean_bf16: out[r, p, h] = mean over the samples sample_offsets[r]..[r+1] of
+ * src[sample, p*1326 + h] (bf16 rows src_stride apart), fp32, ascending sample order; the two
+ * output rows of a root are out_player_stride floats apart. */
+int p2b_chance_expand_features(const float* pre_beliefs, int64_t player_stride, const int64_t* boards,
+                               int32_t board_len, const int64_t* sample_offsets, int64_t num_roots,
+                               int64_t num_samples, const float* context, void* features_bf16,
+                               int64_t feature_stride, int64_t* root_lookup, void* stream);
+int p2b_indexed_mean_bf16(const void* src_bf16, int64_t src_stride, const int64_t* sample_offsets,
+                          int64_t num_roots, float* out, int64_t out_player_stride, void* stream);
 /* p2b_indexed_add_rows: out[index[i], :] (+)= src[i, :] in ascending i, for a sorted int64
  * index (the index_add_ of :468-475); mean != 0 divides by max(count,1) (:476-477);
  * accumulate == 0 overwrites out instead of adding to it. */

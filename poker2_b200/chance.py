@@ -66,3 +66,43 @@ def single_card_chance_values(pre_beliefs: torch.Tensor, boards: torch.Tensor,
     values = value_fn(post, samples, lookup).to(torch.float32).contiguous()
     out = torch.empty(pre_beliefs.shape[0], 2, NUM_HANDS, device=pre_beliefs.device, dtype=torch.float32)
     return indexed_add_rows(out, lookup, values, mean=True, accumulate=False)
+
+
+def sample_offsets_of(boards: torch.Tensor) -> torch.Tensor:
+    """[B+1] int64 exclusive prefix of the number of cards not on each board."""
+    free = 52 - (boards >= 0).sum(dim=1)
+    offsets = torch.zeros(boards.shape[0] + 1, dtype=torch.int64, device=boards.device)
+    offsets[1:] = torch.cumsum(free, dim=0)
+    return offsets
+
+
+def expand_features_bf16(pre_beliefs: torch.Tensor, boards: torch.Tensor, offsets: torch.Tensor, num_samples: int,
+                         context: torch.Tensor, feature_stride: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Network input rows [S, feature_stride] bf16 for every (root, next card) sample: the fused
+    form of `expand_next_card` + cast + board one-hot + context.  pre_beliefs [B,2,W] fp32 with
+    W = 1326 or the padded 1344 (any last-dimension stride of 1)."""
+    _lib.require_cuda(pre_beliefs, "expand_features_bf16")
+    B = pre_beliefs.shape[0]
+    assert pre_beliefs.dtype == torch.float32 and pre_beliefs.stride(2) == 1 and pre_beliefs.stride(0) == 2 * pre_beliefs.stride(1)
+    assert boards.dtype == torch.int64 and boards.is_contiguous() and boards.shape[0] == B
+    assert context.dtype == torch.float32 and context.is_contiguous() and tuple(context.shape) == (B, 3)
+    if out is None:
+        out = torch.empty(num_samples, feature_stride, device=pre_beliefs.device, dtype=torch.bfloat16)
+    assert out.dtype == torch.bfloat16 and out.is_contiguous() and tuple(out.shape) == (num_samples, feature_stride)
+    with torch.cuda.device(pre_beliefs.device):
+        _lib.call("p2b_chance_expand_features", _lib.ptr(pre_beliefs), pre_beliefs.stride(1), _lib.ptr(boards),
+                  boards.shape[1], _lib.ptr(offsets), B, num_samples, _lib.ptr(context), _lib.ptr(out), feature_stride,
+                  None, _lib.stream_ptr(pre_beliefs.device))
+    return out
+
+
+def indexed_mean_bf16(src: torch.Tensor, offsets: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[r, p, :1326] = fp32 mean over the samples offsets[r]..offsets[r+1] of src[sample, p*1326:(p+1)*1326]
+    (bf16 rows); out is [B,2,W] fp32 with W >= 1326."""
+    _lib.require_cuda(src, "indexed_mean_bf16")
+    assert src.dtype == torch.bfloat16 and src.stride(1) == 1 and out.dtype == torch.float32
+    assert out.stride(2) == 1 and out.stride(0) == 2 * out.stride(1)
+    with torch.cuda.device(src.device):
+        _lib.call("p2b_indexed_mean_bf16", _lib.ptr(src), src.stride(0), _lib.ptr(offsets), out.shape[0], _lib.ptr(out),
+                  out.stride(1), _lib.stream_ptr(src.device))
+    return out

@@ -3,6 +3,8 @@
 // (p2/search/chance_node_helper.py:359-479, `single_card_chance_values`).
 #include "common.cuh"
 
+#include <cuda_bf16.h>
+
 namespace p2b {
 namespace {
 
@@ -126,6 +128,124 @@ __global__ void indexed_add_rows_kernel(float* __restrict__ out, const long long
     }
 }
 
+// Fused form of the expansion for a bf16 value network: one block per (root, next card)
+// sample writes the network's input row directly -- both players' re-blocked, re-normalised
+// beliefs (the arithmetic of chance_expand_kernel, then rounded to bf16), the one-hot of the
+// extended board, the root's three context scalars and zero padding up to `feature_stride`
+// -- so that no fp32 copy of the expanded beliefs ever exists.  The two belief rows of a root
+// are `player_stride` floats apart (1326 for packed rows, 1344 for the solver's padded rows).
+constexpr int kHandsPerThread = (P2B_NUM_HANDS + kThreads - 1) / kThreads;  // 6
+
+__global__ void chance_expand_features_kernel(const float* __restrict__ pre_beliefs, long long player_stride,
+                                              const long long* __restrict__ boards, int board_len,
+                                              const long long* __restrict__ sample_offsets, long long num_roots,
+                                              const float* __restrict__ context, const ComboTable* __restrict__ combos,
+                                              __nv_bfloat16* __restrict__ features, long long feature_stride,
+                                              long long* __restrict__ root_lookup) {
+    __shared__ double red[kThreads / 32];
+    __shared__ int cnt[kThreads / 32];
+    __shared__ int s_root;
+    __shared__ unsigned long long s_mask;
+    const long long total = sample_offsets[num_roots];
+    for (long long smp = blockIdx.x; smp < total; smp += gridDim.x) {
+        if (threadIdx.x == 0) {
+            long long lo = 0, hi = num_roots - 1;
+            while (lo < hi) {
+                const long long mid = (lo + hi + 1) >> 1;
+                if (sample_offsets[mid] <= smp) lo = mid;
+                else hi = mid - 1;
+            }
+            unsigned long long mask = 0;
+            for (int j = 0; j < board_len; ++j) {
+                const long long c = boards[lo * board_len + j];
+                if (c >= 0) mask |= 1ull << c;
+            }
+            int k = (int)(smp - sample_offsets[lo]), card = 0;
+            for (;; ++card)
+                if (!((mask >> card) & 1ull) && k-- == 0) break;
+            s_root = (int)lo;
+            s_mask = mask | (1ull << card);
+            if (root_lookup) root_lookup[smp] = lo;
+        }
+        __syncthreads();
+        const unsigned long long mask = s_mask;
+        const long long b = s_root;
+        __nv_bfloat16* row = features + smp * feature_stride;
+        for (int p = 0; p < 2; ++p) {
+            const float* src = pre_beliefs + (b * 2 + p) * player_stride;
+            float v[kHandsPerThread];
+            bool ok[kHandsPerThread];
+            double s = 0.0;
+            int n_allowed = 0;
+#pragma unroll
+            for (int i = 0; i < kHandsPerThread; ++i) {
+                const int h = threadIdx.x + i * kThreads;
+                ok[i] = false;
+                v[i] = 0.0f;
+                if (h < P2B_NUM_HANDS) {
+                    ok[i] = (((mask >> combos->c1[h]) | (mask >> combos->c2[h])) & 1ull) == 0;
+                    v[i] = ok[i] ? src[h] : 0.0f;
+                    s += (double)v[i];
+                    n_allowed += ok[i];
+                }
+            }
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) {
+                s += __shfl_xor_sync(0xffffffffu, s, d);
+                n_allowed += __shfl_xor_sync(0xffffffffu, n_allowed, d);
+            }
+            __syncthreads();
+            if ((threadIdx.x & 31) == 0) {
+                red[threadIdx.x >> 5] = s;
+                cnt[threadIdx.x >> 5] = n_allowed;
+            }
+            __syncthreads();
+            double tot = 0.0;
+            int nall = 0;
+            for (int w = 0; w < kThreads / 32; ++w) {
+                tot += red[w];
+                nall += cnt[w];
+            }
+            const float sum = (float)tot;
+            const float uni = __fdiv_rn(1.0f, fmaxf((float)nall, 1.0f));
+#pragma unroll
+            for (int i = 0; i < kHandsPerThread; ++i) {
+                const int h = threadIdx.x + i * kThreads;
+                if (h < P2B_NUM_HANDS) {
+                    const float x = sum > 1e-12f ? __fdiv_rn(v[i], fmaxf(sum, 1e-12f)) : (ok[i] ? uni : 0.0f);
+                    row[p * P2B_NUM_HANDS + h] = __float2bfloat16_rn(x);
+                }
+            }
+        }
+        // board one-hot, context, padding
+        for (long long j = 2 * P2B_NUM_HANDS + threadIdx.x; j < feature_stride; j += kThreads) {
+            const int r = (int)(j - 2 * P2B_NUM_HANDS);
+            float x = 0.0f;
+            if (r < 52) x = ((mask >> r) & 1ull) ? 1.0f : 0.0f;
+            else if (r < 55) x = context[b * 3 + (r - 52)];
+            row[j] = __float2bfloat16_rn(x);
+        }
+        __syncthreads();
+    }
+}
+
+// out[r, p, h] = mean over the samples of root r (rows sample_offsets[r] .. sample_offsets[r+1])
+// of src[sample, p*1326 + h], bf16 -> fp32, added in ascending sample order and divided by
+// max(count, 1) (chance_node_helper.py:462-477).  Each output element is owned by one thread.
+__global__ void indexed_mean_bf16_kernel(const __nv_bfloat16* __restrict__ src, long long src_stride,
+                                         const long long* __restrict__ sample_offsets, long long num_roots,
+                                         float* __restrict__ out, long long out_player_stride) {
+    const long long n = num_roots * 2 * P2B_NUM_HANDS;
+    for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < n; e += (long long)gridDim.x * blockDim.x) {
+        const long long r = e / (2 * P2B_NUM_HANDS);
+        const int c = (int)(e - r * 2 * P2B_NUM_HANDS), p = c >= P2B_NUM_HANDS, h = c - p * P2B_NUM_HANDS;
+        const long long a = sample_offsets[r], b = sample_offsets[r + 1];
+        float acc = 0.0f;
+        for (long long i = a; i < b; ++i) acc = __fadd_rn(acc, __bfloat162float(src[i * src_stride + c]));
+        out[(r * 2 + p) * out_player_stride + h] = __fdiv_rn(acc, fmaxf((float)(b - a), 1.0f));
+    }
+}
+
 }  // namespace
 
 int sm_count();
@@ -150,6 +270,40 @@ int p2b_chance_expand(const float* pre_beliefs, const int64_t* boards, int32_t b
         pre_beliefs, (const long long*)boards, board_len, (const long long*)sample_offsets, num_roots,
         device_combo_table(), post_beliefs, (long long*)root_lookup, (long long*)board_samples);
     return check_cuda(cudaGetLastError(), "chance_expand_kernel");
+}
+
+int p2b_chance_expand_features(const float* pre_beliefs, int64_t player_stride, const int64_t* boards, int32_t board_len,
+                               const int64_t* sample_offsets, int64_t num_roots, int64_t num_samples,
+                               const float* context, void* features_bf16, int64_t feature_stride, int64_t* root_lookup,
+                               void* stream) {
+    if (num_roots <= 0 || num_samples <= 0) return P2B_OK;
+    if (!pre_beliefs || !boards || !sample_offsets || !context || !features_bf16)
+        return set_error(P2B_ERR_ARG, "p2b_chance_expand_features: null pointer");
+    if (player_stride < P2B_NUM_HANDS || feature_stride < 2 * P2B_NUM_HANDS + 55)
+        return set_error(P2B_ERR_ARG, "p2b_chance_expand_features: stride too small");
+    int rc = ensure_tables();
+    if (rc) return rc;
+    long long grid = num_samples;
+    if (grid > (long long)sm_count() * 16) grid = (long long)sm_count() * 16;
+    chance_expand_features_kernel<<<(unsigned)grid, kThreads, 0, (cudaStream_t)stream>>>(
+        pre_beliefs, player_stride, (const long long*)boards, board_len, (const long long*)sample_offsets, num_roots,
+        context, device_combo_table(), static_cast<__nv_bfloat16*>(features_bf16), feature_stride,
+        (long long*)root_lookup);
+    return check_cuda(cudaGetLastError(), "chance_expand_features_kernel");
+}
+
+int p2b_indexed_mean_bf16(const void* src_bf16, int64_t src_stride, const int64_t* sample_offsets, int64_t num_roots,
+                          float* out, int64_t out_player_stride, void* stream) {
+    if (num_roots <= 0) return P2B_OK;
+    if (!src_bf16 || !sample_offsets || !out) return set_error(P2B_ERR_ARG, "p2b_indexed_mean_bf16: null pointer");
+    if (src_stride < 2 * P2B_NUM_HANDS || out_player_stride < P2B_NUM_HANDS)
+        return set_error(P2B_ERR_ARG, "p2b_indexed_mean_bf16: stride too small");
+    long long blocks = (num_roots * 2 * P2B_NUM_HANDS + kThreads - 1) / kThreads;
+    if (blocks > (long long)sm_count() * 16) blocks = (long long)sm_count() * 16;
+    indexed_mean_bf16_kernel<<<(unsigned)blocks, kThreads, 0, (cudaStream_t)stream>>>(
+        static_cast<const __nv_bfloat16*>(src_bf16), src_stride, (const long long*)sample_offsets, num_roots, out,
+        out_player_stride);
+    return check_cuda(cudaGetLastError(), "indexed_mean_bf16_kernel");
 }
 
 int p2b_indexed_add_rows(float* out, const int64_t* index, const float* src, int64_t num_src, int64_t num_out,

@@ -87,8 +87,29 @@ class ChanceLeafEvaluator:
         self.chunk = int(chunk)
         self.samples_per_call = int((52 - (self.boards >= 0).sum(dim=1)).sum().item())
         self.calls = 0
+        # a bf16 `ValueMLP` takes the fused path: the network input is written directly by the
+        # expansion kernel and its bf16 output is averaged per leaf without an fp32 copy
+        self.fused = isinstance(model, ValueMLP) and model.dtype == torch.bfloat16
+        self._chunks = []
+        for a in range(0, self.boards.shape[0], self.chunk):
+            b = min(a + self.chunk, self.boards.shape[0])
+            off = chance.sample_offsets_of(self.boards[a:b])
+            self._chunks.append((a, b, off, int(off[-1].item())))
+
+    def _call_fused(self, leaf_beliefs: torch.Tensor) -> torch.Tensor:
+        L, W = leaf_beliefs.shape[0], leaf_beliefs.shape[2]
+        out = torch.zeros(L, 2, W, device=leaf_beliefs.device, dtype=torch.float32)
+        for a, b, off, n_samples in self._chunks:
+            x = chance.expand_features_bf16(leaf_beliefs[a:b], self.boards[a:b], off, n_samples, self.context[a:b],
+                                            self.model.IN_PADDED)
+            y = self.model.net(x)
+            chance.indexed_mean_bf16(y, off, out[a:b])
+        self.calls += 1
+        return out
 
     def __call__(self, leaf_beliefs: torch.Tensor) -> torch.Tensor:
+        if self.fused:
+            return self._call_fused(leaf_beliefs)
         L = leaf_beliefs.shape[0]
         out = torch.empty(L, 2, NUM_HANDS, device=leaf_beliefs.device, dtype=torch.float32)
         for a in range(0, L, self.chunk):

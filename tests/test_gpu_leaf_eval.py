@@ -52,3 +52,29 @@ def test_turn_subgames_with_chance_averaged_mlp_leaves(cuda_device):
     # iterations amplify the difference: 1e-3 relative after 6 iterations
     torch.testing.assert_close(got_val, o.values_avg[:n], rtol=1e-3, atol=1e-5)
     torch.testing.assert_close(got_pol, o.policy_avg[n:], rtol=1e-3, atol=1e-4)
+
+
+def test_fused_bf16_leaf_pipeline_equals_generic_path(cuda_device):
+    """The fused expansion (network input rows written directly in bf16) and the bf16 mean give
+    the bits of expand_next_card -> cast -> network -> cast -> indexed mean."""
+    from poker2_b200 import leaf_eval
+
+    g = torch.Generator().manual_seed(5)
+    L = 37
+    boards = torch.full((L, 5), -1, dtype=torch.int64)
+    for i in range(L):
+        boards[i, :4] = torch.randperm(52, generator=g)[:4]
+    bel = torch.zeros(L, 2, 1344)
+    bel[..., :1326] = torch.empty(L, 2, 1326).exponential_(generator=g)
+    bel[3, 1] = 0  # an empty range: uniform fallback over the allowed combos
+    bel = (bel / bel.sum(-1, keepdim=True).clamp(min=1e-30)).to(cuda_device)
+    ctx = torch.rand(L, 3, generator=g)
+    model = leaf_eval.ValueMLP(width=128, depth=2, dtype=torch.bfloat16, seed=1).to(cuda_device)
+    fused = leaf_eval.ChanceLeafEvaluator(model, boards, ctx, cuda_device, chunk=16)
+    assert fused.fused
+    generic = leaf_eval.ChanceLeafEvaluator(model, boards, ctx, cuda_device, chunk=16)
+    generic.fused = False
+    a = fused(bel)
+    b = generic(bel)
+    assert a.shape == (L, 2, 1344) and b.shape == (L, 2, 1326)
+    assert torch.equal(a[..., :1326], b)
