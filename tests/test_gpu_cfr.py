@@ -181,3 +181,27 @@ def test_malformed_subgame_is_reported_and_nothing_runs(cuda_device, golden_dir)
     ok = solver.SubgameSolver(clean.layout, boards, cuda_device)
     res2 = ok.solve(rb, solver.iteration_scalars(int(z["iterations"])))
     assert ok.status() == 0 and torch.equal(res2.root_values, clean.root_values)
+
+
+def test_depth_limited_tree_and_empty_inputs(cuda_device, golden_dir):
+    """A tree cut at depth 2 has non-terminal leaves; without a leaf model they are worth zero,
+    in the kernel as in the oracle.  Empty batches are accepted everywhere."""
+    from oracle import cfr as ocfr
+    from poker2_b200 import rules, showdown, solver, tree as ptree
+
+    z = np.load(os.path.join(golden_dir, "cfr_batch_cap2_t24.npz"))
+    boards, ranges = z["boards"].astype(np.int64), torch.from_numpy(z["ranges"])
+    res, trees = solver.solve_subgames(boards, ranges, z["pot"], z["stack"], iterations=5, max_depth=2,
+                                       device=cuda_device)
+    assert res.layout.num_model_leaves > 0
+    o = ocfr.SubgameOracle(trees.oracle_dict(boards), ranges, iterations=5).solve()
+    n = trees.num_roots
+    torch.testing.assert_close(res.level_major(res.policy_avg).cpu()[n:], o.policy_avg[n:], rtol=RTOL, atol=ATOL)
+    torch.testing.assert_close(res.root_values[..., :1326].cpu(), o.values_avg[:n], rtol=RTOL, atol=ATOL)
+    # empty inputs
+    assert rules.rank_7_cards_single_batch(torch.zeros(0, 7, dtype=torch.int16, device=cuda_device)).shape == (0,)
+    tabs = showdown.BoardTables(torch.from_numpy(boards).to(cuda_device))
+    empty = showdown.showdown_values(tabs, torch.zeros(0, 2, 1326, device=cuda_device),
+                                     torch.zeros(0, 2, dtype=torch.int64), torch.zeros(0),
+                                     table_of_row=torch.zeros(0, dtype=torch.int32))
+    assert empty.shape == (0, 2, 1326)

@@ -122,3 +122,20 @@ def test_sample_leaves_matches_upstream(golden_dir):
     assert torch.equal(bel, torch.from_numpy(z["sampled_beliefs"]))
     assert np.array_equal(t.state.pot[cont.numpy()], z["sampled_pot"])
     assert np.array_equal(t.state.stacks[cont.numpy()], z["sampled_stacks"])
+
+
+def test_layout_rejects_trees_beyond_the_kernel_limits():
+    """Host-side guard: subgames with more than 160 nodes are refused before any launch."""
+    from poker2_b200 import solver
+
+    roots = ptree.root_states(np.array([100]), np.array([4000]), min_raise=2)
+    big = ptree.build_trees(roots, [0.25, 0.5, 1.0], 10, bb=2)  # three bet sizes, no raise cap
+    assert big.total_nodes > solver.MAX_NODES
+    with pytest.raises(ValueError, match="nodes"):
+        solver.device_layout(big, np.array([[0, 1, 2, 3, 4]]))
+    small = ptree.build_trees(roots, [0.5, 1.0], 8, bb=2, max_raises=2)
+    layout = solver.device_layout(small, np.array([[0, 1, 2, 3, 4]]))
+    assert layout.rows == small.total_nodes and layout.num_model_leaves == 0
+    # one root, ragged batch of one: offsets and records are consistent
+    assert layout.subgames[0]["n_nodes"] == small.total_nodes
+    assert int(layout.nodes["kind"][0]) == ptree.KIND_INTERNAL
