@@ -134,7 +134,19 @@ int p2b_cfr_step(const void* subgames, const void* nodes, int32_t num_subgames, 
                  int32_t num_blocks, int32_t pass_begin, int32_t pass_end, int32_t phases,
                  float* carry_sums, float* carry_roots, const int32_t* leaf_begin, float* leaf_beliefs,
                  const float* leaf_values, const int32_t* sample_pass, float* policy_sample,
-                 float* beliefs_last, void* stream);
+                 float* beliefs_last, const float* start_policy, void* stream);
+
+/* Start policy and warm start (initialize_policy_and_beliefs with a policy head,
+ * src/p2/search/cfr_evaluator.py:830-886, and warm_start of type `model`, :887-926).
+ * start_policy [rows,1344] (last argument of p2b_cfr_step, may be NULL = uniform): the policy of
+ * the start pass, one row per non-root node.  p2b_cfr_warm_seed is called between the start
+ * pass (pass -1, both sweeps) and pass 0 of a stepped solve: per non-root row it sets
+ * regrets = start_policy * w and weight_sums = w (may be NULL) with w = weight * mean over the
+ * 1326 hands of max(regret, 0), the regrets being those the start pass left in `regrets`;
+ * weight = warm_start_iterations * warm_start_multiplier.  The caller's scalars array then
+ * starts at the warm-start iteration (see solver.SteppedSolver). */
+int p2b_cfr_warm_seed(const void* nodes, int64_t rows, const float* start_policy, float weight, float* regrets,
+                      float* weight_sums, void* stream);
 
 /* p2b_cfr_solve_noalloc -- the same solve without any allocation.  (No counterpart in the
  * upstream project: it exists for hosts of this library that cannot allocate.)

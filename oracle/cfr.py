@@ -32,7 +32,9 @@ H = cards.NUM_HANDS
 class SubgameOracle:
     def __init__(self, tree: dict, root_beliefs: torch.Tensor, *, iterations: int,
                  alpha: float = 1.5, beta: float = 0.0, gamma: float = 2.0,
-                 dcfr_delay: int = 0, cfr_type: str = "discounted", cfr_plus: bool = False, leaf_fn=None):
+                 dcfr_delay: int = 0, cfr_type: str = "discounted", cfr_plus: bool = False, leaf_fn=None,
+                 start_policy: torch.Tensor | None = None, warm_start_iterations: int = 0,
+                 warm_start_multiplier: float = 1.0):
         t = {k: (torch.from_numpy(np.ascontiguousarray(v)) if isinstance(v, np.ndarray) else v)
              for k, v in tree.items()}
         self.offs = [int(x) for x in tree["depth_offsets"]]
@@ -56,6 +58,11 @@ class SubgameOracle:
         self.cfr_plus = cfr_plus
         # leaves that are not terminal are valued by leaf_fn(beliefs[idx] [L,2,1326], idx) -> [L,2,1326]
         self.leaf_fn = leaf_fn
+        # start policy [M,1326] (the policy head's softmax upstream, :306-330; None = uniform) and the
+        # warm start of type `model` (:887-926): regrets seeded so that regret matching replays it
+        self.start_policy = start_policy
+        self.warm_start_iterations = warm_start_iterations
+        self.warm_start_multiplier = warm_start_multiplier
         self.model_idx = torch.where(self.leaf & ~self.done)[0]
         N, M = self.N, self.M
 
@@ -155,7 +162,7 @@ class SubgameOracle:
         self.policy.zero_()
         for d in range(self.depth):
             a, b, c = self.offs[d], self.offs[d + 1], self.offs[d + 2]
-            self.policy[b:c] = self.uniform[b:c]
+            self.policy[b:c] = self.uniform[b:c] if self.start_policy is None else self.start_policy[b:c]
             self.beliefs[b:c] = self._fan_out(self.beliefs, level=d)
             rows = torch.arange(b, c)
             self.beliefs[rows, self.prev_actor[b:c]] *= self.policy[b:c]
@@ -297,9 +304,25 @@ class SubgameOracle:
         self.set_leaf_values(beliefs=self.beliefs_avg)
         self.expected_values(self.policy_avg, self.beliefs_avg, self.values, self.values_avg)
 
+    def warm_start(self):
+        """Type `model` (cfr_evaluator.py:913-926): cumulative regrets = start policy x weight,
+        weight = iterations x multiplier x mean positive instantaneous regret of the row."""
+        N, ws = self.N, self.warm_start_iterations
+        weight = float(ws) * float(self.warm_start_multiplier)
+        regrets = self.instantaneous_regrets()
+        weights = weight * regrets[N:].clamp(min=0.0).mean(dim=-1)
+        self.regrets[N:] = self.policy[N:] * weights[:, None]
+        self.weight_sums[N:] = weights[:, None]
+        self.update_policy(ws)
+        self.set_leaf_values()
+        self.expected_values()
+        self.values_avg[:] = self.values
+
     def solve(self):
         self.initialize()
-        for t in range(self.iterations):
+        if self.warm_start_iterations > 0:
+            self.warm_start()
+        for t in range(self.warm_start_iterations, self.iterations):
             self.iteration(t)
         self.finalize()
         return self

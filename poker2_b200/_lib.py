@@ -32,7 +32,9 @@ _SIGNATURES = {
     "p2b_cfr_solve": [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64,
                       _vp, _i32, _i32, _i32, _vp, _i32, _vp, _vp, _vp, _vp],
     "p2b_cfr_step": [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64,
-                     _vp, _i32, _i32, _i32, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
+                     _vp, _i32, _i32, _i32, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                     _vp],
+    "p2b_cfr_warm_seed": [_vp, _i64, _vp, _f32, _vp, _vp, _vp],
     "p2b_cfr_solve_noalloc": [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                               _i32, _i32, _i32, _vp],
     "p2b_step_dcfr_update": [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _vp],

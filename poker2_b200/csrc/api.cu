@@ -137,8 +137,10 @@ int p2b_cfr_step(const void* subgames, const void* nodes, int32_t num_subgames, 
                  const void* scalars, int32_t iterations, int32_t cfr_plus, int32_t init_depth, int32_t* work_counter,
                  int32_t num_blocks, int32_t pass_begin, int32_t pass_end, int32_t phases, float* carry_sums,
                  float* carry_roots, const int32_t* leaf_begin, float* leaf_beliefs, const float* leaf_values,
-                 const int32_t* sample_pass, float* policy_sample, float* beliefs_last, void* stream) {
+                 const int32_t* sample_pass, float* policy_sample, float* beliefs_last, const float* start_policy,
+                 void* stream) {
     P2B_REQUIRE(num_subgames >= 0 && iterations >= 1, "bad count");
+    P2B_REQUIRE((reinterpret_cast<uintptr_t>(start_policy) & 15) == 0, "all row arrays must be 16-byte aligned");
     P2B_REQUIRE(!policy_sample || sample_pass, "policy_sample needs sample_pass");
     P2B_REQUIRE(((reinterpret_cast<uintptr_t>(policy_sample) | reinterpret_cast<uintptr_t>(beliefs_last)) & 15) == 0,
                 "all row arrays must be 16-byte aligned");
@@ -200,7 +202,18 @@ int p2b_cfr_step(const void* subgames, const void* nodes, int32_t num_subgames, 
     p.sample_pass = sample_pass;
     p.policy_sample = policy_sample;
     p.beliefs_last = beliefs_last;
+    p.start_policy = start_policy;
     return launch_cfr_solve(p, num_blocks, max_children, (cudaStream_t)stream);
+}
+
+int p2b_cfr_warm_seed(const void* nodes, int64_t rows, const float* start_policy, float weight, float* regrets,
+                      float* weight_sums, void* stream) {
+    P2B_REQUIRE(rows >= 0, "negative count");
+    if (rows == 0) return P2B_OK;
+    P2B_REQUIRE(nodes && start_policy && regrets, "null pointer");
+    P2B_REQUIRE(weight > 0.0f, "the weight must be positive");
+    return launch_cfr_warm_seed(static_cast<const NodeRec*>(nodes), rows, start_policy, weight, regrets, weight_sums,
+                                (cudaStream_t)stream);
 }
 
 int64_t p2b_cfr_noalloc_scratch_floats(void) { return cfr_static_scratch_floats(); }

@@ -188,12 +188,14 @@ __device__ __forceinline__ void children_policy(int mode, const CfrParams& p, co
     const float invk = __fdiv_rn(1.0f, (float)k);
     if (mode == kPassInit) {
 #pragma unroll
-        for (int c = 0; c < K; ++c)
+        for (int c = 0; c < K; ++c) {
+            if (p.start_policy) P[c] = ldv<VPT>(B.row1(const_cast<float*>(p.start_policy), fc + c), tid);
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
-                P[c].v[i] = invk;
+                if (!p.start_policy) P[c].v[i] = invk;
                 Rc[c].v[i] = 0.0f;
             }
+        }
         return;
     }
     if (mode == kPassFinal) {
@@ -1194,6 +1196,36 @@ __global__ void __launch_bounds__(kCfrMaxNodes) cfr_validate_kernel(const CfrPar
     }
 }
 
+// Warm start of type `model` (p2/search/cfr_evaluator.py:913-926), applied between the start
+// pass and the first iteration pass of a stepped solve.  After the start pass a regret row
+// holds the instantaneous regrets of the start policy.  Per non-root row: weight = `weight` x
+// mean over the 1326 hands of max(regret, 0) (the sum in the reference row-reduction order),
+// then regrets = start policy x weight and weight sums = weight.  One block per row.
+__global__ void __launch_bounds__(256) cfr_warm_seed_kernel(const NodeRec* __restrict__ nodes, long long rows,
+                                                            const float* __restrict__ start_policy, float weight,
+                                                            float* __restrict__ regrets, float* __restrict__ weight_sums) {
+    __shared__ __align__(16) float pos[P2B_HPAD];
+    __shared__ float s_sum;
+    for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+        if (nodes[row].depth == 0) continue;  // roots are reached by no action (uniform per block)
+        float* r = regrets + row * P2B_HPAD;
+        for (int h = threadIdx.x; h < P2B_HPAD; h += blockDim.x) pos[h] = h < P2B_NUM_HANDS ? fmaxf(r[h], 0.0f) : 0.0f;
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            const float sum = row_sum_reference_order(pos);
+            if (threadIdx.x == 0) s_sum = sum;
+        }
+        __syncthreads();
+        const float w = __fmul_rn(weight, __fdiv_rn(s_sum, (float)P2B_NUM_HANDS));
+        const float* sp = start_policy + row * P2B_HPAD;
+        for (int h = threadIdx.x; h < P2B_HPAD; h += blockDim.x) {
+            r[h] = __fmul_rn(sp[h], w);
+            if (weight_sums) weight_sums[row * P2B_HPAD + h] = w;
+        }
+        __syncthreads();
+    }
+}
+
 template <int VPT, int MAXC>
 int launch_variant(const CfrParams& p, int num_blocks, cudaStream_t stream) {
     int rc = check_cuda(cudaFuncSetAttribute(cfr_solve_kernel<VPT, MAXC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1219,6 +1251,14 @@ static int dispatch_cfr(const CfrParams& p, int num_blocks, int max_children, cu
     // one kernel serves every child count: node bodies are specialised per count inside it
     if (max_children <= kCfrMaxChildren) return launch_variant<2, kCfrMaxChildren>(p, num_blocks, stream);
     return set_error(P2B_ERR_ARG, "at most %d actions per node are supported, got %d", kCfrMaxChildren, max_children);
+}
+
+int launch_cfr_warm_seed(const NodeRec* nodes, long long rows, const float* start_policy, float weight, float* regrets,
+                         float* weight_sums, cudaStream_t stream) {
+    if (rows <= 0) return P2B_OK;
+    long long grid = rows < (long long)sm_count() * 8 ? rows : (long long)sm_count() * 8;
+    cfr_warm_seed_kernel<<<(unsigned)grid, 256, 0, stream>>>(nodes, rows, start_policy, weight, regrets, weight_sums);
+    return check_cuda(cudaGetLastError(), "cfr_warm_seed_kernel");
 }
 
 int launch_cfr_solve(const CfrParams& params, int num_blocks, int max_children, cudaStream_t stream) {

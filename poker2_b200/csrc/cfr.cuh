@@ -92,6 +92,7 @@ struct CfrParams {
     const int32_t* sample_pass;  // [B] pass whose current policy is kept in policy_sample (may be null)
     float* policy_sample;        // [rows][HPAD] (out, may be null)
     float* beliefs_last;         // [rows][2][HPAD] beliefs of the last iteration at internal nodes (out, may be null)
+    const float* start_policy;   // [rows][HPAD] policy of the start pass (may be null: uniform over the children)
 };
 
 // floats of scratch one block needs: per internal node reach[2], average reach[2], values[2]
@@ -102,6 +103,8 @@ __host__ __device__ inline long long cfr_scratch_floats(int max_internal) {
 int launch_cfr_solve(const CfrParams& p, int num_blocks, int max_children, cudaStream_t stream);
 int cfr_default_blocks();
 int launch_cfr_solve_static(const CfrParams& p, int max_children, cudaStream_t stream);
+int launch_cfr_warm_seed(const NodeRec* nodes, long long rows, const float* start_policy, float weight, float* regrets,
+                         float* weight_sums, cudaStream_t stream);
 long long cfr_static_scratch_floats();
 
 }  // namespace p2b

@@ -67,7 +67,8 @@ class SubgameEvaluator:
                  cfr_type: str = "discounted", alpha: float = 1.5, beta: float = 0.0, gamma: float = 2.0,
                  dcfr_delay: int = 0, cfr_plus: bool = False, max_raises=None, model=None,
                  chance_average: bool = True, leaf_chunk: int = 2048, sample_epsilon: float = 0.25,
-                 generator: torch.Generator | None = None):
+                 generator: torch.Generator | None = None, warm_start_iterations: int = 0,
+                 warm_start_multiplier: float = 1.0):
         self.device = torch.device(device)
         self.cfr_iterations = int(iterations)
         self.bet_bins, self.max_depth, self.bb, self.max_raises = list(bet_bins), max_depth, bb, max_raises
@@ -76,6 +77,9 @@ class SubgameEvaluator:
         self.model, self.chance_average, self.leaf_chunk = model, chance_average, leaf_chunk
         self.sample_epsilon = sample_epsilon
         self.generator = generator
+        # warm start of type `model`: regrets seeded from the start policy (cfr_evaluator.py:887-926)
+        self.warm_start_iterations = int(warm_start_iterations)
+        self.warm_start_multiplier = float(warm_start_multiplier)
         self.stats: dict = {}
         self.root_nodes = 0
         self._result = None
@@ -107,6 +111,7 @@ class SubgameEvaluator:
         self.root_nodes = n
         boards_t = torch.from_numpy(self.boards)
         kw = dict(exploitability=True, keep_node_values=True, sampling=True)
+        self.stepped = bool(self.layout.num_model_leaves) or self.warm_start_iterations > 0
         if self.layout.num_model_leaves:
             if self.model is None:
                 raise ValueError("the subgames have non-terminal leaves: a leaf model is required")
@@ -117,7 +122,8 @@ class SubgameEvaluator:
             extra = dict(chunk=self.leaf_chunk) if self.chance_average else {}
             self.leaf_fn = cls(self.model, leaf_boards, ctx, self.device, **extra)
         else:
-            self.solver = psolver.SubgameSolver(self.layout, boards_t, self.device, **kw)
+            cls = psolver.SteppedSolver if self.stepped else psolver.SubgameSolver
+            self.solver = cls(self.layout, boards_t, self.device, **kw)
             self.leaf_fn = None
         if initial_beliefs is None:
             initial_beliefs = torch.full((n, 2, NUM_HANDS), 1.0 / NUM_HANDS, dtype=torch.float32)
@@ -129,19 +135,28 @@ class SubgameEvaluator:
         self.stats["evaluator_tree_depth"] = float(self.trees.tree_depth)
 
     # ------------------------------------------------------------------ evaluate_cfr
-    def evaluate_cfr(self, training_mode: bool = True) -> SampledStates:
-        """Runs the solve (cfr_evaluator.py:1497-1528) and samples the next public states."""
-        T = self.cfr_iterations
+    def evaluate_cfr(self, training_mode: bool = True, start_policy: torch.Tensor | None = None) -> SampledStates:
+        """Runs the solve (cfr_evaluator.py:1497-1528) and samples the next public states.
+        start_policy [M,1326] (upstream node order): the policy head's softmax at every node;
+        None = uniform, what a head with zero logits gives."""
+        T, ws = self.cfr_iterations, self.warm_start_iterations
         gen_device = self.generator.device if self.generator is not None else torch.device("cpu")
         t_sample = sampling.sampling_schedule(self.root_nodes, T, self.generator, cfr_type=self.cfr_type,
-                                              dcfr_delay=self.dcfr_delay, device=gen_device)
+                                              warm_start_iterations=ws, dcfr_delay=self.dcfr_delay, device=gen_device)
         self.t_sample = t_sample
-        self.solver.set_sampling_schedule(t_sample.to(self.device))
+        self.solver.set_sampling_schedule(t_sample.to(self.device), warm_start_iterations=ws)
         scal = psolver.iteration_scalars(T, cfr_type=self.cfr_type, alpha=self.alpha, beta=self.beta,
                                          gamma=self.gamma, dcfr_delay=self.dcfr_delay)
-        if self.leaf_fn is not None:
-            res = self.solver.solve(self.root_beliefs, scal, self.leaf_fn, cfr_plus=self.cfr_plus)
+        if self.stepped:
+            if ws > 0 and start_policy is None:  # uniform over the children of every parent
+                cc = torch.from_numpy(self.trees.child_count[self.trees.parent_index.clip(min=0)]).clamp(min=1)
+                start_policy = (1.0 / cc.to(torch.float32))[:, None].expand(-1, NUM_HANDS).contiguous()
+            res = self.solver.solve(self.root_beliefs, scal, self.leaf_fn, cfr_plus=self.cfr_plus,
+                                    start_policy=start_policy, warm_start_iterations=ws,
+                                    warm_start_multiplier=self.warm_start_multiplier)
         else:
+            if start_policy is not None:
+                raise ValueError("a start policy needs the stepped solver (set warm_start_iterations or use model leaves)")
             res = self.solver.solve(self.root_beliefs, scal, cfr_plus=self.cfr_plus)
         self._result = res
         # the walk draws from the generator: run it where the generator lives

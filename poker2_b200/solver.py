@@ -232,12 +232,15 @@ class SubgameSolver:
         self.sample_pass = torch.full((B,), -2, device=device, dtype=torch.int32) if sampling else None
         self.launches = 0
 
-    def set_sampling_schedule(self, t_sample: torch.Tensor) -> None:
+    def set_sampling_schedule(self, t_sample: torch.Tensor, warm_start_iterations: int = 0) -> None:
         """t_sample [B]: iteration at whose start each subgame's current policy is kept
-        (`sampling.sampling_schedule`)."""
+        (`sampling.sampling_schedule`).  The policy at the start of iteration t is the policy of
+        pass t-1; after a warm start of w iterations pass k >= 1 runs iteration w+k-1, so it is
+        the policy of pass t-w."""
         if self.sample_pass is None:
             raise ValueError("the solver was built without sampling=True")
-        self.sample_pass.copy_((t_sample.to(torch.int64) - 1).to(torch.int32))
+        shift = warm_start_iterations if warm_start_iterations > 0 else 1
+        self.sample_pass.copy_((t_sample.to(torch.int64) - shift).to(torch.int32))
         self.policy_sample.zero_()
 
     def _result(self) -> "SolveResult":
@@ -299,6 +302,8 @@ class SteppedSolver(SubgameSolver):
         self.leaf_beliefs = torch.zeros(slots, 2, HPAD, **f32)
         self.leaf_values = torch.zeros(slots, 2, HPAD, **f32)
 
+    start_policy_rows = None  # [rows,1344] policy of the start pass (None: uniform)
+
     def _step(self, root_beliefs, sc, iterations, cfr_plus, pass_begin, pass_end, phases) -> None:
         p = _lib.ptr
         with torch.cuda.device(self.device):
@@ -310,13 +315,29 @@ class SteppedSolver(SubgameSolver):
                 self.scratch.numel(), p(sc), iterations, int(cfr_plus), self.layout.tree_depth, p(self.work_counter),
                 self.num_blocks, pass_begin, pass_end, phases, p(self.carry_sums), p(self.carry_roots),
                 p(self.leaf_begin), p(self.leaf_beliefs), p(self.leaf_values), p(self.sample_pass),
-                p(self.policy_sample), p(self.beliefs_last), _lib.stream_ptr(self.device))
+                p(self.policy_sample), p(self.beliefs_last), p(self.start_policy_rows), _lib.stream_ptr(self.device))
         self.launches += 1
 
-    def solve(self, root_beliefs: torch.Tensor, scalars: np.ndarray, leaf_fn=None, *,
-              cfr_plus: bool = False) -> SolveResult:
+    def solve(self, root_beliefs: torch.Tensor, scalars: np.ndarray, leaf_fn=None, *, cfr_plus: bool = False,
+              start_policy: torch.Tensor | None = None, warm_start_iterations: int = 0,
+              warm_start_multiplier: float = 1.0) -> SolveResult:
+        """scalars: `iteration_scalars(T)` for all T iterations.  start_policy [M,1326] in the
+        upstream node order (the policy head's softmax; None = uniform).  With
+        warm_start_iterations = w > 0 (needs a start policy) the regrets are seeded from the start
+        policy after the start pass (`warm_start` of type `model`, cfr_evaluator.py:887-926) and
+        the iterations w..T-1 follow."""
         assert root_beliefs.shape == (self.B, 2, HPAD) and root_beliefs.dtype == torch.float32
         assert root_beliefs.is_contiguous() and root_beliefs.device == self.device
+        ws = int(warm_start_iterations)
+        if ws > 0:
+            if start_policy is None:
+                raise ValueError("a warm start needs a start policy")
+            # pass 0 is warm_start's own update_policy(w): it mixes with t = w, like iteration w after it
+            scalars = np.concatenate([scalars[ws:ws + 1], scalars[ws:]])
+        self.start_policy_rows = None
+        if start_policy is not None:
+            order = torch.from_numpy(self.layout.to_level_major).to(start_policy.device)
+            self.start_policy_rows = pad_rows(start_policy.to(torch.float32)[order]).to(self.device).contiguous()
         iterations = int(scalars.shape[0])
         sc = torch.from_numpy(scalars.view(np.uint8).reshape(iterations, 32).copy()).to(self.device)
         self._scalars = sc
@@ -324,6 +345,12 @@ class SteppedSolver(SubgameSolver):
         if n_leaves and leaf_fn is None:
             raise ValueError("the trees have model-valued leaves: a leaf_fn is required")
         for pas in range(-1, iterations + 1):
+            if pas == 0 and ws > 0:
+                with torch.cuda.device(self.device):
+                    _lib.call("p2b_cfr_warm_seed", _lib.ptr(self.nodes), self.layout.rows, _lib.ptr(self.start_policy_rows),
+                              float(ws) * float(warm_start_multiplier), _lib.ptr(self.regrets), _lib.ptr(self.weight_sums),
+                              _lib.stream_ptr(self.device))
+                self.launches += 1
             if n_leaves == 0:
                 self._step(root_beliefs, sc, iterations, cfr_plus, pas, pas, 3)
                 continue

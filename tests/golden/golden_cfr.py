@@ -341,7 +341,58 @@ def gen_training_data() -> None:
          hand_weights=hand_weights().numpy())
 
 
-SECTIONS = {"tree": gen_tree, "cfr": gen_cfr, "turn": gen_turn, "training_data": gen_training_data}
+class FixedLogitModel(ZeroModel):
+    """Policy head stand-in: the same logits for every node, a fixed function of (hand, action)."""
+
+    def __call__(self, features, include_policy=True, **kw):
+        from p2.models.model_output import ModelOutput
+
+        n = len(features)
+        logits = torch.randn(1326, self.num_actions, generator=torch.Generator().manual_seed(31))
+        return ModelOutput(policy_logits=logits[None].expand(n, -1, -1).clone(), value=torch.zeros(n),
+                           hand_values=torch.zeros(n, 2, 1326))
+
+
+def gen_warm_start() -> None:
+    """River subgames with the model's policy as start policy and regrets seeded from it
+    (`warm_start`, cfr_evaluator.py:887-926, type `model`), then the remaining iterations."""
+    from p2.core.structured_config import WarmStartType
+
+    b, r, p, s = seeded_inputs(13, 2, (20, 200), (100, 1000))
+    iterations, ws, mult, cap, depth = 12, 3, 10.0, 2, 8
+    install_raise_cap(cap)
+    ev = make_evaluator(2, iterations, depth=depth)
+    ev.model = FixedLogitModel(len(BET_BINS) + 3)
+    ev.warm_start_iterations, ev.warm_start_type, ev.warm_start_multiplier = ws, WarmStartType.model, mult
+    captured = {}
+    original = ev.warm_start
+
+    def hooked():
+        captured["start_policy"] = ev.policy_probs.clone()
+        original()
+        captured["seeded_regrets"] = ev.cumulative_regrets.clone()
+        captured["seeded_weights"] = ev.regret_weight_sums.clone()
+
+    ev.warm_start = hooked
+    ev.initialize_subgame(river_env(b, p, s), torch.arange(2), r)
+    ev.generator = torch.Generator().manual_seed(5)
+    ev.evaluate_cfr()
+    ex = ev._compute_exploitability()
+    install_raise_cap(None)
+    print("warm start nodes", ev.total_nodes, "exploitability", ex.local_exploitability.tolist())
+    save("cfr_warm_cap2_t12.npz",
+         boards=b.to(torch.int16).numpy(), ranges=r.numpy(), pot=p.numpy(), stack=s.numpy(),
+         iterations=np.int64(iterations), warm_start_iterations=np.int64(ws), warm_start_multiplier=np.float64(mult),
+         cap=np.int64(cap), max_depth=np.int64(depth), total_nodes=np.int64(ev.total_nodes),
+         start_policy=captured["start_policy"].numpy(), seeded_regrets=captured["seeded_regrets"].numpy(),
+         seeded_weights=captured["seeded_weights"].numpy(), regrets=ev.cumulative_regrets.numpy(),
+         weight_sums=ev.regret_weight_sums.numpy(), policy_avg=ev.policy_probs_avg.numpy(),
+         root_values=ev.values_avg[:2].numpy(), t_sample=ev.t_sample[:2].numpy(),
+         policy_sample=ev.policy_probs_sample.numpy(), exploitability=ex.local_exploitability.numpy())
+
+
+SECTIONS = {"tree": gen_tree, "cfr": gen_cfr, "turn": gen_turn, "training_data": gen_training_data,
+            "warm_start": gen_warm_start}
 
 
 class _BeliefEchoModel:

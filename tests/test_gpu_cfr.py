@@ -205,3 +205,31 @@ def test_depth_limited_tree_and_empty_inputs(cuda_device, golden_dir):
                                      torch.zeros(0, 2, dtype=torch.int64), torch.zeros(0),
                                      table_of_row=torch.zeros(0, dtype=torch.int32))
     assert empty.shape == (0, 2, 1326)
+
+
+def test_start_policy_and_warm_start_match_upstream(cuda_device, golden_dir):
+    """Policy-head start policy, regrets seeded from it (warm start of type `model`), then the
+    remaining iterations: final state, sampling policy and exploitability of the upstream run."""
+    from poker2_b200 import solver, tree as ptree
+
+    z = np.load(os.path.join(golden_dir, "cfr_warm_cap2_t12.npz"))
+    T, ws = int(z["iterations"]), int(z["warm_start_iterations"])
+    trees = ptree.build_trees(ptree.root_states(z["pot"], z["stack"], min_raise=2), [0.5, 1.0], int(z["max_depth"]),
+                              bb=2, max_raises=int(z["cap"]))
+    assert trees.total_nodes == int(z["total_nodes"])
+    boards = z["boards"].astype(np.int64)
+    layout = solver.device_layout(trees, boards)
+    sv = solver.SteppedSolver(layout, torch.from_numpy(boards), cuda_device, exploitability=True, sampling=True)
+    sv.set_sampling_schedule(torch.from_numpy(z["t_sample"]), warm_start_iterations=ws)
+    rb = solver.pad_rows(torch.from_numpy(z["ranges"]).to(cuda_device)).contiguous()
+    res = sv.solve(rb, solver.iteration_scalars(T), start_policy=torch.from_numpy(z["start_policy"]),
+                   warm_start_iterations=ws, warm_start_multiplier=float(z["warm_start_multiplier"]))
+    n = trees.num_roots
+    for name, got in [("regrets", res.regrets), ("weight_sums", res.weight_sums), ("policy_avg", res.policy_avg),
+                      ("policy_sample", res.policy_sample)]:
+        got = res.level_major(got).cpu()[n:]
+        want = torch.from_numpy(z[name])[n:]
+        _report(name, got, want)
+        torch.testing.assert_close(got, want, rtol=RTOL, atol=ATOL)
+    torch.testing.assert_close(res.root_values[..., :1326].cpu(), torch.from_numpy(z["root_values"]), rtol=RTOL, atol=ATOL)
+    torch.testing.assert_close(res.exploitability.cpu(), torch.from_numpy(z["exploitability"]), rtol=1e-4, atol=1e-6)

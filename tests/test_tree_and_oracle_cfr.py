@@ -139,3 +139,27 @@ def test_layout_rejects_trees_beyond_the_kernel_limits():
     # one root, ragged batch of one: offsets and records are consistent
     assert layout.subgames[0]["n_nodes"] == small.total_nodes
     assert int(layout.nodes["kind"][0]) == ptree.KIND_INTERNAL
+
+
+def test_cfr_oracle_warm_start_bit_exact(golden_dir):
+    """Start policy from a policy head and regrets seeded from it (warm start of type `model`),
+    against the upstream evaluator."""
+    z = np.load(os.path.join(golden_dir, "cfr_warm_cap2_t12.npz"))
+    t = _build(z["pot"], z["stack"], int(z["cap"]), int(z["max_depth"]))
+    assert t.total_nodes == int(z["total_nodes"])
+    o = ocfr.SubgameOracle(t.oracle_dict(z["boards"].astype(np.int64)), torch.from_numpy(z["ranges"]),
+                           iterations=int(z["iterations"]), start_policy=torch.from_numpy(z["start_policy"]),
+                           warm_start_iterations=int(z["warm_start_iterations"]),
+                           warm_start_multiplier=float(z["warm_start_multiplier"]))
+    o.initialize()
+    o.warm_start()
+    assert torch.equal(o.regrets, torch.from_numpy(z["seeded_regrets"]))
+    assert torch.equal(o.weight_sums, torch.from_numpy(z["seeded_weights"]))
+    for tt in range(o.warm_start_iterations, o.iterations):
+        o.iteration(tt)
+    o.finalize()
+    assert torch.equal(o.regrets, torch.from_numpy(z["regrets"]))
+    assert torch.equal(o.policy_avg, torch.from_numpy(z["policy_avg"]))
+    assert torch.equal(o.values_avg[: o.N], torch.from_numpy(z["root_values"]))
+    ex, _ = o.exploitability()
+    assert torch.equal(ex, torch.from_numpy(z["exploitability"]))
