@@ -49,3 +49,27 @@ def test_training_data_matches_upstream(cuda_device, golden_dir):
                       (value_batch.statistics["bet_amounts"], "value_bet_amounts"),
                       (policy_batch.statistics["bet_amounts"], "policy_bet_amounts")]:
         assert np.array_equal(got.cpu().numpy(), z[want]), want
+
+
+def test_evaluator_with_warm_start_runs_stepped(cuda_device, golden_dir):
+    """With warm-start iterations the facade solves through the stepped path (uniform start
+    policy when none is given) and still returns well-formed batches."""
+    from poker2_b200 import evaluator, solver, tree as ptree
+
+    z = np.load(os.path.join(golden_dir, "cfr_warm_cap2_t12.npz"))
+    roots = ptree.root_states(z["pot"], z["stack"], min_raise=2)
+    env = evaluator.env_view(roots, z["boards"].astype(np.int64))
+    ev = evaluator.SubgameEvaluator(cuda_device, iterations=int(z["iterations"]), max_depth=int(z["max_depth"]),
+                                    max_raises=int(z["cap"]), generator=torch.Generator().manual_seed(5),
+                                    warm_start_iterations=int(z["warm_start_iterations"]),
+                                    warm_start_multiplier=float(z["warm_start_multiplier"]))
+    ev.initialize_subgame(env, torch.arange(2), torch.from_numpy(z["ranges"]))
+    assert isinstance(ev.solver, solver.SteppedSolver)
+    ev.evaluate_cfr(start_policy=torch.from_numpy(z["start_policy"]))
+    value_batch, _, policy_batch = ev.training_data()
+    torch.testing.assert_close(value_batch.value_targets.cpu(), torch.from_numpy(z["root_values"]).clamp(-1, 1),
+                               rtol=1e-5, atol=1e-6)
+    assert np.array_equal(ev.t_sample.numpy(), z["t_sample"])  # same generator seed as the upstream run
+    ev.evaluate_cfr()  # uniform start policy
+    value_batch, _, policy_batch = ev.training_data()
+    assert torch.isfinite(value_batch.value_targets).all() and torch.isfinite(policy_batch.policy_targets).all()
