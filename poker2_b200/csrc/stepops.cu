@@ -5,6 +5,7 @@
 // cfr.cu is the fast path; these exist for drop-in compatibility.  Scalars that depend on
 // the iteration number are read from device memory (as upstream's TScalars do).
 #include "common.cuh"
+#include "exactdiv.cuh"
 
 namespace p2b {
 
@@ -31,23 +32,60 @@ inline int blocks_for(long long n, int cap) {
     return (int)g;
 }
 
-// fused_cfr_triton.py:72-121 (_fused_dcfr_update_kernel)
+// fused_cfr_triton.py:72-121 (_fused_dcfr_update_kernel).  VEC: all arrays 16-byte aligned, four
+// elements per thread and iteration (the tail is done one by one).
+struct DcfrScalars {
+    float an, bn;
+    Divisor da, db;  // the two divisors are the same for every element (exactdiv.cuh)
+};
+__device__ __forceinline__ void dcfr_update_one(float& c, float& w, float reg, const DcfrScalars& k, int apply_dcfr,
+                                                int cfr_plus) {
+    if (apply_dcfr) {
+        const bool pos = c > 0.0f;
+        const float num = pos ? k.an : k.bn;
+        Divisor d;
+        d.y = pos ? k.da.y : k.db.y;
+        d.r = pos ? k.da.r : k.db.r;
+        d.ok = k.da.ok && k.db.ok;
+        c = div_exact(__fmul_rn(c, num), d);
+        w = div_exact(__fmul_rn(w, num), d);
+    }
+    w = __fadd_rn(w, 1.0f);
+    c = __fadd_rn(c, reg);
+    if (cfr_plus) c = fmaxf(c, 0.0f);
+}
+
+template <bool VEC>
 __global__ void dcfr_update_kernel(const float* __restrict__ regrets, float* __restrict__ cumul,
                                    float* __restrict__ weights, float* __restrict__ pos_out,
                                    const float* __restrict__ scal /* a_num,b_num,a_den,b_den */, long long n,
                                    int apply_dcfr, int cfr_plus) {
-    const float an = scal[0], bn = scal[1], ad = scal[2], bd = scal[3];
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-        float c = cumul[i], w = weights[i];
-        if (apply_dcfr) {
-            const bool pos = c > 0.0f;
-            const float num = pos ? an : bn, den = pos ? ad : bd;
-            c = __fdiv_rn(__fmul_rn(c, num), den);
-            w = __fdiv_rn(__fmul_rn(w, num), den);
+    DcfrScalars k;
+    k.an = scal[0];
+    k.bn = scal[1];
+    k.da = make_divisor(scal[2]);
+    k.db = make_divisor(scal[3]);
+    const long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x, nthreads = (long long)gridDim.x * blockDim.x;
+    long long done = 0;
+    if (VEC) {
+        const long long n4 = n >> 2;
+        for (long long i = tid; i < n4; i += nthreads) {
+            float4 c = reinterpret_cast<float4*>(cumul)[i], w = reinterpret_cast<float4*>(weights)[i];
+            const float4 r = reinterpret_cast<const float4*>(regrets)[i];
+            dcfr_update_one(c.x, w.x, r.x, k, apply_dcfr, cfr_plus);
+            dcfr_update_one(c.y, w.y, r.y, k, apply_dcfr, cfr_plus);
+            dcfr_update_one(c.z, w.z, r.z, k, apply_dcfr, cfr_plus);
+            dcfr_update_one(c.w, w.w, r.w, k, apply_dcfr, cfr_plus);
+            reinterpret_cast<float4*>(cumul)[i] = c;
+            reinterpret_cast<float4*>(weights)[i] = w;
+            if (pos_out)
+                reinterpret_cast<float4*>(pos_out)[i] = make_float4(fmaxf(c.x, 0.0f), fmaxf(c.y, 0.0f), fmaxf(c.z, 0.0f), fmaxf(c.w, 0.0f));
         }
-        w = __fadd_rn(w, 1.0f);
-        c = __fadd_rn(c, regrets[i]);
-        if (cfr_plus) c = fmaxf(c, 0.0f);
+        done = n4 << 2;
+    }
+    for (long long i = done + tid; i < n; i += nthreads) {
+        float c = cumul[i], w = weights[i];
+        dcfr_update_one(c, w, regrets[i], k, apply_dcfr, cfr_plus);
         cumul[i] = c;
         weights[i] = w;
         if (pos_out) pos_out[i] = fmaxf(c, 0.0f);
@@ -59,10 +97,29 @@ __global__ void block_normalize_kernel(float* __restrict__ target, const unsigne
                                        const float* __restrict__ allowed_prob, long long rows, int outer_stride, int H,
                                        float eps) {
     __shared__ double red[kThreads / 32];
+    constexpr int kPer = 6;  // 256 threads x 6 cover rows of up to 1536 entries in registers
     for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
         const long long outer = row / outer_stride;
         float* t = target + row * H;
         const unsigned char* m = allowed + outer * H;
+        if (H <= kPer * kThreads) {
+            float v[kPer];
+            double s = 0.0;
+#pragma unroll
+            for (int i = 0; i < kPer; ++i) {
+                const int h = threadIdx.x + i * kThreads;
+                v[i] = (h < H && m[h]) ? t[h] : 0.0f;
+                s += (double)v[i];
+            }
+            const float total = (float)block_sum(s, red);
+            const Divisor d = make_divisor(total);
+#pragma unroll
+            for (int i = 0; i < kPer; ++i) {
+                const int h = threadIdx.x + i * kThreads;
+                if (h < H) t[h] = total > eps ? div_exact(v[i], d) : allowed_prob[outer * H + h];
+            }
+            continue;
+        }
         double s = 0.0;
         for (int h = threadIdx.x; h < H; h += blockDim.x) {
             const float v = m[h] ? t[h] : 0.0f;
@@ -212,28 +269,57 @@ __global__ void scaled_difference_kernel(const float* __restrict__ a, const floa
         out[i] = __fsub_rn(__fmul_rn(ca, a[i]), __fmul_rn(cb, b[i]));
 }
 
-// Per-card sums and total of one 1326-combo row in fp64; cs must hold 52 doubles.
-__device__ __forceinline__ double row_card_sums(const float* __restrict__ x, const ComboTable* __restrict__ combos,
-                                                double* cs, double* red) {
-    __syncthreads();  // previous users of cs are done
-    // four threads per card, each a quarter of the 51 hands holding it (warps 0..6)
+// Hands holding each card, in combo order: nat[c*51 + i] = combo index of (c, i-th other card).
+constexpr int kNatEntries = P2B_NUM_CARDS * 51;
+__device__ __forceinline__ void fill_card_hand_table(uint16_t* nat) {
+    for (int idx = threadIdx.x; idx < kNatEntries; idx += blockDim.x) {
+        const int c = idx / 51, i = idx % 51, d = i < c ? i : i + 1;
+        nat[idx] = (uint16_t)(c < d ? combo_index(c, d) : combo_index(d, c));
+    }
+}
+
+constexpr int kRowRegs = (P2B_NUM_HANDS + kThreads - 1) / kThreads;  // 6 values per thread cover a row
+
+// This thread's share of a 1326-combo row, from global memory into registers.
+__device__ __forceinline__ void load_row_regs(const float* __restrict__ x, float (&v)[kRowRegs]) {
+#pragma unroll
+    for (int i = 0; i < kRowRegs; ++i) {
+        const int h = threadIdx.x + i * kThreads;
+        v[i] = h < P2B_NUM_HANDS ? x[h] : 0.0f;
+    }
+}
+
+// Puts a row held in registers into shared memory, then computes its per-card sums (four
+// threads per card, each a quarter of the 51 hands holding it) and its total, all in fp64; cs
+// must hold 52 doubles, xs 1326 floats, nat the table above.  Returns the total.
+__device__ __forceinline__ double row_card_sums(const float (&v)[kRowRegs], float* __restrict__ xs,
+                                                const uint16_t* __restrict__ nat, double* cs, double* red) {
+    __syncthreads();  // previous users of xs / cs are done
+    double tot = 0.0;
+#pragma unroll
+    for (int i = 0; i < kRowRegs; ++i) {
+        const int h = threadIdx.x + i * kThreads;
+        if (h < P2B_NUM_HANDS) xs[h] = v[i];
+        tot += (double)v[i];
+    }
+    const double S = block_sum(tot, red);  // contains the barriers that publish xs
     if (threadIdx.x < 224) {
-        const int t = threadIdx.x, c = t >> 2, q = t & 3;
-        const bool valid = t < 208;
+        const int t = threadIdx.x < 208 ? threadIdx.x : 207, c = t >> 2, q = t & 3;
+        // entries q, q+4, ..., q+48 of the card's list; only the last one can fall outside (q = 3)
+        const uint16_t* idx = nat + c * 51 + q;
+        float g[13];
+#pragma unroll
+        for (int i = 0; i < 12; ++i) g[i] = xs[idx[4 * i]];
+        g[12] = q < 3 ? xs[idx[48]] : 0.0f;
         double s = 0.0;
-        if (valid)
-            for (int i = q; i < 51; i += 4) {
-                const int d = i < c ? i : i + 1;
-                s += (double)x[c < d ? combo_index(c, d) : combo_index(d, c)];
-            }
+#pragma unroll
+        for (int i = 0; i < 13; ++i) s += (double)g[i];
         s += __shfl_xor_sync(0xffffffffu, s, 1);
         s += __shfl_xor_sync(0xffffffffu, s, 2);
-        if (valid && q == 0) cs[c] = s;
+        if (threadIdx.x < 208 && q == 0) cs[c] = s;
     }
-    double tot = 0.0;
-    for (int h = threadIdx.x; h < P2B_NUM_HANDS; h += blockDim.x) tot += (double)x[h];
-    (void)combos;
-    return block_sum(tot, red);
+    __syncthreads();
+    return S;
 }
 
 __device__ __forceinline__ float unblocked_value(const double* cs, double S, int c1, int c2, float x) {
@@ -246,12 +332,28 @@ __global__ void unblocked_mass_kernel(const float* __restrict__ src, const long 
                                       const ComboTable* __restrict__ combos, float* __restrict__ out, long long rows) {
     __shared__ double cs[P2B_NUM_CARDS];
     __shared__ double red[kThreads / 32];
+    __shared__ float xs[P2B_NUM_HANDS];
+    __shared__ uint16_t nat[kNatEntries];
+    __shared__ unsigned char c1s[P2B_NUM_HANDS], c2s[P2B_NUM_HANDS];
+    fill_card_hand_table(nat);
+    for (int h = threadIdx.x; h < P2B_NUM_HANDS; h += blockDim.x) {
+        c1s[h] = combos->c1[h];
+        c2s[h] = combos->c2[h];
+    }
+    // the next row is fetched into registers while the current one is processed
+    float cur[kRowRegs], nxt[kRowRegs];
+    if (blockIdx.x < rows) load_row_regs(src + (row_index ? row_index[blockIdx.x] : (long long)blockIdx.x) * P2B_NUM_HANDS, cur);
     for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
-        const float* x = src + (row_index ? row_index[r] : r) * P2B_NUM_HANDS;
-        const double S = row_card_sums(x, combos, cs, red);
-        for (int h = threadIdx.x; h < P2B_NUM_HANDS; h += blockDim.x)
-            out[r * P2B_NUM_HANDS + h] = unblocked_value(cs, S, combos->c1[h], combos->c2[h], x[h]);
-        __syncthreads();
+        const long long rn = r + gridDim.x;
+        if (rn < rows) load_row_regs(src + (row_index ? row_index[rn] : rn) * P2B_NUM_HANDS, nxt);
+        const double S = row_card_sums(cur, xs, nat, cs, red);
+#pragma unroll
+        for (int i = 0; i < kRowRegs; ++i) {
+            const int h = threadIdx.x + i * kThreads;
+            if (h < P2B_NUM_HANDS) out[r * P2B_NUM_HANDS + h] = unblocked_value(cs, S, c1s[h], c2s[h], cur[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < kRowRegs; ++i) cur[i] = nxt[i];
     }
 }
 
@@ -263,17 +365,27 @@ __global__ void unblocked_ratio_kernel(const float* __restrict__ numer, const fl
                                        long long rows, float eps) {
     __shared__ double cs_n[P2B_NUM_CARDS], cs_d[P2B_NUM_CARDS];
     __shared__ double red[kThreads / 32];
+    __shared__ float xn_s[P2B_NUM_HANDS], xd_s[P2B_NUM_HANDS];
+    __shared__ uint16_t nat[kNatEntries];
+    __shared__ unsigned char c1s[P2B_NUM_HANDS], c2s[P2B_NUM_HANDS];
+    fill_card_hand_table(nat);
+    for (int h = threadIdx.x; h < P2B_NUM_HANDS; h += blockDim.x) {
+        c1s[h] = combos->c1[h];
+        c2s[h] = combos->c2[h];
+    }
     for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
         const float* xn = numer + r * P2B_NUM_HANDS;
         const float* xd = denom + (parent_index ? parent_index[r] : r) * P2B_NUM_HANDS;
-        const double Sn = row_card_sums(xn, combos, cs_n, red);
-        const double Sd = row_card_sums(xd, combos, cs_d, red);
+        float vn[kRowRegs], vd[kRowRegs];
+        load_row_regs(xn, vn);
+        load_row_regs(xd, vd);
+        const double Sn = row_card_sums(vn, xn_s, nat, cs_n, red);
+        const double Sd = row_card_sums(vd, xd_s, nat, cs_d, red);
         for (int h = threadIdx.x; h < P2B_NUM_HANDS; h += blockDim.x) {
-            const int c1 = combos->c1[h], c2 = combos->c2[h];
-            const float n = unblocked_value(cs_n, Sn, c1, c2, xn[h]), d = unblocked_value(cs_d, Sd, c1, c2, xd[h]);
+            const int c1 = c1s[h], c2 = c2s[h];
+            const float n = unblocked_value(cs_n, Sn, c1, c2, xn_s[h]), d = unblocked_value(cs_d, Sd, c1, c2, xd_s[h]);
             out[r * P2B_NUM_HANDS + h] = d > eps ? __fdiv_rn(n, d) : 0.0f;
         }
-        __syncthreads();
     }
 }
 
@@ -356,8 +468,14 @@ extern "C" {
 int p2b_step_dcfr_update(const float* regrets, float* cumulative, float* weight_sums, float* positive_out,
                          const float* scalars4, int64_t n, int apply_dcfr, int cfr_plus, void* stream) {
     if (n <= 0) return P2B_OK;
-    dcfr_update_kernel<<<GRID_ELEMS(n), kThreads, 0, (cudaStream_t)stream>>>(regrets, cumulative, weight_sums,
-                                                                            positive_out, scalars4, n, apply_dcfr, cfr_plus);
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(regrets) | reinterpret_cast<uintptr_t>(cumulative) |
+                           reinterpret_cast<uintptr_t>(weight_sums) | reinterpret_cast<uintptr_t>(positive_out);
+    if ((bits & 15) == 0)
+        dcfr_update_kernel<true><<<GRID_ELEMS((n + 3) / 4), kThreads, 0, (cudaStream_t)stream>>>(
+            regrets, cumulative, weight_sums, positive_out, scalars4, n, apply_dcfr, cfr_plus);
+    else
+        dcfr_update_kernel<false><<<GRID_ELEMS(n), kThreads, 0, (cudaStream_t)stream>>>(
+            regrets, cumulative, weight_sums, positive_out, scalars4, n, apply_dcfr, cfr_plus);
     STEP_CHECK("dcfr_update_kernel");
 }
 
