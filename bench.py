@@ -356,8 +356,39 @@ def run_micro(args):
     tabs = showdown.BoardTables(boards)
     ms_eval = _time_ms(lambda: showdown.showdown_values(tabs, bel, pot, scale, out=vals), max(args.steps, 5),
                        max(args.warmup, 3))
+    # step-level kernels (the fused_cfr_triton call signatures) on 100,000 rows of 1326
+    from poker2_b200 import fused_cfr
+
+    del bel, vals, tabs
+    rows_s, H = 100_000, 1326
+    R = torch.randn(rows_s, H, device=device, generator=g)
+    W = torch.rand(rows_s, H, device=device, generator=g)
+    inst = torch.randn(rows_s, H, device=device, generator=g)
+    out_s = torch.empty(rows_s, H, device=device)
+    pos_s = inst.abs()
+    uni = torch.full((rows_s, H), 0.2, device=device)
+    ok = torch.rand(rows_s // 2, H, device=device, generator=g) > 0.18
+    prob = ok.float() / ok.float().sum(-1, keepdim=True)
+    bel2 = torch.rand(rows_s // 2, 2, H, device=device, generator=g)
+
+    class _Discounted:
+        name = "discounted"
+
+    nel = rows_s * H
+    steps_s, warm_s = max(args.steps, 5), max(args.warmup, 3)
+    step_ops = {}
+    for name, nbytes, fn in [
+        ("dcfr_update", 20 * nel, lambda: fused_cfr.fused_dcfr_update_(R, W, inst, 5, _Discounted, 1.5, 0.0, False)),
+        ("regret_matching_divide", 16 * nel, lambda: fused_cfr.fused_regret_matching_divide_(pos_s, W, uni, out_s)),
+        ("block_normalize", 8 * nel + 5 * nel // 2, lambda: fused_cfr.fused_block_and_normalize_beliefs_(bel2, ok, prob)),
+        ("unblocked_mass", 8 * nel, lambda: fused_cfr.unblocked_mass_triton(R)),
+    ]:
+        ms = _time_ms(fn, steps_s, warm_s)
+        step_ops[name] = {"ms": ms, "achieved_gbs": nbytes / ms * 1e-6}
     clocks = sampler.stop()
     peak, peak_kind = measured_peak_gbs()
+    for v in step_ops.values():
+        v["frac"] = v["achieved_gbs"] / peak
     rank_gbs = n_hands * 18 / ms_rank * 1e-6
     both_gbs = m * 26520 / ms_both * 1e-6
     eval_gbs = m * 21216 / ms_eval * 1e-6
@@ -376,6 +407,7 @@ def run_micro(args):
                                "frac": eval_gbs / peak, "algorithmic_bytes_per_board": 21216},
         "rank7": {"hands_per_s": n_hands / (ms_rank / 1e3), "ms": ms_rank, "achieved_gbs": rank_gbs,
                   "frac": rank_gbs / peak, "algorithmic_bytes_per_hand": 18},
+        "step_ops": step_ops,
     }
     print(json.dumps(line))
 
