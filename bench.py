@@ -316,7 +316,7 @@ def run_micro(args):
     """Rules / showdown micro-benchmark: 2^26 seven-card hands ranked to int32; 4096 river
     boards (x `--micro-board-factor` so that the working set exceeds L2) with two Dirichlet(1)
     ranges each, fp32 showdown values for both players."""
-    from poker2_b200 import _lib, build, rules, showdown
+    from poker2_b200 import _lib, build, showdown
 
     build.build()
     device = torch.device("cuda:0")

@@ -7,7 +7,6 @@ evaluate the value function, `index_add_` per root and divide by the sample coun
 """
 from __future__ import annotations
 
-import numpy as np
 import torch
 
 from . import cards

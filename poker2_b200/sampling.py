@@ -10,7 +10,6 @@ the scheduled iteration, kept by the kernel) and `SolveResult.beliefs_last`.
 """
 from __future__ import annotations
 
-import numpy as np
 import torch
 
 NUM_HANDS = 1326

@@ -1,6 +1,5 @@
 """Chance-node helpers (next-card belief expansion, ordered indexed add) against the CPU
 restatement of the upstream helper."""
-import numpy as np
 import pytest
 import torch
 
