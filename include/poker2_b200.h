@@ -266,6 +266,17 @@ int p2b_chance_expand_features(const float* pre_beliefs, int64_t player_stride, 
                                int64_t feature_stride, int64_t* root_lookup, void* stream);
 int p2b_indexed_mean_bf16(const void* src_bf16, int64_t src_stride, const int64_t* sample_offsets,
                           int64_t num_roots, float* out, int64_t out_player_stride, void* stream);
+/* Flop chance node (src/p2/search/chance_node_helper.py:218-357).  p2b_expand_on_boards:
+ * post_beliefs [num_roots*num_boards, 2, 1326] = the beliefs of every root re-blocked and
+ * re-normalised on every given board (boards [num_boards, board_len] int64, -1 = empty slot;
+ * sample = root*num_boards + board; uniform fallback at mass <= 1e-12, :262-284).
+ * p2b_mean_over_hand_perms: out[n, h] = mean over p of values[n, perms[p, h]] (perms
+ * [num_perms, 1326] int32: the hole-card index permutation of each suit permutation), added in
+ * ascending p -- `_avg_over_perms` (:17-27); rows are packed 1326-float rows. */
+int p2b_expand_on_boards(const float* pre_beliefs, int64_t player_stride, const int64_t* boards, int32_t board_len,
+                         int64_t num_roots, int64_t num_boards, float* post_beliefs, void* stream);
+int p2b_mean_over_hand_perms(const float* values, const int32_t* perms, int32_t num_perms, int64_t rows,
+                             float* out, void* stream);
 /* p2b_indexed_add_rows: out[index[i], :] (+)= src[i, :] in ascending i, for a sorted int64
  * index (the index_add_ of :468-475); mean != 0 divides by max(count,1) (:476-477);
  * accumulate == 0 overwrites out instead of adding to it. */

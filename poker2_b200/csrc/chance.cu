@@ -246,6 +246,88 @@ __global__ void indexed_mean_bf16_kernel(const __nv_bfloat16* __restrict__ src, 
     }
 }
 
+// Beliefs re-blocked and re-normalised on explicitly given boards (the flop chance node,
+// chance_node_helper.py:262-284): sample s = root * num_boards + board.  Same arithmetic as
+// chance_expand_kernel; every card of `boards[board]` that is >= 0 blocks.
+__global__ void expand_on_boards_kernel(const float* __restrict__ pre_beliefs, long long player_stride,
+                                        const long long* __restrict__ boards, int board_len, long long num_roots,
+                                        long long num_boards, const ComboTable* __restrict__ combos,
+                                        float* __restrict__ post_beliefs) {
+    __shared__ double red[kThreads / 32];
+    __shared__ int cnt[kThreads / 32];
+    const long long total = num_roots * num_boards;
+    for (long long smp = blockIdx.x; smp < total; smp += gridDim.x) {
+        const long long b = smp / num_boards, f = smp - b * num_boards;
+        unsigned long long mask = 0;
+        for (int j = 0; j < board_len; ++j) {
+            const long long c = boards[f * board_len + j];
+            if (c >= 0) mask |= 1ull << c;
+        }
+        for (int p = 0; p < 2; ++p) {
+            const float* src = pre_beliefs + (b * 2 + p) * player_stride;
+            float* dst = post_beliefs + (smp * 2 + p) * P2B_NUM_HANDS;
+            float v[kHandsPerThread];
+            bool ok[kHandsPerThread];
+            double s = 0.0;
+            int n_allowed = 0;
+#pragma unroll
+            for (int i = 0; i < kHandsPerThread; ++i) {
+                const int h = threadIdx.x + i * kThreads;
+                ok[i] = false;
+                v[i] = 0.0f;
+                if (h < P2B_NUM_HANDS) {
+                    ok[i] = (((mask >> combos->c1[h]) | (mask >> combos->c2[h])) & 1ull) == 0;
+                    v[i] = ok[i] ? src[h] : 0.0f;
+                    s += (double)v[i];
+                    n_allowed += ok[i];
+                }
+            }
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) {
+                s += __shfl_xor_sync(0xffffffffu, s, d);
+                n_allowed += __shfl_xor_sync(0xffffffffu, n_allowed, d);
+            }
+            __syncthreads();
+            if ((threadIdx.x & 31) == 0) {
+                red[threadIdx.x >> 5] = s;
+                cnt[threadIdx.x >> 5] = n_allowed;
+            }
+            __syncthreads();
+            double tot = 0.0;
+            int nall = 0;
+            for (int w = 0; w < kThreads / 32; ++w) {
+                tot += red[w];
+                nall += cnt[w];
+            }
+            const float sum = (float)tot;
+            const float uni = __fdiv_rn(1.0f, fmaxf((float)nall, 1.0f));
+#pragma unroll
+            for (int i = 0; i < kHandsPerThread; ++i) {
+                const int h = threadIdx.x + i * kThreads;
+                if (h < P2B_NUM_HANDS)
+                    dst[h] = sum > 1e-12f ? __fdiv_rn(v[i], fmaxf(sum, 1e-12f)) : (ok[i] ? uni : 0.0f);
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// out[n, h] = (sum over p of values[n, perms[p, h]]) / num_perms, added in ascending p: the mean
+// of a row over the hand-index permutations of a set of suit permutations
+// (`_avg_over_perms`, chance_node_helper.py:17-27).  Rows are 1326 floats, packed.
+__global__ void mean_over_hand_perms_kernel(const float* __restrict__ values, const int* __restrict__ perms,
+                                            int num_perms, long long rows, float* __restrict__ out) {
+    const long long n = rows * P2B_NUM_HANDS;
+    for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < n; e += (long long)gridDim.x * blockDim.x) {
+        const long long r = e / P2B_NUM_HANDS;
+        const int h = (int)(e - r * P2B_NUM_HANDS);
+        const float* row = values + r * P2B_NUM_HANDS;
+        float acc = 0.0f;
+        for (int p = 0; p < num_perms; ++p) acc = __fadd_rn(acc, row[perms[p * P2B_NUM_HANDS + h]]);
+        out[e] = __fdiv_rn(acc, (float)num_perms);
+    }
+}
+
 }  // namespace
 
 int sm_count();
@@ -304,6 +386,32 @@ int p2b_indexed_mean_bf16(const void* src_bf16, int64_t src_stride, const int64_
         static_cast<const __nv_bfloat16*>(src_bf16), src_stride, (const long long*)sample_offsets, num_roots, out,
         out_player_stride);
     return check_cuda(cudaGetLastError(), "indexed_mean_bf16_kernel");
+}
+
+int p2b_expand_on_boards(const float* pre_beliefs, int64_t player_stride, const int64_t* boards, int32_t board_len,
+                         int64_t num_roots, int64_t num_boards, float* post_beliefs, void* stream) {
+    if (num_roots <= 0 || num_boards <= 0) return P2B_OK;
+    if (!pre_beliefs || !boards || !post_beliefs) return set_error(P2B_ERR_ARG, "p2b_expand_on_boards: null pointer");
+    if (player_stride < P2B_NUM_HANDS) return set_error(P2B_ERR_ARG, "p2b_expand_on_boards: stride too small");
+    int rc = ensure_tables();
+    if (rc) return rc;
+    long long grid = num_roots * num_boards;
+    if (grid > (long long)sm_count() * 16) grid = (long long)sm_count() * 16;
+    expand_on_boards_kernel<<<(unsigned)grid, kThreads, 0, (cudaStream_t)stream>>>(
+        pre_beliefs, player_stride, (const long long*)boards, board_len, num_roots, num_boards, device_combo_table(),
+        post_beliefs);
+    return check_cuda(cudaGetLastError(), "expand_on_boards_kernel");
+}
+
+int p2b_mean_over_hand_perms(const float* values, const int32_t* perms, int32_t num_perms, int64_t rows, float* out,
+                             void* stream) {
+    if (rows <= 0) return P2B_OK;
+    if (!values || !perms || !out || num_perms < 1)
+        return set_error(P2B_ERR_ARG, "p2b_mean_over_hand_perms: null pointer or no permutation");
+    long long blocks = (rows * P2B_NUM_HANDS + kThreads - 1) / kThreads;
+    if (blocks > (long long)sm_count() * 16) blocks = (long long)sm_count() * 16;
+    mean_over_hand_perms_kernel<<<(unsigned)blocks, kThreads, 0, (cudaStream_t)stream>>>(values, perms, num_perms, rows, out);
+    return check_cuda(cudaGetLastError(), "mean_over_hand_perms_kernel");
 }
 
 int p2b_indexed_add_rows(float* out, const int64_t* index, const float* src, int64_t num_src, int64_t num_out,

@@ -175,8 +175,8 @@ class SubgameEvaluator:
         (cfr_evaluator.py:1384-1495).  The pre-chance batch holds, for roots at the start of the
         turn or river betting round, the expectation of the value network over the card that
         opened the street, on the beliefs held before it (:1446-1493); it needs the leaf model
-        (None without one).  Roots at the start of the flop round (canonical-flop sampling,
-        chance_node_helper.py:218-357) are not covered and are left out of that batch."""
+        (None without one); for roots at the start of the flop round it is the expectation over
+        the canonical flops and their suit orbits (`flop_chance.flop_chance_values`)."""
         if self._result is None:
             raise RuntimeError("training_data() needs evaluate_cfr() first")
         res, t = self._result, self.trees
@@ -214,18 +214,28 @@ class SubgameEvaluator:
 
         t = self.trees
         N, st = t.num_roots, t.state
-        start = (st.actions_this_round[:N] == 0) & ((st.street[:N] == 2) | (st.street[:N] == 3))
+        from . import flop_chance
+
+        single = (st.actions_this_round[:N] == 0) & ((st.street[:N] == 2) | (st.street[:N] == 3))
+        flop = (st.actions_this_round[:N] == 0) & (st.street[:N] == 1)
+        start = single | flop
         if self.model is None or not start.any():
             return None
         dev = self.device
-        rows = torch.from_numpy(np.nonzero(start)[0]).to(dev)
-        pre = self.root_beliefs[rows][..., :NUM_HANDS].contiguous()
-        boards_pre = torch.from_numpy(self.last_boards[np.nonzero(start)[0]]).to(dev)
-        ctx = leaf_eval.leaf_context(t, np.nonzero(start)[0]).to(dev)
-        expected = chance.single_card_chance_values(
-            pre, boards_pre, lambda post, samples, lookup: self.model(post, samples, ctx[lookup]))
         targets = value_targets.clone()
-        targets[rows] = expected
+        if single.any():
+            rows = torch.from_numpy(np.nonzero(single)[0]).to(dev)
+            pre = self.root_beliefs[rows][..., :NUM_HANDS].contiguous()
+            boards_pre = torch.from_numpy(self.last_boards[np.nonzero(single)[0]]).to(dev)
+            ctx = leaf_eval.leaf_context(t, np.nonzero(single)[0]).to(dev)
+            targets[rows] = chance.single_card_chance_values(
+                pre, boards_pre, lambda post, samples, lookup: self.model(post, samples, ctx[lookup]))
+        if flop.any():  # expectation over the three flop cards (chance_node_helper.py:218-357)
+            rows = torch.from_numpy(np.nonzero(flop)[0]).to(dev)
+            pre = self.root_beliefs[rows].contiguous()
+            ctx = leaf_eval.leaf_context(t, np.nonzero(flop)[0]).to(dev)
+            targets[rows] = flop_chance.flop_chance_values(
+                pre, lambda post, boards, root: self.model(post, boards, ctx[root]), self.generator)
         stats = {k: v.clone() for k, v in value_stats.items()}
         stats["board"] = torch.from_numpy(self.last_boards[:N]).to(dev)
         street = torch.from_numpy(st.street[:N]).to(dev)

@@ -443,3 +443,55 @@ def gen_chance() -> None:
 
 
 SECTIONS["chance"] = gen_chance
+
+
+class _FlopEchoModel:
+    """Deterministic stand-in for the leaf model of the flop chance helper: values depend on the
+    sample's beliefs, on its three board cards and on the hand index, elementwise."""
+
+    def __init__(self, card_w, hand_w):
+        self.cw, self.hw = card_w, hand_w
+
+    def eval(self):
+        pass
+
+    def __call__(self, features, **kw):
+        from p2.models.model_output import ModelOutput
+
+        n = len(features)
+        bel = features.beliefs.view(n, 2, 1326).float()
+        scale = self.cw[features.board[:, :3]].sum(dim=1).view(-1, 1, 1)
+        hv = torch.stack([bel[:, 1], -bel[:, 0]], dim=1) * scale + self.hw.view(1, 1, -1) * 0.125
+        return ModelOutput(policy_logits=None, value=torch.zeros(n), hand_values=hv)
+
+
+def gen_flop_chance() -> None:
+    """flop_chance_values (chance_node_helper.py:218-357): exhaustive over the canonical flops
+    with the full suit orbit, and the sampled form (256 flops, 6 permutations)."""
+    import warnings
+
+    from p2.models.mlp.mlp_features import MLPFeatures
+    from p2.search.chance_node_helper import ChanceNodeHelper
+
+    g = torch.Generator().manual_seed(17)
+    B = 2
+    bel = torch.empty(B, 2, 1326).exponential_(generator=g)
+    bel = bel / bel.sum(-1, keepdim=True)
+    cw = torch.randn(52, generator=torch.Generator().manual_seed(3))
+    hw = torch.randn(1326, generator=torch.Generator().manual_seed(4))
+    helper = ChanceNodeHelper(device=torch.device("cpu"), float_dtype=torch.float32, num_players=2,
+                              model=_FlopEchoModel(cw, hw), generator=torch.Generator().manual_seed(23))
+    feats = MLPFeatures(context=torch.zeros(B, 4), street=torch.zeros(B), to_act=torch.zeros(B, dtype=torch.long),
+                        board=torch.full((B, 5), -1, dtype=torch.long), beliefs=bel.reshape(B, -1))
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        sampled = helper.flop_chance_values(torch.arange(B), feats, bel)
+        helper.FLOP_SAMPLE_SIZE, helper.NUM_PERM_SAMPLES = 0, 0
+        exhaustive = helper.flop_chance_values(torch.arange(B), feats, bel)
+    save("flop_chance.npz", beliefs=bel.numpy(), card_w=cw.numpy(), hand_w=hw.numpy(), sampled=sampled.numpy(),
+         exhaustive=exhaustive.numpy(), sampled_seed=np.int64(23),
+         canonical=helper.flop_id_to_canonical.numpy(), counts=helper.flop_id_to_count.numpy(),
+         combo_perm=helper.combo_perm.numpy().astype(np.int16))
+
+
+SECTIONS["flop_chance"] = gen_flop_chance

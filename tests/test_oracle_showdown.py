@@ -53,3 +53,30 @@ def test_chance_oracle_matches_upstream_helper(golden_dir):
 
     got = ochance.single_card_chance_values(torch.from_numpy(z["beliefs"]), torch.from_numpy(z["boards"]), value_fn)
     assert torch.equal(got, torch.from_numpy(z["expected"]))
+
+
+def _flop_echo_model(z):
+    cw, hw = torch.from_numpy(z["card_w"]), torch.from_numpy(z["hand_w"])
+
+    def fn(post, boards, root):
+        scale = cw.to(post.device)[boards[:, :3]].sum(dim=1).view(-1, 1, 1)
+        return torch.stack([post[:, 1], -post[:, 0]], dim=1) * scale + hw.to(post.device).view(1, 1, -1) * 0.125
+
+    return fn
+
+
+def test_flop_chance_oracle_matches_upstream(golden_dir):
+    """Canonical flops, suit-permutation table and both forms of flop_chance_values against the
+    upstream helper (same generator seed for the sampled form)."""
+    from oracle import flop_chance
+
+    z = np.load(os.path.join(golden_dir, "flop_chance.npz"))
+    canon, counts = flop_chance.canonical_flops()
+    assert np.array_equal(canon, z["canonical"]) and np.array_equal(counts, z["counts"])
+    assert np.array_equal(flop_chance.combo_perm(), z["combo_perm"].astype(np.int64))
+    bel = torch.from_numpy(z["beliefs"])
+    fn = _flop_echo_model(z)
+    sampled = flop_chance.flop_chance_values(bel, fn, torch.Generator().manual_seed(int(z["sampled_seed"])))
+    assert torch.equal(sampled, torch.from_numpy(z["sampled"]))
+    exhaustive = flop_chance.flop_chance_values(bel, fn, None, sample_size=0, num_perm_samples=0)
+    torch.testing.assert_close(exhaustive, torch.from_numpy(z["exhaustive"]), rtol=1e-6, atol=1e-7)
