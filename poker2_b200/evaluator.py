@@ -101,11 +101,12 @@ class SubgameEvaluator:
         self.boards = take("board_indices", np.int64)
         if hasattr(src_env, "last_board_indices"):
             self.last_boards = take("last_board_indices", np.int64)
-        else:  # the board before the newest card was dealt
+        else:  # the board before the last deal: the flop comes as three cards, turn and river as one
             self.last_boards = self.boards.copy()
             n_cards = (self.boards >= 0).sum(axis=1)
-            has = n_cards > 0
-            self.last_boards[np.nonzero(has)[0], n_cards[has] - 1] = -1
+            self.last_boards[n_cards == 3] = -1
+            later = n_cards > 3
+            self.last_boards[np.nonzero(later)[0], n_cards[later] - 1] = -1
         self.trees = ptree.build_trees(roots, self.bet_bins, self.max_depth, bb=self.bb, max_raises=self.max_raises)
         self.layout = psolver.device_layout(self.trees, self.boards)
         self.root_nodes = n

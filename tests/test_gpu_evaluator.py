@@ -73,3 +73,37 @@ def test_evaluator_with_warm_start_runs_stepped(cuda_device, golden_dir):
     ev.evaluate_cfr()  # uniform start policy
     value_batch, _, policy_batch = ev.training_data()
     assert torch.isfinite(value_batch.value_targets).all() and torch.isfinite(policy_batch.policy_targets).all()
+
+
+def test_evaluator_on_flop_subgames_with_network_leaves(cuda_device):
+    """Flop roots: leaves at the start of the turn valued by a small network averaged over the
+    49 turn cards, and a pre-chance batch averaged over the canonical flops."""
+    from poker2_b200 import evaluator, leaf_eval, tree as ptree
+
+    g = torch.Generator().manual_seed(8)
+    n = 2
+    boards = torch.full((n, 5), -1, dtype=torch.int64)
+    for i in range(n):
+        boards[i, :3] = torch.randperm(52, generator=g)[:3]
+    pot, stack = np.array([40, 90]), np.array([400, 250])
+    roots = ptree.root_states(pot, stack, min_raise=2, street=1)
+    env = evaluator.env_view(roots, boards.numpy())
+    model = leaf_eval.ValueMLP(width=64, depth=2, dtype=torch.float32, seed=2).to(cuda_device)
+    ev = evaluator.SubgameEvaluator(cuda_device, iterations=3, max_raises=2, model=model, leaf_chunk=64,
+                                    generator=torch.Generator().manual_seed(1))
+    ranges = torch.empty(n, 2, 1326).exponential_(generator=g)
+    hit = torch.zeros(n, 52, dtype=torch.bool)
+    hit.scatter_(1, boards[:, :3], True)
+    c1, c2 = np.triu_indices(52, k=1)
+    ranges = ranges * (~(hit[:, torch.from_numpy(c1)] | hit[:, torch.from_numpy(c2)]))[:, None, :]
+    ranges = ranges / ranges.sum(-1, keepdim=True)
+    ev.initialize_subgame(env, torch.arange(n), ranges)
+    assert ev.layout.num_model_leaves > 0
+    nxt = ev.evaluate_cfr()
+    assert (nxt.state.street == 2).all() or len(nxt.nodes) == 0 or (nxt.state.street >= 1).all()
+    value_batch, pre_batch, policy_batch = ev.training_data()
+    assert len(value_batch) == n and len(pre_batch) == n
+    assert np.array_equal(pre_batch.statistics["street"].cpu().numpy(), np.zeros(n, dtype=np.int64))
+    assert (pre_batch.statistics["board"].cpu().numpy() == -1).all()  # no board before the flop
+    for t in (value_batch.value_targets, pre_batch.value_targets, policy_batch.policy_targets):
+        assert torch.isfinite(t).all()
