@@ -1,7 +1,7 @@
 // Hand-ranking kernels: packed score of [N,7] card ids, pairwise comparison of card-id
-// and one-hot-plane hands.  HBM-bound by design: 14 B in + 4 B out per hand, staged
-// through shared memory so that global loads are 128-bit and coalesced although a hand
-// row (14 B) is not a power of two.
+// and one-hot-plane hands.  HBM-bound by design: 14 B in + 4 B out per hand; a thread owns
+// four consecutive hands (56 B, seven 8-byte loads) and prefetches its next four while it
+// scores the current ones.
 #include "common.cuh"
 #include "rank7.cuh"
 
@@ -10,9 +10,8 @@ namespace p2b {
 constexpr int kRankThreads = 256;
 constexpr int kHandsPerThread = 4;
 constexpr int kTileHands = kRankThreads * kHandsPerThread;  // 1024 hands = 14336 B per tile
-constexpr int kTileVec = kTileHands * 14 / 16;              // 896 x 16 B
 
-// cards: [n,7] int16; out: [n] int32.  VEC = base pointer is 16-byte aligned.
+// cards: [n,7] int16; out: [n] int32.  VEC = base pointer is 8-byte aligned.
 // A block keeps the 32 KB rank table, the type table and a card -> suit-lane-bit table in
 // shared memory; a hand of distinct cards is scored by the table walk of rank7.cuh
 // (score_distinct_lut), a hand with repeated ids by the general bit-mask scorer.
@@ -22,49 +21,57 @@ __global__ void __launch_bounds__(kRankThreads) rank7_cards_kernel(const int16_t
                                                                    const RankLut* __restrict__ lut) {
     __shared__ __align__(16) uint32_t T[kRankLutEntries];
     __shared__ uint32_t TT[32];
-    __shared__ __align__(16) int16_t tile[kTileHands * 7];
     {
         const uint4* src = reinterpret_cast<const uint4*>(lut->mask_entry);
         for (int i = threadIdx.x; i < kRankLutEntries / 4; i += kRankThreads) reinterpret_cast<uint4*>(T)[i] = __ldg(src + i);
         if (threadIdx.x < 32) TT[threadIdx.x] = threadIdx.x < kTypeLutEntries ? lut->type_entry[threadIdx.x] : 0u;
     }
+    __syncthreads();
+    // A thread takes four consecutive hands: 56 bytes = seven 8-byte words (VEC: 8-byte aligned),
+    // read straight from global memory; the words of its next tile are fetched while the current
+    // four hands are scored, so no barrier separates loading from scoring.
     const int64_t num_tiles = (n + kTileHands - 1) / kTileHands;
+    auto load_words = [&](int64_t t, uint32_t (&w)[14]) {
+        const int64_t h0 = t * kTileHands + kHandsPerThread * threadIdx.x;
+        if (t < num_tiles && VEC && h0 + kHandsPerThread <= n) {
+            const uint2* mine = reinterpret_cast<const uint2*>(cards + h0 * 7);
+#pragma unroll
+            for (int i = 0; i < 7; ++i) {
+                const uint2 v = __ldcs(mine + i);
+                w[2 * i] = v.x;
+                w[2 * i + 1] = v.y;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 14; ++i) {
+                const int64_t e = h0 * 7 + 2 * i;
+                const uint32_t a0 = (t < num_tiles && e < n * 7) ? (uint16_t)cards[e] : 0u;
+                const uint32_t a1 = (t < num_tiles && e + 1 < n * 7) ? (uint16_t)cards[e + 1] : 0u;
+                w[i] = a0 | (a1 << 16);
+            }
+        }
+    };
+    uint32_t w[14], wn[14];
+    load_words(blockIdx.x, w);
     for (int64_t t = blockIdx.x; t < num_tiles; t += gridDim.x) {
         const int64_t hand0 = t * kTileHands;
         const int64_t remaining = n - hand0;
         const int hands = remaining < kTileHands ? (int)remaining : kTileHands;
-        const int16_t* src = cards + hand0 * 7;
-        if (VEC && hands == kTileHands) {
-            const uint4* src4 = reinterpret_cast<const uint4*>(src);
-            uint4* dst4 = reinterpret_cast<uint4*>(tile);
+        load_words(t + gridDim.x, wn);
+        // card id -> bit position in the four 16-bit suit lanes (id + 3 * suit), for both 16-bit
+        // halves of a word at once: (id * 79) >> 10 is id / 13 for ids below 52 and the product
+        // of the low half cannot carry into the high half
+        uint32_t bp[14];
 #pragma unroll
-            for (int i = threadIdx.x; i < kTileVec; i += kRankThreads) dst4[i] = __ldcs(src4 + i);
-        } else {
-            for (int i = threadIdx.x; i < hands * 7; i += kRankThreads) tile[i] = src[i];
-            for (int i = hands * 7 + threadIdx.x; i < kTileHands * 7; i += kRankThreads) tile[i] = 0;
-        }
-        __syncthreads();
-        // a thread takes four consecutive hands: 56 bytes = seven 8-byte words of the tile
-        uint32_t w[14];
-        {
-            const uint2* mine = reinterpret_cast<const uint2*>(tile) + 7 * threadIdx.x;
-#pragma unroll
-            for (int i = 0; i < 7; ++i) {
-                const uint2 v = mine[i];
-                w[2 * i] = v.x;
-                w[2 * i + 1] = v.y;
-            }
-        }
+        for (int k = 0; k < 14; ++k) bp[k] = w[k] + 3u * (((w[k] * 79u) >> 10) & 0x003F003Fu);
         int32_t score[kHandsPerThread];
 #pragma unroll
         for (int j = 0; j < kHandsPerThread; ++j) {
-            int c[7];
             uint32_t lo = 0, hi = 0;
 #pragma unroll
             for (int i = 0; i < 7; ++i) {
                 const int e = 7 * j + i;  // 16-bit element of the thread's 28
-                c[i] = (int)(int16_t)((e & 1) ? (w[e >> 1] >> 16) : (w[e >> 1] & 0xffffu));
-                const uint32_t bit = (uint32_t)card_bit(c[i]);
+                const uint32_t bit = (e & 1) ? (bp[e >> 1] >> 16) : (bp[e >> 1] & 0xffffu);
                 uint32_t blo, bhi;  // 1 << bit as two words: shl.b32 gives 0 for shift counts above 31
                 asm("shl.b32 %0, 1, %1;" : "=r"(blo) : "r"(bit));
                 asm("shl.b32 %0, 1, %1;" : "=r"(bhi) : "r"(bit - 32u));
@@ -73,7 +80,13 @@ __global__ void __launch_bounds__(kRankThreads) rank7_cards_kernel(const int16_t
             }
             if (__popc(lo) + __popc(hi) == 7) {
                 score[j] = score_distinct_lut(lo & 0x1fffu, (lo >> 16) & 0x1fffu, hi & 0x1fffu, (hi >> 16) & 0x1fffu, T, TT);
-            } else {
+            } else {  // repeated (or out-of-range) ids: the general scorer on the ids themselves
+                int c[7];
+#pragma unroll
+                for (int i = 0; i < 7; ++i) {
+                    const int e = 7 * j + i;
+                    c[i] = (int)(int16_t)((e & 1) ? (w[e >> 1] >> 16) : (w[e >> 1] & 0xffffu));
+                }
                 score[j] = score_cards<7>(c);
             }
         }
@@ -85,7 +98,8 @@ __global__ void __launch_bounds__(kRankThreads) rank7_cards_kernel(const int16_t
             for (int j = 0; j < kHandsPerThread; ++j)
                 if (h0 + j < hands) out[hand0 + h0 + j] = score[j];
         }
-        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 14; ++i) w[i] = wn[i];
     }
 }
 
@@ -139,8 +153,18 @@ int launch_rank7_cards(const int16_t* cards, int64_t n, int32_t* out, cudaStream
     if (n == 0) return P2B_OK;
     int rc = ensure_tables();
     if (rc) return rc;
-    const int grid = grid_for(n, kTileHands, sm_count() * 4);  // 4 blocks of 46.6 KB shared memory per SM
-    const bool vec = (reinterpret_cast<uintptr_t>(cards) & 15) == 0;
+    const bool vec = (reinterpret_cast<uintptr_t>(cards) & 7) == 0;
+    // one wave of resident blocks: the tile loop is strided by the grid, so a partial second wave
+    // would leave most SMs idle at the end
+    static int resident[2] = {0, 0};
+    if (resident[vec] == 0) {
+        int per_sm = 0;
+        cudaError_t e = vec ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, rank7_cards_kernel<true>, kRankThreads, 0)
+                            : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, rank7_cards_kernel<false>, kRankThreads, 0);
+        if (e != cudaSuccess) return check_cuda(e, "rank7 occupancy query");
+        resident[vec] = per_sm > 0 ? per_sm : 1;
+    }
+    const int grid = grid_for(n, kTileHands, sm_count() * resident[vec]);
     if (vec) rank7_cards_kernel<true><<<grid, kRankThreads, 0, stream>>>(cards, out, n, device_rank_lut());
     else rank7_cards_kernel<false><<<grid, kRankThreads, 0, stream>>>(cards, out, n, device_rank_lut());
     return check_cuda(cudaGetLastError(), "rank7_cards_kernel");
