@@ -148,6 +148,36 @@ int p2b_cfr_step(const void* subgames, const void* nodes, int32_t num_subgames, 
 int p2b_cfr_warm_seed(const void* nodes, int64_t rows, const float* start_policy, float weight, float* regrets,
                       float* weight_sums, void* stream);
 
+/* Public betting trees built on the device (replaces the level-by-level tensor expansion of
+ * `SparseCFREvaluator._construct_subgame`, src/p2/search/sparse_cfr_evaluator.py:141-306, with
+ * the betting rules of src/p2/env/hunl_tensor_env.py:348-423 (legal bins), :766-992 (step) and
+ * :707-724 (fold reward)); one warp expands one subgame breadth-first.
+ *
+ * roots [num_subgames][16] 32-bit words per subgame: to_act, pot, stack0, stack1, committed0,
+ * committed1, min_raise, actions_this_round, flags (1: player 0 all-in, 2: player 1 all-in,
+ * 4: done), street (0..3), button, starting_stack0, starting_stack1, raises made on the street,
+ * big blind, scale (fp32 bits).  bet_bins: HOST array of num_bet_bins (<= 13) pot fractions;
+ * actions are {fold, check/call, fractions..., all-in}.  max_depth <= 63.  max_raises < 0: no cap
+ * (the cap is not an upstream option).
+ *
+ * p2b_tree_count: counts [num_subgames][8] = nodes, internal nodes, leaves valued by a model,
+ * showdown leaves, largest child count, overflow flag (more nodes than the solver kernel supports,
+ * 160), depth of the tree, 0; level_counts [num_subgames][max_depth+1] nodes per tree level.
+ * p2b_tree_records: given the exclusive prefix sums over the subgames of the node counts
+ * (node_begin), of the model-leaf counts (leaf_begin) and, per level, of the level counts offset by
+ * the level's start in the upstream level-major order (level_base [num_subgames][max_depth+1]),
+ * writes the 32-byte subgame records, the 16-byte node records (subgame-major, breadth-first),
+ * to_level_major [rows] (upstream index of every row), model_rows [model leaves] (row of every
+ * model leaf, slot order; may be NULL when there is none) and, when node_state is not NULL, [rows][8] int32 = pot, stack0, stack1,
+ * starting_stack0, starting_stack1, street, to_act, done.  boards [num_subgames][board_width] int64
+ * card ids, -1 = empty slot. */
+int p2b_tree_count(const void* roots, int32_t num_subgames, const float* bet_bins, int32_t num_bet_bins,
+                   int32_t max_depth, int32_t max_raises, int32_t* counts, int32_t* level_counts, void* stream);
+int p2b_tree_records(const void* roots, const int64_t* boards, int32_t board_width, int32_t num_subgames,
+                     const float* bet_bins, int32_t num_bet_bins, int32_t max_depth, int32_t max_raises,
+                     const int32_t* node_begin, const int32_t* leaf_begin, const int64_t* level_base, void* subgames,
+                     void* nodes, int64_t* to_level_major, int64_t* model_rows, int32_t* node_state, void* stream);
+
 /* p2b_cfr_solve_noalloc -- the same solve without any allocation.  (No counterpart in the
  * upstream project: it exists for hosts of this library that cannot allocate.)
  *

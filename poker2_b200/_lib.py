@@ -59,6 +59,8 @@ _SIGNATURES = {
     "p2b_indexed_mean_bf16": [_vp, _i64, _vp, _i64, _vp, _i64, _vp],
     "p2b_expand_on_boards": [_vp, _i64, _vp, _i32, _i64, _i64, _vp, _vp],
     "p2b_mean_over_hand_perms": [_vp, _vp, _i32, _i64, _vp, _vp],
+    "p2b_tree_count": [_vp, _i32, _vp, _i32, _i32, _i32, _vp, _vp, _vp],
+    "p2b_tree_records": [_vp, _vp, _i32, _i32, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "p2b_selftest_division": [ctypes.c_uint64, ctypes.c_uint32, _vp, _vp, _vp],
 }
 # functions whose return value is a quantity, not a status code

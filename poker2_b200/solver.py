@@ -152,6 +152,16 @@ def device_layout(trees: ptree.PublicTrees, boards: np.ndarray) -> DeviceTreeLay
                             model_nodes=order[model_rows])
 
 
+def layout_tensor(layout, name: str, device, dtype=None) -> torch.Tensor:
+    """Field `name` of a tree layout as a tensor on `device`: the device copy a layout built on
+    the GPU already holds (`device_tree.DeviceBuiltLayout`), else an upload of the numpy array."""
+    t = getattr(layout, name + "_dev", None)
+    if t is None:
+        t = torch.from_numpy(np.ascontiguousarray(getattr(layout, name)))
+    t = t.to(device)
+    return t if dtype is None else t.to(dtype)
+
+
 def pad_rows(x: torch.Tensor) -> torch.Tensor:
     """[..., 1326] -> [..., 1344] zero padded (rows of the kernel are 16-byte aligned)."""
     out = x.new_zeros(*x.shape[:-1], HPAD)
@@ -189,8 +199,7 @@ class SolveResult:
         return pinned
 
     def level_major(self, x: torch.Tensor) -> torch.Tensor:
-        idx = torch.from_numpy(self.layout.from_level_major).to(x.device)
-        return x.index_select(0, idx)[..., :NUM_HANDS]
+        return x.index_select(0, layout_tensor(self.layout, "from_level_major", x.device))[..., :NUM_HANDS]
 
 
 class SubgameSolver:
@@ -203,15 +212,22 @@ class SubgameSolver:
         if device.type != "cuda":
             raise ValueError("SubgameSolver requires a CUDA device.")
         self.layout, self.device = layout, device
-        rows, B = layout.rows, layout.subgames.shape[0]
+        built_on_device = getattr(layout, "subgames_dev", None) is not None
+        rows = layout.rows
+        B = int(layout.subgames_dev.shape[0]) if built_on_device else layout.subgames.shape[0]
         self.B = B
         with torch.cuda.device(device):
             blocks = num_blocks if num_blocks > 0 else int(_lib.lib().p2b_cfr_default_blocks())
         self.num_blocks = min(blocks, B)
         f32 = dict(device=device, dtype=torch.float32)
-        self.subgames = torch.from_numpy(layout.subgames.view(np.uint8).reshape(B, 32)).to(device)
-        self.nodes = torch.from_numpy(layout.nodes.view(np.uint8).reshape(rows, 16)).to(device)
-        self.tables = BoardTables(boards.to(device)) if (layout.subgames["table_index"] >= 0).any() else None
+        if built_on_device:
+            self.subgames, self.nodes = layout.subgames_dev.to(device), layout.nodes_dev.to(device)
+            has_showdown = layout.has_showdown
+        else:
+            self.subgames = torch.from_numpy(layout.subgames.view(np.uint8).reshape(B, 32)).to(device)
+            self.nodes = torch.from_numpy(layout.nodes.view(np.uint8).reshape(rows, 16)).to(device)
+            has_showdown = bool((layout.subgames["table_index"] >= 0).any())
+        self.tables = BoardTables(boards.to(device)) if has_showdown else None
         # zeroed once: the kernel rewrites every non-root row on each solve and never touches
         # the root rows (a root is reached by no action)
         self.regrets = torch.zeros(rows, HPAD, **f32)
@@ -298,7 +314,7 @@ class SteppedSolver(SubgameSolver):
         self.carry_sums = torch.zeros(layout.rows, 2, **f32)
         self.carry_roots = torch.zeros(self.B, 4, HPAD, **f32)
         slots = max(layout.num_model_leaves, 1)
-        self.leaf_begin = torch.from_numpy(np.ascontiguousarray(layout.leaf_begin, dtype=np.int32)).to(device)
+        self.leaf_begin = layout_tensor(layout, "leaf_begin", device, torch.int32)
         self.leaf_beliefs = torch.zeros(slots, 2, HPAD, **f32)
         self.leaf_values = torch.zeros(slots, 2, HPAD, **f32)
 
@@ -336,7 +352,7 @@ class SteppedSolver(SubgameSolver):
             scalars = np.concatenate([scalars[ws:ws + 1], scalars[ws:]])
         self.start_policy_rows = None
         if start_policy is not None:
-            order = torch.from_numpy(self.layout.to_level_major).to(start_policy.device)
+            order = layout_tensor(self.layout, "to_level_major", start_policy.device)
             self.start_policy_rows = pad_rows(start_policy.to(torch.float32)[order]).to(self.device).contiguous()
         iterations = int(scalars.shape[0])
         sc = torch.from_numpy(scalars.view(np.uint8).reshape(iterations, 32).copy()).to(self.device)
@@ -362,7 +378,7 @@ class SteppedSolver(SubgameSolver):
                 self.leaf_values[:n_leaves].copy_(vals)
             if self.beliefs_last is not None and pas == iterations - 1:
                 # beliefs of the last iteration at the model leaves (the states sampling continues from)
-                self.beliefs_last[torch.from_numpy(self.layout.model_rows).to(self.device)] = self.leaf_beliefs[:n_leaves]
+                self.beliefs_last[layout_tensor(self.layout, "model_rows", self.device)] = self.leaf_beliefs[:n_leaves]
             self._step(root_beliefs, sc, iterations, cfr_plus, pas, pas, 2)
         return self._result()
 
@@ -394,16 +410,24 @@ def solve_subgames(boards, ranges, pot, stacks, *, iterations: int, bet_bins=(0.
                    max_raises=None, bb: int = 2, cfr_type: str = "discounted", alpha: float = 1.5, beta: float = 0.0,
                    gamma: float = 2.0, dcfr_delay: int = 0, cfr_plus: bool = False, device=None,
                    keep_policy: bool = False, keep_node_values: bool = False, track_weight_sums: bool = True,
-                   exploitability: bool = False):
+                   exploitability: bool = False, device_tree: bool = False):
     """Solves a batch of river subgames: boards [B,5] card ids, ranges [B,2,1326] fp32,
-    pot [B] and stacks [B] or [B,2] in chips.  Returns (SolveResult, PublicTrees)."""
+    pot [B] and stacks [B] or [B,2] in chips.  Returns (SolveResult, PublicTrees); with
+    `device_tree` the trees are expanded on the GPU (`device_tree.build_device_layout`), no host
+    tree exists and the second value is None (the layout is `result.layout`)."""
     device = torch.device(device if device is not None else "cuda:0")
     boards_np = np.asarray(boards.cpu() if torch.is_tensor(boards) else boards, dtype=np.int64)
     pot_np = np.asarray(pot.cpu() if torch.is_tensor(pot) else pot, dtype=np.int64)
     stacks_np = np.asarray(stacks.cpu() if torch.is_tensor(stacks) else stacks, dtype=np.int64)
     roots = ptree.root_states(pot_np, stacks_np, min_raise=bb)
-    trees = ptree.build_trees(roots, list(bet_bins), max_depth, bb=bb, max_raises=max_raises)
-    layout = device_layout(trees, boards_np)
+    if device_tree:
+        from .device_tree import build_device_layout
+        trees = None
+        layout = build_device_layout(roots, boards_np, list(bet_bins), max_depth, bb=bb, max_raises=max_raises,
+                                     device=device)
+    else:
+        trees = ptree.build_trees(roots, list(bet_bins), max_depth, bb=bb, max_raises=max_raises)
+        layout = device_layout(trees, boards_np)
     solver = SubgameSolver(layout, torch.from_numpy(boards_np), device, track_weight_sums=track_weight_sums,
                            keep_policy=keep_policy, keep_node_values=keep_node_values, exploitability=exploitability)
     rb = pad_rows(torch.as_tensor(ranges, dtype=torch.float32).to(device)).contiguous()
@@ -415,11 +439,14 @@ def solve_subgames_with_model(boards, ranges, pot, stacks, model, *, street: int
                               bet_bins=(0.5, 1.0), max_depth: int = 8, max_raises=None, bb: int = 2,
                               cfr_type: str = "discounted", alpha: float = 1.5, beta: float = 0.0, gamma: float = 2.0,
                               dcfr_delay: int = 0, cfr_plus: bool = False, device=None, chance_average: bool = True,
-                              chunk: int = 2048, exploitability: bool = False, keep_node_values: bool = False):
+                              chunk: int = 2048, exploitability: bool = False, keep_node_values: bool = False,
+                              device_tree: bool = False):
     """Solves a batch of flop (street=1, 3 board cards) or turn (street=2, 4 cards) subgames
     whose leaves at the start of the next street are valued by `model(beliefs, boards,
     context)`, averaged over the next public card when `chance_average` (the
-    `single_card_chance_values` semantics).  Returns (SolveResult, PublicTrees, SteppedSolver)."""
+    `single_card_chance_values` semantics).  Returns (SolveResult, PublicTrees, SteppedSolver);
+    with `device_tree` the trees and the leaf context are built on the GPU and the second value
+    is None."""
     from . import leaf_eval
 
     device = torch.device(device if device is not None else "cuda:0")
@@ -429,12 +456,22 @@ def solve_subgames_with_model(boards, ranges, pot, stacks, model, *, street: int
     pot_np = np.asarray(pot.cpu() if torch.is_tensor(pot) else pot, dtype=np.int64)
     stacks_np = np.asarray(stacks.cpu() if torch.is_tensor(stacks) else stacks, dtype=np.int64)
     roots = ptree.root_states(pot_np, stacks_np, min_raise=bb, street=street)
-    trees = ptree.build_trees(roots, list(bet_bins), max_depth, bb=bb, max_raises=max_raises)
-    layout = device_layout(trees, boards_np)
+    if device_tree:
+        from .device_tree import build_device_layout
+        trees = None
+        layout = build_device_layout(roots, boards_np, list(bet_bins), max_depth, bb=bb, max_raises=max_raises,
+                                     device=device, node_state=True)
+    else:
+        trees = ptree.build_trees(roots, list(bet_bins), max_depth, bb=bb, max_raises=max_raises)
+        layout = device_layout(trees, boards_np)
     sv = SteppedSolver(layout, torch.from_numpy(boards_np), device, exploitability=exploitability,
                        keep_node_values=keep_node_values)
-    leaf_boards = torch.from_numpy(boards_np[trees.root_of[layout.model_nodes]])
-    ctx = leaf_eval.leaf_context(trees, layout.model_nodes)
+    if device_tree:
+        leaf_boards = torch.from_numpy(boards_np).to(device)[layout.root_of_row_dev[layout.model_rows_dev]]
+        ctx = layout.leaf_context()
+    else:
+        leaf_boards = torch.from_numpy(boards_np[trees.root_of[layout.model_nodes]])
+        ctx = leaf_eval.leaf_context(trees, layout.model_nodes)
     if chance_average:
         evaluator = leaf_eval.ChanceLeafEvaluator(model, leaf_boards, ctx, device, chunk=chunk)
     else:

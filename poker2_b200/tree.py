@@ -224,7 +224,10 @@ def build_trees(roots: RoundState, bet_bins, max_depth: int, *, bb=2, max_raises
         if bins.size == 0:
             break
         nxt = cur.take(rows_idx)
-        bb_rows = np.asarray(bb)[rows_idx] if np.ndim(bb) else bb
+        if np.ndim(bb):  # one big blind per root: carried down the levels with the nodes
+            bb_level = np.asarray(bb, dtype=np.int64) if depth == 0 else bb_level
+            bb_level = bb_level[rows_idx]
+        bb_rows = bb_level if np.ndim(bb) else bb
         rew = step(nxt, bins, amounts[rows_idx], A, bb_rows)
         levels.append(nxt)
         parents.append(offs[-2] + rows_idx)
