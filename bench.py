@@ -237,7 +237,8 @@ def run_e2e(args, solver, sv, boards, ranges, pot, stack, layout, scal, gathered
 
     def e2e_step():
         res, _ = solver.solve_subgames(h_boards, h_ranges, pot, stack, iterations=ITERATIONS, bet_bins=BET_BINS,
-                                       max_depth=MAX_DEPTH, max_raises=MAX_RAISES, device=device, exploitability=True)
+                                       max_depth=MAX_DEPTH, max_raises=MAX_RAISES, device=device, exploitability=True,
+                                       device_tree=True)
         from poker2_b200 import sharding
 
         if distributed:
@@ -260,7 +261,7 @@ def run_e2e(args, solver, sv, boards, ranges, pot, stack, layout, scal, gathered
     if distributed:
         dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
     e2e_value = units_per_step * e2e_steps / float(e2e_s.item())
-    h2d = h_boards.numel() * 2 + h_ranges.numel() * 4 + layout.nodes.nbytes + layout.subgames.nbytes + scal.nbytes
+    h2d = h_boards.numel() * 8 + h_ranges.numel() * 4 + BATCH * 64 + scal.nbytes  # boards, ranges, root records, scalars
     d2h = sum(t.numel() * 4 for t in out.values() if torch.is_tensor(t)) + 4 * 8
     return {"value": e2e_value, "unit": "subgame-iterations/s", "h2d_bytes_per_step": int(h2d),
             "d2h_bytes_per_step": int(d2h), "steps": e2e_steps}
