@@ -106,3 +106,28 @@ def test_solve_on_device_tree_equals_solve_on_host_tree(cuda_device):
     for name in ("policy_avg", "regrets", "root_values", "exploitability"):
         assert torch.equal(getattr(a, name), getattr(b, name)), name
     assert torch.equal(a.level_major(a.policy_avg), b.level_major(b.policy_avg))
+
+
+def test_network_leaves_on_device_tree_equal_host_tree(cuda_device):
+    from poker2_b200 import leaf_eval
+
+    rng = np.random.default_rng(5)
+    n, iterations = 6, 5
+    boards = torch.from_numpy(random_boards(rng, n, 4)[:, :4].copy())
+    ranges = torch.rand(n, 2, 1326, generator=torch.Generator().manual_seed(5))
+    for i in range(n):  # zero the blocked combos, normalise
+        ok = torch.from_numpy(~np.isin(np.array(np.triu_indices(52, 1)).T, boards[i].numpy()).any(axis=1))
+        ranges[i] *= ok
+    ranges /= ranges.sum(dim=-1, keepdim=True)
+    pot = torch.from_numpy(rng.integers(20, 200, size=n))
+    stack = torch.from_numpy(rng.integers(100, 1000, size=n))
+    out = []
+    for dev_tree in (False, True):
+        model = leaf_eval.ValueMLP(width=64, depth=2, dtype=torch.float32, seed=3).to(cuda_device)
+        res, trees, sv = solver.solve_subgames_with_model(
+            boards, ranges, pot, stack, model, street=2, iterations=iterations, max_raises=2, device=cuda_device,
+            chunk=16, device_tree=dev_tree)
+        assert sv.layout.num_model_leaves > 0
+        out.append((res.policy_avg.clone(), res.root_values.clone(), res.regrets.clone()))
+    for a, b in zip(*out):
+        assert torch.equal(a, b)
