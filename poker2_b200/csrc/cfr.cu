@@ -220,12 +220,26 @@ __device__ __forceinline__ void children_policy(int mode, const CfrParams& p, co
     Divisor ds[VPT];  // the siblings share the divisor
 #pragma unroll
     for (int i = 0; i < VPT; ++i) ds[i] = make_divisor(fmaxf(sum.v[i], 1e-8f));
+    bool bad = false;
 #pragma unroll
     for (int c = 0; c < K; ++c)
         {
 #pragma unroll
-            for (int i = 0; i < VPT; ++i)
-                P[c].v[i] = sum.v[i] > 1e-8f ? div_exact(fmaxf(Rc[c].v[i], 0.0f), ds[i]) : invk;
+            for (int i = 0; i < VPT; ++i) P[c].v[i] = div_fast<true>(fmaxf(Rc[c].v[i], 0.0f), ds[i], bad);
+        }
+    if (bad) {
+#pragma unroll
+        for (int c = 0; c < K; ++c)
+            {
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) P[c].v[i] = __fdiv_rn(fmaxf(Rc[c].v[i], 0.0f), ds[i].y);
+            }
+    }
+#pragma unroll
+    for (int c = 0; c < K; ++c)
+        {
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) P[c].v[i] = sum.v[i] > 1e-8f ? P[c].v[i] : invk;
         }
 }
 
@@ -234,9 +248,16 @@ __device__ __forceinline__ void children_policy(int mode, const CfrParams& p, co
 template <int VPT>
 __device__ __forceinline__ void apply_norm(const Block& B, const HandInfo<VPT>& hi, FV<VPT>& x, float sum) {
     const Divisor d = make_divisor(sum);
+    bool bad = false;
+    FV<VPT> q;
 #pragma unroll
-    for (int i = 0; i < VPT; ++i)
-        x.v[i] = sum > 1e-5f ? div_exact(x.v[i], d) : (hi.allowed[i] ? B.sg.allowed_prob : 0.0f);
+    for (int i = 0; i < VPT; ++i) q.v[i] = div_fast<true>(x.v[i], d, bad);
+    if (bad) {
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) q.v[i] = __fdiv_rn(x.v[i], sum);
+    }
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) x.v[i] = sum > 1e-5f ? q.v[i] : (hi.allowed[i] ? B.sg.allowed_prob : 0.0f);
 }
 
 // Normalises the two rows x[0], x[1] (one per player) over hands.  Uses staging rows 0 and
@@ -550,25 +571,49 @@ __device__ __forceinline__ void sweep_down(int mode, int pass, const CfrParams& 
                             stv<VPT>(B.rbar(ch.internal_idx, a), tid, t);
                             stv<VPT>(B.rbar(ch.internal_idx, 1 - a), tid, rbna);
                         }
+                        bool bad = false;
+                        FV<VPT> num;
 #pragma unroll
                         for (int i = 0; i < VPT; ++i) {
-                            const float v =
-                                div_exact(__fadd_rn(__fmul_rn(ro.v[i], Pb.v[i]), __fmul_rn(rn.v[i], P[c].v[i])), dmix[i]);
-                            Pn[c].v[i] = v;
-                            sum.v[i] = __fadd_rn(sum.v[i], v);
+                            num.v[i] = __fadd_rn(__fmul_rn(ro.v[i], Pb.v[i]), __fmul_rn(rn.v[i], P[c].v[i]));
+                            Pn[c].v[i] = div_fast<true>(num.v[i], dmix[i], bad);
                         }
+                        if (bad) {
+#pragma unroll
+                            for (int i = 0; i < VPT; ++i) Pn[c].v[i] = __fdiv_rn(num.v[i], dmix[i].y);
+                        }
+#pragma unroll
+                        for (int i = 0; i < VPT; ++i) sum.v[i] = __fadd_rn(sum.v[i], Pn[c].v[i]);
                     }
                 Divisor dsum[VPT];
 #pragma unroll
                 for (int i = 0; i < VPT; ++i) dsum[i] = make_divisor(sum.v[i]);
+                {
+                    bool bad = false;
+                    FV<VPT> Q[K];
 #pragma unroll
-                for (int c = 0; c < K; ++c)
-                    {
+                    for (int c = 0; c < K; ++c)
+                        {
 #pragma unroll
-                        for (int i = 0; i < VPT; ++i)
-                            if (sum.v[i] > 1e-5f) Pn[c].v[i] = div_exact(Pn[c].v[i], dsum[i]);
-                        stv<VPT>(B.row1(p.policy_avg, fc + c), tid, Pn[c]);
+                            for (int i = 0; i < VPT; ++i) Q[c].v[i] = div_fast<true>(Pn[c].v[i], dsum[i], bad);
+                        }
+                    if (bad) {
+#pragma unroll
+                        for (int c = 0; c < K; ++c)
+                            {
+#pragma unroll
+                                for (int i = 0; i < VPT; ++i) Q[c].v[i] = __fdiv_rn(Pn[c].v[i], sum.v[i]);
+                            }
                     }
+#pragma unroll
+                    for (int c = 0; c < K; ++c)
+                        {
+#pragma unroll
+                            for (int i = 0; i < VPT; ++i)
+                                if (sum.v[i] > 1e-5f) Pn[c].v[i] = Q[c].v[i];
+                            stv<VPT>(B.row1(p.policy_avg, fc + c), tid, Pn[c]);
+                        }
+                }
             } else {
 #pragma unroll
                 for (int c = 0; c < K; ++c)
@@ -781,12 +826,21 @@ __device__ __forceinline__ void sweep_up(int mode, int pass, const CfrParams& p,
         for (int c = 0; c < K; ++c) {
             const NodeRec ch = B.nodes[fc + c];
             // policy of this child as seen by each opponent hand (cfr_evaluator.py:1083-1093)
-            FV<VPT> pio;
+            FV<VPT> pio, blk;
+            {
+                bool bad = false;
 #pragma unroll
-            for (int i = 0; i < VPT; ++i) {
-                const float m = __fmul_rn(b_a.v[i], P[c].v[i]);
-                const float blk = unblocked(B.cs + (kRowM + c) * 52, B.S[kRowM + c], hi.c1[i], hi.c2[i], m);
-                pio.v[i] = denm.v[i] > 1e-5f ? div_exact(blk, ddenm[i]) : 0.0f;
+                for (int i = 0; i < VPT; ++i) {
+                    const float m = __fmul_rn(b_a.v[i], P[c].v[i]);
+                    blk.v[i] = unblocked(B.cs + (kRowM + c) * 52, B.S[kRowM + c], hi.c1[i], hi.c2[i], m);
+                    pio.v[i] = div_fast<true>(blk.v[i], ddenm[i], bad);
+                }
+                if (bad) {
+#pragma unroll
+                    for (int i = 0; i < VPT; ++i) pio.v[i] = __fdiv_rn(blk.v[i], denm.v[i]);
+                }
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) pio.v[i] = denm.v[i] > 1e-5f ? pio.v[i] : 0.0f;
             }
             FV<VPT> V_a, V_o;
             if (ch.kind == kFoldLeaf) {
@@ -813,10 +867,18 @@ __device__ __forceinline__ void sweep_up(int mode, int pass, const CfrParams& p,
                 }
                 const float pot_a = a == 0 ? ch.v0 : ch.v1, pot_o = a == 0 ? ch.v1 : ch.v0;
                 const Divisor dscale = make_divisor(B.sg.scale);
+                bool bad = false;
 #pragma unroll
                 for (int i = 0; i < VPT; ++i) {
-                    V_a.v[i] = div_exact(__fmul_rn(eva.v[i], pot_a), dscale);
-                    V_o.v[i] = div_exact(__fmul_rn(evo.v[i], pot_o), dscale);
+                    V_a.v[i] = div_fast(__fmul_rn(eva.v[i], pot_a), dscale, bad);
+                    V_o.v[i] = div_fast(__fmul_rn(evo.v[i], pot_o), dscale, bad);
+                }
+                if (bad) {
+#pragma unroll
+                    for (int i = 0; i < VPT; ++i) {
+                        V_a.v[i] = __fdiv_rn(__fmul_rn(eva.v[i], pot_a), B.sg.scale);
+                        V_o.v[i] = __fdiv_rn(__fmul_rn(evo.v[i], pot_o), B.sg.scale);
+                    }
                 }
             } else if (p.leaf_values) {  // valued by the caller's model between the sweeps
                 V_a = ldv<VPT>(p.leaf_values + B.leaf_row(ch.internal_idx, a), tid);
@@ -864,21 +926,35 @@ __device__ __forceinline__ void sweep_up(int mode, int pass, const CfrParams& p,
 #pragma unroll
             for (int c = 0; c < K; ++c)
                 {
-                    FV<VPT> w = ws[c];
+                    FV<VPT> w = ws[c], rn, wn, rq, wq;
+                    Divisor d[VPT];
+                    bool bad = false;
+#pragma unroll
+                    for (int i = 0; i < VPT; ++i) {
+                        const bool pos = Rc[c].v[i] > 0.0f;
+                        const float num = pos ? sc.num_pos : sc.num_neg;
+                        d[i].y = pos ? d_pos.y : d_neg.y;
+                        d[i].r = pos ? d_pos.r : d_neg.r;
+                        d[i].ok = d_pos.ok && d_neg.ok;
+                        rn.v[i] = __fmul_rn(Rc[c].v[i], num);
+                        wn.v[i] = __fmul_rn(w.v[i], num);
+                        rq.v[i] = div_fast(rn.v[i], d[i], bad);
+                        wq.v[i] = div_fast<true>(wn.v[i], d[i], bad);
+                    }
+                    if (bad) {
+#pragma unroll
+                        for (int i = 0; i < VPT; ++i) {
+                            rq.v[i] = __fdiv_rn(rn.v[i], d[i].y);
+                            wq.v[i] = __fdiv_rn(wn.v[i], d[i].y);
+                        }
+                    }
 #pragma unroll
                     for (int i = 0; i < VPT; ++i) {
                         const float reg = __fmul_rn(wgt.v[i], __fsub_rn(Va[c].v[i], acc_a.v[i]));
-                        const bool pos = Rc[c].v[i] > 0.0f;
-                        const float num = pos ? sc.num_pos : sc.num_neg;
-                        Divisor d;
-                        d.y = pos ? d_pos.y : d_neg.y;
-                        d.r = pos ? d_pos.r : d_neg.r;
-                        d.ok = d_pos.ok && d_neg.ok;
-                        float rr = div_exact(__fmul_rn(Rc[c].v[i], num), d);
-                        rr = __fadd_rn(rr, reg);
+                        float rr = __fadd_rn(rq.v[i], reg);
                         if (p.cfr_plus) rr = fmaxf(rr, 0.0f);
                         Rc[c].v[i] = rr;
-                        w.v[i] = __fadd_rn(div_exact(__fmul_rn(w.v[i], num), d), 1.0f);
+                        w.v[i] = __fadd_rn(wq.v[i], 1.0f);
                     }
                     stv<VPT>(B.row1(p.regrets, fc + c), tid, Rc[c]);
                     if (p.weight_sums) stv<VPT>(B.row1(p.weight_sums, fc + c), tid, w);
