@@ -65,14 +65,16 @@ __device__ __forceinline__ float showdown_hand_ev(const HandRec r, int c1, int c
     const float tie = __fadd_rn(__fsub_rn(__fsub_rn(seg, __fsub_rn(a1, a0)), __fsub_rn(b1, b0)), xh);
     float den = __fadd_rn(__fsub_rn(__fsub_rn(1.0f, pc1[51]), pc2[51]), xh);
     den = fmaxf(den, 1e-8f);
-    float ev = 0.0f;
-    if (den > 1e-8f) {
-        const Divisor d = make_divisor(den);
-        const float wp = div_exact(win, d), tp = div_exact(tie, d);
-        const float lp = __fsub_rn(__fsub_rn(1.0f, wp), tp);
-        ev = __fsub_rn(wp, lp);
+    const Divisor d = make_divisor(den);
+    bool bad = false;
+    float wp = div_fast(win, d, bad), tp = div_fast(tie, d, bad);
+    if (bad) {
+        wp = __fdiv_rn(win, den);
+        tp = __fdiv_rn(tie, den);
     }
-    return allowed ? ev : 0.0f;
+    const float lp = __fsub_rn(__fsub_rn(1.0f, wp), tp);
+    const float ev = __fsub_rn(wp, lp);
+    return (allowed && den > 1e-8f) ? ev : 0.0f;
 }
 
 }  // namespace p2b
