@@ -33,7 +33,6 @@ namespace p2b {
 
 namespace {
 
-constexpr int kNatEntries = 52 * 51;
 constexpr int kBankRows = kCfrMaxChildren;  // child rows staged per node in the top-down sweep
 constexpr int kStageRows = 2 + 2 * kBankRows;  // top-down: two banks of child rows; bottom-up: 2 belief rows,
                                                // one marginal row and one leaf-belief row per child
@@ -49,10 +48,9 @@ constexpr int kOffCs = kOffPc + 2 * 52 * 52 * 4;
 constexpr int kOffWarpTot = kOffCs + kCsRows * 52 * 8;
 constexpr int kOffS = kOffWarpTot + 32 * 8;
 constexpr int kOffSig = kOffS + kCsRows * 8;
-constexpr int kOffNat = kOffSig + kCfrMaxNodes * 2 * 4;
-constexpr int kOffMisc = kOffNat + ((kNatEntries * 2 + 15) / 16) * 16;
+constexpr int kOffMisc = kOffSig + kCfrMaxNodes * 2 * 4;
 constexpr int kCfrSmem = kOffMisc + 64;
-static_assert(kOffXs % 16 == 0 && kOffCs % 8 == 0 && kOffNat % 16 == 0 && kOffSig % 8 == 0, "alignment");
+static_assert(kOffXs % 16 == 0 && kOffCs % 8 == 0 && kOffMisc % 16 == 0 && kOffSig % 8 == 0, "alignment");
 
 // VPT consecutive hands of one row
 template <int VPT>
@@ -157,7 +155,6 @@ struct Block {
     double* warp_tot;
     double* S;
     float* sig;    // [nodes][2] normalisation sums of the node beliefs of the current pass
-    uint16_t* nat;
     int* misc;
     float* fsum;
     // current subgame
@@ -300,7 +297,6 @@ __device__ __forceinline__ void node_tables(Block& B, int cs_row0, int n_cs, con
     const BoardTabView tv = view_tables(B.tab);
     const int tid = threadIdx.x, lane = tid & 31;
     const int quads_cs = n_cs * 208, quads = quads_cs + n_pc * 208;
-    const uint16_t* __restrict__ nat = B.nat;
     const uint16_t* __restrict__ cardlist = tv.cardlist;
     const uint16_t* __restrict__ sorted = tv.sorted;
     const int n_scan = 4 * n_pc, n_units = n_scan + n_cs + (quads + 31) / 32;
@@ -380,11 +376,22 @@ __device__ __forceinline__ void node_tables(Block& B, int cs_row0, int n_cs, con
             // (prefixes: contiguous); in both cases only i = 12 can fall outside the 51 entries,
             // and it does exactly when q = 3.
             float v[13];
-            const uint16_t* __restrict__ idx_base = is_cs ? nat + c * 51 + q : cardlist + 13 * q * 52 + c;
-            const int idx_step = is_cs ? 4 : 52;
+            if (is_cs) {
+                // e-th hand holding card c, in hand order: (e, c) for e < c, then (c, e + 1); its index
+                // is computed, not looked up: the round is bound by shared-memory traffic
+                const int row_part = combo_row_offset(c) - c;
 #pragma unroll
-            for (int i = 0; i < 12; ++i) v[i] = x[idx_base[i * idx_step]];
-            v[12] = q < 3 ? x[idx_base[12 * idx_step]] : 0.0f;
+                for (int i = 0; i < 13; ++i) {
+                    const int e = q + 4 * i;
+                    const int idx = e < c ? ((e * (103 - e)) >> 1) + (c - e - 1) : row_part + e;
+                    v[i] = (i < 12 || q < 3) ? x[idx] : 0.0f;
+                }
+            } else {
+                const uint16_t* __restrict__ idx_base = cardlist + 13 * q * 52 + c;
+#pragma unroll
+                for (int i = 0; i < 12; ++i) v[i] = x[idx_base[i * 52]];
+                v[12] = q < 3 ? x[idx_base[12 * 52]] : 0.0f;
+            }
             double t_even = 0.0, t_odd = 0.0;
 #pragma unroll
             for (int i = 0; i < 13; ++i) {
@@ -1121,17 +1128,11 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
     B.warp_tot = reinterpret_cast<double*>(smem + kOffWarpTot);
     B.S = reinterpret_cast<double*>(smem + kOffS);
     B.sig = reinterpret_cast<float*>(smem + kOffSig);
-    B.nat = reinterpret_cast<uint16_t*>(smem + kOffNat);
     B.misc = reinterpret_cast<int*>(smem + kOffMisc);
     B.fsum = reinterpret_cast<float*>(smem + kOffMisc + 16);
     if (threadIdx.x == 0) B.misc[2] = 0;  // unit counter of node_tables
     const int tid = threadIdx.x;
 
-    // hands holding each card, in combo order (used by the per-card sums)
-    for (int idx = tid; idx < kNatEntries; idx += NT) {
-        const int c = idx / 51, i = idx % 51, d = i < c ? i : i + 1;
-        B.nat[idx] = (uint16_t)(c < d ? combo_index(c, d) : combo_index(d, c));
-    }
     HandInfo<VPT> hi;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
