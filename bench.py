@@ -277,7 +277,7 @@ def finish_gpu_arm(args, rank, world, layout, ms_step, value, clocks, e2e, distr
         achieved = alg_bytes / (ms_step / 1e3) / 1e9
         # DRAM bytes per subgame-pass from the ncu capture of a small case (profiles/), scaled
         # to this launch by the number of subgame-passes (traffic grows in proportion)
-        traffic = 2.81e6 * BATCH * (ITERATIONS + 2)
+        traffic = 2.76e6 * BATCH * (ITERATIONS + 2)
         line = {
             "metric": "subgame-CFR-iterations/sec", "value": value, "unit": "subgame-iterations/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,

@@ -135,14 +135,16 @@ def build_device_layout(roots: ptree.RoundState, boards, bet_bins, max_depth: in
     with torch.cuda.device(device):
         _lib.call("p2b_tree_count", p(packed), B, bins, n_bins, D, cap, p(counts), p(level_counts), stream)
         # prefix sums over the subgames (plumbing): rows, model-leaf slots, level-major bases
+        # (scans run along the contiguous dimension of transposed copies: torch's scan along the
+        # outer dimension of a [B, few] tensor takes about a millisecond)
         c64 = counts.to(torch.int64)
-        csum = torch.cumsum(c64[:, :3], dim=0)
+        csum = torch.cumsum(c64[:, :3].t().contiguous(), dim=1).t()
         node_begin = (csum[:, 0] - c64[:, 0]).to(torch.int32)
         leaf_begin = (csum[:, 2] - c64[:, 2]).to(torch.int32)
         l64 = level_counts.to(torch.int64)
         level_tot = l64.sum(dim=0)
         depth_off = torch.cumsum(level_tot, dim=0) - level_tot
-        level_base = (torch.cumsum(l64, dim=0) - l64 + depth_off[None, :]).contiguous()
+        level_base = (torch.cumsum(l64.t().contiguous(), dim=1).t() - l64 + depth_off[None, :]).contiguous()
         stats = torch.cat([csum[-1, :3], c64[:, 0].max()[None], c64[:, 1].max()[None], c64[:, 3].sum()[None],
                            c64[:, 4].max()[None], c64[:, 5].sum()[None], c64[:, 6].max()[None], level_tot]).cpu().numpy()
     rows, n_model = int(stats[0]), int(stats[2])
