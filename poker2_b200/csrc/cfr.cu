@@ -49,7 +49,8 @@ constexpr int kOffWarpTot = kOffCs + kCsRows * 52 * 8;
 constexpr int kOffS = kOffWarpTot + 32 * 8;
 constexpr int kOffSig = kOffS + kCsRows * 8;
 constexpr int kOffMisc = kOffSig + kCfrMaxNodes * 2 * 4;
-constexpr int kCfrSmem = kOffMisc + 64;
+constexpr int kOffIlist = kOffMisc + 64;  // node index of every internal node, in node order
+constexpr int kCfrSmem = kOffIlist + ((kCfrMaxNodes + 15) / 16) * 16;
 static_assert(kOffXs % 16 == 0 && kOffCs % 8 == 0 && kOffMisc % 16 == 0 && kOffSig % 8 == 0, "alignment");
 
 // VPT consecutive hands of one row
@@ -156,6 +157,7 @@ struct Block {
     double* S;
     float* sig;    // [nodes][2] normalisation sums of the node beliefs of the current pass
     int* misc;
+    uint8_t* ilist;  // [n_internal] node index of the ii-th internal node
     float* fsum;
     // current subgame
     SubgameRec sg;
@@ -469,10 +471,10 @@ __device__ __forceinline__ void sweep_down(int mode, int pass, const CfrParams& 
 #pragma unroll
     for (int i = 0; i < VPT; ++i) mask.v[i] = hi.allowed[i] ? 1.0f : 0.0f;
     int parity = 0;
-    for (int j = 0; j < B.sg.n_nodes; ++j) {
+    for (int ii = 0; ii < B.sg.n_internal; ++ii) {
+        const int j = B.ilist[ii];
         const NodeRec nd = B.nodes[j];
-        if (nd.kind != kInternal) continue;
-        const int a = nd.to_act, k = nd.n_children, fc = nd.first_child, ii = nd.internal_idx;
+        const int a = nd.to_act, k = nd.n_children, fc = nd.first_child;
         auto node_body = [&](auto kc) {
         constexpr int K = decltype(kc)::value;
         FV<VPT> ra = mask, rna = mask, rba = mask, rbna = mask;
@@ -486,10 +488,8 @@ __device__ __forceinline__ void sweep_down(int mode, int pass, const CfrParams& 
         }
         if (mode != kPassInit) {
             // the next internal node's state rows are streamed from HBM: start them now
-            int jn = j + 1;
-            while (jn < B.sg.n_nodes && B.nodes[jn].kind != kInternal) ++jn;
-            if (jn < B.sg.n_nodes) {
-                const NodeRec nn = B.nodes[jn];
+            if (ii + 1 < B.sg.n_internal) {
+                const NodeRec nn = B.nodes[B.ilist[ii + 1]];
                 for (int c = 0; c < nn.n_children; ++c) {
                     prefetch_row<VPT>(B.row1(mode == kPassFinal ? p.policy_avg : p.regrets, nn.first_child + c), tid);
                     if (mix) prefetch_row<VPT>(B.row1(p.policy_avg, nn.first_child + c), tid);
@@ -716,10 +716,10 @@ __device__ __forceinline__ void sweep_up(int mode, int pass, const CfrParams& p,
     FV<VPT> mask;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) mask.v[i] = hi.allowed[i] ? 1.0f : 0.0f;
-    for (int j = B.sg.n_nodes - 1; j >= 0; --j) {
+    for (int ii = B.sg.n_internal - 1; ii >= 0; --ii) {
+        const int j = B.ilist[ii];
         const NodeRec nd = B.nodes[j];
-        if (nd.kind != kInternal) continue;
-        const int a = nd.to_act, o = 1 - a, k = nd.n_children, fc = nd.first_child, ii = nd.internal_idx;
+        const int a = nd.to_act, o = 1 - a, k = nd.n_children, fc = nd.first_child;
         auto node_body = [&](auto kc) {
         constexpr int K = decltype(kc)::value;
         const FV<VPT> prior_a = pick<VPT>(prior, a), prior_o = pick<VPT>(prior, o);
@@ -747,10 +747,8 @@ __device__ __forceinline__ void sweep_up(int mode, int pass, const CfrParams& p,
             }
         }
         {
-            int jn = j - 1;
-            while (jn >= 0 && B.nodes[jn].kind != kInternal) --jn;
-            if (jn >= 0) {
-                const NodeRec nn = B.nodes[jn];
+            if (ii > 0) {
+                const NodeRec nn = B.nodes[B.ilist[ii - 1]];
                 for (int c = 0; c < nn.n_children; ++c) {
                     prefetch_row<VPT>(B.row1(mode == kPassFinal ? p.policy_avg : p.regrets, nn.first_child + c), tid);
                     if (update && p.weight_sums) prefetch_row<VPT>(B.row1(p.weight_sums, nn.first_child + c), tid);
@@ -1129,6 +1127,7 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
     B.S = reinterpret_cast<double*>(smem + kOffS);
     B.sig = reinterpret_cast<float*>(smem + kOffSig);
     B.misc = reinterpret_cast<int*>(smem + kOffMisc);
+    B.ilist = smem + kOffIlist;
     B.fsum = reinterpret_cast<float*>(smem + kOffMisc + 16);
     if (threadIdx.x == 0) B.misc[2] = 0;  // unit counter of node_tables
     const int tid = threadIdx.x;
@@ -1181,6 +1180,11 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
         } else {
             root_b[0] = ldv<VPT>(p.root_beliefs + ((long long)s * 2 + 0) * P2B_HPAD, tid);
             root_b[1] = ldv<VPT>(p.root_beliefs + ((long long)s * 2 + 1) * P2B_HPAD, tid);
+        }
+        __syncthreads();
+        for (int i = tid; i < B.sg.n_nodes; i += NT) {
+            const NodeRec nd = B.nodes[i];
+            if (nd.kind == kInternal && nd.internal_idx < B.sg.n_internal) B.ilist[nd.internal_idx] = (uint8_t)i;
         }
         __syncthreads();
 
@@ -1266,6 +1270,18 @@ __global__ void __launch_bounds__(kCfrMaxNodes) cfr_validate_kernel(const CfrPar
             (nd.n_children < 1 || nd.n_children > kCfrMaxChildren || nd.first_child <= i ||
              nd.first_child + nd.n_children > sg.n_nodes || nd.internal_idx >= p.max_internal))
             bad = 1;
+    }
+    // internal_idx must be the rank among the subgame's internal nodes (the solver walks them
+    // through a list indexed by it) and n_internal their number
+    __shared__ uint8_t s_internal[kCfrMaxNodes];
+    const bool in_tree = !bad && i < sg.n_nodes;
+    s_internal[i] = in_tree && p.nodes[sg.node_begin + i].kind == kInternal;
+    __syncthreads();
+    if (in_tree) {
+        int before = 0;
+        for (int j = 0; j < i; ++j) before += s_internal[j];
+        if (s_internal[i] && before != p.nodes[sg.node_begin + i].internal_idx) bad = 1;
+        if (i == sg.n_nodes - 1 && before + s_internal[i] != sg.n_internal) bad = 1;
     }
     if (__syncthreads_or(bad) && i == 0) {
         atomicMax(p.work_counter + 1, s + 1);

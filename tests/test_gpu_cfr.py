@@ -177,6 +177,16 @@ def test_malformed_subgame_is_reported_and_nothing_runs(cuda_device, golden_dir)
     res = sv.solve(rb, solver.iteration_scalars(int(z["iterations"])))
     assert sv.status() == victim + 1
     assert bool((res.root_values == -7.0).all())  # nothing was solved
+    # two internal nodes claiming the same rank among the internal nodes are refused as well
+    layout2 = solver.device_layout(trees, z["boards"].astype(np.int64))
+    victim2 = 1
+    lo, n = int(layout2.subgames[victim2]["node_begin"]), int(layout2.subgames[victim2]["n_nodes"])
+    internal = [i for i in range(lo, lo + n) if layout2.nodes[i]["kind"] == 0]
+    layout2.nodes[internal[2]]["internal_idx"] = layout2.nodes[internal[1]]["internal_idx"]
+    sv2 = solver.SubgameSolver(layout2, boards, cuda_device)
+    sv2.root_values.fill_(-7.0)
+    res_bad = sv2.solve(rb, solver.iteration_scalars(int(z["iterations"])))
+    assert sv2.status() == victim2 + 1 and bool((res_bad.root_values == -7.0).all())
     # a well-formed batch reports nothing and is solved
     ok = solver.SubgameSolver(clean.layout, boards, cuda_device)
     res2 = ok.solve(rb, solver.iteration_scalars(int(z["iterations"])))
