@@ -826,6 +826,23 @@ __device__ __forceinline__ void sweep_up(int mode, int pass, const CfrParams& p,
             acc_a.v[i] = acc_o.v[i] = 0.0f;
         }
         if (first_sd >= 0) showdown_ev<VPT>(B, hi, tid, B.stage_row(1), B.pref, B.pc, eva);
+        // Further showdown children (rare: none in a river tree): one more round each builds the
+        // child's tables in slot 0 (the acting player's EV, the only user of slot 0, is already in
+        // registers) and the opponent's EV replaces the child's staged beliefs, of which a thread
+        // reads its own two entries only.  Kept out of the unrolled loop below: one copy of the
+        // round's code per node body instead of one per child.
+        if (first_sd >= 0) {
+#pragma unroll 1
+            for (int c = first_sd + 1; c < k; ++c) {
+                if (B.nodes[fc + c].kind != kShowdownLeaf) continue;
+                __syncthreads();
+                int pc_rows[2] = {kRowLeaf + c, kRowLeaf + c};
+                node_tables(B, 0, 0, pc_rows, 1);
+                FV<VPT> evo;
+                showdown_ev<VPT>(B, hi, tid, B.stage_row(kRowLeaf + c), B.pref, B.pc, evo);
+                stv<VPT>(B.stage_row(kRowLeaf + c), tid, evo);
+            }
+        }
 
 #pragma unroll
         for (int c = 0; c < K; ++c) {
@@ -863,12 +880,7 @@ __device__ __forceinline__ void sweep_up(int mode, int pass, const CfrParams& p,
                 if (c == first_sd) {
                     showdown_ev<VPT>(B, hi, tid, B.stage_row(kRowLeaf + c), B.pref + P2B_HPAD, B.pc + 52 * 52, evo);
                 } else {
-                    // a further showdown child: another round builds its tables in slot 0 (the
-                    // acting player's EV, the only user of slot 0, is already in registers)
-                    __syncthreads();
-                    int pc_rows[2] = {kRowLeaf + c, kRowLeaf + c};
-                    node_tables(B, 0, 0, pc_rows, 1);
-                    showdown_ev<VPT>(B, hi, tid, B.stage_row(kRowLeaf + c), B.pref, B.pc, evo);
+                    evo = ldv<VPT>(B.stage_row(kRowLeaf + c), tid);  // computed above
                 }
                 const float pot_a = a == 0 ? ch.v0 : ch.v1, pot_o = a == 0 ? ch.v1 : ch.v0;
                 const Divisor dscale = make_divisor(B.sg.scale);
