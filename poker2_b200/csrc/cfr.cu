@@ -184,7 +184,7 @@ struct Block {
 template <int VPT, int K>
 __device__ __forceinline__ void children_policy(int mode, const CfrParams& p, const Block& B, int fc, int k, int tid,
                                                 FV<VPT> (&P)[K], FV<VPT> (&Rc)[K]) {
-    const float invk = __fdiv_rn(1.0f, (float)k);
+    constexpr float invk = 1.0f / (float)K;  // K == k; folded at compile time, correctly rounded
     if (mode == kPassInit) {
 #pragma unroll
         for (int c = 0; c < K; ++c) {
