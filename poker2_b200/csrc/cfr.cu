@@ -84,6 +84,15 @@ template <int VPT>
 __device__ __forceinline__ void prefetch_row(const float* row, int tid) {
     asm volatile("prefetch.global.L2 [%0];" ::"l"(row + VPT * tid));
 }
+// The same for the n (<= kCfrMaxChildren) consecutive rows that start at `row` (the rows of the
+// children of one node): one address computation, fixed offsets.
+template <int VPT>
+__device__ __forceinline__ void prefetch_rows(const float* row, int n, int tid) {
+    const float* mine = row + VPT * tid;
+#pragma unroll
+    for (int c = 0; c < kCfrMaxChildren; ++c)
+        if (c < n) asm volatile("prefetch.global.L2 [%0];" ::"l"(mine + c * P2B_HPAD));
+}
 
 // x[which] without indexing a register array by a run-time value
 template <int VPT>
@@ -490,10 +499,8 @@ __device__ __forceinline__ void sweep_down(int mode, int pass, const CfrParams& 
             // the next internal node's state rows are streamed from HBM: start them now
             if (ii + 1 < B.sg.n_internal) {
                 const NodeRec nn = B.nodes[B.ilist[ii + 1]];
-                for (int c = 0; c < nn.n_children; ++c) {
-                    prefetch_row<VPT>(B.row1(mode == kPassFinal ? p.policy_avg : p.regrets, nn.first_child + c), tid);
-                    if (mix) prefetch_row<VPT>(B.row1(p.policy_avg, nn.first_child + c), tid);
-                }
+                prefetch_rows<VPT>(B.row1(mode == kPassFinal ? p.policy_avg : p.regrets, nn.first_child), nn.n_children, tid);
+                if (mix) prefetch_rows<VPT>(B.row1(p.policy_avg, nn.first_child), nn.n_children, tid);
             }
         }
         FV<VPT> P[K], Rc[K], Pbs[K];
@@ -749,10 +756,8 @@ __device__ __forceinline__ void sweep_up(int mode, int pass, const CfrParams& p,
         {
             if (ii > 0) {
                 const NodeRec nn = B.nodes[B.ilist[ii - 1]];
-                for (int c = 0; c < nn.n_children; ++c) {
-                    prefetch_row<VPT>(B.row1(mode == kPassFinal ? p.policy_avg : p.regrets, nn.first_child + c), tid);
-                    if (update && p.weight_sums) prefetch_row<VPT>(B.row1(p.weight_sums, nn.first_child + c), tid);
-                }
+                prefetch_rows<VPT>(B.row1(mode == kPassFinal ? p.policy_avg : p.regrets, nn.first_child), nn.n_children, tid);
+                if (update && p.weight_sums) prefetch_rows<VPT>(B.row1(p.weight_sums, nn.first_child), nn.n_children, tid);
             }
         }
         FV<VPT> P[K], Rc[K], Va[K], acc_a, acc_o;
