@@ -56,6 +56,14 @@ __global__ void division_selftest_kernel(uint64_t pairs_per_thread, uint32_t see
         const float got = div_exact(x, d), want = __fdiv_rn(x, y);
         const bool both_nan = (got != got) && (want != want);
         if (__float_as_uint(got) != __float_as_uint(want) && !both_nan) ++bad;
+        // the grouped form the solver uses: branch-free quotient, one fallback for the group
+        // (a group of one here), in both numerator conventions
+        bool redo = false, redo_nn = false;
+        float g1 = div_fast(x, d, redo), g2 = div_fast<true>(x, d, redo_nn);
+        if (redo) g1 = want;
+        if (redo_nn) g2 = want;
+        if (__float_as_uint(g1) != __float_as_uint(want) && !both_nan) ++bad;
+        if (__float_as_uint(g2) != __float_as_uint(want) && !both_nan) ++bad;
         const uint32_t ax = __float_as_uint(x) & 0x7fffffffu;
         if (d.ok && (exactdiv_in_range(ax) || ax == 0u)) ++fast;
     }
