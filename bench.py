@@ -456,7 +456,8 @@ def run_street(args, rank: int, world: int, local_rank: int):
     def step():
         res, trees, sv = solver.solve_subgames_with_model(
             boards, ranges, pot, stack, model, street=street, iterations=iterations, bet_bins=BET_BINS,
-            max_depth=MAX_DEPTH, max_raises=MAX_RAISES, device=device, exploitability=True, chunk=args.leaf_chunk)
+            max_depth=MAX_DEPTH, max_raises=MAX_RAISES, device=device, exploitability=True, chunk=args.leaf_chunk,
+            device_tree=True)
         if distributed:
             sharding.gather_rows(res.root_values)
             sharding.reduce_exploitability(res.exploitability)
