@@ -33,3 +33,21 @@ def test_product_does_not_import_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h")):
                 src = open(os.path.join(dirpath, f)).read()
                 assert "import oracle" not in src and "from oracle" not in src, f
+
+
+def test_tree_builder_rejects_bad_arguments_without_a_gpu():
+    """Argument checks come before any CUDA call: status code and message, no launch."""
+    from poker2_b200 import _lib, build
+
+    build.build()
+    handle = _lib.lib()
+    bins = (ctypes.c_float * 16)(*([0.5] * 16))
+    dummy = (ctypes.c_int32 * 64)()
+    p = ctypes.cast(dummy, ctypes.c_void_p)
+    assert handle.p2b_tree_count(p, 1, bins, 14, 4, -1, p, p, None) == -1  # too many bet bins
+    assert b"bet bins" in handle.p2b_last_error()
+    assert handle.p2b_tree_count(p, 1, bins, 2, 64, -1, p, p, None) == -1  # depth beyond the limit
+    assert b"max_depth" in handle.p2b_last_error()
+    assert handle.p2b_tree_count(None, 1, bins, 2, 4, -1, p, p, None) == -1  # null roots
+    assert handle.p2b_tree_records(p, None, 5, 1, bins, 2, 4, -1, p, p, p, p, p, p, None, None, None) == -1
+    assert handle.p2b_tree_count(p, 0, bins, 2, 4, -1, p, p, None) == 0  # empty batch: nothing to do
