@@ -170,6 +170,65 @@ class SubgameEvaluator:
         return SampledStates(nodes=cont, beliefs=cont_beliefs, state=self.trees.state.take(cont_np),
                              boards=self.boards[self.trees.root_of[cont_np]], all_nodes=nodes)
 
+    # ------------------------------------------------------------------ state by the upstream names
+    # (cfr_evaluator.py:107-170; tests and tools read these attributes).  Node order and widths are
+    # the upstream ones: level-major over the batch, 1326 columns.  Available after evaluate_cfr.
+    def _solved(self):
+        if self._result is None:
+            raise RuntimeError("call evaluate_cfr first")
+        return self._result
+
+    @property
+    def policy_probs_avg(self) -> torch.Tensor:
+        r = self._solved()
+        return r.level_major(r.policy_avg)
+
+    @property
+    def cumulative_regrets(self) -> torch.Tensor:
+        r = self._solved()
+        return r.level_major(r.regrets)
+
+    @property
+    def regret_weight_sums(self) -> torch.Tensor:
+        r = self._solved()
+        return r.level_major(r.weight_sums)
+
+    @property
+    def policy_probs_sample(self) -> torch.Tensor:
+        r = self._solved()
+        return r.level_major(r.policy_sample)
+
+    @property
+    def values_avg(self) -> torch.Tensor:
+        r = self._solved()
+        return r.level_major(r.values_avg)
+
+    @property
+    def beliefs_avg(self) -> torch.Tensor:
+        r = self._solved()
+        return r.level_major(r.beliefs_avg)
+
+    @property
+    def beliefs(self) -> torch.Tensor:
+        """Beliefs of the last iteration (internal nodes and model leaves; zero elsewhere)."""
+        r = self._solved()
+        return r.level_major(r.beliefs_last)
+
+    @property
+    def depth_offsets(self) -> list:
+        return list(self.trees.depth_offsets)
+
+    def _topology(self, name: str) -> torch.Tensor:
+        return torch.from_numpy(np.ascontiguousarray(getattr(self.trees, name)))
+
+    parent_index = property(lambda self: self._topology("parent_index"))
+    action_from_parent = property(lambda self: self._topology("action_from_parent"))
+    child_count = property(lambda self: self._topology("child_count"))
+    child_offsets = property(lambda self: self._topology("child_offsets"))
+    prev_actor = property(lambda self: self._topology("prev_actor"))
+    legal_mask = property(lambda self: self._topology("legal_mask"))
+    leaf_mask = property(lambda self: self._topology("leaf_mask"))
+
     # ------------------------------------------------------------------ training_data
     def training_data(self, exclude_start: bool = True):
         """(value batch, pre-chance value batch, policy batch) as upstream

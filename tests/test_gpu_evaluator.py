@@ -70,6 +70,16 @@ def test_evaluator_with_warm_start_runs_stepped(cuda_device, golden_dir):
     torch.testing.assert_close(value_batch.value_targets.cpu(), torch.from_numpy(z["root_values"]).clamp(-1, 1),
                                rtol=1e-5, atol=1e-6)
     assert np.array_equal(ev.t_sample.numpy(), z["t_sample"])  # same generator seed as the upstream run
+    # the solver state under the upstream attribute names, upstream node order
+    n = ev.root_nodes
+    close = lambda a, b: torch.testing.assert_close(a.cpu(), torch.from_numpy(b), rtol=1e-5, atol=1e-6)  # noqa: E731
+    close(ev.cumulative_regrets[n:], z["regrets"][n:])
+    close(ev.regret_weight_sums[n:], z["weight_sums"][n:])
+    close(ev.policy_probs_avg[n:], z["policy_avg"][n:])
+    close(ev.policy_probs_sample[n:], z["policy_sample"][n:])
+    assert ev.values_avg.shape == (int(z["total_nodes"]), 2, 1326) and ev.beliefs.shape == ev.values_avg.shape
+    assert ev.depth_offsets[-1] == int(z["total_nodes"]) and ev.parent_index.shape[0] == int(z["total_nodes"])
+    assert int(ev.child_count.sum()) == int(z["total_nodes"]) - n and ev.legal_mask.shape[1] == 5
     ev.evaluate_cfr()  # uniform start policy
     value_batch, _, policy_batch = ev.training_data()
     assert torch.isfinite(value_batch.value_targets).all() and torch.isfinite(policy_batch.policy_targets).all()
