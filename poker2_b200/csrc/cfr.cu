@@ -472,9 +472,12 @@ __device__ __forceinline__ void dispatch_children(int k, Body&& body) {
 }
 
 // ---- top-down sweep of one pass -------------------------------------------------------
-template <int VPT, int MAXC>
-__device__ __forceinline__ void sweep_down(int mode, int pass, const CfrParams& p, Block& B, const HandInfo<VPT>& hi,
+template <int VPT, int MAXC, int FIXED_MODE>
+__device__ __forceinline__ void sweep_down(int mode_rt, int pass, const CfrParams& p, Block& B, const HandInfo<VPT>& hi,
                                            const FV<VPT> (&prior)[2], int tid) {
+    // FIXED_MODE >= 0: compiled for that kind of pass alone (the iteration passes: the start- and
+    // final-pass code stays out of the hot loop); otherwise the kind is a run-time value
+    const int mode = FIXED_MODE >= 0 ? FIXED_MODE : mode_rt;
     const bool mix = (mode == kPassIter) && p.scalars[pass].do_mix != 0;
     FV<VPT> mask;
 #pragma unroll
@@ -715,9 +718,10 @@ __device__ __forceinline__ void sweep_down(int mode, int pass, const CfrParams& 
 // the per-hand arithmetic with no further barrier.  Staging rows: 0 = beliefs of the
 // acting player, 1 = of the other player, 2+c = marginal policy of child c, 8+c = beliefs
 // of the acting player at showdown child c.
-template <int VPT, int MAXC>
-__device__ __forceinline__ void sweep_up(int mode, int pass, const CfrParams& p, Block& B, const HandInfo<VPT>& hi,
+template <int VPT, int MAXC, int FIXED_MODE>
+__device__ __forceinline__ void sweep_up(int mode_rt, int pass, const CfrParams& p, Block& B, const HandInfo<VPT>& hi,
                                          const FV<VPT> (&prior)[2], const FV<VPT> (&root_b)[2], int s, int tid) {
+    const int mode = FIXED_MODE >= 0 ? FIXED_MODE : mode_rt;
     const bool update = (mode != kPassFinal) && (pass + 1 < p.iterations);
     constexpr int kRowM = 2, kRowLeaf = 2 + kBankRows;
     FV<VPT> mask;
@@ -1228,8 +1232,13 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
                 // a child's row of the player who did not act is the root's row; so is its sum
                 if (tid < 2) B.sig[tid] = B.fsum[tid];
             }
-            if (run_down) sweep_down<VPT, MAXC>(mode, pass, p, B, hi, prior, tid);
-            if (run_up) sweep_up<VPT, MAXC>(mode, pass, p, B, hi, prior, root_b, s, tid);
+            if (mode == kPassIter) {
+                if (run_down) sweep_down<VPT, MAXC, kPassIter>(mode, pass, p, B, hi, prior, tid);
+                if (run_up) sweep_up<VPT, MAXC, kPassIter>(mode, pass, p, B, hi, prior, root_b, s, tid);
+            } else {
+                if (run_down) sweep_down<VPT, MAXC, -1>(mode, pass, p, B, hi, prior, tid);
+                if (run_up) sweep_up<VPT, MAXC, -1>(mode, pass, p, B, hi, prior, root_b, s, tid);
+            }
         }
         if (p.stepped) {
             __syncthreads();
