@@ -235,7 +235,7 @@ __device__ __forceinline__ void children_policy(int mode, const CfrParams& p, co
 #pragma unroll
             for (int i = 0; i < VPT; ++i) P[c].v[i] = div_fast<true>(fmaxf(Rc[c].v[i], 0.0f), ds[i], bad);
         }
-    if (bad) {
+    if (__builtin_expect(bad, 0)) {
 #pragma unroll
         for (int c = 0; c < K; ++c)
             {
@@ -260,7 +260,7 @@ __device__ __forceinline__ void apply_norm(const Block& B, const HandInfo<VPT>& 
     FV<VPT> q;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) q.v[i] = div_fast<true>(x.v[i], d, bad);
-    if (bad) {
+    if (__builtin_expect(bad, 0)) {
 #pragma unroll
         for (int i = 0; i < VPT; ++i) q.v[i] = __fdiv_rn(x.v[i], sum);
     }
@@ -595,7 +595,7 @@ __device__ __forceinline__ void sweep_down(int mode_rt, int pass, const CfrParam
                             num.v[i] = __fadd_rn(__fmul_rn(ro.v[i], Pb.v[i]), __fmul_rn(rn.v[i], P[c].v[i]));
                             Pn[c].v[i] = div_fast<true>(num.v[i], dmix[i], bad);
                         }
-                        if (bad) {
+                        if (__builtin_expect(bad, 0)) {
 #pragma unroll
                             for (int i = 0; i < VPT; ++i) Pn[c].v[i] = __fdiv_rn(num.v[i], dmix[i].y);
                         }
@@ -614,7 +614,7 @@ __device__ __forceinline__ void sweep_down(int mode_rt, int pass, const CfrParam
 #pragma unroll
                             for (int i = 0; i < VPT; ++i) Q[c].v[i] = div_fast<true>(Pn[c].v[i], dsum[i], bad);
                         }
-                    if (bad) {
+                    if (__builtin_expect(bad, 0)) {
 #pragma unroll
                         for (int c = 0; c < K; ++c)
                             {
@@ -866,7 +866,7 @@ __device__ __forceinline__ void sweep_up(int mode_rt, int pass, const CfrParams&
                     blk.v[i] = unblocked(B.cs + (kRowM + c) * 52, B.S[kRowM + c], hi.c1[i], hi.c2[i], m);
                     pio.v[i] = div_fast<true>(blk.v[i], ddenm[i], bad);
                 }
-                if (bad) {
+                if (__builtin_expect(bad, 0)) {
 #pragma unroll
                     for (int i = 0; i < VPT; ++i) pio.v[i] = __fdiv_rn(blk.v[i], denm.v[i]);
                 }
@@ -899,7 +899,7 @@ __device__ __forceinline__ void sweep_up(int mode_rt, int pass, const CfrParams&
                     V_a.v[i] = div_fast(__fmul_rn(eva.v[i], pot_a), dscale, bad);
                     V_o.v[i] = div_fast(__fmul_rn(evo.v[i], pot_o), dscale, bad);
                 }
-                if (bad) {
+                if (__builtin_expect(bad, 0)) {
 #pragma unroll
                     for (int i = 0; i < VPT; ++i) {
                         V_a.v[i] = __fdiv_rn(__fmul_rn(eva.v[i], pot_a), B.sg.scale);
@@ -967,7 +967,7 @@ __device__ __forceinline__ void sweep_up(int mode_rt, int pass, const CfrParams&
                         rq.v[i] = div_fast(rn.v[i], d[i], bad);
                         wq.v[i] = div_fast<true>(wn.v[i], d[i], bad);
                     }
-                    if (bad) {
+                    if (__builtin_expect(bad, 0)) {
 #pragma unroll
                         for (int i = 0; i < VPT; ++i) {
                             rq.v[i] = __fdiv_rn(rn.v[i], d[i].y);

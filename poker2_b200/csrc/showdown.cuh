@@ -68,7 +68,7 @@ __device__ __forceinline__ float showdown_hand_ev(const HandRec r, int c1, int c
     const Divisor d = make_divisor(den);
     bool bad = false;
     float wp = div_fast(win, d, bad), tp = div_fast(tie, d, bad);
-    if (bad) {
+    if (__builtin_expect(bad, 0)) {
         wp = __fdiv_rn(win, den);
         tp = __fdiv_rn(tie, den);
     }
