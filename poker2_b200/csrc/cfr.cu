@@ -472,11 +472,22 @@ __device__ __forceinline__ void dispatch_children(int k, Body&& body) {
 }
 
 // ---- top-down sweep of one pass -------------------------------------------------------
-template <int VPT, int MAXC, int FIXED_MODE>
-__device__ __forceinline__ void sweep_down(int mode_rt, int pass, const CfrParams& p, Block& B, const HandInfo<VPT>& hi,
+template <int VPT, int MAXC, int FIXED_MODE, bool PLAIN>
+__device__ __forceinline__ void sweep_down(int mode_rt, int pass, const CfrParams& p_in, Block& B, const HandInfo<VPT>& hi,
                                            const FV<VPT> (&prior)[2], int tid) {
-    // FIXED_MODE >= 0: compiled for that kind of pass alone (the iteration passes: the start- and
-    // final-pass code stays out of the hot loop); otherwise the kind is a run-time value
+    // PLAIN: a solve without model leaves, sampling outputs or a kept current policy; their code
+    // is compiled out of this variant
+    CfrParams p = p_in;
+    if (PLAIN) {
+        p.leaf_beliefs = nullptr;
+        p.leaf_values = nullptr;
+        p.policy_sample = nullptr;
+        p.beliefs_last = nullptr;
+        p.policy = nullptr;
+        p.start_policy = nullptr;
+    }
+    // FIXED_MODE >= 0: compiled for that kind of pass alone (the iteration passes of a plain solve:
+    // the start- and final-pass code stays out of the hot loop); otherwise the kind is a run-time value
     const int mode = FIXED_MODE >= 0 ? FIXED_MODE : mode_rt;
     const bool mix = (mode == kPassIter) && p.scalars[pass].do_mix != 0;
     FV<VPT> mask;
@@ -718,9 +729,20 @@ __device__ __forceinline__ void sweep_down(int mode_rt, int pass, const CfrParam
 // the per-hand arithmetic with no further barrier.  Staging rows: 0 = beliefs of the
 // acting player, 1 = of the other player, 2+c = marginal policy of child c, 8+c = beliefs
 // of the acting player at showdown child c.
-template <int VPT, int MAXC, int FIXED_MODE>
-__device__ __forceinline__ void sweep_up(int mode_rt, int pass, const CfrParams& p, Block& B, const HandInfo<VPT>& hi,
+template <int VPT, int MAXC, int FIXED_MODE, bool PLAIN>
+__device__ __forceinline__ void sweep_up(int mode_rt, int pass, const CfrParams& p_in, Block& B, const HandInfo<VPT>& hi,
                                          const FV<VPT> (&prior)[2], const FV<VPT> (&root_b)[2], int s, int tid) {
+    // PLAIN: a solve without model leaves, sampling outputs or a kept current policy; their code
+    // is compiled out of this variant
+    CfrParams p = p_in;
+    if (PLAIN) {
+        p.leaf_beliefs = nullptr;
+        p.leaf_values = nullptr;
+        p.policy_sample = nullptr;
+        p.beliefs_last = nullptr;
+        p.policy = nullptr;
+        p.start_policy = nullptr;
+    }
     const int mode = FIXED_MODE >= 0 ? FIXED_MODE : mode_rt;
     const bool update = (mode != kPassFinal) && (pass + 1 < p.iterations);
     constexpr int kRowM = 2, kRowLeaf = 2 + kBankRows;
@@ -1209,6 +1231,9 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
         }
         __syncthreads();
 
+        // a one-launch solve without optional outputs takes the leanest copy of the sweeps
+        const bool plain = !p.stepped && !p.leaf_beliefs && !p.leaf_values && !p.policy_sample && !p.beliefs_last &&
+                           !p.policy && !p.start_policy;
         for (int pass = pass_first; pass <= pass_last; ++pass) {
             const int mode = pass < 0 ? kPassInit : (pass == p.iterations ? kPassFinal : kPassIter);
             if (!run_down) {
@@ -1232,12 +1257,12 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
                 // a child's row of the player who did not act is the root's row; so is its sum
                 if (tid < 2) B.sig[tid] = B.fsum[tid];
             }
-            if (mode == kPassIter) {
-                if (run_down) sweep_down<VPT, MAXC, kPassIter>(mode, pass, p, B, hi, prior, tid);
-                if (run_up) sweep_up<VPT, MAXC, kPassIter>(mode, pass, p, B, hi, prior, root_b, s, tid);
-            } else {
-                if (run_down) sweep_down<VPT, MAXC, -1>(mode, pass, p, B, hi, prior, tid);
-                if (run_up) sweep_up<VPT, MAXC, -1>(mode, pass, p, B, hi, prior, root_b, s, tid);
+            if (mode == kPassIter && plain) {
+                sweep_down<VPT, MAXC, kPassIter, true>(mode, pass, p, B, hi, prior, tid);
+                sweep_up<VPT, MAXC, kPassIter, true>(mode, pass, p, B, hi, prior, root_b, s, tid);
+            } else {  // start and final passes; every pass of a stepped solve or one with optional outputs
+                if (run_down) sweep_down<VPT, MAXC, -1, false>(mode, pass, p, B, hi, prior, tid);
+                if (run_up) sweep_up<VPT, MAXC, -1, false>(mode, pass, p, B, hi, prior, root_b, s, tid);
             }
         }
         if (p.stepped) {
