@@ -77,16 +77,23 @@ int p2b_showdown_values(const unsigned char* tables, const int32_t* table_of_row
  *  exploitability [num_subgames], br_values [num_subgames,2] out (may be NULL; need values_avg):
  *             local exploitability of the average policy and the best-response value of each
  *             player at the root (cfr_evaluator.py:718-764)
- *  scratch    p2b_cfr_scratch_floats(max_internal, num_blocks) floats of work space
+ *  rows       number of rows of the state arrays (the record check refuses subgames that reach past it)
+ *  scratch    at least p2b_cfr_scratch_floats(max_internal, num_blocks) floats of work space.  With
+ *             p2b_cfr_solve_scratch_floats(max_internal, max_children, num_blocks, num_subgames, rows)
+ *             floats a solve without the optional outputs policy / policy_sample / beliefs_last runs as
+ *             four launches (start pass; iteration passes in a leaner kernel, or in the general one for
+ *             trees with more than one showdown child under a node; final pass) with the same results,
+ *             bit for bit; the extra floats carry the root rows between the launches
  *  scalars    [iterations] 32-byte records {float t^alpha, t^alpha+1, t^beta, t^beta+1,
  *             mix_old, mix_new, fl(mix_old+mix_new); int32 do_mix}
  *  init_depth depth of the deepest tree of the batch (the upstream start pass re-normalises
  *             every belief row once per level of the batch-wide tree)
- *  work_counter two int32, zeroed by the call: [0] the queue the thread blocks take subgames
- *             from; [1] status.  Before solving, a checking kernel compares every subgame's
- *             records with the solver's limits (1..160 nodes per subgame, 1..6 children per
- *             internal node, children stored after their parent and inside the subgame,
- *             internal_idx < max_internal, root internal, a table for every showdown leaf).
+ *  work_counter four int32, zeroed by the call: [0] the queue the thread blocks take subgames
+ *             from; [1] status; [2], [3] internal.  Before every launch a checking kernel compares
+ *             every subgame's records with the solver's limits (1..160 nodes per subgame, all
+ *             inside the `rows` rows, 1..6 children per internal node, children stored after their
+ *             parent and inside the subgame, internal_idx < max_internal, to_act 0 or 1, root
+ *             internal, a table for every showdown leaf, a slot for every model leaf).
  *             On a violation status = 1 + the index of an offending subgame and NOTHING is
  *             solved (outputs untouched); otherwise status stays 0
  *  num_blocks 0 = one block per SM
@@ -97,7 +104,7 @@ int p2b_showdown_values(const unsigned char* tables, const int32_t* table_of_row
  *             sample_pass is outside 0..iterations-1 are left untouched
  *  beliefs_last [rows,2,1344] out (may be NULL): beliefs of the last iteration at the internal
  *             nodes (what sample_leaves returns for the sampled nodes). */
-int p2b_cfr_solve(const void* subgames, const void* nodes, int32_t num_subgames, int32_t max_children,
+int p2b_cfr_solve(const void* subgames, const void* nodes, int32_t num_subgames, int64_t rows, int32_t max_children,
                   int32_t max_internal, const unsigned char* tables, const float* root_beliefs,
                   float* regrets, float* weight_sums, float* policy_avg, float* policy,
                   float* root_values, float* values_avg, float* beliefs_avg, float* exploitability,
@@ -105,6 +112,8 @@ int p2b_cfr_solve(const void* subgames, const void* nodes, int32_t num_subgames,
                   int32_t init_depth, int32_t* work_counter, int32_t num_blocks, const int32_t* sample_pass,
                   float* policy_sample, float* beliefs_last, void* stream);
 int64_t p2b_cfr_scratch_floats(int32_t max_internal, int32_t num_blocks);
+int64_t p2b_cfr_solve_scratch_floats(int32_t max_internal, int32_t max_children, int32_t num_blocks,
+                                     int32_t num_subgames, int64_t rows);
 int p2b_cfr_default_blocks(void);
 
 /* p2b_cfr_step -- part of a solve, for subgames whose non-terminal leaves (start of the next
@@ -120,20 +129,20 @@ int p2b_cfr_default_blocks(void);
  *               work rows per subgame instead of per block)
  *  carry_sums   [rows,2] floats, carry_roots [num_subgames,4,1344] floats (opaque)
  *  leaf_begin   [num_subgames] int32: first leaf slot of each subgame; a node of kind 3 uses
- *               slot leaf_begin[subgame] + its internal_idx field
+ *               slot leaf_begin[subgame] + its internal_idx field; leaf_slots = number of slots
  *  leaf_beliefs [slots,2,1344] out (top-down sweep): both players' beliefs at each such leaf
  *  leaf_values  [slots,2,1344] in (bottom-up sweep): both players' values there, in the units
  *               of the other leaf values (chips / scale)
  * With leaf_beliefs == NULL / leaf_values == NULL such leaves are skipped / valued 0. */
-int p2b_cfr_step(const void* subgames, const void* nodes, int32_t num_subgames, int32_t max_children,
+int p2b_cfr_step(const void* subgames, const void* nodes, int32_t num_subgames, int64_t rows, int32_t max_children,
                  int32_t max_internal, const unsigned char* tables, const float* root_beliefs,
                  float* regrets, float* weight_sums, float* policy_avg, float* policy,
                  float* root_values, float* values_avg, float* beliefs_avg, float* exploitability,
                  float* br_values, float* scratch, int64_t scratch_floats, const void* scalars,
                  int32_t iterations, int32_t cfr_plus, int32_t init_depth, int32_t* work_counter,
                  int32_t num_blocks, int32_t pass_begin, int32_t pass_end, int32_t phases,
-                 float* carry_sums, float* carry_roots, const int32_t* leaf_begin, float* leaf_beliefs,
-                 const float* leaf_values, const int32_t* sample_pass, float* policy_sample,
+                 float* carry_sums, float* carry_roots, const int32_t* leaf_begin, int32_t leaf_slots,
+                 float* leaf_beliefs, const float* leaf_values, const int32_t* sample_pass, float* policy_sample,
                  float* beliefs_last, const float* start_policy, void* stream);
 
 /* Start policy and warm start (initialize_policy_and_beliefs with a policy head,
@@ -196,18 +205,24 @@ int p2b_tree_records(const void* roots, const int64_t* boards, int32_t board_wid
  *   - the number of thread blocks is what fits in the area (at most one per SM), so large
  *     trees run on fewer SMs than with p2b_cfr_solve.
  * The first call on a device resolves the area's addresses and uploads a 2.6 KB table
- * with a blocking copy; make that first call before any stream capture.  Every call uses
+ * with a blocking copy (under a lock, so first calls from several threads are safe); make
+ * that first call before any stream capture.  Every call uses
  * the same area: it zeroes the queue counter itself and needs no other clearing, but two
  * calls that overlap on the GPU (different streams or threads) race on it -- serialise them.
  * It calls no cudaMalloc / cudaFree and no allocating library routine; inputs and outputs
- * are the caller's, with the meaning they have in p2b_cfr_solve. */
-int p2b_cfr_solve_noalloc(const void* subgames, const void* nodes, int32_t num_subgames,
+ * are the caller's, with the meaning they have in p2b_cfr_solve.
+ *
+ * The record check's verdict lives in the same area.  p2b_cfr_noalloc_status waits for
+ * `stream`, then copies it to the HOST word *status: 0, or 1 + the index of a subgame whose
+ * records were refused, in which case the last call solved nothing.  It allocates nothing. */
+int p2b_cfr_solve_noalloc(const void* subgames, const void* nodes, int32_t num_subgames, int64_t rows,
                           int32_t max_children, int32_t max_internal, const unsigned char* tables,
                           const float* root_beliefs, float* regrets, float* weight_sums,
                           float* policy_avg, float* policy, float* root_values, float* values_avg,
                           float* beliefs_avg, float* exploitability, float* br_values, const void* scalars,
                           int32_t iterations, int32_t cfr_plus, int32_t init_depth, void* stream);
 int64_t p2b_cfr_noalloc_scratch_floats(void);
+int p2b_cfr_noalloc_status(int32_t* status, void* stream);
 
 /* ---- step-level kernels (src/p2/search/fused_cfr_triton.py) ----------------------------
  * One entry point per fused kernel of the upstream module, on caller-owned contiguous fp32

@@ -29,13 +29,14 @@ _SIGNATURES = {
     "p2b_compare7_planes": [_vp, _i64, _vp, _vp],
     "p2b_rank_hands": [_vp, _i64, _vp, _vp, _vp, _vp],
     "p2b_showdown_values": [_vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _i64, _vp],
-    "p2b_cfr_solve": [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64,
+    "p2b_cfr_solve": [_vp, _vp, _i32, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64,
                       _vp, _i32, _i32, _i32, _vp, _i32, _vp, _vp, _vp, _vp],
-    "p2b_cfr_step": [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64,
-                     _vp, _i32, _i32, _i32, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
-                     _vp],
+    "p2b_cfr_step": [_vp, _vp, _i32, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64,
+                     _vp, _i32, _i32, _i32, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp,
+                     _vp, _vp],
     "p2b_cfr_warm_seed": [_vp, _i64, _vp, _f32, _vp, _vp, _vp],
-    "p2b_cfr_solve_noalloc": [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+    "p2b_cfr_noalloc_status": [_vp, _vp],
+    "p2b_cfr_solve_noalloc": [_vp, _vp, _i32, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                               _i32, _i32, _i32, _vp],
     "p2b_step_dcfr_update": [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _vp],
     "p2b_step_block_normalize": [_vp, _vp, _vp, _i64, _i32, _i32, _f32, _vp],
@@ -65,6 +66,7 @@ _SIGNATURES = {
 }
 # functions whose return value is a quantity, not a status code
 _VALUE_FUNCS = {"p2b_cfr_scratch_floats": ([_i32, _i32], _i64), "p2b_cfr_default_blocks": ([], _i32),
+                "p2b_cfr_solve_scratch_floats": ([_i32, _i32, _i32, _i32, _i64], _i64),
                 "p2b_cfr_noalloc_scratch_floats": ([], _i64)}
 
 

@@ -9,7 +9,7 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libpoker2_b200.so")
-SOURCES = ["common.cu", "rank7.cu", "showdown.cu", "cfr.cu", "stepops.cu", "chance.cu", "treebuild.cu", "selftest.cu", "api.cu"]
+SOURCES = ["common.cu", "rank7.cu", "showdown.cu", "cfr.cu", "cfr_iter.cu", "stepops.cu", "chance.cu", "treebuild.cu", "selftest.cu", "api.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -73,14 +73,21 @@ int64_t p2b_cfr_scratch_floats(int32_t max_internal, int32_t num_blocks) {
     return cfr_scratch_floats(max_internal) * num_blocks;
 }
 
-int p2b_cfr_solve(const void* subgames, const void* nodes, int32_t num_subgames, int32_t max_children,
+int64_t p2b_cfr_solve_scratch_floats(int32_t max_internal, int32_t max_children, int32_t num_blocks,
+                                     int32_t num_subgames, int64_t rows) {
+    if (num_blocks <= 0) num_blocks = cfr_default_blocks();
+    if (num_blocks > num_subgames) num_blocks = num_subgames > 0 ? num_subgames : 1;
+    return cfr_solve_scratch_floats(max_internal, max_children, num_blocks, num_subgames, rows);
+}
+
+int p2b_cfr_solve(const void* subgames, const void* nodes, int32_t num_subgames, int64_t rows, int32_t max_children,
                   int32_t max_internal, const unsigned char* tables, const float* root_beliefs, float* regrets,
                   float* weight_sums, float* policy_avg, float* policy, float* root_values, float* values_avg,
                   float* beliefs_avg, float* exploitability, float* br_values, float* scratch, int64_t scratch_floats,
                   const void* scalars, int32_t iterations, int32_t cfr_plus, int32_t init_depth, int32_t* work_counter,
                   int32_t num_blocks, const int32_t* sample_pass, float* policy_sample, float* beliefs_last,
                   void* stream) {
-    P2B_REQUIRE(num_subgames >= 0 && iterations >= 0, "negative count");
+    P2B_REQUIRE(num_subgames >= 0 && iterations >= 0 && rows >= 0, "negative count");
     P2B_REQUIRE(!policy_sample || sample_pass, "policy_sample needs sample_pass");
     P2B_REQUIRE(((reinterpret_cast<uintptr_t>(policy_sample) | reinterpret_cast<uintptr_t>(beliefs_last)) & 15) == 0,
                 "all arrays must be 16-byte aligned");
@@ -126,20 +133,25 @@ int p2b_cfr_solve(const void* subgames, const void* nodes, int32_t num_subgames,
     p.sample_pass = sample_pass;
     p.policy_sample = policy_sample;
     p.beliefs_last = beliefs_last;
-    return launch_cfr_solve(p, num_blocks, max_children, (cudaStream_t)stream);
+    p.rows = rows;
+    // with the larger scratch area of p2b_cfr_solve_scratch_floats the iteration passes of a plain
+    // solve run in the lean iteration kernel
+    const bool fast_scratch =
+        scratch_floats >= cfr_solve_scratch_floats(max_internal, max_children, num_blocks, num_subgames, rows);
+    return launch_cfr_solve(p, num_blocks, max_children, (cudaStream_t)stream, fast_scratch);
 }
 
 // Part of a solve: the passes pass_begin..pass_end, top-down and/or bottom-up sweeps.
-int p2b_cfr_step(const void* subgames, const void* nodes, int32_t num_subgames, int32_t max_children,
+int p2b_cfr_step(const void* subgames, const void* nodes, int32_t num_subgames, int64_t rows, int32_t max_children,
                  int32_t max_internal, const unsigned char* tables, const float* root_beliefs, float* regrets,
                  float* weight_sums, float* policy_avg, float* policy, float* root_values, float* values_avg,
                  float* beliefs_avg, float* exploitability, float* br_values, float* scratch, int64_t scratch_floats,
                  const void* scalars, int32_t iterations, int32_t cfr_plus, int32_t init_depth, int32_t* work_counter,
                  int32_t num_blocks, int32_t pass_begin, int32_t pass_end, int32_t phases, float* carry_sums,
-                 float* carry_roots, const int32_t* leaf_begin, float* leaf_beliefs, const float* leaf_values,
-                 const int32_t* sample_pass, float* policy_sample, float* beliefs_last, const float* start_policy,
+                 float* carry_roots, const int32_t* leaf_begin, int32_t leaf_slots, float* leaf_beliefs,
+                 const float* leaf_values, const int32_t* sample_pass, float* policy_sample, float* beliefs_last, const float* start_policy,
                  void* stream) {
-    P2B_REQUIRE(num_subgames >= 0 && iterations >= 1, "bad count");
+    P2B_REQUIRE(num_subgames >= 0 && iterations >= 1 && rows >= 0 && leaf_slots >= 0, "bad count");
     P2B_REQUIRE((reinterpret_cast<uintptr_t>(start_policy) & 15) == 0, "all row arrays must be 16-byte aligned");
     P2B_REQUIRE(!policy_sample || sample_pass, "policy_sample needs sample_pass");
     P2B_REQUIRE(((reinterpret_cast<uintptr_t>(policy_sample) | reinterpret_cast<uintptr_t>(beliefs_last)) & 15) == 0,
@@ -203,6 +215,8 @@ int p2b_cfr_step(const void* subgames, const void* nodes, int32_t num_subgames, 
     p.policy_sample = policy_sample;
     p.beliefs_last = beliefs_last;
     p.start_policy = start_policy;
+    p.rows = rows;
+    p.leaf_slots = leaf_slots;
     return launch_cfr_solve(p, num_blocks, max_children, (cudaStream_t)stream);
 }
 
@@ -220,12 +234,17 @@ int64_t p2b_cfr_noalloc_scratch_floats(void) { return cfr_static_scratch_floats(
 
 // Allocation-free twin of p2b_cfr_solve: work rows, queue counter and combo table come from
 // a fixed device area inside the library (see launch_cfr_solve_static).
-int p2b_cfr_solve_noalloc(const void* subgames, const void* nodes, int32_t num_subgames, int32_t max_children,
-                          int32_t max_internal, const unsigned char* tables, const float* root_beliefs, float* regrets,
+int p2b_cfr_noalloc_status(int32_t* status, void* stream) {
+    P2B_REQUIRE(status != nullptr, "null pointer");
+    return cfr_static_status(status, (cudaStream_t)stream);
+}
+
+int p2b_cfr_solve_noalloc(const void* subgames, const void* nodes, int32_t num_subgames, int64_t rows,
+                          int32_t max_children, int32_t max_internal, const unsigned char* tables, const float* root_beliefs, float* regrets,
                           float* weight_sums, float* policy_avg, float* policy, float* root_values, float* values_avg,
                           float* beliefs_avg, float* exploitability, float* br_values, const void* scalars,
                           int32_t iterations, int32_t cfr_plus, int32_t init_depth, void* stream) {
-    P2B_REQUIRE(num_subgames >= 0 && iterations >= 0, "negative count");
+    P2B_REQUIRE(num_subgames >= 0 && iterations >= 0 && rows >= 0, "negative count");
     if (num_subgames == 0) return P2B_OK;
     P2B_REQUIRE(subgames && nodes && root_beliefs && regrets && policy_avg && root_values && scalars, "null pointer");
     P2B_REQUIRE(max_internal >= 1, "max_internal must be positive");
@@ -257,6 +276,7 @@ int p2b_cfr_solve_noalloc(const void* subgames, const void* nodes, int32_t num_s
     p.iterations = iterations;
     p.cfr_plus = cfr_plus;
     p.init_depth = init_depth;
+    p.rows = rows;
     return launch_cfr_solve_static(p, max_children, (cudaStream_t)stream);
 }
 

@@ -25,7 +25,10 @@
 // accumulates in fp64 and rounds to fp32 (unblocked mass, showdown prefix sums) are
 // accumulated in fp64 here too, in a different order, which changes the rounded fp32
 // result only when the fp64 value lies within ~1e-16 of a rounding boundary.
+#include <mutex>
+
 #include "cfr.cuh"
+#include "cfr_dev.cuh"
 #include "exactdiv.cuh"
 #include "showdown.cuh"
 
@@ -52,105 +55,6 @@ constexpr int kOffMisc = kOffSig + kCfrMaxNodes * 2 * 4;
 constexpr int kOffIlist = kOffMisc + 64;  // node index of every internal node, in node order
 constexpr int kCfrSmem = kOffIlist + ((kCfrMaxNodes + 15) / 16) * 16;
 static_assert(kOffXs % 16 == 0 && kOffCs % 8 == 0 && kOffMisc % 16 == 0 && kOffSig % 8 == 0, "alignment");
-
-// VPT consecutive hands of one row
-template <int VPT>
-struct FV {
-    float v[VPT];
-};
-
-static_assert(P2B_HPAD == 1344, "rows are covered exactly by 672 x 2 or 336 x 4 hands");
-
-template <int VPT>
-__device__ __forceinline__ FV<VPT> ldv(const float* row, int tid) {
-    FV<VPT> r;
-    if (VPT == 4) {
-        const float4 t = *reinterpret_cast<const float4*>(row + 4 * tid);
-        r.v[0] = t.x; r.v[1] = t.y; r.v[VPT - 2] = t.z; r.v[VPT - 1] = t.w;
-    } else {
-        const float2 t = *reinterpret_cast<const float2*>(row + 2 * tid);
-        r.v[0] = t.x; r.v[1] = t.y;
-    }
-    return r;
-}
-template <int VPT>
-__device__ __forceinline__ void stv(float* row, int tid, const FV<VPT>& r) {
-    if (VPT == 4) *reinterpret_cast<float4*>(row + 4 * tid) = make_float4(r.v[0], r.v[1], r.v[VPT - 2], r.v[VPT - 1]);
-    else *reinterpret_cast<float2*>(row + 2 * tid) = make_float2(r.v[0], r.v[1]);
-}
-
-// Hint that this thread's slice of a row will be read soon: pulls the line into L2.
-template <int VPT>
-__device__ __forceinline__ void prefetch_row(const float* row, int tid) {
-    asm volatile("prefetch.global.L2 [%0];" ::"l"(row + VPT * tid));
-}
-// The same for the n (<= kCfrMaxChildren) consecutive rows that start at `row` (the rows of the
-// children of one node): one address computation, fixed offsets.
-template <int VPT>
-__device__ __forceinline__ void prefetch_rows(const float* row, int n, int tid) {
-    const float* mine = row + VPT * tid;
-#pragma unroll
-    for (int c = 0; c < kCfrMaxChildren; ++c)
-        if (c < n) asm volatile("prefetch.global.L2 [%0];" ::"l"(mine + c * P2B_HPAD));
-}
-
-// x[which] without indexing a register array by a run-time value
-template <int VPT>
-__device__ __forceinline__ FV<VPT> pick(const FV<VPT> (&x)[2], int which) {
-    FV<VPT> r;
-#pragma unroll
-    for (int i = 0; i < VPT; ++i) r.v[i] = which ? x[1].v[i] : x[0].v[i];
-    return r;
-}
-
-__device__ __forceinline__ double warp_sum(double v) {
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
-    return v;
-}
-
-// Mass of the hands that share no card with (c1,c2): total - card sums + own mass,
-// evaluated in fp64, rounded to fp32 and clamped at zero (p2/env/card_utils.py:196-222).
-__device__ __forceinline__ float unblocked(const double* cs, double S, int c1, int c2, float x) {
-    const double m = S - cs[c1] - cs[c2] + (double)x;
-    return fmaxf((float)m, 0.0f);
-}
-
-// fp32 sum of x[0..1325] in exactly the association order of the vectorised CPU row
-// reduction the upstream normalisation runs through (`target.sum(dim=-1)`,
-// cfr_evaluator.py:263): 8-wide vectors x 4 interleaved accumulators = 32 chains, each
-// cascaded in blocks of 16, then the 165th vector, the four accumulators, the 6 scalar
-// tail elements and finally the 8 vector lanes, all sequentially.  One warp computes it;
-// every lane returns the sum.
-__device__ __forceinline__ float row_sum_reference_order(const float* __restrict__ x) {
-    const int lane = threadIdx.x & 31;
-    float s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) s1 = __fadd_rn(s1, x[32 * i + lane]);
-#pragma unroll
-    for (int i = 16; i < 32; ++i) s2 = __fadd_rn(s2, x[32 * i + lane]);
-#pragma unroll
-    for (int i = 32; i < 41; ++i) s3 = __fadd_rn(s3, x[32 * i + lane]);
-    float c = __fadd_rn(s3, __fadd_rn(s1, s2));
-    if (lane < 8) c = __fadd_rn(c, x[1312 + lane]);
-    const float c1 = __shfl_down_sync(0xffffffffu, c, 8);
-    const float c2 = __shfl_down_sync(0xffffffffu, c, 16);
-    const float c3 = __shfl_down_sync(0xffffffffu, c, 24);
-    const float pv = __fadd_rn(__fadd_rn(__fadd_rn(c, c1), c2), c3);  // meaningful on lanes 0..7
-    float fa = 0.0f;
-#pragma unroll
-    for (int t = 1320; t < P2B_NUM_HANDS; ++t) fa = __fadd_rn(fa, x[t]);
-#pragma unroll
-    for (int v = 0; v < 8; ++v) fa = __fadd_rn(fa, __shfl_sync(0xffffffffu, pv, v));
-    return fa;
-}
-
-template <int VPT>
-struct HandInfo {
-    int c1[VPT], c2[VPT];
-    bool valid[VPT];    // a real combo (not row padding)
-    bool allowed[VPT];  // and not blocked by the board of the current subgame
-};
 
 enum PassMode { kPassInit = 0, kPassIter = 1, kPassFinal = 2 };
 
@@ -1150,14 +1054,10 @@ __device__ __forceinline__ void dot2_reference_order(Block& B, const FV<VPT>& x0
     out[1] = B.fsum[1];
 }
 
-template <int VPT>
-struct CfrThreads {
-    static constexpr int value = P2B_HPAD / VPT;  // 672 threads for two hands per thread, 336 for four
-};
-
 template <int VPT, int MAXC>
 __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(const CfrParams p) {
     constexpr int NT = CfrThreads<VPT>::value;
+    if (p.gate == 2 && p.work_counter[2] == 0) return;  // these passes ran in cfr_iter_kernel
     extern __shared__ __align__(16) unsigned char smem[];
     Block B;
     B.tab = smem + kOffTab;
@@ -1193,7 +1093,7 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
         if (s >= p.num_subgames) break;
         B.sg = p.subgames[s];
         // work rows: one set per block, or one per subgame when state is carried between launches
-        B.scr = p.scratch + (long long)(p.stepped ? s : (int)blockIdx.x) * p.scratch_stride;
+        B.scr = p.scratch + (long long)((p.stepped && !p.scratch_per_block) ? s : (int)blockIdx.x) * p.scratch_stride;
         B.leaf0 = p.leaf_begin ? p.leaf_begin[s] : 0;
         B.sample_pass = p.sample_pass ? p.sample_pass[s] : -2;
         {
@@ -1304,23 +1204,35 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
     }
 }
 
-// Checks every subgame's records against the solver kernel's limits before it runs: a
-// malformed tree would make it index shared memory out of range.  One block per subgame, one
-// thread per node.  On a violation the status word (work_counter[1]) receives 1 + the
-// subgame index and the subgame queue (work_counter[0]) is set past its end, so that the
-// solver kernel launched next on the stream finds no work at all.
+// Checks every subgame's records against the solver kernels' limits before they run: a
+// malformed tree would make them index shared memory or the work rows out of range.  One block
+// per subgame, one thread per node.  On a violation the status word (work_counter[1]) receives
+// 1 + the subgame index and the subgame queue (work_counter[0]) is set past its end, so that the
+// solver kernel launched next on the stream finds no work at all.  work_counter[2] is set when a
+// node has more than one showdown child, which the iteration kernel (cfr_iter.cu) does not cover.
 __global__ void __launch_bounds__(kCfrMaxNodes) cfr_validate_kernel(const CfrParams p) {
     const int s = blockIdx.x, i = threadIdx.x;
     const SubgameRec sg = p.subgames[s];
-    int bad = sg.n_nodes < 1 || sg.n_nodes > kCfrMaxNodes || sg.n_internal > p.max_internal || sg.node_begin < 0;
+    int bad = sg.n_nodes < 1 || sg.n_nodes > kCfrMaxNodes || sg.n_internal > p.max_internal || sg.node_begin < 0 ||
+              (p.rows > 0 && (long long)sg.node_begin + sg.n_nodes > p.rows);
+    int many_showdowns = 0;
     if (!bad && i < sg.n_nodes) {
         const NodeRec nd = p.nodes[sg.node_begin + i];
         if (nd.kind > kModelLeaf || (nd.kind == kShowdownLeaf && (sg.table_index < 0 || p.tables == nullptr))) bad = 1;
         if (i == 0 && nd.kind != kInternal) bad = 1;
         if (nd.kind == kInternal &&
             (nd.n_children < 1 || nd.n_children > kCfrMaxChildren || nd.first_child <= i ||
-             nd.first_child + nd.n_children > sg.n_nodes || nd.internal_idx >= p.max_internal))
+             nd.first_child + nd.n_children > sg.n_nodes || nd.internal_idx >= p.max_internal || nd.to_act > 1))
             bad = 1;
+        // a leaf valued by the caller's model must own a slot of the leaf arrays
+        if (nd.kind == kModelLeaf && p.leaf_begin && (p.leaf_beliefs || p.leaf_values) &&
+            (p.leaf_begin[s] < 0 || p.leaf_begin[s] + (int)nd.internal_idx >= p.leaf_slots))
+            bad = 1;
+        if (!bad && nd.kind == kInternal) {
+            int n_sd = 0;
+            for (int c = 0; c < nd.n_children; ++c) n_sd += p.nodes[sg.node_begin + nd.first_child + c].kind == kShowdownLeaf;
+            many_showdowns = n_sd > 1;
+        }
     }
     // internal_idx must be the rank among the subgame's internal nodes (the solver walks them
     // through a list indexed by it) and n_internal their number
@@ -1338,6 +1250,7 @@ __global__ void __launch_bounds__(kCfrMaxNodes) cfr_validate_kernel(const CfrPar
         atomicMax(p.work_counter + 1, s + 1);
         atomicMax(p.work_counter, p.num_subgames);
     }
+    if (many_showdowns) atomicOr(p.work_counter + 2, 1);
 }
 
 // Warm start of type `model` (p2/search/cfr_evaluator.py:913-926), applied between the start
@@ -1376,11 +1289,11 @@ int launch_variant(const CfrParams& p, int num_blocks, cudaStream_t stream) {
                                              kCfrSmem),
                         "cfr_solve_kernel shared-memory attribute");
     if (rc) return rc;
-    if (!p.stepped || (p.pass_begin < 0 && (p.phases & 1))) {  // a stepped solve is checked at its first step
-        cfr_validate_kernel<<<p.num_subgames, kCfrMaxNodes, 0, stream>>>(p);
-        rc = check_cuda(cudaGetLastError(), "cfr_validate_kernel");
-        if (rc) return rc;
-    }
+    // every launch is checked, also the later steps of a stepped solve: the launcher has cleared the
+    // status word and the queue, and the kernel must not walk records the check refuses
+    cfr_validate_kernel<<<p.num_subgames, kCfrMaxNodes, 0, stream>>>(p);
+    rc = check_cuda(cudaGetLastError(), "cfr_validate_kernel");
+    if (rc) return rc;
     cfr_solve_kernel<VPT, MAXC><<<num_blocks, CfrThreads<VPT>::value, kCfrSmem, stream>>>(p);
     return check_cuda(cudaGetLastError(), "cfr_solve_kernel");
 }
@@ -1405,16 +1318,68 @@ int launch_cfr_warm_seed(const NodeRec* nodes, long long rows, const float* star
     return check_cuda(cudaGetLastError(), "cfr_warm_seed_kernel");
 }
 
-int launch_cfr_solve(const CfrParams& params, int num_blocks, int max_children, cudaStream_t stream) {
+static int clear_counters(int32_t* work_counter, cudaStream_t stream) {
+    // [0] subgame queue, [1] status, [2] trees outside the iteration kernel, [3] spare
+    return check_cuda(cudaMemsetAsync(work_counter, 0, 4 * sizeof(int32_t), stream), "cudaMemsetAsync(work counter)");
+}
+
+long long cfr_solve_scratch_floats(int max_internal, int max_children, int num_blocks, int num_subgames, long long rows) {
+    long long per_block = cfr_scratch_floats(max_internal);
+    const long long iter_block = cfr_iter_scratch_floats(max_internal, max_children);
+    if (iter_block > per_block) per_block = iter_block;
+    const long long carry_sums = ((rows * 2 + 3) / 4) * 4;
+    return per_block * num_blocks + (long long)num_subgames * 4 * P2B_HPAD + carry_sums;
+}
+
+int launch_cfr_solve(const CfrParams& params, int num_blocks, int max_children, cudaStream_t stream, bool fast_scratch) {
     if (params.num_subgames == 0) return P2B_OK;
     if (params.iterations < 1) return set_error(P2B_ERR_ARG, "at least one iteration is required");
     int rc = ensure_tables();
     if (rc) return rc;
     CfrParams p = params;
     p.combos = device_combo_table();
-    rc = check_cuda(cudaMemsetAsync(p.work_counter, 0, 2 * sizeof(int32_t), stream), "cudaMemsetAsync(work counter)");
-    if (rc) return rc;
-    return dispatch_cfr(p, num_blocks, max_children, stream);
+    const bool plain = !p.stepped && !p.leaf_beliefs && !p.leaf_values && !p.policy_sample && !p.beliefs_last &&
+                       !p.policy && !p.start_policy;
+    if (!(plain && fast_scratch && max_children <= kCfrMaxChildren)) {
+        rc = clear_counters(p.work_counter, stream);
+        if (rc) return rc;
+        return dispatch_cfr(p, num_blocks, max_children, stream);
+    }
+    // A plain solve runs as: start pass (cfr_solve_kernel), iteration passes (cfr_iter_kernel, or
+    // cfr_solve_kernel for trees the record check keeps away from it), final pass with the best
+    // responses (cfr_solve_kernel).  Root rows and their sums travel between the launches in the tail
+    // of the scratch area; work rows do not, so each launch keeps one set per block.
+    long long per_block = cfr_scratch_floats(p.max_internal);
+    const long long iter_block = cfr_iter_scratch_floats(p.max_internal, max_children);
+    if (iter_block > per_block) per_block = iter_block;
+    p.scratch_stride = per_block;
+    p.carry_roots = p.scratch + per_block * num_blocks;
+    p.carry_sums = p.carry_roots + (long long)p.num_subgames * 4 * P2B_HPAD;
+    p.stepped = 1;
+    p.scratch_per_block = 1;
+    p.phases = 3;
+    for (int part = 0; part < 4; ++part) {
+        CfrParams q = p;
+        if (part == 0) q.pass_begin = q.pass_end = -1;
+        if (part == 1 || part == 2) {
+            q.pass_begin = 0;
+            q.pass_end = p.iterations - 1;
+        }
+        if (part == 3) q.pass_begin = q.pass_end = p.iterations;
+        rc = clear_counters(q.work_counter, stream);
+        if (rc) return rc;
+        if (part == 1) {
+            cfr_validate_kernel<<<q.num_subgames, kCfrMaxNodes, 0, stream>>>(q);
+            rc = check_cuda(cudaGetLastError(), "cfr_validate_kernel");
+            if (rc) return rc;
+            rc = launch_cfr_iter(q, num_blocks, stream);
+        } else {
+            q.gate = part == 2 ? 2 : 0;
+            rc = dispatch_cfr(q, num_blocks, max_children, stream);
+        }
+        if (rc) return rc;
+    }
+    return P2B_OK;
 }
 
 // ---- variant that allocates nothing --------------------------------------------------
@@ -1441,7 +1406,7 @@ StaticPointers g_static[kStaticMaxDevices];
 long long cfr_static_scratch_floats() { return kStaticScratchFloats; }
 
 // First call on a device: resolves the three symbols and uploads the combo table with a
-// synchronous copy.  Later calls only enqueue a 4-byte memset and the kernel.
+// synchronous copy.  Later calls only enqueue a 16-byte memset, the record check and the kernel.
 int launch_cfr_solve_static(const CfrParams& params, int max_children, cudaStream_t stream) {
     if (params.num_subgames == 0) return P2B_OK;
     if (params.iterations < 1) return set_error(P2B_ERR_ARG, "at least one iteration is required");
@@ -1450,6 +1415,8 @@ int launch_cfr_solve_static(const CfrParams& params, int max_children, cudaStrea
     if (rc) return rc;
     if (dev < 0 || dev >= kStaticMaxDevices) return set_error(P2B_ERR_STATE, "device ordinal %d out of range", dev);
     StaticPointers& sp = g_static[dev];
+    static std::mutex setup_lock;  // first calls on a device may come from several host threads
+    std::lock_guard<std::mutex> hold(setup_lock);
     if (!sp.ready) {
         rc = check_cuda(cudaGetSymbolAddress((void**)&sp.scratch, g_static_scratch), "cudaGetSymbolAddress(scratch)");
         if (rc) return rc;
@@ -1485,9 +1452,23 @@ int launch_cfr_solve_static(const CfrParams& params, int max_children, cudaStrea
     p.work_counter = sp.counter;
     // the queue counter must start at zero; the work rows need no clearing (every row is
     // written before it is read within a solve)
-    rc = check_cuda(cudaMemsetAsync(sp.counter, 0, 2 * sizeof(int32_t), stream), "cudaMemsetAsync(static counter)");
+    rc = check_cuda(cudaMemsetAsync(sp.counter, 0, 4 * sizeof(int32_t), stream), "cudaMemsetAsync(static counter)");
     if (rc) return rc;
     return dispatch_cfr(p, (int)blocks, max_children, stream);
+}
+
+// Status word of the last allocation-free solve on the current device (0, or 1 + the index of a
+// subgame whose records the check refused, in which case nothing was solved).  Waits for `stream`.
+int cfr_static_status(int32_t* host_status, cudaStream_t stream) {
+    int dev = 0;
+    int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+    if (rc) return rc;
+    if (dev < 0 || dev >= kStaticMaxDevices || !g_static[dev].ready)
+        return set_error(P2B_ERR_STATE, "no allocation-free solve has run on device %d yet", dev);
+    rc = check_cuda(cudaMemcpyAsync(host_status, g_static[dev].counter + 1, sizeof(int32_t), cudaMemcpyDeviceToHost, stream),
+                    "cudaMemcpyAsync(static status)");
+    if (rc) return rc;
+    return check_cuda(cudaStreamSynchronize(stream), "cudaStreamSynchronize(static status)");
 }
 
 }  // namespace p2b

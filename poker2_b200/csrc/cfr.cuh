@@ -93,6 +93,13 @@ struct CfrParams {
     float* policy_sample;        // [rows][HPAD] (out, may be null)
     float* beliefs_last;         // [rows][2][HPAD] beliefs of the last iteration at internal nodes (out, may be null)
     const float* start_policy;   // [rows][HPAD] policy of the start pass (may be null: uniform over the children)
+    // ---- limits the record check compares the records with
+    long long rows;              // rows of the state arrays
+    int32_t leaf_slots;          // model-leaf slots of leaf_beliefs / leaf_values
+    // ---- a one-launch solve split over several launches (start pass, iteration passes, final pass)
+    int32_t scratch_per_block;   // stepped launch whose work rows are not carried: one set per block
+    int32_t gate;                // 0: run; 2: run only when the record check flagged trees the iteration
+                                 // kernel does not cover (work_counter[2] != 0)
 };
 
 // floats of scratch one block needs: per internal node reach[2], average reach[2], values[2]
@@ -100,11 +107,17 @@ __host__ __device__ inline long long cfr_scratch_floats(int max_internal) {
     return (long long)max_internal * 6 * P2B_HPAD;
 }
 
-int launch_cfr_solve(const CfrParams& p, int num_blocks, int max_children, cudaStream_t stream);
+// `fast_scratch`: the scratch area also holds the hand-over rows of a split solve
+// (cfr_solve_scratch_floats), so a plain solve may run its iteration passes in cfr_iter_kernel.
+int launch_cfr_solve(const CfrParams& p, int num_blocks, int max_children, cudaStream_t stream, bool fast_scratch = false);
+long long cfr_iter_scratch_floats(int max_internal, int max_children);
+long long cfr_solve_scratch_floats(int max_internal, int max_children, int num_blocks, int num_subgames, long long rows);
+int launch_cfr_iter(const CfrParams& p, int num_blocks, cudaStream_t stream);
 int cfr_default_blocks();
 int launch_cfr_solve_static(const CfrParams& p, int max_children, cudaStream_t stream);
 int launch_cfr_warm_seed(const NodeRec* nodes, long long rows, const float* start_policy, float weight, float* regrets,
                          float* weight_sums, cudaStream_t stream);
 long long cfr_static_scratch_floats();
+int cfr_static_status(int32_t* host_status, cudaStream_t stream);
 
 }  // namespace p2b

@@ -33,32 +33,75 @@ assert NODE_DTYPE.itemsize == 16 and SUBGAME_DTYPE.itemsize == 32 and SCALAR_DTY
 
 
 def iteration_scalars(iterations: int, *, cfr_type: str = "discounted", alpha: float = 1.5, beta: float = 0.0,
-                      gamma: float = 2.0, dcfr_delay: int = 0) -> np.ndarray:
-    """Per-iteration discount and mixing scalars, evaluated in Python floats and rounded to
-    fp32 exactly as the upstream loop does (cfr_evaluator.py:1346-1360, 285-303, 1197-1205).
-    t is 0-based: 0**0.0 == 1 and 0**1.5 == 0."""
+                      gamma: float = 2.0, dcfr_delay: int = 0, alpha_final: float | None = None,
+                      beta_final: float | None = None, gamma_final: float | None = None,
+                      warm_start_iterations: int = 0) -> np.ndarray:
+    """Per-iteration discount and mixing scalars for t = 0..iterations-1, evaluated in Python
+    floats and rounded to fp32 exactly as the upstream loop does (cfr_evaluator.py:1346-1360,
+    285-303, 1197-1205).  t is 0-based: 0**0.0 == 1 and 0**1.5 == 0.
+
+    alpha / beta / gamma are the initial exponents; with a `*_final` value the exponent of
+    iteration t is interpolated linearly over the iterations after the warm start, as
+    `apply_schedules` does (cfr_evaluator.py:1294-1329):
+    progress = clamp((t - warm_start_iterations) / max(1, iterations - warm_start_iterations), 0, 1).
+    Rows below `warm_start_iterations` are never run by the upstream loop (it starts at the warm
+    start, :1516); they are left at the neutral value 1 instead of evaluating t ** exponent there
+    (0 ** negative raises in Python, which the production setting beta = -1 would hit at t = 0).
+    The row AT `warm_start_iterations` also serves the warm start's own `update_policy(w)` call
+    (:923), which upstream runs before any schedule is applied, i.e. with the initial gamma:
+    `solver.SteppedSolver.solve` builds that extra pass from `warm_start_mix_scalars`."""
+    if cfr_type not in ("standard", "discounted", "discounted_plus", "linear"):
+        raise ValueError(f"unknown cfr_type {cfr_type!r}")
+    if cfr_type == "linear":
+        raise ValueError("linear CFR (alternating updates) is not supported by the fused kernel")
+    ws = max(0, int(warm_start_iterations))
     out = np.zeros(iterations, dtype=SCALAR_DTYPE)
     discounted = cfr_type in ("discounted", "discounted_plus")
+    span = max(1, iterations - ws)
     for t in range(iterations):
+        if t < ws:  # never run: neutral scalars, average policy := current policy
+            out[t]["num_pos"] = out[t]["den_pos"] = out[t]["num_neg"] = out[t]["den_neg"] = 1.0
+            out[t]["mix_old"], out[t]["mix_new"], out[t]["mix_total"], out[t]["do_mix"] = 0.0, 1.0, 1.0, 0
+            continue
+        progress = min(1.0, max(0.0, max(0, t - ws) / float(span)))
+        a_t = alpha if alpha_final is None else alpha + (alpha_final - alpha) * progress
+        b_t = beta if beta_final is None else beta + (beta_final - beta) * progress
+        g_t = gamma if gamma_final is None else gamma + (gamma_final - gamma) * progress
         if discounted:
-            ta, tb = float(t) ** alpha, float(t) ** beta
+            # integer base like upstream (`t**self.dcfr_alpha` with an int t): identical to float(t) ** x
+            ta, tb = t ** a_t, t ** b_t
             out[t]["num_pos"], out[t]["den_pos"] = ta, ta + 1
             out[t]["num_neg"], out[t]["den_neg"] = tb, tb + 1
         else:
             out[t]["num_pos"] = out[t]["den_pos"] = out[t]["num_neg"] = out[t]["den_neg"] = 1.0
-        if cfr_type == "standard":
-            old, new = t, 1
-        elif cfr_type == "linear":
-            raise ValueError("linear CFR (alternating updates) is not supported by the fused kernel")
-        elif cfr_type == "discounted":
-            old, new = float(t) ** gamma, float(t + 1) ** gamma
-        elif cfr_type == "discounted_plus":
-            old, new = (t - dcfr_delay, 2) if t > dcfr_delay else (0, 1)
-        else:
-            raise ValueError(f"unknown cfr_type {cfr_type!r}")
+        old, new = _mixing_weights(cfr_type, t, g_t, dcfr_delay)
         out[t]["mix_old"], out[t]["mix_new"], out[t]["mix_total"] = old, new, old + new
         out[t]["do_mix"] = 0 if (t == 0 or (discounted and t <= dcfr_delay)) else 1
     return out
+
+
+def _mixing_weights(cfr_type: str, t: int, gamma: float, dcfr_delay: int):
+    """`_get_mixing_weights` (cfr_evaluator.py:285-303)."""
+    if cfr_type == "standard":
+        return t, 1
+    if cfr_type == "discounted":
+        return t ** gamma, (t + 1) ** gamma
+    return (t - dcfr_delay, 2) if t > dcfr_delay else (0, 1)  # discounted_plus
+
+
+def warm_start_mix_scalars(scalars: np.ndarray, *, cfr_type: str, gamma: float, dcfr_delay: int,
+                           warm_start_iterations: int) -> np.ndarray:
+    """The scalars of the extra pass a warm start adds in front of the iterations: the warm start
+    ends with `update_policy(w)` (cfr_evaluator.py:923), whose average-policy mix uses t = w and
+    the exponent gamma as it stands before any schedule was applied (the initial value).  The
+    regret-discount fields of that pass are not used (the warm start seeds the regrets itself)."""
+    w = int(warm_start_iterations)
+    row = scalars[w:w + 1].copy()
+    old, new = _mixing_weights(cfr_type, w, gamma, dcfr_delay)
+    row["mix_old"], row["mix_new"], row["mix_total"] = old, new, old + new
+    discounted = cfr_type in ("discounted", "discounted_plus")
+    row["do_mix"] = 0 if (w == 0 or (discounted and w <= dcfr_delay)) else 1
+    return row
 
 
 @dataclass
@@ -207,7 +250,10 @@ class SubgameSolver:
 
     def __init__(self, layout: DeviceTreeLayout, boards: torch.Tensor, device: torch.device, *,
                  track_weight_sums: bool = True, keep_policy: bool = False, keep_node_values: bool = False,
-                 exploitability: bool = False, num_blocks: int = 0, sampling: bool = False):
+                 exploitability: bool = False, num_blocks: int = 0, sampling: bool = False,
+                 lean_iterations: bool = True):
+        """lean_iterations=False gives the kernel only its minimal scratch area, which keeps every
+        pass of a solve in the general kernel (one launch); results are the same bit for bit."""
         keep_node_values = keep_node_values or exploitability  # best responses read the node values
         if device.type != "cuda":
             raise ValueError("SubgameSolver requires a CUDA device.")
@@ -239,7 +285,12 @@ class SubgameSolver:
         self.beliefs_avg = torch.zeros(rows, 2, HPAD, **f32) if keep_node_values else None
         self.exploitability = torch.zeros(B, **f32) if (exploitability and keep_node_values) else None
         self.br_values = torch.zeros(B, 2, **f32) if (exploitability and keep_node_values) else None
-        n_scratch = int(_lib.lib().p2b_cfr_scratch_floats(layout.max_internal, self.num_blocks))
+        # the larger area lets a solve without optional outputs run its iteration passes in the lean kernel
+        if lean_iterations:
+            n_scratch = int(_lib.lib().p2b_cfr_solve_scratch_floats(layout.max_internal, layout.max_children,
+                                                                    self.num_blocks, B, rows))
+        else:
+            n_scratch = int(_lib.lib().p2b_cfr_scratch_floats(layout.max_internal, self.num_blocks))
         self.scratch = torch.empty(n_scratch, **f32)
         self.work_counter = torch.zeros(4, device=device, dtype=torch.int32)
         # leaf sampling: the policy of one scheduled iteration per subgame, beliefs of the last one
@@ -285,7 +336,7 @@ class SubgameSolver:
         p = _lib.ptr
         with torch.cuda.device(self.device):
             _lib.call(
-                "p2b_cfr_solve", p(self.subgames), p(self.nodes), self.B, self.layout.max_children,
+                "p2b_cfr_solve", p(self.subgames), p(self.nodes), self.B, self.layout.rows, self.layout.max_children,
                 self.layout.max_internal, p(self.tables.blob) if self.tables is not None else None, p(root_beliefs),
                 p(self.regrets), p(self.weight_sums), p(self.policy_avg), p(self.policy), p(self.root_values),
                 p(self.values_avg), p(self.beliefs_avg), p(self.exploitability), p(self.br_values), p(self.scratch),
@@ -324,24 +375,27 @@ class SteppedSolver(SubgameSolver):
         p = _lib.ptr
         with torch.cuda.device(self.device):
             _lib.call(
-                "p2b_cfr_step", p(self.subgames), p(self.nodes), self.B, self.layout.max_children,
+                "p2b_cfr_step", p(self.subgames), p(self.nodes), self.B, self.layout.rows, self.layout.max_children,
                 self.layout.max_internal, p(self.tables.blob) if self.tables is not None else None, p(root_beliefs),
                 p(self.regrets), p(self.weight_sums), p(self.policy_avg), p(self.policy), p(self.root_values),
                 p(self.values_avg), p(self.beliefs_avg), p(self.exploitability), p(self.br_values), p(self.scratch),
                 self.scratch.numel(), p(sc), iterations, int(cfr_plus), self.layout.tree_depth, p(self.work_counter),
                 self.num_blocks, pass_begin, pass_end, phases, p(self.carry_sums), p(self.carry_roots),
-                p(self.leaf_begin), p(self.leaf_beliefs), p(self.leaf_values), p(self.sample_pass),
+                p(self.leaf_begin), int(self.leaf_beliefs.shape[0]), p(self.leaf_beliefs), p(self.leaf_values),
+                p(self.sample_pass),
                 p(self.policy_sample), p(self.beliefs_last), p(self.start_policy_rows), _lib.stream_ptr(self.device))
         self.launches += 1
 
     def solve(self, root_beliefs: torch.Tensor, scalars: np.ndarray, leaf_fn=None, *, cfr_plus: bool = False,
               start_policy: torch.Tensor | None = None, warm_start_iterations: int = 0,
-              warm_start_multiplier: float = 1.0) -> SolveResult:
+              warm_start_multiplier: float = 1.0, warm_start_scalars: np.ndarray | None = None) -> SolveResult:
         """scalars: `iteration_scalars(T)` for all T iterations.  start_policy [M,1326] in the
         upstream node order (the policy head's softmax; None = uniform).  With
         warm_start_iterations = w > 0 (needs a start policy) the regrets are seeded from the start
         policy after the start pass (`warm_start` of type `model`, cfr_evaluator.py:887-926) and
-        the iterations w..T-1 follow."""
+        the iterations w..T-1 follow; `warm_start_scalars` (one row, `warm_start_mix_scalars`) gives
+        the mixing weights of the warm start's own policy update when the exponents follow a
+        schedule (default: the row of iteration w)."""
         assert root_beliefs.shape == (self.B, 2, HPAD) and root_beliefs.dtype == torch.float32
         assert root_beliefs.is_contiguous() and root_beliefs.device == self.device
         ws = int(warm_start_iterations)
@@ -349,7 +403,8 @@ class SteppedSolver(SubgameSolver):
             if start_policy is None:
                 raise ValueError("a warm start needs a start policy")
             # pass 0 is warm_start's own update_policy(w): it mixes with t = w, like iteration w after it
-            scalars = np.concatenate([scalars[ws:ws + 1], scalars[ws:]])
+            first = scalars[ws:ws + 1] if warm_start_scalars is None else warm_start_scalars
+            scalars = np.concatenate([first, scalars[ws:]])
         self.start_policy_rows = None
         if start_policy is not None:
             order = layout_tensor(self.layout, "to_level_major", start_policy.device)
@@ -396,7 +451,7 @@ def solve_noalloc(sv: SubgameSolver, root_beliefs: torch.Tensor, scalars_dev: to
     p = _lib.ptr
     with torch.cuda.device(sv.device):
         _lib.call(
-            "p2b_cfr_solve_noalloc", p(sv.subgames), p(sv.nodes), sv.B, sv.layout.max_children,
+            "p2b_cfr_solve_noalloc", p(sv.subgames), p(sv.nodes), sv.B, sv.layout.rows, sv.layout.max_children,
             sv.layout.max_internal, p(sv.tables.blob) if sv.tables is not None else None, p(root_beliefs),
             p(sv.regrets), p(sv.weight_sums), p(sv.policy_avg), p(sv.policy), p(sv.root_values), p(sv.values_avg),
             p(sv.beliefs_avg), p(sv.exploitability), p(sv.br_values), p(scalars_dev), int(scalars_dev.shape[0]),
