@@ -81,9 +81,8 @@ int p2b_showdown_values(const unsigned char* tables, const int32_t* table_of_row
  *  scratch    at least p2b_cfr_scratch_floats(max_internal, num_blocks) floats of work space.  With
  *             p2b_cfr_solve_scratch_floats(max_internal, max_children, num_blocks, num_subgames, rows)
  *             floats a solve without the optional outputs policy / policy_sample / beliefs_last runs as
- *             four launches (start pass; iteration passes in a leaner kernel, or in the general one for
- *             trees with more than one showdown child under a node; final pass) with the same results,
- *             bit for bit; the extra floats carry the root rows between the launches
+ *             three launches (start pass; iteration passes in a leaner kernel; final pass) with the same
+ *             results, bit for bit; the extra floats carry the root rows between the launches
  *  scalars    [iterations] 32-byte records {float t^alpha, t^alpha+1, t^beta, t^beta+1,
  *             mix_old, mix_new, fl(mix_old+mix_new); int32 do_mix}
  *  init_depth depth of the deepest tree of the batch (the upstream start pass re-normalises

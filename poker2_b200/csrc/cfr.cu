@@ -1057,7 +1057,6 @@ __device__ __forceinline__ void dot2_reference_order(Block& B, const FV<VPT>& x0
 template <int VPT, int MAXC>
 __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(const CfrParams p) {
     constexpr int NT = CfrThreads<VPT>::value;
-    if (p.gate == 2 && p.work_counter[2] == 0) return;  // these passes ran in cfr_iter_kernel
     extern __shared__ __align__(16) unsigned char smem[];
     Block B;
     B.tab = smem + kOffTab;
@@ -1208,14 +1207,12 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
 // malformed tree would make them index shared memory or the work rows out of range.  One block
 // per subgame, one thread per node.  On a violation the status word (work_counter[1]) receives
 // 1 + the subgame index and the subgame queue (work_counter[0]) is set past its end, so that the
-// solver kernel launched next on the stream finds no work at all.  work_counter[2] is set when a
-// node has more than one showdown child, which the iteration kernel (cfr_iter.cu) does not cover.
+// solver kernel launched next on the stream finds no work at all.
 __global__ void __launch_bounds__(kCfrMaxNodes) cfr_validate_kernel(const CfrParams p) {
     const int s = blockIdx.x, i = threadIdx.x;
     const SubgameRec sg = p.subgames[s];
     int bad = sg.n_nodes < 1 || sg.n_nodes > kCfrMaxNodes || sg.n_internal > p.max_internal || sg.node_begin < 0 ||
               (p.rows > 0 && (long long)sg.node_begin + sg.n_nodes > p.rows);
-    int many_showdowns = 0;
     if (!bad && i < sg.n_nodes) {
         const NodeRec nd = p.nodes[sg.node_begin + i];
         if (nd.kind > kModelLeaf || (nd.kind == kShowdownLeaf && (sg.table_index < 0 || p.tables == nullptr))) bad = 1;
@@ -1228,11 +1225,6 @@ __global__ void __launch_bounds__(kCfrMaxNodes) cfr_validate_kernel(const CfrPar
         if (nd.kind == kModelLeaf && p.leaf_begin && (p.leaf_beliefs || p.leaf_values) &&
             (p.leaf_begin[s] < 0 || p.leaf_begin[s] + (int)nd.internal_idx >= p.leaf_slots))
             bad = 1;
-        if (!bad && nd.kind == kInternal) {
-            int n_sd = 0;
-            for (int c = 0; c < nd.n_children; ++c) n_sd += p.nodes[sg.node_begin + nd.first_child + c].kind == kShowdownLeaf;
-            many_showdowns = n_sd > 1;
-        }
     }
     // internal_idx must be the rank among the subgame's internal nodes (the solver walks them
     // through a list indexed by it) and n_internal their number
@@ -1250,7 +1242,6 @@ __global__ void __launch_bounds__(kCfrMaxNodes) cfr_validate_kernel(const CfrPar
         atomicMax(p.work_counter + 1, s + 1);
         atomicMax(p.work_counter, p.num_subgames);
     }
-    if (many_showdowns) atomicOr(p.work_counter + 2, 1);
 }
 
 // Warm start of type `model` (p2/search/cfr_evaluator.py:913-926), applied between the start
@@ -1319,7 +1310,7 @@ int launch_cfr_warm_seed(const NodeRec* nodes, long long rows, const float* star
 }
 
 static int clear_counters(int32_t* work_counter, cudaStream_t stream) {
-    // [0] subgame queue, [1] status, [2] trees outside the iteration kernel, [3] spare
+    // [0] subgame queue, [1] status, [2], [3] spare
     return check_cuda(cudaMemsetAsync(work_counter, 0, 4 * sizeof(int32_t), stream), "cudaMemsetAsync(work counter)");
 }
 
@@ -1345,10 +1336,9 @@ int launch_cfr_solve(const CfrParams& params, int num_blocks, int max_children, 
         if (rc) return rc;
         return dispatch_cfr(p, num_blocks, max_children, stream);
     }
-    // A plain solve runs as: start pass (cfr_solve_kernel), iteration passes (cfr_iter_kernel, or
-    // cfr_solve_kernel for trees the record check keeps away from it), final pass with the best
-    // responses (cfr_solve_kernel).  Root rows and their sums travel between the launches in the tail
-    // of the scratch area; work rows do not, so each launch keeps one set per block.
+    // A plain solve runs as: start pass (cfr_solve_kernel), iteration passes (cfr_iter_kernel), final
+    // pass with the best responses (cfr_solve_kernel).  Root rows and their sums travel between the
+    // launches in the tail of the scratch area; work rows do not, so each launch keeps one set per block.
     long long per_block = cfr_scratch_floats(p.max_internal);
     const long long iter_block = cfr_iter_scratch_floats(p.max_internal, max_children);
     if (iter_block > per_block) per_block = iter_block;
@@ -1358,14 +1348,10 @@ int launch_cfr_solve(const CfrParams& params, int num_blocks, int max_children, 
     p.stepped = 1;
     p.scratch_per_block = 1;
     p.phases = 3;
-    for (int part = 0; part < 4; ++part) {
+    for (int part = 0; part < 3; ++part) {
         CfrParams q = p;
-        if (part == 0) q.pass_begin = q.pass_end = -1;
-        if (part == 1 || part == 2) {
-            q.pass_begin = 0;
-            q.pass_end = p.iterations - 1;
-        }
-        if (part == 3) q.pass_begin = q.pass_end = p.iterations;
+        q.pass_begin = part == 0 ? -1 : (part == 1 ? 0 : p.iterations);
+        q.pass_end = part == 0 ? -1 : (part == 1 ? p.iterations - 1 : p.iterations);
         rc = clear_counters(q.work_counter, stream);
         if (rc) return rc;
         if (part == 1) {
@@ -1374,7 +1360,6 @@ int launch_cfr_solve(const CfrParams& params, int num_blocks, int max_children, 
             if (rc) return rc;
             rc = launch_cfr_iter(q, num_blocks, stream);
         } else {
-            q.gate = part == 2 ? 2 : 0;
             rc = dispatch_cfr(q, num_blocks, max_children, stream);
         }
         if (rc) return rc;

@@ -98,8 +98,6 @@ struct CfrParams {
     int32_t leaf_slots;          // model-leaf slots of leaf_beliefs / leaf_values
     // ---- a one-launch solve split over several launches (start pass, iteration passes, final pass)
     int32_t scratch_per_block;   // stepped launch whose work rows are not carried: one set per block
-    int32_t gate;                // 0: run; 2: run only when the record check flagged trees the iteration
-                                 // kernel does not cover (work_counter[2] != 0)
 };
 
 // floats of scratch one block needs: per internal node reach[2], average reach[2], values[2]

@@ -24,6 +24,19 @@
 #include "exactdiv.cuh"
 #include "showdown.cuh"
 
+#ifndef IT_DOWN_ASYNC
+#define IT_DOWN_ASYNC 1
+#endif
+#ifndef IT_STAGE_BATCH
+#define IT_STAGE_BATCH 0
+#endif
+#ifndef IT_HANDS_LAND
+#define IT_HANDS_LAND 0
+#endif
+#ifndef IT_RW_BATCH
+#define IT_RW_BATCH 0
+#endif
+
 namespace p2b {
 
 namespace {
@@ -51,8 +64,10 @@ constexpr int kOffRsrc = kOffSig + kCfrMaxNodes * 2 * 4;               // uint8 
 constexpr int kOffIlist = kOffRsrc + kCfrMaxNodes * 2;                 // uint8 [internal nodes]
 constexpr int kOffSdc = kOffIlist + kCfrMaxNodes;                      // uint8 [internal nodes]
 constexpr int kOffMisc = kOffSdc + kCfrMaxNodes;
-constexpr int kIterSmem = kOffMisc + 64;
-static_assert(kOffStage % 16 == 0 && kOffTs % 16 == 0 && kTsBytes % 16 == 0 && kOffSig % 16 == 0 && kOffMisc % 16 == 0,
+constexpr int kOffLand = kOffMisc + 64;                                // float [kK][HPAD] landing rows of the bottom-up sweep
+constexpr int kIterSmem = kOffLand + (IT_HANDS_LAND ? kK * P2B_HPAD * 4 : 0);
+static_assert(kOffStage % 16 == 0 && kOffTs % 16 == 0 && kTsBytes % 16 == 0 && kOffSig % 16 == 0 && kOffMisc % 16 == 0 &&
+                  kOffLand % 16 == 0,
               "alignment");
 static_assert(kIterSmem <= 227 * 1024, "the block's shared memory must fit one SM");
 // the top-down sweep uses the staging area as two banks of child rows plus one stash row per child
@@ -89,6 +104,17 @@ __device__ __forceinline__ float div_g(float x, float y, float r, DivGuard& g) {
     return b == 0u ? q : q2;
 }
 
+// Asynchronous copy of this thread's slice of a global row into its slice of a shared row.  The
+// issuing thread sees the data after async_wait(); no other thread reads these slices.
+template <int VPT>
+__device__ __forceinline__ void async_row(float* smem_row, const float* global_row, int tid) {
+    static_assert(VPT == 2, "8-byte slices");
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_row + VPT * tid);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(global_row + VPT * tid) : "memory");
+}
+__device__ __forceinline__ void async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void async_wait() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
 struct IterBlock {
     unsigned char* tab;
     NodeRec* nodes;
@@ -98,7 +124,9 @@ struct IterBlock {
     uint8_t* rsrc;   // [node][player] internal index of the node whose reach row holds this player's reach (kNoRow: the mask)
     uint8_t* ilist;  // [ii] node index of the ii-th internal node
     uint8_t* sdc;    // [ii] child slot of the showdown leaf below the ii-th internal node (kNoRow: none)
-    int* misc;       // [0] subgame taken from the queue, [2],[3] unit counters of the two table sets
+    float* land;     // [kK][HPAD] bottom-up sweep: the children's current-policy rows, copied asynchronously
+    int* misc;       // [0] subgame taken from the queue, [2],[3] unit counters of the two table sets, [6] of an extra round
+                     // ([4],[5] hold fsum)
     float* fsum;
     SubgameRec sg;
     float* scr;
@@ -118,7 +146,13 @@ struct IterBlock {
     // top-down sweep: two banks of child rows (rows whose sums normalise the children's beliefs) and a stash
     __device__ __forceinline__ float* bank_row(int parity, int c) const { return stage + (parity * kK + c) * P2B_HPAD; }
     __device__ __forceinline__ float* stash_row(int c) const { return stage + (2 * kK + c) * P2B_HPAD; }
+    // top-down sweep: landing rows of asynchronous copies, in the table area (idle during that sweep):
+    // current policy and average policy of the children of one node
+    __device__ __forceinline__ float* land_row(int which, int c) const {
+        return reinterpret_cast<float*>(ts) + (which * kK + c) * P2B_HPAD;
+    }
 };
+static_assert(2 * kK * P2B_HPAD * 4 <= 2 * kTsBytes, "landing rows must fit the table area");
 
 // x / sum, or the uniform distribution over the allowed hands when the row is (numerically)
 // empty (cfr_evaluator.py:263-273)
@@ -211,13 +245,23 @@ __device__ __forceinline__ void iter_down(int pass, const CfrParams& p, IterBloc
     for (int i = 0; i < VPT; ++i) mask.v[i] = hi.allowed[i] ? 1.0f : 0.0f;
     int parity = 0;
     const int n_internal = B.sg.n_internal;
+    // the children's policy rows (and average-policy rows) land in shared memory one node ahead
+    auto fetch_children = [&](int ii) {
+        const NodeRec nn = B.nodes[B.ilist[ii]];
+        for (int c = 0; c < nn.n_children; ++c) {
+            async_row<VPT>(B.land_row(0, c), B.row_pcur(nn.first_child + c), tid);
+            if (mix) async_row<VPT>(B.land_row(1, c), B.state_row(p.policy_avg, nn.first_child + c), tid);
+        }
+        async_commit();
+    };
+    if (IT_DOWN_ASYNC) fetch_children(0);
 #pragma unroll 1
     for (int ii = 0; ii < n_internal; ++ii) {
         const int j = B.ilist[ii];
         const NodeRec nd = B.nodes[j];
         const int a = nd.to_act, k = nd.n_children, fc = nd.first_child;
-        if (mix && ii + 1 < n_internal) {  // the next node's average-policy rows are streamed from HBM: start them now
-            const NodeRec nn = B.nodes[B.ilist[ii + 1]];
+        if (mix && ii + 2 < n_internal) {  // average-policy rows are streamed from HBM: pull them into L2 two nodes ahead
+            const NodeRec nn = B.nodes[B.ilist[ii + 2]];
             prefetch_rows<VPT>(B.state_row(p.policy_avg, nn.first_child), nn.n_children, tid);
         }
         FV<VPT> ra = mask, rba = mask;
@@ -246,15 +290,25 @@ __device__ __forceinline__ void iter_down(int pass, const CfrParams& p, IterBloc
         }
         const int bank = parity;
         parity ^= 1;
-        // child loop; the rows of the next child are loaded while this one is worked on
-        FV<VPT> Pn = ldv<VPT>(B.row_pcur(fc), tid), Pbn;
-        if (mix) Pbn = ldv<VPT>(B.state_row(p.policy_avg, fc), tid);
+        if (IT_DOWN_ASYNC) async_wait();
+        FV<VPT> Pn, Pbn;
+        if (!IT_DOWN_ASYNC) {
+            Pn = ldv<VPT>(B.row_pcur(fc), tid);
+            if (mix) Pbn = ldv<VPT>(B.state_row(p.policy_avg, fc), tid);
+        }
 #pragma unroll 1
         for (int c = 0; c < k; ++c) {
-            const FV<VPT> P = Pn, Pb = Pbn;
-            if (c + 1 < k) {
-                Pn = ldv<VPT>(B.row_pcur(fc + c + 1), tid);
-                if (mix) Pbn = ldv<VPT>(B.state_row(p.policy_avg, fc + c + 1), tid);
+            FV<VPT> P, Pb;
+            if (IT_DOWN_ASYNC) {
+                P = ldv<VPT>(B.land_row(0, c), tid);
+                if (mix) Pb = ldv<VPT>(B.land_row(1, c), tid);
+            } else {
+                P = Pn;
+                Pb = Pbn;
+                if (c + 1 < k) {
+                    Pn = ldv<VPT>(B.row_pcur(fc + c + 1), tid);
+                    if (mix) Pbn = ldv<VPT>(B.state_row(p.policy_avg, fc + c + 1), tid);
+                }
             }
             const NodeRec ch = B.nodes[fc + c];
             FV<VPT> t;
@@ -294,6 +348,7 @@ __device__ __forceinline__ void iter_down(int pass, const CfrParams& p, IterBloc
                 stv<VPT>(B.state_row(p.policy_avg, fc + c), tid, P);
             }
         }
+        if (IT_DOWN_ASYNC && ii + 1 < n_internal) fetch_children(ii + 1);  // the landing rows are free again
         if (mix) {  // renormalise over the siblings (:1241-1258)
             Divisor dsum[VPT];
             bool dsum_ok = true;
@@ -481,6 +536,14 @@ __device__ __forceinline__ void iter_up_stage(int pass, const CfrParams& p, Iter
     const NodeRec nd = B.nodes[j];
     const int a = nd.to_act, o = 1 - a, k = nd.n_children, fc = nd.first_child;
     const FV<VPT> prior_a = pick<VPT>(prior, a);
+    // every global row this half needs is requested before anything is computed: the child loops
+    // below are unrolled over the largest child count and leave at the node's own count
+    FV<VPT> P[kK];
+#if IT_STAGE_BATCH
+#pragma unroll
+    for (int c = 0; c < kK; ++c)
+        if (c < k) P[c] = ldv<VPT>(B.row_pcur(fc + c), tid);
+#endif
     FV<VPT> r_a, b_a, b_o;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) r_a.v[i] = hi.allowed[i] ? 1.0f : 0.0f;
@@ -508,19 +571,26 @@ __device__ __forceinline__ void iter_up_stage(int pass, const CfrParams& p, Iter
     stv<VPT>(B.set_row(set, 0), tid, b_a);
     stv<VPT>(B.set_row(set, 1), tid, b_o);
     const int sd = B.sdc[ii];
+#if IT_STAGE_BATCH
+#pragma unroll
+    for (int c = 0; c < kK; ++c) {
+        if (c >= k) break;
+        const FV<VPT> Pc = P[c];
+#else
     FV<VPT> Pn = ldv<VPT>(B.row_pcur(fc), tid);
 #pragma unroll 1
     for (int c = 0; c < k; ++c) {
-        const FV<VPT> P = Pn;
+        const FV<VPT> Pc = Pn;
         if (c + 1 < k) Pn = ldv<VPT>(B.row_pcur(fc + c + 1), tid);
+#endif
         FV<VPT> m;
 #pragma unroll
-        for (int i = 0; i < VPT; ++i) m.v[i] = __fmul_rn(b_a.v[i], P.v[i]);
+        for (int i = 0; i < VPT; ++i) m.v[i] = __fmul_rn(b_a.v[i], Pc.v[i]);
         stv<VPT>(B.set_row(set, kRowM + c), tid, m);
         if (c == sd) {
             FV<VPT> bca;
 #pragma unroll
-            for (int i = 0; i < VPT; ++i) bca.v[i] = __fmul_rn(prior_a.v[i], __fmul_rn(r_a.v[i], P.v[i]));
+            for (int i = 0; i < VPT; ++i) bca.v[i] = __fmul_rn(prior_a.v[i], __fmul_rn(r_a.v[i], Pc.v[i]));
             norm_row<VPT>(B.sg.allowed_prob, hi, bca, B.sig[(fc + c) * 2 + a]);
             stv<VPT>(B.set_row(set, kRowLeaf), tid, bca);
         }
@@ -551,7 +621,7 @@ __device__ __forceinline__ void showdown_ev(const IterBlock& B, const HandInfo<V
 // regrets (:1168-1185) into the current-policy rows of the next pass.
 template <int VPT>
 __device__ __forceinline__ void iter_up_hands(int pass, const CfrParams& p, IterBlock& B, const HandInfo<VPT>& hi,
-                                              int ii, int set, int tid) {
+                                              const FV<VPT> (&prior)[2], int ii, int set, int tid) {
     const int j = B.ilist[ii];
     const NodeRec nd = B.nodes[j];
     const int a = nd.to_act, o = 1 - a, k = nd.n_children, fc = nd.first_child;
@@ -560,6 +630,11 @@ __device__ __forceinline__ void iter_up_hands(int pass, const CfrParams& p, Iter
     const double* __restrict__ St = reinterpret_cast<const double*>(ts + kTsS);
     const float* __restrict__ pref = reinterpret_cast<const float*>(ts + kTsPref);
     const float* __restrict__ pc = reinterpret_cast<const float*>(ts + kTsPc);
+    // the children's policy rows travel to shared memory while the showdown formulas are evaluated
+    if (IT_HANDS_LAND) {
+        for (int c = 0; c < k; ++c) async_row<VPT>(B.land + c * P2B_HPAD, B.row_pcur(fc + c), tid);
+        async_commit();
+    }
     const FV<VPT> b_a = ldv<VPT>(B.set_row(set, 0), tid), b_o = ldv<VPT>(B.set_row(set, 1), tid);
     FV<VPT> wgt, denm, eva, evo, acc_a, acc_o;
     Divisor ddenm[VPT];
@@ -582,19 +657,24 @@ __device__ __forceinline__ void iter_up_hands(int pass, const CfrParams& p, Iter
     // ---- children: values and backup ----
     {
         NodeRec chn = B.nodes[fc];
-        FV<VPT> Pn = ldv<VPT>(B.row_pcur(fc), tid), Van, Von;
+        FV<VPT> Van, Von;
         if (chn.kind == kInternal) {
             Van = ldv<VPT>(B.row_val(chn.internal_idx, a), tid);
             Von = ldv<VPT>(B.row_val(chn.internal_idx, o), tid);
         }
+        FV<VPT> Pn;
+        if (IT_HANDS_LAND) async_wait();
+        else Pn = ldv<VPT>(B.row_pcur(fc), tid);
 #pragma unroll 1
         for (int c = 0; c < k; ++c) {
             const NodeRec ch = chn;
-            const FV<VPT> P = Pn;
+            FV<VPT> P;
+            if (IT_HANDS_LAND) P = ldv<VPT>(B.land + c * P2B_HPAD, tid);
+            else P = Pn;
             FV<VPT> V_a = Van, V_o = Von;
             if (c + 1 < k) {
                 chn = B.nodes[fc + c + 1];
-                Pn = ldv<VPT>(B.row_pcur(fc + c + 1), tid);
+                if (!IT_HANDS_LAND) Pn = ldv<VPT>(B.row_pcur(fc + c + 1), tid);
                 if (chn.kind == kInternal) {
                     Van = ldv<VPT>(B.row_val(chn.internal_idx, a), tid);
                     Von = ldv<VPT>(B.row_val(chn.internal_idx, o), tid);
@@ -625,6 +705,26 @@ __device__ __forceinline__ void iter_up_hands(int pass, const CfrParams& p, Iter
                     V_o.v[i] = -va;
                 }
             } else if (ch.kind == kShowdownLeaf) {
+                if (c != sd) {
+                    // A further showdown child (a call and an all-in of the same size; rare): its tables
+                    // are built here, in one more block-wide round, in place of the first one's.
+                    const FV<VPT> prior_a = pick<VPT>(prior, a);
+                    FV<VPT> bca;
+#pragma unroll
+                    for (int i = 0; i < VPT; ++i) bca.v[i] = hi.allowed[i] ? 1.0f : 0.0f;
+                    const int sa = B.rsrc[j * 2 + a];
+                    if (j != 0 && sa != kNoRow) bca = ldv<VPT>(B.row_reach(sa), tid);
+#pragma unroll
+                    for (int i = 0; i < VPT; ++i) bca.v[i] = __fmul_rn(prior_a.v[i], __fmul_rn(bca.v[i], P.v[i]));
+                    norm_row<VPT>(B.sg.allowed_prob, hi, bca, B.sig[(fc + c) * 2 + a]);
+                    __syncthreads();  // every thread is done with the leaf tables of the first showdown child
+                    stv<VPT>(B.set_row(set, kRowLeaf), tid, bca);
+                    if (tid == 0) B.misc[6] = 0;
+                    __syncthreads();
+                    table_units(B, B.set_row(set, 0), B.ts + set * kTsBytes, 0, true, B.misc + 6);
+                    __syncthreads();
+                    showdown_ev<VPT>(B, hi, tid, B.set_row(set, kRowLeaf), pref + P2B_HPAD, pc + 52 * 52, evo);
+                }
                 const float pot_a = a == 0 ? ch.v0 : ch.v1, pot_o = a == 0 ? ch.v1 : ch.v0;
                 const Divisor dscale = make_divisor(B.sg.scale);
                 DivGuard g = guard_begin(dscale.ok);
@@ -669,6 +769,21 @@ __device__ __forceinline__ void iter_up_hands(int pass, const CfrParams& p, Iter
 #pragma unroll
     for (int i = 0; i < VPT; ++i) psum.v[i] = 0.0f;
     {
+        // all state rows of the node are requested at once; the loop is unrolled over the largest
+        // child count and leaves at the node's own
+#if IT_RW_BATCH
+        FV<VPT> Rs[kK], Ws[kK];
+#pragma unroll
+        for (int c = 0; c < kK; ++c)
+            if (c < k) {
+                Rs[c] = ldv<VPT>(B.state_row(p.regrets, fc + c), tid);
+                if (tracked) Ws[c] = ldv<VPT>(B.state_row(p.weight_sums, fc + c), tid);
+            }
+#pragma unroll
+        for (int c = 0; c < kK; ++c) {
+            if (c >= k) break;
+            FV<VPT> R = Rs[c], W = Ws[c];
+#else
         FV<VPT> Rn = ldv<VPT>(B.state_row(p.regrets, fc), tid), Wn;
         if (tracked) Wn = ldv<VPT>(B.state_row(p.weight_sums, fc), tid);
 #pragma unroll 1
@@ -678,6 +793,7 @@ __device__ __forceinline__ void iter_up_hands(int pass, const CfrParams& p, Iter
                 Rn = ldv<VPT>(B.state_row(p.regrets, fc + c + 1), tid);
                 if (tracked) Wn = ldv<VPT>(B.state_row(p.weight_sums, fc + c + 1), tid);
             }
+#endif
             const FV<VPT> Va = ldv<VPT>(B.set_row(set, kRowM + c), tid);
             FV<VPT> rn, wn, rq, wq, dy;
             DivGuard g = guard_begin(d_ok);
@@ -747,8 +863,6 @@ __device__ __forceinline__ void iter_up_hands(int pass, const CfrParams& p, Iter
 template <int VPT>
 __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_iter_kernel(const CfrParams p) {
     constexpr int NT = CfrThreads<VPT>::value;
-    // trees this kernel does not cover (flagged by the record check) are left to cfr_solve_kernel
-    if (p.work_counter[2] != 0) return;
     extern __shared__ __align__(16) unsigned char smem[];
     IterBlock B;
     B.tab = smem + kOffTab;
@@ -761,6 +875,7 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_iter_kernel(con
     B.sdc = smem + kOffSdc;
     B.misc = reinterpret_cast<int*>(smem + kOffMisc);
     B.fsum = reinterpret_cast<float*>(smem + kOffMisc + 16);
+    B.land = reinterpret_cast<float*>(smem + kOffLand);
     B.max_internal = p.max_internal;
     B.scr = p.scratch + (long long)blockIdx.x * p.scratch_stride;
     const int tid = threadIdx.x;
@@ -860,7 +975,7 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_iter_kernel(con
                     table_units(B, B.set_row(set ^ 1, 0), B.ts + (set ^ 1) * kTsBytes, 2 + nd.n_children,
                                 B.sdc[ii - 1] != kNoRow, B.misc + 2 + (set ^ 1));
                 }
-                iter_up_hands<VPT>(pass, p, B, hi, ii, set, tid);
+                iter_up_hands<VPT>(pass, p, B, hi, prior, ii, set, tid);
                 set ^= 1;
             }
             __syncthreads();

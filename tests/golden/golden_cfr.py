@@ -110,7 +110,8 @@ def river_env(boards: torch.Tensor, pot: torch.Tensor, stack: torch.Tensor):
     return env
 
 
-def make_evaluator(n, iterations, depth=8):
+def make_evaluator(n, iterations, depth=8, search=None, enforce_zero_sum=False):
+    """search: overrides of cfg.search fields (name -> value), applied after the defaults below."""
     from p2.core.structured_config import CFRType, Config
     from p2.search.sparse_cfr_evaluator import SparseCFREvaluator
 
@@ -129,8 +130,12 @@ def make_evaluator(n, iterations, depth=8):
     cfg.search.dcfr_alpha, cfg.search.dcfr_beta, cfg.search.dcfr_gamma = 1.5, 0.0, 2.0
     cfg.search.dcfr_plus_delay = 0
     cfg.search.value_targets_from_final_policy = True
-    ev = SparseCFREvaluator(ZeroModel(len(BET_BINS) + 3), torch.device("cpu"), cfg,
-                            generator=torch.Generator().manual_seed(0))
+    for name, value in (search or {}).items():
+        assert hasattr(cfg.search, name), name
+        setattr(cfg.search, name, value)
+    model = ZeroModel(len(BET_BINS) + 3)
+    model.enforce_zero_sum = enforce_zero_sum
+    ev = SparseCFREvaluator(model, torch.device("cpu"), cfg, generator=torch.Generator().manual_seed(0))
     ev.sample_leaves = lambda training_mode: None
     return ev
 

@@ -1,0 +1,145 @@
+"""Golden vectors for solver settings beyond plain DCFR (runs the upstream evaluator): the
+search block of the upstream production configuration, standard CFR, zero-sum enforcement of
+the value targets, and the headline workload at depth (ragged roots x 256 iterations).
+
+Imported by make_golden.py; same river / turn set-up as golden_cfr.py.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+import golden_cfr as gc
+from golden_cfr import BET_BINS, save
+
+
+def _solve(ev, env, n, ranges, seed=5):
+    ev.initialize_subgame(env, torch.arange(n), ranges)
+    ev.generator = torch.Generator().manual_seed(seed)  # consumed by the sampling schedule only
+    ev.evaluate_cfr()
+    return ev._compute_exploitability()
+
+
+def gen_production() -> None:
+    """The search block of conf/config_rebel_cfr.yaml:78-94 (discounted_plus with a delay, exponent
+    schedules alpha 2->4, beta -1->-2, gamma 5->0, warm start of type `model` with 15 iterations and
+    multiplier 10) at a reduced iteration count, with a zero-sum model like the production default."""
+    from p2.core.structured_config import CFRType, WarmStartType
+
+    b, r, p, s = gc.seeded_inputs(21, 2, (20, 200), (100, 1000))
+    iterations, ws, delay, cap, depth = 40, 15, 24, 2, 8
+    search = dict(cfr_type=CFRType.discounted_plus, dcfr_plus_delay=delay, warm_start_iterations=ws,
+                  warm_start_type=WarmStartType.model, warm_start_multiplier=10.0,
+                  dcfr_alpha=2.0, dcfr_alpha_final=4.0, dcfr_beta=-1.0, dcfr_beta_final=-2.0,
+                  dcfr_gamma=5.0, dcfr_gamma_final=0.0)
+    gc.install_raise_cap(cap)
+    ev = gc.make_evaluator(2, iterations, depth=depth, search=search, enforce_zero_sum=True)
+    model = gc.FixedLogitModel(len(BET_BINS) + 3)
+    model.enforce_zero_sum = True
+    ev.model = model
+    captured = {}
+    original = ev.warm_start
+
+    def hooked():
+        captured["start_policy"] = ev.policy_probs.clone()
+        original()
+
+    ev.warm_start = hooked
+    ex = _solve(ev, gc.river_env(b, p, s), 2, r)
+    gc.install_raise_cap(None)
+    print("production block: nodes", ev.total_nodes, "exploitability", ex.local_exploitability.tolist())
+    save("cfr_production_cap2_t40.npz",
+         boards=b.to(torch.int16).numpy(), ranges=r.numpy(), pot=p.numpy(), stack=s.numpy(),
+         iterations=np.int64(iterations), warm_start_iterations=np.int64(ws), warm_start_multiplier=np.float64(10.0),
+         dcfr_delay=np.int64(delay), cap=np.int64(cap), max_depth=np.int64(depth),
+         alpha=np.float64([2.0, 4.0]), beta=np.float64([-1.0, -2.0]), gamma=np.float64([5.0, 0.0]),
+         total_nodes=np.int64(ev.total_nodes), start_policy=captured["start_policy"].numpy(),
+         regrets=ev.cumulative_regrets.numpy(), weight_sums=ev.regret_weight_sums.numpy(),
+         policy_avg=ev.policy_probs_avg.numpy(), root_values=ev.values_avg[:2].numpy(),
+         values_avg=ev.values_avg.numpy(), t_sample=ev.t_sample[:2].numpy(),
+         policy_sample=ev.policy_probs_sample.numpy(), exploitability=ex.local_exploitability.numpy())
+
+
+def gen_standard() -> None:
+    """cfr_type = standard (no discounting, mixing weights (t, 1)), 16 iterations."""
+    from p2.core.structured_config import CFRType
+
+    b, r, p, s = gc.seeded_inputs(22, 2, (20, 200), (100, 1000))
+    iterations, cap, depth = 16, 2, 8
+    gc.install_raise_cap(cap)
+    ev = gc.make_evaluator(2, iterations, depth=depth, search=dict(cfr_type=CFRType.standard))
+    ex = _solve(ev, gc.river_env(b, p, s), 2, r)
+    gc.install_raise_cap(None)
+    print("standard CFR: nodes", ev.total_nodes, "exploitability", ex.local_exploitability.tolist())
+    save("cfr_standard_cap2_t16.npz",
+         boards=b.to(torch.int16).numpy(), ranges=r.numpy(), pot=p.numpy(), stack=s.numpy(),
+         iterations=np.int64(iterations), cap=np.int64(cap), max_depth=np.int64(depth),
+         total_nodes=np.int64(ev.total_nodes), regrets=ev.cumulative_regrets.numpy(),
+         weight_sums=ev.regret_weight_sums.numpy(), policy_avg=ev.policy_probs_avg.numpy(),
+         root_values=ev.values_avg[:2].numpy(), exploitability=ex.local_exploitability.numpy())
+
+
+def gen_zero_sum() -> None:
+    """Value targets with `model.enforce_zero_sum = True` (the model-config default): the shift of
+    `update_average_values_final` (cfr_evaluator.py:1289-1292) on river subgames, and on turn
+    subgames whose model leaves are shifted too."""
+    b, r, p, s = gc.seeded_inputs(23, 2, (20, 200), (100, 1000))
+    iterations, cap, depth = 12, 2, 8
+    gc.install_raise_cap(cap)
+    ev = gc.make_evaluator(2, iterations, depth=depth, enforce_zero_sum=True)
+    ex = _solve(ev, gc.river_env(b, p, s), 2, r)
+    river = dict(
+        river_boards=b.to(torch.int16).numpy(), river_ranges=r.numpy(), river_pot=p.numpy(), river_stack=s.numpy(),
+        river_iterations=np.int64(iterations), river_total_nodes=np.int64(ev.total_nodes),
+        river_policy_avg=ev.policy_probs_avg.numpy(), river_values_avg=ev.values_avg.numpy(),
+        river_beliefs_avg=ev.beliefs_avg.numpy(), river_exploitability=ex.local_exploitability.numpy())
+    print("zero-sum river: nodes", ev.total_nodes, "exploitability", ex.local_exploitability.tolist())
+
+    g = torch.Generator().manual_seed(24)
+    n, iterations_t = 3, 10
+    import make_golden
+    boards = torch.stack([torch.randperm(52, generator=g)[:4] for _ in range(n)])
+    ranges = make_golden.dirichlet_ranges(boards, g)
+    pot = torch.randint(20, 201, (n,), generator=g)
+    stack = torch.randint(100, 1001, (n,), generator=g)
+    ev = gc.make_evaluator(n, iterations_t, depth=depth, enforce_zero_sum=True)
+    model = gc.PotEchoModel(len(BET_BINS) + 3)
+    model.enforce_zero_sum = True
+    ev.model = model
+    ex = _solve(ev, gc.turn_env(boards, pot, stack), n, ranges, seed=123)
+    gc.install_raise_cap(None)
+    model_mask = ev.leaf_mask & ~ev.env.done
+    print("zero-sum turn: nodes", ev.total_nodes, "model leaves", int(model_mask.sum()),
+          "exploitability", ex.local_exploitability.tolist())
+    save("cfr_zero_sum.npz", cap=np.int64(cap), max_depth=np.int64(depth), **river,
+         turn_boards=boards.to(torch.int16).numpy(), turn_ranges=ranges.numpy(), turn_pot=pot.numpy(),
+         turn_stack=stack.numpy(), turn_iterations=np.int64(iterations_t), turn_total_nodes=np.int64(ev.total_nodes),
+         turn_model_mask=model_mask.numpy(), hand_weights=gc.hand_weights().numpy(),
+         turn_policy_avg=ev.policy_probs_avg.numpy(), turn_values_avg=ev.values_avg.numpy(),
+         turn_exploitability=ex.local_exploitability.numpy(), turn_br_values=ex.local_best_response_values.numpy())
+
+
+def gen_ragged256() -> None:
+    """The headline workload at depth: 16 ragged river roots (pot U[20,200], stack U[100,1000]),
+    max 2 raises, DCFR(1.5, 0, 2), 256 iterations.  Kept small: root values, exploitability and a
+    fixed subsample of the average-policy rows."""
+    n, iterations, cap, depth = 16, 256, 2, 8
+    b, r, p, s = gc.seeded_inputs(2, n, (20, 200), (100, 1000))
+    gc.install_raise_cap(cap)
+    ev = gc.make_evaluator(n, iterations, depth=depth)
+    ex = _solve(ev, gc.river_env(b, p, s), n, r)
+    gc.install_raise_cap(None)
+    rows = np.arange(n, ev.total_nodes, 11, dtype=np.int64)  # every 11th non-root node, upstream order
+    print("ragged x256: nodes", ev.total_nodes, "rows kept", len(rows), "exploitability",
+          ex.local_exploitability.tolist()[:4])
+    save("cfr_ragged16_cap2_t256.npz",
+         boards=b.to(torch.int16).numpy(), ranges=r.numpy(), pot=p.numpy(), stack=s.numpy(),
+         iterations=np.int64(iterations), cap=np.int64(cap), max_depth=np.int64(depth),
+         total_nodes=np.int64(ev.total_nodes), policy_rows=rows,
+         policy_avg_rows=ev.policy_probs_avg[torch.from_numpy(rows)].numpy(),
+         regret_rows=ev.cumulative_regrets[torch.from_numpy(rows)].numpy(),
+         root_values=ev.values_avg[:n].numpy(), exploitability=ex.local_exploitability.numpy(),
+         br_values=ex.local_best_response_values.numpy())
+
+
+gc.SECTIONS.update(production=gen_production, standard=gen_standard, zero_sum=gen_zero_sum, ragged256=gen_ragged256)
