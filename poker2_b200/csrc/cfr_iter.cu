@@ -24,23 +24,26 @@
 #include "exactdiv.cuh"
 #include "showdown.cuh"
 
-#ifndef IT_DOWN_ASYNC
-#define IT_DOWN_ASYNC 1
+// Hands per thread and blocks per SM of the iteration kernel: 3 x 448 threads x 2 blocks (28 warps
+// per SM, two subgames interleaving on one SM, single-buffered tables) or 2 x 672 threads x 1 block
+// (21 warps, double-buffered tables with the cross-hand units one node ahead).
+#ifndef P2B_ITER_VPT
+#define P2B_ITER_VPT 3
 #endif
-#ifndef IT_STAGE_BATCH
-#define IT_STAGE_BATCH 0
-#endif
-#ifndef IT_HANDS_LAND
-#define IT_HANDS_LAND 0
-#endif
-#ifndef IT_RW_BATCH
-#define IT_RW_BATCH 0
+#ifndef P2B_ITER_CTAS
+#define P2B_ITER_CTAS 2
 #endif
 
 namespace p2b {
 
 namespace {
 
+constexpr int kVpt = P2B_ITER_VPT;    // hands per thread
+constexpr int kCtas = P2B_ITER_CTAS;  // blocks per SM
+static_assert((kVpt == 2 && kCtas == 1) || (kVpt == 3 && kCtas == 2), "supported configurations");
+constexpr int kNT = P2B_HPAD / kVpt;  // threads per block
+constexpr bool kDouble = kCtas == 1;  // staged rows and tables double buffered, units one node ahead
+constexpr int kSets = kDouble ? 2 : 1;
 constexpr int kK = kCfrMaxChildren;
 constexpr int kSetRows = 2 + kK + 1;  // beliefs of the acting / the other player, one row per child, one leaf row
 constexpr int kRowM = 2;
@@ -57,21 +60,24 @@ constexpr int kTsBytes = kTsPc + 2 * 52 * 52 * 4;
 // ---- shared memory carve-up (bytes) ----
 constexpr int kOffTab = 0;
 constexpr int kOffNodes = kOffTab + kTabBytes;
-constexpr int kOffStage = kOffNodes + kCfrMaxNodes * 16;               // float [2][kSetRows][HPAD]
-constexpr int kOffTs = kOffStage + 2 * kSetRows * P2B_HPAD * 4;        // two table sets
-constexpr int kOffSig = kOffTs + 2 * kTsBytes;                         // float [nodes][2]
+constexpr int kOffStage = kOffNodes + kCfrMaxNodes * 16;               // float [kSets][kSetRows][HPAD]
+constexpr int kOffTs = kOffStage + kSets * kSetRows * P2B_HPAD * 4;    // kSets table sets, right behind the rows
+constexpr int kOffSig = kOffTs + kSets * kTsBytes;                     // float [nodes][2]
 constexpr int kOffRsrc = kOffSig + kCfrMaxNodes * 2 * 4;               // uint8 [nodes][2]
 constexpr int kOffIlist = kOffRsrc + kCfrMaxNodes * 2;                 // uint8 [internal nodes]
 constexpr int kOffSdc = kOffIlist + kCfrMaxNodes;                      // uint8 [internal nodes]
 constexpr int kOffMisc = kOffSdc + kCfrMaxNodes;
-constexpr int kOffLand = kOffMisc + 64;                                // float [kK][HPAD] landing rows of the bottom-up sweep
-constexpr int kIterSmem = kOffLand + (IT_HANDS_LAND ? kK * P2B_HPAD * 4 : 0);
-static_assert(kOffStage % 16 == 0 && kOffTs % 16 == 0 && kTsBytes % 16 == 0 && kOffSig % 16 == 0 && kOffMisc % 16 == 0 &&
-                  kOffLand % 16 == 0,
+constexpr int kIterSmem = kOffMisc + 64;
+static_assert(kOffStage % 16 == 0 && kOffTs % 16 == 0 && kTsBytes % 16 == 0 && kOffSig % 16 == 0 && kOffMisc % 16 == 0,
               "alignment");
-static_assert(kIterSmem <= 227 * 1024, "the block's shared memory must fit one SM");
-// the top-down sweep uses the staging area as two banks of child rows plus one stash row per child
-static_assert(3 * kK <= 2 * kSetRows, "top-down rows must fit the staging area");
+static_assert(kIterSmem + 1024 <= 227 * 1024 / kCtas, "the blocks' shared memory must fit one SM");
+// The top-down sweep uses the staging rows and the (then idle) table area behind them as kSets banks
+// of child rows plus one stash row per child; with two table sets the rest of the table area
+// receives the asynchronous copies of the children's policy rows.
+constexpr int kDownRows = (kSets + 1) * kK;
+static_assert(kDownRows * P2B_HPAD * 4 <= kOffSig - kOffStage, "top-down rows must fit the staging and table areas");
+constexpr bool kDownAsync = kDouble && kVpt == 2;
+static_assert(!kDownAsync || (kDownRows + 2 * kK) * P2B_HPAD * 4 <= kOffSig - kOffStage, "landing rows must fit");
 
 constexpr uint8_t kNoRow = 0xFF;
 
@@ -104,13 +110,50 @@ __device__ __forceinline__ float div_g(float x, float y, float r, DivGuard& g) {
     return b == 0u ? q : q2;
 }
 
+// Hands of a thread: two consecutive ones (64-bit accesses), or three a third of a row apart
+// (32-bit accesses, consecutive threads on consecutive hands).
+template <int VPT>
+__device__ __forceinline__ int hand_of(int tid, int i) {
+    return VPT == 2 ? 2 * tid + i : tid + i * (P2B_HPAD / VPT);
+}
+template <int VPT>
+__device__ __forceinline__ FV<VPT> ldh(const float* row, int tid) {
+    if constexpr (VPT == 2) {
+        return ldv<2>(row, tid);
+    } else {
+        FV<VPT> r;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) r.v[i] = row[tid + i * (P2B_HPAD / VPT)];
+        return r;
+    }
+}
+template <int VPT>
+__device__ __forceinline__ void sth(float* row, int tid, const FV<VPT>& r) {
+    if constexpr (VPT == 2) {
+        stv<2>(row, tid, r);
+    } else {
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) row[tid + i * (P2B_HPAD / VPT)] = r.v[i];
+    }
+}
+// Pulls n consecutive rows into L2: a row is 42 lines of 128 bytes, thread t takes line t of each.
+__device__ __forceinline__ void prefetch_lines(const float* row, int n, int tid) {
+    if (tid < P2B_HPAD / 32) {
+        const float* mine = row + 32 * tid;
+#pragma unroll
+        for (int c = 0; c < kK; ++c)
+            if (c < n) asm volatile("prefetch.global.L2 [%0];" ::"l"(mine + c * P2B_HPAD));
+    }
+}
+
 // Asynchronous copy of this thread's slice of a global row into its slice of a shared row.  The
 // issuing thread sees the data after async_wait(); no other thread reads these slices.
 template <int VPT>
 __device__ __forceinline__ void async_row(float* smem_row, const float* global_row, int tid) {
-    static_assert(VPT == 2, "8-byte slices");
-    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_row + VPT * tid);
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(global_row + VPT * tid) : "memory");
+    if constexpr (VPT == 2) {
+        const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_row + VPT * tid);
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(global_row + VPT * tid) : "memory");
+    }
 }
 __device__ __forceinline__ void async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void async_wait() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
@@ -124,7 +167,6 @@ struct IterBlock {
     uint8_t* rsrc;   // [node][player] internal index of the node whose reach row holds this player's reach (kNoRow: the mask)
     uint8_t* ilist;  // [ii] node index of the ii-th internal node
     uint8_t* sdc;    // [ii] child slot of the showdown leaf below the ii-th internal node (kNoRow: none)
-    float* land;     // [kK][HPAD] bottom-up sweep: the children's current-policy rows, copied asynchronously
     int* misc;       // [0] subgame taken from the queue, [2],[3] unit counters of the two table sets, [6] of an extra round
                      // ([4],[5] hold fsum)
     float* fsum;
@@ -143,16 +185,15 @@ struct IterBlock {
         return base + (long long)(sg.node_begin + node) * P2B_HPAD;
     }
     __device__ __forceinline__ float* set_row(int set, int r) const { return stage + (set * kSetRows + r) * P2B_HPAD; }
-    // top-down sweep: two banks of child rows (rows whose sums normalise the children's beliefs) and a stash
+    // top-down sweep: kSets banks of child rows (rows whose sums normalise the children's beliefs), a stash
+    // row per child and, with asynchronous copies, landing rows for the current policy and the average
+    // policy of the children of one node
     __device__ __forceinline__ float* bank_row(int parity, int c) const { return stage + (parity * kK + c) * P2B_HPAD; }
-    __device__ __forceinline__ float* stash_row(int c) const { return stage + (2 * kK + c) * P2B_HPAD; }
-    // top-down sweep: landing rows of asynchronous copies, in the table area (idle during that sweep):
-    // current policy and average policy of the children of one node
+    __device__ __forceinline__ float* stash_row(int c) const { return stage + (kSets * kK + c) * P2B_HPAD; }
     __device__ __forceinline__ float* land_row(int which, int c) const {
-        return reinterpret_cast<float*>(ts) + (which * kK + c) * P2B_HPAD;
+        return stage + (kDownRows + which * kK + c) * P2B_HPAD;
     }
 };
-static_assert(2 * kK * P2B_HPAD * 4 <= 2 * kTsBytes, "landing rows must fit the table area");
 
 // x / sum, or the uniform distribution over the allowed hands when the row is (numerically)
 // empty (cfr_evaluator.py:263-273)
@@ -175,8 +216,8 @@ __device__ __forceinline__ void norm_row(float allowed_prob, const HandInfo<VPT>
 template <int VPT>
 __device__ __forceinline__ void normalize_pair(IterBlock& B, const HandInfo<VPT>& hi, FV<VPT> (&x)[2]) {
     const int tid = threadIdx.x;
-    stv<VPT>(B.set_row(0, 0), tid, x[0]);
-    stv<VPT>(B.set_row(0, 1), tid, x[1]);
+    sth<VPT>(B.set_row(0, 0), tid, x[0]);
+    sth<VPT>(B.set_row(0, 1), tid, x[1]);
     __syncthreads();
     const int warp = tid >> 5;
     if (warp < 2) {
@@ -200,13 +241,13 @@ __device__ __forceinline__ void policy_from_regrets(const CfrParams& p, IterBloc
     for (int i = 0; i < VPT; ++i) sum.v[i] = 0.0f;
 #pragma unroll 1
     for (int c = 0; c < k; ++c) {
-        FV<VPT> R = ldv<VPT>(B.state_row(p.regrets, fc + c), tid);
+        FV<VPT> R = ldh<VPT>(B.state_row(p.regrets, fc + c), tid);
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             R.v[i] = fmaxf(R.v[i], 0.0f);
             sum.v[i] = __fadd_rn(sum.v[i], R.v[i]);
         }
-        stv<VPT>(B.stash_row(c), tid, R);
+        sth<VPT>(B.stash_row(c), tid, R);
     }
     Divisor ds[VPT];
     bool dok = true;
@@ -217,7 +258,7 @@ __device__ __forceinline__ void policy_from_regrets(const CfrParams& p, IterBloc
     }
 #pragma unroll 1
     for (int c = 0; c < k; ++c) {
-        const FV<VPT> pos = ldv<VPT>(B.stash_row(c), tid);
+        const FV<VPT> pos = ldh<VPT>(B.stash_row(c), tid);
         DivGuard g = guard_begin(dok);
         FV<VPT> P;
 #pragma unroll
@@ -228,7 +269,7 @@ __device__ __forceinline__ void policy_from_regrets(const CfrParams& p, IterBloc
         }
 #pragma unroll
         for (int i = 0; i < VPT; ++i) P.v[i] = sum.v[i] > 1e-8f ? P.v[i] : invk;
-        stv<VPT>(B.row_pcur(fc + c), tid, P);
+        sth<VPT>(B.row_pcur(fc + c), tid, P);
     }
 }
 
@@ -237,7 +278,7 @@ __device__ __forceinline__ void policy_from_regrets(const CfrParams& p, IterBloc
 // (:332-361) and the normalisation sums of the children's beliefs (:254-273).
 template <int VPT>
 __device__ __forceinline__ void iter_down(int pass, const CfrParams& p, IterBlock& B, const HandInfo<VPT>& hi,
-                                          const FV<VPT> (&prior)[2], int tid) {
+                                          const float* __restrict__ cr, int tid) {
     const IterScalars sc = p.scalars[pass];
     const bool mix = sc.do_mix != 0;
     FV<VPT> mask;
@@ -254,7 +295,7 @@ __device__ __forceinline__ void iter_down(int pass, const CfrParams& p, IterBloc
         }
         async_commit();
     };
-    if (IT_DOWN_ASYNC) fetch_children(0);
+    if (kDownAsync) fetch_children(0);
 #pragma unroll 1
     for (int ii = 0; ii < n_internal; ++ii) {
         const int j = B.ilist[ii];
@@ -262,15 +303,15 @@ __device__ __forceinline__ void iter_down(int pass, const CfrParams& p, IterBloc
         const int a = nd.to_act, k = nd.n_children, fc = nd.first_child;
         if (mix && ii + 2 < n_internal) {  // average-policy rows are streamed from HBM: pull them into L2 two nodes ahead
             const NodeRec nn = B.nodes[B.ilist[ii + 2]];
-            prefetch_rows<VPT>(B.state_row(p.policy_avg, nn.first_child), nn.n_children, tid);
+            prefetch_lines(B.state_row(p.policy_avg, nn.first_child), nn.n_children, tid);
         }
         FV<VPT> ra = mask, rba = mask;
         const int sa = B.rsrc[j * 2 + a];
         if (sa != kNoRow) {
-            ra = ldv<VPT>(B.row_reach(sa), tid);
-            if (mix) rba = ldv<VPT>(B.row_rbar(sa), tid);
+            ra = ldh<VPT>(B.row_reach(sa), tid);
+            if (mix) rba = ldh<VPT>(B.row_rbar(sa), tid);
         }
-        const FV<VPT> prior_a = pick<VPT>(prior, a);
+        const FV<VPT> prior_a = ldh<VPT>(cr + a * P2B_HPAD, tid);
         // weights of the old average and of the new policy: reach-weighted, or the plain iteration
         // weights where the hand has (numerically) no reach (:1231-1239)
         FV<VPT> ro, rn, psum;
@@ -289,25 +330,27 @@ __device__ __forceinline__ void iter_down(int pass, const CfrParams& p, IterBloc
             psum.v[i] = 0.0f;
         }
         const int bank = parity;
-        parity ^= 1;
-        if (IT_DOWN_ASYNC) async_wait();
+        if (kDouble) parity ^= 1;
+        if (kDownAsync) async_wait();
+        // with one bank, the warps that add up the previous node's rows must be done with them
+        if (!kDouble && ii > 0) __syncthreads();
         FV<VPT> Pn, Pbn;
-        if (!IT_DOWN_ASYNC) {
-            Pn = ldv<VPT>(B.row_pcur(fc), tid);
-            if (mix) Pbn = ldv<VPT>(B.state_row(p.policy_avg, fc), tid);
+        if (!kDownAsync) {
+            Pn = ldh<VPT>(B.row_pcur(fc), tid);
+            if (mix) Pbn = ldh<VPT>(B.state_row(p.policy_avg, fc), tid);
         }
 #pragma unroll 1
         for (int c = 0; c < k; ++c) {
             FV<VPT> P, Pb;
-            if (IT_DOWN_ASYNC) {
-                P = ldv<VPT>(B.land_row(0, c), tid);
-                if (mix) Pb = ldv<VPT>(B.land_row(1, c), tid);
+            if (kDownAsync) {
+                P = ldh<VPT>(B.land_row(0, c), tid);
+                if (mix) Pb = ldh<VPT>(B.land_row(1, c), tid);
             } else {
                 P = Pn;
                 Pb = Pbn;
                 if (c + 1 < k) {
-                    Pn = ldv<VPT>(B.row_pcur(fc + c + 1), tid);
-                    if (mix) Pbn = ldv<VPT>(B.state_row(p.policy_avg, fc + c + 1), tid);
+                    Pn = ldh<VPT>(B.row_pcur(fc + c + 1), tid);
+                    if (mix) Pbn = ldh<VPT>(B.state_row(p.policy_avg, fc + c + 1), tid);
                 }
             }
             const NodeRec ch = B.nodes[fc + c];
@@ -315,19 +358,19 @@ __device__ __forceinline__ void iter_down(int pass, const CfrParams& p, IterBloc
 #pragma unroll
             for (int i = 0; i < VPT; ++i) t.v[i] = __fmul_rn(ra.v[i], P.v[i]);
             if (ch.kind == kInternal) {
-                stv<VPT>(B.row_reach(ch.internal_idx), tid, t);
+                sth<VPT>(B.row_reach(ch.internal_idx), tid, t);
                 if (mix) {  // average reach under the OLD average policy
                     FV<VPT> tb;
 #pragma unroll
                     for (int i = 0; i < VPT; ++i) tb.v[i] = __fmul_rn(rba.v[i], Pb.v[i]);
-                    stv<VPT>(B.row_rbar(ch.internal_idx), tid, tb);
+                    sth<VPT>(B.row_rbar(ch.internal_idx), tid, tb);
                 }
             }
             if (ch.kind == kInternal || ch.kind == kShowdownLeaf) {
                 FV<VPT> u;
 #pragma unroll
                 for (int i = 0; i < VPT; ++i) u.v[i] = __fmul_rn(prior_a.v[i], t.v[i]);
-                stv<VPT>(B.bank_row(bank, c), tid, u);
+                sth<VPT>(B.bank_row(bank, c), tid, u);
             }
             if (mix) {
                 DivGuard g = guard_begin(dmix_ok);
@@ -343,12 +386,12 @@ __device__ __forceinline__ void iter_down(int pass, const CfrParams& p, IterBloc
                 }
 #pragma unroll
                 for (int i = 0; i < VPT; ++i) psum.v[i] = __fadd_rn(psum.v[i], q.v[i]);
-                stv<VPT>(B.stash_row(c), tid, q);
+                sth<VPT>(B.stash_row(c), tid, q);
             } else {
-                stv<VPT>(B.state_row(p.policy_avg, fc + c), tid, P);
+                sth<VPT>(B.state_row(p.policy_avg, fc + c), tid, P);
             }
         }
-        if (IT_DOWN_ASYNC && ii + 1 < n_internal) fetch_children(ii + 1);  // the landing rows are free again
+        if (kDownAsync && ii + 1 < n_internal) fetch_children(ii + 1);  // the landing rows are free again
         if (mix) {  // renormalise over the siblings (:1241-1258)
             Divisor dsum[VPT];
             bool dsum_ok = true;
@@ -359,7 +402,7 @@ __device__ __forceinline__ void iter_down(int pass, const CfrParams& p, IterBloc
             }
 #pragma unroll 1
             for (int c = 0; c < k; ++c) {
-                FV<VPT> q = ldv<VPT>(B.stash_row(c), tid), r;
+                FV<VPT> q = ldh<VPT>(B.stash_row(c), tid), r;
                 DivGuard g = guard_begin(dsum_ok);
 #pragma unroll
                 for (int i = 0; i < VPT; ++i) r.v[i] = div_g<true>(q.v[i], dsum[i].y, dsum[i].r, g);
@@ -370,7 +413,7 @@ __device__ __forceinline__ void iter_down(int pass, const CfrParams& p, IterBloc
 #pragma unroll
                 for (int i = 0; i < VPT; ++i)
                     if (psum.v[i] > 1e-5f) q.v[i] = r.v[i];
-                stv<VPT>(B.state_row(p.policy_avg, fc + c), tid, q);
+                sth<VPT>(B.state_row(p.policy_avg, fc + c), tid, q);
             }
         }
         __syncthreads();
@@ -530,32 +573,23 @@ __device__ __forceinline__ void table_units(const IterBlock& B, const float* __r
 // acting player's beliefs at the showdown child.
 template <int VPT>
 __device__ __forceinline__ void iter_up_stage(int pass, const CfrParams& p, IterBlock& B, const HandInfo<VPT>& hi,
-                                              const FV<VPT> (&prior)[2], const FV<VPT> (&root_b)[2], int ii, int set,
-                                              int tid) {
+                                              const float* __restrict__ cr, int ii, int set, int tid) {
     const int j = B.ilist[ii];
     const NodeRec nd = B.nodes[j];
     const int a = nd.to_act, o = 1 - a, k = nd.n_children, fc = nd.first_child;
-    const FV<VPT> prior_a = pick<VPT>(prior, a);
-    // every global row this half needs is requested before anything is computed: the child loops
-    // below are unrolled over the largest child count and leave at the node's own count
-    FV<VPT> P[kK];
-#if IT_STAGE_BATCH
-#pragma unroll
-    for (int c = 0; c < kK; ++c)
-        if (c < k) P[c] = ldv<VPT>(B.row_pcur(fc + c), tid);
-#endif
+    const FV<VPT> prior_a = ldh<VPT>(cr + a * P2B_HPAD, tid);
     FV<VPT> r_a, b_a, b_o;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) r_a.v[i] = hi.allowed[i] ? 1.0f : 0.0f;
     if (j == 0) {
-        b_a = pick<VPT>(root_b, a);
-        b_o = pick<VPT>(root_b, o);
+        b_a = ldh<VPT>(cr + (2 + a) * P2B_HPAD, tid);
+        b_o = ldh<VPT>(cr + (2 + o) * P2B_HPAD, tid);
     } else {
-        const FV<VPT> prior_o = pick<VPT>(prior, o);
+        const FV<VPT> prior_o = ldh<VPT>(cr + o * P2B_HPAD, tid);
         FV<VPT> r_o = r_a;
         const int sa = B.rsrc[j * 2 + a], so = B.rsrc[j * 2 + o];
-        if (sa != kNoRow) r_a = ldv<VPT>(B.row_reach(sa), tid);
-        if (so != kNoRow) r_o = ldv<VPT>(B.row_reach(so), tid);
+        if (sa != kNoRow) r_a = ldh<VPT>(B.row_reach(sa), tid);
+        if (so != kNoRow) r_o = ldh<VPT>(B.row_reach(so), tid);
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             b_a.v[i] = __fmul_rn(prior_a.v[i], r_a.v[i]);
@@ -565,34 +599,27 @@ __device__ __forceinline__ void iter_up_stage(int pass, const CfrParams& p, Iter
         norm_row<VPT>(B.sg.allowed_prob, hi, b_o, B.sig[j * 2 + o]);
     }
     if (pass + 1 < p.iterations) {  // rows the second half of this node updates, streamed from HBM
-        prefetch_rows<VPT>(B.state_row(p.regrets, fc), k, tid);
-        if (p.weight_sums) prefetch_rows<VPT>(B.state_row(p.weight_sums, fc), k, tid);
+        prefetch_lines(B.state_row(p.regrets, fc), k, tid);
+        if (p.weight_sums) prefetch_lines(B.state_row(p.weight_sums, fc), k, tid);
     }
-    stv<VPT>(B.set_row(set, 0), tid, b_a);
-    stv<VPT>(B.set_row(set, 1), tid, b_o);
+    sth<VPT>(B.set_row(set, 0), tid, b_a);
+    sth<VPT>(B.set_row(set, 1), tid, b_o);
     const int sd = B.sdc[ii];
-#if IT_STAGE_BATCH
-#pragma unroll
-    for (int c = 0; c < kK; ++c) {
-        if (c >= k) break;
-        const FV<VPT> Pc = P[c];
-#else
-    FV<VPT> Pn = ldv<VPT>(B.row_pcur(fc), tid);
+    FV<VPT> Pn = ldh<VPT>(B.row_pcur(fc), tid);
 #pragma unroll 1
     for (int c = 0; c < k; ++c) {
         const FV<VPT> Pc = Pn;
-        if (c + 1 < k) Pn = ldv<VPT>(B.row_pcur(fc + c + 1), tid);
-#endif
+        if (c + 1 < k) Pn = ldh<VPT>(B.row_pcur(fc + c + 1), tid);
         FV<VPT> m;
 #pragma unroll
         for (int i = 0; i < VPT; ++i) m.v[i] = __fmul_rn(b_a.v[i], Pc.v[i]);
-        stv<VPT>(B.set_row(set, kRowM + c), tid, m);
+        sth<VPT>(B.set_row(set, kRowM + c), tid, m);
         if (c == sd) {
             FV<VPT> bca;
 #pragma unroll
             for (int i = 0; i < VPT; ++i) bca.v[i] = __fmul_rn(prior_a.v[i], __fmul_rn(r_a.v[i], Pc.v[i]));
             norm_row<VPT>(B.sg.allowed_prob, hi, bca, B.sig[(fc + c) * 2 + a]);
-            stv<VPT>(B.set_row(set, kRowLeaf), tid, bca);
+            sth<VPT>(B.set_row(set, kRowLeaf), tid, bca);
         }
     }
 }
@@ -607,7 +634,7 @@ __device__ __forceinline__ void showdown_ev(const IterBlock& B, const HandInfo<V
     for (int i = 0; i < VPT; ++i) {
         float e = 0.0f;
         if (hi.valid[i]) {
-            const int h = VPT * tid + i;
+            const int h = hand_of<VPT>(tid, i);
             e = showdown_hand_ev(tv.rec[h], hi.c1[i], hi.c2[i], x[h], hi.allowed[i], pref, pc);
         }
         ev.v[i] = e;
@@ -621,7 +648,7 @@ __device__ __forceinline__ void showdown_ev(const IterBlock& B, const HandInfo<V
 // regrets (:1168-1185) into the current-policy rows of the next pass.
 template <int VPT>
 __device__ __forceinline__ void iter_up_hands(int pass, const CfrParams& p, IterBlock& B, const HandInfo<VPT>& hi,
-                                              const FV<VPT> (&prior)[2], int ii, int set, int tid) {
+                                              const float* __restrict__ cr, int ii, int set, int tid) {
     const int j = B.ilist[ii];
     const NodeRec nd = B.nodes[j];
     const int a = nd.to_act, o = 1 - a, k = nd.n_children, fc = nd.first_child;
@@ -630,12 +657,7 @@ __device__ __forceinline__ void iter_up_hands(int pass, const CfrParams& p, Iter
     const double* __restrict__ St = reinterpret_cast<const double*>(ts + kTsS);
     const float* __restrict__ pref = reinterpret_cast<const float*>(ts + kTsPref);
     const float* __restrict__ pc = reinterpret_cast<const float*>(ts + kTsPc);
-    // the children's policy rows travel to shared memory while the showdown formulas are evaluated
-    if (IT_HANDS_LAND) {
-        for (int c = 0; c < k; ++c) async_row<VPT>(B.land + c * P2B_HPAD, B.row_pcur(fc + c), tid);
-        async_commit();
-    }
-    const FV<VPT> b_a = ldv<VPT>(B.set_row(set, 0), tid), b_o = ldv<VPT>(B.set_row(set, 1), tid);
+    const FV<VPT> b_a = ldh<VPT>(B.set_row(set, 0), tid), b_o = ldh<VPT>(B.set_row(set, 1), tid);
     FV<VPT> wgt, denm, eva, evo, acc_a, acc_o;
     Divisor ddenm[VPT];
     bool ddenm_ok = true;
@@ -659,29 +681,25 @@ __device__ __forceinline__ void iter_up_hands(int pass, const CfrParams& p, Iter
         NodeRec chn = B.nodes[fc];
         FV<VPT> Van, Von;
         if (chn.kind == kInternal) {
-            Van = ldv<VPT>(B.row_val(chn.internal_idx, a), tid);
-            Von = ldv<VPT>(B.row_val(chn.internal_idx, o), tid);
+            Van = ldh<VPT>(B.row_val(chn.internal_idx, a), tid);
+            Von = ldh<VPT>(B.row_val(chn.internal_idx, o), tid);
         }
-        FV<VPT> Pn;
-        if (IT_HANDS_LAND) async_wait();
-        else Pn = ldv<VPT>(B.row_pcur(fc), tid);
+        FV<VPT> Pn = ldh<VPT>(B.row_pcur(fc), tid);
 #pragma unroll 1
         for (int c = 0; c < k; ++c) {
             const NodeRec ch = chn;
-            FV<VPT> P;
-            if (IT_HANDS_LAND) P = ldv<VPT>(B.land + c * P2B_HPAD, tid);
-            else P = Pn;
+            const FV<VPT> P = Pn;
             FV<VPT> V_a = Van, V_o = Von;
             if (c + 1 < k) {
                 chn = B.nodes[fc + c + 1];
-                if (!IT_HANDS_LAND) Pn = ldv<VPT>(B.row_pcur(fc + c + 1), tid);
+                Pn = ldh<VPT>(B.row_pcur(fc + c + 1), tid);
                 if (chn.kind == kInternal) {
-                    Van = ldv<VPT>(B.row_val(chn.internal_idx, a), tid);
-                    Von = ldv<VPT>(B.row_val(chn.internal_idx, o), tid);
+                    Van = ldh<VPT>(B.row_val(chn.internal_idx, a), tid);
+                    Von = ldh<VPT>(B.row_val(chn.internal_idx, o), tid);
                 }
             }
             // policy of this child as seen by each hand of the other player
-            const FV<VPT> m = ldv<VPT>(B.set_row(set, kRowM + c), tid);
+            const FV<VPT> m = ldh<VPT>(B.set_row(set, kRowM + c), tid);
             FV<VPT> pio, blk;
             {
                 DivGuard g = guard_begin(ddenm_ok);
@@ -708,17 +726,17 @@ __device__ __forceinline__ void iter_up_hands(int pass, const CfrParams& p, Iter
                 if (c != sd) {
                     // A further showdown child (a call and an all-in of the same size; rare): its tables
                     // are built here, in one more block-wide round, in place of the first one's.
-                    const FV<VPT> prior_a = pick<VPT>(prior, a);
+                    const FV<VPT> prior_a = ldh<VPT>(cr + a * P2B_HPAD, tid);
                     FV<VPT> bca;
 #pragma unroll
                     for (int i = 0; i < VPT; ++i) bca.v[i] = hi.allowed[i] ? 1.0f : 0.0f;
                     const int sa = B.rsrc[j * 2 + a];
-                    if (j != 0 && sa != kNoRow) bca = ldv<VPT>(B.row_reach(sa), tid);
+                    if (j != 0 && sa != kNoRow) bca = ldh<VPT>(B.row_reach(sa), tid);
 #pragma unroll
                     for (int i = 0; i < VPT; ++i) bca.v[i] = __fmul_rn(prior_a.v[i], __fmul_rn(bca.v[i], P.v[i]));
                     norm_row<VPT>(B.sg.allowed_prob, hi, bca, B.sig[(fc + c) * 2 + a]);
                     __syncthreads();  // every thread is done with the leaf tables of the first showdown child
-                    stv<VPT>(B.set_row(set, kRowLeaf), tid, bca);
+                    sth<VPT>(B.set_row(set, kRowLeaf), tid, bca);
                     if (tid == 0) B.misc[6] = 0;
                     __syncthreads();
                     table_units(B, B.set_row(set, 0), B.ts + set * kTsBytes, 0, true, B.misc + 6);
@@ -752,12 +770,12 @@ __device__ __forceinline__ void iter_up_hands(int pass, const CfrParams& p, Iter
                 acc_a.v[i] = __fadd_rn(acc_a.v[i], __fmul_rn(V_a.v[i], P.v[i]));
                 acc_o.v[i] = __fadd_rn(acc_o.v[i], __fmul_rn(V_o.v[i], pio.v[i]));
             }
-            stv<VPT>(B.set_row(set, kRowM + c), tid, V_a);  // kept for the regrets below; the marginal row is spent
+            sth<VPT>(B.set_row(set, kRowM + c), tid, V_a);  // kept for the regrets below; the marginal row is spent
         }
     }
     if (j != 0) {
-        stv<VPT>(B.row_val(ii, a), tid, acc_a);
-        stv<VPT>(B.row_val(ii, o), tid, acc_o);
+        sth<VPT>(B.row_val(ii, a), tid, acc_a);
+        sth<VPT>(B.row_val(ii, o), tid, acc_o);
     }
     if (pass + 1 >= p.iterations) return;  // the last iteration leaves the regrets as they are
     // ---- regrets of this pass folded into the discounted update of the next, then its policy ----
@@ -769,32 +787,16 @@ __device__ __forceinline__ void iter_up_hands(int pass, const CfrParams& p, Iter
 #pragma unroll
     for (int i = 0; i < VPT; ++i) psum.v[i] = 0.0f;
     {
-        // all state rows of the node are requested at once; the loop is unrolled over the largest
-        // child count and leaves at the node's own
-#if IT_RW_BATCH
-        FV<VPT> Rs[kK], Ws[kK];
-#pragma unroll
-        for (int c = 0; c < kK; ++c)
-            if (c < k) {
-                Rs[c] = ldv<VPT>(B.state_row(p.regrets, fc + c), tid);
-                if (tracked) Ws[c] = ldv<VPT>(B.state_row(p.weight_sums, fc + c), tid);
-            }
-#pragma unroll
-        for (int c = 0; c < kK; ++c) {
-            if (c >= k) break;
-            FV<VPT> R = Rs[c], W = Ws[c];
-#else
-        FV<VPT> Rn = ldv<VPT>(B.state_row(p.regrets, fc), tid), Wn;
-        if (tracked) Wn = ldv<VPT>(B.state_row(p.weight_sums, fc), tid);
+        FV<VPT> Rn = ldh<VPT>(B.state_row(p.regrets, fc), tid), Wn;
+        if (tracked) Wn = ldh<VPT>(B.state_row(p.weight_sums, fc), tid);
 #pragma unroll 1
         for (int c = 0; c < k; ++c) {
             FV<VPT> R = Rn, W = Wn;
             if (c + 1 < k) {
-                Rn = ldv<VPT>(B.state_row(p.regrets, fc + c + 1), tid);
-                if (tracked) Wn = ldv<VPT>(B.state_row(p.weight_sums, fc + c + 1), tid);
+                Rn = ldh<VPT>(B.state_row(p.regrets, fc + c + 1), tid);
+                if (tracked) Wn = ldh<VPT>(B.state_row(p.weight_sums, fc + c + 1), tid);
             }
-#endif
-            const FV<VPT> Va = ldv<VPT>(B.set_row(set, kRowM + c), tid);
+            const FV<VPT> Va = ldh<VPT>(B.set_row(set, kRowM + c), tid);
             FV<VPT> rn, wn, rq, wq, dy;
             DivGuard g = guard_begin(d_ok);
 #pragma unroll
@@ -828,9 +830,9 @@ __device__ __forceinline__ void iter_up_hands(int pass, const CfrParams& p, Iter
                 posn.v[i] = fmaxf(rr, 0.0f);
                 psum.v[i] = __fadd_rn(psum.v[i], posn.v[i]);
             }
-            stv<VPT>(B.state_row(p.regrets, fc + c), tid, R);
-            if (tracked) stv<VPT>(B.state_row(p.weight_sums, fc + c), tid, W);
-            stv<VPT>(B.set_row(set, kRowM + c), tid, posn);
+            sth<VPT>(B.state_row(p.regrets, fc + c), tid, R);
+            if (tracked) sth<VPT>(B.state_row(p.weight_sums, fc + c), tid, W);
+            sth<VPT>(B.set_row(set, kRowM + c), tid, posn);
         }
     }
     {
@@ -844,7 +846,7 @@ __device__ __forceinline__ void iter_up_hands(int pass, const CfrParams& p, Iter
         }
 #pragma unroll 1
         for (int c = 0; c < k; ++c) {
-            const FV<VPT> posn = ldv<VPT>(B.set_row(set, kRowM + c), tid);
+            const FV<VPT> posn = ldh<VPT>(B.set_row(set, kRowM + c), tid);
             DivGuard g = guard_begin(ds_ok);
             FV<VPT> P;
 #pragma unroll
@@ -855,14 +857,14 @@ __device__ __forceinline__ void iter_up_hands(int pass, const CfrParams& p, Iter
             }
 #pragma unroll
             for (int i = 0; i < VPT; ++i) P.v[i] = psum.v[i] > 1e-8f ? P.v[i] : invk;
-            stv<VPT>(B.row_pcur(fc + c), tid, P);
+            sth<VPT>(B.row_pcur(fc + c), tid, P);
         }
     }
 }
 
 template <int VPT>
-__global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_iter_kernel(const CfrParams p) {
-    constexpr int NT = CfrThreads<VPT>::value;
+__global__ void __launch_bounds__(kNT, kCtas) cfr_iter_kernel(const CfrParams p) {
+    constexpr int NT = kNT;
     extern __shared__ __align__(16) unsigned char smem[];
     IterBlock B;
     B.tab = smem + kOffTab;
@@ -875,15 +877,15 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_iter_kernel(con
     B.sdc = smem + kOffSdc;
     B.misc = reinterpret_cast<int*>(smem + kOffMisc);
     B.fsum = reinterpret_cast<float*>(smem + kOffMisc + 16);
-    B.land = reinterpret_cast<float*>(smem + kOffLand);
     B.max_internal = p.max_internal;
-    B.scr = p.scratch + (long long)blockIdx.x * p.scratch_stride;
+    B.scr = p.scratch + (long long)(blockIdx.x / kCtas) * p.scratch_stride +
+            (long long)(blockIdx.x % kCtas) * (p.scratch_stride / kCtas);
     const int tid = threadIdx.x;
 
     HandInfo<VPT> hi;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-        const int h = VPT * tid + i;
+        const int h = hand_of<VPT>(tid, i);
         hi.valid[i] = h < P2B_NUM_HANDS;
         const int hc = h < P2B_NUM_HANDS ? h : P2B_NUM_HANDS - 1;
         hi.c1[i] = p.combos->c1[hc];
@@ -908,13 +910,10 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_iter_kernel(con
 #pragma unroll
         for (int i = 0; i < VPT; ++i)
             hi.allowed[i] = hi.valid[i] && (((B.sg.board_mask >> hi.c1[i]) | (B.sg.board_mask >> hi.c2[i])) & 1ull) == 0;
-        // root beliefs as the start pass left them
-        FV<VPT> prior[2], root_b[2];
+        // The root rows stay in the hand-over area of the subgame: rows 0, 1 = the root beliefs the node
+        // beliefs of a pass derive from, rows 2, 3 = the root's own rows (renormalised once per pass, like
+        // every other row upstream), as the start pass left them.
         float* cr = p.carry_roots + (long long)s * 4 * P2B_HPAD;
-        root_b[0] = ldv<VPT>(cr + 2 * P2B_HPAD, tid);
-        root_b[1] = ldv<VPT>(cr + 3 * P2B_HPAD, tid);
-        prior[0] = root_b[0];
-        prior[1] = root_b[1];
         __syncthreads();
         // per node: list of the internal nodes, where each player's reach is stored, the showdown child
         for (int i = tid; i < B.sg.n_nodes; i += NT) {
@@ -945,64 +944,81 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_iter_kernel(con
         for (int ii = 0; ii < n_internal; ++ii) policy_from_regrets<VPT>(p, B, B.ilist[ii], tid);
 
         for (int pass = 0; pass < p.iterations; ++pass) {
-            prior[0] = root_b[0];
-            prior[1] = root_b[1];
-            normalize_pair<VPT>(B, hi, root_b);
+            {
+                FV<VPT> root_b[2];
+                root_b[0] = ldh<VPT>(cr + 2 * P2B_HPAD, tid);
+                root_b[1] = ldh<VPT>(cr + 3 * P2B_HPAD, tid);
+                sth<VPT>(cr, tid, root_b[0]);
+                sth<VPT>(cr + P2B_HPAD, tid, root_b[1]);
+                normalize_pair<VPT>(B, hi, root_b);
+                sth<VPT>(cr + 2 * P2B_HPAD, tid, root_b[0]);
+                sth<VPT>(cr + 3 * P2B_HPAD, tid, root_b[1]);
+            }
             // a child's row of the player who did not act is the root's row; so is its sum
             if (tid < 2) B.sig[tid] = B.fsum[tid];
             __syncthreads();
-            iter_down<VPT>(pass, p, B, hi, prior, tid);
+            iter_down<VPT>(pass, p, B, hi, cr, tid);
             if (tid == 0) B.misc[2] = B.misc[3] = 0;
             __syncthreads();
-            // bottom-up: the cross-hand units of a node run while the hands of the node above it
-            // (in sweep order: the one before) are worked on
-            int set = 0;
-            iter_up_stage<VPT>(pass, p, B, hi, prior, root_b, n_internal - 1, set, tid);
-            __syncthreads();
-            {
-                const NodeRec nd = B.nodes[B.ilist[n_internal - 1]];
-                table_units(B, B.set_row(set, 0), B.ts + set * kTsBytes, 2 + nd.n_children,
-                            B.sdc[n_internal - 1] != kNoRow, B.misc + 2 + set);
-            }
-            for (int ii = n_internal - 1; ii >= 0; --ii) {
-                if (ii > 0) {
-                    iter_up_stage<VPT>(pass, p, B, hi, prior, root_b, ii - 1, set ^ 1, tid);
-                    if (tid == 0) B.misc[2 + (set ^ 1)] = 0;
+            if (kDouble) {
+                // bottom-up: the cross-hand units of a node run while the hands of the node above it
+                // (in sweep order: the one before) are worked on
+                int set = 0;
+                iter_up_stage<VPT>(pass, p, B, hi, cr, n_internal - 1, set, tid);
+                __syncthreads();
+                {
+                    const NodeRec nd = B.nodes[B.ilist[n_internal - 1]];
+                    table_units(B, B.set_row(set, 0), B.ts + set * kTsBytes, 2 + nd.n_children,
+                                B.sdc[n_internal - 1] != kNoRow, B.misc + 2 + set);
                 }
-                __syncthreads();  // staged rows of node ii-1 and the tables of node ii are complete
-                if (ii > 0) {
-                    const NodeRec nd = B.nodes[B.ilist[ii - 1]];
-                    table_units(B, B.set_row(set ^ 1, 0), B.ts + (set ^ 1) * kTsBytes, 2 + nd.n_children,
-                                B.sdc[ii - 1] != kNoRow, B.misc + 2 + (set ^ 1));
+                for (int ii = n_internal - 1; ii >= 0; --ii) {
+                    if (ii > 0) {
+                        iter_up_stage<VPT>(pass, p, B, hi, cr, ii - 1, set ^ 1, tid);
+                        if (tid == 0) B.misc[2 + (set ^ 1)] = 0;
+                    }
+                    __syncthreads();  // staged rows of node ii-1 and the tables of node ii are complete
+                    if (ii > 0) {
+                        const NodeRec nd = B.nodes[B.ilist[ii - 1]];
+                        table_units(B, B.set_row(set ^ 1, 0), B.ts + (set ^ 1) * kTsBytes, 2 + nd.n_children,
+                                    B.sdc[ii - 1] != kNoRow, B.misc + 2 + (set ^ 1));
+                    }
+                    iter_up_hands<VPT>(pass, p, B, hi, cr, ii, set, tid);
+                    set ^= 1;
                 }
-                iter_up_hands<VPT>(pass, p, B, hi, prior, ii, set, tid);
-                set ^= 1;
+            } else {
+                // bottom-up with one set of rows and tables: stage, units, hands, two barriers per node;
+                // the other block of the SM fills the gaps
+                for (int ii = n_internal - 1; ii >= 0; --ii) {
+                    iter_up_stage<VPT>(pass, p, B, hi, cr, ii, 0, tid);
+                    if (tid == 0) B.misc[2] = 0;
+                    __syncthreads();  // rows staged; every thread is done with the tables of the node before
+                    const NodeRec nd = B.nodes[B.ilist[ii]];
+                    table_units(B, B.set_row(0, 0), B.ts, 2 + nd.n_children, B.sdc[ii] != kNoRow, B.misc + 2);
+                    __syncthreads();
+                    iter_up_hands<VPT>(pass, p, B, hi, cr, ii, 0, tid);
+                }
             }
             __syncthreads();
         }
-        // hand the root rows and their sums to the final pass
-        stv<VPT>(cr, tid, prior[0]);
-        stv<VPT>(cr + P2B_HPAD, tid, prior[1]);
-        stv<VPT>(cr + 2 * P2B_HPAD, tid, root_b[0]);
-        stv<VPT>(cr + 3 * P2B_HPAD, tid, root_b[1]);
+        // the root rows are in place for the final pass; hand over their sums
         if (tid < 2) p.carry_sums[(long long)B.sg.node_begin * 2 + tid] = B.sig[tid];
     }
 }
 
 }  // namespace
 
-// floats of work rows one block of the iteration kernel needs
+// floats of work rows the blocks of the iteration kernel on one SM need
 long long cfr_iter_scratch_floats(int max_internal, int max_children) {
     long long nodes = (long long)max_internal * max_children + 1;
     if (nodes > kCfrMaxNodes) nodes = kCfrMaxNodes;
-    return ((long long)max_internal * 4 + nodes) * P2B_HPAD;
+    return kCtas * ((long long)max_internal * 4 + nodes) * P2B_HPAD;
 }
 
 int launch_cfr_iter(const CfrParams& p, int num_blocks, cudaStream_t stream) {
-    int rc = check_cuda(cudaFuncSetAttribute(cfr_iter_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kIterSmem),
+    int rc = check_cuda(cudaFuncSetAttribute(cfr_iter_kernel<kVpt>, cudaFuncAttributeMaxDynamicSharedMemorySize, kIterSmem),
                         "cfr_iter_kernel shared-memory attribute");
     if (rc) return rc;
-    cfr_iter_kernel<2><<<num_blocks, CfrThreads<2>::value, kIterSmem, stream>>>(p);
+    cfr_iter_kernel<kVpt><<<num_blocks * kCtas, kNT, kIterSmem, stream>>>(p);
     return check_cuda(cudaGetLastError(), "cfr_iter_kernel");
 }
 
