@@ -605,11 +605,9 @@ __device__ __forceinline__ void iter_up_stage(int pass, const CfrParams& p, Iter
     sth<VPT>(B.set_row(set, 0), tid, b_a);
     sth<VPT>(B.set_row(set, 1), tid, b_o);
     const int sd = B.sdc[ii];
-    FV<VPT> Pn = ldh<VPT>(B.row_pcur(fc), tid);
 #pragma unroll 1
     for (int c = 0; c < k; ++c) {
-        const FV<VPT> Pc = Pn;
-        if (c + 1 < k) Pn = ldh<VPT>(B.row_pcur(fc + c + 1), tid);
+        const FV<VPT> Pc = ldh<VPT>(B.row_pcur(fc + c), tid);
         FV<VPT> m;
 #pragma unroll
         for (int i = 0; i < VPT; ++i) m.v[i] = __fmul_rn(b_a.v[i], Pc.v[i]);
@@ -658,7 +656,7 @@ __device__ __forceinline__ void iter_up_hands(int pass, const CfrParams& p, Iter
     const float* __restrict__ pref = reinterpret_cast<const float*>(ts + kTsPref);
     const float* __restrict__ pc = reinterpret_cast<const float*>(ts + kTsPc);
     const FV<VPT> b_a = ldh<VPT>(B.set_row(set, 0), tid), b_o = ldh<VPT>(B.set_row(set, 1), tid);
-    FV<VPT> wgt, denm, eva, evo, acc_a, acc_o;
+    FV<VPT> wgt, denm, acc_a, acc_o;
     Divisor ddenm[VPT];
     bool ddenm_ok = true;
 #pragma unroll
@@ -667,36 +665,20 @@ __device__ __forceinline__ void iter_up_hands(int pass, const CfrParams& p, Iter
         denm.v[i] = unblocked(cs, St[0], hi.c1[i], hi.c2[i], b_a.v[i]);
         ddenm[i] = make_divisor(denm.v[i]);
         ddenm_ok = ddenm_ok && ddenm[i].ok;
-        eva.v[i] = evo.v[i] = 0.0f;
         acc_a.v[i] = acc_o.v[i] = 0.0f;
     }
+    sth<VPT>(B.set_row(set, 0), tid, wgt);  // needed again for the regrets; the beliefs row is spent
     const int sd = B.sdc[ii];
-    if (sd != kNoRow) {
-        // the acting player's hands against the other player's beliefs, and the reverse at the leaf
-        showdown_ev<VPT>(B, hi, tid, B.set_row(set, 1), pref, pc, eva);
-        showdown_ev<VPT>(B, hi, tid, B.set_row(set, kRowLeaf), pref + P2B_HPAD, pc + 52 * 52, evo);
-    }
     // ---- children: values and backup ----
     {
-        NodeRec chn = B.nodes[fc];
-        FV<VPT> Van, Von;
-        if (chn.kind == kInternal) {
-            Van = ldh<VPT>(B.row_val(chn.internal_idx, a), tid);
-            Von = ldh<VPT>(B.row_val(chn.internal_idx, o), tid);
-        }
-        FV<VPT> Pn = ldh<VPT>(B.row_pcur(fc), tid);
 #pragma unroll 1
         for (int c = 0; c < k; ++c) {
-            const NodeRec ch = chn;
-            const FV<VPT> P = Pn;
-            FV<VPT> V_a = Van, V_o = Von;
-            if (c + 1 < k) {
-                chn = B.nodes[fc + c + 1];
-                Pn = ldh<VPT>(B.row_pcur(fc + c + 1), tid);
-                if (chn.kind == kInternal) {
-                    Van = ldh<VPT>(B.row_val(chn.internal_idx, a), tid);
-                    Von = ldh<VPT>(B.row_val(chn.internal_idx, o), tid);
-                }
+            const NodeRec ch = B.nodes[fc + c];
+            const FV<VPT> P = ldh<VPT>(B.row_pcur(fc + c), tid);
+            FV<VPT> V_a, V_o;
+            if (ch.kind == kInternal) {
+                V_a = ldh<VPT>(B.row_val(ch.internal_idx, a), tid);
+                V_o = ldh<VPT>(B.row_val(ch.internal_idx, o), tid);
             }
             // policy of this child as seen by each hand of the other player
             const FV<VPT> m = ldh<VPT>(B.set_row(set, kRowM + c), tid);
@@ -723,6 +705,10 @@ __device__ __forceinline__ void iter_up_hands(int pass, const CfrParams& p, Iter
                     V_o.v[i] = -va;
                 }
             } else if (ch.kind == kShowdownLeaf) {
+                // the acting player's hands against the other player's beliefs, and the reverse at the leaf
+                FV<VPT> eva, evo;
+                showdown_ev<VPT>(B, hi, tid, B.set_row(set, 1), pref, pc, eva);
+                if (c == sd) showdown_ev<VPT>(B, hi, tid, B.set_row(set, kRowLeaf), pref + P2B_HPAD, pc + 52 * 52, evo);
                 if (c != sd) {
                     // A further showdown child (a call and an all-in of the same size; rare): its tables
                     // are built here, in one more block-wide round, in place of the first one's.
@@ -783,19 +769,15 @@ __device__ __forceinline__ void iter_up_hands(int pass, const CfrParams& p, Iter
     const Divisor d_pos = make_divisor(sc.den_pos), d_neg = make_divisor(sc.den_neg);
     const bool d_ok = d_pos.ok && d_neg.ok;
     const bool tracked = p.weight_sums != nullptr;
+    wgt = ldh<VPT>(B.set_row(set, 0), tid);
     FV<VPT> psum;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) psum.v[i] = 0.0f;
     {
-        FV<VPT> Rn = ldh<VPT>(B.state_row(p.regrets, fc), tid), Wn;
-        if (tracked) Wn = ldh<VPT>(B.state_row(p.weight_sums, fc), tid);
 #pragma unroll 1
         for (int c = 0; c < k; ++c) {
-            FV<VPT> R = Rn, W = Wn;
-            if (c + 1 < k) {
-                Rn = ldh<VPT>(B.state_row(p.regrets, fc + c + 1), tid);
-                if (tracked) Wn = ldh<VPT>(B.state_row(p.weight_sums, fc + c + 1), tid);
-            }
+            FV<VPT> R = ldh<VPT>(B.state_row(p.regrets, fc + c), tid), W;
+            if (tracked) W = ldh<VPT>(B.state_row(p.weight_sums, fc + c), tid);
             const FV<VPT> Va = ldh<VPT>(B.set_row(set, kRowM + c), tid);
             FV<VPT> rn, wn, rq, wq, dy;
             DivGuard g = guard_begin(d_ok);
