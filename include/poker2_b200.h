@@ -85,6 +85,12 @@ int p2b_showdown_values(const unsigned char* tables, const int32_t* table_of_row
  *             results, bit for bit; the extra floats carry the root rows between the launches
  *  scalars    [iterations] 32-byte records {float t^alpha, t^alpha+1, t^beta, t^beta+1,
  *             mix_old, mix_new, fl(mix_old+mix_new); int32 do_mix}
+ *  flags      bit 0: CFR+ (cumulative regrets clamped at zero after every update, cfr_evaluator.py:1366-1368);
+ *             bit 1: the value outputs of the final pass (root_values, values_avg) are shifted to zero
+ *             sum, per node minus the mean over the players of sum_h values * beliefs_avg, except at
+ *             terminal nodes -- what upstream does when model.enforce_zero_sum is set
+ *             (_maybe_enforce_zero_sum :957-980 at the end of update_average_values_final :1289-1292);
+ *             the best responses then start from the shifted leaf values, as upstream
  *  init_depth depth of the deepest tree of the batch (the upstream start pass re-normalises
  *             every belief row once per level of the batch-wide tree)
  *  work_counter four int32, zeroed by the call: [0] the queue the thread blocks take subgames
@@ -107,7 +113,7 @@ int p2b_cfr_solve(const void* subgames, const void* nodes, int32_t num_subgames,
                   int32_t max_internal, const unsigned char* tables, const float* root_beliefs,
                   float* regrets, float* weight_sums, float* policy_avg, float* policy,
                   float* root_values, float* values_avg, float* beliefs_avg, float* exploitability,
-                  float* br_values, float* scratch, int64_t scratch_floats, const void* scalars, int32_t iterations, int32_t cfr_plus,
+                  float* br_values, float* scratch, int64_t scratch_floats, const void* scalars, int32_t iterations, int32_t flags,
                   int32_t init_depth, int32_t* work_counter, int32_t num_blocks, const int32_t* sample_pass,
                   float* policy_sample, float* beliefs_last, void* stream);
 int64_t p2b_cfr_scratch_floats(int32_t max_internal, int32_t num_blocks);
@@ -138,7 +144,7 @@ int p2b_cfr_step(const void* subgames, const void* nodes, int32_t num_subgames, 
                  float* regrets, float* weight_sums, float* policy_avg, float* policy,
                  float* root_values, float* values_avg, float* beliefs_avg, float* exploitability,
                  float* br_values, float* scratch, int64_t scratch_floats, const void* scalars,
-                 int32_t iterations, int32_t cfr_plus, int32_t init_depth, int32_t* work_counter,
+                 int32_t iterations, int32_t flags, int32_t init_depth, int32_t* work_counter,
                  int32_t num_blocks, int32_t pass_begin, int32_t pass_end, int32_t phases,
                  float* carry_sums, float* carry_roots, const int32_t* leaf_begin, int32_t leaf_slots,
                  float* leaf_beliefs, const float* leaf_values, const int32_t* sample_pass, float* policy_sample,
@@ -219,7 +225,7 @@ int p2b_cfr_solve_noalloc(const void* subgames, const void* nodes, int32_t num_s
                           const float* root_beliefs, float* regrets, float* weight_sums,
                           float* policy_avg, float* policy, float* root_values, float* values_avg,
                           float* beliefs_avg, float* exploitability, float* br_values, const void* scalars,
-                          int32_t iterations, int32_t cfr_plus, int32_t init_depth, void* stream);
+                          int32_t iterations, int32_t flags, int32_t init_depth, void* stream);
 int64_t p2b_cfr_noalloc_scratch_floats(void);
 int p2b_cfr_noalloc_status(int32_t* status, void* stream);
 

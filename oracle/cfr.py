@@ -34,7 +34,9 @@ class SubgameOracle:
                  alpha: float = 1.5, beta: float = 0.0, gamma: float = 2.0,
                  dcfr_delay: int = 0, cfr_type: str = "discounted", cfr_plus: bool = False, leaf_fn=None,
                  start_policy: torch.Tensor | None = None, warm_start_iterations: int = 0,
-                 warm_start_multiplier: float = 1.0):
+                 warm_start_multiplier: float = 1.0, alpha_final: float | None = None,
+                 beta_final: float | None = None, gamma_final: float | None = None,
+                 enforce_zero_sum: bool = False):
         t = {k: (torch.from_numpy(np.ascontiguousarray(v)) if isinstance(v, np.ndarray) else v)
              for k, v in tree.items()}
         self.offs = [int(x) for x in tree["depth_offsets"]]
@@ -53,6 +55,11 @@ class SubgameOracle:
         self.scale = t["scale"].float()
         self.iterations = iterations
         self.alpha, self.beta, self.gamma = alpha, beta, gamma
+        # exponent schedules (`apply_schedules`, cfr_evaluator.py:1294-1329) and the zero-sum shift of
+        # the final values (`_maybe_enforce_zero_sum` :957-980, applied at :1289-1292)
+        self.alpha0, self.beta0, self.gamma0 = alpha, beta, gamma
+        self.alpha_final, self.beta_final, self.gamma_final = alpha_final, beta_final, gamma_final
+        self.enforce_zero_sum = enforce_zero_sum
         self.dcfr_delay = dcfr_delay
         self.cfr_type = cfr_type
         self.cfr_plus = cfr_plus
@@ -279,7 +286,15 @@ class SubgameOracle:
         self._reach_weights(self.reach_avg, self.policy_avg)
         self._propagate_beliefs(self.beliefs_avg, self.reach_avg)
 
+    def apply_schedules(self, t):
+        total = max(1, self.iterations - self.warm_start_iterations)
+        progress = min(1.0, max(0.0, max(0, t - self.warm_start_iterations) / float(total)))
+        for name in ("alpha", "beta", "gamma"):
+            first, last = getattr(self, name + "0"), getattr(self, name + "_final")
+            setattr(self, name, first if last is None else first + (last - first) * progress)
+
     def iteration(self, t):
+        self.apply_schedules(t)
         inst = self.instantaneous_regrets()
         if self.cfr_type == "linear":
             inst.masked_fill_(self.prev_actor[:, None] == t % 2, 0.0)
@@ -300,9 +315,13 @@ class SubgameOracle:
         self.expected_values()
 
     def finalize(self):
-        """update_average_values_final (cfr_evaluator.py:1276-1292), no zero-sum shift."""
+        """update_average_values_final (cfr_evaluator.py:1276-1292)."""
         self.set_leaf_values(beliefs=self.beliefs_avg)
         self.expected_values(self.policy_avg, self.beliefs_avg, self.values, self.values_avg)
+        if self.enforce_zero_sum:
+            sums = (self.values_avg * self.beliefs_avg).sum(dim=2, keepdim=True).mean(dim=1, keepdim=True)
+            sums.masked_fill_(self.done[:, None, None], 0.0)
+            self.values_avg = self.values_avg - sums
 
     def warm_start(self):
         """Type `model` (cfr_evaluator.py:913-926): cumulative regrets = start policy x weight,

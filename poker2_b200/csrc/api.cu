@@ -84,7 +84,7 @@ int p2b_cfr_solve(const void* subgames, const void* nodes, int32_t num_subgames,
                   int32_t max_internal, const unsigned char* tables, const float* root_beliefs, float* regrets,
                   float* weight_sums, float* policy_avg, float* policy, float* root_values, float* values_avg,
                   float* beliefs_avg, float* exploitability, float* br_values, float* scratch, int64_t scratch_floats,
-                  const void* scalars, int32_t iterations, int32_t cfr_plus, int32_t init_depth, int32_t* work_counter,
+                  const void* scalars, int32_t iterations, int32_t flags, int32_t init_depth, int32_t* work_counter,
                   int32_t num_blocks, const int32_t* sample_pass, float* policy_sample, float* beliefs_last,
                   void* stream) {
     P2B_REQUIRE(num_subgames >= 0 && iterations >= 0 && rows >= 0, "negative count");
@@ -97,6 +97,7 @@ int p2b_cfr_solve(const void* subgames, const void* nodes, int32_t num_subgames,
     P2B_REQUIRE(iterations == 0 || scalars, "null scalars");
     P2B_REQUIRE(max_internal >= 1, "max_internal must be positive");
     P2B_REQUIRE(!exploitability || values_avg, "exploitability needs values_avg");
+    P2B_REQUIRE(flags >= 0 && flags <= 3, "flags: bit 0 = CFR+ clamp, bit 1 = zero-sum value outputs");
     if (num_blocks <= 0) num_blocks = cfr_default_blocks();
     if (num_blocks > num_subgames) num_blocks = num_subgames;
     P2B_REQUIRE(scratch_floats >= cfr_scratch_floats(max_internal) * num_blocks, "scratch too small");
@@ -127,7 +128,8 @@ int p2b_cfr_solve(const void* subgames, const void* nodes, int32_t num_subgames,
     p.max_internal = max_internal;
     p.scalars = static_cast<const IterScalars*>(scalars);
     p.iterations = iterations;
-    p.cfr_plus = cfr_plus;
+    p.cfr_plus = flags & 1;
+    p.enforce_zero_sum = (flags >> 1) & 1;
     p.init_depth = init_depth;
     p.work_counter = work_counter;
     p.sample_pass = sample_pass;
@@ -146,7 +148,7 @@ int p2b_cfr_step(const void* subgames, const void* nodes, int32_t num_subgames, 
                  int32_t max_internal, const unsigned char* tables, const float* root_beliefs, float* regrets,
                  float* weight_sums, float* policy_avg, float* policy, float* root_values, float* values_avg,
                  float* beliefs_avg, float* exploitability, float* br_values, float* scratch, int64_t scratch_floats,
-                 const void* scalars, int32_t iterations, int32_t cfr_plus, int32_t init_depth, int32_t* work_counter,
+                 const void* scalars, int32_t iterations, int32_t flags, int32_t init_depth, int32_t* work_counter,
                  int32_t num_blocks, int32_t pass_begin, int32_t pass_end, int32_t phases, float* carry_sums,
                  float* carry_roots, const int32_t* leaf_begin, int32_t leaf_slots, float* leaf_beliefs,
                  const float* leaf_values, const int32_t* sample_pass, float* policy_sample, float* beliefs_last, const float* start_policy,
@@ -162,6 +164,7 @@ int p2b_cfr_step(const void* subgames, const void* nodes, int32_t num_subgames, 
                 "null pointer");
     P2B_REQUIRE(max_internal >= 1, "max_internal must be positive");
     P2B_REQUIRE(!exploitability || values_avg, "exploitability needs values_avg");
+    P2B_REQUIRE(flags >= 0 && flags <= 3, "flags: bit 0 = CFR+ clamp, bit 1 = zero-sum value outputs");
     P2B_REQUIRE(pass_begin >= -1 && pass_begin <= pass_end && pass_end <= iterations, "pass range outside [-1, iterations]");
     P2B_REQUIRE(phases >= 1 && phases <= 3, "phases must be 1 (top-down), 2 (bottom-up) or 3 (both)");
     P2B_REQUIRE(phases == 3 || pass_begin == pass_end, "a single sweep direction covers exactly one pass");
@@ -199,7 +202,8 @@ int p2b_cfr_step(const void* subgames, const void* nodes, int32_t num_subgames, 
     p.max_internal = max_internal;
     p.scalars = static_cast<const IterScalars*>(scalars);
     p.iterations = iterations;
-    p.cfr_plus = cfr_plus;
+    p.cfr_plus = flags & 1;
+    p.enforce_zero_sum = (flags >> 1) & 1;
     p.init_depth = init_depth;
     p.work_counter = work_counter;
     p.stepped = 1;
@@ -243,12 +247,13 @@ int p2b_cfr_solve_noalloc(const void* subgames, const void* nodes, int32_t num_s
                           int32_t max_children, int32_t max_internal, const unsigned char* tables, const float* root_beliefs, float* regrets,
                           float* weight_sums, float* policy_avg, float* policy, float* root_values, float* values_avg,
                           float* beliefs_avg, float* exploitability, float* br_values, const void* scalars,
-                          int32_t iterations, int32_t cfr_plus, int32_t init_depth, void* stream) {
+                          int32_t iterations, int32_t flags, int32_t init_depth, void* stream) {
     P2B_REQUIRE(num_subgames >= 0 && iterations >= 0 && rows >= 0, "negative count");
     if (num_subgames == 0) return P2B_OK;
     P2B_REQUIRE(subgames && nodes && root_beliefs && regrets && policy_avg && root_values && scalars, "null pointer");
     P2B_REQUIRE(max_internal >= 1, "max_internal must be positive");
     P2B_REQUIRE(!exploitability || values_avg, "exploitability needs values_avg");
+    P2B_REQUIRE(flags >= 0 && flags <= 3, "flags: bit 0 = CFR+ clamp, bit 1 = zero-sum value outputs");
     const uintptr_t align = reinterpret_cast<uintptr_t>(subgames) | reinterpret_cast<uintptr_t>(nodes) |
                             reinterpret_cast<uintptr_t>(tables) | reinterpret_cast<uintptr_t>(root_beliefs) |
                             reinterpret_cast<uintptr_t>(regrets) | reinterpret_cast<uintptr_t>(weight_sums) |
@@ -274,7 +279,8 @@ int p2b_cfr_solve_noalloc(const void* subgames, const void* nodes, int32_t num_s
     p.max_internal = max_internal;
     p.scalars = static_cast<const IterScalars*>(scalars);
     p.iterations = iterations;
-    p.cfr_plus = cfr_plus;
+    p.cfr_plus = flags & 1;
+    p.enforce_zero_sum = (flags >> 1) & 1;
     p.init_depth = init_depth;
     p.rows = rows;
     return launch_cfr_solve_static(p, max_children, (cudaStream_t)stream);

@@ -375,6 +375,41 @@ __device__ __forceinline__ void dispatch_children(int k, Body&& body) {
     }
 }
 
+// sum over hands of x*y in the reference row-reduction order; stage rows 0/1 must be free.
+template <int VPT>
+__device__ __forceinline__ void dot2_reference_order(Block& B, const FV<VPT>& x0, const FV<VPT>& x1, float (&out)[2]) {
+    const int tid = threadIdx.x;
+    __syncthreads();
+    stv<VPT>(B.stage_row(0), tid, x0);
+    stv<VPT>(B.stage_row(1), tid, x1);
+    __syncthreads();
+    const int warp = tid >> 5;
+    if (warp < 2) {
+        const float sum = row_sum_reference_order(B.stage_row(warp));
+        if ((tid & 31) == 0) B.fsum[warp] = sum;
+    }
+    __syncthreads();
+    out[0] = B.fsum[0];
+    out[1] = B.fsum[1];
+}
+
+// Zero-sum shift of the value outputs of one node (cfr_evaluator.py:957-980): the mean over the two
+// players of sum_h values * beliefs, the sums in the reference row-reduction order.  Block-wide
+// (barriers inside); stage rows 0/1 must be free.
+template <int VPT>
+__device__ __forceinline__ float zero_sum_shift(Block& B, const FV<VPT>& v0, const FV<VPT>& b0, const FV<VPT>& v1,
+                                                const FV<VPT>& b1) {
+    FV<VPT> x0, x1;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        x0.v[i] = __fmul_rn(v0.v[i], b0.v[i]);
+        x1.v[i] = __fmul_rn(v1.v[i], b1.v[i]);
+    }
+    float sums[2];
+    dot2_reference_order<VPT>(B, x0, x1, sums);
+    return __fmul_rn(__fadd_rn(sums[0], sums[1]), 0.5f);
+}
+
 // ---- top-down sweep of one pass -------------------------------------------------------
 template <int VPT, int MAXC, int FIXED_MODE, bool PLAIN>
 __device__ __forceinline__ void sweep_down(int mode_rt, int pass, const CfrParams& p_in, Block& B, const HandInfo<VPT>& hi,
@@ -840,8 +875,20 @@ __device__ __forceinline__ void sweep_up(int mode_rt, int pass, const CfrParams&
                 for (int i = 0; i < VPT; ++i) V_a.v[i] = V_o.v[i] = 0.0f;
             }
             if (mode == kPassFinal && p.values_avg && ch.kind != kInternal) {
-                stv<VPT>(B.row2(p.values_avg, fc + c, a), tid, V_a);
-                stv<VPT>(B.row2(p.values_avg, fc + c, o), tid, V_o);
+                FV<VPT> out_a = V_a, out_o = V_o;
+                if (p.enforce_zero_sum && ch.kind == kModelLeaf && p.leaf_beliefs) {
+                    // a leaf that is not terminal is shifted like an inner node, by its own beliefs
+                    const FV<VPT> la = ldv<VPT>(p.leaf_beliefs + B.leaf_row(ch.internal_idx, a), tid);
+                    const FV<VPT> lo = ldv<VPT>(p.leaf_beliefs + B.leaf_row(ch.internal_idx, o), tid);
+                    const float shift = zero_sum_shift<VPT>(B, V_a, la, V_o, lo);
+#pragma unroll
+                    for (int i = 0; i < VPT; ++i) {
+                        out_a.v[i] = __fsub_rn(V_a.v[i], shift);
+                        out_o.v[i] = __fsub_rn(V_o.v[i], shift);
+                    }
+                }
+                stv<VPT>(B.row2(p.values_avg, fc + c, a), tid, out_a);
+                stv<VPT>(B.row2(p.values_avg, fc + c, o), tid, out_o);
             }
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
@@ -855,13 +902,23 @@ __device__ __forceinline__ void sweep_up(int mode_rt, int pass, const CfrParams&
             stv<VPT>(B.val(ii, o), tid, acc_o);
         }
         if (mode == kPassFinal) {
+            // the outputs may be shifted to zero sum; the work rows the parent backs up from are not
+            FV<VPT> out_a = acc_a, out_o = acc_o;
+            if (p.enforce_zero_sum && (p.values_avg || j == 0)) {
+                const float shift = zero_sum_shift<VPT>(B, acc_a, b_a, acc_o, b_o);
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) {
+                    out_a.v[i] = __fsub_rn(acc_a.v[i], shift);
+                    out_o.v[i] = __fsub_rn(acc_o.v[i], shift);
+                }
+            }
             if (p.values_avg) {
-                stv<VPT>(B.row2(p.values_avg, j, a), tid, acc_a);
-                stv<VPT>(B.row2(p.values_avg, j, o), tid, acc_o);
+                stv<VPT>(B.row2(p.values_avg, j, a), tid, out_a);
+                stv<VPT>(B.row2(p.values_avg, j, o), tid, out_o);
             }
             if (j == 0) {
-                stv<VPT>(p.root_values + ((long long)s * 2 + a) * P2B_HPAD, tid, acc_a);
-                stv<VPT>(p.root_values + ((long long)s * 2 + o) * P2B_HPAD, tid, acc_o);
+                stv<VPT>(p.root_values + ((long long)s * 2 + a) * P2B_HPAD, tid, out_a);
+                stv<VPT>(p.root_values + ((long long)s * 2 + o) * P2B_HPAD, tid, out_o);
             }
         }
         if (update) {
@@ -1034,24 +1091,6 @@ __device__ __forceinline__ void sweep_br(int deviator, const CfrParams& p, Block
         };
         dispatch_children(k, node_body);
     }
-}
-
-// sum over hands of x*y in the reference row-reduction order; stage rows 0/1 must be free.
-template <int VPT>
-__device__ __forceinline__ void dot2_reference_order(Block& B, const FV<VPT>& x0, const FV<VPT>& x1, float (&out)[2]) {
-    const int tid = threadIdx.x;
-    __syncthreads();
-    stv<VPT>(B.stage_row(0), tid, x0);
-    stv<VPT>(B.stage_row(1), tid, x1);
-    __syncthreads();
-    const int warp = tid >> 5;
-    if (warp < 2) {
-        const float sum = row_sum_reference_order(B.stage_row(warp));
-        if ((tid & 31) == 0) B.fsum[warp] = sum;
-    }
-    __syncthreads();
-    out[0] = B.fsum[0];
-    out[1] = B.fsum[1];
 }
 
 template <int VPT, int MAXC>

@@ -72,6 +72,7 @@ struct CfrParams {
     const IterScalars* scalars;  // [iterations]
     int32_t iterations;
     int32_t cfr_plus;
+    int32_t enforce_zero_sum;    // final pass: value outputs shifted to zero sum (cfr_evaluator.py:957-980, 1289-1292)
     int32_t init_depth;          // depth of the deepest tree of the batch the subgames were built in
     int32_t* work_counter;       // dynamic subgame queue (zeroed by the launcher)
     // ---- stepped mode: a launch runs part of the pass sequence and the state that a whole

@@ -205,6 +205,11 @@ def layout_tensor(layout, name: str, device, dtype=None) -> torch.Tensor:
     return t if dtype is None else t.to(dtype)
 
 
+def solve_flags(cfr_plus: bool, enforce_zero_sum: bool) -> int:
+    """The `flags` argument of the solve entry points: bit 0 = CFR+ clamp, bit 1 = zero-sum value outputs."""
+    return int(bool(cfr_plus)) | (int(bool(enforce_zero_sum)) << 1)
+
+
 def pad_rows(x: torch.Tensor) -> torch.Tensor:
     """[..., 1326] -> [..., 1344] zero padded (rows of the kernel are 16-byte aligned)."""
     out = x.new_zeros(*x.shape[:-1], HPAD)
@@ -326,8 +331,11 @@ class SubgameSolver:
                      "exploitability", "br_values", "scratch", "tables", "policy_sample", "beliefs_last"):
             setattr(self, name, None)
 
-    def solve(self, root_beliefs: torch.Tensor, scalars: np.ndarray, *, cfr_plus: bool = False) -> SolveResult:
-        """root_beliefs: [B,2,1344] fp32 on the device (padded).  Enqueues one kernel."""
+    def solve(self, root_beliefs: torch.Tensor, scalars: np.ndarray, *, cfr_plus: bool = False,
+              enforce_zero_sum: bool = False) -> SolveResult:
+        """root_beliefs: [B,2,1344] fp32 on the device (padded).  Enqueues the solve (one to three
+        kernels).  enforce_zero_sum: shift the value outputs to zero sum, as upstream does when
+        `model.enforce_zero_sum` is set (cfr_evaluator.py:957-980, 1289-1292)."""
         assert root_beliefs.shape == (self.B, 2, HPAD) and root_beliefs.dtype == torch.float32
         assert root_beliefs.is_contiguous() and root_beliefs.device == self.device
         iterations = int(scalars.shape[0])
@@ -341,7 +349,8 @@ class SubgameSolver:
                 p(self.regrets), p(self.weight_sums), p(self.policy_avg), p(self.policy), p(self.root_values),
                 p(self.values_avg), p(self.beliefs_avg), p(self.exploitability), p(self.br_values), p(self.scratch),
                 self.scratch.numel(),
-                p(sc) if iterations else None, iterations, int(cfr_plus), self.layout.tree_depth, p(self.work_counter),
+                p(sc) if iterations else None, iterations, solve_flags(cfr_plus, enforce_zero_sum),
+                self.layout.tree_depth, p(self.work_counter),
                 self.num_blocks, p(self.sample_pass), p(self.policy_sample), p(self.beliefs_last),
                 _lib.stream_ptr(self.device))
         self.launches += 1
@@ -371,7 +380,7 @@ class SteppedSolver(SubgameSolver):
 
     start_policy_rows = None  # [rows,1344] policy of the start pass (None: uniform)
 
-    def _step(self, root_beliefs, sc, iterations, cfr_plus, pass_begin, pass_end, phases) -> None:
+    def _step(self, root_beliefs, sc, iterations, flags, pass_begin, pass_end, phases) -> None:
         p = _lib.ptr
         with torch.cuda.device(self.device):
             _lib.call(
@@ -379,7 +388,7 @@ class SteppedSolver(SubgameSolver):
                 self.layout.max_internal, p(self.tables.blob) if self.tables is not None else None, p(root_beliefs),
                 p(self.regrets), p(self.weight_sums), p(self.policy_avg), p(self.policy), p(self.root_values),
                 p(self.values_avg), p(self.beliefs_avg), p(self.exploitability), p(self.br_values), p(self.scratch),
-                self.scratch.numel(), p(sc), iterations, int(cfr_plus), self.layout.tree_depth, p(self.work_counter),
+                self.scratch.numel(), p(sc), iterations, int(flags), self.layout.tree_depth, p(self.work_counter),
                 self.num_blocks, pass_begin, pass_end, phases, p(self.carry_sums), p(self.carry_roots),
                 p(self.leaf_begin), int(self.leaf_beliefs.shape[0]), p(self.leaf_beliefs), p(self.leaf_values),
                 p(self.sample_pass),
@@ -387,7 +396,7 @@ class SteppedSolver(SubgameSolver):
         self.launches += 1
 
     def solve(self, root_beliefs: torch.Tensor, scalars: np.ndarray, leaf_fn=None, *, cfr_plus: bool = False,
-              start_policy: torch.Tensor | None = None, warm_start_iterations: int = 0,
+              enforce_zero_sum: bool = False, start_policy: torch.Tensor | None = None, warm_start_iterations: int = 0,
               warm_start_multiplier: float = 1.0, warm_start_scalars: np.ndarray | None = None) -> SolveResult:
         """scalars: `iteration_scalars(T)` for all T iterations.  start_policy [M,1326] in the
         upstream node order (the policy head's softmax; None = uniform).  With
@@ -399,6 +408,7 @@ class SteppedSolver(SubgameSolver):
         assert root_beliefs.shape == (self.B, 2, HPAD) and root_beliefs.dtype == torch.float32
         assert root_beliefs.is_contiguous() and root_beliefs.device == self.device
         ws = int(warm_start_iterations)
+        flags = solve_flags(cfr_plus, enforce_zero_sum)
         if ws > 0:
             if start_policy is None:
                 raise ValueError("a warm start needs a start policy")
@@ -423,9 +433,9 @@ class SteppedSolver(SubgameSolver):
                               _lib.stream_ptr(self.device))
                 self.launches += 1
             if n_leaves == 0:
-                self._step(root_beliefs, sc, iterations, cfr_plus, pas, pas, 3)
+                self._step(root_beliefs, sc, iterations, flags, pas, pas, 3)
                 continue
-            self._step(root_beliefs, sc, iterations, cfr_plus, pas, pas, 1)
+            self._step(root_beliefs, sc, iterations, flags, pas, pas, 1)
             vals = leaf_fn(self.leaf_beliefs[:n_leaves])
             if vals.shape[-1] == NUM_HANDS:
                 self.leaf_values[:n_leaves, :, :NUM_HANDS].copy_(vals)
@@ -434,12 +444,12 @@ class SteppedSolver(SubgameSolver):
             if self.beliefs_last is not None and pas == iterations - 1:
                 # beliefs of the last iteration at the model leaves (the states sampling continues from)
                 self.beliefs_last[layout_tensor(self.layout, "model_rows", self.device)] = self.leaf_beliefs[:n_leaves]
-            self._step(root_beliefs, sc, iterations, cfr_plus, pas, pas, 2)
+            self._step(root_beliefs, sc, iterations, flags, pas, pas, 2)
         return self._result()
 
 
 def solve_noalloc(sv: SubgameSolver, root_beliefs: torch.Tensor, scalars_dev: torch.Tensor, *,
-                  cfr_plus: bool = False) -> SolveResult:
+                  cfr_plus: bool = False, enforce_zero_sum: bool = False) -> SolveResult:
     """Runs the same solve as `SubgameSolver.solve` through `p2b_cfr_solve_noalloc`, the entry
     point for hosts that cannot allocate GPU memory (a worker confined to a fixed memory
     slice, a latency-critical loop, a process whose framework pool owns all free memory).
@@ -455,7 +465,7 @@ def solve_noalloc(sv: SubgameSolver, root_beliefs: torch.Tensor, scalars_dev: to
             sv.layout.max_internal, p(sv.tables.blob) if sv.tables is not None else None, p(root_beliefs),
             p(sv.regrets), p(sv.weight_sums), p(sv.policy_avg), p(sv.policy), p(sv.root_values), p(sv.values_avg),
             p(sv.beliefs_avg), p(sv.exploitability), p(sv.br_values), p(scalars_dev), int(scalars_dev.shape[0]),
-            int(cfr_plus), sv.layout.tree_depth,
+            solve_flags(cfr_plus, enforce_zero_sum), sv.layout.tree_depth,
             _lib.stream_ptr(sv.device))
     return SolveResult(sv.layout, sv.policy_avg, sv.regrets, sv.weight_sums, sv.policy, sv.root_values,
                        sv.values_avg, sv.beliefs_avg, sv.exploitability, sv.br_values)
@@ -465,7 +475,8 @@ def solve_subgames(boards, ranges, pot, stacks, *, iterations: int, bet_bins=(0.
                    max_raises=None, bb: int = 2, cfr_type: str = "discounted", alpha: float = 1.5, beta: float = 0.0,
                    gamma: float = 2.0, dcfr_delay: int = 0, cfr_plus: bool = False, device=None,
                    keep_policy: bool = False, keep_node_values: bool = False, track_weight_sums: bool = True,
-                   exploitability: bool = False, device_tree: bool = False):
+                   exploitability: bool = False, device_tree: bool = False, enforce_zero_sum: bool = False,
+                   alpha_final=None, beta_final=None, gamma_final=None):
     """Solves a batch of river subgames: boards [B,5] card ids, ranges [B,2,1326] fp32,
     pot [B] and stacks [B] or [B,2] in chips.  Returns (SolveResult, PublicTrees); with
     `device_tree` the trees are expanded on the GPU (`device_tree.build_device_layout`), no host
@@ -486,8 +497,9 @@ def solve_subgames(boards, ranges, pot, stacks, *, iterations: int, bet_bins=(0.
     solver = SubgameSolver(layout, torch.from_numpy(boards_np), device, track_weight_sums=track_weight_sums,
                            keep_policy=keep_policy, keep_node_values=keep_node_values, exploitability=exploitability)
     rb = pad_rows(torch.as_tensor(ranges, dtype=torch.float32).to(device)).contiguous()
-    scal = iteration_scalars(iterations, cfr_type=cfr_type, alpha=alpha, beta=beta, gamma=gamma, dcfr_delay=dcfr_delay)
-    return solver.solve(rb, scal, cfr_plus=cfr_plus), trees
+    scal = iteration_scalars(iterations, cfr_type=cfr_type, alpha=alpha, beta=beta, gamma=gamma, dcfr_delay=dcfr_delay,
+                             alpha_final=alpha_final, beta_final=beta_final, gamma_final=gamma_final)
+    return solver.solve(rb, scal, cfr_plus=cfr_plus, enforce_zero_sum=enforce_zero_sum), trees
 
 
 def solve_subgames_with_model(boards, ranges, pot, stacks, model, *, street: int, iterations: int,
@@ -495,7 +507,7 @@ def solve_subgames_with_model(boards, ranges, pot, stacks, model, *, street: int
                               cfr_type: str = "discounted", alpha: float = 1.5, beta: float = 0.0, gamma: float = 2.0,
                               dcfr_delay: int = 0, cfr_plus: bool = False, device=None, chance_average: bool = True,
                               chunk: int = 2048, exploitability: bool = False, keep_node_values: bool = False,
-                              device_tree: bool = False):
+                              device_tree: bool = False, enforce_zero_sum: bool = False):
     """Solves a batch of flop (street=1, 3 board cards) or turn (street=2, 4 cards) subgames
     whose leaves at the start of the next street are valued by `model(beliefs, boards,
     context)`, averaged over the next public card when `chance_average` (the
@@ -533,5 +545,6 @@ def solve_subgames_with_model(boards, ranges, pot, stacks, model, *, street: int
         evaluator = leaf_eval.DirectLeafEvaluator(model, leaf_boards, ctx, device)
     rb = pad_rows(torch.as_tensor(ranges, dtype=torch.float32).to(device)).contiguous()
     scal = iteration_scalars(iterations, cfr_type=cfr_type, alpha=alpha, beta=beta, gamma=gamma, dcfr_delay=dcfr_delay)
-    res = sv.solve(rb, scal, evaluator if layout.num_model_leaves else None, cfr_plus=cfr_plus)
+    res = sv.solve(rb, scal, evaluator if layout.num_model_leaves else None, cfr_plus=cfr_plus,
+                   enforce_zero_sum=enforce_zero_sum)
     return res, trees, sv

@@ -1,0 +1,128 @@
+"""The CUDA solver under settings beyond plain DCFR, against arrays produced by the upstream
+evaluator: the production search block, standard CFR, zero-sum value targets, and the headline
+workload at depth (16 ragged roots x 256 iterations)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+RTOL, ATOL = 1e-5, 1e-6  # fp32 strategies and values: 1e-5 relative plus a small absolute term near zero
+
+
+def _close(name, got, want, rtol=RTOL, atol=ATOL):
+    err = (got - want).abs()
+    print(f"{name}: max abs {err.max().item():.3e}")
+    torch.testing.assert_close(got, want, rtol=rtol, atol=atol)
+
+
+def test_production_search_block_matches_upstream(cuda_device, golden_dir):
+    """discounted_plus with a delay, exponent schedules (alpha 2->4, beta -1->-2, gamma 5->0), warm
+    start of type `model` (15 iterations, multiplier 10), zero-sum value targets: the search block of
+    the upstream production configuration at a reduced iteration count."""
+    from poker2_b200 import solver, tree as ptree
+
+    z = np.load(os.path.join(golden_dir, "cfr_production_cap2_t40.npz"))
+    T, ws, delay = int(z["iterations"]), int(z["warm_start_iterations"]), int(z["dcfr_delay"])
+    trees = ptree.build_trees(ptree.root_states(z["pot"], z["stack"], min_raise=2), [0.5, 1.0], int(z["max_depth"]),
+                              bb=2, max_raises=int(z["cap"]))
+    assert trees.total_nodes == int(z["total_nodes"])
+    boards = z["boards"].astype(np.int64)
+    layout = solver.device_layout(trees, boards)
+    sv = solver.SteppedSolver(layout, torch.from_numpy(boards), cuda_device, exploitability=True, sampling=True)
+    sv.set_sampling_schedule(torch.from_numpy(z["t_sample"]), warm_start_iterations=ws)
+    rb = solver.pad_rows(torch.from_numpy(z["ranges"]).to(cuda_device)).contiguous()
+    kw = dict(cfr_type="discounted_plus", gamma=float(z["gamma"][0]), dcfr_delay=delay)
+    scal = solver.iteration_scalars(T, alpha=float(z["alpha"][0]), alpha_final=float(z["alpha"][1]),
+                                    beta=float(z["beta"][0]), beta_final=float(z["beta"][1]),
+                                    gamma_final=float(z["gamma"][1]), warm_start_iterations=ws, **kw)
+    first = solver.warm_start_mix_scalars(scal, warm_start_iterations=ws, **kw)
+    res = sv.solve(rb, scal, start_policy=torch.from_numpy(z["start_policy"]), warm_start_iterations=ws,
+                   warm_start_multiplier=float(z["warm_start_multiplier"]), warm_start_scalars=first,
+                   enforce_zero_sum=True)
+    assert sv.status() == 0
+    n = trees.num_roots
+    for name, got in [("regrets", res.regrets), ("weight_sums", res.weight_sums), ("policy_avg", res.policy_avg),
+                      ("policy_sample", res.policy_sample)]:
+        _close(name, res.level_major(got).cpu()[n:], torch.from_numpy(z[name])[n:])
+    _close("root_values", res.root_values[..., :1326].cpu(), torch.from_numpy(z["root_values"]))
+    _close("values_avg", res.level_major(res.values_avg).cpu(), torch.from_numpy(z["values_avg"]))
+    _close("exploitability", res.exploitability.cpu(), torch.from_numpy(z["exploitability"]), rtol=1e-4)
+
+
+def test_standard_cfr_matches_upstream(cuda_device, golden_dir):
+    from poker2_b200 import solver
+
+    z = np.load(os.path.join(golden_dir, "cfr_standard_cap2_t16.npz"))
+    res, trees = solver.solve_subgames(z["boards"].astype(np.int64), torch.from_numpy(z["ranges"]), z["pot"], z["stack"],
+                                       iterations=int(z["iterations"]), max_depth=int(z["max_depth"]),
+                                       max_raises=int(z["cap"]), cfr_type="standard", exploitability=True,
+                                       device=cuda_device)
+    assert trees.total_nodes == int(z["total_nodes"])
+    n = trees.num_roots
+    for name, got in [("regrets", res.regrets), ("weight_sums", res.weight_sums), ("policy_avg", res.policy_avg)]:
+        _close(name, res.level_major(got).cpu()[n:], torch.from_numpy(z[name])[n:])
+    _close("root_values", res.root_values[..., :1326].cpu(), torch.from_numpy(z["root_values"]))
+    _close("exploitability", res.exploitability.cpu(), torch.from_numpy(z["exploitability"]), rtol=1e-4)
+
+
+def test_zero_sum_value_targets_match_upstream(cuda_device, golden_dir):
+    """`model.enforce_zero_sum = True` upstream: every node's final values minus the mean over the
+    players of sum_h values * beliefs_avg, except at terminal nodes.  River subgames through the
+    one-call solve; turn subgames (leaves valued by a stand-in model, shifted too) pass by pass."""
+    from leaf_models import pot_echo_leaf_fn
+    from poker2_b200 import solver, tree as ptree
+
+    z = np.load(os.path.join(golden_dir, "cfr_zero_sum.npz"))
+    cap, depth = int(z["cap"]), int(z["max_depth"])
+    res, trees = solver.solve_subgames(z["river_boards"].astype(np.int64), torch.from_numpy(z["river_ranges"]),
+                                       z["river_pot"], z["river_stack"], iterations=int(z["river_iterations"]),
+                                       max_depth=depth, max_raises=cap, keep_node_values=True, exploitability=True,
+                                       enforce_zero_sum=True, device=cuda_device)
+    assert trees.total_nodes == int(z["river_total_nodes"])
+    n = trees.num_roots
+    _close("river policy_avg", res.level_major(res.policy_avg).cpu()[n:], torch.from_numpy(z["river_policy_avg"])[n:])
+    _close("river values_avg", res.level_major(res.values_avg).cpu(), torch.from_numpy(z["river_values_avg"]))
+    _close("river root_values", res.root_values[..., :1326].cpu(), torch.from_numpy(z["river_values_avg"])[:n])
+    _close("river exploitability", res.exploitability.cpu(), torch.from_numpy(z["river_exploitability"]), rtol=1e-4)
+    # without the flag the root values differ from the shifted ones (the test would notice a no-op)
+    plain, _ = solver.solve_subgames(z["river_boards"].astype(np.int64), torch.from_numpy(z["river_ranges"]),
+                                     z["river_pot"], z["river_stack"], iterations=int(z["river_iterations"]),
+                                     max_depth=depth, max_raises=cap, device=cuda_device)
+    assert (plain.root_values[..., :1326].cpu() - torch.from_numpy(z["river_values_avg"])[:n]).abs().max() > 1e-4
+
+    roots = ptree.root_states(z["turn_pot"], z["turn_stack"], min_raise=2, street=2)
+    trees = ptree.build_trees(roots, [0.5, 1.0], depth, bb=2, max_raises=cap)
+    assert trees.total_nodes == int(z["turn_total_nodes"])
+    boards = np.concatenate([z["turn_boards"].astype(np.int64), np.full((z["turn_boards"].shape[0], 1), -1)], axis=1)
+    layout = solver.device_layout(trees, boards)
+    sv = solver.SteppedSolver(layout, torch.from_numpy(boards), cuda_device, exploitability=True)
+    leaf_fn = pot_echo_leaf_fn(trees, layout.model_nodes, torch.from_numpy(z["hand_weights"]))
+    rb = solver.pad_rows(torch.from_numpy(z["turn_ranges"]).to(cuda_device)).contiguous()
+    res = sv.solve(rb, solver.iteration_scalars(int(z["turn_iterations"])), leaf_fn, enforce_zero_sum=True)
+    n = trees.num_roots
+    _close("turn policy_avg", res.level_major(res.policy_avg).cpu()[n:], torch.from_numpy(z["turn_policy_avg"])[n:])
+    _close("turn values_avg", res.level_major(res.values_avg).cpu(), torch.from_numpy(z["turn_values_avg"]))
+    _close("turn exploitability", res.exploitability.cpu(), torch.from_numpy(z["turn_exploitability"]), rtol=1e-4)
+    _close("turn br_values", res.br_values.cpu(), torch.from_numpy(z["turn_br_values"]), rtol=1e-4)
+
+
+def test_ragged_roots_at_256_iterations_match_upstream(cuda_device, golden_dir):
+    """The headline configuration at depth: 16 ragged river roots (pot U[20,200], stack U[100,1000]),
+    256 DCFR iterations, against the upstream run: root values, exploitability and a fixed subsample
+    of the average-policy and regret rows."""
+    from poker2_b200 import solver
+
+    z = np.load(os.path.join(golden_dir, "cfr_ragged16_cap2_t256.npz"))
+    res, trees = solver.solve_subgames(z["boards"].astype(np.int64), torch.from_numpy(z["ranges"]), z["pot"], z["stack"],
+                                       iterations=int(z["iterations"]), max_depth=int(z["max_depth"]),
+                                       max_raises=int(z["cap"]), exploitability=True, device=cuda_device)
+    assert trees.total_nodes == int(z["total_nodes"])
+    rows = torch.from_numpy(z["policy_rows"])
+    _close("policy_avg rows", res.level_major(res.policy_avg).cpu()[rows], torch.from_numpy(z["policy_avg_rows"]))
+    _close("regret rows", res.level_major(res.regrets).cpu()[rows], torch.from_numpy(z["regret_rows"]))
+    _close("root_values", res.root_values[..., :1326].cpu(), torch.from_numpy(z["root_values"]))
+    _close("exploitability", res.exploitability.cpu(), torch.from_numpy(z["exploitability"]), rtol=1e-4)
+    _close("br_values", res.br_values.cpu(), torch.from_numpy(z["br_values"]), rtol=1e-4)

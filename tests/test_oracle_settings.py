@@ -1,0 +1,106 @@
+"""The CFR oracle under solver settings beyond plain DCFR, against arrays produced by the upstream
+evaluator: the production search block (discounted_plus, delay, exponent schedules, warm start),
+standard CFR, zero-sum value targets, and iteration_scalars against the oracle's own schedule."""
+import os
+
+import numpy as np
+import torch
+
+from leaf_models import pot_echo_leaf_fn
+from oracle import cfr as ocfr
+from poker2_b200 import solver, tree as ptree
+
+BET_BINS = [0.5, 1.0]
+
+
+def _build(pot, stack, cap, depth, street=3):
+    roots = ptree.root_states(pot, stack, min_raise=2, street=street)
+    return ptree.build_trees(roots, BET_BINS, depth, bb=2, max_raises=cap)
+
+
+def test_oracle_production_search_block_bit_exact(golden_dir):
+    z = np.load(os.path.join(golden_dir, "cfr_production_cap2_t40.npz"))
+    t = _build(z["pot"], z["stack"], int(z["cap"]), int(z["max_depth"]))
+    assert t.total_nodes == int(z["total_nodes"])
+    o = ocfr.SubgameOracle(
+        t.oracle_dict(z["boards"].astype(np.int64)), torch.from_numpy(z["ranges"]), iterations=int(z["iterations"]),
+        cfr_type="discounted_plus", dcfr_delay=int(z["dcfr_delay"]), alpha=float(z["alpha"][0]),
+        alpha_final=float(z["alpha"][1]), beta=float(z["beta"][0]), beta_final=float(z["beta"][1]),
+        gamma=float(z["gamma"][0]), gamma_final=float(z["gamma"][1]), start_policy=torch.from_numpy(z["start_policy"]),
+        warm_start_iterations=int(z["warm_start_iterations"]), warm_start_multiplier=float(z["warm_start_multiplier"]),
+        enforce_zero_sum=True).solve()
+    assert torch.equal(o.regrets, torch.from_numpy(z["regrets"]))
+    assert torch.equal(o.weight_sums, torch.from_numpy(z["weight_sums"]))
+    assert torch.equal(o.policy_avg, torch.from_numpy(z["policy_avg"]))
+    assert torch.equal(o.values_avg, torch.from_numpy(z["values_avg"]))
+    ex, _ = o.exploitability()
+    assert torch.equal(ex, torch.from_numpy(z["exploitability"]))
+
+
+def test_oracle_standard_cfr_bit_exact(golden_dir):
+    z = np.load(os.path.join(golden_dir, "cfr_standard_cap2_t16.npz"))
+    t = _build(z["pot"], z["stack"], int(z["cap"]), int(z["max_depth"]))
+    o = ocfr.SubgameOracle(t.oracle_dict(z["boards"].astype(np.int64)), torch.from_numpy(z["ranges"]),
+                           iterations=int(z["iterations"]), cfr_type="standard").solve()
+    assert torch.equal(o.regrets, torch.from_numpy(z["regrets"]))
+    assert torch.equal(o.weight_sums, torch.from_numpy(z["weight_sums"]))
+    assert torch.equal(o.policy_avg, torch.from_numpy(z["policy_avg"]))
+    assert torch.equal(o.values_avg[: o.N], torch.from_numpy(z["root_values"]))
+    ex, _ = o.exploitability()
+    assert torch.equal(ex, torch.from_numpy(z["exploitability"]))
+
+
+def test_oracle_zero_sum_value_targets_bit_exact(golden_dir):
+    z = np.load(os.path.join(golden_dir, "cfr_zero_sum.npz"))
+    cap, depth = int(z["cap"]), int(z["max_depth"])
+    t = _build(z["river_pot"], z["river_stack"], cap, depth)
+    o = ocfr.SubgameOracle(t.oracle_dict(z["river_boards"].astype(np.int64)), torch.from_numpy(z["river_ranges"]),
+                           iterations=int(z["river_iterations"]), enforce_zero_sum=True).solve()
+    assert torch.equal(o.policy_avg, torch.from_numpy(z["river_policy_avg"]))
+    assert torch.equal(o.values_avg, torch.from_numpy(z["river_values_avg"]))
+    # turn subgames: the leaves the model values are shifted too, and the best responses start from them
+    t = _build(z["turn_pot"], z["turn_stack"], cap, depth, street=2)
+    assert t.total_nodes == int(z["turn_total_nodes"])
+    boards = np.concatenate([z["turn_boards"].astype(np.int64), np.full((z["turn_boards"].shape[0], 1), -1)], axis=1)
+    model_nodes = np.nonzero(z["turn_model_mask"])[0]
+    leaf_fn = pot_echo_leaf_fn(t, model_nodes, torch.from_numpy(z["hand_weights"]))
+    o = ocfr.SubgameOracle(t.oracle_dict(boards), torch.from_numpy(z["turn_ranges"]),
+                           iterations=int(z["turn_iterations"]), enforce_zero_sum=True,
+                           leaf_fn=lambda b, idx: leaf_fn(b)).solve()
+    assert torch.equal(o.policy_avg, torch.from_numpy(z["turn_policy_avg"]))
+    assert torch.equal(o.values_avg, torch.from_numpy(z["turn_values_avg"]))
+    ex, br = o.exploitability()
+    assert torch.equal(ex, torch.from_numpy(z["turn_exploitability"]))
+    assert torch.equal(br, torch.from_numpy(z["turn_br_values"]))
+
+
+def test_iteration_scalars_follow_the_schedules():
+    """The host table the kernels read equals what the oracle (pinned to upstream above) computes
+    per iteration, including a negative beta after a warm start."""
+    T, ws, delay = 40, 15, 24
+    sc = solver.iteration_scalars(T, cfr_type="discounted_plus", alpha=2.0, alpha_final=4.0, beta=-1.0,
+                                  beta_final=-2.0, gamma=5.0, gamma_final=0.0, dcfr_delay=delay,
+                                  warm_start_iterations=ws)
+
+    class Sched:
+        pass
+
+    o = Sched()
+    o.iterations, o.warm_start_iterations = T, ws
+    o.alpha0, o.beta0, o.gamma0 = 2.0, -1.0, 5.0
+    o.alpha_final, o.beta_final, o.gamma_final = 4.0, -2.0, 0.0
+    for t in range(ws, T):
+        ocfr.SubgameOracle.apply_schedules(o, t)
+        assert sc[t]["num_pos"] == np.float32(t ** o.alpha) and sc[t]["den_pos"] == np.float32(t ** o.alpha + 1)
+        assert sc[t]["num_neg"] == np.float32(t ** o.beta) and sc[t]["den_neg"] == np.float32(t ** o.beta + 1)
+        assert sc[t]["do_mix"] == (1 if t > delay else 0)
+        if t > delay:
+            assert (sc[t]["mix_old"], sc[t]["mix_new"]) == (t - delay, 2)
+    assert (sc[:ws]["do_mix"] == 0).all() and (sc[:ws]["num_neg"] == 1).all()
+    # plain DCFR keeps its values (t = 0: 0**0 = 1, 0**1.5 = 0)
+    plain = solver.iteration_scalars(4)
+    assert plain[0]["num_pos"] == 0 and plain[0]["num_neg"] == 1 and plain[0]["do_mix"] == 0
+    assert plain[3]["mix_old"] == 9 and plain[3]["mix_new"] == 16
+    # standard CFR: no discount, weights (t, 1)
+    std = solver.iteration_scalars(4, cfr_type="standard")
+    assert std[2]["num_pos"] == 1 and std[2]["den_pos"] == 1 and (std[2]["mix_old"], std[2]["mix_new"]) == (2, 1)
