@@ -9,9 +9,12 @@ fused CFR kernel.  Metric: subgame-CFR-iterations per second over all GPUs.
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
 With N > 1 launch under torch.distributed.run; every rank solves its own B subgames (no
-collective inside the solve) and the value targets are all-gathered at the end of a step.
+collective inside the solve) and the training targets are all-gathered at the end of a step.
 `--impl reference` times the CPU restatement of the upstream evaluator (oracle/) on the
-host cores instead.
+host cores instead.  The JSON line also carries: `roofline` (the iteration kernel, timed
+alone with CUDA events on its stream), `micro` (showdown evals/s and 7-card ranks/s, the
+second half of the metric), `without_weight_sums`, `strong` (N > 1: the SAME 4096 subgames
+split over the ranks), `e2e` and, at N = 1, `cpu_baseline`.
 """
 from __future__ import annotations
 
@@ -29,6 +32,13 @@ import torch
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
+
+# Per-build constants of the iteration kernel from its ncu capture on a small case (592 subgames x 16
+# iterations; summary and command under profiles/): DRAM bytes moved and warp instructions executed
+# per subgame-pass.  Both grow in proportion to the subgame-passes of a launch.
+NCU_DRAM_BYTES_PER_SUBGAME_PASS = 3.25e6
+NCU_WARP_INSTRUCTIONS_PER_SUBGAME_PASS = 1.08e6
+NCU_CAPTURE = "ncu --set full on cfr_iter_kernel, 592 subgames x 16 iterations, scaled by subgame-passes"
 
 BATCH = 4096
 ITERATIONS = 256
@@ -150,7 +160,9 @@ def run_reference_arm(args, rank: int):
         "impl": "reference", "metric": "subgame-CFR-iterations/sec", "value": value, "unit": "subgame-iterations/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sum(secs) / len(secs),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(),
+        "config": dict(workload_config(), workload=f"bounded sample of the batched river workload: {sample}; same tree "
+                                                      "abstraction, ranges, pots and stacks as the B=4096 x 256 GPU arm",
+                       batch_per_gpu=n_roots, iterations=iters),
         "cpu_baseline": {"value": value, "unit": "subgame-iterations/s", "cores": cores, "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": "subgame-iterations/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -166,7 +178,7 @@ def workload_config():
 def run_gpu_arm(args, rank: int, world: int, local_rank: int):
     import torch.distributed as dist
 
-    from poker2_b200 import build, sharding, solver
+    from poker2_b200 import _lib, build, sharding, solver
     from poker2_b200 import tree as ptree
 
     build.build()
@@ -175,6 +187,14 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
     distributed = world > 1
     if distributed:
         dist.init_process_group("nccl", device_id=device)
+
+    def iteration_kernel_ms() -> float:
+        import ctypes
+
+        out = ctypes.c_float(0.0)
+        with torch.cuda.device(device):
+            _lib.call("p2b_cfr_iteration_ms", ctypes.byref(out))
+        return float(out.value)
 
     boards, ranges, pot, stack = make_inputs(BATCH, SEED + rank)
     trees = ptree.build_trees(ptree.root_states(pot.numpy(), stack.numpy()), list(BET_BINS), MAX_DEPTH,
@@ -185,13 +205,19 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
     scal = solver.iteration_scalars(ITERATIONS)
     gathered = None
 
-    def step():
+    iter_ms = []
+
+    def step(timed=False):
         res = sv.solve(rb, scal)
-        if distributed:  # the one exchange of the path: value targets and exploitability statistics
-            sharding.gather_rows(res.root_values)
+        if timed:  # duration of the iteration kernel alone (CUDA events around that launch, on its stream)
+            iter_ms.append(iteration_kernel_ms())
+        if distributed:  # the one exchange of the path: training targets and exploitability statistics
+            sharding.gather_payload({"value_targets": res.root_values, "beliefs": rb})
             sharding.reduce_exploitability(res.exploitability)
         return res
 
+    with torch.cuda.device(device):
+        _lib.call("p2b_cfr_iteration_timing", 1)
     for _ in range(args.warmup):
         step()
     torch.cuda.synchronize()
@@ -204,7 +230,7 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
     torch.cuda.synchronize()
     e0.record()
     for _ in range(args.steps):
-        step()
+        step(timed=True)
     e1.record()
     torch.cuda.synchronize()
     if distributed:
@@ -217,12 +243,69 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
     ms_step = ms_total / args.steps
     units_per_step = world * BATCH * ITERATIONS
     value = units_per_step / (ms_step / 1e3)
+    extras = {"iteration_kernel_ms": sum(iter_ms) / len(iter_ms)}
+
+    if rank == 0 and not distributed and not args.no_extras:
+        # the same step without the regret weight sums (they feed one statistic, cfr_evaluator.py:1642)
+        sv.release()
+        sv2 = solver.SubgameSolver(layout, boards, device, exploitability=True, track_weight_sums=False)
+        ms_nows = _time_ms(lambda: sv2.solve(rb, scal), 1, 1)
+        extras["without_weight_sums"] = {"ms_per_step": ms_nows, "value": BATCH * ITERATIONS / (ms_nows / 1e3),
+                                         "unit": "subgame-iterations/s"}
+        sv2.release()
+        del sv2
+        torch.cuda.empty_cache()
+        extras["micro"] = micro_member(device)
+    if distributed and not args.no_extras:
+        extras["strong"] = run_strong(args, solver, sharding, rank, world, device)
 
     e2e = None
     if not args.no_e2e:
         e2e = run_e2e(args, solver, sv, boards, ranges, pot, stack, layout, scal, gathered, distributed, device,
                       units_per_step)
-    finish_gpu_arm(args, rank, world, layout, ms_step, value, clocks, e2e, distributed)
+    finish_gpu_arm(args, rank, world, layout, ms_step, value, clocks, e2e, distributed, extras)
+
+
+def run_strong(args, solver, sharding, rank, world, device):
+    """Strong scaling: the SAME B subgames (seed of rank 0) split into contiguous blocks of roots,
+    one per rank; device-timed like the main leg, maximum over the ranks."""
+    import torch.distributed as dist
+    from poker2_b200 import tree as ptree
+
+    boards, ranges, pot, stack = make_inputs(BATCH, SEED)
+    lo, hi = sharding.shard_bounds(BATCH, rank, world)
+    trees = ptree.build_trees(ptree.root_states(pot[lo:hi].numpy(), stack[lo:hi].numpy()), list(BET_BINS), MAX_DEPTH,
+                              max_raises=MAX_RAISES)
+    layout = solver.device_layout(trees, boards[lo:hi].numpy())
+    sv = solver.SubgameSolver(layout, boards[lo:hi], device, exploitability=True)
+    rb = solver.pad_rows(ranges[lo:hi].to(device)).contiguous()
+    scal = solver.iteration_scalars(ITERATIONS)
+
+    def step():
+        res = sv.solve(rb, scal)
+        sharding.gather_payload({"value_targets": res.root_values, "beliefs": rb})
+        sharding.reduce_exploitability(res.exploitability)
+
+    step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    steps = max(1, min(args.steps, 3))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    ms = torch.tensor([e0.elapsed_time(e1) / steps], device=device)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    sv.release()
+    blocks = 2 * torch.cuda.get_device_properties(device).multi_processor_count
+    return {"scaling": "strong", "subgames_total": BATCH, "subgames_per_gpu": hi - lo, "steps": steps,
+            "ms_per_step": float(ms.item()), "value": BATCH * ITERATIONS / (float(ms.item()) / 1e3),
+            "unit": "subgame-iterations/s",
+            "waves_per_gpu": (hi - lo) / blocks,
+            "note": f"{blocks} subgames are in flight per GPU (two thread blocks per SM); the last wave is partly empty"}
 
 
 def run_e2e(args, solver, sv, boards, ranges, pot, stack, layout, scal, gathered, distributed, device,
@@ -232,30 +315,41 @@ def run_e2e(args, solver, sv, boards, ranges, pot, stack, layout, scal, gathered
     # ---- end to end through the public call, host buffers in, host buffers out ----
     h_boards = boards.to(torch.int16).pin_memory()
     h_ranges = ranges.pin_memory()
-    pinned = {}
     e2e_steps = max(1, min(args.steps, 3))
 
-    def e2e_step():
+    from poker2_b200 import sharding
+
+    copy_stream = torch.cuda.Stream(device=device)
+    pinned = [{}, {}]  # two sets of pinned buffers: the copy of step i runs under the solve of step i+1
+    in_flight = []
+
+    def e2e_step(i):
         res, _ = solver.solve_subgames(h_boards, h_ranges, pot, stack, iterations=ITERATIONS, bet_bins=BET_BINS,
                                        max_depth=MAX_DEPTH, max_raises=MAX_RAISES, device=device, exploitability=True,
                                        device_tree=True)
-        from poker2_b200 import sharding
-
         if distributed:
-            sharding.gather_rows(res.root_values)
-        out = res.to_host(pinned)
-        out["stats"] = sharding.reduce_exploitability(res.exploitability)  # one small D2H read
+            sharding.gather_payload({"value_targets": res.root_values})
+        stats = sharding.reduce_exploitability(res.exploitability)  # one collective, one small D2H read
+        out, done = res.to_host_async(pinned[i % 2], copy_stream)
+        out["stats"] = stats
+        in_flight.append((res, done))  # keeps the device buffers alive until their copy has finished
+        while len(in_flight) > 1:  # the result of the step before is complete on the host before the next starts
+            in_flight.pop(0)[1].synchronize()
         return out
 
     sv.release()
     torch.cuda.empty_cache()
-    out = e2e_step()  # warm-up: allocator and pinned buffers
+    out = e2e_step(0)  # warm-up: allocator and pinned buffers
+    in_flight.pop(0)[1].synchronize()
+    out = e2e_step(1)
+    in_flight.pop(0)[1].synchronize()
     torch.cuda.synchronize()
     if distributed:
         dist.barrier()
     t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        out = e2e_step()
+    for i in range(e2e_steps):
+        out = e2e_step(i)
+    in_flight.pop(0)[1].synchronize()  # the last step's targets are on the host
     torch.cuda.synchronize()
     e2e_s = torch.tensor([time.perf_counter() - t0], device=device)
     if distributed:
@@ -267,29 +361,42 @@ def run_e2e(args, solver, sv, boards, ranges, pot, stack, layout, scal, gathered
             "d2h_bytes_per_step": int(d2h), "steps": e2e_steps}
 
 
-def finish_gpu_arm(args, rank, world, layout, ms_step, value, clocks, e2e, distributed):
+def finish_gpu_arm(args, rank, world, layout, ms_step, value, clocks, e2e, distributed, extras):
     import torch.distributed as dist
 
     if rank == 0:
         nonroot = int(layout.rows - BATCH)
         alg_bytes = 16.0 * 1326 * nonroot * ITERATIONS  # regrets + average policy, read + write, per iteration
         peak, peak_kind = measured_peak_gbs()
-        achieved = alg_bytes / (ms_step / 1e3) / 1e9
-        # DRAM bytes per subgame-pass from the ncu capture of a small case (profiles/), scaled
-        # to this launch by the number of subgame-passes (traffic grows in proportion)
-        traffic = 2.76e6 * BATCH * (ITERATIONS + 2)
+        # the dominant kernel: all ITERATIONS passes of the batch run in one launch of cfr_iter_kernel,
+        # timed alone with CUDA events on its stream (the start and final passes are separate launches)
+        iter_ms = extras.pop("iteration_kernel_ms")
+        achieved = alg_bytes / (iter_ms / 1e3) / 1e9
+        passes = BATCH * ITERATIONS
+        traffic = NCU_DRAM_BYTES_PER_SUBGAME_PASS * passes
+        sms = torch.cuda.get_device_properties(0).multi_processor_count
+        sm_hz = 1e6 * (clocks.get("sm_mhz") or 1965.0) if clocks else 1.965e9
+        issue_slots = (iter_ms / 1e3) * sms * 4 * sm_hz
         line = {
             "metric": "subgame-CFR-iterations/sec", "value": value, "unit": "subgame-iterations/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": dict(workload_config(), nodes_per_gpu=int(layout.rows),
                            mean_nodes_per_subgame=layout.rows / BATCH),
-            "clocks": clocks, "gpu_launches": 2 * args.steps,  # per step: record check + solver kernel
+            # per step: start pass, iteration passes, final pass, each a record check + a solver kernel
+            "clocks": clocks, "gpu_launches": 6 * args.steps,
             "e2e": e2e,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": traffic, "peak_source": peak_kind,
-                         "kernel": "cfr_solve_kernel", "algorithmic_bytes_per_launch": alg_bytes},
+                         "frac": achieved / peak, "traffic": traffic, "traffic_source": NCU_CAPTURE,
+                         "peak_source": peak_kind, "kernel": "cfr_iter_kernel", "kernel_ms_per_launch": iter_ms,
+                         "algorithmic_bytes_per_launch": alg_bytes,
+                         # second roofline: issue slots (4 schedulers per SM, one warp instruction per cycle each)
+                         "issue": {"warp_instructions_per_launch": NCU_WARP_INSTRUCTIONS_PER_SUBGAME_PASS * passes,
+                                   "issue_slots_per_launch": issue_slots,
+                                   "frac": NCU_WARP_INSTRUCTIONS_PER_SUBGAME_PASS * passes / issue_slots,
+                                   "source": NCU_CAPTURE}},
         }
+        line.update(extras)
         if world == 1 and not args.no_cpu_baseline:
             rate, dt, cores = cpu_port_rate(32, 8, SEED)
             line["cpu_baseline"] = {"value": rate, "unit": "subgame-iterations/s", "cores": cores, "kind": "port",
@@ -311,6 +418,66 @@ def _time_ms(fn, steps: int, warmup: int) -> float:
     e1.record()
     torch.cuda.synchronize()
     return e0.elapsed_time(e1) / steps
+
+
+def micro_member(device, log2_hands: int = 26, board_factor: int = 4, seconds: float = 0.8) -> dict:
+    """The second half of the metric inside the default run: showdown evals/s (board tables built per
+    board, then both players evaluated; and evaluation alone) and 7-card ranks/s, each kernel repeated
+    for about `seconds` so that the clock sampler sees the whole measurement."""
+    from poker2_b200 import _lib, showdown
+
+    g = torch.Generator(device=device).manual_seed(1)
+    n_hands = 1 << log2_hands
+    cards = torch.cat([torch.rand((n_hands // 16, 52), device=device, generator=g).argsort(dim=1)[:, :7].to(torch.int16)
+                       for _ in range(16)])
+    out = torch.empty(n_hands, dtype=torch.int32, device=device)
+    m = 4096 * board_factor
+    boards = torch.rand((m, 52), device=device, generator=g).argsort(dim=1)[:, :5].contiguous()
+    hit = torch.zeros(m, 52, dtype=torch.bool, device=device)
+    hit.scatter_(1, boards, True)
+    c1, c2 = np.triu_indices(52, k=1)
+    blocked = hit[:, torch.from_numpy(c1).to(device)] | hit[:, torch.from_numpy(c2).to(device)]
+    bel = torch.empty(m, 2, 1326, device=device).exponential_(generator=g) * (~blocked)[:, None, :]
+    bel = (bel / bel.sum(-1, keepdim=True)).contiguous()
+    pot = torch.ones((m, 2), dtype=torch.int64, device=device)
+    scale = torch.ones(m, device=device)
+    vals = torch.empty_like(bel)
+    holder = {}
+
+    def rank():
+        _lib.call("p2b_rank7_cards", _lib.ptr(cards), n_hands, _lib.ptr(out), _lib.stream_ptr(device))
+
+    def both():
+        holder["t"] = showdown.BoardTables(boards)
+        showdown.showdown_values(holder["t"], bel, pot, scale, out=vals)
+
+    tabs = showdown.BoardTables(boards)
+
+    def evaluate():
+        showdown.showdown_values(tabs, bel, pot, scale, out=vals)
+
+    def timed(fn):
+        once = _time_ms(fn, 3, 3)
+        reps = max(5, int(seconds * 1e3 / max(once, 1e-3)))
+        return _time_ms(fn, reps, 0), reps
+
+    sampler = ClockSampler(device.index or 0)
+    sampler.start()
+    (ms_rank, n_rank), (ms_both, n_both), (ms_eval, n_eval) = timed(rank), timed(both), timed(evaluate)
+    clocks = sampler.stop()
+    peak, _ = measured_peak_gbs()
+    rank_gbs, both_gbs, eval_gbs = n_hands * 18 / ms_rank * 1e-6, m * 26520 / ms_both * 1e-6, m * 21216 / ms_eval * 1e-6
+    return {
+        "workload": f"{m} river boards x 2 Dirichlet(1) ranges (larger than L2); 2^{log2_hands} seven-card hands",
+        "showdown": {"evals_per_s": 2 * m / (ms_both / 1e3), "ms": ms_both, "launches_timed": 2 * n_both,
+                     "kernels": "board_setup_kernel + showdown_eval_kernel", "algorithmic_bytes_per_board": 26520,
+                     "achieved_gbs": both_gbs, "frac": both_gbs / peak},
+        "showdown_eval_only": {"evals_per_s": 2 * m / (ms_eval / 1e3), "ms": ms_eval, "launches_timed": n_eval,
+                               "algorithmic_bytes_per_board": 21216, "achieved_gbs": eval_gbs, "frac": eval_gbs / peak},
+        "rank7": {"hands_per_s": n_hands / (ms_rank / 1e3), "ms": ms_rank, "launches_timed": n_rank,
+                  "algorithmic_bytes_per_hand": 18, "achieved_gbs": rank_gbs, "frac": rank_gbs / peak},
+        "clocks": clocks,
+    }
 
 
 def run_micro(args):
@@ -514,6 +681,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the micro, without_weight_sums and strong members (profiling runs)")
     ap.add_argument("--batch", type=int, default=BATCH, help="subgames per GPU (default: the headline 4096)")
     ap.add_argument("--iterations", type=int, default=ITERATIONS, help="DCFR iterations (default: 256)")
     ap.add_argument("--workload", default="river", choices=["river", "micro", "turn", "flop"],

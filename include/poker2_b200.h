@@ -120,6 +120,12 @@ int64_t p2b_cfr_scratch_floats(int32_t max_internal, int32_t num_blocks);
 int64_t p2b_cfr_solve_scratch_floats(int32_t max_internal, int32_t max_children, int32_t num_blocks,
                                      int32_t num_subgames, int64_t rows);
 int p2b_cfr_default_blocks(void);
+/* Measurement aid (no counterpart in the upstream project): with timing enabled on the current
+ * device, a p2b_cfr_solve that runs its iteration passes in the lean kernel brackets that one
+ * launch with CUDA events on the caller's stream; p2b_cfr_iteration_ms waits for it and writes
+ * its duration in milliseconds to the HOST float *ms. */
+int p2b_cfr_iteration_timing(int32_t enable);
+int p2b_cfr_iteration_ms(float* ms);
 
 /* p2b_cfr_step -- part of a solve, for subgames whose non-terminal leaves (start of the next
  * street, depth limit) are valued by the caller's model (set_leaf_values,

@@ -68,6 +68,13 @@ int p2b_showdown_values(const unsigned char* tables, const int32_t* table_of_row
 
 int p2b_cfr_default_blocks(void) { return cfr_default_blocks(); }
 
+int p2b_cfr_iteration_timing(int32_t enable) { return cfr_iteration_timing(enable); }
+
+int p2b_cfr_iteration_ms(float* ms) {
+    P2B_REQUIRE(ms != nullptr, "null pointer");
+    return cfr_iteration_ms(ms);
+}
+
 int64_t p2b_cfr_scratch_floats(int32_t max_internal, int32_t num_blocks) {
     if (num_blocks <= 0) num_blocks = cfr_default_blocks();
     return cfr_scratch_floats(max_internal) * num_blocks;

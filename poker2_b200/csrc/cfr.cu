@@ -1348,6 +1348,43 @@ int launch_cfr_warm_seed(const NodeRec* nodes, long long rows, const float* star
     return check_cuda(cudaGetLastError(), "cfr_warm_seed_kernel");
 }
 
+// ---- optional timing of the iteration kernel of a split solve (for benchmarks) ----------------
+namespace {
+struct IterTiming {
+    bool enabled = false;
+    bool recorded = false;
+    cudaEvent_t start = nullptr, stop = nullptr;
+};
+IterTiming g_iter_timing[64];
+IterTiming* iter_timing_of_current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    return &g_iter_timing[dev];
+}
+}  // namespace
+
+int cfr_iteration_timing(int enable) {
+    IterTiming* t = iter_timing_of_current_device();
+    if (!t) return set_error(P2B_ERR_STATE, "no current device");
+    if (enable && !t->start) {
+        int rc = check_cuda(cudaEventCreate(&t->start), "cudaEventCreate");
+        if (rc) return rc;
+        rc = check_cuda(cudaEventCreate(&t->stop), "cudaEventCreate");
+        if (rc) return rc;
+    }
+    t->enabled = enable != 0;
+    t->recorded = false;
+    return P2B_OK;
+}
+
+int cfr_iteration_ms(float* ms) {
+    IterTiming* t = iter_timing_of_current_device();
+    if (!t || !t->recorded) return set_error(P2B_ERR_STATE, "no timed iteration kernel has run on this device");
+    int rc = check_cuda(cudaEventSynchronize(t->stop), "cudaEventSynchronize");
+    if (rc) return rc;
+    return check_cuda(cudaEventElapsedTime(ms, t->start, t->stop), "cudaEventElapsedTime");
+}
+
 static int clear_counters(int32_t* work_counter, cudaStream_t stream) {
     // [0] subgame queue, [1] status, [2], [3] spare
     return check_cuda(cudaMemsetAsync(work_counter, 0, 4 * sizeof(int32_t), stream), "cudaMemsetAsync(work counter)");
@@ -1397,7 +1434,14 @@ int launch_cfr_solve(const CfrParams& params, int num_blocks, int max_children, 
             cfr_validate_kernel<<<q.num_subgames, kCfrMaxNodes, 0, stream>>>(q);
             rc = check_cuda(cudaGetLastError(), "cfr_validate_kernel");
             if (rc) return rc;
+            IterTiming* timing = iter_timing_of_current_device();
+            const bool timed = timing && timing->enabled;
+            if (timed) cudaEventRecord(timing->start, stream);
             rc = launch_cfr_iter(q, num_blocks, stream);
+            if (timed) {
+                cudaEventRecord(timing->stop, stream);
+                timing->recorded = true;
+            }
         } else {
             rc = dispatch_cfr(q, num_blocks, max_children, stream);
         }

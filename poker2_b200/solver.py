@@ -246,6 +246,24 @@ class SolveResult:
         torch.cuda.current_stream(self.root_values.device).synchronize()
         return pinned
 
+    def to_host_async(self, pinned: dict, copy_stream: "torch.cuda.Stream"):
+        """Starts the copy of the training targets to pinned host memory on `copy_stream`, after the
+        work already queued on the current stream; returns (pinned, event).  The targets are on the
+        host once the event has completed; this object must stay alive until then.  Lets the copy of
+        one batch run while the next batch is being solved."""
+        dev = self.root_values.device
+        ready = torch.cuda.Event()
+        ready.record(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(ready)
+            for name, src in (("root_values", self.root_values), ("policy_avg", self.policy_avg)):
+                if name not in pinned or pinned[name].shape != src.shape:
+                    pinned[name] = torch.empty(src.shape, dtype=src.dtype, pin_memory=True)
+                pinned[name].copy_(src, non_blocking=True)
+            done = torch.cuda.Event()
+            done.record(copy_stream)
+        return pinned, done
+
     def level_major(self, x: torch.Tensor) -> torch.Tensor:
         return x.index_select(0, layout_tensor(self.layout, "from_level_major", x.device))[..., :NUM_HANDS]
 
@@ -332,10 +350,11 @@ class SubgameSolver:
             setattr(self, name, None)
 
     def solve(self, root_beliefs: torch.Tensor, scalars: np.ndarray, *, cfr_plus: bool = False,
-              enforce_zero_sum: bool = False) -> SolveResult:
+              enforce_zero_sum: bool = False, check: bool = False) -> SolveResult:
         """root_beliefs: [B,2,1344] fp32 on the device (padded).  Enqueues the solve (one to three
         kernels).  enforce_zero_sum: shift the value outputs to zero sum, as upstream does when
-        `model.enforce_zero_sum` is set (cfr_evaluator.py:957-980, 1289-1292)."""
+        `model.enforce_zero_sum` is set (cfr_evaluator.py:957-980, 1289-1292).  check: read the
+        status word afterwards (synchronises) and raise if the record check refused the batch."""
         assert root_beliefs.shape == (self.B, 2, HPAD) and root_beliefs.dtype == torch.float32
         assert root_beliefs.is_contiguous() and root_beliefs.device == self.device
         iterations = int(scalars.shape[0])
@@ -354,7 +373,14 @@ class SubgameSolver:
                 self.num_blocks, p(self.sample_pass), p(self.policy_sample), p(self.beliefs_last),
                 _lib.stream_ptr(self.device))
         self.launches += 1
+        if check:
+            self.raise_if_refused()
         return self._result()
+
+    def raise_if_refused(self) -> None:
+        st = self.status()
+        if st != 0:
+            raise RuntimeError(f"subgame {st - 1}: tree records exceed the solver's limits; nothing was solved")
 
 
 class SteppedSolver(SubgameSolver):
@@ -469,6 +495,19 @@ def solve_noalloc(sv: SubgameSolver, root_beliefs: torch.Tensor, scalars_dev: to
             _lib.stream_ptr(sv.device))
     return SolveResult(sv.layout, sv.policy_avg, sv.regrets, sv.weight_sums, sv.policy, sv.root_values,
                        sv.values_avg, sv.beliefs_avg, sv.exploitability, sv.br_values)
+
+
+def noalloc_status(device) -> int:
+    """Verdict of the record check of the last `solve_noalloc` on `device`: 0, or 1 + the index of a
+    subgame whose records were refused (that call then solved nothing).  Waits for the current
+    stream; allocates nothing on the device."""
+    import ctypes
+
+    device = torch.device(device)
+    out = ctypes.c_int32(-1)
+    with torch.cuda.device(device):
+        _lib.call("p2b_cfr_noalloc_status", ctypes.byref(out), _lib.stream_ptr(device))
+    return int(out.value)
 
 
 def solve_subgames(boards, ranges, pot, stacks, *, iterations: int, bet_bins=(0.5, 1.0), max_depth: int = 8,

@@ -193,6 +193,32 @@ def test_malformed_subgame_is_reported_and_nothing_runs(cuda_device, golden_dir)
     assert ok.status() == 0 and torch.equal(res2.root_values, clean.root_values)
 
 
+def test_malformed_subgame_is_refused_at_every_step(cuda_device, golden_dir):
+    """Stepped solves check the records at every launch: the status survives the whole solve, no
+    step follows the malformed records, outputs stay untouched; `check=True` raises."""
+    from poker2_b200 import solver
+
+    z = np.load(os.path.join(golden_dir, "cfr_batch_cap2_t24.npz"))
+    _, trees = _solve_golden(z, cuda_device)
+    boards = torch.from_numpy(z["boards"].astype(np.int64))
+    layout = solver.device_layout(trees, z["boards"].astype(np.int64))
+    victim = 1
+    layout.nodes[int(layout.subgames[victim]["node_begin"])]["n_children"] = 9
+    rb = solver.pad_rows(torch.from_numpy(z["ranges"]).to(cuda_device)).contiguous()
+    sv = solver.SteppedSolver(layout, boards, cuda_device)
+    sv.root_values.fill_(-7.0)
+    sv.regrets.fill_(-7.0)
+    res = sv.solve(rb, solver.iteration_scalars(4))
+    assert sv.status() == victim + 1
+    assert bool((res.root_values == -7.0).all()) and bool((res.regrets == -7.0).all())
+    # a step that does not begin at the start pass is checked too
+    sv._step(rb, sv._scalars, 4, 0, 2, 2, 3)
+    assert sv.status() == victim + 1 and bool((sv.regrets == -7.0).all())
+    one = solver.SubgameSolver(layout, boards, cuda_device)
+    with pytest.raises(RuntimeError, match="subgame 1"):
+        one.solve(rb, solver.iteration_scalars(4), check=True)
+
+
 def test_depth_limited_tree_and_empty_inputs(cuda_device, golden_dir):
     """A tree cut at depth 2 has non-terminal leaves; without a leaf model they are worth zero,
     in the kernel as in the oracle.  Empty batches are accepted everywhere."""

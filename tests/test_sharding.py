@@ -59,3 +59,64 @@ def test_single_process_is_identity():
     assert sharding.gather_rows(x) is x
     stats = sharding.reduce_exploitability(torch.tensor([0.25, 0.75]))
     assert stats["local_exploitability"] == 0.5 and stats["count"] == 2
+
+
+def _worker_mismatch(rank, world, port, result_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        local = torch.zeros(3, 2, 16 if rank == 0 else 8)  # rank 1 holds rows of another width
+        try:
+            sharding.gather_rows(local)
+            outcome = "gathered"
+        except ValueError as e:
+            outcome = "raised" if "disagree" in str(e) else "other"
+        with open(os.path.join(result_dir, f"mismatch{rank}.txt"), "w") as fh:
+            fh.write(outcome)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_shards_of_different_width_raise_on_every_rank(tmp_path):
+    mp.spawn(_worker_mismatch, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        assert open(tmp_path / f"mismatch{r}.txt").read() == "raised"
+
+
+def _worker_leaver(rank, world, port, result_dir):
+    """Rank 1 leaves between steps, before the final gather; rank 0 must not wait for ever."""
+    import datetime
+    import time
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    full = torch.rand(4, 2, 16, generator=torch.Generator().manual_seed(5))
+    lo, hi = sharding.shard_bounds(4, rank, world)
+    first = sharding.gather_rows(full[lo:hi].clone())  # a step in which both ranks take part
+    if rank == 1:
+        os._exit(0)  # gone: no destroy, no further collective
+    t0 = time.perf_counter()
+    try:
+        sharding.gather_rows(full[lo:hi].clone())
+        outcome = "gathered"
+    except Exception as e:  # the process group reports the missing peer (timeout or closed connection)
+        outcome = f"raised {type(e).__name__}"
+    waited = time.perf_counter() - t0
+    with open(os.path.join(result_dir, "leaver0.txt"), "w") as fh:
+        fh.write(f"{outcome}|{torch.equal(first, full)}|{waited:.1f}")
+    os._exit(0)  # the group is broken; skip its teardown
+
+
+def test_a_rank_that_leaves_before_the_gather_makes_the_others_raise(tmp_path):
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_leaver, args=(r, 2, port, str(tmp_path))) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=60)
+        assert not p.is_alive()
+    outcome, first_ok, waited = open(tmp_path / "leaver0.txt").read().split("|")
+    assert outcome.startswith("raised") and first_ok == "True" and float(waited) < 30
