@@ -68,12 +68,18 @@ class SubgameEvaluator:
                  dcfr_delay: int = 0, cfr_plus: bool = False, max_raises=None, model=None,
                  chance_average: bool = True, leaf_chunk: int = 2048, sample_epsilon: float = 0.25,
                  generator: torch.Generator | None = None, warm_start_iterations: int = 0,
-                 warm_start_multiplier: float = 1.0):
+                 warm_start_multiplier: float = 1.0, alpha_final: float | None = None,
+                 beta_final: float | None = None, gamma_final: float | None = None,
+                 enforce_zero_sum: bool = False):
         self.device = torch.device(device)
         self.cfr_iterations = int(iterations)
         self.bet_bins, self.max_depth, self.bb, self.max_raises = list(bet_bins), max_depth, bb, max_raises
         self.cfr_type, self.alpha, self.beta, self.gamma = cfr_type, alpha, beta, gamma
         self.dcfr_delay, self.cfr_plus = dcfr_delay, cfr_plus
+        # exponent schedules (`apply_schedules`, cfr_evaluator.py:1294-1329) and the zero-sum shift of the
+        # value targets upstream applies when `model.enforce_zero_sum` is set (:957-980, 1289-1292)
+        self.alpha_final, self.beta_final, self.gamma_final = alpha_final, beta_final, gamma_final
+        self.enforce_zero_sum = bool(enforce_zero_sum)
         self.model, self.chance_average, self.leaf_chunk = model, chance_average, leaf_chunk
         self.sample_epsilon = sample_epsilon
         self.generator = generator
@@ -147,19 +153,30 @@ class SubgameEvaluator:
         self.t_sample = t_sample
         self.solver.set_sampling_schedule(t_sample.to(self.device), warm_start_iterations=ws)
         scal = psolver.iteration_scalars(T, cfr_type=self.cfr_type, alpha=self.alpha, beta=self.beta,
-                                         gamma=self.gamma, dcfr_delay=self.dcfr_delay)
+                                         gamma=self.gamma, dcfr_delay=self.dcfr_delay, alpha_final=self.alpha_final,
+                                         beta_final=self.beta_final, gamma_final=self.gamma_final,
+                                         warm_start_iterations=ws)
         if self.stepped:
             if ws > 0 and start_policy is None:  # uniform over the children of every parent
                 cc = torch.from_numpy(self.trees.child_count[self.trees.parent_index.clip(min=0)]).clamp(min=1)
                 start_policy = (1.0 / cc.to(torch.float32))[:, None].expand(-1, NUM_HANDS).contiguous()
+            first = None
+            if ws > 0:
+                first = psolver.warm_start_mix_scalars(scal, cfr_type=self.cfr_type, gamma=self.gamma,
+                                                       dcfr_delay=self.dcfr_delay, warm_start_iterations=ws)
             res = self.solver.solve(self.root_beliefs, scal, self.leaf_fn, cfr_plus=self.cfr_plus,
-                                    start_policy=start_policy, warm_start_iterations=ws,
-                                    warm_start_multiplier=self.warm_start_multiplier)
+                                    enforce_zero_sum=self.enforce_zero_sum, start_policy=start_policy,
+                                    warm_start_iterations=ws, warm_start_multiplier=self.warm_start_multiplier,
+                                    warm_start_scalars=first)
         else:
             if start_policy is not None:
                 raise ValueError("a start policy needs the stepped solver (set warm_start_iterations or use model leaves)")
-            res = self.solver.solve(self.root_beliefs, scal, cfr_plus=self.cfr_plus)
+            res = self.solver.solve(self.root_beliefs, scal, cfr_plus=self.cfr_plus,
+                                    enforce_zero_sum=self.enforce_zero_sum)
         self._result = res
+        from . import stats as pstats
+
+        self.stats.update(pstats.evaluator_stats(res, self.trees, self.boards))
         # the walk draws from the generator: run it where the generator lives
         pol = res.level_major(res.policy_sample).to(gen_device)
         bel = res.level_major(res.beliefs_last).to(gen_device)
@@ -254,7 +271,10 @@ class SubgameEvaluator:
         st = t.state
         as_t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)  # noqa: E731
         statistics = {"to_act": as_t(st.to_act), "street": as_t(st.street), "stage": as_t(2 * st.street),
-                      "board": as_t(self.boards[t.root_of]), "pot": as_t(st.pot), "bet_amounts": as_t(amounts)}
+                      "board": as_t(self.boards[t.root_of]), "pot": as_t(st.pot), "bet_amounts": as_t(amounts),
+                      # inputs of the feature context (rebel_feature_encoder.py:96-113)
+                      "button": as_t(st.button), "total_starting": as_t(st.starting_stacks.sum(axis=1).astype(np.float32)),
+                      "has_bet": as_t((st.committed[:, 0] != st.committed[:, 1]) & (st.actions_this_round > 0))}
         legal_t = as_t(legal)
         value_stats = {k: v[:N] for k, v in statistics.items()}
         value_stats["local_exploitability"] = res.exploitability
