@@ -183,6 +183,7 @@ if __name__ == "__main__":
     try:
         import golden_cfr  # noqa: F401  (registers the tree and cfr sections)
 
+        import golden_replay  # noqa: F401  (registers replay)
         import golden_rounds  # noqa: F401  (registers rounds)
         import golden_settings  # noqa: F401  (registers production, standard, zero_sum, ragged256)
 
