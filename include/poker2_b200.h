@@ -80,7 +80,7 @@ int p2b_showdown_values(const unsigned char* tables, const int32_t* table_of_row
  *  rows       number of rows of the state arrays (the record check refuses subgames that reach past it)
  *  scratch    at least p2b_cfr_scratch_floats(max_internal, num_blocks) floats of work space.  With
  *             p2b_cfr_solve_scratch_floats(max_internal, max_children, num_blocks, num_subgames, rows)
- *             floats a solve without the optional outputs policy / policy_sample / beliefs_last runs as
+ *             floats the solve runs as
  *             three launches (start pass; iteration passes in a leaner kernel; final pass) with the same
  *             results, bit for bit; the extra floats carry the root rows between the launches
  *  scalars    [iterations] 32-byte records {float t^alpha, t^alpha+1, t^beta, t^beta+1,
@@ -347,6 +347,11 @@ int p2b_indexed_add_rows(float* out, const int64_t* index, const float* src, int
  * sequence to *short_path (device pointers, cleared by the caller). */
 int p2b_selftest_division(uint64_t num_pairs, uint32_t seed, unsigned long long* mismatches,
                           unsigned long long* short_path, void* stream);
+/* Directed form: all 2^23 divisor mantissas at five exponents (both ends of the valid range
+ * included), each against 16 numerators placed on rounding boundaries (1, the largest mantissa, the
+ * divisor one ulp up and down, its mirrored mantissa, a neighbouring exponent, pseudo-random ones).
+ * ADDS the differing results to *mismatches and the quotients compared to *checked. */
+int p2b_selftest_division_sweep(unsigned long long* mismatches, unsigned long long* checked, void* stream);
 
 #ifdef __cplusplus
 }

@@ -65,6 +65,7 @@ _SIGNATURES = {
     "p2b_tree_count": [_vp, _i32, _vp, _i32, _i32, _i32, _vp, _vp, _vp],
     "p2b_tree_records": [_vp, _vp, _i32, _i32, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "p2b_selftest_division": [ctypes.c_uint64, ctypes.c_uint32, _vp, _vp, _vp],
+    "p2b_selftest_division_sweep": [_vp, _vp, _vp],
 }
 # functions whose return value is a quantity, not a status code
 _VALUE_FUNCS = {"p2b_cfr_scratch_floats": ([_i32, _i32], _i64), "p2b_cfr_default_blocks": ([], _i32),

@@ -44,21 +44,28 @@ def build(force: bool = False, verbose: bool = False) -> str:
     build_dir = os.path.join(PKG_DIR, "build")
     os.makedirs(build_dir, exist_ok=True)
     nvcc = nvcc_path()
+    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
+    headers.append(os.path.join(PKG_DIR, "..", "include", "poker2_b200.h"))
+    newest_header = max(os.path.getmtime(h) for h in headers)
     procs = []
     for src in SOURCES:
         obj = os.path.join(build_dir, src.replace(".cu", ".o"))
-        cmd = [nvcc, *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
+        objs.append(obj)
+        src_path = os.path.join(CSRC, src)
+        # an object is reused when it is newer than its source and than every header
+        if not force and os.path.exists(obj) and os.path.getmtime(obj) > max(os.path.getmtime(src_path), newest_header):
+            continue
+        cmd = [nvcc, *NVCC_FLAGS, "-c", src_path, "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
-        objs.append(obj)
     for src, p in procs:
         out, _ = p.communicate()
         if verbose or p.returncode != 0:
             sys.stderr.write(out)
         if p.returncode != 0:
             raise RuntimeError(f"nvcc failed on {src}")
-    cmd = [nvcc, "-shared", "-o", LIB_PATH, *objs]
+    cmd = [nvcc, "-shared", "-Wno-deprecated-gpu-targets", "-o", LIB_PATH, *objs]
     subprocess.run(cmd, check=True)
     return LIB_PATH
 

@@ -1405,8 +1405,8 @@ int launch_cfr_solve(const CfrParams& params, int num_blocks, int max_children, 
     if (rc) return rc;
     CfrParams p = params;
     p.combos = device_combo_table();
-    const bool plain = !p.stepped && !p.leaf_beliefs && !p.leaf_values && !p.policy_sample && !p.beliefs_last &&
-                       !p.policy && !p.start_policy;
+    // leaves all terminal, uniform start policy, all passes in this call: the iteration kernel applies
+    const bool plain = !p.stepped && !p.leaf_beliefs && !p.leaf_values && !p.start_policy;
     if (!(plain && fast_scratch && max_children <= kCfrMaxChildren)) {
         rc = clear_counters(p.work_counter, stream);
         if (rc) return rc;

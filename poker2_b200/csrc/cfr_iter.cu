@@ -1,4 +1,4 @@
-// Iteration passes of a plain subgame solve (no model leaves, no optional outputs): the lean
+// Iteration passes of a subgame solve whose leaves are all terminal (no model leaves, no start policy): the lean
 // copy of the two sweeps of cfr.cu, used for the passes 0..iterations-1 between the start pass
 // and the final pass, which stay in cfr_solve_kernel.  Same arithmetic, bit for bit; what
 // differs is how the work is laid out on the SM:
@@ -81,35 +81,6 @@ static_assert(!kDownAsync || (kDownRows + 2 * kK) * P2B_HPAD * 4 <= kOffSig - kO
 
 constexpr uint8_t kNoRow = 0xFF;
 
-// ---- short division with a cheap range check ---------------------------------------------
-// The quotient sequence of exactdiv.cuh is valid for numerators that are zero or lie in
-// [2^-60, 2^60).  Instead of testing each numerator, a group of quotients keeps the smallest
-// (bits - 1) and the largest bits of its numerators (zero wraps to the largest value and so
-// passes the lower bound); one comparison pair at the end of the group decides whether the
-// whole group is redone with IEEE divisions.
-struct DivGuard {
-    unsigned lo, hi;
-    bool dok;  // every divisor of the group is inside the valid range
-};
-constexpr unsigned kDivLo = 67u << 23, kDivHi = 187u << 23;
-__device__ __forceinline__ DivGuard guard_begin(bool divisors_ok) { return DivGuard{0xffffffffu, 0u, divisors_ok}; }
-__device__ __forceinline__ bool guard_bad(const DivGuard& g) { return !g.dok || g.hi >= kDivHi || g.lo < kDivLo - 1u; }
-
-// NONNEG: the numerator is +0 or positive (anything else is reported through the guard); the
-// sequence itself then returns +0 for a zero numerator.  Otherwise a zero numerator returns
-// x * r, which carries the sign IEEE division gives.
-template <bool NONNEG>
-__device__ __forceinline__ float div_g(float x, float y, float r, DivGuard& g) {
-    const float q = __fmul_rn(x, r);
-    const float e = __fmaf_rn(-q, y, x);
-    const float q2 = __fmaf_rn(e, r, q);
-    const unsigned b = NONNEG ? __float_as_uint(x) : (__float_as_uint(x) & 0x7fffffffu);
-    g.lo = min(g.lo, b - 1u);
-    g.hi = max(g.hi, b);
-    if (NONNEG) return q2;
-    return b == 0u ? q : q2;
-}
-
 // Hands of a thread: two consecutive ones (64-bit accesses), or three a third of a row apart
 // (32-bit accesses, consecutive threads on consecutive hands).
 template <int VPT>
@@ -173,6 +144,7 @@ struct IterBlock {
     SubgameRec sg;
     float* scr;
     int max_internal;
+    int sample_pass;  // pass whose policy is the sampling policy of the current subgame (-2: none)
     // work rows of the block: per internal node one reach row, one average-reach row and the values of
     // both players; then one current-policy row per node
     __device__ __forceinline__ float* row_reach(int x) const { return scr + (long long)(x * 4) * P2B_HPAD; }
@@ -281,6 +253,8 @@ __device__ __forceinline__ void iter_down(int pass, const CfrParams& p, IterBloc
                                           const float* __restrict__ cr, int tid) {
     const IterScalars sc = p.scalars[pass];
     const bool mix = sc.do_mix != 0;
+    const bool keep_policy = p.policy != nullptr && pass == p.iterations - 1;
+    const bool keep_sample = p.policy_sample != nullptr && pass == B.sample_pass;
     FV<VPT> mask;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) mask.v[i] = hi.allowed[i] ? 1.0f : 0.0f;
@@ -354,6 +328,9 @@ __device__ __forceinline__ void iter_down(int pass, const CfrParams& p, IterBloc
                 }
             }
             const NodeRec ch = B.nodes[fc + c];
+            // optional outputs: the current policy of the last iteration and of the subgame's sampling pass
+            if (keep_policy) sth<VPT>(B.state_row(p.policy, fc + c), tid, P);
+            if (keep_sample) sth<VPT>(B.state_row(p.policy_sample, fc + c), tid, P);
             FV<VPT> t;
 #pragma unroll
             for (int i = 0; i < VPT; ++i) t.v[i] = __fmul_rn(ra.v[i], P.v[i]);
@@ -604,6 +581,10 @@ __device__ __forceinline__ void iter_up_stage(int pass, const CfrParams& p, Iter
     }
     sth<VPT>(B.set_row(set, 0), tid, b_a);
     sth<VPT>(B.set_row(set, 1), tid, b_o);
+    if (p.beliefs_last && pass == p.iterations - 1) {  // optional output: what leaf sampling continues from
+        sth<VPT>(p.beliefs_last + ((long long)(B.sg.node_begin + j) * 2 + a) * P2B_HPAD, tid, b_a);
+        sth<VPT>(p.beliefs_last + ((long long)(B.sg.node_begin + j) * 2 + o) * P2B_HPAD, tid, b_o);
+    }
     const int sd = B.sdc[ii];
 #pragma unroll 1
     for (int c = 0; c < k; ++c) {
@@ -881,6 +862,7 @@ __global__ void __launch_bounds__(kNT, kCtas) cfr_iter_kernel(const CfrParams p)
         const int s = B.misc[0];
         if (s >= p.num_subgames) break;
         B.sg = p.subgames[s];
+        B.sample_pass = p.sample_pass ? p.sample_pass[s] : -2;
         {
             const uint4* src = reinterpret_cast<const uint4*>(p.nodes + B.sg.node_begin);
             for (int i = tid; i < B.sg.n_nodes; i += NT) reinterpret_cast<uint4*>(B.nodes)[i] = src[i];
