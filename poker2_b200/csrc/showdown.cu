@@ -503,13 +503,15 @@ __global__ void __launch_bounds__(kEvalThreads, 2) showdown_eval_kernel(
         float* vrow = values + row * value_row_stride;
         const float pot0 = (float)potential[row * 2], pot1 = (float)potential[row * 2 + 1];
         const Divisor dscale = make_divisor(scale[row]);
-        for (int i = tid; i < 2 * P2B_NUM_HANDS; i += kEvalThreads) {
-            const int hero = i >= P2B_NUM_HANDS, h = i - hero * P2B_NUM_HANDS, opp = 1 - hero;
+        // a thread takes a hand for both players: cards, board check and the hand's record are shared
+        for (int h = tid; h < P2B_NUM_HANDS; h += kEvalThreads) {
             const int c1 = c1s[h], c2 = c2s[h];
             const bool allowed = (((bmask >> c1) | (bmask >> c2)) & 1ull) == 0;
-            const float ev = showdown_hand_ev(tv.rec[h], c1, c2, x[opp * P2B_NUM_HANDS + h], allowed, P + opp * P2B_HPAD,
-                                              PC + opp * 52 * 52);
-            __stcs(vrow + i, div_exact(__fmul_rn(ev, hero ? pot1 : pot0), dscale));
+            const HandRec r = tv.rec[h];
+            const float ev0 = showdown_hand_ev(r, c1, c2, x[P2B_NUM_HANDS + h], allowed, P + P2B_HPAD, PC + 52 * 52);
+            const float ev1 = showdown_hand_ev(r, c1, c2, x[h], allowed, P, PC);
+            __stcs(vrow + h, div_exact(__fmul_rn(ev0, pot0), dscale));
+            __stcs(vrow + P2B_NUM_HANDS + h, div_exact(__fmul_rn(ev1, pot1), dscale));
         }
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");

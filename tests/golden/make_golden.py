@@ -185,6 +185,7 @@ if __name__ == "__main__":
 
         import golden_replay  # noqa: F401  (registers replay)
         import golden_rounds  # noqa: F401  (registers rounds)
+        import golden_steps  # noqa: F401  (registers steps)
         import golden_settings  # noqa: F401  (registers production, standard, zero_sum, ragged256)
 
         SECTIONS.update(golden_cfr.SECTIONS)
