@@ -117,3 +117,24 @@ def test_evaluator_on_flop_subgames_with_network_leaves(cuda_device):
     assert (pre_batch.statistics["board"].cpu().numpy() == -1).all()  # no board before the flop
     for t in (value_batch.value_targets, pre_batch.value_targets, policy_batch.policy_targets):
         assert torch.isfinite(t).all()
+    # against the CPU oracle running the same network (fp32 GEMMs in another summation order, three
+    # iterations of amplification: 1e-3; the solver alone is held to 1e-5 in test_gpu_leaf_eval.py)
+    from oracle import cfr as ocfr, chance as ochance
+
+    cpu_model = leaf_eval.ValueMLP(width=64, depth=2, dtype=torch.float32, seed=2)
+    trees = ev.trees
+    root_of = torch.from_numpy(trees.root_of)
+
+    def leaf_fn(beliefs, idx):
+        ctx = leaf_eval.leaf_context(trees, idx.numpy())
+        return ochance.single_card_chance_values(
+            beliefs, boards[root_of[idx]], lambda post, samples, lookup: cpu_model(post, samples, ctx[lookup]))
+
+    o = ocfr.SubgameOracle(trees.oracle_dict(boards.numpy()), ranges, iterations=3, leaf_fn=leaf_fn).solve()
+    torch.testing.assert_close(value_batch.value_targets.cpu(), o.values_avg[:n].clamp(-1, 1), rtol=1e-3, atol=1e-5)
+    top = trees.depth_offsets[-2]
+    A = trees.num_actions
+    by_src = torch.zeros(top, A, 1326)
+    by_src[torch.from_numpy(trees.parent_index[n:]), torch.from_numpy(trees.action_from_parent[n:])] = o.policy_avg[n:]
+    keep = torch.from_numpy(~trees.leaf_mask[:top])
+    torch.testing.assert_close(policy_batch.policy_targets.cpu(), by_src.permute(0, 2, 1)[keep], rtol=1e-3, atol=1e-4)
