@@ -90,7 +90,12 @@ int p2b_showdown_values(const unsigned char* tables, const int32_t* table_of_row
  *             sum, per node minus the mean over the players of sum_h values * beliefs_avg, except at
  *             terminal nodes -- what upstream does when model.enforce_zero_sum is set
  *             (_maybe_enforce_zero_sum :957-980 at the end of update_average_values_final :1289-1292);
- *             the best responses then start from the shifted leaf values, as upstream
+ *             the best responses then start from the shifted leaf values, as upstream;
+ *             bit 2: `cfr_avg` upstream (cfr_evaluator.py:1029, :1133): in the iteration passes the showdown
+ *             values, the regret weights and the leaf_beliefs handed to the caller's model are taken at the
+ *             beliefs under the average policy instead of the current one (the de-averaging of the model's
+ *             values, :997-1018, is the caller's part of set_leaf_values); such a solve keeps every pass in
+ *             the general kernel
  *  init_depth depth of the deepest tree of the batch (the upstream start pass re-normalises
  *             every belief row once per level of the batch-wide tree)
  *  work_counter four int32, zeroed by the call: [0] the queue the thread blocks take subgames
@@ -138,7 +143,7 @@ int p2b_cfr_iteration_ms(float* ms);
  * step(pass, 2); }.  Arrays as in p2b_cfr_solve, plus state carried between calls:
  *  scratch      p2b_cfr_scratch_floats(max_internal, 1) * num_subgames floats (one set of
  *               work rows per subgame instead of per block)
- *  carry_sums   [rows,2] floats, carry_roots [num_subgames,4,1344] floats (opaque)
+ *  carry_sums   [rows,2] floats ([2,rows,2] with flags bit 2), carry_roots [num_subgames,4,1344] floats (opaque)
  *  leaf_begin   [num_subgames] int32: first leaf slot of each subgame; a node of kind 3 uses
  *               slot leaf_begin[subgame] + its internal_idx field; leaf_slots = number of slots
  *  leaf_beliefs [slots,2,1344] out (top-down sweep): both players' beliefs at each such leaf
@@ -256,7 +261,9 @@ int p2b_step_update_average_values(float* values_avg, const float* latest, const
                                    const float* inv_total, int64_t n, void* stream);
 /* fused_avg_values_zero_sum_ (:623-668) with subtract_b=0, scale=1/(old+new);
  * fused_model_values_mix_zero_sum (:1739-1775) with subtract_b=1, scale=NULL:
- * out = (a*coef_a +/- b*coef_b) [*scale] - 0.5*sum_p sum_h out*beliefs (rows of [2,H]) */
+ * out = (a*coef_a +/- b*coef_b) [*scale] - 0.5*sum_p sum_h out*beliefs (rows of [2,H]).
+ * enforce_zero_sum: 0 = no shift; 1 = the sum accumulated in fp64; 2 (H = 1326) = two fp32 sums in the
+ * order of the CPU row reduction the non-fused upstream code goes through (cfr_evaluator.py:973-976) */
 int p2b_step_mix_zero_sum(const float* a, const float* b, const float* beliefs, const uint8_t* ignore,
                           const float* coef_a, const float* coef_b, const float* scale, float* out, int64_t rows,
                           int32_t H, int subtract_b, int enforce_zero_sum, void* stream);

@@ -36,7 +36,7 @@ class SubgameOracle:
                  start_policy: torch.Tensor | None = None, warm_start_iterations: int = 0,
                  warm_start_multiplier: float = 1.0, alpha_final: float | None = None,
                  beta_final: float | None = None, gamma_final: float | None = None,
-                 enforce_zero_sum: bool = False):
+                 enforce_zero_sum: bool = False, cfr_avg: bool = False):
         t = {k: (torch.from_numpy(np.ascontiguousarray(v)) if isinstance(v, np.ndarray) else v)
              for k, v in tree.items()}
         self.offs = [int(x) for x in tree["depth_offsets"]]
@@ -60,6 +60,11 @@ class SubgameOracle:
         self.alpha0, self.beta0, self.gamma0 = alpha, beta, gamma
         self.alpha_final, self.beta_final, self.gamma_final = alpha_final, beta_final, gamma_final
         self.enforce_zero_sum = enforce_zero_sum
+        # `cfr_avg` upstream (cfr_evaluator.py:997-1018, :1029, :1133): leaf values and regret weights come
+        # from the beliefs under the AVERAGE policy, and from the second iteration on the model's leaf
+        # values are taken as a running average and de-averaged
+        self.cfr_avg = cfr_avg
+        self.last_model_values = None
         self.dcfr_delay = dcfr_delay
         self.cfr_type = cfr_type
         self.cfr_plus = cfr_plus
@@ -187,10 +192,22 @@ class SubgameOracle:
         self.values_avg[:] = self.values
 
     # ---- leaves and backup ----
-    def set_leaf_values(self, beliefs=None):
-        beliefs = self.beliefs if beliefs is None else beliefs
+    def set_leaf_values(self, t=0, beliefs=None):
+        if beliefs is None:
+            beliefs = self.beliefs_avg if self.cfr_avg else self.beliefs
         if self.model_idx.numel() and self.leaf_fn is not None:
-            self.values[self.model_idx] = self.leaf_fn(beliefs[self.model_idx], self.model_idx).float()
+            b = beliefs[self.model_idx]
+            hv = self.leaf_fn(b, self.model_idx).float()
+            if not self.cfr_avg or t <= 1 or self.last_model_values is None:
+                self.values[self.model_idx] = hv
+            else:  # the model's output is the average over the iterations so far: recover this iteration's
+                old, new = self.mixing_weights(t)
+                unmixed = (old + new) * hv - old * self.last_model_values
+                unmixed /= new
+                if self.enforce_zero_sum:
+                    unmixed = unmixed - (unmixed * b).sum(dim=2, keepdim=True).mean(dim=1, keepdim=True)
+                self.values[self.model_idx] = unmixed
+            self.last_model_values = hv.clone()
         if self.sd_idx.numel():
             vals = showdown.showdown_values(self.sd_boards, beliefs[self.sd_idx], self.sd_potential,
                                             self.scale[self.sd_idx])
@@ -229,7 +246,8 @@ class SubgameOracle:
         out = torch.zeros_like(self.policy)
         actor = self.to_act[:, None, None].expand(-1, -1, H)
         pa = self.prev_actor[N:, None, None].expand(-1, -1, H)
-        opp_reach = unblocked.unblocked_mass(self.beliefs.flip(dims=[1]))
+        beliefs = self.beliefs_avg if self.cfr_avg else self.beliefs
+        opp_reach = unblocked.unblocked_mass(beliefs.flip(dims=[1]))
         weights = self._fan_out(opp_reach.gather(1, actor).squeeze(1))
         expected = self._fan_out(self.values.gather(1, actor).squeeze(1))
         achieved = self.values[N:].gather(1, pa).squeeze(1)
@@ -311,12 +329,12 @@ class SubgameOracle:
         if self.cfr_plus:
             self.regrets.clamp_(min=0)
         self.update_policy(t)
-        self.set_leaf_values()
+        self.set_leaf_values(t)
         self.expected_values()
 
     def finalize(self):
         """update_average_values_final (cfr_evaluator.py:1276-1292)."""
-        self.set_leaf_values(beliefs=self.beliefs_avg)
+        self.set_leaf_values(0, beliefs=self.beliefs_avg)
         self.expected_values(self.policy_avg, self.beliefs_avg, self.values, self.values_avg)
         if self.enforce_zero_sum:
             sums = (self.values_avg * self.beliefs_avg).sum(dim=2, keepdim=True).mean(dim=1, keepdim=True)

@@ -104,7 +104,9 @@ int p2b_cfr_solve(const void* subgames, const void* nodes, int32_t num_subgames,
     P2B_REQUIRE(iterations == 0 || scalars, "null scalars");
     P2B_REQUIRE(max_internal >= 1, "max_internal must be positive");
     P2B_REQUIRE(!exploitability || values_avg, "exploitability needs values_avg");
-    P2B_REQUIRE(flags >= 0 && flags <= 3, "flags: bit 0 = CFR+ clamp, bit 1 = zero-sum value outputs");
+    P2B_REQUIRE(flags >= 0 && flags <= 7,
+                "flags: bit 0 = CFR+ clamp, bit 1 = zero-sum value outputs, bit 2 = leaf values and regret weights at the "
+                "average-policy beliefs");
     if (num_blocks <= 0) num_blocks = cfr_default_blocks();
     if (num_blocks > num_subgames) num_blocks = num_subgames;
     P2B_REQUIRE(scratch_floats >= cfr_scratch_floats(max_internal) * num_blocks, "scratch too small");
@@ -137,6 +139,7 @@ int p2b_cfr_solve(const void* subgames, const void* nodes, int32_t num_subgames,
     p.iterations = iterations;
     p.cfr_plus = flags & 1;
     p.enforce_zero_sum = (flags >> 1) & 1;
+    p.cfr_avg = (flags >> 2) & 1;
     p.init_depth = init_depth;
     p.work_counter = work_counter;
     p.sample_pass = sample_pass;
@@ -171,7 +174,9 @@ int p2b_cfr_step(const void* subgames, const void* nodes, int32_t num_subgames, 
                 "null pointer");
     P2B_REQUIRE(max_internal >= 1, "max_internal must be positive");
     P2B_REQUIRE(!exploitability || values_avg, "exploitability needs values_avg");
-    P2B_REQUIRE(flags >= 0 && flags <= 3, "flags: bit 0 = CFR+ clamp, bit 1 = zero-sum value outputs");
+    P2B_REQUIRE(flags >= 0 && flags <= 7,
+                "flags: bit 0 = CFR+ clamp, bit 1 = zero-sum value outputs, bit 2 = leaf values and regret weights at the "
+                "average-policy beliefs");
     P2B_REQUIRE(pass_begin >= -1 && pass_begin <= pass_end && pass_end <= iterations, "pass range outside [-1, iterations]");
     P2B_REQUIRE(phases >= 1 && phases <= 3, "phases must be 1 (top-down), 2 (bottom-up) or 3 (both)");
     P2B_REQUIRE(phases == 3 || pass_begin == pass_end, "a single sweep direction covers exactly one pass");
@@ -211,6 +216,7 @@ int p2b_cfr_step(const void* subgames, const void* nodes, int32_t num_subgames, 
     p.iterations = iterations;
     p.cfr_plus = flags & 1;
     p.enforce_zero_sum = (flags >> 1) & 1;
+    p.cfr_avg = (flags >> 2) & 1;
     p.init_depth = init_depth;
     p.work_counter = work_counter;
     p.stepped = 1;
@@ -260,7 +266,9 @@ int p2b_cfr_solve_noalloc(const void* subgames, const void* nodes, int32_t num_s
     P2B_REQUIRE(subgames && nodes && root_beliefs && regrets && policy_avg && root_values && scalars, "null pointer");
     P2B_REQUIRE(max_internal >= 1, "max_internal must be positive");
     P2B_REQUIRE(!exploitability || values_avg, "exploitability needs values_avg");
-    P2B_REQUIRE(flags >= 0 && flags <= 3, "flags: bit 0 = CFR+ clamp, bit 1 = zero-sum value outputs");
+    P2B_REQUIRE(flags >= 0 && flags <= 7,
+                "flags: bit 0 = CFR+ clamp, bit 1 = zero-sum value outputs, bit 2 = leaf values and regret weights at the "
+                "average-policy beliefs");
     const uintptr_t align = reinterpret_cast<uintptr_t>(subgames) | reinterpret_cast<uintptr_t>(nodes) |
                             reinterpret_cast<uintptr_t>(tables) | reinterpret_cast<uintptr_t>(root_beliefs) |
                             reinterpret_cast<uintptr_t>(regrets) | reinterpret_cast<uintptr_t>(weight_sums) |
@@ -288,6 +296,7 @@ int p2b_cfr_solve_noalloc(const void* subgames, const void* nodes, int32_t num_s
     p.iterations = iterations;
     p.cfr_plus = flags & 1;
     p.enforce_zero_sum = (flags >> 1) & 1;
+    p.cfr_avg = (flags >> 2) & 1;
     p.init_depth = init_depth;
     p.rows = rows;
     return launch_cfr_solve_static(p, max_children, (cudaStream_t)stream);

@@ -51,7 +51,8 @@ constexpr int kOffCs = kOffPc + 2 * 52 * 52 * 4;
 constexpr int kOffWarpTot = kOffCs + kCsRows * 52 * 8;
 constexpr int kOffS = kOffWarpTot + 32 * 8;
 constexpr int kOffSig = kOffS + kCsRows * 8;
-constexpr int kOffMisc = kOffSig + kCfrMaxNodes * 2 * 4;
+constexpr int kOffSigB = kOffSig + kCfrMaxNodes * 2 * 4;  // the same sums for the beliefs under the average policy
+constexpr int kOffMisc = kOffSigB + kCfrMaxNodes * 2 * 4;
 constexpr int kOffIlist = kOffMisc + 64;  // node index of every internal node, in node order
 constexpr int kCfrSmem = kOffIlist + ((kCfrMaxNodes + 15) / 16) * 16;
 static_assert(kOffXs % 16 == 0 && kOffCs % 8 == 0 && kOffMisc % 16 == 0 && kOffSig % 8 == 0, "alignment");
@@ -69,6 +70,7 @@ struct Block {
     double* warp_tot;
     double* S;
     float* sig;    // [nodes][2] normalisation sums of the node beliefs of the current pass
+    float* sigb;   // [nodes][2] the same for the beliefs under the average policy (iteration passes with cfr_avg)
     int* misc;
     uint8_t* ilist;  // [n_internal] node index of the ii-th internal node
     float* fsum;
@@ -78,6 +80,9 @@ struct Block {
     __device__ __forceinline__ float* reach(int ii, int pl) const { return scr + (long long)(ii * 6 + pl) * P2B_HPAD; }
     __device__ __forceinline__ float* rbar(int ii, int pl) const { return scr + (long long)(ii * 6 + 2 + pl) * P2B_HPAD; }
     __device__ __forceinline__ float* val(int ii, int pl) const { return scr + (long long)(ii * 6 + 4 + pl) * P2B_HPAD; }
+    // Reach under the NEW average policy of the pass (cfr_avg only).  Shares the value rows: the top-down
+    // sweep writes it, the bottom-up visit of the node reads it before it stores the node's values there.
+    __device__ __forceinline__ float* rnew(int ii, int pl) const { return val(ii, pl); }
     __device__ __forceinline__ float* row1(float* base, int node) const {
         return base + (long long)(sg.node_begin + node) * P2B_HPAD;
     }
@@ -424,11 +429,15 @@ __device__ __forceinline__ void sweep_down(int mode_rt, int pass, const CfrParam
         p.beliefs_last = nullptr;
         p.policy = nullptr;
         p.start_policy = nullptr;
+        p.cfr_avg = 0;
     }
     // FIXED_MODE >= 0: compiled for that kind of pass alone (the iteration passes of a plain solve:
     // the start- and final-pass code stays out of the hot loop); otherwise the kind is a run-time value
     const int mode = FIXED_MODE >= 0 ? FIXED_MODE : mode_rt;
     const bool mix = (mode == kPassIter) && p.scalars[pass].do_mix != 0;
+    // cfr_avg (cfr_evaluator.py:1029, :1133): the bottom-up sweep of an iteration pass takes leaf values and
+    // regret weights at the beliefs under the average policy this sweep has just updated
+    const bool avgb = (mode == kPassIter) && p.cfr_avg != 0;
     FV<VPT> mask;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) mask.v[i] = hi.allowed[i] ? 1.0f : 0.0f;
@@ -615,7 +624,7 @@ __device__ __forceinline__ void sweep_down(int mode_rt, int pass, const CfrParam
                     u.v[i] = __fmul_rn(prior_a.v[i], t.v[i]);
                 }
                 stv<VPT>(B.stage_row(bank + c), tid, u);
-                if (ch.kind == kModelLeaf) {
+                if (ch.kind == kModelLeaf && !avgb) {
                     // unnormalised rows now; normalised in place at the end of the sweep, when
                     // the sums are known
                     const FV<VPT> prior_o = pick<VPT>(prior, 1 - a);
@@ -642,6 +651,52 @@ __device__ __forceinline__ void sweep_down(int mode_rt, int pass, const CfrParam
                 }
             }
         }
+        if (avgb) {
+            // the same once more under the average policy as updated above (its rows were just stored by
+            // this thread): reach, the rows whose sums normalise the children's average beliefs
+            FV<VPT> rwa = mask, rwna = mask;
+            if (j != 0) {
+                rwa = ldv<VPT>(B.rnew(ii, a), tid);
+                rwna = ldv<VPT>(B.rnew(ii, 1 - a), tid);
+            }
+            __syncthreads();  // the warps are done adding up the bank
+#pragma unroll
+            for (int c = 0; c < K; ++c) {
+                const NodeRec ch = B.nodes[fc + c];
+                if (ch.kind == kFoldLeaf || (ch.kind == kModelLeaf && !p.leaf_beliefs)) continue;
+                const FV<VPT> Pa = ldv<VPT>(B.row1(p.policy_avg, fc + c), tid);
+                FV<VPT> t, u;
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) {
+                    t.v[i] = __fmul_rn(rwa.v[i], Pa.v[i]);
+                    u.v[i] = __fmul_rn(prior_a.v[i], t.v[i]);
+                }
+                stv<VPT>(B.stage_row(bank + c), tid, u);
+                if (ch.kind == kModelLeaf) {
+                    const FV<VPT> prior_o = pick<VPT>(prior, 1 - a);
+                    FV<VPT> w;
+#pragma unroll
+                    for (int i = 0; i < VPT; ++i) w.v[i] = __fmul_rn(prior_o.v[i], rwna.v[i]);
+                    stv<VPT>(p.leaf_beliefs + B.leaf_row(ch.internal_idx, a), tid, u);
+                    stv<VPT>(p.leaf_beliefs + B.leaf_row(ch.internal_idx, 1 - a), tid, w);
+                }
+                if (ch.kind == kInternal) {
+                    stv<VPT>(B.rnew(ch.internal_idx, a), tid, t);
+                    stv<VPT>(B.rnew(ch.internal_idx, 1 - a), tid, rwna);
+                }
+            }
+            __syncthreads();
+            if (warp < k) {
+                const NodeRec ch = B.nodes[fc + warp];
+                if (ch.kind == kInternal || ch.kind == kShowdownLeaf || (ch.kind == kModelLeaf && p.leaf_beliefs)) {
+                    const float sum = row_sum_reference_order(B.stage_row(bank + warp));
+                    if ((tid & 31) == 0) {
+                        B.sigb[(fc + warp) * 2 + a] = sum;
+                        B.sigb[(fc + warp) * 2 + 1 - a] = B.sigb[j * 2 + 1 - a];
+                    }
+                }
+            }
+        }
         };
         dispatch_children(k, node_body);
     }
@@ -655,7 +710,7 @@ __device__ __forceinline__ void sweep_down(int mode_rt, int pass, const CfrParam
             for (int pl = 0; pl < 2; ++pl) {
                 float* row = p.leaf_beliefs + B.leaf_row(nd.internal_idx, pl);
                 FV<VPT> x = ldv<VPT>(row, tid);
-                apply_norm<VPT>(B, hi, x, B.sig[j * 2 + pl]);
+                apply_norm<VPT>(B, hi, x, (avgb ? B.sigb : B.sig)[j * 2 + pl]);
                 stv<VPT>(row, tid, x);
             }
         }
@@ -681,9 +736,11 @@ __device__ __forceinline__ void sweep_up(int mode_rt, int pass, const CfrParams&
         p.beliefs_last = nullptr;
         p.policy = nullptr;
         p.start_policy = nullptr;
+        p.cfr_avg = 0;
     }
     const int mode = FIXED_MODE >= 0 ? FIXED_MODE : mode_rt;
     const bool update = (mode != kPassFinal) && (pass + 1 < p.iterations);
+    const bool avgb = (mode == kPassIter) && p.cfr_avg != 0;  // see sweep_down
     constexpr int kRowM = 2, kRowLeaf = 2 + kBankRows;
     FV<VPT> mask;
 #pragma unroll
@@ -718,6 +775,20 @@ __device__ __forceinline__ void sweep_up(int mode_rt, int pass, const CfrParams&
                 apply_norm<VPT>(B, hi, b_o, B.sig[j * 2 + o]);
             }
         }
+        // x_o: the other player's beliefs that weight the regrets and meet the acting player's hands at a
+        // showdown; rw_a: the acting player's reach the showdown leaves' beliefs derive from.  With cfr_avg
+        // both are taken under the average policy (at the root the two kinds of beliefs are the same row).
+        FV<VPT> x_o = b_o, rw_a = r_a;
+        if (avgb) {
+            rw_a = mask;
+            if (j != 0) {
+                rw_a = ldv<VPT>(B.rnew(ii, a), tid);
+                const FV<VPT> rw_o = ldv<VPT>(B.rnew(ii, o), tid);
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) x_o.v[i] = __fmul_rn(prior_o.v[i], rw_o.v[i]);
+                apply_norm<VPT>(B, hi, x_o, B.sigb[j * 2 + o]);
+            }
+        }
         {
             if (ii > 0) {
                 const NodeRec nn = B.nodes[B.ilist[ii - 1]];
@@ -746,6 +817,11 @@ __device__ __forceinline__ void sweep_up(int mode_rt, int pass, const CfrParams&
                 }
                 for (int rep = ch.depth; rep <= p.init_depth; ++rep) normalize2<VPT>(B, hi, x);
                 bca = pick<VPT>(x, a);
+            } else if (avgb) {
+                const FV<VPT> Pa = ldv<VPT>(B.row1(p.policy_avg, fc + c), tid);
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) bca.v[i] = __fmul_rn(prior_a.v[i], __fmul_rn(rw_a.v[i], Pa.v[i]));
+                apply_norm<VPT>(B, hi, bca, B.sigb[(fc + c) * 2 + a]);
             } else {
 #pragma unroll
                 for (int i = 0; i < VPT; ++i) bca.v[i] = __fmul_rn(prior_a.v[i], __fmul_rn(r_a.v[i], P[c].v[i]));
@@ -758,7 +834,7 @@ __device__ __forceinline__ void sweep_up(int mode_rt, int pass, const CfrParams&
             }
         }
         stv<VPT>(B.stage_row(0), tid, b_a);
-        stv<VPT>(B.stage_row(1), tid, b_o);
+        stv<VPT>(B.stage_row(1), tid, x_o);
 #pragma unroll
         for (int c = 0; c < K; ++c)
             {
@@ -789,7 +865,7 @@ __device__ __forceinline__ void sweep_up(int mode_rt, int pass, const CfrParams&
         Divisor ddenm[VPT];
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
-            wgt.v[i] = unblocked(B.cs + 52, B.S[1], hi.c1[i], hi.c2[i], b_o.v[i]);
+            wgt.v[i] = unblocked(B.cs + 52, B.S[1], hi.c1[i], hi.c2[i], x_o.v[i]);
             denm.v[i] = unblocked(B.cs, B.S[0], hi.c1[i], hi.c2[i], b_a.v[i]);
             ddenm[i] = make_divisor(denm.v[i]);
             eva.v[i] = 0.0f;
@@ -1107,6 +1183,7 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
     B.warp_tot = reinterpret_cast<double*>(smem + kOffWarpTot);
     B.S = reinterpret_cast<double*>(smem + kOffS);
     B.sig = reinterpret_cast<float*>(smem + kOffSig);
+    B.sigb = reinterpret_cast<float*>(smem + kOffSigB);
     B.misc = reinterpret_cast<int*>(smem + kOffMisc);
     B.ilist = smem + kOffIlist;
     B.fsum = reinterpret_cast<float*>(smem + kOffMisc + 16);
@@ -1158,6 +1235,9 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
             root_b[0] = ldv<VPT>(cr + 2 * P2B_HPAD, tid);
             root_b[1] = ldv<VPT>(cr + 3 * P2B_HPAD, tid);
             for (int i = tid; i < 2 * B.sg.n_nodes; i += NT) B.sig[i] = p.carry_sums[(long long)B.sg.node_begin * 2 + i];
+            if (p.cfr_avg)  // the sums under the average policy follow the [rows][2] block of the current ones
+                for (int i = tid; i < 2 * B.sg.n_nodes; i += NT)
+                    B.sigb[i] = p.carry_sums[(p.rows + B.sg.node_begin) * 2 + i];
         } else {
             root_b[0] = ldv<VPT>(p.root_beliefs + ((long long)s * 2 + 0) * P2B_HPAD, tid);
             root_b[1] = ldv<VPT>(p.root_beliefs + ((long long)s * 2 + 1) * P2B_HPAD, tid);
@@ -1171,7 +1251,7 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
 
         // a one-launch solve without optional outputs takes the leanest copy of the sweeps
         const bool plain = !p.stepped && !p.leaf_beliefs && !p.leaf_values && !p.policy_sample && !p.beliefs_last &&
-                           !p.policy && !p.start_policy;
+                           !p.policy && !p.start_policy && !p.cfr_avg;
         for (int pass = pass_first; pass <= pass_last; ++pass) {
             const int mode = pass < 0 ? kPassInit : (pass == p.iterations ? kPassFinal : kPassIter);
             if (!run_down) {
@@ -1193,7 +1273,7 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
                 prior[1] = root_b[1];
                 normalize2<VPT>(B, hi, root_b);
                 // a child's row of the player who did not act is the root's row; so is its sum
-                if (tid < 2) B.sig[tid] = B.fsum[tid];
+                if (tid < 2) B.sig[tid] = B.sigb[tid] = B.fsum[tid];
             }
             if (mode == kPassIter && plain) {
                 sweep_down<VPT, MAXC, kPassIter, true>(mode, pass, p, B, hi, prior, tid);
@@ -1211,6 +1291,9 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
             stv<VPT>(cr + 2 * P2B_HPAD, tid, root_b[0]);
             stv<VPT>(cr + 3 * P2B_HPAD, tid, root_b[1]);
             for (int i = tid; i < 2 * B.sg.n_nodes; i += NT) p.carry_sums[(long long)B.sg.node_begin * 2 + i] = B.sig[i];
+            if (p.cfr_avg)
+                for (int i = tid; i < 2 * B.sg.n_nodes; i += NT)
+                    p.carry_sums[(p.rows + B.sg.node_begin) * 2 + i] = B.sigb[i];
         }
         if (p.exploitability && p.values_avg && run_up && pass_last == p.iterations) {
             // local exploitability of the average policy (cfr_evaluator.py:718-764)
@@ -1406,7 +1489,7 @@ int launch_cfr_solve(const CfrParams& params, int num_blocks, int max_children, 
     CfrParams p = params;
     p.combos = device_combo_table();
     // leaves all terminal, uniform start policy, all passes in this call: the iteration kernel applies
-    const bool plain = !p.stepped && !p.leaf_beliefs && !p.leaf_values && !p.start_policy;
+    const bool plain = !p.stepped && !p.leaf_beliefs && !p.leaf_values && !p.start_policy && !p.cfr_avg;
     if (!(plain && fast_scratch && max_children <= kCfrMaxChildren)) {
         rc = clear_counters(p.work_counter, stream);
         if (rc) return rc;

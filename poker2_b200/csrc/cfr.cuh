@@ -73,6 +73,8 @@ struct CfrParams {
     int32_t iterations;
     int32_t cfr_plus;
     int32_t enforce_zero_sum;    // final pass: value outputs shifted to zero sum (cfr_evaluator.py:957-980, 1289-1292)
+    int32_t cfr_avg;             // iteration passes: showdown values, regret weights and the beliefs handed to the
+                                 // caller's model come from the beliefs under the average policy (:1029, :1133)
     int32_t init_depth;          // depth of the deepest tree of the batch the subgames were built in
     int32_t* work_counter;       // dynamic subgame queue (zeroed by the launcher)
     // ---- stepped mode: a launch runs part of the pass sequence and the state that a whole
@@ -84,7 +86,7 @@ struct CfrParams {
     int32_t pass_end;            // last pass of this launch (inclusive)
     int32_t phases;              // bit 0: top-down sweep, bit 1: bottom-up sweep (+ best responses after
                                  // the final pass)
-    float* carry_sums;           // [rows][2] normalisation sums of the node beliefs
+    float* carry_sums;           // [rows][2] normalisation sums of the node beliefs ([2][rows][2] with cfr_avg)
     float* carry_roots;          // [B][4][HPAD] prior (2 rows) and root beliefs (2 rows) of the pass
     const int32_t* leaf_begin;   // [B] first model-leaf slot of each subgame
     float* leaf_beliefs;         // [slots][2][HPAD] beliefs at the model leaves (out, top-down sweep)

@@ -4,6 +4,7 @@
 // that module can switch to this library step by step.  The whole-subgame kernel in
 // cfr.cu is the fast path; these exist for drop-in compatibility.  Scalars that depend on
 // the iteration number are read from device memory (as upstream's TScalars do).
+#include "cfr_dev.cuh"
 #include "common.cuh"
 #include "exactdiv.cuh"
 
@@ -173,6 +174,10 @@ __global__ void mix_zero_sum_kernel(const float* __restrict__ a, const float* __
                                     const float* __restrict__ scale_p, float* __restrict__ out, long long rows, int H,
                                     int subtract_b, int enforce_zs) {
     __shared__ double red[kThreads / 32];
+    // enforce_zs == 2 (H == 1326 only): the two sums over hands run in fp32 in the order of the CPU row
+    // reduction the non-fused upstream code goes through (cfr_evaluator.py:973-976), then their mean
+    __shared__ float prod[2][P2B_HPAD];
+    __shared__ float rsum[2];
     const float ca = *ca_p, cb = *cb_p, sc = scale_p ? *scale_p : 1.0f;
     for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
         const long long base = row * 2 * H;
@@ -182,12 +187,26 @@ __global__ void mix_zero_sum_kernel(const float* __restrict__ a, const float* __
             float v = subtract_b ? __fsub_rn(x, y) : __fadd_rn(x, y);
             if (scale_p) v = __fmul_rn(v, sc);
             out[base + i] = v;
-            if (enforce_zs) s += (double)__fmul_rn(v, beliefs[base + i]);
+            if (enforce_zs == 1) s += (double)__fmul_rn(v, beliefs[base + i]);
+            if (enforce_zs == 2) prod[i >= H][i >= H ? i - H : i] = __fmul_rn(v, beliefs[base + i]);
         }
         if (enforce_zs) {  // uniform branch: all threads take it
-            float shift = 0.5f * (float)block_sum(s, red);
+            float shift;
+            if (enforce_zs == 2) {
+                __syncthreads();
+                const int warp = threadIdx.x >> 5;
+                if (warp < 2) {
+                    const float t = row_sum_reference_order(prod[warp]);
+                    if ((threadIdx.x & 31) == 0) rsum[warp] = t;
+                }
+                __syncthreads();
+                shift = __fmul_rn(__fadd_rn(rsum[0], rsum[1]), 0.5f);
+            } else {
+                shift = 0.5f * (float)block_sum(s, red);
+            }
             if (ignore && ignore[row]) shift = 0.0f;
             for (int i = threadIdx.x; i < 2 * H; i += blockDim.x) out[base + i] = __fsub_rn(out[base + i], shift);
+            __syncthreads();
         }
     }
 }
@@ -514,6 +533,8 @@ int p2b_step_mix_zero_sum(const float* a, const float* b, const float* beliefs, 
                           const float* coef_a, const float* coef_b, const float* scale, float* out, int64_t rows,
                           int32_t H, int subtract_b, int enforce_zero_sum, void* stream) {
     if (rows <= 0) return P2B_OK;
+    if (enforce_zero_sum == 2 && H != P2B_NUM_HANDS)
+        return set_error(P2B_ERR_ARG, "enforce_zero_sum = 2 (sums in the CPU row-reduction order) needs H = %d", P2B_NUM_HANDS);
     mix_zero_sum_kernel<<<GRID_ROWS(rows), kThreads, 0, (cudaStream_t)stream>>>(a, b, beliefs, ignore, coef_a, coef_b, scale,
                                                                                out, rows, H, subtract_b, enforce_zero_sum);
     STEP_CHECK("mix_zero_sum_kernel");

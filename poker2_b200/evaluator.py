@@ -70,7 +70,7 @@ class SubgameEvaluator:
                  generator: torch.Generator | None = None, warm_start_iterations: int = 0,
                  warm_start_multiplier: float = 1.0, alpha_final: float | None = None,
                  beta_final: float | None = None, gamma_final: float | None = None,
-                 enforce_zero_sum: bool = False):
+                 enforce_zero_sum: bool = False, cfr_avg: bool = False):
         self.device = torch.device(device)
         self.cfr_iterations = int(iterations)
         self.bet_bins, self.max_depth, self.bb, self.max_raises = list(bet_bins), max_depth, bb, max_raises
@@ -80,6 +80,9 @@ class SubgameEvaluator:
         # value targets upstream applies when `model.enforce_zero_sum` is set (:957-980, 1289-1292)
         self.alpha_final, self.beta_final, self.gamma_final = alpha_final, beta_final, gamma_final
         self.enforce_zero_sum = bool(enforce_zero_sum)
+        # `cfr_avg` upstream: leaf values and regret weights at the beliefs under the average policy, model
+        # values de-averaged (cfr_evaluator.py:997-1018, :1029, :1133)
+        self.cfr_avg = bool(cfr_avg)
         self.model, self.chance_average, self.leaf_chunk = model, chance_average, leaf_chunk
         self.sample_epsilon = sample_epsilon
         self.generator = generator
@@ -167,12 +170,12 @@ class SubgameEvaluator:
             res = self.solver.solve(self.root_beliefs, scal, self.leaf_fn, cfr_plus=self.cfr_plus,
                                     enforce_zero_sum=self.enforce_zero_sum, start_policy=start_policy,
                                     warm_start_iterations=ws, warm_start_multiplier=self.warm_start_multiplier,
-                                    warm_start_scalars=first)
+                                    warm_start_scalars=first, cfr_avg=self.cfr_avg)
         else:
             if start_policy is not None:
                 raise ValueError("a start policy needs the stepped solver (set warm_start_iterations or use model leaves)")
             res = self.solver.solve(self.root_beliefs, scal, cfr_plus=self.cfr_plus,
-                                    enforce_zero_sum=self.enforce_zero_sum)
+                                    enforce_zero_sum=self.enforce_zero_sum, cfr_avg=self.cfr_avg)
         self._result = res
         from . import stats as pstats
 

@@ -272,6 +272,20 @@ def fused_model_values_mix_zero_sum(hand_values, last_model_values, beliefs, old
           _p(old_plus_new_over_new), _p(old_over_new), None, _p(out), m, h, 1, int(enforce_zero_sum))
 
 
+def mix_zero_sum(a, b, beliefs, coef_a, coef_b, out, mode: int = 1) -> None:
+    """out = a*coef_a - b*coef_b, minus 0.5 * sum over players and hands of out * beliefs (rows of [2,H]).
+    mode 1: the sum in fp64; mode 2 (H = 1326): fp32 sums in the order of the CPU row reduction, which
+    reproduces `_maybe_enforce_zero_sum` of the non-fused upstream evaluator (cfr_evaluator.py:957-980) bit
+    for bit."""
+    _require()
+    for t in (a, b, beliefs, out):
+        assert t.is_contiguous()
+    assert a.shape == b.shape == beliefs.shape == out.shape and a.shape[1] == 2
+    m, _, h = a.shape
+    _call("p2b_step_mix_zero_sum", out.device, _p(a), _p(b), _p(beliefs), None, _p(coef_a), _p(coef_b), None, _p(out),
+          m, h, 1, int(mode))
+
+
 def fused_weighted_parent_sum(values, prev_actor, policy_hero, policy_opp, child_offsets, child_count,
                               parent_base: int, max_children: int = 8, block_h: int = 2048) -> None:
     _require()

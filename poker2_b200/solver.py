@@ -205,9 +205,10 @@ def layout_tensor(layout, name: str, device, dtype=None) -> torch.Tensor:
     return t if dtype is None else t.to(dtype)
 
 
-def solve_flags(cfr_plus: bool, enforce_zero_sum: bool) -> int:
-    """The `flags` argument of the solve entry points: bit 0 = CFR+ clamp, bit 1 = zero-sum value outputs."""
-    return int(bool(cfr_plus)) | (int(bool(enforce_zero_sum)) << 1)
+def solve_flags(cfr_plus: bool, enforce_zero_sum: bool, cfr_avg: bool = False) -> int:
+    """The `flags` argument of the solve entry points: bit 0 = CFR+ clamp, bit 1 = zero-sum value outputs,
+    bit 2 = leaf values and regret weights at the beliefs under the average policy (`cfr_avg` upstream)."""
+    return int(bool(cfr_plus)) | (int(bool(enforce_zero_sum)) << 1) | (int(bool(cfr_avg)) << 2)
 
 
 def pad_rows(x: torch.Tensor) -> torch.Tensor:
@@ -350,11 +351,13 @@ class SubgameSolver:
             setattr(self, name, None)
 
     def solve(self, root_beliefs: torch.Tensor, scalars: np.ndarray, *, cfr_plus: bool = False,
-              enforce_zero_sum: bool = False, check: bool = False) -> SolveResult:
+              enforce_zero_sum: bool = False, cfr_avg: bool = False, check: bool = False) -> SolveResult:
         """root_beliefs: [B,2,1344] fp32 on the device (padded).  Enqueues the solve (one to three
         kernels).  enforce_zero_sum: shift the value outputs to zero sum, as upstream does when
-        `model.enforce_zero_sum` is set (cfr_evaluator.py:957-980, 1289-1292).  check: read the
-        status word afterwards (synchronises) and raise if the record check refused the batch."""
+        `model.enforce_zero_sum` is set (cfr_evaluator.py:957-980, 1289-1292).  cfr_avg: showdown values
+        and regret weights at the beliefs under the average policy (:1029, :1133; one launch, general
+        kernel).  check: read the status word afterwards (synchronises) and raise if the record check
+        refused the batch."""
         assert root_beliefs.shape == (self.B, 2, HPAD) and root_beliefs.dtype == torch.float32
         assert root_beliefs.is_contiguous() and root_beliefs.device == self.device
         iterations = int(scalars.shape[0])
@@ -368,7 +371,7 @@ class SubgameSolver:
                 p(self.regrets), p(self.weight_sums), p(self.policy_avg), p(self.policy), p(self.root_values),
                 p(self.values_avg), p(self.beliefs_avg), p(self.exploitability), p(self.br_values), p(self.scratch),
                 self.scratch.numel(),
-                p(sc) if iterations else None, iterations, solve_flags(cfr_plus, enforce_zero_sum),
+                p(sc) if iterations else None, iterations, solve_flags(cfr_plus, enforce_zero_sum, cfr_avg),
                 self.layout.tree_depth, p(self.work_counter),
                 self.num_blocks, p(self.sample_pass), p(self.policy_sample), p(self.beliefs_last),
                 _lib.stream_ptr(self.device))
@@ -397,7 +400,7 @@ class SteppedSolver(SubgameSolver):
         f32 = dict(device=device, dtype=torch.float32)
         n_scratch = int(_lib.lib().p2b_cfr_scratch_floats(layout.max_internal, 1)) * self.B
         self.scratch = torch.empty(n_scratch, **f32)
-        self.carry_sums = torch.zeros(layout.rows, 2, **f32)
+        self.carry_sums = torch.zeros(2, layout.rows, 2, **f32)  # current-policy sums, average-policy sums
         self.carry_roots = torch.zeros(self.B, 4, HPAD, **f32)
         slots = max(layout.num_model_leaves, 1)
         self.leaf_begin = layout_tensor(layout, "leaf_begin", device, torch.int32)
@@ -405,6 +408,30 @@ class SteppedSolver(SubgameSolver):
         self.leaf_values = torch.zeros(slots, 2, HPAD, **f32)
 
     start_policy_rows = None  # [rows,1344] policy of the start pass (None: uniform)
+    _last_model_values = None
+
+    def _de_average(self, vals, t, scalars, enforce_zero_sum, n_leaves):
+        """The CFR-AVG branch of `_set_model_values_impl` (cfr_evaluator.py:997-1018): from t = 2 on the
+        model's values are read as the average over the iterations, so this iteration's are
+        ((old + new) * values - old * last) / new, shifted to zero sum by the leaf beliefs if asked."""
+        raw = vals[..., :NUM_HANDS].to(torch.float32)
+        last, self._last_model_values = self._last_model_values, raw.clone()
+        if t <= 1 or last is None:
+            return vals
+        row = scalars[t]
+        old, total = float(row["mix_old"]), float(row["mix_total"])
+        new = torch.tensor(float(row["mix_new"]), device=raw.device, dtype=torch.float32)
+        unmixed = (total * raw - old * last) / new  # a tensor divisor: an IEEE division, like the CPU's
+        if enforce_zero_sum:
+            from . import fused_cfr as F
+
+            one, zero = (torch.tensor(v, device=raw.device, dtype=torch.float32) for v in (1.0, 0.0))
+            out = torch.empty_like(unmixed)
+            # unmixed * 1 - 0 * 0 is unmixed itself; the kernel adds the shift, its sums in the CPU's order
+            F.mix_zero_sum(unmixed.contiguous(), torch.zeros_like(unmixed),
+                           self.leaf_beliefs[:n_leaves, :, :NUM_HANDS].contiguous(), one, zero, out, mode=2)
+            unmixed = out
+        return unmixed
 
     def _step(self, root_beliefs, sc, iterations, flags, pass_begin, pass_end, phases) -> None:
         p = _lib.ptr
@@ -423,18 +450,22 @@ class SteppedSolver(SubgameSolver):
 
     def solve(self, root_beliefs: torch.Tensor, scalars: np.ndarray, leaf_fn=None, *, cfr_plus: bool = False,
               enforce_zero_sum: bool = False, start_policy: torch.Tensor | None = None, warm_start_iterations: int = 0,
-              warm_start_multiplier: float = 1.0, warm_start_scalars: np.ndarray | None = None) -> SolveResult:
+              warm_start_multiplier: float = 1.0, warm_start_scalars: np.ndarray | None = None,
+              cfr_avg: bool = False) -> SolveResult:
         """scalars: `iteration_scalars(T)` for all T iterations.  start_policy [M,1326] in the
         upstream node order (the policy head's softmax; None = uniform).  With
         warm_start_iterations = w > 0 (needs a start policy) the regrets are seeded from the start
         policy after the start pass (`warm_start` of type `model`, cfr_evaluator.py:887-926) and
         the iterations w..T-1 follow; `warm_start_scalars` (one row, `warm_start_mix_scalars`) gives
         the mixing weights of the warm start's own policy update when the exponents follow a
-        schedule (default: the row of iteration w)."""
+        schedule (default: the row of iteration w).  cfr_avg: `cfr_avg` upstream -- leaf_fn sees the
+        beliefs under the average policy, and from the second iteration on its values are taken as a
+        running average over the iterations and de-averaged (cfr_evaluator.py:997-1018)."""
         assert root_beliefs.shape == (self.B, 2, HPAD) and root_beliefs.dtype == torch.float32
         assert root_beliefs.is_contiguous() and root_beliefs.device == self.device
         ws = int(warm_start_iterations)
-        flags = solve_flags(cfr_plus, enforce_zero_sum)
+        flags = solve_flags(cfr_plus, enforce_zero_sum, cfr_avg)
+        all_scalars = scalars
         if ws > 0:
             if start_policy is None:
                 raise ValueError("a warm start needs a start policy")
@@ -451,6 +482,7 @@ class SteppedSolver(SubgameSolver):
         n_leaves = self.layout.num_model_leaves
         if n_leaves and leaf_fn is None:
             raise ValueError("the trees have model-valued leaves: a leaf_fn is required")
+        self._last_model_values = None
         for pas in range(-1, iterations + 1):
             if pas == 0 and ws > 0:
                 with torch.cuda.device(self.device):
@@ -463,6 +495,11 @@ class SteppedSolver(SubgameSolver):
                 continue
             self._step(root_beliefs, sc, iterations, flags, pas, pas, 1)
             vals = leaf_fn(self.leaf_beliefs[:n_leaves])
+            if cfr_avg:
+                # iteration the pass belongs to, as `set_leaf_values(t)` sees it: the start pass, the pass
+                # that follows a warm start and the final pass pass t = 0 (:1511, :1288)
+                t = 0 if (pas < 0 or pas == iterations) else (pas if ws == 0 else (0 if pas == 0 else ws + pas - 1))
+                vals = self._de_average(vals, t, all_scalars, enforce_zero_sum, n_leaves)
             if vals.shape[-1] == NUM_HANDS:
                 self.leaf_values[:n_leaves, :, :NUM_HANDS].copy_(vals)
             else:
@@ -515,7 +552,7 @@ def solve_subgames(boards, ranges, pot, stacks, *, iterations: int, bet_bins=(0.
                    gamma: float = 2.0, dcfr_delay: int = 0, cfr_plus: bool = False, device=None,
                    keep_policy: bool = False, keep_node_values: bool = False, track_weight_sums: bool = True,
                    exploitability: bool = False, device_tree: bool = False, enforce_zero_sum: bool = False,
-                   alpha_final=None, beta_final=None, gamma_final=None):
+                   alpha_final=None, beta_final=None, gamma_final=None, cfr_avg: bool = False):
     """Solves a batch of river subgames: boards [B,5] card ids, ranges [B,2,1326] fp32,
     pot [B] and stacks [B] or [B,2] in chips.  Returns (SolveResult, PublicTrees); with
     `device_tree` the trees are expanded on the GPU (`device_tree.build_device_layout`), no host
@@ -538,7 +575,7 @@ def solve_subgames(boards, ranges, pot, stacks, *, iterations: int, bet_bins=(0.
     rb = pad_rows(torch.as_tensor(ranges, dtype=torch.float32).to(device)).contiguous()
     scal = iteration_scalars(iterations, cfr_type=cfr_type, alpha=alpha, beta=beta, gamma=gamma, dcfr_delay=dcfr_delay,
                              alpha_final=alpha_final, beta_final=beta_final, gamma_final=gamma_final)
-    return solver.solve(rb, scal, cfr_plus=cfr_plus, enforce_zero_sum=enforce_zero_sum), trees
+    return solver.solve(rb, scal, cfr_plus=cfr_plus, enforce_zero_sum=enforce_zero_sum, cfr_avg=cfr_avg), trees
 
 
 def solve_subgames_with_model(boards, ranges, pot, stacks, model, *, street: int, iterations: int,
@@ -546,7 +583,7 @@ def solve_subgames_with_model(boards, ranges, pot, stacks, model, *, street: int
                               cfr_type: str = "discounted", alpha: float = 1.5, beta: float = 0.0, gamma: float = 2.0,
                               dcfr_delay: int = 0, cfr_plus: bool = False, device=None, chance_average: bool = True,
                               chunk: int = 2048, exploitability: bool = False, keep_node_values: bool = False,
-                              device_tree: bool = False, enforce_zero_sum: bool = False):
+                              device_tree: bool = False, enforce_zero_sum: bool = False, cfr_avg: bool = False):
     """Solves a batch of flop (street=1, 3 board cards) or turn (street=2, 4 cards) subgames
     whose leaves at the start of the next street are valued by `model(beliefs, boards,
     context)`, averaged over the next public card when `chance_average` (the
@@ -585,5 +622,5 @@ def solve_subgames_with_model(boards, ranges, pot, stacks, model, *, street: int
     rb = pad_rows(torch.as_tensor(ranges, dtype=torch.float32).to(device)).contiguous()
     scal = iteration_scalars(iterations, cfr_type=cfr_type, alpha=alpha, beta=beta, gamma=gamma, dcfr_delay=dcfr_delay)
     res = sv.solve(rb, scal, evaluator if layout.num_model_leaves else None, cfr_plus=cfr_plus,
-                   enforce_zero_sum=enforce_zero_sum)
+                   enforce_zero_sum=enforce_zero_sum, cfr_avg=cfr_avg)
     return res, trees, sv

@@ -19,8 +19,8 @@ touches:
 
 No upstream module is imported.  The leaf model is called as `model(beliefs [S,2,1326], boards [S,5],
 context [S,3])` (see `leaf_eval`); a model object may carry that callable as `b200_leaf_model`.
-Not covered: `cfr_avg=True`, `value_targets_from_final_policy=False`, warm start of type `model_br`,
-linear CFR (each raises at construction).
+Not covered: `value_targets_from_final_policy=False`, warm start of type `model_br`, linear CFR (each
+raises at construction).
 """
 from __future__ import annotations
 
@@ -171,8 +171,6 @@ class B200CFREvaluator:
 
     def __init__(self, model, device, cfg, generator: torch.Generator | None = None, *, max_raises=None):
         s, e = cfg.search, cfg.env
-        if getattr(s, "cfr_avg", False):
-            raise NotImplementedError("cfr_avg=True (running average values, de-averaged model values) is not supported")
         if not getattr(s, "value_targets_from_final_policy", True):
             raise NotImplementedError("value targets from running averages are not supported: "
                                       "set search.value_targets_from_final_policy")
@@ -195,7 +193,7 @@ class B200CFREvaluator:
             max_raises=max_raises, model=leaf_model, chance_average=False,
             sample_epsilon=float(getattr(s, "sample_epsilon", 0.25)), generator=generator, warm_start_iterations=ws,
             warm_start_multiplier=float(getattr(s, "warm_start_multiplier", 1.0)),
-            enforce_zero_sum=bool(getattr(model, "enforce_zero_sum", False)))
+            enforce_zero_sum=bool(getattr(model, "enforce_zero_sum", False)), cfr_avg=bool(getattr(s, "cfr_avg", False)))
         self.root_nodes = int(cfg.num_envs)
         self.warm_start_iterations = ws
         self.generator = generator

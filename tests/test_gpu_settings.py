@@ -126,3 +126,46 @@ def test_ragged_roots_at_256_iterations_match_upstream(cuda_device, golden_dir):
     _close("root_values", res.root_values[..., :1326].cpu(), torch.from_numpy(z["root_values"]))
     _close("exploitability", res.exploitability.cpu(), torch.from_numpy(z["exploitability"]), rtol=1e-4)
     _close("br_values", res.br_values.cpu(), torch.from_numpy(z["br_values"]), rtol=1e-4)
+
+
+def test_cfr_avg_matches_upstream(cuda_device, golden_dir):
+    """`cfr_avg = True` upstream (the dataclass default): showdown values and regret weights at the beliefs
+    under the average policy.  River subgames through the one-call solve; turn subgames pass by pass, the
+    stand-in model seeing the average beliefs and its values de-averaged from the second iteration on."""
+    from leaf_models import pot_echo_leaf_fn
+    from poker2_b200 import solver, tree as ptree
+
+    z = np.load(os.path.join(golden_dir, "cfr_avg.npz"))
+    cap, depth = int(z["cap"]), int(z["max_depth"])
+    res, trees = solver.solve_subgames(z["river_boards"].astype(np.int64), torch.from_numpy(z["river_ranges"]),
+                                       z["river_pot"], z["river_stack"], iterations=int(z["river_iterations"]),
+                                       max_depth=depth, max_raises=cap, keep_node_values=True, exploitability=True,
+                                       enforce_zero_sum=True, cfr_avg=True, device=cuda_device)
+    assert trees.total_nodes == int(z["river_total_nodes"])
+    n = trees.num_roots
+    _close("river regrets", res.level_major(res.regrets).cpu()[n:], torch.from_numpy(z["river_regrets"])[n:])
+    _close("river policy_avg", res.level_major(res.policy_avg).cpu()[n:], torch.from_numpy(z["river_policy_avg"])[n:])
+    _close("river values_avg", res.level_major(res.values_avg).cpu(), torch.from_numpy(z["river_values_avg"]))
+    _close("river exploitability", res.exploitability.cpu(), torch.from_numpy(z["river_exploitability"]), rtol=1e-4)
+    # the flag matters: without it the regrets differ visibly
+    plain, _ = solver.solve_subgames(z["river_boards"].astype(np.int64), torch.from_numpy(z["river_ranges"]),
+                                     z["river_pot"], z["river_stack"], iterations=int(z["river_iterations"]),
+                                     max_depth=depth, max_raises=cap, device=cuda_device)
+    assert (plain.level_major(plain.regrets).cpu() - torch.from_numpy(z["river_regrets"])).abs().max() > 1e-4
+
+    roots = ptree.root_states(z["turn_pot"], z["turn_stack"], min_raise=2, street=2)
+    trees = ptree.build_trees(roots, [0.5, 1.0], depth, bb=2, max_raises=cap)
+    assert trees.total_nodes == int(z["turn_total_nodes"])
+    boards = np.concatenate([z["turn_boards"].astype(np.int64), np.full((z["turn_boards"].shape[0], 1), -1)], axis=1)
+    layout = solver.device_layout(trees, boards)
+    sv = solver.SteppedSolver(layout, torch.from_numpy(boards), cuda_device, exploitability=True)
+    leaf_fn = pot_echo_leaf_fn(trees, layout.model_nodes, torch.from_numpy(z["hand_weights"]))
+    rb = solver.pad_rows(torch.from_numpy(z["turn_ranges"]).to(cuda_device)).contiguous()
+    res = sv.solve(rb, solver.iteration_scalars(int(z["turn_iterations"])), leaf_fn, enforce_zero_sum=True, cfr_avg=True)
+    assert sv.status() == 0
+    n = trees.num_roots
+    _close("turn regrets", res.level_major(res.regrets).cpu()[n:], torch.from_numpy(z["turn_regrets"])[n:])
+    _close("turn policy_avg", res.level_major(res.policy_avg).cpu()[n:], torch.from_numpy(z["turn_policy_avg"])[n:])
+    _close("turn values_avg", res.level_major(res.values_avg).cpu(), torch.from_numpy(z["turn_values_avg"]))
+    _close("turn exploitability", res.exploitability.cpu(), torch.from_numpy(z["turn_exploitability"]), rtol=1e-4)
+    _close("turn br_values", res.br_values.cpu(), torch.from_numpy(z["turn_br_values"]), rtol=1e-4)

@@ -104,3 +104,35 @@ def test_iteration_scalars_follow_the_schedules():
     # standard CFR: no discount, weights (t, 1)
     std = solver.iteration_scalars(4, cfr_type="standard")
     assert std[2]["num_pos"] == 1 and std[2]["den_pos"] == 1 and (std[2]["mix_old"], std[2]["mix_new"]) == (2, 1)
+
+
+def test_oracle_cfr_avg_bit_exact(golden_dir):
+    """cfr_avg = True upstream: showdown values and regret weights at the beliefs under the average
+    policy (river), model values de-averaged from the second iteration on and shifted to zero sum (turn)."""
+    z = np.load(os.path.join(golden_dir, "cfr_avg.npz"))
+    cap, depth = int(z["cap"]), int(z["max_depth"])
+    t = _build(z["river_pot"], z["river_stack"], cap, depth)
+    assert t.total_nodes == int(z["river_total_nodes"])
+    o = ocfr.SubgameOracle(t.oracle_dict(z["river_boards"].astype(np.int64)), torch.from_numpy(z["river_ranges"]),
+                           iterations=int(z["river_iterations"]), enforce_zero_sum=True, cfr_avg=True).solve()
+    assert torch.equal(o.regrets, torch.from_numpy(z["river_regrets"]))
+    assert torch.equal(o.policy_avg, torch.from_numpy(z["river_policy_avg"]))
+    assert torch.equal(o.values_avg, torch.from_numpy(z["river_values_avg"]))
+    # the flag matters: without it the regrets differ
+    plain = ocfr.SubgameOracle(t.oracle_dict(z["river_boards"].astype(np.int64)), torch.from_numpy(z["river_ranges"]),
+                               iterations=int(z["river_iterations"]), enforce_zero_sum=True).solve()
+    assert not torch.equal(plain.regrets, o.regrets)
+    t = _build(z["turn_pot"], z["turn_stack"], cap, depth, street=2)
+    assert t.total_nodes == int(z["turn_total_nodes"])
+    boards = np.concatenate([z["turn_boards"].astype(np.int64), np.full((z["turn_boards"].shape[0], 1), -1)], axis=1)
+    model_nodes = np.nonzero(z["turn_model_mask"])[0]
+    leaf_fn = pot_echo_leaf_fn(t, model_nodes, torch.from_numpy(z["hand_weights"]))
+    o = ocfr.SubgameOracle(t.oracle_dict(boards), torch.from_numpy(z["turn_ranges"]),
+                           iterations=int(z["turn_iterations"]), enforce_zero_sum=True, cfr_avg=True,
+                           leaf_fn=lambda b, idx: leaf_fn(b)).solve()
+    assert torch.equal(o.regrets, torch.from_numpy(z["turn_regrets"]))
+    assert torch.equal(o.policy_avg, torch.from_numpy(z["turn_policy_avg"]))
+    assert torch.equal(o.values_avg, torch.from_numpy(z["turn_values_avg"]))
+    ex, br = o.exploitability()
+    assert torch.equal(ex, torch.from_numpy(z["turn_exploitability"]))
+    assert torch.equal(br, torch.from_numpy(z["turn_br_values"]))
