@@ -59,9 +59,9 @@ __device__ __forceinline__ uint32_t straight_windows(uint32_t ranks) {
     return ext & (ext >> 1) & (ext >> 2) & (ext >> 3) & (ext >> 4);
 }
 
-__device__ __forceinline__ int32_t score_from_masks(uint32_t m0, uint32_t m1, uint32_t m2, uint32_t m3,
-                                                    const RankClasses& rc) {
-    const uint32_t seen = m0 | m1 | m2 | m3;
+// The part of the score that depends on the ranks alone: the multiplicity category with its kickers
+// and the straight.  `seen` is the union of the ranks.
+__device__ __forceinline__ int32_t score_rank_part(const RankClasses& rc, uint32_t seen) {
     // ---- rank-multiplicity categories: pop ranks by (count desc, rank desc) ----
     uint64_t w = ((uint64_t)((rc.quads << 13) | rc.trips) << 26) | (uint64_t)((rc.pairs << 13) | rc.singles);
     uint32_t zeros = ~seen & 0x1fffu;
@@ -94,6 +94,12 @@ __device__ __forceinline__ int32_t score_from_masks(uint32_t m0, uint32_t m1, ui
     // ---- straight (lowest window) ----
     const uint32_t sw = straight_windows(seen);
     if (sw) best = max(best, (int32_t)((5u << 20) | ((uint32_t)(__ffs((int)sw) - 1) << 16)));
+    return best;
+}
+
+__device__ __forceinline__ int32_t score_from_masks(uint32_t m0, uint32_t m1, uint32_t m2, uint32_t m3,
+                                                    const RankClasses& rc) {
+    int32_t best = score_rank_part(rc, m0 | m1 | m2 | m3);
 
     // ---- flush / straight flush ----
     const int c0 = __popc(m0), c1 = __popc(m1), c2 = __popc(m2), c3 = __popc(m3);

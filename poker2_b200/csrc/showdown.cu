@@ -8,14 +8,20 @@ namespace p2b {
 // ---------------------------------------------------------------------------------------
 // Board set-up.  One block per board, 352 threads, four keys per thread.
 //   1. strength of every combo (board cards + two hole cards; combos that overlap the board
-//      are scored with repeated card ids, as p2/env/rules_triton.py:139-146 does);
+//      are scored with repeated card ids, as p2/env/rules_triton.py:139-146 does).  On a fixed
+//      board the rank part of the score (multiplicity category, kickers, straight) depends on
+//      the two hole RANKS only: it is computed once per rank pair (169 threads) and looked up
+//      per combo; only the board's suit with three or more cards, if any, can make a flush,
+//      which costs a combo one table entry of the suit's rank mask;
 //   2. stable LSD radix sort of the 24-bit strengths, four passes of six bits.  A warp ranks
 //      32 consecutive keys with a match instruction; counts per (digit, chunk of 32) are
 //      bytes, scanned in digit-major order to give every key its destination;
 //   3. tie groups [L,R) from the sorted strengths (one block-wide max scan);
-//   4. per-card hand lists in strength order: the 2652 (card, hand) incidences, walked in
-//      strength order, are counting-sorted by card with the same rank/scan machinery;
-//   5. per hand, how many entries of its two cards' lists lie before L and before R.
+//   4. per card, a bit mask over the sorted positions of the hands that hold it, and the
+//      running bit counts per 32-position word;
+//   5. per hand: its index in the strength-ordered list of each of its two cards, and how
+//      many entries of those lists lie before L and before R -- each a count of mask bits
+//      below a position.
 // The table blob is assembled in shared memory and written out with 16-byte stores.
 // ---------------------------------------------------------------------------------------
 constexpr int kSetupThreads = 352;
@@ -24,27 +30,27 @@ constexpr int kSortChunks = 44;                         // chunks of 32 keys
 constexpr int kSortN = kSortChunks * 32;                // 1408 >= 1326
 constexpr int kSortRounds = kSortChunks / kSetupWarps;  // 4 chunks per warp
 constexpr int kDigitBits = 6, kDigits = 1 << kDigitBits, kSortPasses = 4;
-constexpr int kIncidences = 2 * P2B_NUM_HANDS;          // 2652
-constexpr int kIncChunks = 84;                          // chunks of 32 incidences (83 used), multiple of 4
-constexpr int kIncRounds = (kIncChunks + kSetupWarps - 1) / kSetupWarps;  // 8
-static_assert(kSortChunks % 4 == 0 && kIncChunks % 4 == 0, "count bytes are scanned four at a time");
+static_assert(kSortChunks % 4 == 0, "count bytes are scanned four at a time");
 static_assert(kSortChunks == kSortRounds * kSetupWarps, "every warp sorts the same number of chunks");
-
-constexpr int kCntWords = (52 * kIncChunks) / 4;        // 1092 words of four byte counters (>= 64*44/4)
-constexpr int kOffEntries = 52 * kIncChunks;            // 4368 uint16 offsets (>= 64*44)
+constexpr int kSortCntWords = kDigits * kSortChunks / 4;  // 704 words of four byte counters
+constexpr int kMaskWords = 42;                            // 32-position words of a card's mask (1326 positions, and 1326 itself)
+constexpr int kMaskStride = 43;                           // odd: the cards of one word fall into distinct banks
+static_assert(kMaskWords * 32 > P2B_NUM_HANDS && kMaskStride >= kMaskWords, "a mask covers positions 0..1326");
 
 // shared-memory carve-up (bytes)
 constexpr int kSuKey = 0;                                // uint32 [2][kSortN]
 constexpr int kSuVal = kSuKey + 2 * kSortN * 4;          // uint16 [2][kSortN]
-constexpr int kSuCnt = kSuVal + 2 * kSortN * 2;          // uint32 [kCntWords]
-constexpr int kSuOff = kSuCnt + kCntWords * 4;           // uint16 [kOffEntries]
-constexpr int kSuLg = kSuOff + kOffEntries * 2;          // uint16 [kSortN]   tie-group start per sorted position
+constexpr int kSuCnt = kSuVal + 2 * kSortN * 2;          // uint32: sort counters [kSortCntWords], then card masks [52][kMaskStride]
+constexpr int kSuCntWords = 52 * kMaskStride;            // 2236 >= kSortCntWords
+constexpr int kSuOff = kSuCnt + kSuCntWords * 4;         // rank-pair scores int32 [169], then sort offsets uint16 [64*44],
+constexpr int kSuOffBytes = kDigits * kSortChunks * 2;   // then mask bit counts uint16 [52][kMaskStride]
+static_assert(kSuOffBytes >= 52 * kMaskStride * 2 && kSuOffBytes >= 169 * 4 && kSuCntWords >= kSortCntWords, "shared areas");
+constexpr int kSuLg = kSuOff + kSuOffBytes;              // uint16 [kSortN]   tie-group start per sorted position
 constexpr int kSuRt = kSuLg + kSortN * 2;                // uint16 [kSortN]   tie-group end, indexed by group start
-constexpr int kSuLp = kSuRt + kSortN * 2;                // uint16 [52][52]   sorted position of list entries
-constexpr int kSuBlob = (kSuLp + 52 * 52 * 2 + 15) / 16 * 16;  // the table blob
+constexpr int kSuBlob = (kSuRt + kSortN * 2 + 15) / 16 * 16;  // the table blob
 constexpr int kSuWarp = kSuBlob + kTabBytes;             // uint32 [16] warp totals of the block scan
 constexpr int kSetupSmem = kSuWarp + 64;
-static_assert(kSuCnt % 4 == 0 && kSuBlob % 16 == 0 && kSuWarp % 4 == 0, "alignment");
+static_assert(kSuCnt % 4 == 0 && kSuOff % 4 == 0 && kSuBlob % 16 == 0 && kSuWarp % 4 == 0, "alignment");
 
 // Exclusive prefix over `words*4` byte counters (in memory order) -> uint16 offsets.  Every
 // thread takes `words_per_thread` consecutive words.  Ends with a barrier.
@@ -102,17 +108,19 @@ __global__ void __launch_bounds__(kSetupThreads, 3) board_setup_kernel(const int
     uint16_t* val = reinterpret_cast<uint16_t*>(smem + kSuVal);
     uint32_t* cnt = reinterpret_cast<uint32_t*>(smem + kSuCnt);
     unsigned char* cnt8 = smem + kSuCnt;
+    uint32_t* cmask = reinterpret_cast<uint32_t*>(smem + kSuCnt);   // [52][kMaskStride], after the sort
     uint16_t* off = reinterpret_cast<uint16_t*>(smem + kSuOff);
+    int32_t* pair_score = reinterpret_cast<int32_t*>(smem + kSuOff);  // [13][13], before the sort
+    uint16_t* cpre = reinterpret_cast<uint16_t*>(smem + kSuOff);      // [52][kMaskStride], after the sort
     uint16_t* lg = reinterpret_cast<uint16_t*>(smem + kSuLg);
     uint16_t* rt = reinterpret_cast<uint16_t*>(smem + kSuRt);
-    uint16_t* lp = reinterpret_cast<uint16_t*>(smem + kSuLp);
     unsigned char* blob = smem + kSuBlob;
     uint32_t* warp_tot = reinterpret_cast<uint32_t*>(smem + kSuWarp);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t lt_mask = (1u << lane) - 1u;
     const int64_t b = blockIdx.x;
 
-    // ---- 1. strengths.  The board's share of the suit masks and rank counts is common ----
+    // ---- 1. strengths ----
     int bc[5];
 #pragma unroll
     for (int i = 0; i < 5; ++i) bc[i] = boards[b * 5 + i];
@@ -124,29 +132,47 @@ __global__ void __launch_bounds__(kSetupThreads, 3) board_setup_kernel(const int
         bsuits |= 1ull << bit;
         bchain.add(1u << (bit & 15));
     }
+    if (tid < 169) {  // rank part per pair of hole ranks (every occurrence of a rank counts, repeated card ids included)
+        const int r1 = tid / 13, r2 = tid - 13 * r1;
+        RankChain ch = bchain;
+        ch.add(1u << r1);
+        ch.add(1u << r2);
+        pair_score[tid] = score_rank_part(ch.classes(), ch.seen);
+    }
+    // the one suit of the board that can make a flush (three or more cards), if any
+    int fsuit = -1;
+    uint32_t fboard = 0;
+#pragma unroll
+    for (int su = 0; su < 4; ++su) {
+        const uint32_t ms = (uint32_t)(bsuits >> (16 * su)) & 0x1fffu;
+        if (__popc(ms) >= 3) {
+            fsuit = su;
+            fboard = ms;
+        }
+    }
+    for (int i = tid; i < kSortCntWords; i += kSetupThreads) cnt[i] = 0u;
+    __syncthreads();
     for (int h = tid; h < kSortN; h += kSetupThreads) {
         uint32_t k = 0xffffffffu;
         if (h < P2B_NUM_HANDS) {
             const int b1 = card_bit(combos->c1[h]), b2 = card_bit(combos->c2[h]);
-            const uint64_t suits = bsuits | (1ull << b1) | (1ull << b2);
-            RankChain ch = bchain;
-            ch.add(1u << (b1 & 15));
-            ch.add(1u << (b2 & 15));
-            const uint32_t lo = (uint32_t)suits, hi = (uint32_t)(suits >> 32);
-            int32_t s;
-            if (__popcll(suits) == 7)  // seven distinct cards: table walk (tables read through L1)
-                s = score_distinct_lut(lo & 0x1fffu, (lo >> 16) & 0x1fffu, hi & 0x1fffu, (hi >> 16) & 0x1fffu,
-                                       lut->mask_entry, lut->type_entry);
-            else
-                s = score_from_masks(lo & 0x1fffu, (lo >> 16) & 0x1fffu, hi & 0x1fffu, (hi >> 16) & 0x1fffu,
-                                     ch.classes());
+            int32_t s = pair_score[(b1 & 15) * 13 + (b2 & 15)];
+            if (fsuit >= 0) {
+                const uint32_t fm = fboard | ((b1 >> 4) == fsuit ? 1u << (b1 & 15) : 0u) |
+                                    ((b2 >> 4) == fsuit ? 1u << (b2 & 15) : 0u);
+                if (__popc(fm) >= 5) {  // flush: the five highest ranks of the suit; straight flush: its highest window
+                    const uint32_t ef = lut->mask_entry[fm];
+                    s = max(s, (int32_t)((6u << 20) | (ef & 0xFFFFFu)));
+                    const uint32_t sf = ef >> 28;
+                    if (sf) s = max(s, (int32_t)((9u << 20) | ((sf - 1u) << 16)));
+                }
+            }
             if (scores) scores[b * P2B_NUM_HANDS + h] = s;
             k = (uint32_t)s;
         }
         key[h] = k;
         val[h] = (uint16_t)h;
     }
-    for (int i = tid; i < kCntWords; i += kSetupThreads) cnt[i] = 0u;
     __syncthreads();
 
     // ---- 2. stable radix sort; buffers alternate, the result ends in buffer 0 ----
@@ -172,14 +198,15 @@ __global__ void __launch_bounds__(kSetupThreads, 3) board_setup_kernel(const int
             if (rnk[i] == 0) cnt8[slot[i]] = (unsigned char)__popc(peers);
         }
         __syncthreads();
-        scan_byte_counts<2>(cnt, kDigits * kSortChunks / 4, off, warp_tot);
+        scan_byte_counts<2>(cnt, kSortCntWords, off, warp_tot);
 #pragma unroll
         for (int i = 0; i < kSortRounds; ++i) {
             const int dest = off[slot[i]] + rnk[i];
             kdst[dest] = kk[i];
             vdst[dest] = vv[i];
         }
-        for (int i = tid; i < kCntWords; i += kSetupThreads) cnt[i] = 0u;
+        // the counters of the next pass, or (after the last one) the card masks that take their place
+        for (int i = tid; i < (pass + 1 < kSortPasses ? kSortCntWords : kSuCntWords); i += kSetupThreads) cnt[i] = 0u;
         __syncthreads();
     }
 
@@ -217,44 +244,22 @@ __global__ void __launch_bounds__(kSetupThreads, 3) board_setup_kernel(const int
             if (k > 0 && k <= P2B_NUM_HANDS && lg[k] == k) rt[lg[k - 1]] = (uint16_t)k;
         }
     }
-    __syncthreads();
 
-    // ---- 4. per-card lists: incidence i = (sorted position i/2, lower or upper card) ----
-#pragma unroll 1
-    for (int r = 0; r < kIncRounds; ++r) {
-        const int chunk = warp + kSetupWarps * r;
-        if (chunk >= kIncChunks) break;  // uniform per warp
-        const int i = 32 * chunk + lane;
-        int card = 63;
-        if (i < kIncidences) {
-            const int h = val[i >> 1];
-            card = (i & 1) ? combos->c2[h] : combos->c1[h];
-        }
-        const uint32_t peers = __match_any_sync(0xffffffffu, card);
-        if (card < 52 && __popc(peers & lt_mask) == 0) cnt8[card * kIncChunks + chunk] = (unsigned char)__popc(peers);
-    }
-    __syncthreads();
-    scan_byte_counts<4>(cnt, kCntWords, off, warp_tot);
+    // ---- 4. per card: which sorted positions hold a hand with that card ----
     BoardTabView tv = view_tables(blob);
     uint16_t* sorted_s = const_cast<uint16_t*>(tv.sorted);
     uint16_t* cardlist_s = const_cast<uint16_t*>(tv.cardlist);
     HandRec* rec_s = const_cast<HandRec*>(tv.rec);
-#pragma unroll 1
-    for (int r = 0; r < kIncRounds; ++r) {
-        const int chunk = warp + kSetupWarps * r;
-        if (chunk >= kIncChunks) break;
-        const int i = 32 * chunk + lane;
-        int card = 63, h = 0;
-        if (i < kIncidences) {
-            h = val[i >> 1];
-            card = (i & 1) ? combos->c2[h] : combos->c1[h];
-        }
-        const uint32_t peers = __match_any_sync(0xffffffffu, card);
-        if (card < 52) {
-            // every card has 51 incidences, so its list starts at 51*card in the card-major scan
-            const int t = off[card * kIncChunks + chunk] - 51 * card + __popc(peers & lt_mask);
-            cardlist_s[t * 52 + card] = (uint16_t)h;
-            lp[card * 52 + t] = (uint16_t)(i >> 1);
+    int hh[kSortRounds], c1s[kSortRounds], c2s[kSortRounds];
+#pragma unroll
+    for (int i = 0; i < kSortRounds; ++i) {
+        const int k = tid + kSetupThreads * i;
+        hh[i] = k < P2B_NUM_HANDS ? val[k] : 0;
+        c1s[i] = combos->c1[hh[i]];
+        c2s[i] = combos->c2[hh[i]];
+        if (k < P2B_NUM_HANDS) {
+            atomicOr(cmask + c1s[i] * kMaskStride + (k >> 5), 1u << (k & 31));
+            atomicOr(cmask + c2s[i] * kMaskStride + (k >> 5), 1u << (k & 31));
         }
     }
     if (tid < (kTabCardListBytes - 51 * 52 * 2) / 2) cardlist_s[51 * 52 + tid] = 0;
@@ -270,70 +275,46 @@ __global__ void __launch_bounds__(kSetupThreads, 3) board_setup_kernel(const int
         reinterpret_cast<unsigned long long*>(blob)[1] = 0ull;
     }
     __syncthreads();
-
-    // ---- 5. list entries before the tie group and before its end, per hand and card ----
-    // Entries of one tie group are consecutive in a card's list.  A warp takes a list (51
-    // entries: lane and lane+32): nb = index of the first entry of the run, ne = index after
-    // its last one, by a max scan and a reverse min scan over run starts.
+    // bits of a card's mask before each of its words: a warp per card, a lane per word (and word + 32)
     for (int card = warp; card < 52; card += kSetupWarps) {
-        const uint16_t* list = lp + card * 52;
-        const int tA = lane, tB = lane + 32;
-        const bool hasB = tB < 51;
-        const int kA = list[tA], kB = hasB ? list[tB] : 0;
-        const int LA = lg[kA], LB = hasB ? (int)lg[kB] : -1;
-        int prevA = __shfl_up_sync(0xffffffffu, LA, 1);
-        int prevB = __shfl_up_sync(0xffffffffu, LB, 1);
-        const int lastA = __shfl_sync(0xffffffffu, LA, 31);
-        if (lane == 0) {
-            prevA = -2;
-            prevB = lastA;
-        }
-        const bool startA = LA != prevA, startB = hasB && LB != prevB;
-        // latest run start at or before each entry
-        int nbA = startA ? tA : -1, nbB = startB ? tB : -1;
+        const uint32_t* mrow = cmask + card * kMaskStride;
+        const int v0 = __popc(mrow[lane]), v1 = lane + 32 < kMaskWords ? __popc(mrow[lane + 32]) : 0;
+        int i0 = v0, i1 = v1;
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
-            const int ua = __shfl_up_sync(0xffffffffu, nbA, d), ub = __shfl_up_sync(0xffffffffu, nbB, d);
+            const int u0 = __shfl_up_sync(0xffffffffu, i0, d), u1 = __shfl_up_sync(0xffffffffu, i1, d);
             if (lane >= d) {
-                nbA = max(nbA, ua);
-                nbB = max(nbB, ub);
+                i0 += u0;
+                i1 += u1;
             }
         }
-        nbB = max(nbB, __shfl_sync(0xffffffffu, nbA, 31));
-        // first run start after each entry (51 if none)
-        int neA = startA ? tA : 51, neB = startB ? tB : 51;
+        const int first32 = __shfl_sync(0xffffffffu, i0, 31);
+        cpre[card * kMaskStride + lane] = (uint16_t)(i0 - v0);
+        if (lane + 32 < kMaskWords) cpre[card * kMaskStride + lane + 32] = (uint16_t)(first32 + i1 - v1);
+    }
+    __syncthreads();
+
+    // ---- 5. per hand: place it in its two cards' lists; list entries before its tie group and before the group's end ----
+    auto below = [&](int card, int pos) {  // entries of the card's list at sorted positions < pos (pos <= 1326)
+        const int w = pos >> 5;
+        return (int)cpre[card * kMaskStride + w] + __popc(cmask[card * kMaskStride + w] & ((1u << (pos & 31)) - 1u));
+    };
 #pragma unroll
-        for (int d = 1; d < 32; d <<= 1) {
-            const int da = __shfl_down_sync(0xffffffffu, neA, d), db = __shfl_down_sync(0xffffffffu, neB, d);
-            if (lane + d < 32) {
-                neA = min(neA, da);
-                neB = min(neB, db);
-            }
-        }
-        // neA/neB now hold the first start at or after the entry; shift by one entry
-        const int firstB = __shfl_sync(0xffffffffu, neB, 0);
-        int afterA = __shfl_down_sync(0xffffffffu, neA, 1), afterB = __shfl_down_sync(0xffffffffu, neB, 1);
-        if (lane == 31) {
-            afterA = firstB;
-            afterB = 51;
-        }
-        afterA = min(afterA, firstB);
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-            if (half == 1 && !hasB) break;
-            const int k = half ? kB : kA, L = half ? LB : LA, nb = half ? nbB : nbA, ne = half ? afterB : afterA;
-            const int h = val[k];
-            HandRec* rr = rec_s + h;
-            if (card == combos->c1[h]) {  // the hand's lower card
-                rr->lpos = (uint16_t)L;
-                rr->rpos = rt[L];
-                rr->nb0 = (uint8_t)nb;
-                rr->ne0 = (uint8_t)ne;
-            } else {
-                rr->nb1 = (uint8_t)nb;
-                rr->ne1 = (uint8_t)ne;
-            }
-        }
+    for (int i = 0; i < kSortRounds; ++i) {
+        const int k = tid + kSetupThreads * i;
+        if (k >= P2B_NUM_HANDS) continue;
+        const int h = hh[i], c1 = c1s[i], c2 = c2s[i];
+        const int L = lg[k], R = rt[L];
+        cardlist_s[below(c1, k) * 52 + c1] = (uint16_t)h;
+        cardlist_s[below(c2, k) * 52 + c2] = (uint16_t)h;
+        HandRec r;
+        r.lpos = (uint16_t)L;
+        r.rpos = (uint16_t)R;
+        r.nb0 = (uint8_t)below(c1, L);
+        r.ne0 = (uint8_t)below(c1, R);
+        r.nb1 = (uint8_t)below(c2, L);
+        r.ne1 = (uint8_t)below(c2, R);
+        rec_s[h] = r;
     }
     __syncthreads();
     if (tabs) {
