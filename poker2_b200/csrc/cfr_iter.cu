@@ -40,8 +40,10 @@ namespace {
 
 constexpr int kVpt = P2B_ITER_VPT;    // hands per thread
 constexpr int kCtas = P2B_ITER_CTAS;  // blocks per SM
-static_assert((kVpt == 2 && kCtas == 1) || (kVpt == 3 && kCtas == 2), "supported configurations");
-constexpr int kNT = P2B_HPAD / kVpt;  // threads per block
+static_assert((kVpt == 2 && kCtas == 1) || (kVpt == 3 && kCtas == 2) || (kVpt == 4 && kCtas == 2), "supported configurations");
+constexpr int kHT = P2B_HPAD / kVpt;          // threads that own hands
+constexpr int kNT = (kHT + 31) / 32 * 32;     // threads per block: whole warps; the extra ones repeat the last hand thread's
+                                              // per-hand work (same loads, same values stored) and share the cross-hand units
 constexpr bool kDouble = kCtas == 1;  // staged rows and tables double buffered, units one node ahead
 constexpr int kSets = kDouble ? 2 : 1;
 constexpr int kK = kCfrMaxChildren;
@@ -55,7 +57,8 @@ constexpr int kTsCs = 0;                                // double [kCsRows][52] 
 constexpr int kTsS = kTsCs + kCsRows * 52 * 8;          // double [kCsRows] row totals
 constexpr int kTsPref = kTsS + kCsRows * 8;             // float [2][HPAD] strength-order prefix sums
 constexpr int kTsPc = kTsPref + 2 * P2B_HPAD * 4;       // float [2][52*52] per-card prefix sums
-constexpr int kTsBytes = kTsPc + 2 * 52 * 52 * 4;
+constexpr int kTsTot = kTsPc + 2 * 52 * 52 * 4;         // float [2][64] whole mass per card (consecutive cards, consecutive banks)
+constexpr int kTsBytes = kTsTot + 2 * 64 * 4;
 
 // ---- shared memory carve-up (bytes) ----
 constexpr int kOffTab = 0;
@@ -186,8 +189,7 @@ __device__ __forceinline__ void norm_row(float allowed_prob, const HandInfo<VPT>
 
 // Normalises the rows x[0], x[1] over hands through rows 0 and 1 of staging set 0; leaves the sums in B.fsum.
 template <int VPT>
-__device__ __forceinline__ void normalize_pair(IterBlock& B, const HandInfo<VPT>& hi, FV<VPT> (&x)[2]) {
-    const int tid = threadIdx.x;
+__device__ __forceinline__ void normalize_pair(IterBlock& B, const HandInfo<VPT>& hi, FV<VPT> (&x)[2], int tid) {
     sth<VPT>(B.set_row(0, 0), tid, x[0]);
     sth<VPT>(B.set_row(0, 1), tid, x[1]);
     __syncthreads();
@@ -429,6 +431,7 @@ __device__ __forceinline__ void table_units(const IterBlock& B, const float* __r
     double* __restrict__ S_out = reinterpret_cast<double*>(ts + kTsS);
     float* __restrict__ pref_out = reinterpret_cast<float*>(ts + kTsPref);
     float* __restrict__ pc_out = reinterpret_cast<float*>(ts + kTsPc);
+    float* __restrict__ tot_out = reinterpret_cast<float*>(ts + kTsTot);
     while (true) {
         int unit = 0;
         if (lane == 0) unit = atomicAdd(queue, 1);
@@ -538,6 +541,7 @@ __device__ __forceinline__ void table_units(const IterBlock& B, const float* __r
                         out[i] = (float)acc;
                     }
                     if (q < 3) out[12] = (float)(acc + (double)v[12]);
+                    else tot_out[slot * 64 + c] = (float)acc;  // == row[51]
                 }
             }
         }
@@ -607,14 +611,14 @@ __device__ __forceinline__ void iter_up_stage(int pass, const CfrParams& p, Iter
 template <int VPT>
 __device__ __forceinline__ void showdown_ev(const IterBlock& B, const HandInfo<VPT>& hi, int tid,
                                             const float* __restrict__ x, const float* __restrict__ pref,
-                                            const float* __restrict__ pc, FV<VPT>& ev) {
+                                            const float* __restrict__ pc, const float* __restrict__ tot, FV<VPT>& ev) {
     const BoardTabView tv = view_tables(B.tab);
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
         float e = 0.0f;
         if (hi.valid[i]) {
             const int h = hand_of<VPT>(tid, i);
-            e = showdown_hand_ev(tv.rec[h], hi.c1[i], hi.c2[i], x[h], hi.allowed[i], pref, pc);
+            e = showdown_hand_ev(tv.rec[h], hi.c1[i], hi.c2[i], x[h], hi.allowed[i], pref, pc, tot[hi.c1[i]], tot[hi.c2[i]]);
         }
         ev.v[i] = e;
     }
@@ -636,6 +640,7 @@ __device__ __forceinline__ void iter_up_hands(int pass, const CfrParams& p, Iter
     const double* __restrict__ St = reinterpret_cast<const double*>(ts + kTsS);
     const float* __restrict__ pref = reinterpret_cast<const float*>(ts + kTsPref);
     const float* __restrict__ pc = reinterpret_cast<const float*>(ts + kTsPc);
+    const float* __restrict__ tot = reinterpret_cast<const float*>(ts + kTsTot);
     const FV<VPT> b_a = ldh<VPT>(B.set_row(set, 0), tid), b_o = ldh<VPT>(B.set_row(set, 1), tid);
     FV<VPT> wgt, denm, acc_a, acc_o;
     Divisor ddenm[VPT];
@@ -688,8 +693,8 @@ __device__ __forceinline__ void iter_up_hands(int pass, const CfrParams& p, Iter
             } else if (ch.kind == kShowdownLeaf) {
                 // the acting player's hands against the other player's beliefs, and the reverse at the leaf
                 FV<VPT> eva, evo;
-                showdown_ev<VPT>(B, hi, tid, B.set_row(set, 1), pref, pc, eva);
-                if (c == sd) showdown_ev<VPT>(B, hi, tid, B.set_row(set, kRowLeaf), pref + P2B_HPAD, pc + 52 * 52, evo);
+                showdown_ev<VPT>(B, hi, tid, B.set_row(set, 1), pref, pc, tot, eva);
+                if (c == sd) showdown_ev<VPT>(B, hi, tid, B.set_row(set, kRowLeaf), pref + P2B_HPAD, pc + 52 * 52, tot + 64, evo);
                 if (c != sd) {
                     // A further showdown child (a call and an all-in of the same size; rare): its tables
                     // are built here, in one more block-wide round, in place of the first one's.
@@ -708,7 +713,7 @@ __device__ __forceinline__ void iter_up_hands(int pass, const CfrParams& p, Iter
                     __syncthreads();
                     table_units(B, B.set_row(set, 0), B.ts + set * kTsBytes, 0, true, B.misc + 6);
                     __syncthreads();
-                    showdown_ev<VPT>(B, hi, tid, B.set_row(set, kRowLeaf), pref + P2B_HPAD, pc + 52 * 52, evo);
+                    showdown_ev<VPT>(B, hi, tid, B.set_row(set, kRowLeaf), pref + P2B_HPAD, pc + 52 * 52, tot + 64, evo);
                 }
                 const float pot_a = a == 0 ? ch.v0 : ch.v1, pot_o = a == 0 ? ch.v1 : ch.v0;
                 const Divisor dscale = make_divisor(B.sg.scale);
@@ -843,7 +848,8 @@ __global__ void __launch_bounds__(kNT, kCtas) cfr_iter_kernel(const CfrParams p)
     B.max_internal = p.max_internal;
     B.scr = p.scratch + (long long)(blockIdx.x / kCtas) * p.scratch_stride +
             (long long)(blockIdx.x % kCtas) * (p.scratch_stride / kCtas);
-    const int tid = threadIdx.x;
+    const int rtid = threadIdx.x;                        // this thread
+    const int tid = rtid < kHT ? rtid : kHT - 1;         // the hand thread whose per-hand work it does
 
     HandInfo<VPT> hi;
 #pragma unroll
@@ -857,7 +863,7 @@ __global__ void __launch_bounds__(kNT, kCtas) cfr_iter_kernel(const CfrParams p)
 
     while (true) {
         __syncthreads();
-        if (tid == 0) B.misc[0] = atomicAdd(p.work_counter, 1);
+        if (rtid == 0) B.misc[0] = atomicAdd(p.work_counter, 1);
         __syncthreads();
         const int s = B.misc[0];
         if (s >= p.num_subgames) break;
@@ -865,10 +871,10 @@ __global__ void __launch_bounds__(kNT, kCtas) cfr_iter_kernel(const CfrParams p)
         B.sample_pass = p.sample_pass ? p.sample_pass[s] : -2;
         {
             const uint4* src = reinterpret_cast<const uint4*>(p.nodes + B.sg.node_begin);
-            for (int i = tid; i < B.sg.n_nodes; i += NT) reinterpret_cast<uint4*>(B.nodes)[i] = src[i];
+            for (int i = rtid; i < B.sg.n_nodes; i += NT) reinterpret_cast<uint4*>(B.nodes)[i] = src[i];
             if (B.sg.table_index >= 0) {
                 const uint4* t = reinterpret_cast<const uint4*>(p.tables + (long long)B.sg.table_index * kTabBytes);
-                for (int i = tid; i < kTabBytes / 16; i += NT) reinterpret_cast<uint4*>(B.tab)[i] = t[i];
+                for (int i = rtid; i < kTabBytes / 16; i += NT) reinterpret_cast<uint4*>(B.tab)[i] = t[i];
             }
         }
 #pragma unroll
@@ -880,7 +886,7 @@ __global__ void __launch_bounds__(kNT, kCtas) cfr_iter_kernel(const CfrParams p)
         float* cr = p.carry_roots + (long long)s * 4 * P2B_HPAD;
         __syncthreads();
         // per node: list of the internal nodes, where each player's reach is stored, the showdown child
-        for (int i = tid; i < B.sg.n_nodes; i += NT) {
+        for (int i = rtid; i < B.sg.n_nodes; i += NT) {
             const NodeRec nd = B.nodes[i];
             if (nd.kind != kInternal) continue;
             B.ilist[nd.internal_idx] = (uint8_t)i;
@@ -914,7 +920,7 @@ __global__ void __launch_bounds__(kNT, kCtas) cfr_iter_kernel(const CfrParams p)
                 root_b[1] = ldh<VPT>(cr + 3 * P2B_HPAD, tid);
                 sth<VPT>(cr, tid, root_b[0]);
                 sth<VPT>(cr + P2B_HPAD, tid, root_b[1]);
-                normalize_pair<VPT>(B, hi, root_b);
+                normalize_pair<VPT>(B, hi, root_b, tid);
                 sth<VPT>(cr + 2 * P2B_HPAD, tid, root_b[0]);
                 sth<VPT>(cr + 3 * P2B_HPAD, tid, root_b[1]);
             }

@@ -344,7 +344,8 @@ constexpr int kEvP = 2 * kEvStage;                      // float [2][HPAD]   (tw
 constexpr int kEvPC = kEvP + 2 * P2B_HPAD * 4;          // float [2][52*52]
 constexpr int kEvQ = kEvPC + 2 * 52 * 52 * 4;           // double [8]
 constexpr int kEvCombo = kEvQ + 64;                     // uint8 [2][1326 (+pad)]
-constexpr int kEvalSmem = kEvCombo + 2 * 1328;
+constexpr int kEvTot = kEvCombo + 2 * 1328;             // float [2][64] mass of all hands holding a card
+constexpr int kEvalSmem = kEvTot + 2 * 64 * 4;
 static_assert(kEvQ % 8 == 0, "alignment");
 
 __global__ void __launch_bounds__(kEvalThreads, 2) showdown_eval_kernel(
@@ -357,6 +358,7 @@ __global__ void __launch_bounds__(kEvalThreads, 2) showdown_eval_kernel(
     double* qtot = reinterpret_cast<double*>(smem + kEvQ);
     uint8_t* c1s = smem + kEvCombo;
     uint8_t* c2s = c1s + 1328;
+    float* PCT = reinterpret_cast<float*>(smem + kEvTot);  // consecutive cards in consecutive banks
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     for (int h = tid; h < P2B_NUM_HANDS; h += kEvalThreads) {
         c1s[h] = combos->c1[h];
@@ -432,6 +434,7 @@ __global__ void __launch_bounds__(kEvalThreads, 2) showdown_eval_kernel(
                         acc += (double)v[i];
                         out[13 * q + i + 1] = (float)acc;
                     }
+                if (q == 3) PCT[p * 64 + c] = (float)acc;  // == out[51]
             }
         }
         // quarter totals of the strength-order scans: task = player*4 + quarter, last warps first
@@ -489,8 +492,9 @@ __global__ void __launch_bounds__(kEvalThreads, 2) showdown_eval_kernel(
             const int c1 = c1s[h], c2 = c2s[h];
             const bool allowed = (((bmask >> c1) | (bmask >> c2)) & 1ull) == 0;
             const HandRec r = tv.rec[h];
-            const float ev0 = showdown_hand_ev(r, c1, c2, x[P2B_NUM_HANDS + h], allowed, P + P2B_HPAD, PC + 52 * 52);
-            const float ev1 = showdown_hand_ev(r, c1, c2, x[h], allowed, P, PC);
+            const float ev0 = showdown_hand_ev(r, c1, c2, x[P2B_NUM_HANDS + h], allowed, P + P2B_HPAD, PC + 52 * 52,
+                                               PCT[64 + c1], PCT[64 + c2]);
+            const float ev1 = showdown_hand_ev(r, c1, c2, x[h], allowed, P, PC, PCT[c1], PCT[c2]);
             __stcs(vrow + h, div_exact(__fmul_rn(ev0, pot0), dscale));
             __stcs(vrow + P2B_NUM_HANDS + h, div_exact(__fmul_rn(ev1, pot1), dscale));
         }

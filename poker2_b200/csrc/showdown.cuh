@@ -53,9 +53,12 @@ __host__ __device__ __forceinline__ BoardTabView view_tables(const unsigned char
 }
 
 // One hero hand of the showdown formula.  P: [1327] prefix in strength order; PC: [52][52]
-// per-card prefix (PC[c*52+t] = mass of the t weakest hands holding c); x: opponent range.
+// per-card prefix (PC[c*52+t] = mass of the t weakest hands holding c); x: opponent range;
+// tot1, tot2: the whole mass of the hands holding c1 / c2 (PC[c*52+51], which a caller may keep in a
+// table of its own).
 __device__ __forceinline__ float showdown_hand_ev(const HandRec r, int c1, int c2, float xh, bool allowed,
-                                                  const float* __restrict__ P, const float* __restrict__ PC) {
+                                                  const float* __restrict__ P, const float* __restrict__ PC, float tot1,
+                                                  float tot2) {
     const float PL = P[r.lpos], PR = P[r.rpos];
     const float* pc1 = PC + c1 * 52;
     const float* pc2 = PC + c2 * 52;
@@ -63,7 +66,7 @@ __device__ __forceinline__ float showdown_hand_ev(const HandRec r, int c1, int c
     const float win = __fsub_rn(__fsub_rn(PL, a0), b0);
     const float seg = __fsub_rn(PR, PL);
     const float tie = __fadd_rn(__fsub_rn(__fsub_rn(seg, __fsub_rn(a1, a0)), __fsub_rn(b1, b0)), xh);
-    float den = __fadd_rn(__fsub_rn(__fsub_rn(1.0f, pc1[51]), pc2[51]), xh);
+    float den = __fadd_rn(__fsub_rn(__fsub_rn(1.0f, tot1), tot2), xh);
     den = fmaxf(den, 1e-8f);
     const Divisor d = make_divisor(den);
     bool bad = false;
@@ -75,6 +78,10 @@ __device__ __forceinline__ float showdown_hand_ev(const HandRec r, int c1, int c
     const float lp = __fsub_rn(__fsub_rn(1.0f, wp), tp);
     const float ev = __fsub_rn(wp, lp);
     return (allowed && den > 1e-8f) ? ev : 0.0f;
+}
+__device__ __forceinline__ float showdown_hand_ev(const HandRec r, int c1, int c2, float xh, bool allowed,
+                                                  const float* __restrict__ P, const float* __restrict__ PC) {
+    return showdown_hand_ev(r, c1, c2, xh, allowed, P, PC, PC[c1 * 52 + 51], PC[c2 * 52 + 51]);
 }
 
 }  // namespace p2b

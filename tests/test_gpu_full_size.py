@@ -46,16 +46,28 @@ def test_river_batch_4096_subgames(cuda_device):
     allowed = torch.from_numpy(cards.allowed_mask(boards.numpy()))[torch.from_numpy(trees.root_of[:top])]
     dev = (sums - 1.0).abs()[internal][allowed[internal]]
     assert dev.max().item() < 1e-5
-    # (c) two subgames against the oracle
-    two = np.array([17, 4001])
-    t2 = ptree.build_trees(ptree.root_states(pot[two].numpy(), stack[two].numpy()), [0.5, 1.0], 8, max_raises=2)
-    o = ocfr.SubgameOracle(t2.oracle_dict(boards[two].numpy()), ranges[two], iterations=T).solve()
-    got, _ = solver.solve_subgames(boards[two], ranges[two], pot[two], stack[two], iterations=T, max_raises=2,
-                                   device=cuda_device)
-    torch.testing.assert_close(got.level_major(got.policy_avg).cpu()[2:], o.policy_avg[2:], rtol=1e-5, atol=1e-6)
-    torch.testing.assert_close(got.root_values[..., :1326].cpu(), o.values_avg[:2], rtol=1e-5, atol=1e-6)
-    for s_local, s_global in enumerate(two):
-        assert torch.equal(got.root_values[s_local], res.root_values[s_global])
+    # (c) every 64th subgame of the batch (64 roots, ragged trees) against the oracle: the rows the full
+    # batch produced for them, not a separate solve
+    pick = np.arange(0, B, 64)
+    t2 = ptree.build_trees(ptree.root_states(pot[pick].numpy(), stack[pick].numpy()), [0.5, 1.0], 8, max_raises=2)
+    o = ocfr.SubgameOracle(t2.oracle_dict(boards[pick].numpy()), ranges[pick], iterations=T).solve()
+    ex, _ = o.exploitability()
+    sub_layout = solver.device_layout(t2, boards[pick].numpy())
+    to_level = torch.from_numpy(np.asarray(sub_layout.from_level_major))  # level-major row -> subgame-major row of the subsample
+    rows = []
+    for s_local, s_global in enumerate(pick):
+        a, b = layout.subgames[s_global], sub_layout.subgames[s_local]
+        assert a["n_nodes"] == b["n_nodes"]
+        rows.append(torch.arange(int(a["node_begin"]), int(a["node_begin"] + a["n_nodes"])))
+    rows = torch.cat(rows).to(cuda_device)  # rows of the full batch in the subsample's subgame-major order
+    pol = res.policy_avg[rows][to_level.to(cuda_device)][:, :1326].cpu()
+    reg = res.regrets[rows][to_level.to(cuda_device)][:, :1326].cpu()
+    n2 = len(pick)
+    torch.testing.assert_close(pol[n2:], o.policy_avg[n2:], rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(reg[n2:], o.regrets[n2:], rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(res.root_values[torch.from_numpy(pick).to(cuda_device)][..., :1326].cpu(), o.values_avg[:n2],
+                               rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(res.exploitability[torch.from_numpy(pick).to(cuda_device)].cpu(), ex, rtol=1e-4, atol=1e-6)
 
 
 def test_rank_2_pow_26_hands(cuda_device):
