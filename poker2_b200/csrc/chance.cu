@@ -2,6 +2,7 @@
 // indexed add that averages the leaf-model values back per root
 // (p2/search/chance_node_helper.py:359-479, `single_card_chance_values`).
 #include "common.cuh"
+#include "exactdiv.cuh"
 
 #include <cuda_bf16.h>
 
@@ -128,7 +129,7 @@ __global__ void indexed_add_rows_kernel(float* __restrict__ out, const long long
     }
 }
 
-// Fused form of the expansion for a bf16 value network: one block per (root, next card)
+// Fused form of the expansion for a bf16 value network: per (root, next card)
 // sample writes the network's input row directly -- both players' re-blocked, re-normalised
 // beliefs (the arithmetic of chance_expand_kernel, then rounded to bf16), the one-hot of the
 // extended board, the root's three context scalars and zero padding up to `feature_stride`
@@ -136,96 +137,128 @@ __global__ void indexed_add_rows_kernel(float* __restrict__ out, const long long
 // are `player_stride` floats apart (1326 for packed rows, 1344 for the solver's padded rows).
 constexpr int kHandsPerThread = (P2B_NUM_HANDS + kThreads - 1) / kThreads;  // 6
 
-__global__ void chance_expand_features_kernel(const float* __restrict__ pre_beliefs, long long player_stride,
-                                              const long long* __restrict__ boards, int board_len,
-                                              const long long* __restrict__ sample_offsets, long long num_roots,
-                                              const float* __restrict__ context, const ComboTable* __restrict__ combos,
-                                              __nv_bfloat16* __restrict__ features, long long feature_stride,
-                                              long long* __restrict__ root_lookup) {
-    __shared__ double red[kThreads / 32];
-    __shared__ int cnt[kThreads / 32];
-    __shared__ int s_root;
-    __shared__ unsigned long long s_mask;
-    const long long total = sample_offsets[num_roots];
-    for (long long smp = blockIdx.x; smp < total; smp += gridDim.x) {
-        if (threadIdx.x == 0) {
-            long long lo = 0, hi = num_roots - 1;
-            while (lo < hi) {
-                const long long mid = (lo + hi + 1) >> 1;
-                if (sample_offsets[mid] <= smp) lo = mid;
-                else hi = mid - 1;
-            }
-            unsigned long long mask = 0;
-            for (int j = 0; j < board_len; ++j) {
-                const long long c = boards[lo * board_len + j];
-                if (c >= 0) mask |= 1ull << c;
-            }
-            int k = (int)(smp - sample_offsets[lo]), card = 0;
-            for (;; ++card)
-                if (!((mask >> card) & 1ull) && k-- == 0) break;
-            s_root = (int)lo;
-            s_mask = mask | (1ull << card);
-            if (root_lookup) root_lookup[smp] = lo;
-        }
-        __syncthreads();
-        const unsigned long long mask = s_mask;
-        const long long b = s_root;
-        __nv_bfloat16* row = features + smp * feature_stride;
-        for (int p = 0; p < 2; ++p) {
-            const float* src = pre_beliefs + (b * 2 + p) * player_stride;
-            float v[kHandsPerThread];
-            bool ok[kHandsPerThread];
-            double s = 0.0;
-            int n_allowed = 0;
+// A block takes up to kCardsPerBlock consecutive next cards of one root: the root's two belief rows are
+// read once into registers, every card's block-wide sums (mass of the combos that stay allowed, their
+// number) are gathered with one barrier pair for the whole group, then the rows are written.  The
+// per-thread partial sums, the shuffle tree and the order over warps are those of chance_expand_kernel,
+// so the normalised values are the same bits.
+constexpr int kCardsPerBlock = 8;
+constexpr int kCardGroups = (P2B_NUM_CARDS + kCardsPerBlock - 1) / kCardsPerBlock;  // groups per root (the last ones may be empty)
+
+__global__ void __launch_bounds__(kThreads) chance_expand_features_kernel(
+    const float* __restrict__ pre_beliefs, long long player_stride, const long long* __restrict__ boards, int board_len,
+    const long long* __restrict__ sample_offsets, long long num_roots, const float* __restrict__ context,
+    const ComboTable* __restrict__ combos, __nv_bfloat16* __restrict__ features, long long feature_stride,
+    long long* __restrict__ root_lookup) {
+    __shared__ double red[kCardsPerBlock][2][kThreads / 32];
+    __shared__ int cnt[kCardsPerBlock][kThreads / 32];
+    // the two cards of this thread's hands do not depend on the root
+    int c1[kHandsPerThread], c2[kHandsPerThread];
 #pragma unroll
-            for (int i = 0; i < kHandsPerThread; ++i) {
-                const int h = threadIdx.x + i * kThreads;
-                ok[i] = false;
-                v[i] = 0.0f;
-                if (h < P2B_NUM_HANDS) {
-                    ok[i] = (((mask >> combos->c1[h]) | (mask >> combos->c2[h])) & 1ull) == 0;
-                    v[i] = ok[i] ? src[h] : 0.0f;
-                    s += (double)v[i];
-                    n_allowed += ok[i];
+    for (int i = 0; i < kHandsPerThread; ++i) {
+        const int h = threadIdx.x + i * kThreads;
+        c1[i] = h < P2B_NUM_HANDS ? combos->c1[h] : 0;
+        c2[i] = h < P2B_NUM_HANDS ? combos->c2[h] : 0;
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (long long task = blockIdx.x; task < num_roots * kCardGroups; task += gridDim.x) {
+        const long long b = task / kCardGroups;
+        const int k0 = (int)(task - b * kCardGroups) * kCardsPerBlock;
+        const long long first = sample_offsets[b];
+        const int n_free = (int)(sample_offsets[b + 1] - first);
+        if (k0 >= n_free) continue;  // uniform over the block
+        const int n_here = min(kCardsPerBlock, n_free - k0);
+        unsigned long long board_mask = 0;
+        for (int j = 0; j < board_len; ++j) {
+            const long long c = boards[b * board_len + j];
+            if (c >= 0) board_mask |= 1ull << c;
+        }
+        // the k0-th free card, in ascending order; the following ones are the next set bits
+        unsigned long long free_cards = ~board_mask & ((1ull << P2B_NUM_CARDS) - 1ull);
+        for (int k = 0; k < k0; ++k) free_cards &= free_cards - 1ull;
+        const float* src0 = pre_beliefs + (b * 2) * player_stride;
+        const float* src1 = src0 + player_stride;
+        float v0[kHandsPerThread], v1[kHandsPerThread];
+#pragma unroll
+        for (int i = 0; i < kHandsPerThread; ++i) {
+            const int h = threadIdx.x + i * kThreads;
+            const bool on = h < P2B_NUM_HANDS && (((board_mask >> c1[i]) | (board_mask >> c2[i])) & 1ull) == 0;
+            v0[i] = on ? src0[h] : 0.0f;
+            v1[i] = on ? src1[h] : 0.0f;
+            if (!on) c1[i] |= 64;  // marks a hand that no card of this root allows
+        }
+        __syncthreads();  // the previous task's sums have been read
+        {
+            unsigned long long rest = free_cards;
+            for (int k = 0; k < n_here; ++k) {
+                const int card = __ffsll((long long)rest) - 1;
+                rest &= rest - 1ull;
+                double s0 = 0.0, s1 = 0.0;
+                int n_allowed = 0;
+#pragma unroll
+                for (int i = 0; i < kHandsPerThread; ++i) {
+                    const bool ok = c1[i] != card && c2[i] != card && c1[i] < 64;
+                    s0 += (double)(ok ? v0[i] : 0.0f);
+                    s1 += (double)(ok ? v1[i] : 0.0f);
+                    n_allowed += ok;
+                }
+#pragma unroll
+                for (int d = 16; d > 0; d >>= 1) {
+                    s0 += __shfl_xor_sync(0xffffffffu, s0, d);
+                    s1 += __shfl_xor_sync(0xffffffffu, s1, d);
+                    n_allowed += __shfl_xor_sync(0xffffffffu, n_allowed, d);
+                }
+                if (lane == 0) {
+                    red[k][0][warp] = s0;
+                    red[k][1][warp] = s1;
+                    cnt[k][warp] = n_allowed;
                 }
             }
-#pragma unroll
-            for (int d = 16; d > 0; d >>= 1) {
-                s += __shfl_xor_sync(0xffffffffu, s, d);
-                n_allowed += __shfl_xor_sync(0xffffffffu, n_allowed, d);
-            }
-            __syncthreads();
-            if ((threadIdx.x & 31) == 0) {
-                red[threadIdx.x >> 5] = s;
-                cnt[threadIdx.x >> 5] = n_allowed;
-            }
-            __syncthreads();
-            double tot = 0.0;
+        }
+        __syncthreads();
+        unsigned long long rest = free_cards;
+        for (int k = 0; k < n_here; ++k) {
+            const int card = __ffsll((long long)rest) - 1;
+            rest &= rest - 1ull;
+            const long long smp = first + k0 + k;
+            if (threadIdx.x == 0 && root_lookup) root_lookup[smp] = b;
+            __nv_bfloat16* row = features + smp * feature_stride;
+            double tot0 = 0.0, tot1 = 0.0;
             int nall = 0;
+#pragma unroll
             for (int w = 0; w < kThreads / 32; ++w) {
-                tot += red[w];
-                nall += cnt[w];
+                tot0 += red[k][0][w];
+                tot1 += red[k][1][w];
+                nall += cnt[k][w];
             }
-            const float sum = (float)tot;
             const float uni = __fdiv_rn(1.0f, fmaxf((float)nall, 1.0f));
 #pragma unroll
-            for (int i = 0; i < kHandsPerThread; ++i) {
-                const int h = threadIdx.x + i * kThreads;
-                if (h < P2B_NUM_HANDS) {
-                    const float x = sum > 1e-12f ? __fdiv_rn(v[i], fmaxf(sum, 1e-12f)) : (ok[i] ? uni : 0.0f);
-                    row[p * P2B_NUM_HANDS + h] = __float2bfloat16_rn(x);
+            for (int p = 0; p < 2; ++p) {
+                const float sum = (float)(p ? tot1 : tot0);
+                const Divisor d = make_divisor(fmaxf(sum, 1e-12f));  // one divisor per row: exactly rounded quotients
+#pragma unroll
+                for (int i = 0; i < kHandsPerThread; ++i) {
+                    const int h = threadIdx.x + i * kThreads;
+                    if (h < P2B_NUM_HANDS) {
+                        const bool ok = c1[i] != card && c2[i] != card && c1[i] < 64;
+                        const float v = ok ? (p ? v1[i] : v0[i]) : 0.0f;
+                        const float x = sum > 1e-12f ? div_exact(v, d) : (ok ? uni : 0.0f);
+                        row[p * P2B_NUM_HANDS + h] = __float2bfloat16_rn(x);
+                    }
                 }
             }
+            // board one-hot, context, padding
+            const unsigned long long mask = board_mask | (1ull << card);
+            for (long long j = 2 * P2B_NUM_HANDS + threadIdx.x; j < feature_stride; j += kThreads) {
+                const int r = (int)(j - 2 * P2B_NUM_HANDS);
+                float x = 0.0f;
+                if (r < 52) x = ((mask >> r) & 1ull) ? 1.0f : 0.0f;
+                else if (r < 55) x = context[b * 3 + (r - 52)];
+                row[j] = __float2bfloat16_rn(x);
+            }
         }
-        // board one-hot, context, padding
-        for (long long j = 2 * P2B_NUM_HANDS + threadIdx.x; j < feature_stride; j += kThreads) {
-            const int r = (int)(j - 2 * P2B_NUM_HANDS);
-            float x = 0.0f;
-            if (r < 52) x = ((mask >> r) & 1ull) ? 1.0f : 0.0f;
-            else if (r < 55) x = context[b * 3 + (r - 52)];
-            row[j] = __float2bfloat16_rn(x);
-        }
-        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < kHandsPerThread; ++i) c1[i] &= 63;
     }
 }
 
@@ -365,7 +398,7 @@ int p2b_chance_expand_features(const float* pre_beliefs, int64_t player_stride, 
         return set_error(P2B_ERR_ARG, "p2b_chance_expand_features: stride too small");
     int rc = ensure_tables();
     if (rc) return rc;
-    long long grid = num_samples;
+    long long grid = num_roots * kCardGroups;
     if (grid > (long long)sm_count() * 16) grid = (long long)sm_count() * 16;
     chance_expand_features_kernel<<<(unsigned)grid, kThreads, 0, (cudaStream_t)stream>>>(
         pre_beliefs, player_stride, (const long long*)boards, board_len, (const long long*)sample_offsets, num_roots,
