@@ -113,14 +113,17 @@ int p2b_showdown_values(const unsigned char* tables, const int32_t* table_of_row
  *             iteration t_sample, i.e. the policy of pass t_sample-1); rows of subgames whose
  *             sample_pass is outside 0..iterations-1 are left untouched
  *  beliefs_last [rows,2,1344] out (may be NULL): beliefs of the last iteration at the internal
- *             nodes (what sample_leaves returns for the sampled nodes). */
+ *             nodes (what sample_leaves returns for the sampled nodes).
+ *  queue_order [num_subgames] int32 (may be NULL: input order): the subgame taken at each position of the
+ *             queue the thread blocks draw from.  A permutation with the largest trees first shortens the
+ *             tail in which few blocks are still busy; results do not depend on it. */
 int p2b_cfr_solve(const void* subgames, const void* nodes, int32_t num_subgames, int64_t rows, int32_t max_children,
                   int32_t max_internal, const unsigned char* tables, const float* root_beliefs,
                   float* regrets, float* weight_sums, float* policy_avg, float* policy,
                   float* root_values, float* values_avg, float* beliefs_avg, float* exploitability,
                   float* br_values, float* scratch, int64_t scratch_floats, const void* scalars, int32_t iterations, int32_t flags,
                   int32_t init_depth, int32_t* work_counter, int32_t num_blocks, const int32_t* sample_pass,
-                  float* policy_sample, float* beliefs_last, void* stream);
+                  float* policy_sample, float* beliefs_last, const int32_t* queue_order, void* stream);
 int64_t p2b_cfr_scratch_floats(int32_t max_internal, int32_t num_blocks);
 int64_t p2b_cfr_solve_scratch_floats(int32_t max_internal, int32_t max_children, int32_t num_blocks,
                                      int32_t num_subgames, int64_t rows);

@@ -1204,8 +1204,8 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
         __syncthreads();
         if (tid == 0) B.misc[0] = atomicAdd(p.work_counter, 1);
         __syncthreads();
-        const int s = B.misc[0];
-        if (s >= p.num_subgames) break;
+        if (B.misc[0] >= p.num_subgames) break;
+        const int s = p.queue_order ? p.queue_order[B.misc[0]] : B.misc[0];
         B.sg = p.subgames[s];
         // work rows: one set per block, or one per subgame when state is carried between launches
         B.scr = p.scratch + (long long)((p.stepped && !p.scratch_per_block) ? s : (int)blockIdx.x) * p.scratch_stride;
@@ -1334,7 +1334,8 @@ __global__ void __launch_bounds__(kCfrMaxNodes) cfr_validate_kernel(const CfrPar
     const int s = blockIdx.x, i = threadIdx.x;
     const SubgameRec sg = p.subgames[s];
     int bad = sg.n_nodes < 1 || sg.n_nodes > kCfrMaxNodes || sg.n_internal > p.max_internal || sg.node_begin < 0 ||
-              (p.rows > 0 && (long long)sg.node_begin + sg.n_nodes > p.rows);
+              (p.rows > 0 && (long long)sg.node_begin + sg.n_nodes > p.rows) ||
+              (p.queue_order && (unsigned)p.queue_order[s] >= (unsigned)p.num_subgames);
     if (!bad && i < sg.n_nodes) {
         const NodeRec nd = p.nodes[sg.node_begin + i];
         if (nd.kind > kModelLeaf || (nd.kind == kShowdownLeaf && (sg.table_index < 0 || p.tables == nullptr))) bad = 1;

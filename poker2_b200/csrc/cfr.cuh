@@ -77,6 +77,8 @@ struct CfrParams {
                                  // caller's model come from the beliefs under the average policy (:1029, :1133)
     int32_t init_depth;          // depth of the deepest tree of the batch the subgames were built in
     int32_t* work_counter;       // dynamic subgame queue (zeroed by the launcher)
+    const int32_t* queue_order;  // [B] subgame taken at each queue position (may be null: input order); a caller puts
+                                 // the largest trees first so that the last blocks to finish hold small ones
     // ---- stepped mode: a launch runs part of the pass sequence and the state that a whole
     // solve keeps on chip is carried between launches in global memory.  Used when leaves are
     // valued by a caller-side model between the two sweeps of a pass.  All zero / null in

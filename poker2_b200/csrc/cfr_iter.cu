@@ -865,8 +865,8 @@ __global__ void __launch_bounds__(kNT, kCtas) cfr_iter_kernel(const CfrParams p)
         __syncthreads();
         if (rtid == 0) B.misc[0] = atomicAdd(p.work_counter, 1);
         __syncthreads();
-        const int s = B.misc[0];
-        if (s >= p.num_subgames) break;
+        if (B.misc[0] >= p.num_subgames) break;
+        const int s = p.queue_order ? p.queue_order[B.misc[0]] : B.misc[0];
         B.sg = p.subgames[s];
         B.sample_pass = p.sample_pass ? p.sample_pass[s] : -2;
         {

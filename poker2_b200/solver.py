@@ -317,6 +317,13 @@ class SubgameSolver:
             n_scratch = int(_lib.lib().p2b_cfr_scratch_floats(layout.max_internal, self.num_blocks))
         self.scratch = torch.empty(n_scratch, **f32)
         self.work_counter = torch.zeros(4, device=device, dtype=torch.int32)
+        # the thread blocks take subgames from a queue: largest trees first, so that the blocks that finish
+        # last hold small ones (a stable sort: equal sizes keep their input order)
+        if built_on_device:
+            n_nodes = self.subgames.view(torch.int32).reshape(B, 8)[:, 1]
+        else:
+            n_nodes = torch.from_numpy(np.ascontiguousarray(layout.subgames["n_nodes"])).to(device)
+        self.queue_order = torch.argsort(n_nodes, descending=True, stable=True).to(torch.int32).contiguous()
         # leaf sampling: the policy of one scheduled iteration per subgame, beliefs of the last one
         self.policy_sample = torch.zeros(rows, HPAD, **f32) if sampling else None
         self.beliefs_last = torch.zeros(rows, 2, HPAD, **f32) if sampling else None
@@ -374,7 +381,7 @@ class SubgameSolver:
                 p(sc) if iterations else None, iterations, solve_flags(cfr_plus, enforce_zero_sum, cfr_avg),
                 self.layout.tree_depth, p(self.work_counter),
                 self.num_blocks, p(self.sample_pass), p(self.policy_sample), p(self.beliefs_last),
-                _lib.stream_ptr(self.device))
+                p(self.queue_order), _lib.stream_ptr(self.device))
         self.launches += 1
         if check:
             self.raise_if_refused()
