@@ -127,6 +127,13 @@ __device__ __forceinline__ void async_row(float* smem_row, const float* global_r
     if constexpr (VPT == 2) {
         const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_row + VPT * tid);
         asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(global_row + VPT * tid) : "memory");
+    } else {
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int h = tid + i * (P2B_HPAD / VPT);
+            const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_row + h);
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(global_row + h) : "memory");
+        }
     }
 }
 __device__ __forceinline__ void async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
@@ -655,6 +662,25 @@ __device__ __forceinline__ void iter_up_hands(int pass, const CfrParams& p, Iter
     }
     sth<VPT>(B.set_row(set, 0), tid, wgt);  // needed again for the regrets; the beliefs row is spent
     const int sd = B.sdc[ii];
+    // ---- policy of every child as seen by each hand of the other player; replaces the marginal rows ----
+#pragma unroll 1
+    for (int c = 0; c < k; ++c) {
+        const FV<VPT> m = ldh<VPT>(B.set_row(set, kRowM + c), tid);
+        FV<VPT> pio, blk;
+        DivGuard g = guard_begin(ddenm_ok);
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            blk.v[i] = unblocked(cs + (kRowM + c) * 52, St[kRowM + c], hi.c1[i], hi.c2[i], m.v[i]);
+            pio.v[i] = div_g<true>(blk.v[i], ddenm[i].y, ddenm[i].r, g);
+        }
+        if (__builtin_expect(guard_bad(g), 0)) {
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) pio.v[i] = __fdiv_rn(blk.v[i], denm.v[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) pio.v[i] = denm.v[i] > 1e-5f ? pio.v[i] : 0.0f;
+        sth<VPT>(B.set_row(set, kRowM + c), tid, pio);
+    }
     // ---- children: values and backup ----
     {
 #pragma unroll 1
@@ -666,23 +692,7 @@ __device__ __forceinline__ void iter_up_hands(int pass, const CfrParams& p, Iter
                 V_a = ldh<VPT>(B.row_val(ch.internal_idx, a), tid);
                 V_o = ldh<VPT>(B.row_val(ch.internal_idx, o), tid);
             }
-            // policy of this child as seen by each hand of the other player
-            const FV<VPT> m = ldh<VPT>(B.set_row(set, kRowM + c), tid);
-            FV<VPT> pio, blk;
-            {
-                DivGuard g = guard_begin(ddenm_ok);
-#pragma unroll
-                for (int i = 0; i < VPT; ++i) {
-                    blk.v[i] = unblocked(cs + (kRowM + c) * 52, St[kRowM + c], hi.c1[i], hi.c2[i], m.v[i]);
-                    pio.v[i] = div_g<true>(blk.v[i], ddenm[i].y, ddenm[i].r, g);
-                }
-                if (__builtin_expect(guard_bad(g), 0)) {
-#pragma unroll
-                    for (int i = 0; i < VPT; ++i) pio.v[i] = __fdiv_rn(blk.v[i], denm.v[i]);
-                }
-#pragma unroll
-                for (int i = 0; i < VPT; ++i) pio.v[i] = denm.v[i] > 1e-5f ? pio.v[i] : 0.0f;
-            }
+            const FV<VPT> pio = ldh<VPT>(B.set_row(set, kRowM + c), tid);  // computed by the loop above
             if (ch.kind == kFoldLeaf) {
                 const float va = a == 0 ? ch.v0 : -ch.v0;
 #pragma unroll
@@ -742,7 +752,7 @@ __device__ __forceinline__ void iter_up_hands(int pass, const CfrParams& p, Iter
                 acc_a.v[i] = __fadd_rn(acc_a.v[i], __fmul_rn(V_a.v[i], P.v[i]));
                 acc_o.v[i] = __fadd_rn(acc_o.v[i], __fmul_rn(V_o.v[i], pio.v[i]));
             }
-            sth<VPT>(B.set_row(set, kRowM + c), tid, V_a);  // kept for the regrets below; the marginal row is spent
+            sth<VPT>(B.set_row(set, kRowM + c), tid, V_a);  // kept for the regrets below; the row's pio is spent
         }
     }
     if (j != 0) {
