@@ -162,7 +162,7 @@ def run_reference_arm(args, rank: int):
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": dict(workload_config(), workload=f"bounded sample of the batched river workload: {sample}; same tree "
                                                       "abstraction, ranges, pots and stacks as the B=4096 x 256 GPU arm",
-                       batch_per_gpu=n_roots, iterations=iters),
+                       batch_per_gpu=n_roots, iterations=iters, l2="not applicable: host run"),
         "cpu_baseline": {"value": value, "unit": "subgame-iterations/s", "cores": cores, "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": "subgame-iterations/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
