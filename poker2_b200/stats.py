@@ -4,7 +4,8 @@ Same keys and definitions as the upstream evaluator records after a solve
 (p2/search/cfr_evaluator.py: `_record_cfr_entropy` :1607-1616, `_record_cumulative_regret`
 :1634-1672, `_record_action_mix` :1674-1690); the trainer merges them into its metrics
 (p2/rl/cfr_trainer.py:422).  `cfr_delta.*` (the policy change at five iterations, :1574-1605) needs
-the policy before and after single iterations and is not recorded here.
+the policy before and after single iterations and is not recorded here (the upstream graphed fused
+evaluator skips it as well, p2/search/fused_sparse_cfr_evaluator.py:522-527).
 """
 from __future__ import annotations
 
