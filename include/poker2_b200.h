@@ -95,7 +95,11 @@ int p2b_showdown_values(const unsigned char* tables, const int32_t* table_of_row
  *             values, the regret weights and the leaf_beliefs handed to the caller's model are taken at the
  *             beliefs under the average policy instead of the current one (the de-averaging of the model's
  *             values, :997-1018, is the caller's part of set_leaf_values); such a solve keeps every pass in
- *             the general kernel
+ *             the general kernel;
+ *             bit 3 (p2b_cfr_step only): the bottom-up sweep of the start pass and of every iteration pass stores
+ *             the values of every node in values_avg and (iteration passes) the beliefs under the average
+ *             policy, at inner nodes and at the leaves a model values, in beliefs_avg -- the inputs of the
+ *             running value average upstream keeps when value_targets_from_final_policy is off (:1260-1274)
  *  init_depth depth of the deepest tree of the batch (the upstream start pass re-normalises
  *             every belief row once per level of the batch-wide tree)
  *  work_counter four int32, zeroed by the call: [0] the queue the thread blocks take subgames
@@ -141,12 +145,14 @@ int p2b_cfr_iteration_ms(float* ms);
  * pass (policy, reach, beliefs) and its bottom-up sweep (values, regrets).  Passes are
  * numbered -1 (start pass), 0..iterations-1 (DCFR iterations), iterations (final evaluation
  * of the average policy).  A call runs the passes pass_begin..pass_end; `phases` selects the
- * top-down sweep (1), the bottom-up sweep (2) or both (3); with 1 or 2 the range is one pass.
+ * top-down sweep (1), the bottom-up sweep (2) or both (3); with 1 or 2 the range is one pass; 4 (with
+ * pass_begin = pass_end = iterations) runs only the best responses, from the state the final pass left and
+ * the leaf values found in values_avg.
  * The caller's loop is: for every pass { step(pass, 1); leaf_values = model(leaf_beliefs);
  * step(pass, 2); }.  Arrays as in p2b_cfr_solve, plus state carried between calls:
  *  scratch      p2b_cfr_scratch_floats(max_internal, 1) * num_subgames floats (one set of
  *               work rows per subgame instead of per block)
- *  carry_sums   [rows,2] floats ([2,rows,2] with flags bit 2), carry_roots [num_subgames,4,1344] floats (opaque)
+ *  carry_sums   [rows,2] floats ([2,rows,2] with flags bit 2 or 3), carry_roots [num_subgames,4,1344] floats (opaque)
  *  leaf_begin   [num_subgames] int32: first leaf slot of each subgame; a node of kind 3 uses
  *               slot leaf_begin[subgame] + its internal_idx field; leaf_slots = number of slots
  *  leaf_beliefs [slots,2,1344] out (top-down sweep): both players' beliefs at each such leaf
@@ -265,7 +271,9 @@ int p2b_step_update_average_values(float* values_avg, const float* latest, const
 /* fused_avg_values_zero_sum_ (:623-668) with subtract_b=0, scale=1/(old+new);
  * fused_model_values_mix_zero_sum (:1739-1775) with subtract_b=1, scale=NULL:
  * out = (a*coef_a +/- b*coef_b) [*scale] - 0.5*sum_p sum_h out*beliefs (rows of [2,H]).
- * enforce_zero_sum: 0 = no shift; 1 = the sum accumulated in fp64; 2 (H = 1326) = two fp32 sums in the
+ * subtract_b: bit 0 = subtract b's term, bit 1 = divide by *scale instead of multiplying (the non-fused
+ * `update_average_values`, cfr_evaluator.py:1260-1274, divides by old + new).
+ * enforce_zero_sum: 0 = no shift; 1 = the sum accumulated in fp64; 2 (H = 1326, or rows padded to 1344) = two fp32 sums in the
  * order of the CPU row reduction the non-fused upstream code goes through (cfr_evaluator.py:973-976) */
 int p2b_step_mix_zero_sum(const float* a, const float* b, const float* beliefs, const uint8_t* ignore,
                           const float* coef_a, const float* coef_b, const float* scale, float* out, int64_t rows,

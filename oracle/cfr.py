@@ -36,7 +36,7 @@ class SubgameOracle:
                  start_policy: torch.Tensor | None = None, warm_start_iterations: int = 0,
                  warm_start_multiplier: float = 1.0, alpha_final: float | None = None,
                  beta_final: float | None = None, gamma_final: float | None = None,
-                 enforce_zero_sum: bool = False, cfr_avg: bool = False):
+                 enforce_zero_sum: bool = False, cfr_avg: bool = False, final_policy_values: bool = True):
         t = {k: (torch.from_numpy(np.ascontiguousarray(v)) if isinstance(v, np.ndarray) else v)
              for k, v in tree.items()}
         self.offs = [int(x) for x in tree["depth_offsets"]]
@@ -65,6 +65,9 @@ class SubgameOracle:
         # values are taken as a running average and de-averaged
         self.cfr_avg = cfr_avg
         self.last_model_values = None
+        # False: `value_targets_from_final_policy = False` upstream -- values_avg is a running mix of the
+        # per-iteration values (`update_average_values`, :1260-1274) and no final pass recomputes it
+        self.final_policy_values = final_policy_values
         self.dcfr_delay = dcfr_delay
         self.cfr_type = cfr_type
         self.cfr_plus = cfr_plus
@@ -331,6 +334,22 @@ class SubgameOracle:
         self.update_policy(t)
         self.set_leaf_values(t)
         self.expected_values()
+        if not self.final_policy_values:
+            self.update_average_values(t)
+
+    def _zero_sum(self, values, beliefs):
+        sums = (values * beliefs).sum(dim=2, keepdim=True).mean(dim=1, keepdim=True)
+        sums.masked_fill_(self.done[:, None, None], 0.0)
+        return values - sums
+
+    def update_average_values(self, t):
+        """cfr_evaluator.py:1260-1274."""
+        old, new = self.mixing_weights(t)
+        self.values_avg *= old
+        self.values_avg += new * self.values
+        self.values_avg /= old + new
+        if self.enforce_zero_sum:
+            self.values_avg = self._zero_sum(self.values_avg, self.beliefs_avg)
 
     def finalize(self):
         """update_average_values_final (cfr_evaluator.py:1276-1292)."""
@@ -361,7 +380,8 @@ class SubgameOracle:
             self.warm_start()
         for t in range(self.warm_start_iterations, self.iterations):
             self.iteration(t)
-        self.finalize()
+        if self.final_policy_values:
+            self.finalize()
         return self
 
     # ---- local exploitability of the average policy (cfr_evaluator.py:603-764) ----

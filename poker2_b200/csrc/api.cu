@@ -175,12 +175,16 @@ int p2b_cfr_step(const void* subgames, const void* nodes, int32_t num_subgames, 
                 "null pointer");
     P2B_REQUIRE(max_internal >= 1, "max_internal must be positive");
     P2B_REQUIRE(!exploitability || values_avg, "exploitability needs values_avg");
-    P2B_REQUIRE(flags >= 0 && flags <= 7,
+    P2B_REQUIRE(flags >= 0 && flags <= 15,
                 "flags: bit 0 = CFR+ clamp, bit 1 = zero-sum value outputs, bit 2 = leaf values and regret weights at the "
-                "average-policy beliefs");
+                "average-policy beliefs, bit 3 = keep the node values of every pass");
+    P2B_REQUIRE(!(flags & 8) || (values_avg && beliefs_avg), "flags bit 3 needs values_avg and beliefs_avg");
     P2B_REQUIRE(pass_begin >= -1 && pass_begin <= pass_end && pass_end <= iterations, "pass range outside [-1, iterations]");
-    P2B_REQUIRE(phases >= 1 && phases <= 3, "phases must be 1 (top-down), 2 (bottom-up) or 3 (both)");
+    P2B_REQUIRE((phases >= 1 && phases <= 3) || phases == 4,
+                "phases must be 1 (top-down), 2 (bottom-up), 3 (both) or 4 (best responses only)");
     P2B_REQUIRE(phases == 3 || pass_begin == pass_end, "a single sweep direction covers exactly one pass");
+    P2B_REQUIRE(phases != 4 || (pass_begin == iterations && exploitability), "phases = 4 runs after the final pass and needs "
+                                                                              "the exploitability output");
     P2B_REQUIRE((!leaf_beliefs && !leaf_values) || leaf_begin, "leaf arrays need leaf_begin");
     if (num_blocks <= 0) num_blocks = cfr_default_blocks();
     if (num_blocks > num_subgames) num_blocks = num_subgames;
@@ -218,6 +222,7 @@ int p2b_cfr_step(const void* subgames, const void* nodes, int32_t num_subgames, 
     p.cfr_plus = flags & 1;
     p.enforce_zero_sum = (flags >> 1) & 1;
     p.cfr_avg = (flags >> 2) & 1;
+    p.iter_values = (flags >> 3) & 1;
     p.init_depth = init_depth;
     p.work_counter = work_counter;
     p.stepped = 1;

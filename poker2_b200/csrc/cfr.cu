@@ -430,6 +430,7 @@ __device__ __forceinline__ void sweep_down(int mode_rt, int pass, const CfrParam
         p.policy = nullptr;
         p.start_policy = nullptr;
         p.cfr_avg = 0;
+        p.iter_values = 0;
     }
     // FIXED_MODE >= 0: compiled for that kind of pass alone (the iteration passes of a plain solve:
     // the start- and final-pass code stays out of the hot loop); otherwise the kind is a run-time value
@@ -438,6 +439,9 @@ __device__ __forceinline__ void sweep_down(int mode_rt, int pass, const CfrParam
     // cfr_avg (cfr_evaluator.py:1029, :1133): the bottom-up sweep of an iteration pass takes leaf values and
     // regret weights at the beliefs under the average policy this sweep has just updated
     const bool avgb = (mode == kPassIter) && p.cfr_avg != 0;
+    // the reach and the normalisation sums under the updated average policy are also needed when the node
+    // values of every iteration are kept (their zero-sum shift uses the average beliefs, :1260-1274)
+    const bool avgd = (mode == kPassIter) && (p.cfr_avg != 0 || p.iter_values != 0);
     FV<VPT> mask;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) mask.v[i] = hi.allowed[i] ? 1.0f : 0.0f;
@@ -651,7 +655,7 @@ __device__ __forceinline__ void sweep_down(int mode_rt, int pass, const CfrParam
                 }
             }
         }
-        if (avgb) {
+        if (avgd) {
             // the same once more under the average policy as updated above (its rows were just stored by
             // this thread): reach, the rows whose sums normalise the children's average beliefs
             FV<VPT> rwa = mask, rwna = mask;
@@ -672,7 +676,7 @@ __device__ __forceinline__ void sweep_down(int mode_rt, int pass, const CfrParam
                     u.v[i] = __fmul_rn(prior_a.v[i], t.v[i]);
                 }
                 stv<VPT>(B.stage_row(bank + c), tid, u);
-                if (ch.kind == kModelLeaf) {
+                if (ch.kind == kModelLeaf && avgb) {  // the caller's model sees the average beliefs
                     const FV<VPT> prior_o = pick<VPT>(prior, 1 - a);
                     FV<VPT> w;
 #pragma unroll
@@ -737,10 +741,14 @@ __device__ __forceinline__ void sweep_up(int mode_rt, int pass, const CfrParams&
         p.policy = nullptr;
         p.start_policy = nullptr;
         p.cfr_avg = 0;
+        p.iter_values = 0;
     }
     const int mode = FIXED_MODE >= 0 ? FIXED_MODE : mode_rt;
     const bool update = (mode != kPassFinal) && (pass + 1 < p.iterations);
     const bool avgb = (mode == kPassIter) && p.cfr_avg != 0;  // see sweep_down
+    const bool avgd = (mode == kPassIter) && (p.cfr_avg != 0 || p.iter_values != 0);
+    const bool keep_values = (mode == kPassFinal || p.iter_values != 0) && p.values_avg != nullptr;
+    const bool keep_avg_beliefs = mode == kPassIter && p.iter_values != 0 && p.beliefs_avg != nullptr;
     constexpr int kRowM = 2, kRowLeaf = 2 + kBankRows;
     FV<VPT> mask;
 #pragma unroll
@@ -779,14 +787,38 @@ __device__ __forceinline__ void sweep_up(int mode_rt, int pass, const CfrParams&
         // showdown; rw_a: the acting player's reach the showdown leaves' beliefs derive from.  With cfr_avg
         // both are taken under the average policy (at the root the two kinds of beliefs are the same row).
         FV<VPT> x_o = b_o, rw_a = r_a;
-        if (avgb) {
-            rw_a = mask;
-            if (j != 0) {
-                rw_a = ldv<VPT>(B.rnew(ii, a), tid);
-                const FV<VPT> rw_o = ldv<VPT>(B.rnew(ii, o), tid);
+        FV<VPT> bbar_o = b_o, rbar_a = mask;  // average beliefs of the other player, average reach of the acting one
+        if (avgd && j != 0) {
+            rbar_a = ldv<VPT>(B.rnew(ii, a), tid);
+            const FV<VPT> rw_o = ldv<VPT>(B.rnew(ii, o), tid);
 #pragma unroll
-                for (int i = 0; i < VPT; ++i) x_o.v[i] = __fmul_rn(prior_o.v[i], rw_o.v[i]);
-                apply_norm<VPT>(B, hi, x_o, B.sigb[j * 2 + o]);
+            for (int i = 0; i < VPT; ++i) bbar_o.v[i] = __fmul_rn(prior_o.v[i], rw_o.v[i]);
+            apply_norm<VPT>(B, hi, bbar_o, B.sigb[j * 2 + o]);
+        }
+        if (avgb) {
+            rw_a = rbar_a;
+            x_o = bbar_o;
+        }
+        if (keep_avg_beliefs) {
+            // beliefs under the average policy at this node and at the leaves below it that the caller's
+            // model values (terminal nodes are exempt from the zero-sum shift that reads them)
+            FV<VPT> bbar_a = b_a;
+            if (j != 0) {
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) bbar_a.v[i] = __fmul_rn(prior_a.v[i], rbar_a.v[i]);
+                apply_norm<VPT>(B, hi, bbar_a, B.sigb[j * 2 + a]);
+            }
+            stv<VPT>(B.row2(p.beliefs_avg, j, a), tid, bbar_a);
+            stv<VPT>(B.row2(p.beliefs_avg, j, o), tid, bbar_o);
+            for (int c = 0; c < k; ++c) {
+                if (B.nodes[fc + c].kind != kModelLeaf) continue;
+                const FV<VPT> Pa = ldv<VPT>(B.row1(p.policy_avg, fc + c), tid);
+                FV<VPT> bl;
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) bl.v[i] = __fmul_rn(prior_a.v[i], __fmul_rn(rbar_a.v[i], Pa.v[i]));
+                apply_norm<VPT>(B, hi, bl, B.sigb[(fc + c) * 2 + a]);
+                stv<VPT>(B.row2(p.beliefs_avg, fc + c, a), tid, bl);
+                stv<VPT>(B.row2(p.beliefs_avg, fc + c, o), tid, bbar_o);
             }
         }
         {
@@ -950,9 +982,9 @@ __device__ __forceinline__ void sweep_up(int mode_rt, int pass, const CfrParams&
 #pragma unroll
                 for (int i = 0; i < VPT; ++i) V_a.v[i] = V_o.v[i] = 0.0f;
             }
-            if (mode == kPassFinal && p.values_avg && ch.kind != kInternal) {
+            if (keep_values && ch.kind != kInternal) {
                 FV<VPT> out_a = V_a, out_o = V_o;
-                if (p.enforce_zero_sum && ch.kind == kModelLeaf && p.leaf_beliefs) {
+                if (mode == kPassFinal && p.enforce_zero_sum && ch.kind == kModelLeaf && p.leaf_beliefs) {
                     // a leaf that is not terminal is shifted like an inner node, by its own beliefs
                     const FV<VPT> la = ldv<VPT>(p.leaf_beliefs + B.leaf_row(ch.internal_idx, a), tid);
                     const FV<VPT> lo = ldv<VPT>(p.leaf_beliefs + B.leaf_row(ch.internal_idx, o), tid);
@@ -976,6 +1008,10 @@ __device__ __forceinline__ void sweep_up(int mode_rt, int pass, const CfrParams&
         if (j != 0) {
             stv<VPT>(B.val(ii, a), tid, acc_a);
             stv<VPT>(B.val(ii, o), tid, acc_o);
+        }
+        if (mode != kPassFinal && keep_values) {  // the values of this iteration, as they are
+            stv<VPT>(B.row2(p.values_avg, j, a), tid, acc_a);
+            stv<VPT>(B.row2(p.values_avg, j, o), tid, acc_o);
         }
         if (mode == kPassFinal) {
             // the outputs may be shifted to zero sum; the work rows the parent backs up from are not
@@ -1235,7 +1271,7 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
             root_b[0] = ldv<VPT>(cr + 2 * P2B_HPAD, tid);
             root_b[1] = ldv<VPT>(cr + 3 * P2B_HPAD, tid);
             for (int i = tid; i < 2 * B.sg.n_nodes; i += NT) B.sig[i] = p.carry_sums[(long long)B.sg.node_begin * 2 + i];
-            if (p.cfr_avg)  // the sums under the average policy follow the [rows][2] block of the current ones
+            if (p.cfr_avg || p.iter_values)  // the sums under the average policy follow the [rows][2] block of the current ones
                 for (int i = tid; i < 2 * B.sg.n_nodes; i += NT)
                     B.sigb[i] = p.carry_sums[(p.rows + B.sg.node_begin) * 2 + i];
         } else {
@@ -1291,11 +1327,11 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
             stv<VPT>(cr + 2 * P2B_HPAD, tid, root_b[0]);
             stv<VPT>(cr + 3 * P2B_HPAD, tid, root_b[1]);
             for (int i = tid; i < 2 * B.sg.n_nodes; i += NT) p.carry_sums[(long long)B.sg.node_begin * 2 + i] = B.sig[i];
-            if (p.cfr_avg)
+            if (p.cfr_avg || p.iter_values)
                 for (int i = tid; i < 2 * B.sg.n_nodes; i += NT)
                     p.carry_sums[(p.rows + B.sg.node_begin) * 2 + i] = B.sigb[i];
         }
-        if (p.exploitability && p.values_avg && run_up && pass_last == p.iterations) {
+        if (p.exploitability && p.values_avg && (run_up || (p.stepped && (p.phases & 4))) && pass_last == p.iterations) {
             // local exploitability of the average policy (cfr_evaluator.py:718-764)
             __syncthreads();
             FV<VPT> base[2], br[2];

@@ -75,6 +75,9 @@ struct CfrParams {
     int32_t enforce_zero_sum;    // final pass: value outputs shifted to zero sum (cfr_evaluator.py:957-980, 1289-1292)
     int32_t cfr_avg;             // iteration passes: showdown values, regret weights and the beliefs handed to the
                                  // caller's model come from the beliefs under the average policy (:1029, :1133)
+    int32_t iter_values;         // start and iteration passes store the values of every node in values_avg and (iteration
+                                 // passes) the beliefs under the average policy in beliefs_avg: what a caller mixes into
+                                 // running average values (`update_average_values`, cfr_evaluator.py:1260-1274)
     int32_t init_depth;          // depth of the deepest tree of the batch the subgames were built in
     int32_t* work_counter;       // dynamic subgame queue (zeroed by the launcher)
     const int32_t* queue_order;  // [B] subgame taken at each queue position (may be null: input order); a caller puts
@@ -87,8 +90,9 @@ struct CfrParams {
     int32_t pass_begin;          // first pass of this launch (-1 = start pass, iterations = final pass)
     int32_t pass_end;            // last pass of this launch (inclusive)
     int32_t phases;              // bit 0: top-down sweep, bit 1: bottom-up sweep (+ best responses after
-                                 // the final pass)
-    float* carry_sums;           // [rows][2] normalisation sums of the node beliefs ([2][rows][2] with cfr_avg)
+                                 // the final pass); 4 alone: only the best responses, from the state the final
+                                 // pass left and the leaf values in values_avg
+    float* carry_sums;           // [rows][2] normalisation sums of the node beliefs ([2][rows][2] with cfr_avg or iter_values)
     float* carry_roots;          // [B][4][HPAD] prior (2 rows) and root beliefs (2 rows) of the pass
     const int32_t* leaf_begin;   // [B] first model-leaf slot of each subgame
     float* leaf_beliefs;         // [slots][2][HPAD] beliefs at the model leaves (out, top-down sweep)

@@ -184,8 +184,8 @@ __global__ void mix_zero_sum_kernel(const float* __restrict__ a, const float* __
         double s = 0.0;
         for (int i = threadIdx.x; i < 2 * H; i += blockDim.x) {
             const float x = __fmul_rn(a[base + i], ca), y = __fmul_rn(b[base + i], cb);
-            float v = subtract_b ? __fsub_rn(x, y) : __fadd_rn(x, y);
-            if (scale_p) v = __fmul_rn(v, sc);
+            float v = (subtract_b & 1) ? __fsub_rn(x, y) : __fadd_rn(x, y);
+            if (scale_p) v = (subtract_b & 2) ? __fdiv_rn(v, sc) : __fmul_rn(v, sc);
             out[base + i] = v;
             if (enforce_zs == 1) s += (double)__fmul_rn(v, beliefs[base + i]);
             if (enforce_zs == 2) prod[i >= H][i >= H ? i - H : i] = __fmul_rn(v, beliefs[base + i]);
@@ -533,8 +533,9 @@ int p2b_step_mix_zero_sum(const float* a, const float* b, const float* beliefs, 
                           const float* coef_a, const float* coef_b, const float* scale, float* out, int64_t rows,
                           int32_t H, int subtract_b, int enforce_zero_sum, void* stream) {
     if (rows <= 0) return P2B_OK;
-    if (enforce_zero_sum == 2 && H != P2B_NUM_HANDS)
-        return set_error(P2B_ERR_ARG, "enforce_zero_sum = 2 (sums in the CPU row-reduction order) needs H = %d", P2B_NUM_HANDS);
+    if (enforce_zero_sum == 2 && H != P2B_NUM_HANDS && H != P2B_HPAD)
+        return set_error(P2B_ERR_ARG, "enforce_zero_sum = 2 (sums in the CPU row-reduction order) needs H = %d or rows padded to %d",
+                         P2B_NUM_HANDS, P2B_HPAD);
     mix_zero_sum_kernel<<<GRID_ROWS(rows), kThreads, 0, (cudaStream_t)stream>>>(a, b, beliefs, ignore, coef_a, coef_b, scale,
                                                                                out, rows, H, subtract_b, enforce_zero_sum);
     STEP_CHECK("mix_zero_sum_kernel");

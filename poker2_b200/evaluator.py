@@ -70,7 +70,7 @@ class SubgameEvaluator:
                  generator: torch.Generator | None = None, warm_start_iterations: int = 0,
                  warm_start_multiplier: float = 1.0, alpha_final: float | None = None,
                  beta_final: float | None = None, gamma_final: float | None = None,
-                 enforce_zero_sum: bool = False, cfr_avg: bool = False):
+                 enforce_zero_sum: bool = False, cfr_avg: bool = False, running_values: bool = False):
         self.device = torch.device(device)
         self.cfr_iterations = int(iterations)
         self.bet_bins, self.max_depth, self.bb, self.max_raises = list(bet_bins), max_depth, bb, max_raises
@@ -83,6 +83,9 @@ class SubgameEvaluator:
         # `cfr_avg` upstream: leaf values and regret weights at the beliefs under the average policy, model
         # values de-averaged (cfr_evaluator.py:997-1018, :1029, :1133)
         self.cfr_avg = bool(cfr_avg)
+        # `value_targets_from_final_policy = False` upstream: value targets from the running average of the
+        # per-iteration values (`update_average_values`, :1260-1274); solved pass by pass
+        self.running_values = bool(running_values)
         self.model, self.chance_average, self.leaf_chunk = model, chance_average, leaf_chunk
         self.sample_epsilon = sample_epsilon
         self.generator = generator
@@ -121,7 +124,7 @@ class SubgameEvaluator:
         self.root_nodes = n
         boards_t = torch.from_numpy(self.boards)
         kw = dict(exploitability=True, keep_node_values=True, sampling=True)
-        self.stepped = bool(self.layout.num_model_leaves) or self.warm_start_iterations > 0
+        self.stepped = bool(self.layout.num_model_leaves) or self.warm_start_iterations > 0 or self.running_values
         if self.layout.num_model_leaves:
             if self.model is None:
                 raise ValueError("the subgames have non-terminal leaves: a leaf model is required")
@@ -170,7 +173,7 @@ class SubgameEvaluator:
             res = self.solver.solve(self.root_beliefs, scal, self.leaf_fn, cfr_plus=self.cfr_plus,
                                     enforce_zero_sum=self.enforce_zero_sum, start_policy=start_policy,
                                     warm_start_iterations=ws, warm_start_multiplier=self.warm_start_multiplier,
-                                    warm_start_scalars=first, cfr_avg=self.cfr_avg)
+                                    warm_start_scalars=first, cfr_avg=self.cfr_avg, running_values=self.running_values)
         else:
             if start_policy is not None:
                 raise ValueError("a start policy needs the stepped solver (set warm_start_iterations or use model leaves)")

@@ -286,6 +286,20 @@ def mix_zero_sum(a, b, beliefs, coef_a, coef_b, out, mode: int = 1) -> None:
           m, h, 1, int(mode))
 
 
+def mix_zero_sum_rows(a, b, beliefs, ignore, coef_a, coef_b, scale, out, *, divide: bool = False, mode: int = 1) -> None:
+    """out = (a*coef_a + b*coef_b) * scale (or / scale with `divide`), minus the zero-sum shift of rows of [2,H]
+    whose `ignore` byte is 0 (mode 0: no shift, 1: fp64 sum, 2: fp32 sums in the CPU row-reduction order; H may be
+    padded beyond 1326 only in modes 0 and 1).  The non-fused `update_average_values` upstream
+    (cfr_evaluator.py:1260-1274) is divide=True, mode=2."""
+    _require()
+    for t in (a, b, beliefs, out):
+        assert t.is_contiguous() and t.shape == a.shape
+    m, two, h = a.shape
+    assert two == 2 and (ignore is None or (ignore.is_contiguous() and ignore.shape == (m,)))
+    _call("p2b_step_mix_zero_sum", out.device, _p(a), _p(b), _p(beliefs), _p(ignore), _p(coef_a), _p(coef_b), _p(scale),
+          _p(out), m, h, 2 if divide else 0, int(mode))
+
+
 def fused_weighted_parent_sum(values, prev_actor, policy_hero, policy_opp, child_offsets, child_count,
                               parent_base: int, max_children: int = 8, block_h: int = 2048) -> None:
     _require()

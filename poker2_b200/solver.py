@@ -205,10 +205,12 @@ def layout_tensor(layout, name: str, device, dtype=None) -> torch.Tensor:
     return t if dtype is None else t.to(dtype)
 
 
-def solve_flags(cfr_plus: bool, enforce_zero_sum: bool, cfr_avg: bool = False) -> int:
+def solve_flags(cfr_plus: bool, enforce_zero_sum: bool, cfr_avg: bool = False, iter_values: bool = False) -> int:
     """The `flags` argument of the solve entry points: bit 0 = CFR+ clamp, bit 1 = zero-sum value outputs,
-    bit 2 = leaf values and regret weights at the beliefs under the average policy (`cfr_avg` upstream)."""
-    return int(bool(cfr_plus)) | (int(bool(enforce_zero_sum)) << 1) | (int(bool(cfr_avg)) << 2)
+    bit 2 = leaf values and regret weights at the beliefs under the average policy (`cfr_avg` upstream),
+    bit 3 (stepped solves) = keep the node values and average beliefs of every pass."""
+    return (int(bool(cfr_plus)) | (int(bool(enforce_zero_sum)) << 1) | (int(bool(cfr_avg)) << 2)
+            | (int(bool(iter_values)) << 3))
 
 
 def pad_rows(x: torch.Tensor) -> torch.Tensor:
@@ -458,7 +460,7 @@ class SteppedSolver(SubgameSolver):
     def solve(self, root_beliefs: torch.Tensor, scalars: np.ndarray, leaf_fn=None, *, cfr_plus: bool = False,
               enforce_zero_sum: bool = False, start_policy: torch.Tensor | None = None, warm_start_iterations: int = 0,
               warm_start_multiplier: float = 1.0, warm_start_scalars: np.ndarray | None = None,
-              cfr_avg: bool = False) -> SolveResult:
+              cfr_avg: bool = False, running_values: bool = False) -> SolveResult:
         """scalars: `iteration_scalars(T)` for all T iterations.  start_policy [M,1326] in the
         upstream node order (the policy head's softmax; None = uniform).  With
         warm_start_iterations = w > 0 (needs a start policy) the regrets are seeded from the start
@@ -467,11 +469,17 @@ class SteppedSolver(SubgameSolver):
         the mixing weights of the warm start's own policy update when the exponents follow a
         schedule (default: the row of iteration w).  cfr_avg: `cfr_avg` upstream -- leaf_fn sees the
         beliefs under the average policy, and from the second iteration on its values are taken as a
-        running average over the iterations and de-averaged (cfr_evaluator.py:997-1018)."""
+        running average over the iterations and de-averaged (cfr_evaluator.py:997-1018).
+        running_values: `value_targets_from_final_policy = False` upstream -- the value outputs are the
+        running mix of the per-iteration node values, shifted to zero sum every iteration if asked
+        (`update_average_values`, :1260-1274), instead of the values of the final average policy; the
+        solver must have been built with keep_node_values=True (or exploitability=True)."""
         assert root_beliefs.shape == (self.B, 2, HPAD) and root_beliefs.dtype == torch.float32
         assert root_beliefs.is_contiguous() and root_beliefs.device == self.device
         ws = int(warm_start_iterations)
-        flags = solve_flags(cfr_plus, enforce_zero_sum, cfr_avg)
+        flags = solve_flags(cfr_plus, enforce_zero_sum, cfr_avg, running_values)
+        if running_values and self.values_avg is None:
+            raise ValueError("running_values needs a solver built with keep_node_values=True")
         all_scalars = scalars
         if ws > 0:
             if start_policy is None:
@@ -490,6 +498,7 @@ class SteppedSolver(SubgameSolver):
         if n_leaves and leaf_fn is None:
             raise ValueError("the trees have model-valued leaves: a leaf_fn is required")
         self._last_model_values = None
+        self._running = None
         for pas in range(-1, iterations + 1):
             if pas == 0 and ws > 0:
                 with torch.cuda.device(self.device):
@@ -497,8 +506,13 @@ class SteppedSolver(SubgameSolver):
                               float(ws) * float(warm_start_multiplier), _lib.ptr(self.regrets), _lib.ptr(self.weight_sums),
                               _lib.stream_ptr(self.device))
                 self.launches += 1
+            if running_values and pas == iterations:
+                self._finish_running_values(root_beliefs, sc, iterations, flags, leaf_fn, n_leaves)
+                break
             if n_leaves == 0:
                 self._step(root_beliefs, sc, iterations, flags, pas, pas, 3)
+                if running_values:
+                    self._mix_running_values(pas, ws, all_scalars, enforce_zero_sum)
                 continue
             self._step(root_beliefs, sc, iterations, flags, pas, pas, 1)
             vals = leaf_fn(self.leaf_beliefs[:n_leaves])
@@ -515,7 +529,66 @@ class SteppedSolver(SubgameSolver):
                 # beliefs of the last iteration at the model leaves (the states sampling continues from)
                 self.beliefs_last[layout_tensor(self.layout, "model_rows", self.device)] = self.leaf_beliefs[:n_leaves]
             self._step(root_beliefs, sc, iterations, flags, pas, pas, 2)
+            if running_values:
+                self._mix_running_values(pas, ws, all_scalars, enforce_zero_sum)
         return self._result()
+
+    # ---- running average of the node values (`value_targets_from_final_policy = False`) ----
+    _running = None  # [rows,2,1344] the running average
+    _terminal = None  # [rows] uint8: 1 at the leaves that end the hand (exempt from the zero-sum shift)
+
+    def _mix_running_values(self, pas, ws, scalars, enforce_zero_sum) -> None:
+        """After the bottom-up sweep of pass `pas` (whose node values are in self.values_avg, the average
+        beliefs in self.beliefs_avg): the start pass, or the pass that follows a warm start, sets the
+        average to the values (cfr_evaluator.py:1513); an iteration pass mixes them in with the weights
+        of its iteration and shifts the result to zero sum (:1260-1274)."""
+        from . import fused_cfr as F
+
+        first = 0 if ws > 0 else -1
+        if pas < first:
+            return
+        if pas == first:
+            self._running = self.values_avg.clone()
+            return
+        t = pas if ws == 0 else ws + pas - 1
+        row = scalars[t]
+        dev = self.device
+        old, new, total = (torch.tensor(float(row[k]), device=dev, dtype=torch.float32)
+                           for k in ("mix_old", "mix_new", "mix_total"))
+        if self._terminal is None:
+            nodes = self.nodes.view(torch.uint8).reshape(-1, 16)
+            self._terminal = ((nodes[:, 4] == 1) | (nodes[:, 4] == 2)).to(torch.uint8).contiguous()
+        out = torch.empty_like(self._running)
+        F.mix_zero_sum_rows(self._running, self.values_avg, self.beliefs_avg, self._terminal, old, new, total, out,
+                            divide=True, mode=2 if enforce_zero_sum else 0)
+        self._running = out
+
+    def _finish_running_values(self, root_beliefs, sc, iterations, flags, leaf_fn, n_leaves) -> None:
+        """No final evaluation of the average policy in this mode: the final pass still runs, because the
+        best responses start from its reach rows and normalisation sums, but its values go to a scratch
+        copy; the outputs are the running averages."""
+        running = self._running
+        keep = self.values_avg
+        flags_final = flags & ~8
+        expl = self.exploitability
+        self.exploitability = None  # the best responses come later, from the running averages
+        if n_leaves == 0:
+            self._step(root_beliefs, sc, iterations, flags_final, iterations, iterations, 3)
+        else:
+            self._step(root_beliefs, sc, iterations, flags_final, iterations, iterations, 1)
+            vals = leaf_fn(self.leaf_beliefs[:n_leaves])
+            if vals.shape[-1] == NUM_HANDS:
+                self.leaf_values[:n_leaves, :, :NUM_HANDS].copy_(vals)
+            else:
+                self.leaf_values[:n_leaves].copy_(vals)
+            self._step(root_beliefs, sc, iterations, flags_final, iterations, iterations, 2)
+        self.exploitability = expl
+        self.values_avg = running
+        roots = layout_tensor(self.layout, "from_level_major", self.device)[: self.B]
+        self.root_values.copy_(running.index_select(0, roots))
+        if expl is not None:
+            self._step(root_beliefs, sc, iterations, flags_final, iterations, iterations, 4)
+        del keep
 
 
 def solve_noalloc(sv: SubgameSolver, root_beliefs: torch.Tensor, scalars_dev: torch.Tensor, *,

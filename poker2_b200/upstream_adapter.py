@@ -19,8 +19,7 @@ touches:
 
 No upstream module is imported.  The leaf model is called as `model(beliefs [S,2,1326], boards [S,5],
 context [S,3])` (see `leaf_eval`); a model object may carry that callable as `b200_leaf_model`.
-Not covered: `value_targets_from_final_policy=False`, warm start of type `model_br`, linear CFR (each
-raises at construction).
+Not covered: warm start of type `model_br`, linear CFR (each raises at construction).
 """
 from __future__ import annotations
 
@@ -171,9 +170,6 @@ class B200CFREvaluator:
 
     def __init__(self, model, device, cfg, generator: torch.Generator | None = None, *, max_raises=None):
         s, e = cfg.search, cfg.env
-        if not getattr(s, "value_targets_from_final_policy", True):
-            raise NotImplementedError("value targets from running averages are not supported: "
-                                      "set search.value_targets_from_final_policy")
         cfr_type = _enum_name(s.cfr_type)
         iterations = int(s.iterations)
         # same clamp as upstream (sparse_cfr_evaluator.py:39-41)
@@ -193,7 +189,8 @@ class B200CFREvaluator:
             max_raises=max_raises, model=leaf_model, chance_average=False,
             sample_epsilon=float(getattr(s, "sample_epsilon", 0.25)), generator=generator, warm_start_iterations=ws,
             warm_start_multiplier=float(getattr(s, "warm_start_multiplier", 1.0)),
-            enforce_zero_sum=bool(getattr(model, "enforce_zero_sum", False)), cfr_avg=bool(getattr(s, "cfr_avg", False)))
+            enforce_zero_sum=bool(getattr(model, "enforce_zero_sum", False)), cfr_avg=bool(getattr(s, "cfr_avg", False)),
+            running_values=not bool(getattr(s, "value_targets_from_final_policy", True)))
         self.root_nodes = int(cfg.num_envs)
         self.warm_start_iterations = ws
         self.generator = generator

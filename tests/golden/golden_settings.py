@@ -184,5 +184,46 @@ def gen_cfr_avg() -> None:
          turn_br_values=ex.local_best_response_values.numpy())
 
 
+def gen_running_values() -> None:
+    """`value_targets_from_final_policy = False` (the dataclass default upstream): values_avg is the running
+    mix of the per-iteration values with the zero-sum shift applied every iteration
+    (`update_average_values`, cfr_evaluator.py:1260-1274); no final pass.  River and turn subgames."""
+    b, r, p, s = gc.seeded_inputs(41, 2, (20, 200), (100, 1000))
+    iterations, cap, depth = 12, 2, 8
+    gc.install_raise_cap(cap)
+    search = dict(value_targets_from_final_policy=False)
+    ev = gc.make_evaluator(2, iterations, depth=depth, search=search, enforce_zero_sum=True)
+    ex = _solve(ev, gc.river_env(b, p, s), 2, r)
+    river = dict(
+        river_boards=b.to(torch.int16).numpy(), river_ranges=r.numpy(), river_pot=p.numpy(), river_stack=s.numpy(),
+        river_iterations=np.int64(iterations), river_total_nodes=np.int64(ev.total_nodes),
+        river_policy_avg=ev.policy_probs_avg.numpy(), river_values_avg=ev.values_avg.numpy(),
+        river_exploitability=ex.local_exploitability.numpy(), river_br_values=ex.local_best_response_values.numpy())
+    print("running values river: nodes", ev.total_nodes, "exploitability", ex.local_exploitability.tolist())
+
+    g = torch.Generator().manual_seed(42)
+    n, iterations_t = 2, 10
+    import make_golden
+    boards = torch.stack([torch.randperm(52, generator=g)[:4] for _ in range(n)])
+    ranges = make_golden.dirichlet_ranges(boards, g)
+    pot = torch.randint(20, 201, (n,), generator=g)
+    stack = torch.randint(100, 1001, (n,), generator=g)
+    ev = gc.make_evaluator(n, iterations_t, depth=depth, search=search, enforce_zero_sum=True)
+    model = gc.PotEchoModel(len(BET_BINS) + 3)
+    model.enforce_zero_sum = True
+    ev.model = model
+    ex = _solve(ev, gc.turn_env(boards, pot, stack), n, ranges, seed=123)
+    gc.install_raise_cap(None)
+    model_mask = ev.leaf_mask & ~ev.env.done
+    print("running values turn: nodes", ev.total_nodes, "model leaves", int(model_mask.sum()),
+          "exploitability", ex.local_exploitability.tolist())
+    save("cfr_running_values.npz", cap=np.int64(cap), max_depth=np.int64(depth), **river,
+         turn_boards=boards.to(torch.int16).numpy(), turn_ranges=ranges.numpy(), turn_pot=pot.numpy(),
+         turn_stack=stack.numpy(), turn_iterations=np.int64(iterations_t), turn_total_nodes=np.int64(ev.total_nodes),
+         turn_model_mask=model_mask.numpy(), hand_weights=gc.hand_weights().numpy(),
+         turn_policy_avg=ev.policy_probs_avg.numpy(), turn_values_avg=ev.values_avg.numpy(),
+         turn_exploitability=ex.local_exploitability.numpy(), turn_br_values=ex.local_best_response_values.numpy())
+
+
 gc.SECTIONS.update(production=gen_production, standard=gen_standard, zero_sum=gen_zero_sum, ragged256=gen_ragged256,
-                   cfr_avg=gen_cfr_avg)
+                   cfr_avg=gen_cfr_avg, running_values=gen_running_values)

@@ -169,3 +169,36 @@ def test_cfr_avg_matches_upstream(cuda_device, golden_dir):
     _close("turn values_avg", res.level_major(res.values_avg).cpu(), torch.from_numpy(z["turn_values_avg"]))
     _close("turn exploitability", res.exploitability.cpu(), torch.from_numpy(z["turn_exploitability"]), rtol=1e-4)
     _close("turn br_values", res.br_values.cpu(), torch.from_numpy(z["turn_br_values"]), rtol=1e-4)
+
+
+def test_running_value_average_matches_upstream(cuda_device, golden_dir):
+    """`value_targets_from_final_policy = False` upstream: the value outputs are the running mix of the
+    per-iteration node values, shifted to zero sum every iteration; the best responses start from those
+    averages at the leaves.  River and turn subgames, pass by pass."""
+    from leaf_models import pot_echo_leaf_fn
+    from poker2_b200 import solver, tree as ptree
+
+    z = np.load(os.path.join(golden_dir, "cfr_running_values.npz"))
+    cap, depth = int(z["cap"]), int(z["max_depth"])
+    for street, tag in ((3, "river"), (2, "turn")):
+        roots = ptree.root_states(z[f"{tag}_pot"], z[f"{tag}_stack"], min_raise=2, street=street)
+        trees = ptree.build_trees(roots, [0.5, 1.0], depth, bb=2, max_raises=cap)
+        assert trees.total_nodes == int(z[f"{tag}_total_nodes"])
+        boards = z[f"{tag}_boards"].astype(np.int64)
+        if boards.shape[1] < 5:
+            boards = np.concatenate([boards, np.full((boards.shape[0], 5 - boards.shape[1]), -1)], axis=1)
+        layout = solver.device_layout(trees, boards)
+        sv = solver.SteppedSolver(layout, torch.from_numpy(boards), cuda_device, exploitability=True)
+        leaf_fn = None
+        if street == 2:
+            leaf_fn = pot_echo_leaf_fn(trees, layout.model_nodes, torch.from_numpy(z["hand_weights"]))
+        rb = solver.pad_rows(torch.from_numpy(z[f"{tag}_ranges"]).to(cuda_device)).contiguous()
+        res = sv.solve(rb, solver.iteration_scalars(int(z[f"{tag}_iterations"])), leaf_fn, enforce_zero_sum=True,
+                       running_values=True)
+        assert sv.status() == 0
+        n = trees.num_roots
+        _close(f"{tag} policy_avg", res.level_major(res.policy_avg).cpu()[n:], torch.from_numpy(z[f"{tag}_policy_avg"])[n:])
+        _close(f"{tag} values_avg", res.level_major(res.values_avg).cpu(), torch.from_numpy(z[f"{tag}_values_avg"]))
+        _close(f"{tag} root_values", res.root_values[..., :1326].cpu(), torch.from_numpy(z[f"{tag}_values_avg"])[:n])
+        _close(f"{tag} exploitability", res.exploitability.cpu(), torch.from_numpy(z[f"{tag}_exploitability"]), rtol=1e-4)
+        _close(f"{tag} br_values", res.br_values.cpu(), torch.from_numpy(z[f"{tag}_br_values"]), rtol=1e-4)

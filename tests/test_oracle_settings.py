@@ -136,3 +136,32 @@ def test_oracle_cfr_avg_bit_exact(golden_dir):
     ex, br = o.exploitability()
     assert torch.equal(ex, torch.from_numpy(z["turn_exploitability"]))
     assert torch.equal(br, torch.from_numpy(z["turn_br_values"]))
+
+
+def test_oracle_running_value_average_bit_exact(golden_dir):
+    """value_targets_from_final_policy = False upstream: values_avg is the running mix of the per-iteration
+    values, shifted to zero sum every iteration; there is no final pass."""
+    z = np.load(os.path.join(golden_dir, "cfr_running_values.npz"))
+    cap, depth = int(z["cap"]), int(z["max_depth"])
+    t = _build(z["river_pot"], z["river_stack"], cap, depth)
+    assert t.total_nodes == int(z["river_total_nodes"])
+    o = ocfr.SubgameOracle(t.oracle_dict(z["river_boards"].astype(np.int64)), torch.from_numpy(z["river_ranges"]),
+                           iterations=int(z["river_iterations"]), enforce_zero_sum=True, final_policy_values=False).solve()
+    assert torch.equal(o.policy_avg, torch.from_numpy(z["river_policy_avg"]))
+    assert torch.equal(o.values_avg, torch.from_numpy(z["river_values_avg"]))
+    ex, br = o.exploitability()
+    assert torch.equal(ex, torch.from_numpy(z["river_exploitability"]))
+    assert torch.equal(br, torch.from_numpy(z["river_br_values"]))
+    t = _build(z["turn_pot"], z["turn_stack"], cap, depth, street=2)
+    assert t.total_nodes == int(z["turn_total_nodes"])
+    boards = np.concatenate([z["turn_boards"].astype(np.int64), np.full((z["turn_boards"].shape[0], 1), -1)], axis=1)
+    model_nodes = np.nonzero(z["turn_model_mask"])[0]
+    leaf_fn = pot_echo_leaf_fn(t, model_nodes, torch.from_numpy(z["hand_weights"]))
+    o = ocfr.SubgameOracle(t.oracle_dict(boards), torch.from_numpy(z["turn_ranges"]),
+                           iterations=int(z["turn_iterations"]), enforce_zero_sum=True, final_policy_values=False,
+                           leaf_fn=lambda b, idx: leaf_fn(b)).solve()
+    assert torch.equal(o.policy_avg, torch.from_numpy(z["turn_policy_avg"]))
+    assert torch.equal(o.values_avg, torch.from_numpy(z["turn_values_avg"]))
+    ex, br = o.exploitability()
+    assert torch.equal(ex, torch.from_numpy(z["turn_exploitability"]))
+    assert torch.equal(br, torch.from_numpy(z["turn_br_values"]))
