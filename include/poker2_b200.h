@@ -147,7 +147,11 @@ int p2b_cfr_iteration_ms(float* ms);
  * of the average policy).  A call runs the passes pass_begin..pass_end; `phases` selects the
  * top-down sweep (1), the bottom-up sweep (2) or both (3); with 1 or 2 the range is one pass; 4 (with
  * pass_begin = pass_end = iterations) runs only the best responses, from the state the final pass left and
- * the leaf values found in values_avg.
+ * the leaf values found in values_avg; 8 (with pass_begin = pass_end = -1, after a start pass run with flags
+ * bit 3) is the best-response pass of a warm start of type `model_br` (cfr_evaluator.py:927-955): it sets the
+ * regrets of every child to unblocked(other player's start beliefs) x (best-response value of the child for the
+ * player who acted - that player's value of the parent under the start policy); the caller multiplies by
+ * warm_start_iterations x multiplier, sets the weight sums to that factor and goes on with pass 0.
  * The caller's loop is: for every pass { step(pass, 1); leaf_values = model(leaf_beliefs);
  * step(pass, 2); }.  Arrays as in p2b_cfr_solve, plus state carried between calls:
  *  scratch      p2b_cfr_scratch_floats(max_internal, 1) * num_subgames floats (one set of

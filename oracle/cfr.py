@@ -36,7 +36,8 @@ class SubgameOracle:
                  start_policy: torch.Tensor | None = None, warm_start_iterations: int = 0,
                  warm_start_multiplier: float = 1.0, alpha_final: float | None = None,
                  beta_final: float | None = None, gamma_final: float | None = None,
-                 enforce_zero_sum: bool = False, cfr_avg: bool = False, final_policy_values: bool = True):
+                 enforce_zero_sum: bool = False, cfr_avg: bool = False, final_policy_values: bool = True,
+                 warm_start_type: str = "model"):
         t = {k: (torch.from_numpy(np.ascontiguousarray(v)) if isinstance(v, np.ndarray) else v)
              for k, v in tree.items()}
         self.offs = [int(x) for x in tree["depth_offsets"]]
@@ -78,6 +79,7 @@ class SubgameOracle:
         self.start_policy = start_policy
         self.warm_start_iterations = warm_start_iterations
         self.warm_start_multiplier = warm_start_multiplier
+        self.warm_start_type = warm_start_type  # "model" (:913-926) or "model_br" (:927-955)
         self.model_idx = torch.where(self.leaf & ~self.done)[0]
         N, M = self.N, self.M
 
@@ -244,17 +246,21 @@ class SubgameOracle:
             self._pull_back_sum(weighted, values, level=d)
 
     # ---- one iteration (cfr_evaluator.py:1331-1381) ----
-    def instantaneous_regrets(self):
+    def instantaneous_regrets(self, achieved=None, expected=None):
+        """`compute_instantaneous_regrets` (cfr_evaluator.py:1117-1165): values achieved by each child against the
+        values expected at its parent (both the latest values unless given)."""
         N = self.N
+        achieved = self.values if achieved is None else achieved
+        expected = self.values if expected is None else expected
         out = torch.zeros_like(self.policy)
         actor = self.to_act[:, None, None].expand(-1, -1, H)
         pa = self.prev_actor[N:, None, None].expand(-1, -1, H)
         beliefs = self.beliefs_avg if self.cfr_avg else self.beliefs
         opp_reach = unblocked.unblocked_mass(beliefs.flip(dims=[1]))
         weights = self._fan_out(opp_reach.gather(1, actor).squeeze(1))
-        expected = self._fan_out(self.values.gather(1, actor).squeeze(1))
-        achieved = self.values[N:].gather(1, pa).squeeze(1)
-        out[N:] = weights * (achieved - expected)
+        exp = self._fan_out(expected.gather(1, actor).squeeze(1))
+        ach = achieved[N:].gather(1, pa).squeeze(1)
+        out[N:] = weights * (ach - exp)
         return out
 
     def mixing_weights(self, t):
@@ -362,13 +368,22 @@ class SubgameOracle:
 
     def warm_start(self):
         """Type `model` (cfr_evaluator.py:913-926): cumulative regrets = start policy x weight,
-        weight = iterations x multiplier x mean positive instantaneous regret of the row."""
+        weight = iterations x multiplier x mean positive instantaneous regret of the row.
+        Type `model_br` (:927-955): cumulative regrets = iterations x multiplier x the regrets of not playing
+        a best response against the start policy."""
         N, ws = self.N, self.warm_start_iterations
         weight = float(ws) * float(self.warm_start_multiplier)
-        regrets = self.instantaneous_regrets()
-        weights = weight * regrets[N:].clamp(min=0.0).mean(dim=-1)
-        self.regrets[N:] = self.policy[N:] * weights[:, None]
-        self.weight_sums[N:] = weights[:, None]
+        if self.warm_start_type == "model":
+            regrets = self.instantaneous_regrets()
+            weights = weight * regrets[N:].clamp(min=0.0).mean(dim=-1)
+            self.regrets[N:] = self.policy[N:] * weights[:, None]
+            self.weight_sums[N:] = weights[:, None]
+        else:
+            br = [self._best_response(self.policy, self.beliefs, self.values, torch.full((self.M,), pl, dtype=torch.long))
+                  for pl in range(2)]
+            values_br = torch.where(self.prev_actor[:, None, None] == 0, br[0], br[1])
+            self.regrets += weight * self.instantaneous_regrets(values_br, self.values)
+            self.weight_sums += weight
         self.update_policy(ws)
         self.set_leaf_values()
         self.expected_values()

@@ -1093,10 +1093,17 @@ __device__ __forceinline__ void sweep_up(int mode_rt, int pass, const CfrParams&
 // [-1,1] (:730), read back from p.values_avg.  deviator < 0: plain expectation under the
 // average policy (`base_values`, :732-735); deviator = d: player d plays a best response.
 // Returns the root values of both players in root_v (index = player).
+//
+// warm = true: the best-response pass of a warm start of type `model_br` (:927-955), run after the start
+// pass.  Beliefs are the start beliefs (kept in the rbar rows by that pass), the policy is the start policy
+// (stored as the average policy), leaf values are the start pass's own (values_avg, not clamped), and at
+// every node where the deviator acts the regrets of its children are SET to
+// unblocked(other player's beliefs) x (best-response value of the child - the node's value under the
+// start policy) -- `compute_instantaneous_regrets(values_br, latest_values)`; the caller scales them.
 template <int VPT, int MAXC>
 __device__ __forceinline__ void sweep_br(int deviator, const CfrParams& p, Block& B, const HandInfo<VPT>& hi,
                                          const FV<VPT> (&prior)[2], const FV<VPT> (&root_b)[2], int tid,
-                                         FV<VPT> (&root_v)[2]) {
+                                         FV<VPT> (&root_v)[2], bool warm = false) {
     constexpr int kRowM = 2;
     FV<VPT> mask;
 #pragma unroll
@@ -1109,8 +1116,13 @@ __device__ __forceinline__ void sweep_br(int deviator, const CfrParams& p, Block
         constexpr int K = decltype(kc)::value;
         const bool deviates = deviator == a;
         FV<VPT> b_a;  // beliefs of the acting player under the average policy
+        FV<VPT> b_o;  // warm start only: the other player's
         if (j == 0) {
             b_a = pick<VPT>(root_b, a);
+            b_o = pick<VPT>(root_b, o);
+        } else if (warm) {
+            b_a = ldv<VPT>(B.rbar(ii, a), tid);
+            b_o = ldv<VPT>(B.rbar(ii, o), tid);
         } else {
             const FV<VPT> prior_a = pick<VPT>(prior, a);
             const FV<VPT> r_a = ldv<VPT>(B.reach(ii, a), tid);
@@ -1129,10 +1141,12 @@ __device__ __forceinline__ void sweep_br(int deviator, const CfrParams& p, Block
             } else {
                 Va[c] = ldv<VPT>(B.row2(p.values_avg, fc + c, a), tid);
                 Vo[c] = ldv<VPT>(B.row2(p.values_avg, fc + c, o), tid);
+                if (!warm) {
 #pragma unroll
-                for (int i = 0; i < VPT; ++i) {
-                    Va[c].v[i] = fminf(fmaxf(Va[c].v[i], -1.0f), 1.0f);
-                    Vo[c].v[i] = fminf(fmaxf(Vo[c].v[i], -1.0f), 1.0f);
+                    for (int i = 0; i < VPT; ++i) {
+                        Va[c].v[i] = fminf(fmaxf(Va[c].v[i], -1.0f), 1.0f);
+                        Vo[c].v[i] = fminf(fmaxf(Vo[c].v[i], -1.0f), 1.0f);
+                    }
                 }
             }
             P[c] = ldv<VPT>(B.row1(p.policy_avg, fc + c), tid);
@@ -1158,7 +1172,7 @@ __device__ __forceinline__ void sweep_br(int deviator, const CfrParams& p, Block
         // rows whose unblocked mass is needed: the acting player's beliefs (matchup mass) and,
         // per child, either the belief mass that picks it (deviator) or belief x policy
         stv<VPT>(B.stage_row(0), tid, b_a);
-        stv<VPT>(B.stage_row(1), tid, b_a);
+        stv<VPT>(B.stage_row(1), tid, warm ? b_o : b_a);
 #pragma unroll
         for (int c = 0; c < K; ++c)
             {
@@ -1189,6 +1203,19 @@ __device__ __forceinline__ void sweep_br(int deviator, const CfrParams& p, Block
                     acc_a.v[i] = __fadd_rn(acc_a.v[i], __fmul_rn(Va[c].v[i], P[c].v[i]));
                 }
             }
+        if (warm && deviates) {
+            const FV<VPT> ev_a = ldv<VPT>(B.row2(p.values_avg, j, a), tid);  // value of the node under the start policy
+#pragma unroll
+            for (int c = 0; c < K; ++c) {
+                FV<VPT> r;
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) {
+                    const float wgt = unblocked(B.cs + 52, B.S[1], hi.c1[i], hi.c2[i], b_o.v[i]);
+                    r.v[i] = __fmul_rn(wgt, __fsub_rn(Va[c].v[i], ev_a.v[i]));
+                }
+                stv<VPT>(B.row1(p.regrets, fc + c), tid, r);
+            }
+        }
         if (deviates) acc_a = best_v;
         if (j != 0) {
             stv<VPT>(B.val(ii, a), tid, acc_a);
@@ -1330,6 +1357,14 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
             if (p.cfr_avg || p.iter_values)
                 for (int i = tid; i < 2 * B.sg.n_nodes; i += NT)
                     p.carry_sums[(p.rows + B.sg.node_begin) * 2 + i] = B.sigb[i];
+        }
+        if (p.stepped && (p.phases & 8) && p.values_avg) {
+            // best-response pass of a `model_br` warm start: one sweep per deviating player
+            FV<VPT> unused[2];
+            for (int d = 0; d < 2; ++d) {
+                __syncthreads();
+                sweep_br<VPT, MAXC>(d, p, B, hi, prior, root_b, tid, unused, true);
+            }
         }
         if (p.exploitability && p.values_avg && (run_up || (p.stepped && (p.phases & 4))) && pass_last == p.iterations) {
             // local exploitability of the average policy (cfr_evaluator.py:718-764)

@@ -91,7 +91,8 @@ struct CfrParams {
     int32_t pass_end;            // last pass of this launch (inclusive)
     int32_t phases;              // bit 0: top-down sweep, bit 1: bottom-up sweep (+ best responses after
                                  // the final pass); 4 alone: only the best responses, from the state the final
-                                 // pass left and the leaf values in values_avg
+                                 // pass left and the leaf values in values_avg; 8 alone: the best-response pass of a
+                                 // `model_br` warm start, after the start pass (values_avg holds its node values)
     float* carry_sums;           // [rows][2] normalisation sums of the node beliefs ([2][rows][2] with cfr_avg or iter_values)
     float* carry_roots;          // [B][4][HPAD] prior (2 rows) and root beliefs (2 rows) of the pass
     const int32_t* leaf_begin;   // [B] first model-leaf slot of each subgame

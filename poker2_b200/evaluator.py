@@ -70,7 +70,8 @@ class SubgameEvaluator:
                  generator: torch.Generator | None = None, warm_start_iterations: int = 0,
                  warm_start_multiplier: float = 1.0, alpha_final: float | None = None,
                  beta_final: float | None = None, gamma_final: float | None = None,
-                 enforce_zero_sum: bool = False, cfr_avg: bool = False, running_values: bool = False):
+                 enforce_zero_sum: bool = False, cfr_avg: bool = False, running_values: bool = False,
+                 warm_start_type: str = "model"):
         self.device = torch.device(device)
         self.cfr_iterations = int(iterations)
         self.bet_bins, self.max_depth, self.bb, self.max_raises = list(bet_bins), max_depth, bb, max_raises
@@ -92,6 +93,7 @@ class SubgameEvaluator:
         # warm start of type `model`: regrets seeded from the start policy (cfr_evaluator.py:887-926)
         self.warm_start_iterations = int(warm_start_iterations)
         self.warm_start_multiplier = float(warm_start_multiplier)
+        self.warm_start_type = warm_start_type  # "model" (:913-926) or "model_br" (:927-955)
         self.stats: dict = {}
         self.root_nodes = 0
         self._result = None
@@ -173,7 +175,8 @@ class SubgameEvaluator:
             res = self.solver.solve(self.root_beliefs, scal, self.leaf_fn, cfr_plus=self.cfr_plus,
                                     enforce_zero_sum=self.enforce_zero_sum, start_policy=start_policy,
                                     warm_start_iterations=ws, warm_start_multiplier=self.warm_start_multiplier,
-                                    warm_start_scalars=first, cfr_avg=self.cfr_avg, running_values=self.running_values)
+                                    warm_start_scalars=first, cfr_avg=self.cfr_avg, running_values=self.running_values,
+                                    warm_start_type=self.warm_start_type)
         else:
             if start_policy is not None:
                 raise ValueError("a start policy needs the stepped solver (set warm_start_iterations or use model leaves)")

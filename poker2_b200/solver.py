@@ -460,7 +460,7 @@ class SteppedSolver(SubgameSolver):
     def solve(self, root_beliefs: torch.Tensor, scalars: np.ndarray, leaf_fn=None, *, cfr_plus: bool = False,
               enforce_zero_sum: bool = False, start_policy: torch.Tensor | None = None, warm_start_iterations: int = 0,
               warm_start_multiplier: float = 1.0, warm_start_scalars: np.ndarray | None = None,
-              cfr_avg: bool = False, running_values: bool = False) -> SolveResult:
+              cfr_avg: bool = False, running_values: bool = False, warm_start_type: str = "model") -> SolveResult:
         """scalars: `iteration_scalars(T)` for all T iterations.  start_policy [M,1326] in the
         upstream node order (the policy head's softmax; None = uniform).  With
         warm_start_iterations = w > 0 (needs a start policy) the regrets are seeded from the start
@@ -473,13 +473,21 @@ class SteppedSolver(SubgameSolver):
         running_values: `value_targets_from_final_policy = False` upstream -- the value outputs are the
         running mix of the per-iteration node values, shifted to zero sum every iteration if asked
         (`update_average_values`, :1260-1274), instead of the values of the final average policy; the
-        solver must have been built with keep_node_values=True (or exploitability=True)."""
+        solver must have been built with keep_node_values=True (or exploitability=True).
+        warm_start_type: "model" (above) or "model_br" (:927-955; needs keep_node_values too): the regrets
+        are seeded with w x multiplier x the regrets of not playing a best response against the start
+        policy."""
         assert root_beliefs.shape == (self.B, 2, HPAD) and root_beliefs.dtype == torch.float32
         assert root_beliefs.is_contiguous() and root_beliefs.device == self.device
         ws = int(warm_start_iterations)
         flags = solve_flags(cfr_plus, enforce_zero_sum, cfr_avg, running_values)
         if running_values and self.values_avg is None:
             raise ValueError("running_values needs a solver built with keep_node_values=True")
+        if warm_start_type not in ("model", "model_br"):
+            raise ValueError(f"unknown warm_start_type {warm_start_type!r}")
+        warm_br = ws > 0 and warm_start_type == "model_br"
+        if warm_br and self.values_avg is None:
+            raise ValueError("a warm start of type model_br needs a solver built with keep_node_values=True")
         all_scalars = scalars
         if ws > 0:
             if start_policy is None:
@@ -500,7 +508,14 @@ class SteppedSolver(SubgameSolver):
         self._last_model_values = None
         self._running = None
         for pas in range(-1, iterations + 1):
-            if pas == 0 and ws > 0:
+            if pas == 0 and warm_br:
+                # best responses against the start policy, from the node values the start pass has stored
+                self._step(root_beliefs, sc, iterations, flags, -1, -1, 8)
+                weight = float(ws) * float(warm_start_multiplier)
+                self.regrets.mul_(weight)
+                if self.weight_sums is not None:
+                    self.weight_sums.fill_(weight)
+            elif pas == 0 and ws > 0:
                 with torch.cuda.device(self.device):
                     _lib.call("p2b_cfr_warm_seed", _lib.ptr(self.nodes), self.layout.rows, _lib.ptr(self.start_policy_rows),
                               float(ws) * float(warm_start_multiplier), _lib.ptr(self.regrets), _lib.ptr(self.weight_sums),
@@ -509,12 +524,16 @@ class SteppedSolver(SubgameSolver):
             if running_values and pas == iterations:
                 self._finish_running_values(root_beliefs, sc, iterations, flags, leaf_fn, n_leaves)
                 break
+            if pas == -1 and warm_br:
+                flags_pass = flags | 8  # the start pass keeps its node values for the best responses
+            else:
+                flags_pass = flags
             if n_leaves == 0:
-                self._step(root_beliefs, sc, iterations, flags, pas, pas, 3)
+                self._step(root_beliefs, sc, iterations, flags_pass, pas, pas, 3)
                 if running_values:
                     self._mix_running_values(pas, ws, all_scalars, enforce_zero_sum)
                 continue
-            self._step(root_beliefs, sc, iterations, flags, pas, pas, 1)
+            self._step(root_beliefs, sc, iterations, flags_pass, pas, pas, 1)
             vals = leaf_fn(self.leaf_beliefs[:n_leaves])
             if cfr_avg:
                 # iteration the pass belongs to, as `set_leaf_values(t)` sees it: the start pass, the pass
@@ -528,7 +547,7 @@ class SteppedSolver(SubgameSolver):
             if self.beliefs_last is not None and pas == iterations - 1:
                 # beliefs of the last iteration at the model leaves (the states sampling continues from)
                 self.beliefs_last[layout_tensor(self.layout, "model_rows", self.device)] = self.leaf_beliefs[:n_leaves]
-            self._step(root_beliefs, sc, iterations, flags, pas, pas, 2)
+            self._step(root_beliefs, sc, iterations, flags_pass, pas, pas, 2)
             if running_values:
                 self._mix_running_values(pas, ws, all_scalars, enforce_zero_sum)
         return self._result()

@@ -19,7 +19,7 @@ touches:
 
 No upstream module is imported.  The leaf model is called as `model(beliefs [S,2,1326], boards [S,5],
 context [S,3])` (see `leaf_eval`); a model object may carry that callable as `b200_leaf_model`.
-Not covered: warm start of type `model_br`, linear CFR (each raises at construction).
+Not covered: linear CFR (raises at construction).
 """
 from __future__ import annotations
 
@@ -174,8 +174,9 @@ class B200CFREvaluator:
         iterations = int(s.iterations)
         # same clamp as upstream (sparse_cfr_evaluator.py:39-41)
         ws = max(0, min(int(s.warm_start_iterations), max(1, iterations - 1)))
-        if ws > 0 and _enum_name(getattr(s, "warm_start_type", "model")) != "model":
-            raise NotImplementedError("only the warm start of type `model` is supported")
+        ws_type = _enum_name(getattr(s, "warm_start_type", "model"))
+        if ws > 0 and ws_type not in ("model", "model_br"):
+            raise NotImplementedError(f"warm start of type {ws_type!r} is not supported")
         self.model, self.cfg = model, cfg
         self.device = torch.device(device)
         self.bet_bins = list(e.bet_bins)
@@ -190,7 +191,8 @@ class B200CFREvaluator:
             sample_epsilon=float(getattr(s, "sample_epsilon", 0.25)), generator=generator, warm_start_iterations=ws,
             warm_start_multiplier=float(getattr(s, "warm_start_multiplier", 1.0)),
             enforce_zero_sum=bool(getattr(model, "enforce_zero_sum", False)), cfr_avg=bool(getattr(s, "cfr_avg", False)),
-            running_values=not bool(getattr(s, "value_targets_from_final_policy", True)))
+            running_values=not bool(getattr(s, "value_targets_from_final_policy", True)),
+            warm_start_type=ws_type if ws > 0 else "model")
         self.root_nodes = int(cfg.num_envs)
         self.warm_start_iterations = ws
         self.generator = generator

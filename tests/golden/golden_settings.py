@@ -225,5 +225,62 @@ def gen_running_values() -> None:
          turn_exploitability=ex.local_exploitability.numpy(), turn_br_values=ex.local_best_response_values.numpy())
 
 
+def gen_warm_br() -> None:
+    """Warm start of type `model_br` (the dataclass default upstream; cfr_evaluator.py:927-955): regrets seeded
+    with the regrets of not playing a best response against the model's policy.  River subgames with a fixed
+    policy head, and turn subgames with a stand-in value model."""
+    from p2.core.structured_config import WarmStartType
+
+    out = {}
+    for tag, seed in (("river", 51), ("turn", 52)):
+        iterations, ws, mult, cap, depth = 10, 3, 4.0, 2, 8
+        gc.install_raise_cap(cap)
+        ev = gc.make_evaluator(2, iterations, depth=depth)
+        if tag == "river":
+            b, r, p, s = gc.seeded_inputs(seed, 2, (20, 200), (100, 1000))
+            ev.model = gc.FixedLogitModel(len(BET_BINS) + 3)
+            env = gc.river_env(b, p, s)
+        else:
+            g = torch.Generator().manual_seed(seed)
+            import make_golden
+            b = torch.stack([torch.randperm(52, generator=g)[:4] for _ in range(2)])
+            r = make_golden.dirichlet_ranges(b, g)
+            p = torch.randint(20, 201, (2,), generator=g)
+            s = torch.randint(100, 1001, (2,), generator=g)
+
+            class Both(gc.PotEchoModel):  # value head of PotEchoModel, policy head of FixedLogitModel
+                def __call__(self, features, include_policy=True, **kw):
+                    o = gc.PotEchoModel.__call__(self, features, include_policy, **kw)
+                    o.policy_logits = gc.FixedLogitModel.__call__(self, features, include_policy, **kw).policy_logits
+                    return o
+
+            ev.model = Both(len(BET_BINS) + 3)
+            env = gc.turn_env(b, p, s)
+        ev.warm_start_iterations, ev.warm_start_type, ev.warm_start_multiplier = ws, WarmStartType.model_br, mult
+        captured = {}
+        original = ev.warm_start
+
+        def hooked(ev=ev, captured=captured, original=original):
+            captured["start_policy"] = ev.policy_probs.clone()
+            original()
+            captured["seeded_regrets"] = ev.cumulative_regrets.clone()
+
+        ev.warm_start = hooked
+        ex = _solve(ev, env, 2, r)
+        gc.install_raise_cap(None)
+        model_mask = ev.leaf_mask & ~ev.env.done
+        print(f"model_br warm start, {tag}: nodes", ev.total_nodes, "exploitability", ex.local_exploitability.tolist())
+        out.update({f"{tag}_boards": b.to(torch.int16).numpy(), f"{tag}_ranges": r.numpy(), f"{tag}_pot": p.numpy(),
+                    f"{tag}_stack": s.numpy(), f"{tag}_total_nodes": np.int64(ev.total_nodes),
+                    f"{tag}_model_mask": model_mask.numpy(), f"{tag}_start_policy": captured["start_policy"].numpy(),
+                    f"{tag}_seeded_regrets": captured["seeded_regrets"].numpy(),
+                    f"{tag}_policy_avg": ev.policy_probs_avg.numpy(),
+                    f"{tag}_root_values": ev.values_avg[:2].numpy(),
+                    f"{tag}_exploitability": ex.local_exploitability.numpy()})
+    save("cfr_warm_br.npz", iterations=np.int64(10), warm_start_iterations=np.int64(3),
+         warm_start_multiplier=np.float64(4.0), cap=np.int64(2), max_depth=np.int64(8),
+         hand_weights=gc.hand_weights().numpy(), **out)
+
+
 gc.SECTIONS.update(production=gen_production, standard=gen_standard, zero_sum=gen_zero_sum, ragged256=gen_ragged256,
-                   cfr_avg=gen_cfr_avg, running_values=gen_running_values)
+                   cfr_avg=gen_cfr_avg, running_values=gen_running_values, warm_br=gen_warm_br)

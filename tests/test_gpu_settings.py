@@ -202,3 +202,52 @@ def test_running_value_average_matches_upstream(cuda_device, golden_dir):
         _close(f"{tag} root_values", res.root_values[..., :1326].cpu(), torch.from_numpy(z[f"{tag}_values_avg"])[:n])
         _close(f"{tag} exploitability", res.exploitability.cpu(), torch.from_numpy(z[f"{tag}_exploitability"]), rtol=1e-4)
         _close(f"{tag} br_values", res.br_values.cpu(), torch.from_numpy(z[f"{tag}_br_values"]), rtol=1e-4)
+
+
+def test_model_br_warm_start_matches_upstream(cuda_device, golden_dir):
+    """Warm start of type `model_br` (the dataclass default upstream): after the start pass, a best-response
+    pass against the start policy seeds the regrets; river subgames and turn subgames with a stand-in model."""
+    from leaf_models import pot_echo_leaf_fn
+    from poker2_b200 import solver, tree as ptree
+
+    z = np.load(os.path.join(golden_dir, "cfr_warm_br.npz"))
+    cap, depth, T, ws = int(z["cap"]), int(z["max_depth"]), int(z["iterations"]), int(z["warm_start_iterations"])
+    for tag, street in (("river", 3), ("turn", 2)):
+        roots = ptree.root_states(z[f"{tag}_pot"], z[f"{tag}_stack"], min_raise=2, street=street)
+        trees = ptree.build_trees(roots, [0.5, 1.0], depth, bb=2, max_raises=cap)
+        assert trees.total_nodes == int(z[f"{tag}_total_nodes"])
+        boards = z[f"{tag}_boards"].astype(np.int64)
+        if boards.shape[1] < 5:
+            boards = np.concatenate([boards, np.full((boards.shape[0], 5 - boards.shape[1]), -1)], axis=1)
+        layout = solver.device_layout(trees, boards)
+        sv = solver.SteppedSolver(layout, torch.from_numpy(boards), cuda_device, exploitability=True)
+        leaf_fn = None
+        if street == 2:
+            leaf_fn = pot_echo_leaf_fn(trees, layout.model_nodes, torch.from_numpy(z["hand_weights"]))
+        rb = solver.pad_rows(torch.from_numpy(z[f"{tag}_ranges"]).to(cuda_device)).contiguous()
+        res = sv.solve(rb, solver.iteration_scalars(T, warm_start_iterations=ws), leaf_fn,
+                       start_policy=torch.from_numpy(z[f"{tag}_start_policy"]), warm_start_iterations=ws,
+                       warm_start_multiplier=float(z["warm_start_multiplier"]), warm_start_type="model_br")
+        assert sv.status() == 0
+        n = trees.num_roots
+        _close(f"{tag} policy_avg", res.level_major(res.policy_avg).cpu()[n:], torch.from_numpy(z[f"{tag}_policy_avg"])[n:])
+        _close(f"{tag} root_values", res.root_values[..., :1326].cpu(), torch.from_numpy(z[f"{tag}_root_values"]))
+        _close(f"{tag} exploitability", res.exploitability.cpu(), torch.from_numpy(z[f"{tag}_exploitability"]), rtol=1e-4)
+        # the seeding itself: one more solve that stops after the warm start's own policy update
+        sv2 = solver.SteppedSolver(layout, torch.from_numpy(boards), cuda_device, exploitability=True)
+        seen = {}
+        orig = sv2._step
+
+        def spy(root_beliefs, sc, iterations, flags, pb, pe, phases, orig=orig, sv2=sv2, seen=seen):
+            orig(root_beliefs, sc, iterations, flags, pb, pe, phases)
+            if phases == 8:
+                seen["raw"] = sv2.regrets.clone()
+
+        sv2._step = spy
+        sv2.solve(rb, solver.iteration_scalars(T, warm_start_iterations=ws), leaf_fn,
+                  start_policy=torch.from_numpy(z[f"{tag}_start_policy"]), warm_start_iterations=ws,
+                  warm_start_multiplier=float(z["warm_start_multiplier"]), warm_start_type="model_br")
+        weight = float(ws) * float(z["warm_start_multiplier"])
+        order = solver.layout_tensor(layout, "from_level_major", cuda_device)
+        seeded = (seen["raw"] * weight).index_select(0, order)[:, :1326].cpu()
+        _close(f"{tag} seeded regrets", seeded[n:], torch.from_numpy(z[f"{tag}_seeded_regrets"])[n:])

@@ -165,3 +165,34 @@ def test_oracle_running_value_average_bit_exact(golden_dir):
     ex, br = o.exploitability()
     assert torch.equal(ex, torch.from_numpy(z["turn_exploitability"]))
     assert torch.equal(br, torch.from_numpy(z["turn_br_values"]))
+
+
+def test_oracle_model_br_warm_start_bit_exact(golden_dir):
+    """Warm start of type `model_br`: regrets seeded with iterations x multiplier x the regrets of not playing a
+    best response against the start policy, on river subgames and on turn subgames with a stand-in model."""
+    z = np.load(os.path.join(golden_dir, "cfr_warm_br.npz"))
+    cap, depth, T, ws = int(z["cap"]), int(z["max_depth"]), int(z["iterations"]), int(z["warm_start_iterations"])
+    for tag, street in (("river", 3), ("turn", 2)):
+        t = _build(z[f"{tag}_pot"], z[f"{tag}_stack"], cap, depth, street=street)
+        assert t.total_nodes == int(z[f"{tag}_total_nodes"])
+        boards = z[f"{tag}_boards"].astype(np.int64)
+        if boards.shape[1] < 5:
+            boards = np.concatenate([boards, np.full((boards.shape[0], 5 - boards.shape[1]), -1)], axis=1)
+        leaf = None
+        if street == 2:
+            fn = pot_echo_leaf_fn(t, np.nonzero(z["turn_model_mask"])[0], torch.from_numpy(z["hand_weights"]))
+            leaf = lambda b, idx, fn=fn: fn(b)  # noqa: E731
+        o = ocfr.SubgameOracle(t.oracle_dict(boards), torch.from_numpy(z[f"{tag}_ranges"]), iterations=T,
+                               start_policy=torch.from_numpy(z[f"{tag}_start_policy"]), warm_start_iterations=ws,
+                               warm_start_multiplier=float(z["warm_start_multiplier"]), warm_start_type="model_br",
+                               leaf_fn=leaf)
+        o.initialize()
+        o.warm_start()
+        assert torch.equal(o.regrets, torch.from_numpy(z[f"{tag}_seeded_regrets"]))
+        for it in range(ws, T):
+            o.iteration(it)
+        o.finalize()
+        assert torch.equal(o.policy_avg, torch.from_numpy(z[f"{tag}_policy_avg"]))
+        assert torch.equal(o.values_avg[: o.N], torch.from_numpy(z[f"{tag}_root_values"]))
+        ex, _ = o.exploitability()
+        assert torch.equal(ex, torch.from_numpy(z[f"{tag}_exploitability"]))
