@@ -84,7 +84,7 @@ int p2b_showdown_values(const unsigned char* tables, const int32_t* table_of_row
  *             three launches (start pass; iteration passes in a leaner kernel; final pass) with the same
  *             results, bit for bit; the extra floats carry the root rows between the launches
  *  scalars    [iterations] 32-byte records {float t^alpha, t^alpha+1, t^beta, t^beta+1,
- *             mix_old, mix_new, fl(mix_old+mix_new); int32 do_mix}
+ *             mix_old, mix_new, fl(mix_old+mix_new); int32 do_mix (bit 0; bits 1-2 see flags bit 4)}
  *  flags      bit 0: CFR+ (cumulative regrets clamped at zero after every update, cfr_evaluator.py:1366-1368);
  *             bit 1: the value outputs of the final pass (root_values, values_avg) are shifted to zero
  *             sum, per node minus the mean over the players of sum_h values * beliefs_avg, except at
@@ -96,6 +96,9 @@ int p2b_showdown_values(const unsigned char* tables, const int32_t* table_of_row
  *             beliefs under the average policy instead of the current one (the de-averaging of the model's
  *             values, :997-1018, is the caller's part of set_leaf_values); such a solve keeps every pass in
  *             the general kernel;
+ *             bit 4: linear CFR (alternating updates, cfr_evaluator.py:1348-1349): the `do_mix` word of every
+ *             scalars record then carries, in bits 1-2, 1 + the player whose actions get no regret at that
+ *             iteration; such a solve keeps every pass in the general kernel;
  *             bit 3 (p2b_cfr_step only): the bottom-up sweep of the start pass and of every iteration pass stores
  *             the values of every node in values_avg and (iteration passes) the beliefs under the average
  *             policy, at inner nodes and at the leaves a model values, in beliefs_avg -- the inputs of the

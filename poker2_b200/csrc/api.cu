@@ -104,9 +104,9 @@ int p2b_cfr_solve(const void* subgames, const void* nodes, int32_t num_subgames,
     P2B_REQUIRE(iterations == 0 || scalars, "null scalars");
     P2B_REQUIRE(max_internal >= 1, "max_internal must be positive");
     P2B_REQUIRE(!exploitability || values_avg, "exploitability needs values_avg");
-    P2B_REQUIRE(flags >= 0 && flags <= 7,
+    P2B_REQUIRE(flags >= 0 && flags <= 31 && !(flags & 8),
                 "flags: bit 0 = CFR+ clamp, bit 1 = zero-sum value outputs, bit 2 = leaf values and regret weights at the "
-                "average-policy beliefs");
+                "average-policy beliefs, bit 4 = linear CFR");
     if (num_blocks <= 0) num_blocks = cfr_default_blocks();
     if (num_blocks > num_subgames) num_blocks = num_subgames;
     P2B_REQUIRE(scratch_floats >= cfr_scratch_floats(max_internal) * num_blocks, "scratch too small");
@@ -140,6 +140,7 @@ int p2b_cfr_solve(const void* subgames, const void* nodes, int32_t num_subgames,
     p.cfr_plus = flags & 1;
     p.enforce_zero_sum = (flags >> 1) & 1;
     p.cfr_avg = (flags >> 2) & 1;
+    p.linear = (flags >> 4) & 1;
     p.init_depth = init_depth;
     p.work_counter = work_counter;
     p.sample_pass = sample_pass;
@@ -175,9 +176,9 @@ int p2b_cfr_step(const void* subgames, const void* nodes, int32_t num_subgames, 
                 "null pointer");
     P2B_REQUIRE(max_internal >= 1, "max_internal must be positive");
     P2B_REQUIRE(!exploitability || values_avg, "exploitability needs values_avg");
-    P2B_REQUIRE(flags >= 0 && flags <= 15,
+    P2B_REQUIRE(flags >= 0 && flags <= 31,
                 "flags: bit 0 = CFR+ clamp, bit 1 = zero-sum value outputs, bit 2 = leaf values and regret weights at the "
-                "average-policy beliefs, bit 3 = keep the node values of every pass");
+                "average-policy beliefs, bit 3 = keep the node values of every pass, bit 4 = linear CFR");
     P2B_REQUIRE(!(flags & 8) || (values_avg && beliefs_avg), "flags bit 3 needs values_avg and beliefs_avg");
     P2B_REQUIRE(pass_begin >= -1 && pass_begin <= pass_end && pass_end <= iterations, "pass range outside [-1, iterations]");
     P2B_REQUIRE((phases >= 1 && phases <= 3) || phases == 4 || phases == 8,
@@ -224,6 +225,7 @@ int p2b_cfr_step(const void* subgames, const void* nodes, int32_t num_subgames, 
     p.cfr_plus = flags & 1;
     p.enforce_zero_sum = (flags >> 1) & 1;
     p.cfr_avg = (flags >> 2) & 1;
+    p.linear = (flags >> 4) & 1;
     p.iter_values = (flags >> 3) & 1;
     p.init_depth = init_depth;
     p.work_counter = work_counter;
@@ -274,9 +276,9 @@ int p2b_cfr_solve_noalloc(const void* subgames, const void* nodes, int32_t num_s
     P2B_REQUIRE(subgames && nodes && root_beliefs && regrets && policy_avg && root_values && scalars, "null pointer");
     P2B_REQUIRE(max_internal >= 1, "max_internal must be positive");
     P2B_REQUIRE(!exploitability || values_avg, "exploitability needs values_avg");
-    P2B_REQUIRE(flags >= 0 && flags <= 7,
+    P2B_REQUIRE(flags >= 0 && flags <= 31 && !(flags & 8),
                 "flags: bit 0 = CFR+ clamp, bit 1 = zero-sum value outputs, bit 2 = leaf values and regret weights at the "
-                "average-policy beliefs");
+                "average-policy beliefs, bit 4 = linear CFR");
     const uintptr_t align = reinterpret_cast<uintptr_t>(subgames) | reinterpret_cast<uintptr_t>(nodes) |
                             reinterpret_cast<uintptr_t>(tables) | reinterpret_cast<uintptr_t>(root_beliefs) |
                             reinterpret_cast<uintptr_t>(regrets) | reinterpret_cast<uintptr_t>(weight_sums) |
@@ -305,6 +307,7 @@ int p2b_cfr_solve_noalloc(const void* subgames, const void* nodes, int32_t num_s
     p.cfr_plus = flags & 1;
     p.enforce_zero_sum = (flags >> 1) & 1;
     p.cfr_avg = (flags >> 2) & 1;
+    p.linear = (flags >> 4) & 1;
     p.init_depth = init_depth;
     p.rows = rows;
     return launch_cfr_solve_static(p, max_children, (cudaStream_t)stream);

@@ -435,7 +435,7 @@ __device__ __forceinline__ void sweep_down(int mode_rt, int pass, const CfrParam
     // FIXED_MODE >= 0: compiled for that kind of pass alone (the iteration passes of a plain solve:
     // the start- and final-pass code stays out of the hot loop); otherwise the kind is a run-time value
     const int mode = FIXED_MODE >= 0 ? FIXED_MODE : mode_rt;
-    const bool mix = (mode == kPassIter) && p.scalars[pass].do_mix != 0;
+    const bool mix = (mode == kPassIter) && (p.scalars[pass].do_mix & 1) != 0;
     // cfr_avg (cfr_evaluator.py:1029, :1133): the bottom-up sweep of an iteration pass takes leaf values and
     // regret weights at the beliefs under the average policy this sweep has just updated
     const bool avgb = (mode == kPassIter) && p.cfr_avg != 0;
@@ -1037,6 +1037,8 @@ __device__ __forceinline__ void sweep_up(int mode_rt, int pass, const CfrParams&
             // instantaneous regrets of this pass folded into the discounted update of the next
             const IterScalars sc = p.scalars[pass + 1];
             const Divisor d_pos = make_divisor(sc.den_pos), d_neg = make_divisor(sc.den_neg);
+            // linear CFR: at that iteration the actions of one player get no regret (:1348-1349)
+            const bool no_regret = ((sc.do_mix >> 1) & 3) == a + 1;
             FV<VPT> ws[K];
 #pragma unroll
             for (int c = 0; c < K; ++c) {
@@ -1071,7 +1073,7 @@ __device__ __forceinline__ void sweep_up(int mode_rt, int pass, const CfrParams&
                     }
 #pragma unroll
                     for (int i = 0; i < VPT; ++i) {
-                        const float reg = __fmul_rn(wgt.v[i], __fsub_rn(Va[c].v[i], acc_a.v[i]));
+                        const float reg = no_regret ? 0.0f : __fmul_rn(wgt.v[i], __fsub_rn(Va[c].v[i], acc_a.v[i]));
                         float rr = __fadd_rn(rq.v[i], reg);
                         if (p.cfr_plus) rr = fmaxf(rr, 0.0f);
                         Rc[c].v[i] = rr;
@@ -1314,7 +1316,7 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
 
         // a one-launch solve without optional outputs takes the leanest copy of the sweeps
         const bool plain = !p.stepped && !p.leaf_beliefs && !p.leaf_values && !p.policy_sample && !p.beliefs_last &&
-                           !p.policy && !p.start_policy && !p.cfr_avg;
+                           !p.policy && !p.start_policy && !p.cfr_avg && !p.linear;
         for (int pass = pass_first; pass <= pass_last; ++pass) {
             const int mode = pass < 0 ? kPassInit : (pass == p.iterations ? kPassFinal : kPassIter);
             if (!run_down) {
@@ -1561,7 +1563,7 @@ int launch_cfr_solve(const CfrParams& params, int num_blocks, int max_children, 
     CfrParams p = params;
     p.combos = device_combo_table();
     // leaves all terminal, uniform start policy, all passes in this call: the iteration kernel applies
-    const bool plain = !p.stepped && !p.leaf_beliefs && !p.leaf_values && !p.start_policy && !p.cfr_avg;
+    const bool plain = !p.stepped && !p.leaf_beliefs && !p.leaf_values && !p.start_policy && !p.cfr_avg && !p.linear;
     if (!(plain && fast_scratch && max_children <= kCfrMaxChildren)) {
         rc = clear_counters(p.work_counter, stream);
         if (rc) return rc;

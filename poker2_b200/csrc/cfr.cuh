@@ -42,7 +42,9 @@ struct IterScalars {  // 32 bytes
     float num_pos, den_pos;  // t^alpha, t^alpha + 1      (regret discount, positive regrets)
     float num_neg, den_neg;  // t^beta,  t^beta + 1       (non-positive regrets)
     float mix_old, mix_new, mix_total;  // average-policy mixing weights and fl(old+new)
-    int32_t do_mix;          // 0: average policy := current policy at this iteration
+    int32_t do_mix;          // bit 0: 0 = average policy := current policy at this iteration; bits 1-2: linear CFR's
+                             // alternating update, 1 + the player whose actions get no regret at this iteration
+                             // (0: every action is updated); the lean iteration kernel never sees bits 1-2
 };
 
 constexpr int kCfrThreads = 672;  // 672 threads x 2 hands cover the 1344-float padded row
@@ -75,6 +77,8 @@ struct CfrParams {
     int32_t enforce_zero_sum;    // final pass: value outputs shifted to zero sum (cfr_evaluator.py:957-980, 1289-1292)
     int32_t cfr_avg;             // iteration passes: showdown values, regret weights and the beliefs handed to the
                                  // caller's model come from the beliefs under the average policy (:1029, :1133)
+    int32_t linear;              // linear CFR (alternating updates, cfr_evaluator.py:1348-1349): the scalars carry the
+                                 // skipped player per iteration; every pass stays in the general kernel
     int32_t iter_values;         // start and iteration passes store the values of every node in values_avg and (iteration
                                  // passes) the beliefs under the average policy in beliefs_avg: what a caller mixes into
                                  // running average values (`update_average_values`, cfr_evaluator.py:1260-1274)

@@ -52,8 +52,6 @@ def iteration_scalars(iterations: int, *, cfr_type: str = "discounted", alpha: f
     `solver.SteppedSolver.solve` builds that extra pass from `warm_start_mix_scalars`."""
     if cfr_type not in ("standard", "discounted", "discounted_plus", "linear"):
         raise ValueError(f"unknown cfr_type {cfr_type!r}")
-    if cfr_type == "linear":
-        raise ValueError("linear CFR (alternating updates) is not supported by the fused kernel")
     ws = max(0, int(warm_start_iterations))
     out = np.zeros(iterations, dtype=SCALAR_DTYPE)
     discounted = cfr_type in ("discounted", "discounted_plus")
@@ -77,6 +75,8 @@ def iteration_scalars(iterations: int, *, cfr_type: str = "discounted", alpha: f
         old, new = _mixing_weights(cfr_type, t, g_t, dcfr_delay)
         out[t]["mix_old"], out[t]["mix_new"], out[t]["mix_total"] = old, new, old + new
         out[t]["do_mix"] = 0 if (t == 0 or (discounted and t <= dcfr_delay)) else 1
+        if cfr_type == "linear":  # alternating updates: the actions of player t % 2 get no regret (:1348-1349)
+            out[t]["do_mix"] |= ((t % 2) + 1) << 1
     return out
 
 
@@ -84,6 +84,8 @@ def _mixing_weights(cfr_type: str, t: int, gamma: float, dcfr_delay: int):
     """`_get_mixing_weights` (cfr_evaluator.py:285-303)."""
     if cfr_type == "standard":
         return t, 1
+    if cfr_type == "linear":
+        return t, 2
     if cfr_type == "discounted":
         return t ** gamma, (t + 1) ** gamma
     return (t - dcfr_delay, 2) if t > dcfr_delay else (0, 1)  # discounted_plus
@@ -100,7 +102,7 @@ def warm_start_mix_scalars(scalars: np.ndarray, *, cfr_type: str, gamma: float, 
     old, new = _mixing_weights(cfr_type, w, gamma, dcfr_delay)
     row["mix_old"], row["mix_new"], row["mix_total"] = old, new, old + new
     discounted = cfr_type in ("discounted", "discounted_plus")
-    row["do_mix"] = 0 if (w == 0 or (discounted and w <= dcfr_delay)) else 1
+    row["do_mix"] = (0 if (w == 0 or (discounted and w <= dcfr_delay)) else 1) | (int(row["do_mix"][0]) & 6)
     return row
 
 
@@ -205,12 +207,19 @@ def layout_tensor(layout, name: str, device, dtype=None) -> torch.Tensor:
     return t if dtype is None else t.to(dtype)
 
 
-def solve_flags(cfr_plus: bool, enforce_zero_sum: bool, cfr_avg: bool = False, iter_values: bool = False) -> int:
+def scalars_are_linear(scalars: np.ndarray) -> bool:
+    """True if the table was made for linear CFR (some iteration skips a player's regrets)."""
+    return bool((scalars["do_mix"] & 6).any())
+
+
+def solve_flags(cfr_plus: bool, enforce_zero_sum: bool, cfr_avg: bool = False, iter_values: bool = False,
+                linear: bool = False) -> int:
     """The `flags` argument of the solve entry points: bit 0 = CFR+ clamp, bit 1 = zero-sum value outputs,
     bit 2 = leaf values and regret weights at the beliefs under the average policy (`cfr_avg` upstream),
-    bit 3 (stepped solves) = keep the node values and average beliefs of every pass."""
+    bit 3 (stepped solves) = keep the node values and average beliefs of every pass, bit 4 = linear CFR (the
+    scalars carry the skipped player; every pass in the general kernel)."""
     return (int(bool(cfr_plus)) | (int(bool(enforce_zero_sum)) << 1) | (int(bool(cfr_avg)) << 2)
-            | (int(bool(iter_values)) << 3))
+            | (int(bool(iter_values)) << 3) | (int(bool(linear)) << 4))
 
 
 def pad_rows(x: torch.Tensor) -> torch.Tensor:
@@ -380,7 +389,8 @@ class SubgameSolver:
                 p(self.regrets), p(self.weight_sums), p(self.policy_avg), p(self.policy), p(self.root_values),
                 p(self.values_avg), p(self.beliefs_avg), p(self.exploitability), p(self.br_values), p(self.scratch),
                 self.scratch.numel(),
-                p(sc) if iterations else None, iterations, solve_flags(cfr_plus, enforce_zero_sum, cfr_avg),
+                p(sc) if iterations else None, iterations,
+                solve_flags(cfr_plus, enforce_zero_sum, cfr_avg, linear=scalars_are_linear(scalars)),
                 self.layout.tree_depth, p(self.work_counter),
                 self.num_blocks, p(self.sample_pass), p(self.policy_sample), p(self.beliefs_last),
                 p(self.queue_order), _lib.stream_ptr(self.device))
@@ -480,7 +490,7 @@ class SteppedSolver(SubgameSolver):
         assert root_beliefs.shape == (self.B, 2, HPAD) and root_beliefs.dtype == torch.float32
         assert root_beliefs.is_contiguous() and root_beliefs.device == self.device
         ws = int(warm_start_iterations)
-        flags = solve_flags(cfr_plus, enforce_zero_sum, cfr_avg, running_values)
+        flags = solve_flags(cfr_plus, enforce_zero_sum, cfr_avg, running_values, linear=scalars_are_linear(scalars))
         if running_values and self.values_avg is None:
             raise ValueError("running_values needs a solver built with keep_node_values=True")
         if warm_start_type not in ("model", "model_br"):

@@ -19,7 +19,9 @@ touches:
 
 No upstream module is imported.  The leaf model is called as `model(beliefs [S,2,1326], boards [S,5],
 context [S,3])` (see `leaf_eval`); a model object may carry that callable as `b200_leaf_model`.
-Not covered: linear CFR (raises at construction).
+Every `cfg.search` combination of the sparse evaluator is accepted (CFR types standard, linear, discounted,
+discounted_plus; `cfr_plus`, `cfr_avg`, both warm start types, value targets from the final policy or from the
+running average).
 """
 from __future__ import annotations
 

@@ -282,5 +282,26 @@ def gen_warm_br() -> None:
          hand_weights=gc.hand_weights().numpy(), **out)
 
 
+def gen_linear() -> None:
+    """cfr_type = linear (the dataclass default upstream): no discounting, alternating updates (the actions of
+    player t % 2 get no regret at iteration t, cfr_evaluator.py:1348-1349), mixing weights (t, 2); with the CFR+
+    clamp the dataclass default also sets.  River subgames, 13 iterations."""
+    from p2.core.structured_config import CFRType
+
+    b, r, p, s = gc.seeded_inputs(61, 2, (20, 200), (100, 1000))
+    iterations, cap, depth = 13, 2, 8
+    gc.install_raise_cap(cap)
+    ev = gc.make_evaluator(2, iterations, depth=depth, search=dict(cfr_type=CFRType.linear, cfr_plus=True))
+    ex = _solve(ev, gc.river_env(b, p, s), 2, r)
+    gc.install_raise_cap(None)
+    print("linear CFR: nodes", ev.total_nodes, "exploitability", ex.local_exploitability.tolist())
+    save("cfr_linear_cap2_t13.npz",
+         boards=b.to(torch.int16).numpy(), ranges=r.numpy(), pot=p.numpy(), stack=s.numpy(),
+         iterations=np.int64(iterations), cap=np.int64(cap), max_depth=np.int64(depth),
+         total_nodes=np.int64(ev.total_nodes), regrets=ev.cumulative_regrets.numpy(),
+         weight_sums=ev.regret_weight_sums.numpy(), policy_avg=ev.policy_probs_avg.numpy(),
+         root_values=ev.values_avg[:2].numpy(), exploitability=ex.local_exploitability.numpy())
+
+
 gc.SECTIONS.update(production=gen_production, standard=gen_standard, zero_sum=gen_zero_sum, ragged256=gen_ragged256,
-                   cfr_avg=gen_cfr_avg, running_values=gen_running_values, warm_br=gen_warm_br)
+                   cfr_avg=gen_cfr_avg, running_values=gen_running_values, warm_br=gen_warm_br, linear=gen_linear)

@@ -251,3 +251,21 @@ def test_model_br_warm_start_matches_upstream(cuda_device, golden_dir):
         order = solver.layout_tensor(layout, "from_level_major", cuda_device)
         seeded = (seen["raw"] * weight).index_select(0, order)[:, :1326].cpu()
         _close(f"{tag} seeded regrets", seeded[n:], torch.from_numpy(z[f"{tag}_seeded_regrets"])[n:])
+
+
+def test_linear_cfr_matches_upstream(cuda_device, golden_dir):
+    """cfr_type = linear with the CFR+ clamp: alternating updates, mixing weights (t, 2); every pass in the
+    general kernel.  Through the one-call solve and through the allocation-free entry."""
+    from poker2_b200 import solver
+
+    z = np.load(os.path.join(golden_dir, "cfr_linear_cap2_t13.npz"))
+    res, trees = solver.solve_subgames(z["boards"].astype(np.int64), torch.from_numpy(z["ranges"]), z["pot"], z["stack"],
+                                       iterations=int(z["iterations"]), max_depth=int(z["max_depth"]),
+                                       max_raises=int(z["cap"]), cfr_type="linear", cfr_plus=True, exploitability=True,
+                                       device=cuda_device)
+    assert trees.total_nodes == int(z["total_nodes"])
+    n = trees.num_roots
+    for name, got in [("regrets", res.regrets), ("weight_sums", res.weight_sums), ("policy_avg", res.policy_avg)]:
+        _close(name, res.level_major(got).cpu()[n:], torch.from_numpy(z[name])[n:])
+    _close("root_values", res.root_values[..., :1326].cpu(), torch.from_numpy(z["root_values"]))
+    _close("exploitability", res.exploitability.cpu(), torch.from_numpy(z["exploitability"]), rtol=1e-4)

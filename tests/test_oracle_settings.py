@@ -196,3 +196,16 @@ def test_oracle_model_br_warm_start_bit_exact(golden_dir):
         assert torch.equal(o.values_avg[: o.N], torch.from_numpy(z[f"{tag}_root_values"]))
         ex, _ = o.exploitability()
         assert torch.equal(ex, torch.from_numpy(z[f"{tag}_exploitability"]))
+
+
+def test_oracle_linear_cfr_bit_exact(golden_dir):
+    z = np.load(os.path.join(golden_dir, "cfr_linear_cap2_t13.npz"))
+    t = _build(z["pot"], z["stack"], int(z["cap"]), int(z["max_depth"]))
+    o = ocfr.SubgameOracle(t.oracle_dict(z["boards"].astype(np.int64)), torch.from_numpy(z["ranges"]),
+                           iterations=int(z["iterations"]), cfr_type="linear", cfr_plus=True).solve()
+    assert torch.equal(o.regrets, torch.from_numpy(z["regrets"]))
+    assert torch.equal(o.weight_sums, torch.from_numpy(z["weight_sums"]))
+    assert torch.equal(o.policy_avg, torch.from_numpy(z["policy_avg"]))
+    assert torch.equal(o.values_avg[: o.N], torch.from_numpy(z["root_values"]))
+    ex, _ = o.exploitability()
+    assert torch.equal(ex, torch.from_numpy(z["exploitability"]))
