@@ -196,6 +196,49 @@ class SubgameEvaluator:
         return SampledStates(nodes=cont, beliefs=cont_beliefs, state=self.trees.state.take(cont_np),
                              boards=self.boards[self.trees.root_of[cont_np]], all_nodes=nodes)
 
+    # ------------------------------------------------------------------ start policy from a policy head
+    def start_policy_from_head(self, logits_fn) -> torch.Tensor:
+        """The level-by-level start of `initialize_policy_and_beliefs` (cfr_evaluator.py:832-886): a policy head
+        that reads the node beliefs gives the policy of one tree level at a time, because the beliefs of a level
+        follow from the policies of the levels above.  For every level,
+        `logits_fn(nodes [K] int64 upstream node indices, beliefs [K,2,1326] fp32) -> [K,1326,A]` policy logits;
+        they are masked by the legal actions (the lowest finite value, :306-330), soft-maxed and pushed down to
+        the children; the children's beliefs are the parent's, times the policy for the player who acted,
+        and every row is blocked by its board and re-normalised once per level, as upstream does.
+        Returns the start policy [M,1326] in the upstream node order, to hand to `evaluate_cfr`."""
+        t, dev = self.trees, self.device
+        offs, M, N, A = t.depth_offsets, t.total_nodes, t.num_roots, t.num_actions
+        as_t = lambda a, dt=None: torch.from_numpy(np.ascontiguousarray(a)).to(dev, dt)  # noqa: E731
+        parent, action, to_act = as_t(t.parent_index, torch.int64), as_t(t.action_from_parent, torch.int64), as_t(t.state.to_act, torch.int64)
+        legal, child_count = as_t(t.legal_mask, torch.bool), as_t(t.child_count, torch.int64)
+        root_of = as_t(t.root_of, torch.int64)
+        c1, c2 = np.triu_indices(52, k=1)  # the 1326 combos in their order: (c1 < c2), c1-major
+        hit = torch.zeros(N, 53, dtype=torch.bool, device=dev)
+        cards = torch.from_numpy(self.boards).to(dev)
+        hit.scatter_(1, torch.where(cards >= 0, cards, torch.full_like(cards, 52)), True)
+        allowed_root = ~(hit[:, as_t(c1, torch.int64)] | hit[:, as_t(c2, torch.int64)])  # combos off the board
+        prob_root = allowed_root.to(torch.float32)
+        prob_root = prob_root / prob_root.sum(-1, keepdim=True).clamp(min=1.0)
+        allowed, allowed_prob = allowed_root[root_of], prob_root[root_of]
+        beliefs = torch.zeros(M, 2, NUM_HANDS, device=dev, dtype=torch.float32)
+        beliefs[:N] = self.root_beliefs[..., :NUM_HANDS]
+        policy = torch.zeros(M, NUM_HANDS, device=dev, dtype=torch.float32)
+        for d in range(t.tree_depth):
+            a, b, c = int(offs[d]), int(offs[d + 1]), int(offs[d + 2])
+            logits = logits_fn(torch.arange(a, b), beliefs[a:b]).to(dev, torch.float32)
+            masked = logits.masked_fill(~legal[a:b][:, None, :], torch.finfo(torch.float32).min)
+            probs = torch.softmax(masked, dim=-1)
+            probs.masked_fill_((child_count[a:b] == 0)[:, None, None], 0.0)
+            policy[b:c] = probs[parent[b:c] - a, :, action[b:c]]
+            level = beliefs[parent[b:c]].clone()
+            rows = torch.arange(c - b, device=dev)
+            level[rows, to_act[parent[b:c]]] *= policy[b:c]
+            beliefs[b:c] = level
+            beliefs.masked_fill_((~allowed)[:, None, :], 0.0)
+            denom = beliefs.sum(dim=-1, keepdim=True)
+            beliefs = torch.where(denom > 1e-5, beliefs / denom, allowed_prob[:, None, :].expand_as(beliefs))
+        return policy
+
     # ------------------------------------------------------------------ state by the upstream names
     # (cfr_evaluator.py:107-170; tests and tools read these attributes).  Node order and widths are
     # the upstream ones: level-major over the batch, 1326 columns.  Available after evaluate_cfr.

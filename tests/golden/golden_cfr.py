@@ -358,6 +358,24 @@ class FixedLogitModel(ZeroModel):
                            hand_values=torch.zeros(n, 2, 1326))
 
 
+class BeliefLogitModel(ZeroModel):
+    """Policy head stand-in whose logits depend on the node's beliefs: fixed (hand, action) logits plus
+    30 x the belief of the player to act in that hand x a per-action weight.  The start policy of a level
+    then depends on the beliefs the levels above produced (`initialize_policy_and_beliefs` :832-886)."""
+
+    def __call__(self, features, include_policy=True, **kw):
+        from p2.models.model_output import ModelOutput
+
+        n = len(features)
+        g = torch.Generator().manual_seed(31)
+        fixed = torch.randn(1326, self.num_actions, generator=g)
+        w = torch.linspace(-1.0, 1.0, self.num_actions)
+        bel = features.beliefs.view(n, 2, 1326).float()
+        mine = bel.gather(1, features.to_act.long()[:, None, None].expand(-1, 1, 1326)).squeeze(1)  # [n,1326]
+        logits = fixed[None] + 30.0 * mine[:, :, None] * w[None, None, :]
+        return ModelOutput(policy_logits=logits, value=torch.zeros(n), hand_values=torch.zeros(n, 2, 1326))
+
+
 def gen_warm_start() -> None:
     """River subgames with the model's policy as start policy and regrets seeded from it
     (`warm_start`, cfr_evaluator.py:887-926, type `model`), then the remaining iterations."""

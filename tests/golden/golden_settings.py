@@ -303,5 +303,38 @@ def gen_linear() -> None:
          root_values=ev.values_avg[:2].numpy(), exploitability=ex.local_exploitability.numpy())
 
 
+def gen_policy_head() -> None:
+    """Start policy from a policy head that reads the node beliefs, level by level
+    (`initialize_policy_and_beliefs`, cfr_evaluator.py:832-886), then a warm start of type `model` and the
+    remaining iterations.  River subgames."""
+    from p2.core.structured_config import WarmStartType
+
+    b, r, p, s = gc.seeded_inputs(71, 2, (20, 200), (100, 1000))
+    iterations, ws, mult, cap, depth = 8, 2, 5.0, 2, 8
+    gc.install_raise_cap(cap)
+    ev = gc.make_evaluator(2, iterations, depth=depth)
+    ev.model = gc.BeliefLogitModel(len(BET_BINS) + 3)
+    ev.warm_start_iterations, ev.warm_start_type, ev.warm_start_multiplier = ws, WarmStartType.model, mult
+    captured = {}
+    original = ev.warm_start
+
+    def hooked():
+        captured["start_policy"] = ev.policy_probs.clone()
+        captured["start_beliefs"] = ev.beliefs.clone()
+        original()
+
+    ev.warm_start = hooked
+    ex = _solve(ev, gc.river_env(b, p, s), 2, r)
+    gc.install_raise_cap(None)
+    print("policy head: nodes", ev.total_nodes, "exploitability", ex.local_exploitability.tolist())
+    save("cfr_policy_head.npz",
+         boards=b.to(torch.int16).numpy(), ranges=r.numpy(), pot=p.numpy(), stack=s.numpy(),
+         iterations=np.int64(iterations), warm_start_iterations=np.int64(ws), warm_start_multiplier=np.float64(mult),
+         cap=np.int64(cap), max_depth=np.int64(depth), total_nodes=np.int64(ev.total_nodes),
+         start_policy=captured["start_policy"].numpy(), start_beliefs=captured["start_beliefs"].numpy(),
+         policy_avg=ev.policy_probs_avg.numpy(), root_values=ev.values_avg[:2].numpy(),
+         exploitability=ex.local_exploitability.numpy())
+
+
 gc.SECTIONS.update(production=gen_production, standard=gen_standard, zero_sum=gen_zero_sum, ragged256=gen_ragged256,
-                   cfr_avg=gen_cfr_avg, running_values=gen_running_values, warm_br=gen_warm_br, linear=gen_linear)
+                   cfr_avg=gen_cfr_avg, running_values=gen_running_values, warm_br=gen_warm_br, linear=gen_linear, policy_head=gen_policy_head)

@@ -138,3 +138,48 @@ def test_evaluator_on_flop_subgames_with_network_leaves(cuda_device):
     by_src[torch.from_numpy(trees.parent_index[n:]), torch.from_numpy(trees.action_from_parent[n:])] = o.policy_avg[n:]
     keep = torch.from_numpy(~trees.leaf_mask[:top])
     torch.testing.assert_close(policy_batch.policy_targets.cpu(), by_src.permute(0, 2, 1)[keep], rtol=1e-3, atol=1e-4)
+
+
+def test_start_policy_from_a_belief_dependent_policy_head(cuda_device, golden_dir):
+    """`initialize_policy_and_beliefs` upstream asks the policy head level by level, because a level's beliefs
+    follow from the policies above it.  With a head whose logits read the beliefs: the start policy equals the
+    upstream one, and the solve that follows (warm start of type `model`) matches too."""
+    import os
+
+    from poker2_b200 import evaluator as pev, tree as ptree
+
+    z = np.load(os.path.join(golden_dir, "cfr_policy_head.npz"))
+    n = z["boards"].shape[0]
+    roots = ptree.root_states(z["pot"], z["stack"], min_raise=2)
+    ev = pev.SubgameEvaluator(cuda_device, iterations=int(z["iterations"]), max_depth=int(z["max_depth"]),
+                              max_raises=int(z["cap"]), warm_start_iterations=int(z["warm_start_iterations"]),
+                              warm_start_multiplier=float(z["warm_start_multiplier"]),
+                              generator=torch.Generator().manual_seed(5))
+    env = pev.env_view(roots, z["boards"].astype(np.int64))
+    ev.initialize_subgame(env, torch.arange(n), torch.from_numpy(z["ranges"]))
+    assert ev.trees.total_nodes == int(z["total_nodes"])
+    A = ev.trees.num_actions
+    fixed = torch.randn(1326, A, generator=torch.Generator().manual_seed(31))
+    w = torch.linspace(-1.0, 1.0, A)
+    to_act = torch.from_numpy(ev.trees.state.to_act).long()
+
+    def head(nodes, beliefs):
+        mine = beliefs.cpu().gather(1, to_act[nodes][:, None, None].expand(-1, 1, 1326)).squeeze(1)
+        return fixed[None] + 30.0 * mine[:, :, None] * w[None, None, :]
+
+    start = ev.start_policy_from_head(head)
+    torch.testing.assert_close(start.cpu()[n:], torch.from_numpy(z["start_policy"])[n:], rtol=1e-5, atol=1e-6)
+    # the solve that follows: from the helper's policy (its 1e-7 differences from the upstream start policy
+    # grow through the warm start's seeding and eight iterations of regret matching: 2e-3), and from the
+    # upstream start policy itself (the solver's usual tolerance)
+    ev.evaluate_cfr(start_policy=start.cpu())
+    res = ev._result
+    torch.testing.assert_close(res.level_major(res.policy_avg).cpu()[n:], torch.from_numpy(z["policy_avg"])[n:],
+                               rtol=2e-3, atol=5e-4)
+    torch.testing.assert_close(res.root_values[..., :1326].cpu(), torch.from_numpy(z["root_values"]), rtol=2e-3, atol=5e-4)
+    ev.evaluate_cfr(start_policy=torch.from_numpy(z["start_policy"]))
+    res = ev._result
+    torch.testing.assert_close(res.level_major(res.policy_avg).cpu()[n:], torch.from_numpy(z["policy_avg"])[n:],
+                               rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(res.root_values[..., :1326].cpu(), torch.from_numpy(z["root_values"]), rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(res.exploitability.cpu(), torch.from_numpy(z["exploitability"]), rtol=1e-4, atol=1e-6)
