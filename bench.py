@@ -255,6 +255,7 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
         sv2.release()
         del sv2
         torch.cuda.empty_cache()
+        extras["production_search_block"] = production_member(solver, layout, boards, rb, device)
         extras["micro"] = micro_member(device)
     if distributed and not args.no_extras:
         extras["strong"] = run_strong(args, solver, sharding, rank, world, device)
@@ -264,6 +265,47 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
         e2e = run_e2e(args, solver, sv, boards, ranges, pot, stack, layout, scal, gathered, distributed, device,
                       units_per_step)
     finish_gpu_arm(args, rank, world, layout, ms_step, value, clocks, e2e, distributed, extras)
+
+
+def production_member(solver, layout, boards, rb, device):
+    """The same 4096 river subgames under the search block of the upstream production configuration
+    (conf/config_rebel_cfr.yaml:78-94: discounted_plus with a delay of 80, exponent schedules alpha 2->4,
+    beta -1->-2, gamma 5->0, 200 iterations of which a warm start of type `model` replaces the first 15,
+    multiplier 10, zero-sum value targets), through the one-call solve.  The start policy stands in for the
+    policy head's soft-max: a fixed random soft-max per (node, hand)."""
+    T, ws, delay, mult = 200, 15, 80, 10.0
+    kw = dict(cfr_type="discounted_plus", gamma=5.0, dcfr_delay=delay)
+    scal = solver.iteration_scalars(T, alpha=2.0, alpha_final=4.0, beta=-1.0, beta_final=-2.0, gamma_final=0.0,
+                                    warm_start_iterations=ws, **kw)
+    first = solver.warm_start_mix_scalars(scal, warm_start_iterations=ws, **kw)
+    sv = solver.SubgameSolver(layout, boards, device, exploitability=True)
+    # start policy in the kernel's row order: soft-max of seeded logits over the siblings of every node
+    g = torch.Generator(device=device).manual_seed(SEED)
+    logits = torch.randn(layout.rows, 1326, device=device, generator=g)
+    nodes = sv.nodes.view(torch.uint8).reshape(-1, 16)
+    sub = sv.subgames.view(torch.int32).reshape(-1, 8)
+    row_sub = torch.repeat_interleave(torch.arange(sub.shape[0], device=device), sub[:, 1].long())
+    parent_row = sub[:, 0].long()[row_sub] + nodes[:, 0].long()  # node_begin + local parent index
+    e = logits.exp()
+    denom = torch.zeros_like(e).index_add_(0, parent_row, e)
+    policy_rows = e / denom[parent_row]
+    to_level = solver.layout_tensor(layout, "from_level_major", device)
+    start_policy = policy_rows.index_select(0, to_level)  # the call takes the upstream node order
+    del logits, e, denom, policy_rows
+
+    def step():
+        sv.solve(rb, scal, start_policy=start_policy, warm_start_iterations=ws, warm_start_multiplier=mult,
+                 warm_start_scalars=first, enforce_zero_sum=True)
+
+    ms = _time_ms(step, 1, 1)
+    passes = T - ws + 1  # the warm start's own policy update and iterations 15..199
+    sv.release()
+    del start_policy
+    torch.cuda.empty_cache()
+    return {"workload": "B=4096 river subgames, discounted_plus (delay 80, alpha 2->4, beta -1->-2, gamma 5->0), 200 "
+                        "iterations with a 15-iteration warm start of type model x 10, zero-sum targets",
+            "ms_per_step": ms, "iteration_passes": passes, "value": BATCH * passes / (ms / 1e3),
+            "unit": "subgame-iterations/s (passes actually run)"}
 
 
 def run_strong(args, solver, sharding, rank, world, device):

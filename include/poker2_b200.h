@@ -123,14 +123,22 @@ int p2b_showdown_values(const unsigned char* tables, const int32_t* table_of_row
  *             nodes (what sample_leaves returns for the sampled nodes).
  *  queue_order [num_subgames] int32 (may be NULL: input order): the subgame taken at each position of the
  *             queue the thread blocks draw from.  A permutation with the largest trees first shortens the
- *             tail in which few blocks are still busy; results do not depend on it. */
+ *             tail in which few blocks are still busy; results do not depend on it.
+ *  start_policy [rows,1344] (may be NULL: uniform over the children): the policy of the start pass, i.e. the
+ *             soft-max of the model's policy head at every node (initialize_policy_and_beliefs :832-886)
+ *  warm_start_weight  0, or warm-start iterations x multiplier: after the start pass the regrets are seeded so
+ *             that regret matching replays the start policy (warm_start of type `model`, :913-926).  scalars[0]
+ *             then belongs to the warm start's own policy update (update_policy(w), :923) and scalars[k], k >= 1,
+ *             to iteration w + k - 1; `iterations` counts these passes.  Needs the scratch area of
+ *             p2b_cfr_solve_scratch_floats. */
 int p2b_cfr_solve(const void* subgames, const void* nodes, int32_t num_subgames, int64_t rows, int32_t max_children,
                   int32_t max_internal, const unsigned char* tables, const float* root_beliefs,
                   float* regrets, float* weight_sums, float* policy_avg, float* policy,
                   float* root_values, float* values_avg, float* beliefs_avg, float* exploitability,
                   float* br_values, float* scratch, int64_t scratch_floats, const void* scalars, int32_t iterations, int32_t flags,
                   int32_t init_depth, int32_t* work_counter, int32_t num_blocks, const int32_t* sample_pass,
-                  float* policy_sample, float* beliefs_last, const int32_t* queue_order, void* stream);
+                  float* policy_sample, float* beliefs_last, const int32_t* queue_order, const float* start_policy,
+                  float warm_start_weight, void* stream);
 int64_t p2b_cfr_scratch_floats(int32_t max_internal, int32_t num_blocks);
 int64_t p2b_cfr_solve_scratch_floats(int32_t max_internal, int32_t max_children, int32_t num_blocks,
                                      int32_t num_subgames, int64_t rows);

@@ -93,8 +93,11 @@ int p2b_cfr_solve(const void* subgames, const void* nodes, int32_t num_subgames,
                   float* beliefs_avg, float* exploitability, float* br_values, float* scratch, int64_t scratch_floats,
                   const void* scalars, int32_t iterations, int32_t flags, int32_t init_depth, int32_t* work_counter,
                   int32_t num_blocks, const int32_t* sample_pass, float* policy_sample, float* beliefs_last,
-                  const int32_t* queue_order, void* stream) {
+                  const int32_t* queue_order, const float* start_policy, float warm_start_weight, void* stream) {
     P2B_REQUIRE(num_subgames >= 0 && iterations >= 0 && rows >= 0, "negative count");
+    P2B_REQUIRE(warm_start_weight >= 0.0f && (warm_start_weight == 0.0f || (start_policy && rows > 0)),
+                "a warm start needs a start policy, the row count and a non-negative weight");
+    P2B_REQUIRE((reinterpret_cast<uintptr_t>(start_policy) & 15) == 0, "all arrays must be 16-byte aligned");
     P2B_REQUIRE(!policy_sample || sample_pass, "policy_sample needs sample_pass");
     P2B_REQUIRE(((reinterpret_cast<uintptr_t>(policy_sample) | reinterpret_cast<uintptr_t>(beliefs_last)) & 15) == 0,
                 "all arrays must be 16-byte aligned");
@@ -148,6 +151,8 @@ int p2b_cfr_solve(const void* subgames, const void* nodes, int32_t num_subgames,
     p.beliefs_last = beliefs_last;
     p.rows = rows;
     p.queue_order = queue_order;
+    p.start_policy = start_policy;
+    p.warm_weight = warm_start_weight;
     // with the larger scratch area of p2b_cfr_solve_scratch_floats the iteration passes of a plain
     // solve run in the lean iteration kernel
     const bool fast_scratch =

@@ -1551,7 +1551,7 @@ long long cfr_solve_scratch_floats(int max_internal, int max_children, int num_b
     long long per_block = cfr_scratch_floats(max_internal);
     const long long iter_block = cfr_iter_scratch_floats(max_internal, max_children);
     if (iter_block > per_block) per_block = iter_block;
-    const long long carry_sums = ((rows * 2 + 3) / 4) * 4;
+    const long long carry_sums = rows * 4;  // current-policy sums and, for cfr_avg, average-policy sums
     return per_block * num_blocks + (long long)num_subgames * 4 * P2B_HPAD + carry_sums;
 }
 
@@ -1563,8 +1563,42 @@ int launch_cfr_solve(const CfrParams& params, int num_blocks, int max_children, 
     CfrParams p = params;
     p.combos = device_combo_table();
     // leaves all terminal, uniform start policy, all passes in this call: the iteration kernel applies
-    const bool plain = !p.stepped && !p.leaf_beliefs && !p.leaf_values && !p.start_policy && !p.cfr_avg && !p.linear;
+    if (p.warm_weight > 0.0f && (!p.start_policy || !p.rows))
+        return set_error(P2B_ERR_ARG, "a warm start needs a start policy and the row count of the state arrays");
+    // leaves all terminal, all passes in this call: the iteration kernel applies (a start policy only concerns
+    // the start pass, a warm start of type `model` is a kernel of its own between that pass and the iterations)
+    const bool plain = !p.stepped && !p.leaf_beliefs && !p.leaf_values && !p.cfr_avg && !p.linear;
+    long long per_block = cfr_scratch_floats(p.max_internal);
+    const long long iter_block = cfr_iter_scratch_floats(p.max_internal, max_children);
+    if (iter_block > per_block) per_block = iter_block;
     if (!(plain && fast_scratch && max_children <= kCfrMaxChildren)) {
+        if (p.warm_weight > 0.0f) {
+            // the general kernel in two launches around the seeding: start pass, then every other pass
+            if (p.stepped) return set_error(P2B_ERR_ARG, "a stepped solve seeds its warm start itself");
+            if (!fast_scratch)
+                return set_error(P2B_ERR_ARG, "a warm start needs the scratch area of p2b_cfr_solve_scratch_floats "
+                                              "(hand-over rows between the launches)");
+            CfrParams q = p;
+            q.scratch_stride = per_block;
+            q.carry_roots = p.scratch + per_block * num_blocks;
+            q.carry_sums = q.carry_roots + (long long)p.num_subgames * 4 * P2B_HPAD;
+            q.stepped = 1;
+            q.scratch_per_block = 1;
+            q.phases = 3;
+            for (int part = 0; part < 2; ++part) {
+                q.pass_begin = part == 0 ? -1 : 0;
+                q.pass_end = part == 0 ? -1 : p.iterations;
+                rc = clear_counters(q.work_counter, stream);
+                if (rc) return rc;
+                rc = dispatch_cfr(q, num_blocks, max_children, stream);
+                if (rc) return rc;
+                if (part == 0) {
+                    rc = launch_cfr_warm_seed(p.nodes, p.rows, p.start_policy, p.warm_weight, p.regrets, p.weight_sums, stream);
+                    if (rc) return rc;
+                }
+            }
+            return P2B_OK;
+        }
         rc = clear_counters(p.work_counter, stream);
         if (rc) return rc;
         return dispatch_cfr(p, num_blocks, max_children, stream);
@@ -1572,9 +1606,6 @@ int launch_cfr_solve(const CfrParams& params, int num_blocks, int max_children, 
     // A plain solve runs as: start pass (cfr_solve_kernel), iteration passes (cfr_iter_kernel), final
     // pass with the best responses (cfr_solve_kernel).  Root rows and their sums travel between the
     // launches in the tail of the scratch area; work rows do not, so each launch keeps one set per block.
-    long long per_block = cfr_scratch_floats(p.max_internal);
-    const long long iter_block = cfr_iter_scratch_floats(p.max_internal, max_children);
-    if (iter_block > per_block) per_block = iter_block;
     p.scratch_stride = per_block;
     p.carry_roots = p.scratch + per_block * num_blocks;
     p.carry_sums = p.carry_roots + (long long)p.num_subgames * 4 * P2B_HPAD;
@@ -1603,6 +1634,10 @@ int launch_cfr_solve(const CfrParams& params, int num_blocks, int max_children, 
             rc = dispatch_cfr(q, num_blocks, max_children, stream);
         }
         if (rc) return rc;
+        if (part == 0 && p.warm_weight > 0.0f) {
+            rc = launch_cfr_warm_seed(p.nodes, p.rows, p.start_policy, p.warm_weight, p.regrets, p.weight_sums, stream);
+            if (rc) return rc;
+        }
     }
     return P2B_OK;
 }

@@ -107,6 +107,9 @@ struct CfrParams {
     float* policy_sample;        // [rows][HPAD] (out, may be null)
     float* beliefs_last;         // [rows][2][HPAD] beliefs of the last iteration at internal nodes (out, may be null)
     const float* start_policy;   // [rows][HPAD] policy of the start pass (may be null: uniform over the children)
+    float warm_weight;           // one-call solve only: > 0 = warm start of type `model` (cfr_evaluator.py:913-926) after the
+                                 // start pass, weight = warm-start iterations x multiplier; scalars[0] then belongs to the
+                                 // warm start's own policy update
     // ---- limits the record check compares the records with
     long long rows;              // rows of the state arrays
     int32_t leaf_slots;          // model-leaf slots of leaf_beliefs / leaf_values

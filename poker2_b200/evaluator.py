@@ -126,7 +126,11 @@ class SubgameEvaluator:
         self.root_nodes = n
         boards_t = torch.from_numpy(self.boards)
         kw = dict(exploitability=True, keep_node_values=True, sampling=True)
-        self.stepped = bool(self.layout.num_model_leaves) or self.warm_start_iterations > 0 or self.running_values
+        # pass by pass only where something happens between the passes: leaves valued by the network, running
+        # value averages, the best-response pass of a `model_br` warm start; a warm start of type `model` and a
+        # start policy fit the one-call solve, whose iteration passes run in the lean kernel
+        self.stepped = (bool(self.layout.num_model_leaves) or self.running_values
+                        or (self.warm_start_iterations > 0 and self.warm_start_type == "model_br"))
         if self.layout.num_model_leaves:
             if self.model is None:
                 raise ValueError("the subgames have non-terminal leaves: a leaf model is required")
@@ -164,24 +168,24 @@ class SubgameEvaluator:
                                          gamma=self.gamma, dcfr_delay=self.dcfr_delay, alpha_final=self.alpha_final,
                                          beta_final=self.beta_final, gamma_final=self.gamma_final,
                                          warm_start_iterations=ws)
+        if ws > 0 and start_policy is None:  # uniform over the children of every parent
+            cc = torch.from_numpy(self.trees.child_count[self.trees.parent_index.clip(min=0)]).clamp(min=1)
+            start_policy = (1.0 / cc.to(torch.float32))[:, None].expand(-1, NUM_HANDS).contiguous()
+        first = None
+        if ws > 0:
+            first = psolver.warm_start_mix_scalars(scal, cfr_type=self.cfr_type, gamma=self.gamma,
+                                                   dcfr_delay=self.dcfr_delay, warm_start_iterations=ws)
         if self.stepped:
-            if ws > 0 and start_policy is None:  # uniform over the children of every parent
-                cc = torch.from_numpy(self.trees.child_count[self.trees.parent_index.clip(min=0)]).clamp(min=1)
-                start_policy = (1.0 / cc.to(torch.float32))[:, None].expand(-1, NUM_HANDS).contiguous()
-            first = None
-            if ws > 0:
-                first = psolver.warm_start_mix_scalars(scal, cfr_type=self.cfr_type, gamma=self.gamma,
-                                                       dcfr_delay=self.dcfr_delay, warm_start_iterations=ws)
             res = self.solver.solve(self.root_beliefs, scal, self.leaf_fn, cfr_plus=self.cfr_plus,
                                     enforce_zero_sum=self.enforce_zero_sum, start_policy=start_policy,
                                     warm_start_iterations=ws, warm_start_multiplier=self.warm_start_multiplier,
                                     warm_start_scalars=first, cfr_avg=self.cfr_avg, running_values=self.running_values,
                                     warm_start_type=self.warm_start_type)
         else:
-            if start_policy is not None:
-                raise ValueError("a start policy needs the stepped solver (set warm_start_iterations or use model leaves)")
             res = self.solver.solve(self.root_beliefs, scal, cfr_plus=self.cfr_plus,
-                                    enforce_zero_sum=self.enforce_zero_sum, cfr_avg=self.cfr_avg)
+                                    enforce_zero_sum=self.enforce_zero_sum, cfr_avg=self.cfr_avg,
+                                    start_policy=start_policy, warm_start_iterations=ws,
+                                    warm_start_multiplier=self.warm_start_multiplier, warm_start_scalars=first)
         self._result = res
         from . import stats as pstats
 

@@ -369,15 +369,31 @@ class SubgameSolver:
             setattr(self, name, None)
 
     def solve(self, root_beliefs: torch.Tensor, scalars: np.ndarray, *, cfr_plus: bool = False,
-              enforce_zero_sum: bool = False, cfr_avg: bool = False, check: bool = False) -> SolveResult:
+              enforce_zero_sum: bool = False, cfr_avg: bool = False, check: bool = False,
+              start_policy: torch.Tensor | None = None, warm_start_iterations: int = 0,
+              warm_start_multiplier: float = 1.0, warm_start_scalars: np.ndarray | None = None) -> SolveResult:
         """root_beliefs: [B,2,1344] fp32 on the device (padded).  Enqueues the solve (one to three
-        kernels).  enforce_zero_sum: shift the value outputs to zero sum, as upstream does when
+        kernels, one more for a warm start).  start_policy [M,1326] in the upstream node order (the policy head's
+        soft-max; None = uniform); with warm_start_iterations = w > 0 the regrets are seeded from it after the
+        start pass (`warm_start` of type `model`, cfr_evaluator.py:887-926) and iterations w..T-1 follow, as in
+        `SteppedSolver.solve` (same meaning of `scalars` and `warm_start_scalars`).  enforce_zero_sum: shift the value outputs to zero sum, as upstream does when
         `model.enforce_zero_sum` is set (cfr_evaluator.py:957-980, 1289-1292).  cfr_avg: showdown values
         and regret weights at the beliefs under the average policy (:1029, :1133; one launch, general
         kernel).  check: read the status word afterwards (synchronises) and raise if the record check
         refused the batch."""
         assert root_beliefs.shape == (self.B, 2, HPAD) and root_beliefs.dtype == torch.float32
         assert root_beliefs.is_contiguous() and root_beliefs.device == self.device
+        ws = int(warm_start_iterations)
+        if ws > 0:
+            if start_policy is None:
+                raise ValueError("a warm start needs a start policy")
+            first = scalars[ws:ws + 1] if warm_start_scalars is None else warm_start_scalars
+            scalars = np.concatenate([first, scalars[ws:]])
+        start_rows = None
+        if start_policy is not None:
+            order = layout_tensor(self.layout, "to_level_major", start_policy.device)
+            start_rows = pad_rows(start_policy.to(torch.float32)[order]).to(self.device).contiguous()
+        self._start_rows = start_rows  # alive until the kernels have run
         iterations = int(scalars.shape[0])
         sc = torch.from_numpy(scalars.view(np.uint8).reshape(max(iterations, 0), 32).copy()).to(self.device)
         self._scalars = sc
@@ -393,7 +409,8 @@ class SubgameSolver:
                 solve_flags(cfr_plus, enforce_zero_sum, cfr_avg, linear=scalars_are_linear(scalars)),
                 self.layout.tree_depth, p(self.work_counter),
                 self.num_blocks, p(self.sample_pass), p(self.policy_sample), p(self.beliefs_last),
-                p(self.queue_order), _lib.stream_ptr(self.device))
+                p(self.queue_order), p(start_rows), float(ws) * float(warm_start_multiplier) if ws > 0 else 0.0,
+                _lib.stream_ptr(self.device))
         self.launches += 1
         if check:
             self.raise_if_refused()

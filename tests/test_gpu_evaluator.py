@@ -51,9 +51,9 @@ def test_training_data_matches_upstream(cuda_device, golden_dir):
         assert np.array_equal(got.cpu().numpy(), z[want]), want
 
 
-def test_evaluator_with_warm_start_runs_stepped(cuda_device, golden_dir):
-    """With warm-start iterations the facade solves through the stepped path (uniform start
-    policy when none is given) and still returns well-formed batches."""
+def test_evaluator_with_warm_start(cuda_device, golden_dir):
+    """With warm-start iterations of type `model` the facade still solves terminal-leaf trees through the
+    one-call solve (uniform start policy when none is given) and returns well-formed batches."""
     from poker2_b200 import evaluator, solver, tree as ptree
 
     z = np.load(os.path.join(golden_dir, "cfr_warm_cap2_t12.npz"))
@@ -64,7 +64,7 @@ def test_evaluator_with_warm_start_runs_stepped(cuda_device, golden_dir):
                                     warm_start_iterations=int(z["warm_start_iterations"]),
                                     warm_start_multiplier=float(z["warm_start_multiplier"]))
     ev.initialize_subgame(env, torch.arange(2), torch.from_numpy(z["ranges"]))
-    assert isinstance(ev.solver, solver.SteppedSolver)
+    assert not isinstance(ev.solver, solver.SteppedSolver)
     ev.evaluate_cfr(start_policy=torch.from_numpy(z["start_policy"]))
     value_batch, _, policy_batch = ev.training_data()
     torch.testing.assert_close(value_batch.value_targets.cpu(), torch.from_numpy(z["root_values"]).clamp(-1, 1),

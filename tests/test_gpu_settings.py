@@ -269,3 +269,49 @@ def test_linear_cfr_matches_upstream(cuda_device, golden_dir):
         _close(name, res.level_major(got).cpu()[n:], torch.from_numpy(z[name])[n:])
     _close("root_values", res.root_values[..., :1326].cpu(), torch.from_numpy(z["root_values"]))
     _close("exploitability", res.exploitability.cpu(), torch.from_numpy(z["exploitability"]), rtol=1e-4)
+
+
+def test_production_search_block_through_the_one_call_solve(cuda_device, golden_dir):
+    """The production search block (warm start of type `model`, discounted_plus with a delay, exponent
+    schedules, zero-sum targets) through `SubgameSolver.solve`, whose iteration passes run in the lean
+    kernel: same fixture as the stepped test above, and the same bits as the stepped solve."""
+    from poker2_b200 import solver, tree as ptree
+
+    z = np.load(os.path.join(golden_dir, "cfr_production_cap2_t40.npz"))
+    T, ws, delay = int(z["iterations"]), int(z["warm_start_iterations"]), int(z["dcfr_delay"])
+    trees = ptree.build_trees(ptree.root_states(z["pot"], z["stack"], min_raise=2), [0.5, 1.0], int(z["max_depth"]),
+                              bb=2, max_raises=int(z["cap"]))
+    boards = z["boards"].astype(np.int64)
+    layout = solver.device_layout(trees, boards)
+    rb = solver.pad_rows(torch.from_numpy(z["ranges"]).to(cuda_device)).contiguous()
+    kw = dict(cfr_type="discounted_plus", gamma=float(z["gamma"][0]), dcfr_delay=delay)
+    scal = solver.iteration_scalars(T, alpha=float(z["alpha"][0]), alpha_final=float(z["alpha"][1]),
+                                    beta=float(z["beta"][0]), beta_final=float(z["beta"][1]),
+                                    gamma_final=float(z["gamma"][1]), warm_start_iterations=ws, **kw)
+    first = solver.warm_start_mix_scalars(scal, warm_start_iterations=ws, **kw)
+    args = dict(start_policy=torch.from_numpy(z["start_policy"]), warm_start_iterations=ws,
+                warm_start_multiplier=float(z["warm_start_multiplier"]), warm_start_scalars=first, enforce_zero_sum=True)
+    results = []
+    for lean in (True, False):
+        sv = solver.SubgameSolver(layout, torch.from_numpy(boards), cuda_device, exploitability=True, sampling=True,
+                                  lean_iterations=lean)
+        sv.set_sampling_schedule(torch.from_numpy(z["t_sample"]), warm_start_iterations=ws)
+        res = sv.solve(rb, scal, check=True, **args) if lean else None
+        if not lean:
+            # the general kernel needs the larger scratch area for the hand-over between its two launches
+            with pytest.raises(RuntimeError):
+                sv.solve(rb, scal, **args)
+            continue
+        n = trees.num_roots
+        for name, got in [("regrets", res.regrets), ("weight_sums", res.weight_sums), ("policy_avg", res.policy_avg),
+                          ("policy_sample", res.policy_sample)]:
+            _close(name, res.level_major(got).cpu()[n:], torch.from_numpy(z[name])[n:])
+        _close("root_values", res.root_values[..., :1326].cpu(), torch.from_numpy(z["root_values"]))
+        _close("values_avg", res.level_major(res.values_avg).cpu(), torch.from_numpy(z["values_avg"]))
+        _close("exploitability", res.exploitability.cpu(), torch.from_numpy(z["exploitability"]), rtol=1e-4)
+        results.append(res)
+    stepped = solver.SteppedSolver(layout, torch.from_numpy(boards), cuda_device, exploitability=True, sampling=True)
+    stepped.set_sampling_schedule(torch.from_numpy(z["t_sample"]), warm_start_iterations=ws)
+    ref = stepped.solve(rb, scal, **args)
+    for name in ("regrets", "weight_sums", "policy_avg", "root_values", "values_avg", "exploitability"):
+        assert torch.equal(getattr(results[0], name), getattr(ref, name)), name
