@@ -245,19 +245,30 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
     value = units_per_step / (ms_step / 1e3)
     extras = {"iteration_kernel_ms": sum(iter_ms) / len(iter_ms)}
 
+    def guarded(name, fn):
+        """An extra member must not cost the headline line: a failure is reported in its place."""
+        try:
+            extras[name] = fn()
+        except Exception as exc:  # noqa: BLE001
+            extras[name] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+
     if rank == 0 and not distributed and not args.no_extras:
         # the same step without the regret weight sums (they feed one statistic, cfr_evaluator.py:1642)
         sv.release()
-        sv2 = solver.SubgameSolver(layout, boards, device, exploitability=True, track_weight_sums=False)
-        ms_nows = _time_ms(lambda: sv2.solve(rb, scal), 1, 1)
-        extras["without_weight_sums"] = {"ms_per_step": ms_nows, "value": BATCH * ITERATIONS / (ms_nows / 1e3),
-                                         "unit": "subgame-iterations/s"}
-        sv2.release()
-        del sv2
+
+        def without_weight_sums():
+            sv2 = solver.SubgameSolver(layout, boards, device, exploitability=True, track_weight_sums=False)
+            ms_nows = _time_ms(lambda: sv2.solve(rb, scal), 1, 1)
+            sv2.release()
+            return {"ms_per_step": ms_nows, "value": BATCH * ITERATIONS / (ms_nows / 1e3), "unit": "subgame-iterations/s"}
+
+        guarded("without_weight_sums", without_weight_sums)
         torch.cuda.empty_cache()
-        extras["production_search_block"] = production_member(solver, layout, boards, rb, device)
-        extras["micro"] = micro_member(device)
+        guarded("production_search_block", lambda: production_member(solver, layout, boards, rb, device))
+        torch.cuda.empty_cache()
+        guarded("micro", lambda: micro_member(device))
     if distributed and not args.no_extras:
+        # every rank takes part in its collectives, so a failure here is not caught rank by rank
         extras["strong"] = run_strong(args, solver, sharding, rank, world, device)
 
     e2e = None
