@@ -70,7 +70,8 @@ constexpr int kOffRsrc = kOffSig + kCfrMaxNodes * 2 * 4;               // uint8 
 constexpr int kOffIlist = kOffRsrc + kCfrMaxNodes * 2;                 // uint8 [internal nodes]
 constexpr int kOffSdc = kOffIlist + kCfrMaxNodes;                      // uint8 [internal nodes]
 constexpr int kOffMisc = kOffSdc + kCfrMaxNodes;
-constexpr int kIterSmem = kOffMisc + 64;
+constexpr int kOffCsIdx = kOffMisc + 64;                               // uint16 [52][52] hand index of the e-th hand holding a card
+constexpr int kIterSmem = kOffCsIdx + 52 * 52 * 2;
 static_assert(kOffStage % 16 == 0 && kOffTs % 16 == 0 && kTsBytes % 16 == 0 && kOffSig % 16 == 0 && kOffMisc % 16 == 0,
               "alignment");
 static_assert(kIterSmem + 1024 <= 227 * 1024 / kCtas, "the blocks' shared memory must fit one SM");
@@ -148,6 +149,7 @@ struct IterBlock {
     uint8_t* rsrc;   // [node][player] internal index of the node whose reach row holds this player's reach (kNoRow: the mask)
     uint8_t* ilist;  // [ii] node index of the ii-th internal node
     uint8_t* sdc;    // [ii] child slot of the showdown leaf below the ii-th internal node (kNoRow: none)
+    const uint16_t* csidx;  // [card][e] index of the e-th hand holding the card, hands in their natural order
     int* misc;       // [0] subgame taken from the queue, [2],[3] unit counters of the two table sets, [6] of an extra round
                      // ([4],[5] hold fsum)
     float* fsum;
@@ -510,14 +512,12 @@ __device__ __forceinline__ void table_units(const IterBlock& B, const float* __r
             const float* __restrict__ x = rows + (is_cs ? slot : (slot ? kRowLeaf : 1)) * P2B_HPAD;
             float v[13];
             if (is_cs) {
-                // e-th hand holding card c, in hand order: (e, c) for e < c, then (c, e + 1)
-                const int row_part = combo_row_offset(c) - c;
+                // e-th hand holding card c, in hand order ((e, c) for e < c, then (c, e + 1)): its index comes from
+                // a table of the block; computing it costs more issue slots than the load costs shared-memory cycles
+                const uint16_t* __restrict__ ib = B.csidx + c * 52 + q;
 #pragma unroll
-                for (int i = 0; i < 13; ++i) {
-                    const int e = q + 4 * i;
-                    const int idx = e < c ? ((e * (103 - e)) >> 1) + (c - e - 1) : row_part + e;
-                    v[i] = (i < 12 || q < 3) ? x[idx] : 0.0f;
-                }
+                for (int i = 0; i < 12; ++i) v[i] = x[ib[4 * i]];
+                v[12] = q < 3 ? x[ib[48]] : 0.0f;
             } else {
                 const uint16_t* __restrict__ idx_base = cardlist + 13 * q * 52 + c;
 #pragma unroll
@@ -854,6 +854,15 @@ __global__ void __launch_bounds__(kNT, kCtas) cfr_iter_kernel(const CfrParams p)
     B.ilist = smem + kOffIlist;
     B.sdc = smem + kOffSdc;
     B.misc = reinterpret_cast<int*>(smem + kOffMisc);
+    {
+        uint16_t* t = reinterpret_cast<uint16_t*>(smem + kOffCsIdx);
+        for (int i = threadIdx.x; i < 52 * 52; i += kNT) {
+            const int c = i / 52, e = i % 52;
+            const int ee = e < 51 ? e : 50;
+            t[i] = (uint16_t)(ee < c ? ((ee * (103 - ee)) >> 1) + (c - ee - 1) : combo_row_offset(c) - c + ee);
+        }
+        B.csidx = t;
+    }
     B.fsum = reinterpret_cast<float*>(smem + kOffMisc + 16);
     B.max_internal = p.max_internal;
     B.scr = p.scratch + (long long)(blockIdx.x / kCtas) * p.scratch_stride +
