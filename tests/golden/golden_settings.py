@@ -336,5 +336,64 @@ def gen_policy_head() -> None:
          exploitability=ex.local_exploitability.numpy())
 
 
+def gen_dataclass_defaults() -> None:
+    """The search settings a bare `SearchConfig()` gives (structured_config.py:236-265), all at once: linear CFR
+    with the CFR+ clamp, `cfr_avg`, value targets from the running average, warm start of type `model_br`
+    (3 of 9 iterations here), zero-sum model.  River subgames with a fixed policy head, turn subgames with a
+    stand-in value model."""
+    from p2.core.structured_config import CFRType, WarmStartType
+
+    out = {}
+    for tag, seed in (("river", 81), ("turn", 82)):
+        iterations, ws, mult, cap, depth = 9, 3, 1.0, 2, 8
+        gc.install_raise_cap(cap)
+        search = dict(cfr_type=CFRType.linear, cfr_plus=True, cfr_avg=True, value_targets_from_final_policy=False)
+        ev = gc.make_evaluator(2, iterations, depth=depth, search=search, enforce_zero_sum=True)
+        if tag == "river":
+            b, r, p, s = gc.seeded_inputs(seed, 2, (20, 200), (100, 1000))
+            model = gc.FixedLogitModel(len(BET_BINS) + 3)
+            env = gc.river_env(b, p, s)
+        else:
+            g = torch.Generator().manual_seed(seed)
+            import make_golden
+            b = torch.stack([torch.randperm(52, generator=g)[:4] for _ in range(2)])
+            r = make_golden.dirichlet_ranges(b, g)
+            p = torch.randint(20, 201, (2,), generator=g)
+            s = torch.randint(100, 1001, (2,), generator=g)
+
+            class Both(gc.PotEchoModel):
+                def __call__(self, features, include_policy=True, **kw):
+                    o = gc.PotEchoModel.__call__(self, features, include_policy, **kw)
+                    o.policy_logits = gc.FixedLogitModel.__call__(self, features, include_policy, **kw).policy_logits
+                    return o
+
+            model = Both(len(BET_BINS) + 3)
+            env = gc.turn_env(b, p, s)
+        model.enforce_zero_sum = True
+        ev.model = model
+        ev.warm_start_iterations, ev.warm_start_type, ev.warm_start_multiplier = ws, WarmStartType.model_br, mult
+        captured = {}
+        original = ev.warm_start
+
+        def hooked(ev=ev, captured=captured, original=original):
+            captured["start_policy"] = ev.policy_probs.clone()
+            original()
+
+        ev.warm_start = hooked
+        ex = _solve(ev, env, 2, r)
+        gc.install_raise_cap(None)
+        model_mask = ev.leaf_mask & ~ev.env.done
+        print(f"dataclass defaults, {tag}: nodes", ev.total_nodes, "exploitability", ex.local_exploitability.tolist())
+        out.update({f"{tag}_boards": b.to(torch.int16).numpy(), f"{tag}_ranges": r.numpy(), f"{tag}_pot": p.numpy(),
+                    f"{tag}_stack": s.numpy(), f"{tag}_total_nodes": np.int64(ev.total_nodes),
+                    f"{tag}_model_mask": model_mask.numpy(), f"{tag}_start_policy": captured["start_policy"].numpy(),
+                    f"{tag}_policy_avg": ev.policy_probs_avg.numpy(), f"{tag}_regrets": ev.cumulative_regrets.numpy(),
+                    f"{tag}_root_values": ev.values_avg[:2].numpy(),
+                    f"{tag}_exploitability": ex.local_exploitability.numpy()})
+    save("cfr_dataclass_defaults.npz", iterations=np.int64(9), warm_start_iterations=np.int64(3),
+         warm_start_multiplier=np.float64(1.0), cap=np.int64(2), max_depth=np.int64(8),
+         hand_weights=gc.hand_weights().numpy(), **out)
+
+
 gc.SECTIONS.update(production=gen_production, standard=gen_standard, zero_sum=gen_zero_sum, ragged256=gen_ragged256,
-                   cfr_avg=gen_cfr_avg, running_values=gen_running_values, warm_br=gen_warm_br, linear=gen_linear, policy_head=gen_policy_head)
+                   cfr_avg=gen_cfr_avg, running_values=gen_running_values, warm_br=gen_warm_br, linear=gen_linear, policy_head=gen_policy_head, dataclass_defaults=gen_dataclass_defaults)

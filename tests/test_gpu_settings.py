@@ -315,3 +315,43 @@ def test_production_search_block_through_the_one_call_solve(cuda_device, golden_
     ref = stepped.solve(rb, scal, **args)
     for name in ("regrets", "weight_sums", "policy_avg", "root_values", "values_avg", "exploitability"):
         assert torch.equal(getattr(results[0], name), getattr(ref, name)), name
+
+
+def test_dataclass_default_search_settings_match_upstream(cuda_device, golden_dir):
+    """Everything a bare SearchConfig() switches on, together: linear CFR with the CFR+ clamp, cfr_avg, value
+    targets from the running average, warm start of type model_br, zero-sum model; river and turn subgames."""
+    from leaf_models import pot_echo_leaf_fn
+    from poker2_b200 import solver, tree as ptree
+
+    z = np.load(os.path.join(golden_dir, "cfr_dataclass_defaults.npz"))
+    cap, depth, T, ws = int(z["cap"]), int(z["max_depth"]), int(z["iterations"]), int(z["warm_start_iterations"])
+    for tag, street in (("river", 3), ("turn", 2)):
+        roots = ptree.root_states(z[f"{tag}_pot"], z[f"{tag}_stack"], min_raise=2, street=street)
+        trees = ptree.build_trees(roots, [0.5, 1.0], depth, bb=2, max_raises=cap)
+        assert trees.total_nodes == int(z[f"{tag}_total_nodes"])
+        boards = z[f"{tag}_boards"].astype(np.int64)
+        if boards.shape[1] < 5:
+            boards = np.concatenate([boards, np.full((boards.shape[0], 5 - boards.shape[1]), -1)], axis=1)
+        layout = solver.device_layout(trees, boards)
+        sv = solver.SteppedSolver(layout, torch.from_numpy(boards), cuda_device, exploitability=True)
+        leaf_fn = None
+        if street == 2:
+            leaf_fn = pot_echo_leaf_fn(trees, layout.model_nodes, torch.from_numpy(z["hand_weights"]))
+        rb = solver.pad_rows(torch.from_numpy(z[f"{tag}_ranges"]).to(cuda_device)).contiguous()
+        scal = solver.iteration_scalars(T, cfr_type="linear", warm_start_iterations=ws)
+        first = solver.warm_start_mix_scalars(scal, cfr_type="linear", gamma=2.0, dcfr_delay=0, warm_start_iterations=ws)
+        res = sv.solve(rb, scal, leaf_fn, cfr_plus=True, cfr_avg=True, running_values=True, enforce_zero_sum=True,
+                       start_policy=torch.from_numpy(z[f"{tag}_start_policy"]), warm_start_iterations=ws,
+                       warm_start_multiplier=float(z["warm_start_multiplier"]), warm_start_type="model_br",
+                       warm_start_scalars=first)
+        assert sv.status() == 0
+        n = trees.num_roots
+        # the best responses of the seeding add up in another fp64 order than the CPU's, and the clamped regret
+        # matching that follows amplifies the last-bit differences: 1e-4 relative / 5e-6 absolute here (one policy
+        # entry in 1.5e5 is 4e-5 off; the single settings are held to 1e-5 / 1e-6 by the tests above)
+        tol = dict(rtol=1e-4, atol=5e-6)
+        _close(f"{tag} regrets", res.level_major(res.regrets).cpu()[n:], torch.from_numpy(z[f"{tag}_regrets"])[n:], **tol)
+        _close(f"{tag} policy_avg", res.level_major(res.policy_avg).cpu()[n:], torch.from_numpy(z[f"{tag}_policy_avg"])[n:],
+               **tol)
+        _close(f"{tag} root_values", res.root_values[..., :1326].cpu(), torch.from_numpy(z[f"{tag}_root_values"]), **tol)
+        _close(f"{tag} exploitability", res.exploitability.cpu(), torch.from_numpy(z[f"{tag}_exploitability"]), rtol=1e-4)

@@ -209,3 +209,36 @@ def test_oracle_linear_cfr_bit_exact(golden_dir):
     assert torch.equal(o.values_avg[: o.N], torch.from_numpy(z["root_values"]))
     ex, _ = o.exploitability()
     assert torch.equal(ex, torch.from_numpy(z["exploitability"]))
+
+
+def _defaults_case(z, tag, street):
+    cap, depth = int(z["cap"]), int(z["max_depth"])
+    t = _build(z[f"{tag}_pot"], z[f"{tag}_stack"], cap, depth, street=street)
+    assert t.total_nodes == int(z[f"{tag}_total_nodes"])
+    boards = z[f"{tag}_boards"].astype(np.int64)
+    if boards.shape[1] < 5:
+        boards = np.concatenate([boards, np.full((boards.shape[0], 5 - boards.shape[1]), -1)], axis=1)
+    return t, boards
+
+
+def test_oracle_dataclass_default_search_settings_bit_exact(golden_dir):
+    """Everything a bare SearchConfig() switches on, together: linear CFR + CFR+ clamp, cfr_avg, running value
+    averages, warm start of type model_br, zero-sum model."""
+    z = np.load(os.path.join(golden_dir, "cfr_dataclass_defaults.npz"))
+    T, ws = int(z["iterations"]), int(z["warm_start_iterations"])
+    for tag, street in (("river", 3), ("turn", 2)):
+        t, boards = _defaults_case(z, tag, street)
+        leaf = None
+        if street == 2:
+            fn = pot_echo_leaf_fn(t, np.nonzero(z["turn_model_mask"])[0], torch.from_numpy(z["hand_weights"]))
+            leaf = lambda b, idx, fn=fn: fn(b)  # noqa: E731
+        o = ocfr.SubgameOracle(t.oracle_dict(boards), torch.from_numpy(z[f"{tag}_ranges"]), iterations=T,
+                               cfr_type="linear", cfr_plus=True, cfr_avg=True, final_policy_values=False,
+                               enforce_zero_sum=True, start_policy=torch.from_numpy(z[f"{tag}_start_policy"]),
+                               warm_start_iterations=ws, warm_start_multiplier=float(z["warm_start_multiplier"]),
+                               warm_start_type="model_br", leaf_fn=leaf).solve()
+        assert torch.equal(o.regrets, torch.from_numpy(z[f"{tag}_regrets"]))
+        assert torch.equal(o.policy_avg, torch.from_numpy(z[f"{tag}_policy_avg"]))
+        assert torch.equal(o.values_avg[: o.N], torch.from_numpy(z[f"{tag}_root_values"]))
+        ex, _ = o.exploitability()
+        assert torch.equal(ex, torch.from_numpy(z[f"{tag}_exploitability"]))
