@@ -163,3 +163,30 @@ def test_cfr_oracle_warm_start_bit_exact(golden_dir):
     assert torch.equal(o.values_avg[: o.N], torch.from_numpy(z["root_values"]))
     ex, _ = o.exploitability()
     assert torch.equal(ex, torch.from_numpy(z["exploitability"]))
+
+
+@pytest.mark.parametrize("cfr_type", ["standard", "linear", "discounted", "discounted_plus"])
+def test_iteration_scalars_follow_the_oracle_schedule(cfr_type):
+    """The per-pass records the kernels read against the oracle's own schedule functions: mixing
+    weights (`_get_mixing_weights`, cfr_evaluator.py:285-303), the pass that only copies the policy
+    (:1197-1205) and, for linear CFR, the player whose actions take no regret (:1348-1349)."""
+    from poker2_b200 import solver
+
+    iterations, delay = 9, 3
+    sc = solver.iteration_scalars(iterations, cfr_type=cfr_type, alpha=1.5, beta=0.5, gamma=2.0, dcfr_delay=delay)
+    o = ocfr.SubgameOracle.__new__(ocfr.SubgameOracle)
+    o.cfr_type, o.gamma, o.dcfr_delay = cfr_type, 2.0, delay
+    for t in range(iterations):
+        old, new = o.mixing_weights(t)
+        assert sc[t]["mix_old"] == np.float32(old) and sc[t]["mix_new"] == np.float32(new)
+        assert sc[t]["mix_total"] == np.float32(old + new)
+        copies = t == 0 or (cfr_type in ("discounted", "discounted_plus") and t <= delay)
+        assert (int(sc[t]["do_mix"]) & 1) == (0 if copies else 1)
+        skipped = (int(sc[t]["do_mix"]) >> 1) & 3
+        assert skipped == ((t % 2) + 1 if cfr_type == "linear" else 0)
+        if cfr_type in ("discounted", "discounted_plus"):
+            assert sc[t]["num_pos"] == np.float32(t ** 1.5) and sc[t]["den_pos"] == np.float32(t ** 1.5 + 1)
+            assert sc[t]["num_neg"] == np.float32(t ** 0.5) and sc[t]["den_neg"] == np.float32(t ** 0.5 + 1)
+        else:
+            assert sc[t]["num_pos"] == sc[t]["den_pos"] == sc[t]["num_neg"] == sc[t]["den_neg"] == 1.0
+    assert solver.scalars_are_linear(sc) == (cfr_type == "linear")
