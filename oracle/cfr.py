@@ -120,6 +120,7 @@ class SubgameOracle:
         self.values[fold, 0] = self.fold_value[fold][:, None]
         self.values[fold, 1] = -self.fold_value[fold][:, None]
         self.values_avg = self.values.clone()
+        self.stats = {}  # `cfr_delta.*`, filled while solving
 
     # ---- tree primitives (sparse_cfr_evaluator.py:428-538) ----
     def _fan_out(self, x, level=None):
@@ -337,11 +338,31 @@ class SubgameOracle:
         self.regrets += inst
         if self.cfr_plus:
             self.regrets.clamp_(min=0)
+        before = self.policy.clone()
         self.update_policy(t)
+        self.record_policy_delta(t, before)
         self.set_leaf_values(t)
         self.expected_values()
         if not self.final_policy_values:
             self.update_average_values(t)
+
+    def record_policy_delta(self, t, before):
+        """`_record_stats` (cfr_evaluator.py:1573-1605): at the iterations linspace(warm start, T - 1, 5), the
+        absolute change of the policy summed over actions and reachable hands, per reachable hand, averaged
+        over the nodes some hand reaches (all nodes above the deepest level).  Where two of the five points
+        fall on one iteration the first one names the key."""
+        points = torch.linspace(self.warm_start_iterations, self.iterations - 1, 5).round().int().tolist()
+        if t not in points:
+            return
+        percentile = (0, 25, 50, 75, 100)[points.index(t)]
+        diff = self._pull_back(self.policy) - self._pull_back(before)
+        reachable = (self.reach > 0).any(dim=1)[: self.top]
+        diff.masked_fill_(~reachable[:, None, :], 0.0)
+        count = reachable.sum(dim=-1)
+        nodes = count > 0
+        total = diff.abs().sum(dim=1).sum(dim=1)
+        delta = torch.where(nodes, total / count, 0.0)
+        self.stats[f"cfr_delta.{percentile}"] = (delta.sum() / nodes.sum()).item()
 
     def _zero_sum(self, values, beliefs):
         sums = (values * beliefs).sum(dim=2, keepdim=True).mean(dim=1, keepdim=True)

@@ -71,7 +71,7 @@ class SubgameEvaluator:
                  warm_start_multiplier: float = 1.0, alpha_final: float | None = None,
                  beta_final: float | None = None, gamma_final: float | None = None,
                  enforce_zero_sum: bool = False, cfr_avg: bool = False, running_values: bool = False,
-                 warm_start_type: str = "model"):
+                 warm_start_type: str = "model", policy_delta_stats: bool = False):
         self.device = torch.device(device)
         self.cfr_iterations = int(iterations)
         self.bet_bins, self.max_depth, self.bb, self.max_raises = list(bet_bins), max_depth, bb, max_raises
@@ -94,6 +94,9 @@ class SubgameEvaluator:
         self.warm_start_iterations = int(warm_start_iterations)
         self.warm_start_multiplier = float(warm_start_multiplier)
         self.warm_start_type = warm_start_type  # "model" (:913-926) or "model_br" (:927-955)
+        # `cfr_delta.*` in `stats` (`_record_stats`, :1573-1605): needs the regrets on both sides of five
+        # iterations, so such a solve runs pass by pass
+        self.policy_delta_stats = bool(policy_delta_stats)
         self.stats: dict = {}
         self.root_nodes = 0
         self._result = None
@@ -129,7 +132,7 @@ class SubgameEvaluator:
         # pass by pass only where something happens between the passes: leaves valued by the network, running
         # value averages, the best-response pass of a `model_br` warm start; a warm start of type `model` and a
         # start policy fit the one-call solve, whose iteration passes run in the lean kernel
-        self.stepped = (bool(self.layout.num_model_leaves) or self.running_values
+        self.stepped = (bool(self.layout.num_model_leaves) or self.running_values or self.policy_delta_stats
                         or (self.warm_start_iterations > 0 and self.warm_start_type == "model_br"))
         if self.layout.num_model_leaves:
             if self.model is None:
@@ -144,6 +147,11 @@ class SubgameEvaluator:
             cls = psolver.SteppedSolver if self.stepped else psolver.SubgameSolver
             self.solver = cls(self.layout, boards_t, self.device, **kw)
             self.leaf_fn = None
+        self._policy_delta = None
+        if self.policy_delta_stats:
+            from . import stats as pstats
+
+            self._policy_delta = pstats.PolicyDelta(self.trees, self.boards, self.layout, self.device)
         if initial_beliefs is None:
             initial_beliefs = torch.full((n, 2, NUM_HANDS), 1.0 / NUM_HANDS, dtype=torch.float32)
         self.root_beliefs = psolver.pad_rows(initial_beliefs.to(device=self.device, dtype=torch.float32)).contiguous()
@@ -180,7 +188,7 @@ class SubgameEvaluator:
                                     enforce_zero_sum=self.enforce_zero_sum, start_policy=start_policy,
                                     warm_start_iterations=ws, warm_start_multiplier=self.warm_start_multiplier,
                                     warm_start_scalars=first, cfr_avg=self.cfr_avg, running_values=self.running_values,
-                                    warm_start_type=self.warm_start_type)
+                                    warm_start_type=self.warm_start_type, policy_delta=self._policy_delta)
         else:
             res = self.solver.solve(self.root_beliefs, scal, cfr_plus=self.cfr_plus,
                                     enforce_zero_sum=self.enforce_zero_sum, cfr_avg=self.cfr_avg,
@@ -190,6 +198,10 @@ class SubgameEvaluator:
         from . import stats as pstats
 
         self.stats.update(pstats.evaluator_stats(res, self.trees, self.boards))
+        if self._policy_delta is not None and self.solver.policy_deltas:
+            keys = sorted(self.solver.policy_deltas)
+            vals = torch.stack([self.solver.policy_deltas[q] for q in keys]).cpu().tolist()  # one read
+            self.stats.update({f"cfr_delta.{q}": v for q, v in zip(keys, vals)})
         # the walk draws from the generator: run it where the generator lives
         pol = res.level_major(res.policy_sample).to(gen_device)
         bel = res.level_major(res.beliefs_last).to(gen_device)

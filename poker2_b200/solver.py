@@ -487,7 +487,8 @@ class SteppedSolver(SubgameSolver):
     def solve(self, root_beliefs: torch.Tensor, scalars: np.ndarray, leaf_fn=None, *, cfr_plus: bool = False,
               enforce_zero_sum: bool = False, start_policy: torch.Tensor | None = None, warm_start_iterations: int = 0,
               warm_start_multiplier: float = 1.0, warm_start_scalars: np.ndarray | None = None,
-              cfr_avg: bool = False, running_values: bool = False, warm_start_type: str = "model") -> SolveResult:
+              cfr_avg: bool = False, running_values: bool = False, warm_start_type: str = "model",
+              policy_delta=None) -> SolveResult:
         """scalars: `iteration_scalars(T)` for all T iterations.  start_policy [M,1326] in the
         upstream node order (the policy head's softmax; None = uniform).  With
         warm_start_iterations = w > 0 (needs a start policy) the regrets are seeded from the start
@@ -503,7 +504,11 @@ class SteppedSolver(SubgameSolver):
         solver must have been built with keep_node_values=True (or exploitability=True).
         warm_start_type: "model" (above) or "model_br" (:927-955; needs keep_node_values too): the regrets
         are seeded with w x multiplier x the regrets of not playing a best response against the start
-        policy."""
+        policy.
+        policy_delta: a `stats.PolicyDelta` of this batch -- the change of the current policy at the five
+        iterations of `stats.delta_checkpoints` is left in `self.policy_deltas` (percentile -> 0-dim device
+        tensor), from the regrets on either side of those iterations' updates (`_record_stats`,
+        cfr_evaluator.py:1573-1605)."""
         assert root_beliefs.shape == (self.B, 2, HPAD) and root_beliefs.dtype == torch.float32
         assert root_beliefs.is_contiguous() and root_beliefs.device == self.device
         ws = int(warm_start_iterations)
@@ -534,6 +539,16 @@ class SteppedSolver(SubgameSolver):
             raise ValueError("the trees have model-valued leaves: a leaf_fn is required")
         self._last_model_values = None
         self._running = None
+        self.policy_deltas = {}
+        delta_at = {}
+        if policy_delta is not None:
+            from . import stats as pstats
+
+            # the regret update of upstream iteration t happens in the bottom-up sweep of the pass before
+            # the one that plays the updated policy: the start pass for iteration 0, pass t - w after a
+            # warm start (whose pass 0 is the warm start's own policy update)
+            for t, q in pstats.delta_checkpoints(ws, all_scalars.shape[0]).items():
+                delta_at[t - ws + (0 if ws > 0 else -1)] = q
         for pas in range(-1, iterations + 1):
             if pas == 0 and warm_br:
                 # best responses against the start policy, from the node values the start pass has stored
@@ -555,10 +570,15 @@ class SteppedSolver(SubgameSolver):
                 flags_pass = flags | 8  # the start pass keeps its node values for the best responses
             else:
                 flags_pass = flags
+            before = None
+            if pas in delta_at:  # the policy this pass plays; its bottom-up sweep updates the regrets
+                before = policy_delta.start_policy(start_policy) if pas < 0 else policy_delta.policy_of(self.regrets)
             if n_leaves == 0:
                 self._step(root_beliefs, sc, iterations, flags_pass, pas, pas, 3)
                 if running_values:
                     self._mix_running_values(pas, ws, all_scalars, enforce_zero_sum)
+                if before is not None:
+                    self.policy_deltas[delta_at[pas]] = policy_delta(before, policy_delta.policy_of(self.regrets))
                 continue
             self._step(root_beliefs, sc, iterations, flags_pass, pas, pas, 1)
             vals = leaf_fn(self.leaf_beliefs[:n_leaves])
@@ -577,6 +597,8 @@ class SteppedSolver(SubgameSolver):
             self._step(root_beliefs, sc, iterations, flags_pass, pas, pas, 2)
             if running_values:
                 self._mix_running_values(pas, ws, all_scalars, enforce_zero_sum)
+            if before is not None:
+                self.policy_deltas[delta_at[pas]] = policy_delta(before, policy_delta.policy_of(self.regrets))
         return self._result()
 
     # ---- running average of the node values (`value_targets_from_final_policy = False`) ----

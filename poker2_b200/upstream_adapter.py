@@ -170,7 +170,11 @@ class B200CFREvaluator:
 
     num_players = 2
 
-    def __init__(self, model, device, cfg, generator: torch.Generator | None = None, *, max_raises=None):
+    def __init__(self, model, device, cfg, generator: torch.Generator | None = None, *, max_raises=None,
+                 policy_delta_stats: bool = False):
+        """policy_delta_stats: also record `cfr_delta.*` (`_record_stats`, cfr_evaluator.py:1573-1605); such
+        a solve runs pass by pass instead of through the one-call solve (upstream pays for these keys the
+        same way: its graphed iteration leaves them out, fused_sparse_cfr_evaluator.py:522-527)."""
         s, e = cfg.search, cfg.env
         cfr_type = _enum_name(s.cfr_type)
         iterations = int(s.iterations)
@@ -194,7 +198,7 @@ class B200CFREvaluator:
             warm_start_multiplier=float(getattr(s, "warm_start_multiplier", 1.0)),
             enforce_zero_sum=bool(getattr(model, "enforce_zero_sum", False)), cfr_avg=bool(getattr(s, "cfr_avg", False)),
             running_values=not bool(getattr(s, "value_targets_from_final_policy", True)),
-            warm_start_type=ws_type if ws > 0 else "model")
+            warm_start_type=ws_type if ws > 0 else "model", policy_delta_stats=policy_delta_stats)
         self.root_nodes = int(cfg.num_envs)
         self.warm_start_iterations = ws
         self.generator = generator

@@ -395,5 +395,47 @@ def gen_dataclass_defaults() -> None:
          hand_weights=gc.hand_weights().numpy(), **out)
 
 
+def gen_policy_delta() -> None:
+    """The `cfr_delta.*` statistics (`_record_stats`, cfr_evaluator.py:1573-1605): mean absolute change of the
+    policy over the reachable hands at the iterations linspace(warm start, T - 1, 5).  Three river solves:
+    plain DCFR; three iterations only (the five points collide, the first key of a collision is the one
+    written); a warm start of type `model` from a policy head."""
+    from p2.core.structured_config import WarmStartType
+
+    out = {}
+    cap, depth = 2, 8
+    for tag, seed, iterations, ws in (("plain", 81, 9, 0), ("short", 82, 3, 0), ("warm", 83, 10, 3)):
+        b, r, p, s = gc.seeded_inputs(seed, 2, (20, 200), (100, 1000))
+        gc.install_raise_cap(cap)
+        ev = gc.make_evaluator(2, iterations, depth=depth)
+        captured = {}
+        if ws:
+            ev.model = gc.BeliefLogitModel(len(BET_BINS) + 3)
+            ev.warm_start_iterations, ev.warm_start_type, ev.warm_start_multiplier = ws, WarmStartType.model, 4.0
+            original = ev.warm_start
+
+            def hooked(ev=ev, captured=captured, original=original):
+                captured["start_policy"] = ev.policy_probs.clone()
+                original()
+
+            ev.warm_start = hooked
+        ex = _solve(ev, gc.river_env(b, p, s), 2, r)
+        gc.install_raise_cap(None)
+        deltas = {k: v for k, v in ev.stats.items() if k.startswith("cfr_delta.")}
+        print(f"policy delta, {tag}: nodes", ev.total_nodes, deltas)
+        out.update({f"{tag}_boards": b.to(torch.int16).numpy(), f"{tag}_ranges": r.numpy(), f"{tag}_pot": p.numpy(),
+                    f"{tag}_stack": s.numpy(), f"{tag}_iterations": np.int64(iterations),
+                    f"{tag}_warm_start_iterations": np.int64(ws), f"{tag}_total_nodes": np.int64(ev.total_nodes),
+                    f"{tag}_exploitability": ex.local_exploitability.numpy(),
+                    f"{tag}_delta_keys": np.array(sorted(int(k.split(".")[1]) for k in deltas), dtype=np.int64),
+                    f"{tag}_delta_values": np.array([deltas[f"cfr_delta.{q}"] for q in
+                                                     sorted(int(k.split(".")[1]) for k in deltas)], dtype=np.float64)})
+        if ws:
+            out[f"{tag}_start_policy"] = captured["start_policy"].numpy()
+    save("cfr_policy_delta.npz", cap=np.int64(cap), max_depth=np.int64(depth), warm_start_multiplier=np.float64(4.0),
+         **out)
+
+
 gc.SECTIONS.update(production=gen_production, standard=gen_standard, zero_sum=gen_zero_sum, ragged256=gen_ragged256,
-                   cfr_avg=gen_cfr_avg, running_values=gen_running_values, warm_br=gen_warm_br, linear=gen_linear, policy_head=gen_policy_head, dataclass_defaults=gen_dataclass_defaults)
+                   cfr_avg=gen_cfr_avg, running_values=gen_running_values, warm_br=gen_warm_br, linear=gen_linear, policy_head=gen_policy_head, dataclass_defaults=gen_dataclass_defaults,
+                   policy_delta=gen_policy_delta)

@@ -48,6 +48,29 @@ def _check_stats(stats, z, prefix):
         assert value == pytest.approx(float(z[f"{prefix}local_exploitability_street.{name}"]), rel=1e-4, abs=1e-6)
 
 
+def test_policy_delta_statistics_of_both_rounds(cuda_device, golden_dir):
+    """`cfr_delta.*` recorded on request (the solve then runs pass by pass): turn subgames with leaves valued by
+    the model in round one, river subgames in round two, against the statistics of the upstream trace."""
+    from poker2_b200 import upstream_adapter as ua
+
+    z = np.load(os.path.join(golden_dir, "rounds_turn_river.npz"))
+    n = z["boards"].shape[0]
+    env = SimpleNamespace(**{name: z["env0_" + name] for name in ua.ENV_FIELDS}, raises=z["env0_raises"])
+    model = PotEcho(torch.from_numpy(z["hand_weights"]))
+    beliefs, idx = torch.from_numpy(z["ranges"]), torch.arange(n)
+    for prefix, seed in (("stats1_", "seed_round1"), ("stats2_", "seed_round2")):
+        ev = ua.B200CFREvaluator(model, cuda_device, _cfg(z, idx.shape[0]), torch.Generator().manual_seed(int(z[seed])),
+                                 max_raises=int(z["cap"]), policy_delta_stats=True)
+        ev.initialize_subgame(env, idx, beliefs)
+        pbs = ev.evaluate_cfr()
+        _check_stats(ev.stats, z, prefix)
+        for q in (0, 25, 50, 75, 100):
+            got, want = ev.stats[f"cfr_delta.{q}"], float(z[f"{prefix}cfr_delta.{q}"])
+            print(f"{prefix}cfr_delta.{q}: {got:.8f} (upstream {want:.8f})")
+            assert got == pytest.approx(want, rel=1e-4, abs=1e-6)
+        env, beliefs, idx = pbs.env, pbs.beliefs, torch.arange(pbs.env.N, device=cuda_device)
+
+
 def test_two_rounds_match_the_upstream_loop(cuda_device, golden_dir):
     from poker2_b200 import upstream_adapter as ua
 

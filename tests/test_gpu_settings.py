@@ -355,3 +355,36 @@ def test_dataclass_default_search_settings_match_upstream(cuda_device, golden_di
                **tol)
         _close(f"{tag} root_values", res.root_values[..., :1326].cpu(), torch.from_numpy(z[f"{tag}_root_values"]), **tol)
         _close(f"{tag} exploitability", res.exploitability.cpu(), torch.from_numpy(z[f"{tag}_exploitability"]), rtol=1e-4)
+
+
+def test_policy_delta_statistics_match_upstream(cuda_device, golden_dir):
+    """`cfr_delta.*` (`_record_stats`, cfr_evaluator.py:1573-1605) from the regrets on either side of the five
+    recorded iterations: a plain solve, a three-iteration solve (two of the five points fall together, so
+    upstream writes three keys) and a solve warm-started from a policy head.  The sums behind the statistic
+    run in another order than upstream's tensor reductions, hence 1e-5 relative."""
+    from poker2_b200 import solver, stats as pstats, tree as ptree
+
+    z = np.load(os.path.join(golden_dir, "cfr_policy_delta.npz"))
+    for tag in ("plain", "short", "warm"):
+        T, ws = int(z[f"{tag}_iterations"]), int(z[f"{tag}_warm_start_iterations"])
+        trees = ptree.build_trees(ptree.root_states(z[f"{tag}_pot"], z[f"{tag}_stack"], min_raise=2), [0.5, 1.0],
+                                  int(z["max_depth"]), bb=2, max_raises=int(z["cap"]))
+        assert trees.total_nodes == int(z[f"{tag}_total_nodes"])
+        boards = z[f"{tag}_boards"].astype(np.int64)
+        layout = solver.device_layout(trees, boards)
+        sv = solver.SteppedSolver(layout, torch.from_numpy(boards), cuda_device, exploitability=True)
+        rb = solver.pad_rows(torch.from_numpy(z[f"{tag}_ranges"]).to(cuda_device)).contiguous()
+        scal = solver.iteration_scalars(T, warm_start_iterations=ws)
+        kw = {}
+        if ws:
+            kw = dict(start_policy=torch.from_numpy(z[f"{tag}_start_policy"]), warm_start_iterations=ws,
+                      warm_start_multiplier=float(z["warm_start_multiplier"]),
+                      warm_start_scalars=solver.warm_start_mix_scalars(scal, cfr_type="discounted", gamma=2.0, dcfr_delay=0,
+                                                                       warm_start_iterations=ws))
+        res = sv.solve(rb, scal, policy_delta=pstats.PolicyDelta(trees, boards, layout, cuda_device), **kw)
+        _close(f"{tag} exploitability", res.exploitability.cpu(), torch.from_numpy(z[f"{tag}_exploitability"]), rtol=1e-4)
+        assert sorted(sv.policy_deltas) == [int(q) for q in z[f"{tag}_delta_keys"]]
+        for q, want in zip(z[f"{tag}_delta_keys"], z[f"{tag}_delta_values"]):
+            got = float(sv.policy_deltas[int(q)])
+            print(f"{tag} cfr_delta.{int(q)}: {got:.8f} (upstream {want:.8f})")
+            assert got == pytest.approx(float(want), rel=1e-5, abs=1e-7)

@@ -4,6 +4,7 @@ standard CFR, zero-sum value targets, and iteration_scalars against the oracle's
 import os
 
 import numpy as np
+import pytest
 import torch
 
 from leaf_models import pot_echo_leaf_fn
@@ -242,3 +243,55 @@ def test_oracle_dataclass_default_search_settings_bit_exact(golden_dir):
         assert torch.equal(o.values_avg[: o.N], torch.from_numpy(z[f"{tag}_root_values"]))
         ex, _ = o.exploitability()
         assert torch.equal(ex, torch.from_numpy(z[f"{tag}_exploitability"]))
+
+
+def test_oracle_policy_delta_statistics_bit_exact(golden_dir):
+    """`cfr_delta.*` of `_record_stats` (cfr_evaluator.py:1573-1605): the same keys (two of the five points
+    fall on one iteration in the three-iteration solve) and the same fp32 values as upstream records."""
+    z = np.load(os.path.join(golden_dir, "cfr_policy_delta.npz"))
+    cap, depth = int(z["cap"]), int(z["max_depth"])
+    for tag in ("plain", "short", "warm"):
+        t = _build(z[f"{tag}_pot"], z[f"{tag}_stack"], cap, depth)
+        assert t.total_nodes == int(z[f"{tag}_total_nodes"])
+        ws = int(z[f"{tag}_warm_start_iterations"])
+        kw = {}
+        if ws:
+            kw = dict(start_policy=torch.from_numpy(z[f"{tag}_start_policy"]), warm_start_iterations=ws,
+                      warm_start_multiplier=float(z["warm_start_multiplier"]))
+        o = ocfr.SubgameOracle(t.oracle_dict(z[f"{tag}_boards"].astype(np.int64)), torch.from_numpy(z[f"{tag}_ranges"]),
+                               iterations=int(z[f"{tag}_iterations"]), **kw).solve()
+        ex, _ = o.exploitability()
+        assert torch.equal(ex, torch.from_numpy(z[f"{tag}_exploitability"]))
+        keys = [f"cfr_delta.{int(q)}" for q in z[f"{tag}_delta_keys"]]
+        assert sorted(o.stats) == sorted(keys)
+        for k, want in zip(keys, z[f"{tag}_delta_values"]):
+            assert o.stats[k] == want, (tag, k, o.stats[k], want)
+
+
+def test_policy_delta_host_computation_against_the_oracle(golden_dir):
+    """`stats.PolicyDelta` (what the evaluator records `cfr_delta.*` with) on the CPU: fed the oracle's
+    regrets on either side of the recorded iterations, in the solver's row order."""
+    from poker2_b200 import solver, stats as pstats
+
+    z = np.load(os.path.join(golden_dir, "cfr_policy_delta.npz"))
+    tag = "plain"
+    t = _build(z[f"{tag}_pot"], z[f"{tag}_stack"], int(z["cap"]), int(z["max_depth"]))
+    boards = z[f"{tag}_boards"].astype(np.int64)
+    T = int(z[f"{tag}_iterations"])
+    layout = solver.device_layout(t, boards)
+    pd = pstats.PolicyDelta(t, boards, layout, "cpu")
+    order = torch.from_numpy(np.ascontiguousarray(layout.to_level_major)).long()
+    rows = lambda x: solver.pad_rows(x[order])  # noqa: E731  upstream node order -> solver rows
+    points = pstats.delta_checkpoints(0, T)
+    assert points == {0: 0, 2: 25, 4: 50, 6: 75, 8: 100}
+    assert pstats.delta_checkpoints(0, 3) == {0: 0, 1: 50, 2: 75}
+    assert pstats.delta_checkpoints(3, 10) == {3: 0, 4: 25, 6: 50, 8: 75, 9: 100}  # 4.5 and 7.5 round to even
+    o = ocfr.SubgameOracle(t.oracle_dict(boards), torch.from_numpy(z[f"{tag}_ranges"]), iterations=T)
+    o.initialize()
+    for it in range(T):
+        before = pd.start_policy(None) if it == 0 else pd.policy_of(rows(o.regrets))
+        o.iteration(it)
+        if it in points:
+            got = float(pd(before, pd.policy_of(rows(o.regrets))))
+            assert got == pytest.approx(o.stats[f"cfr_delta.{points[it]}"], rel=1e-6), it
+    assert len(o.stats) == 5
