@@ -677,7 +677,7 @@ def run_street(args, rank: int, world: int, local_rank: int):
         res, trees, sv = solver.solve_subgames_with_model(
             boards, ranges, pot, stack, model, street=street, iterations=iterations, bet_bins=BET_BINS,
             max_depth=MAX_DEPTH, max_raises=MAX_RAISES, device=device, exploitability=True, chunk=args.leaf_chunk,
-            device_tree=True)
+            device_tree=True, graph=args.graph)
         if distributed:
             sharding.gather_rows(res.root_values)
             sharding.reduce_exploitability(res.exploitability)
@@ -718,7 +718,8 @@ def run_street(args, rank: int, world: int, local_rank: int):
                                    f"{cards_next} next cards; tree build, host->device copies and the final "
                                    "exploitability pass inside the timed region",
                        "batch_per_gpu": batch, "iterations": iterations, "model_leaves_per_gpu": info["leaves"],
-                       "network_samples_per_pass": info["leaves"] * cards_next, "nodes_per_gpu": info["rows"]},
+                       "network_samples_per_pass": info["leaves"] * cards_next, "nodes_per_gpu": info["rows"],
+                       "passes": "iteration passes replayed from one CUDA graph" if args.graph else "plain launches"},
             "clocks": clocks, "gpu_launches": info["launches"] * args.steps,
         }))
     if distributed:
@@ -744,6 +745,8 @@ def main():
     ap.add_argument("--micro-log2-hands", type=int, default=26)
     ap.add_argument("--micro-board-factor", type=int, default=4, help="boards = 4096 x this")
     ap.add_argument("--leaf-chunk", type=int, default=2048, help="leaves per network batch (x ~48 samples)")
+    ap.add_argument("--graph", action="store_true",
+                    help="turn / flop: replay the iteration passes (two sweeps and the leaf network) from one CUDA graph")
     args = ap.parse_args()
     BATCH, ITERATIONS = args.batch, args.iterations
     rank = int(os.environ.get("RANK", "0"))

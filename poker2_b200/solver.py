@@ -365,7 +365,7 @@ class SubgameSolver:
     def release(self) -> None:
         """Drops the device buffers (they return to the caching allocator)."""
         for name in ("regrets", "policy_avg", "weight_sums", "policy", "root_values", "values_avg", "beliefs_avg",
-                     "exploitability", "br_values", "scratch", "tables", "policy_sample", "beliefs_last"):
+                     "exploitability", "br_values", "scratch", "tables", "policy_sample", "beliefs_last", "_graphed"):
             setattr(self, name, None)
 
     def solve(self, root_beliefs: torch.Tensor, scalars: np.ndarray, *, cfr_plus: bool = False,
@@ -445,6 +445,7 @@ class SteppedSolver(SubgameSolver):
 
     start_policy_rows = None  # [rows,1344] policy of the start pass (None: uniform)
     _last_model_values = None
+    _graphed = None  # (key, GraphedCFRIteration) of the last solve with graph=True
 
     def _de_average(self, vals, t, scalars, enforce_zero_sum, n_leaves):
         """The CFR-AVG branch of `_set_model_values_impl` (cfr_evaluator.py:997-1018): from t = 2 on the
@@ -469,8 +470,10 @@ class SteppedSolver(SubgameSolver):
             unmixed = out
         return unmixed
 
-    def _step(self, root_beliefs, sc, iterations, flags, pass_begin, pass_end, phases) -> None:
+    def _step(self, root_beliefs, sc, iterations, flags, pass_begin, pass_end, phases, sample_pass=None) -> None:
         p = _lib.ptr
+        if sample_pass is None:
+            sample_pass = self.sample_pass
         with torch.cuda.device(self.device):
             _lib.call(
                 "p2b_cfr_step", p(self.subgames), p(self.nodes), self.B, self.layout.rows, self.layout.max_children,
@@ -480,7 +483,7 @@ class SteppedSolver(SubgameSolver):
                 self.scratch.numel(), p(sc), iterations, int(flags), self.layout.tree_depth, p(self.work_counter),
                 self.num_blocks, pass_begin, pass_end, phases, p(self.carry_sums), p(self.carry_roots),
                 p(self.leaf_begin), int(self.leaf_beliefs.shape[0]), p(self.leaf_beliefs), p(self.leaf_values),
-                p(self.sample_pass),
+                p(sample_pass),
                 p(self.policy_sample), p(self.beliefs_last), p(self.start_policy_rows), _lib.stream_ptr(self.device))
         self.launches += 1
 
@@ -488,7 +491,7 @@ class SteppedSolver(SubgameSolver):
               enforce_zero_sum: bool = False, start_policy: torch.Tensor | None = None, warm_start_iterations: int = 0,
               warm_start_multiplier: float = 1.0, warm_start_scalars: np.ndarray | None = None,
               cfr_avg: bool = False, running_values: bool = False, warm_start_type: str = "model",
-              policy_delta=None) -> SolveResult:
+              policy_delta=None, graph: bool = False) -> SolveResult:
         """scalars: `iteration_scalars(T)` for all T iterations.  start_policy [M,1326] in the
         upstream node order (the policy head's softmax; None = uniform).  With
         warm_start_iterations = w > 0 (needs a start policy) the regrets are seeded from the start
@@ -508,7 +511,10 @@ class SteppedSolver(SubgameSolver):
         policy_delta: a `stats.PolicyDelta` of this batch -- the change of the current policy at the five
         iterations of `stats.delta_checkpoints` is left in `self.policy_deltas` (percentile -> 0-dim device
         tensor), from the regrets on either side of those iterations' updates (`_record_stats`,
-        cfr_evaluator.py:1573-1605)."""
+        cfr_evaluator.py:1573-1605).
+        graph: replay the iteration passes 1..T-2 from one CUDA graph (`GraphedCFRIteration`) instead of
+        launching their kernels and the leaf model's one by one; same kernels, same results.  Ignored
+        where the host works between the passes (cfr_avg, running_values, policy_delta)."""
         assert root_beliefs.shape == (self.B, 2, HPAD) and root_beliefs.dtype == torch.float32
         assert root_beliefs.is_contiguous() and root_beliefs.device == self.device
         ws = int(warm_start_iterations)
@@ -540,6 +546,14 @@ class SteppedSolver(SubgameSolver):
         self._last_model_values = None
         self._running = None
         self.policy_deltas = {}
+        graphed = None
+        if graph and not (cfr_avg or running_values or policy_delta is not None) and iterations >= 4:
+            # a graph is tied to the addresses and settings it was captured with: kept across solves that share them
+            key = (root_beliefs.data_ptr(), iterations, flags, id(leaf_fn))
+            if self._graphed is None or self._graphed[0] != key:
+                self._graphed = (key, GraphedCFRIteration(self, root_beliefs, sc, iterations, flags, leaf_fn))
+            graphed = self._graphed[1]
+            graphed.scalars = sc
         delta_at = {}
         if policy_delta is not None:
             from . import stats as pstats
@@ -570,6 +584,11 @@ class SteppedSolver(SubgameSolver):
                 flags_pass = flags | 8  # the start pass keeps its node values for the best responses
             else:
                 flags_pass = flags
+            if graphed is not None and 1 <= pas <= iterations - 2:
+                if graphed.captured_t is None:
+                    graphed.capture(pas)  # passes -1 and 0 have run: every lazy set-up is done
+                graphed.replay(pas)
+                continue
             before = None
             if pas in delta_at:  # the policy this pass plays; its bottom-up sweep updates the regrets
                 before = policy_delta.start_policy(start_policy) if pas < 0 else policy_delta.policy_of(self.regrets)
@@ -659,6 +678,82 @@ class SteppedSolver(SubgameSolver):
         del keep
 
 
+class GraphedCFRIteration:
+    """One iteration pass of a `SteppedSolver` (top-down sweep, the leaf model, bottom-up sweep) captured in
+    a CUDA graph and replayed for the other iterations: the counterpart of upstream's
+    `GraphedCFRIteration` (p2/search/fused_cfr_triton.py:2359-2457), which captures `cfr_iteration` and
+    refreshes its device scalars (`TScalars`) outside the captured region before every replay.
+
+    Here the kernels take the pass number by value, so the graph is captured as pass 0 of a table window:
+    before a replay for pass t the rows t and t+1 of the discount / mixing table are copied into a
+    two-row device buffer the captured launches read as rows 0 and 1, and the passes at which subgames
+    keep their sampling policy are shifted by t the same way.  A pass in the window must be an ordinary
+    one: 1 <= t <= iterations - 2 (the start pass, pass 0 after it, the last iteration and the final
+    pass take other branches in the kernels and run as plain launches).  Tree records, state arrays and
+    the root beliefs tensor are baked in at capture time, as upstream."""
+
+    def __init__(self, sv: "SteppedSolver", root_beliefs: torch.Tensor, scalars_dev: torch.Tensor, iterations: int,
+                 flags: int, leaf_fn=None):
+        if sv.device.type != "cuda":
+            raise ValueError("GraphedCFRIteration requires a CUDA solver.")
+        if iterations < 4:
+            raise ValueError("nothing to replay: fewer than four iterations")
+        self.sv, self.root_beliefs, self.scalars, self.iterations = sv, root_beliefs, scalars_dev, int(iterations)
+        self.flags, self.leaf_fn = int(flags), leaf_fn
+        self.window = torch.zeros(2, 32, dtype=torch.uint8, device=sv.device)
+        self.sample_window = None if sv.sample_pass is None else torch.full_like(sv.sample_pass, -2)
+        self._graph = None
+        self._captured_t = None
+        self._launches = 0
+
+    def _refresh(self, t: int) -> None:
+        self.window.copy_(self.scalars[t:t + 2])
+        if self.sample_window is not None:
+            torch.sub(self.sv.sample_pass, int(t), out=self.sample_window)
+
+    def _pass(self) -> None:
+        sv, n_leaves = self.sv, self.sv.layout.num_model_leaves
+        args = (self.root_beliefs, self.window, self.iterations, self.flags, 0, 0)
+        if n_leaves == 0:
+            sv._step(*args, 3, sample_pass=self.sample_window)
+            return
+        sv._step(*args, 1, sample_pass=self.sample_window)
+        vals = self.leaf_fn(sv.leaf_beliefs[:n_leaves])
+        if vals.shape[-1] == NUM_HANDS:
+            sv.leaf_values[:n_leaves, :, :NUM_HANDS].copy_(vals)
+        else:
+            sv.leaf_values[:n_leaves].copy_(vals)
+        sv._step(*args, 2, sample_pass=self.sample_window)
+
+    def capture(self, t_capture: int) -> None:
+        """Records the graph; nothing runs and the solver state does not move.  The solver must have run
+        at least one pass with the same leaf model before (lazy set-up happens there, not under capture)."""
+        if not 1 <= t_capture <= self.iterations - 2:
+            raise ValueError("only the passes 1..iterations-2 can be captured")
+        if self.sv.layout.num_model_leaves and self.leaf_fn is None:
+            raise ValueError("the trees have model-valued leaves: a leaf_fn is required")
+        self._refresh(t_capture)
+        before = self.sv.launches
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.device(self.sv.device), torch.cuda.graph(graph):
+            self._pass()
+        self._launches, self.sv.launches = self.sv.launches - before, before
+        self._graph, self._captured_t = graph, int(t_capture)
+
+    def replay(self, t: int) -> None:
+        if self._graph is None:
+            raise RuntimeError("capture() must be called before replay().")
+        if not 1 <= t <= self.iterations - 2:
+            raise ValueError("only the passes 1..iterations-2 can be replayed")
+        self._refresh(t)
+        self._graph.replay()
+        self.sv.launches += self._launches
+
+    @property
+    def captured_t(self):
+        return self._captured_t
+
+
 def solve_noalloc(sv: SubgameSolver, root_beliefs: torch.Tensor, scalars_dev: torch.Tensor, *,
                   cfr_plus: bool = False, enforce_zero_sum: bool = False) -> SolveResult:
     """Runs the same solve as `SubgameSolver.solve` through `p2b_cfr_solve_noalloc`, the entry
@@ -731,7 +826,8 @@ def solve_subgames_with_model(boards, ranges, pot, stacks, model, *, street: int
                               cfr_type: str = "discounted", alpha: float = 1.5, beta: float = 0.0, gamma: float = 2.0,
                               dcfr_delay: int = 0, cfr_plus: bool = False, device=None, chance_average: bool = True,
                               chunk: int = 2048, exploitability: bool = False, keep_node_values: bool = False,
-                              device_tree: bool = False, enforce_zero_sum: bool = False, cfr_avg: bool = False):
+                              device_tree: bool = False, enforce_zero_sum: bool = False, cfr_avg: bool = False,
+                              graph: bool = False):
     """Solves a batch of flop (street=1, 3 board cards) or turn (street=2, 4 cards) subgames
     whose leaves at the start of the next street are valued by `model(beliefs, boards,
     context)`, averaged over the next public card when `chance_average` (the
@@ -770,5 +866,5 @@ def solve_subgames_with_model(boards, ranges, pot, stacks, model, *, street: int
     rb = pad_rows(torch.as_tensor(ranges, dtype=torch.float32).to(device)).contiguous()
     scal = iteration_scalars(iterations, cfr_type=cfr_type, alpha=alpha, beta=beta, gamma=gamma, dcfr_delay=dcfr_delay)
     res = sv.solve(rb, scal, evaluator if layout.num_model_leaves else None, cfr_plus=cfr_plus,
-                   enforce_zero_sum=enforce_zero_sum, cfr_avg=cfr_avg)
+                   enforce_zero_sum=enforce_zero_sum, cfr_avg=cfr_avg, graph=graph)
     return res, trees, sv

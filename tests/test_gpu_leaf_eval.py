@@ -164,3 +164,44 @@ def test_fused_bf16_leaf_pipeline_equals_generic_path(cuda_device):
     b = generic(bel)
     assert a.shape == (L, 2, 1344) and b.shape == (L, 2, 1326)
     assert torch.equal(a[..., :1326], b)
+
+
+def test_graph_replayed_passes_equal_plain_launches(cuda_device):
+    """The iteration passes 1..T-2 replayed from one CUDA graph (two sweeps and the bf16 leaf network, scalars
+    and sampling passes read through a window refreshed before each replay) give the bits of the plain
+    launches: turn subgames with network leaves, and river subgames with a sampling schedule."""
+    from poker2_b200 import leaf_eval, solver, tree as ptree
+
+    n, iterations = 5, 9
+    boards, ranges, pot, stack = _inputs(n, 33)
+    model = leaf_eval.ValueMLP(width=128, depth=2, dtype=torch.bfloat16, seed=4).to(cuda_device)
+    out = []
+    for graph in (False, True):
+        res, trees, sv = solver.solve_subgames_with_model(
+            boards, ranges, pot, stack, model, street=2, iterations=iterations, max_raises=2, device=cuda_device,
+            chunk=16, exploitability=True, graph=graph)
+        assert sv.launches == 2 * (iterations + 2)  # two sweeps per pass, replayed or not
+        out.append([x.clone() for x in (res.policy_avg, res.regrets, res.weight_sums, res.root_values, res.exploitability)])
+        assert (sv._graphed is not None) == graph
+        if graph:
+            assert sv._graphed[1].captured_t == 1
+    for a, b in zip(*out):
+        assert torch.equal(a, b)
+
+    # river subgames (no model leaves: one launch per pass), policy kept at a per-subgame sampling pass
+    g = torch.Generator().manual_seed(8)
+    boards5 = torch.stack([torch.randperm(52, generator=g)[:5] for _ in range(n)]).numpy()
+    trees = ptree.build_trees(ptree.root_states(pot.numpy(), stack.numpy(), min_raise=2), [0.5, 1.0], 8, bb=2, max_raises=2)
+    layout = solver.device_layout(trees, boards5)
+    rb = solver.pad_rows(torch.empty(n, 2, 1326).exponential_(generator=g).to(cuda_device)).contiguous()
+    scal = solver.iteration_scalars(iterations)
+    t_sample = torch.tensor([1, 3, 4, 8, 6])
+    out = []
+    for graph in (False, True):
+        sv = solver.SteppedSolver(layout, torch.from_numpy(boards5), cuda_device, exploitability=True, sampling=True)
+        sv.set_sampling_schedule(t_sample)
+        for _ in range(2):  # the second solve reuses the captured graph
+            res = sv.solve(rb, scal, graph=graph)
+        out.append([x.clone() for x in (res.policy_avg, res.regrets, res.policy_sample, res.beliefs_last, res.root_values)])
+    for a, b in zip(*out):
+        assert torch.equal(a, b)
