@@ -58,6 +58,17 @@ int p2b_showdown_values(const unsigned char* tables, const int32_t* table_of_row
                         const int64_t* potential, const float* scale, float* values,
                         int64_t value_row_stride, int64_t rows, void* stream);
 
+/* showdown_ev_triton (src/p2/search/fused_cfr_triton.py:2271-2320): the EV of every strength-sorted
+ * position straight from sorted-order inputs, `rows` rows of `hands` (<= 1344) entries each:
+ * b_sorted fp32 opponent range in strength order, c1_sorted / c2_sorted int32 hole cards of the
+ * position (0..51; anything else counts as no card), l_idx / r_idx int32 tie group [L,R) of the
+ * position.  out [rows,hands] fp32 = win/den - loss/den with the formula of _showdown_value
+ * (cfr_evaluator.py:544-596), 0 where den <= eps.  The caller permutes back, masks the hands on
+ * the board and scales by the pot, as upstream. */
+int p2b_showdown_ev_sorted(const float* b_sorted, const int32_t* c1_sorted, const int32_t* c2_sorted,
+                           const int32_t* l_idx, const int32_t* r_idx, int64_t rows, int32_t hands,
+                           float eps, float* out, void* stream);
+
 /* ---- fused subgame CFR (src/p2/search/cfr_evaluator.py:1497-1528 evaluate_cfr with
  * cfr_iteration :1331-1381, on the ragged tree of sparse_cfr_evaluator.py:141-306) ----
  * One persistent kernel runs the start pass, `iterations` DCFR iterations and the final

@@ -32,6 +32,46 @@ def tie_groups(scores: np.ndarray, order: np.ndarray):
     return L, R
 
 
+def sorted_ev(boards, opp_beliefs, rank_mode: int = rank7.MODE_PLANES):
+    """The sorted-order stage of `_showdown_value` (cfr_evaluator.py:532-596) on its own: for boards [M,5] and
+    opponent beliefs [M,1326] fp32 (zero on the hands that use a board card), returns a dict with the
+    inputs of that stage (`b_sorted`, `c1_sorted`, `c2_sorted`, `L`, `R`, all [M,1326], and `order`) and its
+    result `ev_sorted` (win - loss as fractions of den, before the inverse permutation, the hand mask and the
+    pot scaling), computed like `showdown_values` below."""
+    boards = np.asarray(boards)
+    x_all = torch.as_tensor(opp_beliefs, dtype=torch.float32)
+    m = boards.shape[0]
+    scores, order = rank7.rank_hands(boards, rank_mode)
+    L_np, R_np = tie_groups(scores, order)
+    srt, L, R = torch.from_numpy(order), torch.from_numpy(L_np), torch.from_numpy(R_np)
+    cmb = torch.from_numpy(cards.combos())
+    onehot = torch.from_numpy(cards.combo_onehot())
+    c_sorted = cmb[srt]
+    c1, c2 = c_sorted[..., 0], c_sorted[..., 1]
+    x = x_all.gather(1, srt)
+    ev = torch.empty(m, H, dtype=torch.float32)
+    for b in range(m):
+        card_ok = torch.ones(52, dtype=torch.bool)
+        card_ok[torch.from_numpy(boards[b].astype(np.int64))] = False
+        inc = onehot[srt[b]] & card_ok[None, :]
+        xb = x[b]
+        P = torch.cat([torch.zeros(1), torch.cumsum(xb, dim=0)])
+        PC = torch.cat([torch.zeros(1, 52), torch.cumsum(inc.float() * xb[:, None], dim=0)], dim=0)
+        at = lambda pos, card: PC[pos, card]  # noqa: E731
+        PL, PR = P[L[b]], P[R[b]]
+        a0, b0, a1, b1 = at(L[b], c1[b]), at(L[b], c2[b]), at(R[b], c1[b]), at(R[b], c2[b])
+        win = PL - a0 - b0
+        tie = (PR - PL) - (a1 - a0) - (b1 - b0) + xb
+        tot = PC[-1]
+        den = (1.0 - tot[c1[b]] - tot[c2[b]] + xb).clamp(min=1e-8)
+        ok = den > 1e-8
+        wp = torch.where(ok, win / den, torch.zeros(()))
+        tp = torch.where(ok, tie / den, torch.zeros(()))
+        lp = torch.where(ok, 1.0 - wp - tp, torch.zeros(()))
+        ev[b] = wp - lp
+    return dict(b_sorted=x, c1_sorted=c1, c2_sorted=c2, L=L, R=R, order=srt, ev_sorted=ev)
+
+
 def showdown_values(boards, beliefs, potential, scale, rank_mode: int = rank7.MODE_PLANES, chunk: int = 16):
     """boards [M,5] ints, beliefs [M,2,1326] fp32, potential [M,2] int64, scale [M] fp32
     -> values [M,2,1326] fp32 (value of player p's hands against beliefs[:,1-p])."""

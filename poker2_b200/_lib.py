@@ -29,6 +29,7 @@ _SIGNATURES = {
     "p2b_compare7_planes": [_vp, _i64, _vp, _vp],
     "p2b_rank_hands": [_vp, _i64, _vp, _vp, _vp, _vp],
     "p2b_showdown_values": [_vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _i64, _vp],
+    "p2b_showdown_ev_sorted": [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _f32, _vp, _vp],
     "p2b_cfr_solve": [_vp, _vp, _i32, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64,
                       _vp, _i32, _i32, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _f32, _vp],
     "p2b_cfr_step": [_vp, _vp, _i32, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64,

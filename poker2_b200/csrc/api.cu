@@ -12,6 +12,8 @@ int launch_compare7_planes(const int8_t*, int64_t, int32_t*, cudaStream_t);
 int launch_board_setup(const int16_t*, int64_t, unsigned char*, int32_t*, long long*, cudaStream_t);
 int launch_showdown_eval(const unsigned char*, const int32_t*, const float*, int64_t, const long long*, const float*,
                          float*, int64_t, int64_t, cudaStream_t);
+int launch_showdown_ev_sorted(const float*, const int32_t*, const int32_t*, const int32_t*, const int32_t*, int64_t, int,
+                              float, float*, cudaStream_t);
 }  // namespace p2b
 
 using namespace p2b;
@@ -64,6 +66,14 @@ int p2b_showdown_values(const unsigned char* tables, const int32_t* table_of_row
     return launch_showdown_eval(tables, table_of_row, beliefs, belief_row_stride,
                                 reinterpret_cast<const long long*>(potential), scale, values, value_row_stride, rows,
                                 (cudaStream_t)stream);
+}
+
+int p2b_showdown_ev_sorted(const float* b_sorted, const int32_t* c1_sorted, const int32_t* c2_sorted, const int32_t* l_idx,
+                           const int32_t* r_idx, int64_t rows, int32_t hands, float eps, float* out, void* stream) {
+    P2B_REQUIRE(rows >= 0 && hands >= 0, "negative count");
+    P2B_REQUIRE(rows == 0 || hands == 0 || (b_sorted && c1_sorted && c2_sorted && l_idx && r_idx && out), "null pointer");
+    return launch_showdown_ev_sorted(b_sorted, c1_sorted, c2_sorted, l_idx, r_idx, rows, hands, eps, out,
+                                     (cudaStream_t)stream);
 }
 
 int p2b_cfr_default_blocks(void) { return cfr_default_blocks(); }

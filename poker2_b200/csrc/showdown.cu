@@ -535,4 +535,165 @@ int launch_showdown_eval(const unsigned char* tabs, const int32_t* tab_of_row, c
     return check_cuda(cudaGetLastError(), "showdown_eval_kernel");
 }
 
+// ---- showdown EV straight from strength-sorted inputs ------------------------------------
+// Counterpart of `showdown_ev_triton` (p2/search/fused_cfr_triton.py:2271-2320): per row the opponent
+// range in strength order, the two hole cards of every sorted position and its tie group [L,R); out is
+// the EV of every sorted position, before the caller permutes it back, masks the hands on the board and
+// scales by the pot.  The upstream kernel scans all 1326 positions for each hero position; here the
+// row gets one prefix over the positions and one prefix per card over that card's (at most 51)
+// positions, found through a bit mask of the positions per card.  Prefixes are accumulated in fp64 and
+// rounded to fp32 one by one and the formula runs in the operation order of `_showdown_value`
+// (p2/search/cfr_evaluator.py:544-596), so a row equals that function's sorted-order EV.
+constexpr int kEvsThreads = 384;
+constexpr int kEvsWarps = kEvsThreads / 32;
+constexpr int kEvsMaxHands = 1344;
+constexpr int kEvsWords = kEvsMaxHands / 32;  // 42 mask words per card
+
+__global__ void __launch_bounds__(kEvsThreads) showdown_ev_sorted_kernel(
+    const float* __restrict__ b_sorted, const int32_t* __restrict__ c1_sorted, const int32_t* __restrict__ c2_sorted,
+    const int32_t* __restrict__ l_idx, const int32_t* __restrict__ r_idx, int64_t rows, int hands, float eps,
+    float* __restrict__ out) {
+    __shared__ float s_b[kEvsMaxHands];
+    __shared__ float s_P[kEvsMaxHands + 1];        // s_P[k] = rounded mass of the positions before k
+    __shared__ float s_pc[52 * 52];                // first the card's values in list order, then their prefixes
+    __shared__ uint32_t s_mask[52 * kEvsWords];    // bit k of card c: position k holds c
+    __shared__ uint16_t s_pre[52 * (kEvsWords + 1)];  // set bits of card c in the words before w
+    __shared__ uint8_t s_c1[kEvsMaxHands], s_c2[kEvsMaxHands];
+    __shared__ double s_warp[kEvsWarps];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const int64_t base = row * hands;
+        for (int k = tid; k < kEvsMaxHands; k += kEvsThreads) {
+            const bool in = k < hands;
+            const int a = in ? c1_sorted[base + k] : -1, c = in ? c2_sorted[base + k] : -1;
+            s_b[k] = in ? b_sorted[base + k] : 0.0f;
+            s_c1[k] = (unsigned)a < 52u ? (uint8_t)a : 255;
+            s_c2[k] = ((unsigned)c < 52u && c != a) ? (uint8_t)c : 255;
+        }
+        for (int i = tid; i < 52 * kEvsWords; i += kEvsThreads) s_mask[i] = 0u;
+        for (int i = tid; i < 52 * 52; i += kEvsThreads) s_pc[i] = 0.0f;
+        __syncthreads();
+        for (int k = tid; k < hands; k += kEvsThreads) {
+            if (s_c1[k] != 255) atomicOr(&s_mask[s_c1[k] * kEvsWords + (k >> 5)], 1u << (k & 31));
+            if (s_c2[k] != 255) atomicOr(&s_mask[s_c2[k] * kEvsWords + (k >> 5)], 1u << (k & 31));
+        }
+        __syncthreads();
+        for (int c = warp; c < 52; c += kEvsWarps) {  // bit counts before every word
+            const int n0 = __popc(s_mask[c * kEvsWords + lane]);
+            const int n1 = lane + 32 < kEvsWords ? __popc(s_mask[c * kEvsWords + lane + 32]) : 0;
+            int i0 = n0, i1 = n1;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int u0 = __shfl_up_sync(0xffffffffu, i0, d), u1 = __shfl_up_sync(0xffffffffu, i1, d);
+                if (lane >= d) {
+                    i0 += u0;
+                    i1 += u1;
+                }
+            }
+            const int first = __shfl_sync(0xffffffffu, i0, 31);
+            s_pre[c * (kEvsWords + 1) + lane] = (uint16_t)(i0 - n0);
+            if (lane + 32 <= kEvsWords) s_pre[c * (kEvsWords + 1) + lane + 32] = (uint16_t)(first + i1 - n1);
+        }
+        __syncthreads();
+        for (int k = tid; k < hands; k += kEvsThreads) {  // the card lists: values in strength order
+            const uint32_t below = (1u << (k & 31)) - 1u;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int c = j == 0 ? s_c1[k] : s_c2[k];
+                if (c == 255) continue;
+                const int t = s_pre[c * (kEvsWords + 1) + (k >> 5)] + __popc(s_mask[c * kEvsWords + (k >> 5)] & below);
+                if (t < 52) s_pc[c * 52 + t] = s_b[k];
+            }
+        }
+        __syncthreads();
+        for (int c = warp; c < 52; c += kEvsWarps) {  // per card: mass of its t weakest hands, t = 0..51
+            const double v0 = s_pc[c * 52 + lane], v1 = lane + 32 < 52 ? s_pc[c * 52 + lane + 32] : 0.0;
+            double i0 = v0, i1 = v1;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const double u0 = __shfl_up_sync(0xffffffffu, i0, d), u1 = __shfl_up_sync(0xffffffffu, i1, d);
+                if (lane >= d) {
+                    i0 += u0;
+                    i1 += u1;
+                }
+            }
+            const double first = __shfl_sync(0xffffffffu, i0, 31);
+            __syncwarp();
+            s_pc[c * 52 + lane] = (float)(i0 - v0);
+            if (lane + 32 < 52) s_pc[c * 52 + lane + 32] = (float)(first + (i1 - v1));
+        }
+        {  // prefix over all positions: four consecutive positions per thread
+            double v[4], run = 0.0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int k = 4 * tid + i;
+                v[i] = k < kEvsMaxHands ? (double)s_b[k] : 0.0;
+                run += v[i];
+            }
+            double inc = run;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const double u = __shfl_up_sync(0xffffffffu, inc, d);
+                if (lane >= d) inc += u;
+            }
+            if (lane == 31) s_warp[warp] = inc;
+            __syncthreads();
+            double before = inc - run;
+            for (int w = 0; w < warp; ++w) before += s_warp[w];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int k = 4 * tid + i;
+                if (k == 0) s_P[0] = 0.0f;
+                before += v[i];
+                if (k < kEvsMaxHands) s_P[k + 1] = (float)before;
+            }
+        }
+        __syncthreads();
+        for (int k = tid; k < hands; k += kEvsThreads) {
+            int L = l_idx[base + k], R = r_idx[base + k];
+            L = min(max(L, 0), hands);
+            R = min(max(R, 0), hands);
+            const float x = s_b[k];
+            float at[2][3];  // per card: mass before L, before R, in all
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int c = j == 0 ? s_c1[k] : s_c2[k];
+                at[j][0] = at[j][1] = at[j][2] = 0.0f;
+                if (c == 255) continue;
+                const uint32_t* m = s_mask + c * kEvsWords;
+                const uint16_t* pre = s_pre + c * (kEvsWords + 1);
+                const int tl = pre[L >> 5] + ((L >> 5) < kEvsWords ? __popc(m[L >> 5] & ((1u << (L & 31)) - 1u)) : 0);
+                const int tr = pre[R >> 5] + ((R >> 5) < kEvsWords ? __popc(m[R >> 5] & ((1u << (R & 31)) - 1u)) : 0);
+                at[j][0] = s_pc[c * 52 + min(tl, 51)];
+                at[j][1] = s_pc[c * 52 + min(tr, 51)];
+                at[j][2] = s_pc[c * 52 + 51];
+            }
+            const float PL = s_P[L], PR = s_P[R];
+            const float win = __fsub_rn(__fsub_rn(PL, at[0][0]), at[1][0]);
+            const float seg = __fsub_rn(PR, PL);
+            const float tie = __fadd_rn(
+                __fsub_rn(__fsub_rn(seg, __fsub_rn(at[0][1], at[0][0])), __fsub_rn(at[1][1], at[1][0])), x);
+            const float den = __fadd_rn(__fsub_rn(__fsub_rn(1.0f, at[0][2]), at[1][2]), x);
+            const float safe = fmaxf(den, eps);
+            const float wp = __fdiv_rn(win, safe), tp = __fdiv_rn(tie, safe);
+            const float lp = __fsub_rn(__fsub_rn(1.0f, wp), tp);
+            out[base + k] = den > eps ? __fsub_rn(wp, lp) : 0.0f;
+        }
+        __syncthreads();
+    }
+}
+
+int launch_showdown_ev_sorted(const float* b_sorted, const int32_t* c1_sorted, const int32_t* c2_sorted,
+                              const int32_t* l_idx, const int32_t* r_idx, int64_t rows, int hands, float eps, float* out,
+                              cudaStream_t stream) {
+    if (rows == 0 || hands == 0) return P2B_OK;
+    if (hands < 0 || hands > kEvsMaxHands) return set_error(P2B_ERR_ARG, "a row holds at most %d hands", kEvsMaxHands);
+    int64_t grid = rows;
+    const int64_t cap = (int64_t)sm_count() * 4;
+    if (grid > cap) grid = cap;
+    showdown_ev_sorted_kernel<<<(unsigned)grid, kEvsThreads, 0, stream>>>(b_sorted, c1_sorted, c2_sorted, l_idx, r_idx,
+                                                                        rows, hands, eps, out);
+    return check_cuda(cudaGetLastError(), "showdown_ev_sorted_kernel");
+}
+
 }  // namespace p2b

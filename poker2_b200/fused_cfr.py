@@ -392,3 +392,26 @@ class TScalars:
             self.mix_onon.fill_(total / float(mix_new))
             self.mix_oon.fill_(float(mix_old) / float(mix_new))
         self.t_tensor.fill_(int(t))
+
+
+# ---- showdown EV from strength-sorted inputs (fused_cfr_triton.py:2271-2320) --------------
+def showdown_ev_triton(b_opp_sorted: torch.Tensor, c1_sorted: torch.Tensor, c2_sorted: torch.Tensor,
+                       L_idx: torch.Tensor, R_idx: torch.Tensor, eps: float = 1e-8, block_k: int = 32,
+                       block_j: int = 128) -> torch.Tensor:
+    """`EV_hand_sorted` [M,H] from sorted-order inputs: b_opp_sorted [M,H] fp32 (the opponent's normalised
+    beliefs in strength order, zero on the hands that use a board card), c1_sorted / c2_sorted [M,H] the
+    hole cards of every sorted position, L_idx / R_idx [M,H] its tie group [L,R).  As upstream, the caller
+    permutes the result back, multiplies by the hand mask and scales by potential / scale.  block_k and
+    block_j tune the upstream kernel's tiles and are accepted for the signature only: one thread block
+    handles a row with one prefix over the positions and one per card."""
+    _require()
+    if b_opp_sorted.device.type != "cuda":
+        raise ValueError("showdown_ev_triton requires CUDA tensors.")
+    assert b_opp_sorted.is_contiguous() and b_opp_sorted.dim() == 2 and b_opp_sorted.dtype == torch.float32
+    M, H = b_opp_sorted.shape
+    assert c1_sorted.shape == (M, H) and c2_sorted.shape == (M, H)
+    assert L_idx.shape == (M, H) and R_idx.shape == (M, H)
+    c1, c2, lo, hi = (x.to(torch.int32).contiguous() for x in (c1_sorted, c2_sorted, L_idx, R_idx))
+    out = torch.empty(M, H, device=b_opp_sorted.device, dtype=torch.float32)
+    _call("p2b_showdown_ev_sorted", out.device, _p(b_opp_sorted), _p(c1), _p(c2), _p(lo), _p(hi), M, H, float(eps), _p(out))
+    return out

@@ -67,3 +67,35 @@ def test_showdown_zero_sum_property(cuda_device):
     w1 = bel[:, 1].double() * unblocked.unblocked_mass(bel[:, 0]).double()
     total = (vals[:, 0] * w0).sum(-1) + (vals[:, 1] * w1).sum(-1)
     assert total.abs().max().item() < 1e-5
+
+
+def test_showdown_ev_from_sorted_inputs(cuda_device, golden_dir):
+    """`showdown_ev_triton` (sorted-order inputs in, sorted-order EV out) against the sorted stage of the CPU
+    oracle, which is pinned to upstream's `_showdown_value`: same bits on the golden boards, with the ranges of
+    both players, a delta range, an all-zero range (den = 1, EV = 0 - 0) and a row of ties only."""
+    from poker2_b200 import fused_cfr as F
+
+    z = np.load(os.path.join(golden_dir, "showdown.npz"))
+    boards = z["boards"][:8]
+    bel = torch.from_numpy(z["beliefs"][:8])
+    for x in (bel[:, 0], bel[:, 1]):
+        x = x.clone()
+        x[3] = 0.0
+        first = int(np.flatnonzero(cards.allowed_mask(boards.astype(np.int64))[3])[17])
+        x[3, first] = 1.0  # delta range
+        x[5] = 0.0  # empty range
+        st = oshow.sorted_ev(boards, x)
+        got = F.showdown_ev_triton(st["b_sorted"].to(cuda_device).contiguous(), st["c1_sorted"].to(cuda_device),
+                                   st["c2_sorted"].to(cuda_device), st["L"].to(cuda_device), st["R"].to(cuda_device))
+        assert got.shape == st["ev_sorted"].shape and got.dtype == torch.float32
+        diff = (got.cpu() - st["ev_sorted"]).abs().max().item()
+        print("max abs difference", diff)
+        assert torch.equal(got.cpu(), st["ev_sorted"])
+    # one tie group over all positions: nobody wins or loses
+    st = oshow.sorted_ev(boards[:1], bel[:1, 0])
+    L, R = torch.zeros_like(st["L"]), torch.full_like(st["R"], 1326)
+    got = F.showdown_ev_triton(st["b_sorted"].to(cuda_device).contiguous(), st["c1_sorted"].to(cuda_device),
+                               st["c2_sorted"].to(cuda_device), L.to(cuda_device), R.to(cuda_device))
+    assert got.abs().max().item() < 1e-6
+    with pytest.raises(ValueError):
+        F.showdown_ev_triton(st["b_sorted"], st["c1_sorted"], st["c2_sorted"], L, R)

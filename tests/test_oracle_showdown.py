@@ -13,6 +13,20 @@ def test_showdown_oracle_bit_exact(golden_dir):
     assert torch.equal(got, torch.from_numpy(z["values"]))
 
 
+def test_sorted_stage_of_the_showdown_oracle_bit_exact(golden_dir):
+    """`showdown.sorted_ev` (what the sorted-input kernel is checked against) composed with the inverse
+    permutation, the hand mask and the pot scaling gives the upstream values."""
+    z = np.load(os.path.join(golden_dir, "showdown.npz"))
+    boards, bel = z["boards"][:6], torch.from_numpy(z["beliefs"][:6])
+    allowed = torch.from_numpy(cards.allowed_mask(boards.astype(np.int64))).float()
+    pot, scale = torch.from_numpy(z["potential"][:6]), torch.from_numpy(z["scale"][:6])
+    for hero in range(2):
+        st = showdown.sorted_ev(boards, bel[:, 1 - hero])
+        ev = st["ev_sorted"].gather(1, torch.argsort(st["order"], dim=1)) * allowed
+        got = ev * pot[:, hero][:, None] / scale[:, None]
+        assert torch.equal(got, torch.from_numpy(z["values"][:6, hero]))
+
+
 def test_showdown_oracle_against_enumeration(golden_dir):
     """Independent check: enumerate opponent hands for a handful of hero hands."""
     from oracle import rank7
