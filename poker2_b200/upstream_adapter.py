@@ -203,6 +203,35 @@ class B200CFREvaluator:
         self.warm_start_iterations = ws
         self.generator = generator
 
+    @classmethod
+    def from_keywords(cls, search_batch_size: int, env_proto, model, bet_bins, max_depth: int, cfr_iterations: int,
+                      device, float_dtype=torch.float32, generator: torch.Generator | None = None,
+                      warm_start_iterations: int = 15, warm_start_type="model_br", warm_start_multiplier: float = 1.0,
+                      num_supervisions: int = 1, cfr_type="linear", cfr_avg: bool = True, cfr_plus: bool = True,
+                      dcfr_alpha: float = 1.5, dcfr_beta: float = 0.0, dcfr_gamma: float = 2.0,
+                      dcfr_alpha_final: float | None = None, dcfr_beta_final: float | None = None,
+                      dcfr_gamma_final: float | None = None, dcfr_delay: int = 0, sample_epsilon: float = 0.25,
+                      value_targets_from_final_policy: bool = False, **kw) -> "B200CFREvaluator":
+        """The keyword constructor of the dense `RebelCFREvaluator` (rebel_cfr_evaluator.py:73-100), same
+        argument names and defaults, on this evaluator: the solve is the same CFR on the same public tree;
+        the state tensors keep the sparse node order (valid nodes only, level-major), not the dense
+        A**depth layout.  `env_proto` supplies the big blind; solver state is fp32 whatever `float_dtype`
+        says, and `num_supervisions` belongs to the trainer."""
+        from types import SimpleNamespace
+
+        if float_dtype not in (torch.float32, None):
+            raise ValueError("the solver state is fp32")
+        search = SimpleNamespace(
+            depth=int(max_depth), iterations=int(cfr_iterations), warm_start_iterations=int(warm_start_iterations),
+            warm_start_type=warm_start_type, warm_start_multiplier=float(warm_start_multiplier), cfr_type=cfr_type,
+            cfr_avg=bool(cfr_avg), cfr_plus=bool(cfr_plus), dcfr_alpha=dcfr_alpha, dcfr_beta=dcfr_beta,
+            dcfr_gamma=dcfr_gamma, dcfr_alpha_final=dcfr_alpha_final, dcfr_beta_final=dcfr_beta_final,
+            dcfr_gamma_final=dcfr_gamma_final, dcfr_plus_delay=int(dcfr_delay), sample_epsilon=float(sample_epsilon),
+            value_targets_from_final_policy=bool(value_targets_from_final_policy))
+        env = SimpleNamespace(bet_bins=list(bet_bins), sb=int(getattr(env_proto, "sb", 1)), bb=int(getattr(env_proto, "bb", 2)))
+        cfg = SimpleNamespace(search=search, env=env, num_envs=int(search_batch_size), seed=0)
+        return cls(model, device, cfg, generator, **kw)
+
     # attributes the trainer reads or mutates (cfr_trainer.py:194-234)
     @property
     def cfr_iterations(self) -> int:

@@ -39,3 +39,29 @@ def test_replay_ring_matches_upstream_buffer(golden_dir):
     assert np.array_equal(strat.features.street.numpy(), z["strat_street"])
     buf.clear()
     assert len(buf) == 0
+
+
+def test_dense_evaluator_keyword_constructor_maps_to_the_solver_settings():
+    """`B200CFREvaluator.from_keywords` takes the arguments of the dense `RebelCFREvaluator`
+    (rebel_cfr_evaluator.py:73-100) with its defaults: linear CFR with the CFR+ clamp, cfr_avg, a `model_br`
+    warm start of 15 iterations and running value targets."""
+    from types import SimpleNamespace
+
+    import torch
+
+    from poker2_b200.upstream_adapter import B200CFREvaluator
+
+    ev = B200CFREvaluator.from_keywords(8, SimpleNamespace(sb=5, bb=10), None, [0.5, 1.0], 4, 40, torch.device("cpu"),
+                                        torch.float32, torch.Generator().manual_seed(0))
+    inner = ev._ev
+    assert ev.root_nodes == 8 and ev.cfr_iterations == 40 and ev.num_actions == 5 and ev.num_players == 2
+    assert (inner.cfr_type, inner.cfr_plus, inner.cfr_avg, inner.running_values) == ("linear", True, True, True)
+    assert (inner.warm_start_iterations, inner.warm_start_type, inner.warm_start_multiplier) == (15, "model_br", 1.0)
+    assert (inner.bb, inner.max_depth, inner.sample_epsilon) == (10, 4, 0.25)
+    ev = B200CFREvaluator.from_keywords(2, SimpleNamespace(bb=2), None, [1.0], 3, 12, "cpu", warm_start_iterations=0,
+                                        cfr_type="discounted_plus", cfr_avg=False, cfr_plus=False, dcfr_alpha=2.0,
+                                        dcfr_alpha_final=4.0, dcfr_delay=5, value_targets_from_final_policy=True,
+                                        policy_delta_stats=True)
+    inner = ev._ev
+    assert (inner.cfr_type, inner.alpha, inner.alpha_final, inner.dcfr_delay) == ("discounted_plus", 2.0, 4.0, 5)
+    assert not inner.running_values and not inner.cfr_avg and inner.policy_delta_stats and ev.num_actions == 4
