@@ -98,6 +98,8 @@ __global__ void block_normalize_kernel(float* __restrict__ target, const unsigne
                                        const float* __restrict__ allowed_prob, long long rows, int outer_stride, int H,
                                        float eps) {
     __shared__ double red[kThreads / 32];
+    __shared__ float srow[P2B_HPAD];
+    __shared__ float s_total;
     constexpr int kPer = 6;  // 256 threads x 6 cover rows of up to 1536 entries in registers
     for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
         const long long outer = row / outer_stride;
@@ -112,7 +114,25 @@ __global__ void block_normalize_kernel(float* __restrict__ target, const unsigne
                 v[i] = (h < H && m[h]) ? t[h] : 0.0f;
                 s += (double)v[i];
             }
-            const float total = (float)block_sum(s, red);
+            float total;
+            if (H == P2B_NUM_HANDS) {
+                // a row of 1326 hands is summed in fp32 in the order of the upstream CPU reduction
+                // (cfr_evaluator.py:263-273 through torch.sum), so the quotients carry its bits
+#pragma unroll
+                for (int i = 0; i < kPer; ++i) {
+                    const int h = threadIdx.x + i * kThreads;
+                    if (h < H) srow[h] = v[i];
+                }
+                __syncthreads();
+                if (threadIdx.x < 32) {
+                    const float r = row_sum_reference_order(srow);
+                    if (threadIdx.x == 0) s_total = r;
+                }
+                __syncthreads();
+                total = s_total;
+            } else {
+                total = (float)block_sum(s, red);
+            }
             const Divisor d = make_divisor(total);
 #pragma unroll
             for (int i = 0; i < kPer; ++i) {
@@ -455,6 +475,8 @@ __global__ void deep_beliefs_kernel(float* __restrict__ out, const float* __rest
                                     const long long* __restrict__ root_index, long long num_roots, long long total,
                                     int H, float eps) {
     __shared__ double red[kThreads / 32];
+    __shared__ float srow[P2B_HPAD];
+    __shared__ float s_total;
     const long long rows = (total - num_roots) * 2;
     for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
         const long long node = num_roots + r / 2;
@@ -462,9 +484,22 @@ __global__ void deep_beliefs_kernel(float* __restrict__ out, const float* __rest
         const float* rb = root_beliefs + (root_index[node] * 2 + p) * H;
         const float* rw = reach + (node * 2 + p) * H;
         float* o = out + (node * 2 + p) * H;
-        double s = 0.0;
-        for (int h = threadIdx.x; h < H; h += blockDim.x) s += (double)__fmul_rn(rb[h], rw[h]);
-        const float tot = (float)block_sum(s, red);
+        float tot;
+        if (H == P2B_NUM_HANDS) {  // fp32 sum in the order of the upstream CPU reduction, as in block_normalize_kernel
+            __syncthreads();       // the previous row's sum has been read
+            for (int h = threadIdx.x; h < H; h += blockDim.x) srow[h] = __fmul_rn(rb[h], rw[h]);
+            __syncthreads();
+            if (threadIdx.x < 32) {
+                const float v = row_sum_reference_order(srow);
+                if (threadIdx.x == 0) s_total = v;
+            }
+            __syncthreads();
+            tot = s_total;
+        } else {
+            double s = 0.0;
+            for (int h = threadIdx.x; h < H; h += blockDim.x) s += (double)__fmul_rn(rb[h], rw[h]);
+            tot = (float)block_sum(s, red);
+        }
         for (int h = threadIdx.x; h < H; h += blockDim.x)
             o[h] = tot > eps ? __fdiv_rn(__fmul_rn(rb[h], rw[h]), tot) : allowed_prob[node * H + h];
     }
