@@ -415,3 +415,80 @@ def showdown_ev_triton(b_opp_sorted: torch.Tensor, c1_sorted: torch.Tensor, c2_s
     out = torch.empty(M, H, device=b_opp_sorted.device, dtype=torch.float32)
     _call("p2b_showdown_ev_sorted", out.device, _p(b_opp_sorted), _p(c1), _p(c2), _p(lo), _p(hi), M, H, float(eps), _p(out))
     return out
+
+
+# ---- CUDA graph capture of a whole cfr_iteration (fused_cfr_triton.py:2322-2457) ---------
+class _EvaluatorStateSnapshot:
+    """Copies of the evaluator tensors an iteration changes; `restore_to` puts them back."""
+
+    NAMES = ("policy_probs", "policy_probs_avg", "policy_probs_sample", "cumulative_regrets", "regret_weight_sums",
+             "self_reach", "self_reach_avg", "beliefs", "beliefs_avg", "latest_values", "values_avg")
+
+    def __init__(self, names, tensors):
+        self.names, self.tensors = tuple(names), tuple(tensors)
+
+    @classmethod
+    def from_evaluator(cls, evaluator) -> "_EvaluatorStateSnapshot":
+        names = [n for n in cls.NAMES if isinstance(getattr(evaluator, n, None), torch.Tensor)]
+        return cls(names, [getattr(evaluator, n).detach().clone() for n in names])
+
+    def restore_to(self, evaluator) -> None:
+        for name, saved in zip(self.names, self.tensors):
+            getattr(evaluator, name).copy_(saved)
+
+    def max_abs_diff(self, other: "_EvaluatorStateSnapshot") -> dict:
+        assert self.names == other.names
+        return {n: (a - b).abs().max().item() for n, a, b in zip(self.names, self.tensors, other.tensors)}
+
+
+class GraphedCFRIteration:
+    """Captures `evaluator.cfr_iteration` in a CUDA graph and replays it for other iterations, with the
+    interface of upstream's class: `capture(t_capture, num_warmup)` runs real warm-up iterations (they move
+    the evaluator's state, as upstream's do), then records one iteration; `replay(t)` refreshes the device
+    scalars through `evaluator.prepare_replay(t)` outside the graph and launches it.  The evaluator must
+    keep its iteration scalars on the device and honour `_skip_t_scalars_update`
+    (`step_evaluator.StepCFREvaluator` does).  Replayed iterations must take the Python branches of the
+    captured one (both past the average-policy delay, for one), and the trees are baked in."""
+
+    def __init__(self, evaluator) -> None:
+        if evaluator.device.type != "cuda":
+            raise ValueError("GraphedCFRIteration requires a CUDA evaluator.")
+        self.evaluator = evaluator
+        self._graph = None
+        self._captured_t = None
+
+    def capture(self, t_capture: int, num_warmup: int = 2) -> None:
+        ev = self.evaluator
+        if not hasattr(ev, "_t_scalars"):
+            raise ValueError("Evaluator must keep its iteration scalars on the device (a ._t_scalars TScalars holder) "
+                             "for graph capture.")
+        for i in range(num_warmup):
+            ev.cfr_iteration(t_capture + i)
+        ev.prepare_replay(t_capture)
+        prev_skip = ev._skip_t_scalars_update
+        ev._skip_t_scalars_update = True
+        try:
+            with torch.cuda.device(ev.device):
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    ev.cfr_iteration(t_capture)  # one run on the capture stream, scalars already filled
+                torch.cuda.current_stream().wait_stream(side)
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    ev.cfr_iteration(t_capture)
+        finally:
+            ev._skip_t_scalars_update = prev_skip
+        self._graph, self._captured_t = graph, int(t_capture)
+
+    def replay(self, t: int | None = None) -> None:
+        if self._graph is None:
+            raise RuntimeError("capture() must be called before replay().")
+        if t is not None:
+            self.evaluator.prepare_replay(t)
+        self._graph.replay()
+
+    @property
+    def captured_t(self):
+        return self._captured_t

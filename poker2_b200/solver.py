@@ -445,7 +445,7 @@ class SteppedSolver(SubgameSolver):
 
     start_policy_rows = None  # [rows,1344] policy of the start pass (None: uniform)
     _last_model_values = None
-    _graphed = None  # (key, GraphedCFRIteration) of the last solve with graph=True
+    _graphed = None  # (key, GraphedPass) of the last solve with graph=True
 
     def _de_average(self, vals, t, scalars, enforce_zero_sum, n_leaves):
         """The CFR-AVG branch of `_set_model_values_impl` (cfr_evaluator.py:997-1018): from t = 2 on the
@@ -512,7 +512,7 @@ class SteppedSolver(SubgameSolver):
         iterations of `stats.delta_checkpoints` is left in `self.policy_deltas` (percentile -> 0-dim device
         tensor), from the regrets on either side of those iterations' updates (`_record_stats`,
         cfr_evaluator.py:1573-1605).
-        graph: replay the iteration passes 1..T-2 from one CUDA graph (`GraphedCFRIteration`) instead of
+        graph: replay the iteration passes 1..T-2 from one CUDA graph (`GraphedPass`) instead of
         launching their kernels and the leaf model's one by one; same kernels, same results.  Ignored
         where the host works between the passes (cfr_avg, running_values, policy_delta)."""
         assert root_beliefs.shape == (self.B, 2, HPAD) and root_beliefs.dtype == torch.float32
@@ -551,7 +551,7 @@ class SteppedSolver(SubgameSolver):
             # a graph is tied to the addresses and settings it was captured with: kept across solves that share them
             key = (root_beliefs.data_ptr(), iterations, flags, id(leaf_fn))
             if self._graphed is None or self._graphed[0] != key:
-                self._graphed = (key, GraphedCFRIteration(self, root_beliefs, sc, iterations, flags, leaf_fn))
+                self._graphed = (key, GraphedPass(self, root_beliefs, sc, iterations, flags, leaf_fn))
             graphed = self._graphed[1]
             graphed.scalars = sc
         delta_at = {}
@@ -678,7 +678,7 @@ class SteppedSolver(SubgameSolver):
         del keep
 
 
-class GraphedCFRIteration:
+class GraphedPass:
     """One iteration pass of a `SteppedSolver` (top-down sweep, the leaf model, bottom-up sweep) captured in
     a CUDA graph and replayed for the other iterations: the counterpart of upstream's
     `GraphedCFRIteration` (p2/search/fused_cfr_triton.py:2359-2457), which captures `cfr_iteration` and
@@ -695,7 +695,7 @@ class GraphedCFRIteration:
     def __init__(self, sv: "SteppedSolver", root_beliefs: torch.Tensor, scalars_dev: torch.Tensor, iterations: int,
                  flags: int, leaf_fn=None):
         if sv.device.type != "cuda":
-            raise ValueError("GraphedCFRIteration requires a CUDA solver.")
+            raise ValueError("GraphedPass requires a CUDA solver.")
         if iterations < 4:
             raise ValueError("nothing to replay: fewer than four iterations")
         self.sv, self.root_beliefs, self.scalars, self.iterations = sv, root_beliefs, scalars_dev, int(iterations)

@@ -88,6 +88,10 @@ class StepCFREvaluator:
         self.latest_values[fold, 0] = fv[fold][:, None]
         self.latest_values[fold, 1] = -fv[fold][:, None]
         self.values_avg = self.latest_values.clone()
+        # iteration scalars on the device, so that one captured iteration can be replayed for another t
+        # (fused_sparse_cfr_evaluator.py:100-107, 535-550)
+        self._t_scalars = F.TScalars(dev)
+        self._skip_t_scalars_update = False
 
     # ---- reach and beliefs (cfr_evaluator.py:248-273, 332-380) ------------------------------
     def _calculate_reach_weights(self, target: torch.Tensor, policy: torch.Tensor) -> None:
@@ -181,10 +185,9 @@ class StepCFREvaluator:
             self.policy_probs_avg.copy_(self.policy_probs)
             return
         N, top = self.root_nodes, self.top
-        old, new = self._get_mixing_weights(t)
-        avg = self.policy_probs_avg
-        F.fused_average_policy_mix_(avg, self.policy_probs, self.self_reach, self.self_reach_avg, self.to_act,
-                                    self.parent_index, old=old, new=new, bottom=N)
+        avg, ts = self.policy_probs_avg, self._t_scalars
+        F.fused_average_policy_mix_with_tensors_(avg, self.policy_probs, self.self_reach, self.self_reach_avg, self.to_act,
+                                                 self.parent_index, ts.mix_old, ts.mix_new, ts.mix_total, bottom=N)
         psum = F.fused_parent_sum(avg, self.child_offsets[:top].contiguous(), self.child_count[:top].contiguous(),
                                   max_children=self.num_actions)
         child = avg[N:].contiguous()
@@ -204,14 +207,23 @@ class StepCFREvaluator:
         self._calculate_reach_weights(self.self_reach_avg, self.policy_probs_avg)
         self._propagate_all_beliefs(self.beliefs_avg, self.self_reach_avg)
 
+    def prepare_replay(self, t: int) -> None:
+        """Fills the device scalars of iteration t (discount factors, mixing weights); `cfr_iteration` does it
+        itself unless `_skip_t_scalars_update` is set, which a graph capture sets so that the fills stay outside
+        the captured region (fused_sparse_cfr_evaluator.py:535-550)."""
+        old, new = self._get_mixing_weights(t)
+        discounted = self.cfr_type in ("discounted", "discounted_plus")
+        self._t_scalars.update(int(t), self.dcfr_alpha if discounted else 0.0, self.dcfr_beta if discounted else 0.0,
+                               old, new)
+
     def cfr_iteration(self, t: int) -> None:
+        if not self._skip_t_scalars_update:
+            self.prepare_replay(t)
         regrets = self.compute_instantaneous_regrets(self.latest_values)
-
-        class _Kind:
-            name = self.cfr_type
-
-        F.fused_dcfr_update_(self.cumulative_regrets, self.regret_weight_sums, regrets, int(t), _Kind, self.dcfr_alpha,
-                             self.dcfr_beta, self.cfr_plus)
+        ts = self._t_scalars
+        F.fused_dcfr_update_with_tensors_(self.cumulative_regrets, self.regret_weight_sums, regrets, ts.t_alpha_num,
+                                          ts.t_beta_num, ts.t_alpha_den, ts.t_beta_den,
+                                          self.cfr_type in ("discounted", "discounted_plus"), self.cfr_plus)
         self.update_policy(t)
         self.set_leaf_values(t)
         self.compute_expected_values()

@@ -111,3 +111,42 @@ def test_step_methods_with_model_leaves(cuda_device, golden_dir):
     _close("policy_probs_avg", ev.policy_probs_avg[n:], z["policy_avg"][n:])
     _close("cumulative_regrets", ev.cumulative_regrets[n:], z["regrets"][n:])
     _close("root values", ev.values_avg[:n], z["root_values"])
+
+
+def test_graphed_iteration_replays_across_t(cuda_device, golden_dir):
+    """`fused_cfr.GraphedCFRIteration` on the step evaluator, the way upstream tests its own
+    (tests/test_fused_cfr_triton.py:631-760): capture one `cfr_iteration` at t = 3, restore the state from
+    before, then replay it for t = 3, 4, 5 with the device scalars refreshed outside the graph; every replay
+    must leave the bits of an uncaptured iteration at that t."""
+    from poker2_b200 import fused_cfr as F, step_evaluator, tree as ptree
+
+    z = np.load(os.path.join(golden_dir, "cfr_batch_cap2_t24.npz"))
+    pot, stack, boards = z["pot"][:2], z["stack"][:2], z["boards"][:2].astype(np.int64)
+    trees = ptree.build_trees(ptree.root_states(pot, stack, min_raise=2), [0.5, 1.0], int(z["max_depth"]), bb=2,
+                              max_raises=int(z["cap"]))
+
+    def fresh():
+        ev = step_evaluator.StepCFREvaluator(trees, boards, torch.from_numpy(z["ranges"][:2]), cuda_device, iterations=8)
+        ev.initialize_policy_and_beliefs()
+        ev.set_leaf_values(0)
+        ev.compute_expected_values()
+        ev.values_avg.copy_(ev.latest_values)
+        for t in range(3):  # past the t = 0 branch of the average-policy update
+            ev.cfr_iteration(t)
+        return ev
+
+    base, graphed = fresh(), fresh()
+    pre = F._EvaluatorStateSnapshot.from_evaluator(graphed)
+    runner = F.GraphedCFRIteration(graphed)
+    with pytest.raises(RuntimeError):
+        runner.replay(3)
+    runner.capture(t_capture=3, num_warmup=1)  # the warm-up iterations move the state ...
+    assert runner.captured_t == 3
+    pre.restore_to(graphed)  # ... so it is put back before the replays
+    for t in (3, 4, 5):
+        base.cfr_iteration(t)
+        runner.replay(t)
+        torch.cuda.synchronize()
+        diffs = F._EvaluatorStateSnapshot.from_evaluator(base).max_abs_diff(F._EvaluatorStateSnapshot.from_evaluator(graphed))
+        print(t, diffs)
+        assert max(diffs.values()) == 0.0, (t, diffs)
