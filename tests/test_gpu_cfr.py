@@ -269,3 +269,36 @@ def test_start_policy_and_warm_start_match_upstream(cuda_device, golden_dir):
         torch.testing.assert_close(got, want, rtol=RTOL, atol=ATOL)
     torch.testing.assert_close(res.root_values[..., :1326].cpu(), torch.from_numpy(z["root_values"]), rtol=RTOL, atol=ATOL)
     torch.testing.assert_close(res.exploitability.cpu(), torch.from_numpy(z["exploitability"]), rtol=1e-4, atol=1e-6)
+
+
+@pytest.mark.parametrize("name,extra", [
+    ("cfr_single_cap2_t8", {}), ("cfr_single_cap2_t256", {}), ("cfr_single_nocap_t32", {}), ("cfr_batch_cap2_t24", {}),
+    ("cfr_ragged16_cap2_t256", {}), ("cfr_standard_cap2_t16", {"cfr_type": "standard"})])
+def test_one_call_solve_equals_the_upstream_run_bit_for_bit(cuda_device, golden_dir, name, extra):
+    """The tolerance the other tests state (1e-5) is the required bar; what the kernels actually deliver on these
+    upstream runs is equality of every fp32 bit -- strategies, regrets, weight sums, root values and local
+    exploitability, after up to 256 iterations -- because every sum and quotient follows the upstream CPU
+    operation order.  This test pins that stronger property so a change that loses it is noticed."""
+    from poker2_b200 import solver
+
+    z = np.load(os.path.join(golden_dir, name + ".npz"))
+    cap = int(z["cap"]) if int(z["cap"]) > 0 else None
+    res, trees = solver.solve_subgames(z["boards"].astype(np.int64), torch.from_numpy(z["ranges"]), z["pot"], z["stack"],
+                                       iterations=int(z["iterations"]), max_depth=int(z["max_depth"]), max_raises=cap,
+                                       exploitability=True, device=cuda_device, **extra)
+    assert trees.total_nodes == int(z["total_nodes"])
+    n = trees.num_roots
+    checked = 0
+    for key, got in [("policy_avg", res.level_major(res.policy_avg)[n:]), ("regrets", res.level_major(res.regrets)[n:]),
+                     ("weight_sums", res.level_major(res.weight_sums)[n:]), ("root_values", res.root_values[..., :1326]),
+                     ("exploitability", res.exploitability)]:
+        if key not in z.files:
+            continue
+        want = torch.from_numpy(z[key])
+        if want.shape[0] == trees.total_nodes and key != "root_values" and key != "exploitability":
+            want = want[n:]
+        if want.shape != got.shape:  # a fixture that keeps a row subsample only
+            continue
+        assert torch.equal(got.cpu(), want), (key, int((got.cpu() != want).sum()))
+        checked += 1
+    assert checked >= 2
