@@ -22,8 +22,8 @@ def test_showdown_golden(cuda_device, golden_dir):
                                    torch.from_numpy(z["potential"]), torch.from_numpy(z["scale"]))
     want = torch.from_numpy(z["values"])
     torch.testing.assert_close(got.cpu(), want, rtol=RTOL, atol=ATOL)
-    # in practice the match is far tighter than the tolerance
-    assert (got.cpu() - want).abs().max().item() < 1e-6
+    # the stated bar is the tolerance above; what the kernel delivers is every bit of upstream's fp32 values
+    assert torch.equal(got.cpu(), want), int((got.cpu() != want).sum())
 
 
 def test_showdown_random_boards_shared_tables(cuda_device):
