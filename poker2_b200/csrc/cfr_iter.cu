@@ -111,6 +111,33 @@ __device__ __forceinline__ void sth(float* row, int tid, const FV<VPT>& r) {
         for (int i = 0; i < VPT; ++i) row[tid + i * (P2B_HPAD / VPT)] = r.v[i];
     }
 }
+// State rows (regrets, weight sums, average policy) are read once and written once per pass and not touched again
+// before the next pass, by which time the other blocks have pushed far more than the L2 holds through it; the
+// streaming forms mark their lines as the first to evict, in favour of the block's work rows (bit 0: loads,
+// bit 1: stores).  Measured on 1184 subgames x 64 iterations: stores 0.5 % faster, loads no effect.
+#ifndef P2B_ITER_STREAM
+#define P2B_ITER_STREAM 2
+#endif
+template <int VPT>
+__device__ __forceinline__ FV<VPT> ldh_state(const float* row, int tid) {
+    if constexpr ((P2B_ITER_STREAM & 1) != 0 && VPT != 2) {
+        FV<VPT> r;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) r.v[i] = __ldcs(row + tid + i * (P2B_HPAD / VPT));
+        return r;
+    } else {
+        return ldh<VPT>(row, tid);
+    }
+}
+template <int VPT>
+__device__ __forceinline__ void sth_state(float* row, int tid, const FV<VPT>& r) {
+    if constexpr ((P2B_ITER_STREAM & 2) != 0 && VPT != 2) {
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) __stcs(row + tid + i * (P2B_HPAD / VPT), r.v[i]);
+    } else {
+        sth<VPT>(row, tid, r);
+    }
+}
 // Pulls n consecutive rows into L2: a row is 42 lines of 128 bytes, thread t takes line t of each.
 __device__ __forceinline__ void prefetch_lines(const float* row, int n, int tid) {
     if (tid < P2B_HPAD / 32) {
@@ -322,7 +349,7 @@ __device__ __forceinline__ void iter_down(int pass, const CfrParams& p, IterBloc
         FV<VPT> Pn, Pbn;
         if (!kDownAsync) {
             Pn = ldh<VPT>(B.row_pcur(fc), tid);
-            if (mix) Pbn = ldh<VPT>(B.state_row(p.policy_avg, fc), tid);
+            if (mix) Pbn = ldh_state<VPT>(B.state_row(p.policy_avg, fc), tid);
         }
 #pragma unroll 1
         for (int c = 0; c < k; ++c) {
@@ -335,7 +362,7 @@ __device__ __forceinline__ void iter_down(int pass, const CfrParams& p, IterBloc
                 Pb = Pbn;
                 if (c + 1 < k) {
                     Pn = ldh<VPT>(B.row_pcur(fc + c + 1), tid);
-                    if (mix) Pbn = ldh<VPT>(B.state_row(p.policy_avg, fc + c + 1), tid);
+                    if (mix) Pbn = ldh_state<VPT>(B.state_row(p.policy_avg, fc + c + 1), tid);
                 }
             }
             const NodeRec ch = B.nodes[fc + c];
@@ -376,7 +403,7 @@ __device__ __forceinline__ void iter_down(int pass, const CfrParams& p, IterBloc
                 for (int i = 0; i < VPT; ++i) psum.v[i] = __fadd_rn(psum.v[i], q.v[i]);
                 sth<VPT>(B.stash_row(c), tid, q);
             } else {
-                sth<VPT>(B.state_row(p.policy_avg, fc + c), tid, P);
+                sth_state<VPT>(B.state_row(p.policy_avg, fc + c), tid, P);
             }
         }
         if (kDownAsync && ii + 1 < n_internal) fetch_children(ii + 1);  // the landing rows are free again
@@ -401,7 +428,7 @@ __device__ __forceinline__ void iter_down(int pass, const CfrParams& p, IterBloc
 #pragma unroll
                 for (int i = 0; i < VPT; ++i)
                     if (psum.v[i] > 1e-5f) q.v[i] = r.v[i];
-                sth<VPT>(B.state_row(p.policy_avg, fc + c), tid, q);
+                sth_state<VPT>(B.state_row(p.policy_avg, fc + c), tid, q);
             }
         }
         __syncthreads();
@@ -772,8 +799,8 @@ __device__ __forceinline__ void iter_up_hands(int pass, const CfrParams& p, Iter
     {
 #pragma unroll 1
         for (int c = 0; c < k; ++c) {
-            FV<VPT> R = ldh<VPT>(B.state_row(p.regrets, fc + c), tid), W;
-            if (tracked) W = ldh<VPT>(B.state_row(p.weight_sums, fc + c), tid);
+            FV<VPT> R = ldh_state<VPT>(B.state_row(p.regrets, fc + c), tid), W;
+            if (tracked) W = ldh_state<VPT>(B.state_row(p.weight_sums, fc + c), tid);
             const FV<VPT> Va = ldh<VPT>(B.set_row(set, kRowM + c), tid);
             FV<VPT> rn, wn, rq, wq, dy;
             DivGuard g = guard_begin(d_ok);
@@ -808,8 +835,8 @@ __device__ __forceinline__ void iter_up_hands(int pass, const CfrParams& p, Iter
                 posn.v[i] = fmaxf(rr, 0.0f);
                 psum.v[i] = __fadd_rn(psum.v[i], posn.v[i]);
             }
-            sth<VPT>(B.state_row(p.regrets, fc + c), tid, R);
-            if (tracked) sth<VPT>(B.state_row(p.weight_sums, fc + c), tid, W);
+            sth_state<VPT>(B.state_row(p.regrets, fc + c), tid, R);
+            if (tracked) sth_state<VPT>(B.state_row(p.weight_sums, fc + c), tid, W);
             sth<VPT>(B.set_row(set, kRowM + c), tid, posn);
         }
     }
