@@ -514,7 +514,8 @@ class SteppedSolver(SubgameSolver):
         cfr_evaluator.py:1573-1605).
         graph: replay the iteration passes 1..T-2 from one CUDA graph (`GraphedPass`) instead of
         launching their kernels and the leaf model's one by one; same kernels, same results.  Ignored
-        where the host works between the passes (cfr_avg, running_values, policy_delta)."""
+        where the host works between the passes (cfr_avg, running_values, policy_delta).  The leaf model must
+        be capturable: device work only, the same shapes every pass, no host synchronisation."""
         assert root_beliefs.shape == (self.B, 2, HPAD) and root_beliefs.dtype == torch.float32
         assert root_beliefs.is_contiguous() and root_beliefs.device == self.device
         ws = int(warm_start_iterations)
