@@ -36,7 +36,7 @@ sys.path.insert(0, ROOT)
 # Per-build constants of the iteration kernel from its ncu capture on a small case (592 subgames x 16
 # iterations; summary and command under profiles/): DRAM bytes moved and warp instructions executed
 # per subgame-pass.  Both grow in proportion to the subgame-passes of a launch.
-NCU_DRAM_BYTES_PER_SUBGAME_PASS = 3.15e6
+NCU_DRAM_BYTES_PER_SUBGAME_PASS = 3.07e6
 NCU_WARP_INSTRUCTIONS_PER_SUBGAME_PASS = 0.968e6
 NCU_CAPTURE = "ncu --set full on cfr_iter_kernel, 592 subgames x 16 iterations, scaled by subgame-passes"
 
