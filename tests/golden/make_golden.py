@@ -6,9 +6,10 @@ its `src` directory and P2_REFERENCE_TESTS to its `tests` directory:
     P2_REFERENCE_SRC=<checkout>/src P2_REFERENCE_TESTS=<checkout>/tests \
         python tests/golden/make_golden.py [section ...]
 
-Sections: rules, showdown, unblocked, tree, cfr, chance, turn, training_data (default: all).  The outputs are small
-.npz files that travel with the repository; the test-suite reads only those files, never
-the upstream checkout.
+Sections (default: all): rules, showdown, unblocked, tree, cfr, turn, training_data, warm_start, chance, flop_chance,
+replay, rounds, steps, production, standard, zero_sum, ragged256, cfr_avg, running_values, warm_br, linear,
+policy_head, dataclass_defaults, policy_delta.  The outputs are small .npz files that travel with the repository;
+the test-suite reads only those files, never the upstream checkout.
 """
 from __future__ import annotations
 
