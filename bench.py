@@ -146,7 +146,7 @@ def run_reference_arm(args, rank: int):
     machine; its CPU restatement (validated bit-for-bit against it) is what is timed."""
     if rank != 0:
         return
-    n_roots, iters = 32, 6
+    n_roots, iters = 32, 16
     for _ in range(args.warmup):
         cpu_port_rate(4, 1, SEED)
     rates, secs = [], []
@@ -451,9 +451,9 @@ def finish_gpu_arm(args, rank, world, layout, ms_step, value, clocks, e2e, distr
         }
         line.update(extras)
         if world == 1 and not args.no_cpu_baseline:
-            rate, dt, cores = cpu_port_rate(32, 8, SEED)
+            rate, dt, cores = cpu_port_rate(32, 32, SEED)
             line["cpu_baseline"] = {"value": rate, "unit": "subgame-iterations/s", "cores": cores, "kind": "port",
-                                    "sample": f"32 subgames x 8 iterations ({dt:.1f} s), torch CPU eager restatement "
+                                    "sample": f"32 subgames x 32 iterations ({dt:.1f} s), torch CPU eager restatement "
                                               "of the upstream evaluator"}
         print(json.dumps(line))
     if distributed:
