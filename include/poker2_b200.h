@@ -78,9 +78,13 @@ int p2b_showdown_ev_sorted(const float* b_sorted, const int32_t* c1_sorted, cons
  *
  *  subgames   [num_subgames] 32-byte records {int32 node_begin, n_nodes, n_internal,
  *             table_index; float scale, allowed_prob; uint64 board_mask}
- *  nodes      [rows] 16-byte records {uint8 parent, first_child, n_children, to_act, kind
- *             (0 internal, 1 fold leaf, 2 showdown leaf, 3 other leaf), action, depth,
- *             internal_idx; float v0, v1}, breadth-first per subgame, local indices
+ *  nodes      [rows] 16-byte records {uint16 parent, first_child; uint8 n_children, kind_act
+ *             (bits 0-1 kind: 0 internal, 1 fold leaf, 2 showdown leaf, 3 other leaf; bit 7 the
+ *             player to act; the other bits zero), depth, internal_idx; float v0, v1},
+ *             breadth-first per subgame, local indices.  A subgame has at most 320 nodes (a
+ *             depth-5 tree over {fold, call, two bet sizes, all-in} has at most 273); subgames of
+ *             up to 160 nodes run their iteration passes in the lean kernel, larger ones in the
+ *             general kernel, within the same call
  *  tables     showdown tables from p2b_rank_hands, indexed by table_index
  *  root_beliefs [num_subgames,2,1344] input ranges
  *  regrets, weight_sums (may be NULL), policy_avg, policy (may be NULL): [rows,1344] out
@@ -118,9 +122,9 @@ int p2b_showdown_ev_sorted(const float* b_sorted, const int32_t* c1_sorted, cons
  *             every belief row once per level of the batch-wide tree)
  *  work_counter four int32, zeroed by the call: [0] the queue the thread blocks take subgames
  *             from; [1] status; [2], [3] internal.  Before every launch a checking kernel compares
- *             every subgame's records with the solver's limits (1..160 nodes per subgame, all
+ *             every subgame's records with the solver's limits (1..320 nodes per subgame, all
  *             inside the `rows` rows, 1..6 children per internal node, children stored after their
- *             parent and inside the subgame, internal_idx < max_internal, to_act 0 or 1, root
+ *             parent and inside the subgame, internal_idx < max_internal, unused record bits zero, root
  *             internal, a table for every showdown leaf, a slot for every model leaf).
  *             On a violation status = 1 + the index of an offending subgame and NOTHING is
  *             solved (outputs untouched); otherwise status stays 0
@@ -222,7 +226,7 @@ int p2b_cfr_warm_seed(const void* nodes, int64_t rows, const float* start_policy
  *
  * p2b_tree_count: counts [num_subgames][8] = nodes, internal nodes, leaves valued by a model,
  * showdown leaves, largest child count, overflow flag (more nodes than the solver kernel supports,
- * 160), depth of the tree, 0; level_counts [num_subgames][max_depth+1] nodes per tree level.
+ * 320), depth of the tree, 0; level_counts [num_subgames][max_depth+1] nodes per tree level.
  * p2b_tree_records: given the exclusive prefix sums over the subgames of the node counts
  * (node_begin), of the model-leaf counts (leaf_begin) and, per level, of the level counts offset by
  * the level's start in the upstream level-major order (level_base [num_subgames][max_depth+1]),

@@ -132,7 +132,7 @@ int p2b_cfr_solve(const void* subgames, const void* nodes, int32_t num_subgames,
     P2B_REQUIRE((align & 15) == 0, "all arrays must be 16-byte aligned");
     CfrParams p{};
     p.subgames = static_cast<const SubgameRec*>(subgames);
-    p.nodes = static_cast<const NodeRec*>(nodes);
+    p.nodes = static_cast<const NodeRecPacked*>(nodes);
     p.num_subgames = num_subgames;
     p.tables = tables;
     p.root_beliefs = root_beliefs;
@@ -219,7 +219,7 @@ int p2b_cfr_step(const void* subgames, const void* nodes, int32_t num_subgames, 
     P2B_REQUIRE((align & 15) == 0, "all row arrays must be 16-byte aligned");
     CfrParams p{};
     p.subgames = static_cast<const SubgameRec*>(subgames);
-    p.nodes = static_cast<const NodeRec*>(nodes);
+    p.nodes = static_cast<const NodeRecPacked*>(nodes);
     p.num_subgames = num_subgames;
     p.tables = tables;
     p.root_beliefs = root_beliefs;
@@ -268,7 +268,7 @@ int p2b_cfr_warm_seed(const void* nodes, int64_t rows, const float* start_policy
     if (rows == 0) return P2B_OK;
     P2B_REQUIRE(nodes && start_policy && regrets, "null pointer");
     P2B_REQUIRE(weight > 0.0f, "the weight must be positive");
-    return launch_cfr_warm_seed(static_cast<const NodeRec*>(nodes), rows, start_policy, weight, regrets, weight_sums,
+    return launch_cfr_warm_seed(static_cast<const NodeRecPacked*>(nodes), rows, start_policy, weight, regrets, weight_sums,
                                 (cudaStream_t)stream);
 }
 
@@ -303,7 +303,7 @@ int p2b_cfr_solve_noalloc(const void* subgames, const void* nodes, int32_t num_s
     P2B_REQUIRE((align & 15) == 0, "all arrays must be 16-byte aligned");
     CfrParams p{};
     p.subgames = static_cast<const SubgameRec*>(subgames);
-    p.nodes = static_cast<const NodeRec*>(nodes);
+    p.nodes = static_cast<const NodeRecPacked*>(nodes);
     p.num_subgames = num_subgames;
     p.tables = tables;
     p.root_beliefs = root_beliefs;

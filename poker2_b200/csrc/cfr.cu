@@ -44,7 +44,7 @@ constexpr int kCsRows = 2 + kBankRows;       // rows whose per-card sums are nee
 // ---- shared memory carve-up (bytes) ----
 constexpr int kOffTab = 0;
 constexpr int kOffNodes = kOffTab + kTabBytes;
-constexpr int kOffXs = kOffNodes + kCfrMaxNodes * 16;
+constexpr int kOffXs = kOffNodes + kCfrMaxNodes * (int)sizeof(NodeRec);
 constexpr int kOffPref = kOffXs + kStageRows * P2B_HPAD * 4;
 constexpr int kOffPc = kOffPref + 2 * P2B_HPAD * 4;
 constexpr int kOffCs = kOffPc + 2 * 52 * 52 * 4;
@@ -54,7 +54,7 @@ constexpr int kOffSig = kOffS + kCsRows * 8;
 constexpr int kOffSigB = kOffSig + kCfrMaxNodes * 2 * 4;  // the same sums for the beliefs under the average policy
 constexpr int kOffMisc = kOffSigB + kCfrMaxNodes * 2 * 4;
 constexpr int kOffIlist = kOffMisc + 64;  // node index of every internal node, in node order
-constexpr int kCfrSmem = kOffIlist + ((kCfrMaxNodes + 15) / 16) * 16;
+constexpr int kCfrSmem = kOffIlist + ((kCfrMaxNodes * 2 + 15) / 16) * 16;
 static_assert(kOffXs % 16 == 0 && kOffCs % 8 == 0 && kOffMisc % 16 == 0 && kOffSig % 8 == 0, "alignment");
 
 enum PassMode { kPassInit = 0, kPassIter = 1, kPassFinal = 2 };
@@ -72,7 +72,7 @@ struct Block {
     float* sig;    // [nodes][2] normalisation sums of the node beliefs of the current pass
     float* sigb;   // [nodes][2] the same for the beliefs under the average policy (iteration passes with cfr_avg)
     int* misc;
-    uint8_t* ilist;  // [n_internal] node index of the ii-th internal node
+    uint16_t* ilist;  // [n_internal] node index of the ii-th internal node
     float* fsum;
     // current subgame
     SubgameRec sg;
@@ -1250,7 +1250,7 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
     B.sig = reinterpret_cast<float*>(smem + kOffSig);
     B.sigb = reinterpret_cast<float*>(smem + kOffSigB);
     B.misc = reinterpret_cast<int*>(smem + kOffMisc);
-    B.ilist = smem + kOffIlist;
+    B.ilist = reinterpret_cast<uint16_t*>(smem + kOffIlist);
     B.fsum = reinterpret_cast<float*>(smem + kOffMisc + 16);
     if (threadIdx.x == 0) B.misc[2] = 0;  // unit counter of node_tables
     const int tid = threadIdx.x;
@@ -1272,13 +1272,13 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
         if (B.misc[0] >= p.num_subgames) break;
         const int s = p.queue_order ? p.queue_order[B.misc[0]] : B.misc[0];
         B.sg = p.subgames[s];
+        if (p.large_only && B.sg.n_nodes <= kIterMaxNodes) continue;  // the lean iteration kernel has solved these passes
         // work rows: one set per block, or one per subgame when state is carried between launches
         B.scr = p.scratch + (long long)((p.stepped && !p.scratch_per_block) ? s : (int)blockIdx.x) * p.scratch_stride;
         B.leaf0 = p.leaf_begin ? p.leaf_begin[s] : 0;
         B.sample_pass = p.sample_pass ? p.sample_pass[s] : -2;
         {
-            const uint4* src = reinterpret_cast<const uint4*>(p.nodes + B.sg.node_begin);
-            for (int i = tid; i < B.sg.n_nodes; i += NT) reinterpret_cast<uint4*>(B.nodes)[i] = src[i];
+            for (int i = tid; i < B.sg.n_nodes; i += NT) B.nodes[i] = load_node(p.nodes + B.sg.node_begin + i);
             if (B.sg.table_index >= 0) {
                 const uint4* t = reinterpret_cast<const uint4*>(p.tables + (long long)B.sg.table_index * kTabBytes);
                 for (int i = tid; i < kTabBytes / 16; i += NT) reinterpret_cast<uint4*>(B.tab)[i] = t[i];
@@ -1310,7 +1310,7 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
         __syncthreads();
         for (int i = tid; i < B.sg.n_nodes; i += NT) {
             const NodeRec nd = B.nodes[i];
-            if (nd.kind == kInternal && nd.internal_idx < B.sg.n_internal) B.ilist[nd.internal_idx] = (uint8_t)i;
+            if (nd.kind == kInternal && nd.internal_idx < B.sg.n_internal) B.ilist[nd.internal_idx] = (uint16_t)i;
         }
         __syncthreads();
 
@@ -1410,7 +1410,9 @@ __global__ void __launch_bounds__(kCfrMaxNodes) cfr_validate_kernel(const CfrPar
               (p.rows > 0 && (long long)sg.node_begin + sg.n_nodes > p.rows) ||
               (p.queue_order && (unsigned)p.queue_order[s] >= (unsigned)p.num_subgames);
     if (!bad && i < sg.n_nodes) {
-        const NodeRec nd = p.nodes[sg.node_begin + i];
+        const NodeRecPacked raw = p.nodes[sg.node_begin + i];
+        const NodeRec nd = unpack_node(raw);
+        if (raw.kind_act & 0x7c) bad = 1;  // bits that carry nothing must be zero
         if (nd.kind > kModelLeaf || (nd.kind == kShowdownLeaf && (sg.table_index < 0 || p.tables == nullptr))) bad = 1;
         if (i == 0 && nd.kind != kInternal) bad = 1;
         if (nd.kind == kInternal &&
@@ -1426,7 +1428,7 @@ __global__ void __launch_bounds__(kCfrMaxNodes) cfr_validate_kernel(const CfrPar
     // through a list indexed by it) and n_internal their number
     __shared__ uint8_t s_internal[kCfrMaxNodes];
     const bool in_tree = !bad && i < sg.n_nodes;
-    s_internal[i] = in_tree && p.nodes[sg.node_begin + i].kind == kInternal;
+    s_internal[i] = in_tree && (p.nodes[sg.node_begin + i].kind_act & 3) == kInternal;
     __syncthreads();
     if (in_tree) {
         int before = 0;
@@ -1445,7 +1447,7 @@ __global__ void __launch_bounds__(kCfrMaxNodes) cfr_validate_kernel(const CfrPar
 // holds the instantaneous regrets of the start policy.  Per non-root row: weight = `weight` x
 // mean over the 1326 hands of max(regret, 0) (the sum in the reference row-reduction order),
 // then regrets = start policy x weight and weight sums = weight.  One block per row.
-__global__ void __launch_bounds__(256) cfr_warm_seed_kernel(const NodeRec* __restrict__ nodes, long long rows,
+__global__ void __launch_bounds__(256) cfr_warm_seed_kernel(const NodeRecPacked* __restrict__ nodes, long long rows,
                                                             const float* __restrict__ start_policy, float weight,
                                                             float* __restrict__ regrets, float* __restrict__ weight_sums) {
     __shared__ __align__(16) float pos[P2B_HPAD];
@@ -1497,7 +1499,7 @@ static int dispatch_cfr(const CfrParams& p, int num_blocks, int max_children, cu
     return set_error(P2B_ERR_ARG, "at most %d actions per node are supported, got %d", kCfrMaxChildren, max_children);
 }
 
-int launch_cfr_warm_seed(const NodeRec* nodes, long long rows, const float* start_policy, float weight, float* regrets,
+int launch_cfr_warm_seed(const NodeRecPacked* nodes, long long rows, const float* start_policy, float weight, float* regrets,
                          float* weight_sums, cudaStream_t stream) {
     if (rows <= 0) return P2B_OK;
     long long grid = rows < (long long)sm_count() * 8 ? rows : (long long)sm_count() * 8;
@@ -1629,6 +1631,15 @@ int launch_cfr_solve(const CfrParams& params, int num_blocks, int max_children, 
             if (timed) {
                 cudaEventRecord(timing->stop, stream);
                 timing->recorded = true;
+            }
+            // Subgames with more nodes than the iteration kernel holds in shared memory were skipped by it:
+            // the general kernel runs their iteration passes.  The batch can only contain such a subgame
+            // if the bound below exceeds the limit.
+            if (!rc && (long long)p.max_internal * max_children + 1 > kIterMaxNodes) {
+                rc = clear_counters(q.work_counter, stream);
+                if (rc) return rc;
+                q.large_only = 1;
+                rc = dispatch_cfr(q, num_blocks, max_children, stream);
             }
         } else {
             rc = dispatch_cfr(q, num_blocks, max_children, stream);

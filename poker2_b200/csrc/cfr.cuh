@@ -7,23 +7,55 @@ namespace p2b {
 
 enum NodeKind : uint8_t { kInternal = 0, kFoldLeaf = 1, kShowdownLeaf = 2, kModelLeaf = 3 };
 
-// One public-tree node, 16 bytes.  Nodes of a subgame are stored breadth-first (parents
-// before children, children of a node contiguous in action order); indices are local to
+// One public-tree node as callers hand it in, 16 bytes.  Nodes of a subgame are stored breadth-first
+// (parents before children, children of a node contiguous in action order); indices are local to
 // the subgame.
-struct NodeRec {
-    uint8_t parent;
-    uint8_t first_child;
+struct NodeRecPacked {
+    uint16_t parent;
+    uint16_t first_child;
     uint8_t n_children;
-    uint8_t to_act;
-    uint8_t kind;
-    uint8_t action;
+    uint8_t kind_act;      // bits 0-1: NodeKind, bit 7: player to act
     uint8_t depth;
     uint8_t internal_idx;  // rank of this node among the internal nodes of its subgame (model leaf: rank
                            // among the model leaves of its subgame)
     float v0;              // fold leaf: value of player 0; showdown leaf: chips player 0 can win
     float v1;              // showdown leaf: chips player 1 can win
 };
-static_assert(sizeof(NodeRec) == 16, "NodeRec must be 16 bytes");
+static_assert(sizeof(NodeRecPacked) == 16, "NodeRecPacked must be 16 bytes");
+
+// The same node as the kernels keep it in shared memory.
+struct NodeRec {
+    uint16_t parent;
+    uint16_t first_child;
+    uint8_t n_children;
+    uint8_t to_act;
+    uint8_t kind;
+    uint8_t depth;
+    uint8_t internal_idx;
+    float v0;
+    float v1;
+};
+static_assert(sizeof(NodeRec) == 20, "NodeRec is five words");
+
+__host__ __device__ __forceinline__ NodeRec unpack_node(const NodeRecPacked& r) {
+    NodeRec n;
+    n.parent = r.parent;
+    n.first_child = r.first_child;
+    n.n_children = r.n_children;
+    n.to_act = r.kind_act >> 7;
+    n.kind = r.kind_act & 3;
+    n.depth = r.depth;
+    n.internal_idx = r.internal_idx;
+    n.v0 = r.v0;
+    n.v1 = r.v1;
+    return n;
+}
+__device__ __forceinline__ NodeRec load_node(const NodeRecPacked* p) {  // one 16-byte load
+    const uint4 w = *reinterpret_cast<const uint4*>(p);
+    NodeRecPacked r;
+    *reinterpret_cast<uint4*>(&r) = w;
+    return unpack_node(r);
+}
 
 struct SubgameRec {  // 32 bytes
     int32_t node_begin;   // first row of the subgame in the [rows][HPAD] state arrays
@@ -48,12 +80,13 @@ struct IterScalars {  // 32 bytes
 };
 
 constexpr int kCfrThreads = 672;  // 672 threads x 2 hands cover the 1344-float padded row
-constexpr int kCfrMaxNodes = 160;
+constexpr int kCfrMaxNodes = 320;   // nodes of one subgame (a depth-5 tree over {fold, call, two bets, all-in} has at most 273)
+constexpr int kIterMaxNodes = 160;  // what the lean iteration kernel holds; larger subgames stay in the general kernel
 constexpr int kCfrMaxChildren = 6;
 
 struct CfrParams {
     const SubgameRec* subgames;
-    const NodeRec* nodes;        // indexed by node_begin + local index
+    const NodeRecPacked* nodes;  // indexed by node_begin + local index
     int32_t num_subgames;
     const unsigned char* tables; // [*, kTabBytes] board tables
     const ComboTable* combos;    // filled in by the launcher
@@ -115,6 +148,7 @@ struct CfrParams {
     int32_t leaf_slots;          // model-leaf slots of leaf_beliefs / leaf_values
     // ---- a one-launch solve split over several launches (start pass, iteration passes, final pass)
     int32_t scratch_per_block;   // stepped launch whose work rows are not carried: one set per block
+    int32_t large_only;          // general kernel: skip the subgames the lean iteration kernel holds (it skips the others)
 };
 
 // floats of scratch one block needs: per internal node reach[2], average reach[2], values[2]
@@ -132,7 +166,7 @@ int cfr_iteration_timing(int enable);
 int cfr_iteration_ms(float* ms);
 int cfr_default_blocks();
 int launch_cfr_solve_static(const CfrParams& p, int max_children, cudaStream_t stream);
-int launch_cfr_warm_seed(const NodeRec* nodes, long long rows, const float* start_policy, float weight, float* regrets,
+int launch_cfr_warm_seed(const NodeRecPacked* nodes, long long rows, const float* start_policy, float weight, float* regrets,
                          float* weight_sums, cudaStream_t stream);
 long long cfr_static_scratch_floats();
 int cfr_static_status(int32_t* host_status, cudaStream_t stream);

@@ -63,13 +63,13 @@ constexpr int kTsBytes = kTsTot + 2 * 64 * 4;
 // ---- shared memory carve-up (bytes) ----
 constexpr int kOffTab = 0;
 constexpr int kOffNodes = kOffTab + kTabBytes;
-constexpr int kOffStage = kOffNodes + kCfrMaxNodes * 16;               // float [kSets][kSetRows][HPAD]
+constexpr int kOffStage = kOffNodes + kIterMaxNodes * (int)sizeof(NodeRec);  // float [kSets][kSetRows][HPAD]
 constexpr int kOffTs = kOffStage + kSets * kSetRows * P2B_HPAD * 4;    // kSets table sets, right behind the rows
 constexpr int kOffSig = kOffTs + kSets * kTsBytes;                     // float [nodes][2]
-constexpr int kOffRsrc = kOffSig + kCfrMaxNodes * 2 * 4;               // uint8 [nodes][2]
-constexpr int kOffIlist = kOffRsrc + kCfrMaxNodes * 2;                 // uint8 [internal nodes]
-constexpr int kOffSdc = kOffIlist + kCfrMaxNodes;                      // uint8 [internal nodes]
-constexpr int kOffMisc = kOffSdc + kCfrMaxNodes;
+constexpr int kOffRsrc = kOffSig + kIterMaxNodes * 2 * 4;              // uint8 [nodes][2]
+constexpr int kOffIlist = kOffRsrc + kIterMaxNodes * 2;                // uint8 [internal nodes]
+constexpr int kOffSdc = kOffIlist + kIterMaxNodes;                     // uint8 [internal nodes]
+constexpr int kOffMisc = kOffSdc + kIterMaxNodes;
 constexpr int kOffCsIdx = kOffMisc + 64;                               // uint16 [52][52] hand index of the e-th hand holding a card
 constexpr int kIterSmem = kOffCsIdx + 52 * 52 * 2;
 static_assert(kOffStage % 16 == 0 && kOffTs % 16 == 0 && kTsBytes % 16 == 0 && kOffSig % 16 == 0 && kOffMisc % 16 == 0,
@@ -914,10 +914,10 @@ __global__ void __launch_bounds__(kNT, kCtas) cfr_iter_kernel(const CfrParams p)
         if (B.misc[0] >= p.num_subgames) break;
         const int s = p.queue_order ? p.queue_order[B.misc[0]] : B.misc[0];
         B.sg = p.subgames[s];
+        if (B.sg.n_nodes > kIterMaxNodes) continue;  // too large for this kernel's tables: the general kernel runs its passes
         B.sample_pass = p.sample_pass ? p.sample_pass[s] : -2;
         {
-            const uint4* src = reinterpret_cast<const uint4*>(p.nodes + B.sg.node_begin);
-            for (int i = rtid; i < B.sg.n_nodes; i += NT) reinterpret_cast<uint4*>(B.nodes)[i] = src[i];
+            for (int i = rtid; i < B.sg.n_nodes; i += NT) B.nodes[i] = load_node(p.nodes + B.sg.node_begin + i);
             if (B.sg.table_index >= 0) {
                 const uint4* t = reinterpret_cast<const uint4*>(p.tables + (long long)B.sg.table_index * kTabBytes);
                 for (int i = rtid; i < kTabBytes / 16; i += NT) reinterpret_cast<uint4*>(B.tab)[i] = t[i];
@@ -1026,7 +1026,7 @@ __global__ void __launch_bounds__(kNT, kCtas) cfr_iter_kernel(const CfrParams p)
 // floats of work rows the blocks of the iteration kernel on one SM need
 long long cfr_iter_scratch_floats(int max_internal, int max_children) {
     long long nodes = (long long)max_internal * max_children + 1;
-    if (nodes > kCfrMaxNodes) nodes = kCfrMaxNodes;
+    if (nodes > kIterMaxNodes) nodes = kIterMaxNodes;
     return kCtas * ((long long)max_internal * 4 + nodes) * P2B_HPAD;
 }
 

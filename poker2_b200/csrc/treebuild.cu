@@ -19,7 +19,7 @@ int sm_count();
 
 namespace {
 
-constexpr int kTreeWarps = 4;          // subgames per block
+constexpr int kTreeWarps = 2;          // subgames per block (two node tables of kTreeMaxNodes states in static shared memory)
 constexpr int kTreeMaxNodes = kCfrMaxNodes;  // what the solver kernel holds in shared memory
 constexpr int kTreeMaxDepth = 63;
 constexpr int kTreeMaxBetBins = 13;    // + fold, check/call, all-in <= 16 actions
@@ -56,7 +56,7 @@ struct TreeParams {
     const int32_t* leaf_begin;  // [B]
     const int64_t* level_base;  // [B][max_depth + 1] level-major index of the subgame's first node of each level
     SubgameRec* subgames;
-    NodeRec* nodes;
+    NodeRecPacked* nodes;
     int64_t* to_level_major;  // [rows]
     int64_t* model_rows;      // [model leaves]
     int32_t* node_state;      // [rows][8] or null: pot, stack0, stack1, start0, start1, street, to_act, done
@@ -65,7 +65,7 @@ struct TreeParams {
 template <bool EMIT>
 __global__ void __launch_bounds__(kTreeWarps * 32) tree_build_kernel(const TreeParams P) {
     __shared__ BetState s_state[kTreeWarps][kTreeMaxNodes];
-    __shared__ uint32_t s_meta[kTreeWarps][kTreeMaxNodes];  // parent | action << 8 | depth << 16 (action 255: root)
+    __shared__ uint32_t s_meta[kTreeWarps][kTreeMaxNodes];  // parent | action << 12 | depth << 20 (action 255: root)
     __shared__ float s_reward[kTreeWarps][kTreeMaxNodes];
     __shared__ int32_t s_level[kTreeWarps][kTreeMaxDepth + 1];
     const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(kTreeWarps * 32) tree_build_kernel(const TreeP
         r.small = (uint32_t)root.to_act | ((uint32_t)root.flags << 8) | ((uint32_t)root.street << 16) | ((uint32_t)root.raises << 24);
         r.actions_this_round = root.actions_this_round;
         st[0] = r;
-        meta[0] = 0u | (255u << 8);
+        meta[0] = 0u | (255u << 12);
         reward[0] = 0.0f;
     }
     __syncwarp();
@@ -96,7 +96,7 @@ __global__ void __launch_bounds__(kTreeWarps * 32) tree_build_kernel(const TreeP
     for (int j = 0; j < n; ++j) {
         const BetState cur = st[j];
         const uint32_t m = meta[j];
-        const int parent = m & 255, action = (m >> 8) & 255, depth = (m >> 16) & 255;
+        const int parent = m & 4095, action = (m >> 12) & 255, depth = (m >> 20) & 255;
         const int me = cur.small & 1, opp = 1 - me;
         const int flags = (cur.small >> 8) & 255, street = (cur.small >> 16) & 255, raises = cur.small >> 24;
         const bool done = flags & 4;
@@ -170,7 +170,7 @@ __global__ void __launch_bounds__(kTreeWarps * 32) tree_build_kernel(const TreeP
             }
             nx.small = (uint32_t)nto_act | ((uint32_t)nflags << 8) | ((uint32_t)nstreet << 16) | ((uint32_t)nraises << 24);
             st[idx] = nx;
-            meta[idx] = (uint32_t)j | ((uint32_t)lane << 8) | ((uint32_t)(depth + 1) << 16);
+            meta[idx] = (uint32_t)j | ((uint32_t)lane << 12) | ((uint32_t)(depth + 1) << 20);
             reward[idx] = rew;
         }
         // ---- this node's record ----
@@ -178,13 +178,11 @@ __global__ void __launch_bounds__(kTreeWarps * 32) tree_build_kernel(const TreeP
         const int kind = k > 0 ? 0 : (is_fold ? 1 : (street == 4 ? 2 : 3));
         const int rank_in_level = level[depth];
         if (EMIT && lane == 0) {
-            NodeRec rec;
-            rec.parent = (uint8_t)parent;
-            rec.first_child = (uint8_t)(k > 0 ? n : 0);
+            NodeRecPacked rec;
+            rec.parent = (uint16_t)parent;
+            rec.first_child = (uint16_t)(k > 0 ? n : 0);
             rec.n_children = (uint8_t)k;
-            rec.to_act = (uint8_t)me;
-            rec.kind = (uint8_t)kind;
-            rec.action = (uint8_t)(action == 255 ? 0 : action);
+            rec.kind_act = (uint8_t)(kind | (me << 7));
             rec.depth = (uint8_t)depth;
             rec.internal_idx = (uint8_t)(kind == 3 ? n_model : n_internal);
             const float pot0 = (float)(cur.stack[0] + cur.pot - root.start0);
@@ -293,7 +291,7 @@ int p2b_tree_records(const void* roots, const int64_t* boards, int32_t board_wid
     P.leaf_begin = leaf_begin;
     P.level_base = level_base;
     P.subgames = static_cast<SubgameRec*>(subgames);
-    P.nodes = static_cast<NodeRec*>(nodes);
+    P.nodes = static_cast<NodeRecPacked*>(nodes);
     P.to_level_major = to_level_major;
     P.model_rows = model_rows;
     P.node_state = node_state;

@@ -19,17 +19,26 @@ from .showdown import BoardTables
 
 HPAD = 1344
 NUM_HANDS = 1326
-MAX_NODES = 160
+MAX_NODES = 320  # nodes of one subgame (general kernel); the lean iteration kernel takes those of up to 160
 MAX_CHILDREN = 6
 
-NODE_DTYPE = np.dtype([("parent", "u1"), ("first_child", "u1"), ("n_children", "u1"), ("to_act", "u1"),
-                       ("kind", "u1"), ("action", "u1"), ("depth", "u1"), ("internal_idx", "u1"),
-                       ("v0", "<f4"), ("v1", "<f4")])
+NODE_DTYPE = np.dtype([("parent", "<u2"), ("first_child", "<u2"), ("n_children", "u1"), ("kind_act", "u1"),
+                       ("depth", "u1"), ("internal_idx", "u1"), ("v0", "<f4"), ("v1", "<f4")])
 SUBGAME_DTYPE = np.dtype([("node_begin", "<i4"), ("n_nodes", "<i4"), ("n_internal", "<i4"), ("table_index", "<i4"),
                           ("scale", "<f4"), ("allowed_prob", "<f4"), ("board_mask", "<u8")])
 SCALAR_DTYPE = np.dtype([("num_pos", "<f4"), ("den_pos", "<f4"), ("num_neg", "<f4"), ("den_neg", "<f4"),
                          ("mix_old", "<f4"), ("mix_new", "<f4"), ("mix_total", "<f4"), ("do_mix", "<i4")])
 assert NODE_DTYPE.itemsize == 16 and SUBGAME_DTYPE.itemsize == 32 and SCALAR_DTYPE.itemsize == 32
+
+
+def node_kind(records):
+    """Kind of node records (`tree.KIND_*`): bits 0-1 of the `kind_act` byte."""
+    return records["kind_act"] & 3
+
+
+def node_to_act(records):
+    """Player to act at node records: bit 7 of the `kind_act` byte."""
+    return records["kind_act"] >> 7
 
 
 def iteration_scalars(iterations: int, *, cfr_type: str = "discounted", alpha: float = 1.5, beta: float = 0.0,
@@ -155,8 +164,8 @@ def device_layout(trees: ptree.PublicTrees, boards: np.ndarray) -> DeviceTreeLay
     parent_local = np.where(trees.parent_index >= 0, local[np.maximum(trees.parent_index, 0)], 0)
     first_child = np.where(internal, local[np.minimum(trees.child_offsets, M - 1)], 0)
     rec["parent"], rec["first_child"] = parent_local, first_child
-    rec["n_children"], rec["to_act"], rec["kind"] = trees.child_count, st.to_act, kind
-    rec["action"] = np.maximum(trees.action_from_parent, 0)
+    rec["n_children"] = trees.child_count
+    rec["kind_act"] = kind | (st.to_act.astype(np.uint8) << 7)
     rec["depth"] = trees.depth_of
     rec["v0"] = np.where(fold, trees.fold_value, trees.showdown_potential[:, 0].astype(np.float32))
     rec["v1"] = trees.showdown_potential[:, 1].astype(np.float32)
@@ -168,7 +177,7 @@ def device_layout(trees: ptree.PublicTrees, boards: np.ndarray) -> DeviceTreeLay
     rec["internal_idx"] = csum - csum[node_begin[root_sorted]]
     n_internal = np.bincount(trees.root_of, weights=internal, minlength=B).astype(np.int64)
     # model leaves: rank among the model leaves of the subgame, slots in row order
-    is_model = rec["kind"] == ptree.KIND_MODEL
+    is_model = node_kind(rec) == ptree.KIND_MODEL
     mdl = is_model.astype(np.int64)
     msum = np.cumsum(mdl) - mdl
     rec["internal_idx"] = np.where(is_model, msum - msum[node_begin[root_sorted]], rec["internal_idx"])
@@ -644,8 +653,8 @@ class SteppedSolver(SubgameSolver):
         old, new, total = (torch.tensor(float(row[k]), device=dev, dtype=torch.float32)
                            for k in ("mix_old", "mix_new", "mix_total"))
         if self._terminal is None:
-            nodes = self.nodes.view(torch.uint8).reshape(-1, 16)
-            self._terminal = ((nodes[:, 4] == 1) | (nodes[:, 4] == 2)).to(torch.uint8).contiguous()
+            kind = self.nodes.view(torch.uint8).reshape(-1, 16)[:, 5] & 3  # the kind_act byte of every record
+            self._terminal = ((kind == 1) | (kind == 2)).to(torch.uint8).contiguous()
         out = torch.empty_like(self._running)
         F.mix_zero_sum_rows(self._running, self.values_avg, self.beliefs_avg, self._terminal, old, new, total, out,
                             divide=True, mode=2 if enforce_zero_sum else 0)
@@ -796,7 +805,8 @@ def solve_subgames(boards, ranges, pot, stacks, *, iterations: int, bet_bins=(0.
                    gamma: float = 2.0, dcfr_delay: int = 0, cfr_plus: bool = False, device=None,
                    keep_policy: bool = False, keep_node_values: bool = False, track_weight_sums: bool = True,
                    exploitability: bool = False, device_tree: bool = False, enforce_zero_sum: bool = False,
-                   alpha_final=None, beta_final=None, gamma_final=None, cfr_avg: bool = False):
+                   alpha_final=None, beta_final=None, gamma_final=None, cfr_avg: bool = False,
+                   lean_iterations: bool = True):
     """Solves a batch of river subgames: boards [B,5] card ids, ranges [B,2,1326] fp32,
     pot [B] and stacks [B] or [B,2] in chips.  Returns (SolveResult, PublicTrees); with
     `device_tree` the trees are expanded on the GPU (`device_tree.build_device_layout`), no host
@@ -815,7 +825,8 @@ def solve_subgames(boards, ranges, pot, stacks, *, iterations: int, bet_bins=(0.
         trees = ptree.build_trees(roots, list(bet_bins), max_depth, bb=bb, max_raises=max_raises)
         layout = device_layout(trees, boards_np)
     solver = SubgameSolver(layout, torch.from_numpy(boards_np), device, track_weight_sums=track_weight_sums,
-                           keep_policy=keep_policy, keep_node_values=keep_node_values, exploitability=exploitability)
+                           keep_policy=keep_policy, keep_node_values=keep_node_values, exploitability=exploitability,
+                           lean_iterations=lean_iterations)
     rb = pad_rows(torch.as_tensor(ranges, dtype=torch.float32).to(device)).contiguous()
     scal = iteration_scalars(iterations, cfr_type=cfr_type, alpha=alpha, beta=beta, gamma=gamma, dcfr_delay=dcfr_delay,
                              alpha_final=alpha_final, beta_final=beta_final, gamma_final=gamma_final)

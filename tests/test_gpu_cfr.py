@@ -181,7 +181,7 @@ def test_malformed_subgame_is_reported_and_nothing_runs(cuda_device, golden_dir)
     layout2 = solver.device_layout(trees, z["boards"].astype(np.int64))
     victim2 = 1
     lo, n = int(layout2.subgames[victim2]["node_begin"]), int(layout2.subgames[victim2]["n_nodes"])
-    internal = [i for i in range(lo, lo + n) if layout2.nodes[i]["kind"] == 0]
+    internal = [i for i in range(lo, lo + n) if solver.node_kind(layout2.nodes[i]) == 0]
     layout2.nodes[internal[2]]["internal_idx"] = layout2.nodes[internal[1]]["internal_idx"]
     sv2 = solver.SubgameSolver(layout2, boards, cuda_device)
     sv2.root_values.fill_(-7.0)

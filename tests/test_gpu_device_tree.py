@@ -83,7 +83,7 @@ def test_device_tree_equals_host_tree(cuda_device, case):
 def test_device_tree_reports_oversized_subgames(cuda_device):
     roots = ptree.root_states(np.array([100, 100]), np.array([20000, 400]))
     boards = random_boards(np.random.default_rng(0), 2, 5)
-    with pytest.raises(ValueError, match="more than 160 nodes"):
+    with pytest.raises(ValueError, match="more than 320 nodes"):
         device_tree.build_device_layout(roots, boards, [0.25, 0.5, 1.0], 12, device=cuda_device)
 
 

@@ -125,10 +125,10 @@ def test_sample_leaves_matches_upstream(golden_dir):
 
 
 def test_layout_rejects_trees_beyond_the_kernel_limits():
-    """Host-side guard: subgames with more than 160 nodes are refused before any launch."""
+    """Host-side guard: subgames with more nodes than the kernels hold are refused before any launch."""
     from poker2_b200 import solver
 
-    roots = ptree.root_states(np.array([100]), np.array([4000]), min_raise=2)
+    roots = ptree.root_states(np.array([100]), np.array([8000]), min_raise=2)
     big = ptree.build_trees(roots, [0.25, 0.5, 1.0], 10, bb=2)  # three bet sizes, no raise cap
     assert big.total_nodes > solver.MAX_NODES
     with pytest.raises(ValueError, match="nodes"):
@@ -138,7 +138,7 @@ def test_layout_rejects_trees_beyond_the_kernel_limits():
     assert layout.rows == small.total_nodes and layout.num_model_leaves == 0
     # one root, ragged batch of one: offsets and records are consistent
     assert layout.subgames[0]["n_nodes"] == small.total_nodes
-    assert int(layout.nodes["kind"][0]) == ptree.KIND_INTERNAL
+    assert int(solver.node_kind(layout.nodes)[0]) == ptree.KIND_INTERNAL and int(solver.node_to_act(layout.nodes)[0]) in (0, 1)
 
 
 def test_cfr_oracle_warm_start_bit_exact(golden_dir):

@@ -102,7 +102,7 @@ def test_noalloc_entry_reports_a_refused_batch(cuda_device):
     trees = ptree.build_trees(ptree.root_states(pot.numpy(), stack.numpy()), [0.5, 1.0], 8, max_raises=2)
     layout = solver.device_layout(trees, boards.numpy())
     victim = 4
-    layout.nodes[int(layout.subgames[victim]["node_begin"])]["to_act"] = 3  # no such player
+    layout.nodes[int(layout.subgames[victim]["node_begin"])]["first_child"] = 0  # the root as its own child
     sv = solver.SubgameSolver(layout, boards, cuda_device)
     scal = solver.iteration_scalars(3)
     scal_dev = torch.from_numpy(scal.view(np.uint8).reshape(3, 32).copy()).to(cuda_device)
