@@ -84,7 +84,8 @@ int p2b_showdown_ev_sorted(const float* b_sorted, const int32_t* c1_sorted, cons
  *             breadth-first per subgame, local indices.  A subgame has at most 320 nodes (a
  *             depth-5 tree over {fold, call, two bet sizes, all-in} has at most 273); subgames of
  *             up to 160 nodes run their iteration passes in the lean kernel, larger ones in the
- *             general kernel, within the same call
+ *             general kernel, within the same call; max_children <= 8, and a batch with more than
+ *             6 children at some node runs every pass in the general kernel
  *  tables     showdown tables from p2b_rank_hands, indexed by table_index
  *  root_beliefs [num_subgames,2,1344] input ranges
  *  regrets, weight_sums (may be NULL), policy_avg, policy (may be NULL): [rows,1344] out
@@ -123,7 +124,7 @@ int p2b_showdown_ev_sorted(const float* b_sorted, const int32_t* c1_sorted, cons
  *  work_counter four int32, zeroed by the call: [0] the queue the thread blocks take subgames
  *             from; [1] status; [2], [3] internal.  Before every launch a checking kernel compares
  *             every subgame's records with the solver's limits (1..320 nodes per subgame, all
- *             inside the `rows` rows, 1..6 children per internal node, children stored after their
+ *             inside the `rows` rows, 1..8 children per internal node, children stored after their
  *             parent and inside the subgame, internal_idx < max_internal, unused record bits zero, root
  *             internal, a table for every showdown leaf, a slot for every model leaf).
  *             On a violation status = 1 + the index of an offending subgame and NOTHING is

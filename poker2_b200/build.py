@@ -9,7 +9,7 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libpoker2_b200.so")
-SOURCES = ["common.cu", "rank7.cu", "showdown.cu", "cfr.cu", "cfr_iter.cu", "stepops.cu", "chance.cu", "treebuild.cu", "selftest.cu", "api.cu"]
+SOURCES = ["common.cu", "rank7.cu", "showdown.cu", "cfr.cu", "cfr_wide.cu", "cfr_iter.cu", "stepops.cu", "chance.cu", "treebuild.cu", "selftest.cu", "api.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -52,8 +52,12 @@ def build(force: bool = False, verbose: bool = False) -> str:
         obj = os.path.join(build_dir, src.replace(".cu", ".o"))
         objs.append(obj)
         src_path = os.path.join(CSRC, src)
-        # an object is reused when it is newer than its source and than every header
-        if not force and os.path.exists(obj) and os.path.getmtime(obj) > max(os.path.getmtime(src_path), newest_header):
+        # an object is reused when it is newer than its source (cfr_wide.cu is cfr.cu compiled a second time)
+        # and than every header
+        newest_source = os.path.getmtime(src_path)
+        if src == "cfr_wide.cu":
+            newest_source = max(newest_source, os.path.getmtime(os.path.join(CSRC, "cfr.cu")))
+        if not force and os.path.exists(obj) and os.path.getmtime(obj) > max(newest_source, newest_header):
             continue
         cmd = [nvcc, *NVCC_FLAGS, "-c", src_path, "-o", obj]
         if verbose:

@@ -36,7 +36,17 @@ namespace p2b {
 
 namespace {
 
-constexpr int kBankRows = kCfrMaxChildren;  // child rows staged per node in the top-down sweep
+// This file is compiled twice: as it is, for trees of up to kIterMaxChildren actions per node (the kernel every
+// shipped configuration runs), and from cfr_wide.cu with P2B_CFR_WIDE defined, which yields only the kernel
+// for up to kCfrMaxChildren actions and its launcher.  Node bodies are unrolled per child count, so the two
+// widest counts cost most of the compile time and stack frame; they stay out of the common kernel.
+#ifdef P2B_CFR_WIDE
+constexpr bool kWide = true;
+#else
+constexpr bool kWide = false;
+#endif
+constexpr int kMaxC = kWide ? kCfrMaxChildren : kIterMaxChildren;
+constexpr int kBankRows = kMaxC;  // child rows staged per node in the top-down sweep
 constexpr int kStageRows = 2 + 2 * kBankRows;  // top-down: two banks of child rows; bottom-up: 2 belief rows,
                                                // one marginal row and one leaf-belief row per child
 constexpr int kCsRows = 2 + kBankRows;       // rows whose per-card sums are needed at one node
@@ -376,7 +386,15 @@ __device__ __forceinline__ void dispatch_children(int k, Body&& body) {
         case 3: body(ChildCount<3>{}); break;
         case 4: body(ChildCount<4>{}); break;
         case 5: body(ChildCount<5>{}); break;
-        default: body(ChildCount<kCfrMaxChildren>{}); break;
+        default:
+            if constexpr (kMaxC > 6) {
+                if (k == 6) body(ChildCount<6>{});
+                else if (k == 7) body(ChildCount<7>{});
+                else body(ChildCount<kMaxC>{});
+            } else {
+                body(ChildCount<kMaxC>{});
+            }
+            break;
     }
 }
 
@@ -1340,10 +1358,15 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
                 // a child's row of the player who did not act is the root's row; so is its sum
                 if (tid < 2) B.sig[tid] = B.sigb[tid] = B.fsum[tid];
             }
-            if (mode == kPassIter && plain) {
-                sweep_down<VPT, MAXC, kPassIter, true>(mode, pass, p, B, hi, prior, tid);
-                sweep_up<VPT, MAXC, kPassIter, true>(mode, pass, p, B, hi, prior, root_b, s, tid);
-            } else {  // start and final passes; every pass of a stepped solve or one with optional outputs
+            bool done_plain = false;
+            if constexpr (!kWide) {
+                if (mode == kPassIter && plain) {
+                    sweep_down<VPT, MAXC, kPassIter, true>(mode, pass, p, B, hi, prior, tid);
+                    sweep_up<VPT, MAXC, kPassIter, true>(mode, pass, p, B, hi, prior, root_b, s, tid);
+                    done_plain = true;
+                }
+            }
+            if (!done_plain) {  // start and final passes; every pass of a stepped solve or one with optional outputs
                 if (run_down) sweep_down<VPT, MAXC, -1, false>(mode, pass, p, B, hi, prior, tid);
                 if (run_up) sweep_up<VPT, MAXC, -1, false>(mode, pass, p, B, hi, prior, root_b, s, tid);
             }
@@ -1398,6 +1421,7 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
     }
 }
 
+#ifndef P2B_CFR_WIDE
 // Checks every subgame's records against the solver kernels' limits before they run: a
 // malformed tree would make them index shared memory or the work rows out of range.  One block
 // per subgame, one thread per node.  On a violation the status word (work_counter[1]) receives
@@ -1472,16 +1496,13 @@ __global__ void __launch_bounds__(256) cfr_warm_seed_kernel(const NodeRecPacked*
     }
 }
 
+#endif  // !P2B_CFR_WIDE
+
 template <int VPT, int MAXC>
-int launch_variant(const CfrParams& p, int num_blocks, cudaStream_t stream) {
+int launch_kernel(const CfrParams& p, int num_blocks, cudaStream_t stream) {
     int rc = check_cuda(cudaFuncSetAttribute(cfr_solve_kernel<VPT, MAXC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              kCfrSmem),
                         "cfr_solve_kernel shared-memory attribute");
-    if (rc) return rc;
-    // every launch is checked, also the later steps of a stepped solve: the launcher has cleared the
-    // status word and the queue, and the kernel must not walk records the check refuses
-    cfr_validate_kernel<<<p.num_subgames, kCfrMaxNodes, 0, stream>>>(p);
-    rc = check_cuda(cudaGetLastError(), "cfr_validate_kernel");
     if (rc) return rc;
     cfr_solve_kernel<VPT, MAXC><<<num_blocks, CfrThreads<VPT>::value, kCfrSmem, stream>>>(p);
     return check_cuda(cudaGetLastError(), "cfr_solve_kernel");
@@ -1489,14 +1510,32 @@ int launch_variant(const CfrParams& p, int num_blocks, cudaStream_t stream) {
 
 }  // namespace
 
+#ifdef P2B_CFR_WIDE
+// the launcher of the kernel for up to kCfrMaxChildren actions per node (the record check runs before it)
+int launch_cfr_wide(const CfrParams& p, int num_blocks, cudaStream_t stream) {
+    return launch_kernel<2, kMaxC>(p, num_blocks, stream);
+}
+
+}  // namespace p2b
+#else
+
+int launch_cfr_wide(const CfrParams& p, int num_blocks, cudaStream_t stream);  // cfr_wide.cu
+
 int sm_count();
 
 int cfr_default_blocks() { return sm_count(); }
 
 static int dispatch_cfr(const CfrParams& p, int num_blocks, int max_children, cudaStream_t stream) {
-    // one kernel serves every child count: node bodies are specialised per count inside it
-    if (max_children <= kCfrMaxChildren) return launch_variant<2, kCfrMaxChildren>(p, num_blocks, stream);
-    return set_error(P2B_ERR_ARG, "at most %d actions per node are supported, got %d", kCfrMaxChildren, max_children);
+    if (max_children > kCfrMaxChildren)
+        return set_error(P2B_ERR_ARG, "at most %d actions per node are supported, got %d", kCfrMaxChildren, max_children);
+    // every launch is checked, also the later steps of a stepped solve: the launcher has cleared the
+    // status word and the queue, and the kernel must not walk records the check refuses
+    cfr_validate_kernel<<<p.num_subgames, kCfrMaxNodes, 0, stream>>>(p);
+    const int rc = check_cuda(cudaGetLastError(), "cfr_validate_kernel");
+    if (rc) return rc;
+    // one kernel serves every child count up to its width: node bodies are specialised per count inside it
+    if (max_children <= kMaxC) return launch_kernel<2, kMaxC>(p, num_blocks, stream);
+    return launch_cfr_wide(p, num_blocks, stream);
 }
 
 int launch_cfr_warm_seed(const NodeRecPacked* nodes, long long rows, const float* start_policy, float weight, float* regrets,
@@ -1573,7 +1612,7 @@ int launch_cfr_solve(const CfrParams& params, int num_blocks, int max_children, 
     long long per_block = cfr_scratch_floats(p.max_internal);
     const long long iter_block = cfr_iter_scratch_floats(p.max_internal, max_children);
     if (iter_block > per_block) per_block = iter_block;
-    if (!(plain && fast_scratch && max_children <= kCfrMaxChildren)) {
+    if (!(plain && fast_scratch && max_children <= kIterMaxChildren)) {
         if (p.warm_weight > 0.0f) {
             // the general kernel in two launches around the seeding: start pass, then every other pass
             if (p.stepped) return set_error(P2B_ERR_ARG, "a stepped solve seeds its warm start itself");
@@ -1743,3 +1782,4 @@ int cfr_static_status(int32_t* host_status, cudaStream_t stream) {
 }
 
 }  // namespace p2b
+#endif  // P2B_CFR_WIDE

@@ -82,7 +82,8 @@ struct IterScalars {  // 32 bytes
 constexpr int kCfrThreads = 672;  // 672 threads x 2 hands cover the 1344-float padded row
 constexpr int kCfrMaxNodes = 320;   // nodes of one subgame (a depth-5 tree over {fold, call, two bets, all-in} has at most 273)
 constexpr int kIterMaxNodes = 160;  // what the lean iteration kernel holds; larger subgames stay in the general kernel
-constexpr int kCfrMaxChildren = 6;
+constexpr int kCfrMaxChildren = 8;   // actions per node (fold, call, five bet sizes, all-in: the upstream dataclass default)
+constexpr int kIterMaxChildren = 6;  // the lean iteration kernel's staging rows; batches with more stay in the general kernel
 
 struct CfrParams {
     const SubgameRec* subgames;

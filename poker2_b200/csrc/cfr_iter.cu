@@ -46,7 +46,7 @@ constexpr int kNT = (kHT + 31) / 32 * 32;     // threads per block: whole warps;
                                               // per-hand work (same loads, same values stored) and share the cross-hand units
 constexpr bool kDouble = kCtas == 1;  // staged rows and tables double buffered, units one node ahead
 constexpr int kSets = kDouble ? 2 : 1;
-constexpr int kK = kCfrMaxChildren;
+constexpr int kK = kIterMaxChildren;
 constexpr int kSetRows = 2 + kK + 1;  // beliefs of the acting / the other player, one row per child, one leaf row
 constexpr int kRowM = 2;
 constexpr int kRowLeaf = 2 + kK;

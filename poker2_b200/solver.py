@@ -20,7 +20,7 @@ from .showdown import BoardTables
 HPAD = 1344
 NUM_HANDS = 1326
 MAX_NODES = 320  # nodes of one subgame (general kernel); the lean iteration kernel takes those of up to 160
-MAX_CHILDREN = 6
+MAX_CHILDREN = 8  # actions per node (general kernel); batches of up to 6 run their iteration passes in the lean kernel
 
 NODE_DTYPE = np.dtype([("parent", "<u2"), ("first_child", "<u2"), ("n_children", "u1"), ("kind_act", "u1"),
                        ("depth", "u1"), ("internal_idx", "u1"), ("v0", "<f4"), ("v1", "<f4")])

@@ -91,7 +91,7 @@ def test_device_tree_reports_too_many_actions(cuda_device):
     roots = ptree.root_states(np.array([100]), np.array([5000]))
     boards = random_boards(np.random.default_rng(0), 1, 5)
     with pytest.raises(ValueError, match="actions per node"):
-        device_tree.build_device_layout(roots, boards, [0.25, 0.5, 0.75, 1.0, 1.5], 1, device=cuda_device)
+        device_tree.build_device_layout(roots, boards, [0.2, 0.3, 0.4, 0.5, 0.75, 1.0, 1.5], 1, device=cuda_device)
 
 
 def test_solve_on_device_tree_equals_solve_on_host_tree(cuda_device):

@@ -125,3 +125,65 @@ def test_evaluator_with_the_production_depth_and_deep_stacks(cuda_device):
     # the policy targets are distributions over the legal actions
     sums = policy_batch.policy_targets.sum(dim=-1)
     torch.testing.assert_close(sums, torch.ones_like(sums), rtol=1e-4, atol=1e-4)
+
+
+DEFAULT_BINS = [0.5, 0.75, 1.0, 1.5, 2.0]  # EnvConfig.bet_bins of the upstream dataclass: 8 actions per node
+
+
+def test_eight_actions_per_node_on_terminal_trees(cuda_device):
+    """River subgames over the dataclass-default bet sizes (fold, call, five bets, all-in) with a raise cap, so
+    that every leaf is terminal: nodes with 6, 7 and 8 children, trees of 59 ... 207 nodes in one batch.  The
+    one-call solve keeps such a batch in the general kernel (its wide build); equal bits with the oracle."""
+    from oracle import cards, cfr as ocfr
+    from poker2_b200 import solver, tree as ptree
+
+    g = torch.Generator().manual_seed(29)
+    pot, stack = np.array([100, 40, 200, 100]), np.array([400, 1000, 300, 250])
+    n, T = 4, 6
+    boards = torch.stack([torch.randperm(52, generator=g)[:5] for _ in range(n)]).numpy()
+    ranges = torch.empty(n, 2, 1326).exponential_(generator=g) * torch.from_numpy(cards.allowed_mask(boards)).float()[:, None, :]
+    ranges = ranges / ranges.sum(-1, keepdim=True)
+    trees = ptree.build_trees(ptree.root_states(pot, stack, min_raise=2), DEFAULT_BINS, 12, bb=2, max_raises=2)
+    assert np.bincount(trees.root_of).tolist() == [159, 207, 59, 117] and int(trees.child_count.max()) == 8
+    o = ocfr.SubgameOracle(trees.oracle_dict(boards), ranges, iterations=T).solve()
+    ex, _ = o.exploitability()
+    for kw in ({}, dict(device_tree=True)):
+        res, _ = solver.solve_subgames(boards, ranges, pot, stack, iterations=T, bet_bins=DEFAULT_BINS, max_depth=12,
+                                       max_raises=2, exploitability=True, device=cuda_device, **kw)
+        for key, got, want in [("policy_avg", res.level_major(res.policy_avg)[n:], o.policy_avg[n:]),
+                               ("regrets", res.level_major(res.regrets)[n:], o.regrets[n:]),
+                               ("root_values", res.root_values[..., :1326], o.values_avg[:n]), ("exploitability", res.exploitability, ex)]:
+            diff = (got.cpu() - want).abs().max().item()
+            print(f"{kw} {key}: max abs {diff:.3e}")
+            assert torch.equal(got.cpu(), want), (key, diff)
+
+
+def test_default_bet_sizes_at_depth_three_with_model_leaves(cuda_device):
+    """The dataclass-default bet sizes without a raise cap at depth 3: up to 282 nodes, 8 children, most leaves
+    valued by the stand-in model; pass-by-pass solver against the oracle."""
+    from oracle import cards, cfr as ocfr
+    from poker2_b200 import solver, tree as ptree
+
+    g = torch.Generator().manual_seed(31)
+    pot, stack = np.array([20, 100, 200]), np.array([990, 400, 300])
+    n, T = 3, 5
+    boards = torch.stack([torch.randperm(52, generator=g)[:5] for _ in range(n)]).numpy()
+    ranges = torch.empty(n, 2, 1326).exponential_(generator=g) * torch.from_numpy(cards.allowed_mask(boards)).float()[:, None, :]
+    ranges = ranges / ranges.sum(-1, keepdim=True)
+    trees = ptree.build_trees(ptree.root_states(pot, stack, min_raise=2), DEFAULT_BINS, 3, bb=2)
+    assert np.bincount(trees.root_of).tolist() == [282, 143, 52] and int(trees.child_count.max()) == 8
+    w = torch.linspace(-1.0, 1.0, 1326)
+    o = ocfr.SubgameOracle(trees.oracle_dict(boards), ranges, iterations=T,
+                           leaf_fn=lambda b, idx: pot_echo_leaf_fn(trees, idx, w)(b)).solve()
+    ex, _ = o.exploitability()
+    layout = solver.device_layout(trees, boards)
+    sv = solver.SteppedSolver(layout, torch.from_numpy(boards), cuda_device, exploitability=True)
+    res = sv.solve(solver.pad_rows(ranges.to(cuda_device)).contiguous(), solver.iteration_scalars(T),
+                   pot_echo_leaf_fn(trees, layout.model_nodes, w))
+    assert sv.status() == 0
+    for key, got, want in [("policy_avg", res.level_major(res.policy_avg)[n:], o.policy_avg[n:]),
+                           ("regrets", res.level_major(res.regrets)[n:], o.regrets[n:]),
+                           ("root_values", res.root_values[..., :1326], o.values_avg[:n]), ("exploitability", res.exploitability, ex)]:
+        diff = (got.cpu() - want).abs().max().item()
+        print(f"{key}: max abs {diff:.3e}")
+        torch.testing.assert_close(got.cpu(), want, rtol=1e-5, atol=1e-6)
