@@ -267,6 +267,10 @@ def run_gpu_arm(args, rank: int, world: int, local_rank: int):
         guarded("production_search_block", lambda: production_member(solver, layout, boards, rb, device))
         torch.cuda.empty_cache()
         guarded("micro", lambda: micro_member(device))
+        if "micro" in extras and isinstance(extras["micro"], dict) and "showdown" in extras["micro"] and not args.no_cpu_baseline:
+            guarded("micro_cpu", micro_cpu_baselines)
+            if isinstance(extras.get("micro_cpu"), dict) and "showdown" in extras["micro_cpu"]:
+                extras["micro"]["cpu_baseline"] = extras.pop("micro_cpu")
     if distributed and not args.no_extras:
         # every rank takes part in its collectives, so a failure here is not caught rank by rank
         extras["strong"] = run_strong(args, solver, sharding, rank, world, device)
@@ -531,6 +535,36 @@ def micro_member(device, log2_hands: int = 26, board_factor: int = 4, seconds: f
                   "algorithmic_bytes_per_hand": 18, "achieved_gbs": rank_gbs, "frac": rank_gbs / peak},
         "clocks": clocks,
     }
+
+
+def micro_cpu_baselines() -> dict:
+    """The CPU restatements of the two micro-benchmark paths on bounded samples of the same inputs: the showdown
+    oracle (torch CPU eager, the operations of upstream's `_showdown_value`, strength tables included) and the
+    C restatement of the seven-card ranker (one core)."""
+    from oracle import cards as ocards, rank7 as orank, showdown as oshow
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    g = torch.Generator().manual_seed(1)
+    m = 1024
+    boards = torch.rand((m, 52), generator=g).argsort(dim=1)[:, :5].numpy()
+    bel = torch.empty(m, 2, 1326).exponential_(generator=g) * torch.from_numpy(ocards.allowed_mask(boards)).float()[:, None, :]
+    bel = bel / bel.sum(-1, keepdim=True)
+    pot, scale = np.ones((m, 2), dtype=np.int64), np.ones(m, dtype=np.float32)
+    oshow.showdown_values(boards[:4], bel[:4], pot[:4], scale[:4])
+    t0 = time.perf_counter()
+    oshow.showdown_values(boards, bel, pot, scale)
+    dt_sd = time.perf_counter() - t0
+    n = 1 << 22
+    hands = torch.rand((n // 16, 52), generator=g).argsort(dim=1)[:, :7].to(torch.int16).numpy()
+    orank.rank7(hands[:1024])
+    t0 = time.perf_counter()
+    for _ in range(16):
+        orank.rank7(hands)
+    dt_rank = time.perf_counter() - t0
+    return {"showdown": {"evals_per_s": 2 * m / dt_sd, "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": f"{m} boards, tables included ({dt_sd:.1f} s), torch CPU eager"},
+            "rank7": {"hands_per_s": n / dt_rank, "cores": 1, "kind": "port",
+                      "sample": f"2^22 hands ({dt_rank:.1f} s), C restatement, one core"}}
 
 
 def run_micro(args):
