@@ -196,11 +196,12 @@ int p2b_cfr_step(const void* subgames, const void* nodes, int32_t num_subgames, 
                 "average-policy beliefs, bit 3 = keep the node values of every pass, bit 4 = linear CFR");
     P2B_REQUIRE(!(flags & 8) || (values_avg && beliefs_avg), "flags bit 3 needs values_avg and beliefs_avg");
     P2B_REQUIRE(pass_begin >= -1 && pass_begin <= pass_end && pass_end <= iterations, "pass range outside [-1, iterations]");
-    P2B_REQUIRE((phases >= 1 && phases <= 3) || phases == 4 || phases == 8,
-                "phases must be 1 (top-down), 2 (bottom-up), 3 (both), 4 (best responses only) or 8 (best-response pass of "
-                "a warm start)");
+    P2B_REQUIRE((phases >= 1 && phases <= 3) || phases == 4 || phases == 8 || phases == 16,
+                "phases must be 1 (top-down), 2 (bottom-up), 3 (both), 4 (best responses only), 8 (best-response pass of "
+                "a warm start) or 16 (bottom-up sweep of pass_begin, then top-down sweep of pass_begin + 1)");
     P2B_REQUIRE(phases != 8 || (pass_begin == -1 && values_avg), "phases = 8 runs after the start pass and needs values_avg");
-    P2B_REQUIRE(phases == 3 || pass_begin == pass_end, "a single sweep direction covers exactly one pass");
+    P2B_REQUIRE(phases == 3 || phases == 16 || pass_begin == pass_end, "a single sweep direction covers exactly one pass");
+    P2B_REQUIRE(phases != 16 || pass_end == pass_begin + 1, "phases = 16 joins two consecutive passes");
     P2B_REQUIRE(phases != 4 || (pass_begin == iterations && exploitability), "phases = 4 runs after the final pass and needs "
                                                                               "the exploitability output");
     P2B_REQUIRE((!leaf_beliefs && !leaf_values) || leaf_begin, "leaf arrays need leaf_begin");

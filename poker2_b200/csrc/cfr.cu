@@ -1309,8 +1309,10 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
         // root's own row, renormalised once per pass like every other row upstream.
         FV<VPT> prior[2], root_b[2];
         const int pass_first = p.stepped ? p.pass_begin : -1, pass_last = p.stepped ? p.pass_end : p.iterations;
-        const bool run_down = !p.stepped || (p.phases & 1), run_up = !p.stepped || (p.phases & 2);
-        const bool resume = p.stepped && !(pass_first < 0 && run_down);  // continue from carried state
+        // phases 16: the bottom-up sweep of pass_begin and the top-down sweep of pass_begin + 1 in one visit
+        const bool joint = p.stepped && p.phases == 16;
+        const bool run_down = !p.stepped || (p.phases & 1) || joint, run_up = !p.stepped || (p.phases & 2) || joint;
+        const bool resume = p.stepped && !(pass_first < 0 && run_down && !joint);  // continue from carried state
         if (resume) {
             const float* cr = p.carry_roots + (long long)s * 4 * P2B_HPAD;
             prior[0] = ldv<VPT>(cr, tid);
@@ -1337,7 +1339,9 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
                            !p.policy && !p.start_policy && !p.cfr_avg && !p.linear;
         for (int pass = pass_first; pass <= pass_last; ++pass) {
             const int mode = pass < 0 ? kPassInit : (pass == p.iterations ? kPassFinal : kPassIter);
-            if (!run_down) {
+            const bool down_now = run_down && !(joint && pass == pass_first);
+            const bool up_now = run_up && !(joint && pass == pass_last);
+            if (!down_now) {
                 // the top-down sweep of this pass ran in an earlier launch
             } else if (mode == kPassInit) {
                 // prior = the given ranges restricted to the allowed hands; the root's own row is
@@ -1367,8 +1371,8 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
                 }
             }
             if (!done_plain) {  // start and final passes; every pass of a stepped solve or one with optional outputs
-                if (run_down) sweep_down<VPT, MAXC, -1, false>(mode, pass, p, B, hi, prior, tid);
-                if (run_up) sweep_up<VPT, MAXC, -1, false>(mode, pass, p, B, hi, prior, root_b, s, tid);
+                if (down_now) sweep_down<VPT, MAXC, -1, false>(mode, pass, p, B, hi, prior, tid);
+                if (up_now) sweep_up<VPT, MAXC, -1, false>(mode, pass, p, B, hi, prior, root_b, s, tid);
             }
         }
         if (p.stepped) {
@@ -1391,7 +1395,8 @@ __global__ void __launch_bounds__(CfrThreads<VPT>::value, 1) cfr_solve_kernel(co
                 sweep_br<VPT, MAXC>(d, p, B, hi, prior, root_b, tid, unused, true);
             }
         }
-        if (p.exploitability && p.values_avg && (run_up || (p.stepped && (p.phases & 4))) && pass_last == p.iterations) {
+        if (p.exploitability && p.values_avg && !joint && (run_up || (p.stepped && (p.phases & 4))) &&
+            pass_last == p.iterations) {
             // local exploitability of the average policy (cfr_evaluator.py:718-764)
             __syncthreads();
             FV<VPT> base[2], br[2];

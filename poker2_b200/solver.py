@@ -500,7 +500,7 @@ class SteppedSolver(SubgameSolver):
               enforce_zero_sum: bool = False, start_policy: torch.Tensor | None = None, warm_start_iterations: int = 0,
               warm_start_multiplier: float = 1.0, warm_start_scalars: np.ndarray | None = None,
               cfr_avg: bool = False, running_values: bool = False, warm_start_type: str = "model",
-              policy_delta=None, graph: bool = False) -> SolveResult:
+              policy_delta=None, graph: bool = False, joint_sweeps: bool = False) -> SolveResult:
         """scalars: `iteration_scalars(T)` for all T iterations.  start_policy [M,1326] in the
         upstream node order (the policy head's softmax; None = uniform).  With
         warm_start_iterations = w > 0 (needs a start policy) the regrets are seeded from the start
@@ -524,7 +524,12 @@ class SteppedSolver(SubgameSolver):
         graph: replay the iteration passes 1..T-2 from one CUDA graph (`GraphedPass`) instead of
         launching their kernels and the leaf model's one by one; same kernels, same results.  Ignored
         where the host works between the passes (cfr_avg, running_values, policy_delta).  The leaf model must
-        be capturable: device work only, the same shapes every pass, no host synchronisation."""
+        be capturable: device work only, the same shapes every pass, no host synchronisation.
+        joint_sweeps: with model leaves, launch the bottom-up sweep of a pass together with the top-down sweep
+        of the next one (`phases` 16 of `p2b_cfr_step`) wherever the host has nothing to do between them, so
+        that a pass is one solver launch instead of two; same results.  Off by default: measured on 192
+        flop subgames of 273 nodes it changes nothing (2.50 against 2.47 ms per pass), the time of a pass is
+        the blocks' walk over the subgames, not the launches."""
         assert root_beliefs.shape == (self.B, 2, HPAD) and root_beliefs.dtype == torch.float32
         assert root_beliefs.is_contiguous() and root_beliefs.device == self.device
         ws = int(warm_start_iterations)
@@ -573,6 +578,10 @@ class SteppedSolver(SubgameSolver):
             # warm start (whose pass 0 is the warm start's own policy update)
             for t, q in pstats.delta_checkpoints(ws, all_scalars.shape[0]).items():
                 delta_at[t - ws + (0 if ws > 0 else -1)] = q
+        # the bottom-up sweep of a pass waits for the top-down sweep of the next one where they can share a launch
+        fuse = (joint_sweeps and n_leaves > 0 and graphed is None
+                and not (cfr_avg or running_values or policy_delta is not None))
+        pending_up = None
         for pas in range(-1, iterations + 1):
             if pas == 0 and warm_br:
                 # best responses against the start policy, from the node values the start pass has stored
@@ -609,7 +618,11 @@ class SteppedSolver(SubgameSolver):
                 if before is not None:
                     self.policy_deltas[delta_at[pas]] = policy_delta(before, policy_delta.policy_of(self.regrets))
                 continue
-            self._step(root_beliefs, sc, iterations, flags_pass, pas, pas, 1)
+            if pending_up is not None:
+                self._step(root_beliefs, sc, iterations, flags_pass, pending_up, pas, 16)
+                pending_up = None
+            else:
+                self._step(root_beliefs, sc, iterations, flags_pass, pas, pas, 1)
             vals = leaf_fn(self.leaf_beliefs[:n_leaves])
             if cfr_avg:
                 # iteration the pass belongs to, as `set_leaf_values(t)` sees it: the start pass, the pass
@@ -623,6 +636,9 @@ class SteppedSolver(SubgameSolver):
             if self.beliefs_last is not None and pas == iterations - 1:
                 # beliefs of the last iteration at the model leaves (the states sampling continues from)
                 self.beliefs_last[layout_tensor(self.layout, "model_rows", self.device)] = self.leaf_beliefs[:n_leaves]
+            if fuse and pas < iterations and not (pas == -1 and ws > 0):  # (a warm start seeds the regrets before pass 0)
+                pending_up = pas
+                continue
             self._step(root_beliefs, sc, iterations, flags_pass, pas, pas, 2)
             if running_values:
                 self._mix_running_values(pas, ws, all_scalars, enforce_zero_sum)

@@ -187,3 +187,42 @@ def test_default_bet_sizes_at_depth_three_with_model_leaves(cuda_device):
         diff = (got.cpu() - want).abs().max().item()
         print(f"{key}: max abs {diff:.3e}")
         torch.testing.assert_close(got.cpu(), want, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("warm", [False, True])
+def test_joint_sweeps_equal_separate_launches(cuda_device, warm):
+    """A pass as one launch (bottom-up sweep of the pass before it + its own top-down sweep, `phases` 16) against
+    the two launches per pass: same bits, on trees of 52 ... 282 nodes with model leaves, with and without a
+    warm start (whose seeding keeps the first two sweeps apart)."""
+    from oracle import cards
+    from poker2_b200 import solver, tree as ptree
+
+    g = torch.Generator().manual_seed(37)
+    pot, stack = np.array([20, 100, 200, 60]), np.array([990, 400, 300, 970])
+    n, T = 4, 6
+    boards = torch.stack([torch.randperm(52, generator=g)[:5] for _ in range(n)]).numpy()
+    ranges = torch.empty(n, 2, 1326).exponential_(generator=g) * torch.from_numpy(cards.allowed_mask(boards)).float()[:, None, :]
+    ranges = ranges / ranges.sum(-1, keepdim=True)
+    trees = ptree.build_trees(ptree.root_states(pot, stack, min_raise=2), DEFAULT_BINS, 3, bb=2)
+    layout = solver.device_layout(trees, boards)
+    w = torch.linspace(-1.0, 1.0, 1326)
+    fn = pot_echo_leaf_fn(trees, layout.model_nodes, w)
+    rb = solver.pad_rows(ranges.to(cuda_device)).contiguous()
+    scal = solver.iteration_scalars(T, warm_start_iterations=2 if warm else 0)
+    kw = {}
+    if warm:
+        cc = torch.from_numpy(trees.child_count[trees.parent_index.clip(min=0)]).clamp(min=1)
+        kw = dict(start_policy=(1.0 / cc.float())[:, None].expand(-1, 1326).contiguous(), warm_start_iterations=2,
+                  warm_start_multiplier=3.0)
+    out, launches = [], []
+    for joint in (False, True):
+        sv = solver.SteppedSolver(layout, torch.from_numpy(boards), cuda_device, exploitability=True, sampling=True)
+        sv.set_sampling_schedule(torch.tensor([2, 3, 5, 4]), warm_start_iterations=2 if warm else 0)
+        res = sv.solve(rb, scal, fn, joint_sweeps=joint, **kw)
+        assert sv.status() == 0
+        launches.append(sv.launches)
+        out.append([x.clone() for x in (res.policy_avg, res.regrets, res.weight_sums, res.root_values, res.exploitability,
+                                        res.policy_sample, res.beliefs_last)])
+    assert launches[1] < launches[0]
+    for a, b in zip(*out):
+        assert torch.equal(a, b)
