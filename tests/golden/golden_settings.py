@@ -436,6 +436,38 @@ def gen_policy_delta() -> None:
          **out)
 
 
+def gen_depth5() -> None:
+    """The tree shape of the production search settings (conf/config_rebel_cfr.yaml:65-73: bet sizes {0.5, 1.0},
+    depth 5, no raise cap) on turn roots with deep stacks: 273 nodes per root, 68 of them internal, leaves at
+    depth 5 and at the start of the river valued by the stand-in model.  Stores root values, exploitability and
+    every 7th row of the average policy and the regrets."""
+    import make_golden
+
+    g = torch.Generator().manual_seed(91)
+    n, iterations, depth = 2, 6, 5
+    boards = torch.stack([torch.randperm(52, generator=g)[:4] for _ in range(n)])
+    ranges = make_golden.dirichlet_ranges(boards, g)
+    pot, stack = torch.tensor([20, 60]), torch.tensor([990, 970])
+    gc.install_raise_cap(None)
+    ev = gc.make_evaluator(n, iterations, depth=depth)
+    ev.model = gc.PotEchoModel(len(BET_BINS) + 3)
+    ev.initialize_subgame(gc.turn_env(boards, pot, stack), torch.arange(n), ranges)
+    ev.generator = torch.Generator().manual_seed(5)
+    ev.evaluate_cfr()
+    ex = ev._compute_exploitability()
+    model_mask = ev.leaf_mask & ~ev.env.done
+    rows = torch.arange(n, ev.total_nodes, 7)
+    print("depth 5, no cap: nodes", ev.total_nodes, "model leaves", int(model_mask.sum()), "exploitability",
+          ex.local_exploitability.tolist())
+    save("cfr_depth5_nocap_t6.npz",
+         boards=boards.to(torch.int16).numpy(), ranges=ranges.numpy(), pot=pot.numpy(), stack=stack.numpy(),
+         iterations=np.int64(iterations), max_depth=np.int64(depth), total_nodes=np.int64(ev.total_nodes),
+         model_mask=model_mask.numpy(), hand_weights=gc.hand_weights().numpy(), rows=rows.numpy(),
+         policy_avg_rows=ev.policy_probs_avg[rows].numpy(), regrets_rows=ev.cumulative_regrets[rows].numpy(),
+         root_values=ev.values_avg[:n].numpy(), exploitability=ex.local_exploitability.numpy(),
+         br_values=ex.local_best_response_values.numpy())
+
+
 gc.SECTIONS.update(production=gen_production, standard=gen_standard, zero_sum=gen_zero_sum, ragged256=gen_ragged256,
                    cfr_avg=gen_cfr_avg, running_values=gen_running_values, warm_br=gen_warm_br, linear=gen_linear, policy_head=gen_policy_head, dataclass_defaults=gen_dataclass_defaults,
-                   policy_delta=gen_policy_delta)
+                   policy_delta=gen_policy_delta, depth5=gen_depth5)

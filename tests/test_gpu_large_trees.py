@@ -226,3 +226,32 @@ def test_joint_sweeps_equal_separate_launches(cuda_device, warm):
     assert launches[1] < launches[0]
     for a, b in zip(*out):
         assert torch.equal(a, b)
+
+
+def test_production_tree_shape_against_the_upstream_run(cuda_device, golden_dir):
+    """The same trees (depth 5, no raise cap, 273 and 242 nodes) solved pass by pass on the GPU, against the
+    arrays the upstream evaluator produced."""
+    import os
+
+    from poker2_b200 import solver, tree as ptree
+
+    z = np.load(os.path.join(golden_dir, "cfr_depth5_nocap_t6.npz"))
+    trees = ptree.build_trees(ptree.root_states(z["pot"], z["stack"], min_raise=2, street=2), [0.5, 1.0],
+                              int(z["max_depth"]), bb=2)
+    assert trees.total_nodes == int(z["total_nodes"])
+    boards = np.concatenate([z["boards"].astype(np.int64), np.full((2, 1), -1)], axis=1)
+    layout = solver.device_layout(trees, boards)
+    sv = solver.SteppedSolver(layout, torch.from_numpy(boards), cuda_device, exploitability=True)
+    fn = pot_echo_leaf_fn(trees, layout.model_nodes, torch.from_numpy(z["hand_weights"]))
+    rb = solver.pad_rows(torch.from_numpy(z["ranges"]).to(cuda_device)).contiguous()
+    res = sv.solve(rb, solver.iteration_scalars(int(z["iterations"])), fn)
+    assert sv.status() == 0
+    rows = torch.from_numpy(z["rows"])
+    for key, got, want in [("policy_avg", res.level_major(res.policy_avg).cpu()[rows], z["policy_avg_rows"]),
+                           ("regrets", res.level_major(res.regrets).cpu()[rows], z["regrets_rows"]),
+                           ("root_values", res.root_values[..., :1326].cpu(), z["root_values"]),
+                           ("exploitability", res.exploitability.cpu(), z["exploitability"]),
+                           ("br_values", res.br_values.cpu(), z["br_values"])]:
+        want = torch.from_numpy(want)
+        print(f"{key}: max abs {(got - want).abs().max().item():.3e}")
+        torch.testing.assert_close(got, want, rtol=1e-5, atol=1e-6)

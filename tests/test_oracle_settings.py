@@ -295,3 +295,22 @@ def test_policy_delta_host_computation_against_the_oracle(golden_dir):
             got = float(pd(before, pd.policy_of(rows(o.regrets))))
             assert got == pytest.approx(o.stats[f"cfr_delta.{points[it]}"], rel=1e-6), it
     assert len(o.stats) == 5
+
+
+def test_oracle_on_the_production_tree_shape_bit_exact(golden_dir):
+    """Depth 5, bet sizes {0.5, 1.0}, no raise cap, deep stacks: the trees of the production search settings
+    (273 and 242 nodes), leaves valued by the stand-in model, against the upstream run."""
+    z = np.load(os.path.join(golden_dir, "cfr_depth5_nocap_t6.npz"))
+    t = ptree.build_trees(ptree.root_states(z["pot"], z["stack"], min_raise=2, street=2), BET_BINS, int(z["max_depth"]), bb=2)
+    assert t.total_nodes == int(z["total_nodes"]) and np.bincount(t.root_of).tolist() == [273, 242]
+    assert np.array_equal(t.leaf_mask & ~t.state.done, z["model_mask"])
+    boards = np.concatenate([z["boards"].astype(np.int64), np.full((2, 1), -1)], axis=1)
+    w = torch.from_numpy(z["hand_weights"])
+    o = ocfr.SubgameOracle(t.oracle_dict(boards), torch.from_numpy(z["ranges"]), iterations=int(z["iterations"]),
+                           leaf_fn=lambda b, idx: pot_echo_leaf_fn(t, idx, w)(b)).solve()
+    rows = torch.from_numpy(z["rows"])
+    assert torch.equal(o.policy_avg[rows], torch.from_numpy(z["policy_avg_rows"]))
+    assert torch.equal(o.regrets[rows], torch.from_numpy(z["regrets_rows"]))
+    assert torch.equal(o.values_avg[:2], torch.from_numpy(z["root_values"]))
+    ex, br = o.exploitability()
+    assert torch.equal(ex, torch.from_numpy(z["exploitability"])) and torch.equal(br, torch.from_numpy(z["br_values"]))
