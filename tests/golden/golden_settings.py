@@ -468,6 +468,38 @@ def gen_depth5() -> None:
          br_values=ex.local_best_response_values.numpy())
 
 
+def gen_default_bins() -> None:
+    """The bet sizes of the upstream configuration dataclass ({0.5, 0.75, 1.0, 1.5, 2.0}: eight actions per
+    node) on river roots at depth 3 without a raise cap: trees of up to 280 nodes whose deepest leaves are
+    valued by the stand-in model.  Stores root values, exploitability and every 5th row of the average policy
+    and the regrets."""
+    bins = [0.5, 0.75, 1.0, 1.5, 2.0]
+    b, r, p, s = gc.seeded_inputs(93, 2, (20, 200), (100, 1000))
+    p, s = torch.tensor([40, 100]), torch.tensor([1000, 400])
+    iterations, depth = 6, 3
+    old = gc.BET_BINS
+    gc.BET_BINS = bins
+    try:
+        gc.install_raise_cap(None)
+        ev = gc.make_evaluator(2, iterations, depth=depth)
+        ev.model = gc.PotEchoModel(len(bins) + 3)
+        ex = _solve(ev, gc.river_env(b, p, s), 2, r)
+    finally:
+        gc.BET_BINS = old
+    model_mask = ev.leaf_mask & ~ev.env.done
+    rows = torch.arange(2, ev.total_nodes, 5)
+    print("default bet sizes: nodes", ev.total_nodes, "actions", ev.num_actions, "model leaves", int(model_mask.sum()),
+          "exploitability", ex.local_exploitability.tolist())
+    save("cfr_default_bins_depth3_t6.npz",
+         boards=b.to(torch.int16).numpy(), ranges=r.numpy(), pot=p.numpy(), stack=s.numpy(), bet_bins=np.float64(bins),
+         iterations=np.int64(iterations), max_depth=np.int64(depth), total_nodes=np.int64(ev.total_nodes),
+         model_mask=model_mask.numpy(), hand_weights=gc.hand_weights().numpy(), rows=rows.numpy(),
+         policy_avg_rows=ev.policy_probs_avg[rows].numpy(), regrets_rows=ev.cumulative_regrets[rows].numpy(),
+         root_values=ev.values_avg[:2].numpy(), exploitability=ex.local_exploitability.numpy(),
+         br_values=ex.local_best_response_values.numpy())
+
+
 gc.SECTIONS.update(production=gen_production, standard=gen_standard, zero_sum=gen_zero_sum, ragged256=gen_ragged256,
                    cfr_avg=gen_cfr_avg, running_values=gen_running_values, warm_br=gen_warm_br, linear=gen_linear, policy_head=gen_policy_head, dataclass_defaults=gen_dataclass_defaults,
-                   policy_delta=gen_policy_delta, depth5=gen_depth5)
+                   policy_delta=gen_policy_delta, depth5=gen_depth5,
+                   default_bins=gen_default_bins)

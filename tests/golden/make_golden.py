@@ -8,7 +8,8 @@ its `src` directory and P2_REFERENCE_TESTS to its `tests` directory:
 
 Sections (default: all): rules, showdown, unblocked, tree, cfr, turn, training_data, warm_start, chance, flop_chance,
 replay, rounds, steps, production, standard, zero_sum, ragged256, cfr_avg, running_values, warm_br, linear,
-policy_head, dataclass_defaults, policy_delta, depth5.  The outputs are small .npz files that travel with the repository;
+policy_head, dataclass_defaults, policy_delta, depth5,
+default_bins.  The outputs are small .npz files that travel with the repository;
 the test-suite reads only those files, never the upstream checkout.
 """
 from __future__ import annotations

@@ -255,3 +255,33 @@ def test_production_tree_shape_against_the_upstream_run(cuda_device, golden_dir)
         want = torch.from_numpy(want)
         print(f"{key}: max abs {(got - want).abs().max().item():.3e}")
         torch.testing.assert_close(got, want, rtol=1e-5, atol=1e-6)
+
+
+def test_default_bet_sizes_against_the_upstream_run(cuda_device, golden_dir):
+    """Eight actions per node at depth 3 (280 and 143 nodes, model leaves at the depth limit) on the GPU, against
+    the arrays of the upstream run."""
+    import os
+
+    from poker2_b200 import solver, tree as ptree
+
+    z = np.load(os.path.join(golden_dir, "cfr_default_bins_depth3_t6.npz"))
+    bins = [float(x) for x in z["bet_bins"]]
+    trees = ptree.build_trees(ptree.root_states(z["pot"], z["stack"], min_raise=2), bins, int(z["max_depth"]), bb=2)
+    assert trees.total_nodes == int(z["total_nodes"])
+    boards = z["boards"].astype(np.int64)
+    layout = solver.device_layout(trees, boards)
+    assert layout.max_children == 8
+    sv = solver.SteppedSolver(layout, torch.from_numpy(boards), cuda_device, exploitability=True)
+    fn = pot_echo_leaf_fn(trees, layout.model_nodes, torch.from_numpy(z["hand_weights"]))
+    rb = solver.pad_rows(torch.from_numpy(z["ranges"]).to(cuda_device)).contiguous()
+    res = sv.solve(rb, solver.iteration_scalars(int(z["iterations"])), fn)
+    assert sv.status() == 0
+    rows = torch.from_numpy(z["rows"])
+    for key, got, want in [("policy_avg", res.level_major(res.policy_avg).cpu()[rows], z["policy_avg_rows"]),
+                           ("regrets", res.level_major(res.regrets).cpu()[rows], z["regrets_rows"]),
+                           ("root_values", res.root_values[..., :1326].cpu(), z["root_values"]),
+                           ("exploitability", res.exploitability.cpu(), z["exploitability"]),
+                           ("br_values", res.br_values.cpu(), z["br_values"])]:
+        want = torch.from_numpy(want)
+        print(f"{key}: max abs {(got - want).abs().max().item():.3e}")
+        torch.testing.assert_close(got, want, rtol=1e-5, atol=1e-6)

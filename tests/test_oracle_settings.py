@@ -314,3 +314,23 @@ def test_oracle_on_the_production_tree_shape_bit_exact(golden_dir):
     assert torch.equal(o.values_avg[:2], torch.from_numpy(z["root_values"]))
     ex, br = o.exploitability()
     assert torch.equal(ex, torch.from_numpy(z["exploitability"])) and torch.equal(br, torch.from_numpy(z["br_values"]))
+
+
+def test_oracle_with_the_default_bet_sizes_bit_exact(golden_dir):
+    """Eight actions per node (the bet sizes of the upstream dataclass) at depth 3 without a raise cap, leaves at
+    the depth limit valued by the stand-in model: trees of 280 and 143 nodes against the upstream run."""
+    z = np.load(os.path.join(golden_dir, "cfr_default_bins_depth3_t6.npz"))
+    bins = [float(x) for x in z["bet_bins"]]
+    t = ptree.build_trees(ptree.root_states(z["pot"], z["stack"], min_raise=2), bins, int(z["max_depth"]), bb=2)
+    assert t.total_nodes == int(z["total_nodes"]) and t.num_actions == 8 and int(t.child_count.max()) == 8
+    assert np.array_equal(t.leaf_mask & ~t.state.done, z["model_mask"])
+    boards = z["boards"].astype(np.int64)
+    w = torch.from_numpy(z["hand_weights"])
+    o = ocfr.SubgameOracle(t.oracle_dict(boards), torch.from_numpy(z["ranges"]), iterations=int(z["iterations"]),
+                           leaf_fn=lambda b, idx: pot_echo_leaf_fn(t, idx, w)(b)).solve()
+    rows = torch.from_numpy(z["rows"])
+    assert torch.equal(o.policy_avg[rows], torch.from_numpy(z["policy_avg_rows"]))
+    assert torch.equal(o.regrets[rows], torch.from_numpy(z["regrets_rows"]))
+    assert torch.equal(o.values_avg[:2], torch.from_numpy(z["root_values"]))
+    ex, br = o.exploitability()
+    assert torch.equal(ex, torch.from_numpy(z["exploitability"])) and torch.equal(br, torch.from_numpy(z["br_values"]))
