@@ -31,7 +31,6 @@ import numpy as np
 import torch
 
 from . import evaluator as pevaluator
-from . import tree as ptree
 
 NUM_HANDS = 1326
 
