@@ -159,6 +159,13 @@ int64_t p2b_cfr_scratch_floats(int32_t max_internal, int32_t num_blocks);
 int64_t p2b_cfr_solve_scratch_floats(int32_t max_internal, int32_t max_children, int32_t num_blocks,
                                      int32_t num_subgames, int64_t rows);
 int p2b_cfr_default_blocks(void);
+/* Which kernel runs the iteration passes of a p2b_cfr_solve whose leaves are all terminal (process-wide
+ * setting, no counterpart in the upstream project).  0, the default: the lean kernel, except for batches so
+ * small that the general kernel is quicker (at most one subgame per SM; or fewer than eight per SM while
+ * max_internal x max_children + 1 exceeds 160, i.e. some subgame may be too large for the lean kernel).
+ * 1: the lean kernel whenever it applies.  Results are the same bits either way.  Returns the previous
+ * setting; a negative argument only queries. */
+int p2b_cfr_path_policy(int32_t policy);
 /* Measurement aid (no counterpart in the upstream project): with timing enabled on the current
  * device, a p2b_cfr_solve that runs its iteration passes in the lean kernel brackets that one
  * launch with CUDA events on the caller's stream; p2b_cfr_iteration_ms waits for it and writes

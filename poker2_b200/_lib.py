@@ -71,7 +71,7 @@ _SIGNATURES = {
 # functions whose return value is a quantity, not a status code
 _VALUE_FUNCS = {"p2b_cfr_scratch_floats": ([_i32, _i32], _i64), "p2b_cfr_default_blocks": ([], _i32),
                 "p2b_cfr_solve_scratch_floats": ([_i32, _i32, _i32, _i32, _i64], _i64),
-                "p2b_cfr_noalloc_scratch_floats": ([], _i64)}
+                "p2b_cfr_noalloc_scratch_floats": ([], _i64), "p2b_cfr_path_policy": ([_i32], _i32)}
 
 
 def library_available() -> bool:

@@ -78,6 +78,8 @@ int p2b_showdown_ev_sorted(const float* b_sorted, const int32_t* c1_sorted, cons
 
 int p2b_cfr_default_blocks(void) { return cfr_default_blocks(); }
 
+int p2b_cfr_path_policy(int32_t policy) { return cfr_path_policy(policy); }
+
 int p2b_cfr_iteration_timing(int32_t enable) { return cfr_iteration_timing(enable); }
 
 int p2b_cfr_iteration_ms(float* ms) {

@@ -25,6 +25,7 @@
 // accumulates in fp64 and rounds to fp32 (unblocked mass, showdown prefix sums) are
 // accumulated in fp64 here too, in a different order, which changes the rounded fp32
 // result only when the fp64 value lies within ~1e-16 of a rounding boundary.
+#include <atomic>
 #include <mutex>
 
 #include "cfr.cuh"
@@ -1566,6 +1567,20 @@ IterTiming* iter_timing_of_current_device() {
 }
 }  // namespace
 
+// Which kernel runs the iteration passes of a plain one-call solve.  0 (default): the lean kernel, unless the
+// batch is so small that the general kernel is quicker -- at most one subgame per SM (a lone 448-thread block
+// leaves an SM idler than the general kernel's 672 threads: 22.3 against 30.2 ms for 148 subgames x 64
+// iterations), or fewer than eight per SM when some subgame may exceed the lean kernel's node limit (the lean
+// launch and the launch for the large subgames would then both run half empty, one after the other: 36 against
+// 64 ms for 192 ragged subgames of up to 237 nodes x 24 iterations).  1: the lean kernel whenever it applies.
+static std::atomic<int> g_path_policy{0};
+
+int cfr_path_policy(int policy) {
+    const int before = g_path_policy.load();
+    if (policy >= 0) g_path_policy.store(policy != 0);
+    return before;
+}
+
 int cfr_iteration_timing(int enable) {
     IterTiming* t = iter_timing_of_current_device();
     if (!t) return set_error(P2B_ERR_STATE, "no current device");
@@ -1617,7 +1632,10 @@ int launch_cfr_solve(const CfrParams& params, int num_blocks, int max_children, 
     long long per_block = cfr_scratch_floats(p.max_internal);
     const long long iter_block = cfr_iter_scratch_floats(p.max_internal, max_children);
     if (iter_block > per_block) per_block = iter_block;
-    if (!(plain && fast_scratch && max_children <= kIterMaxChildren)) {
+    const bool maybe_large = (long long)p.max_internal * max_children + 1 > kIterMaxNodes;
+    const bool few = g_path_policy.load() == 0 &&
+                     (p.num_subgames <= sm_count() || (maybe_large && p.num_subgames < 8 * sm_count()));
+    if (!(plain && fast_scratch && max_children <= kIterMaxChildren && !few)) {
         if (p.warm_weight > 0.0f) {
             // the general kernel in two launches around the seeding: start pass, then every other pass
             if (p.stepped) return set_error(P2B_ERR_ARG, "a stepped solve seeds its warm start itself");
@@ -1679,7 +1697,7 @@ int launch_cfr_solve(const CfrParams& params, int num_blocks, int max_children, 
             // Subgames with more nodes than the iteration kernel holds in shared memory were skipped by it:
             // the general kernel runs their iteration passes.  The batch can only contain such a subgame
             // if the bound below exceeds the limit.
-            if (!rc && (long long)p.max_internal * max_children + 1 > kIterMaxNodes) {
+            if (!rc && maybe_large) {
                 rc = clear_counters(q.work_counter, stream);
                 if (rc) return rc;
                 q.large_only = 1;

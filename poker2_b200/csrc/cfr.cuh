@@ -163,6 +163,7 @@ int launch_cfr_solve(const CfrParams& p, int num_blocks, int max_children, cudaS
 long long cfr_iter_scratch_floats(int max_internal, int max_children);
 long long cfr_solve_scratch_floats(int max_internal, int max_children, int num_blocks, int num_subgames, long long rows);
 int launch_cfr_iter(const CfrParams& p, int num_blocks, cudaStream_t stream);
+int cfr_path_policy(int policy);  // returns the previous one; < 0 only queries
 int cfr_iteration_timing(int enable);
 int cfr_iteration_ms(float* ms);
 int cfr_default_blocks();

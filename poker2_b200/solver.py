@@ -31,6 +31,16 @@ SCALAR_DTYPE = np.dtype([("num_pos", "<f4"), ("den_pos", "<f4"), ("num_neg", "<f
 assert NODE_DTYPE.itemsize == 16 and SUBGAME_DTYPE.itemsize == 32 and SCALAR_DTYPE.itemsize == 32
 
 
+def set_path_policy(policy: str) -> str:
+    """Which kernel runs the iteration passes of one-call solves in this process: "auto" (default: the lean
+    kernel except for batches so small that the general kernel is quicker, see `p2b_cfr_path_policy`) or "lean"
+    (the lean kernel whenever it applies).  Returns the previous setting; results do not depend on it."""
+    names = ("auto", "lean")
+    if policy not in names:
+        raise ValueError(f"unknown path policy {policy!r}")
+    return names[int(_lib.lib().p2b_cfr_path_policy(names.index(policy)))]
+
+
 def node_kind(records):
     """Kind of node records (`tree.KIND_*`): bits 0-1 of the `kind_act` byte."""
     return records["kind_act"] & 3

@@ -28,4 +28,9 @@ def cuda_device():
     from poker2_b200 import build
 
     build.build()
+    # The fixtures are batches of a few subgames, which the default policy would hand to the general kernel;
+    # the suite wants the lean iteration kernel on them too (tests/test_gpu_path_policy.py covers the default).
+    from poker2_b200 import solver
+
+    solver.set_path_policy("lean")
     return torch.device("cuda:0")
