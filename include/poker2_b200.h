@@ -202,7 +202,10 @@ int p2b_cfr_iteration_ms(float* ms);
  *  leaf_beliefs [slots,2,1344] out (top-down sweep): both players' beliefs at each such leaf
  *  leaf_values  [slots,2,1344] in (bottom-up sweep): both players' values there, in the units
  *               of the other leaf values (chips / scale)
- * With leaf_beliefs == NULL / leaf_values == NULL such leaves are skipped / valued 0. */
+ * With leaf_beliefs == NULL / leaf_values == NULL such leaves are skipped / valued 0.
+ * queue_order (may be NULL) as in p2b_cfr_solve: the order in which the blocks take the subgames; the
+ * largest trees first shortens a launch over a ragged batch (192 subgames of 9..237 nodes: 35.8 against
+ * 41.8 ms for 24 iterations). */
 int p2b_cfr_step(const void* subgames, const void* nodes, int32_t num_subgames, int64_t rows, int32_t max_children,
                  int32_t max_internal, const unsigned char* tables, const float* root_beliefs,
                  float* regrets, float* weight_sums, float* policy_avg, float* policy,
@@ -212,7 +215,7 @@ int p2b_cfr_step(const void* subgames, const void* nodes, int32_t num_subgames, 
                  int32_t num_blocks, int32_t pass_begin, int32_t pass_end, int32_t phases,
                  float* carry_sums, float* carry_roots, const int32_t* leaf_begin, int32_t leaf_slots,
                  float* leaf_beliefs, const float* leaf_values, const int32_t* sample_pass, float* policy_sample,
-                 float* beliefs_last, const float* start_policy, void* stream);
+                 float* beliefs_last, const int32_t* queue_order, const float* start_policy, void* stream);
 
 /* Start policy and warm start (initialize_policy_and_beliefs with a policy head,
  * src/p2/search/cfr_evaluator.py:830-886, and warm_start of type `model`, :887-926).

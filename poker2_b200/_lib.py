@@ -34,7 +34,7 @@ _SIGNATURES = {
                       _vp, _i32, _i32, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _f32, _vp],
     "p2b_cfr_step": [_vp, _vp, _i32, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64,
                      _vp, _i32, _i32, _i32, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp,
-                     _vp, _vp],
+                     _vp, _vp, _vp],
     "p2b_cfr_warm_seed": [_vp, _i64, _vp, _f32, _vp, _vp, _vp],
     "p2b_cfr_noalloc_status": [_vp, _vp],
     "p2b_cfr_iteration_timing": [_i32],

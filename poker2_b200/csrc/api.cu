@@ -180,8 +180,8 @@ int p2b_cfr_step(const void* subgames, const void* nodes, int32_t num_subgames, 
                  const void* scalars, int32_t iterations, int32_t flags, int32_t init_depth, int32_t* work_counter,
                  int32_t num_blocks, int32_t pass_begin, int32_t pass_end, int32_t phases, float* carry_sums,
                  float* carry_roots, const int32_t* leaf_begin, int32_t leaf_slots, float* leaf_beliefs,
-                 const float* leaf_values, const int32_t* sample_pass, float* policy_sample, float* beliefs_last, const float* start_policy,
-                 void* stream) {
+                 const float* leaf_values, const int32_t* sample_pass, float* policy_sample, float* beliefs_last,
+                 const int32_t* queue_order, const float* start_policy, void* stream) {
     P2B_REQUIRE(num_subgames >= 0 && iterations >= 1 && rows >= 0 && leaf_slots >= 0, "bad count");
     P2B_REQUIRE((reinterpret_cast<uintptr_t>(start_policy) & 15) == 0, "all row arrays must be 16-byte aligned");
     P2B_REQUIRE(!policy_sample || sample_pass, "policy_sample needs sample_pass");
@@ -259,6 +259,7 @@ int p2b_cfr_step(const void* subgames, const void* nodes, int32_t num_subgames, 
     p.sample_pass = sample_pass;
     p.policy_sample = policy_sample;
     p.beliefs_last = beliefs_last;
+    p.queue_order = queue_order;
     p.start_policy = start_policy;
     p.rows = rows;
     p.leaf_slots = leaf_slots;

@@ -503,7 +503,8 @@ class SteppedSolver(SubgameSolver):
                 self.num_blocks, pass_begin, pass_end, phases, p(self.carry_sums), p(self.carry_roots),
                 p(self.leaf_begin), int(self.leaf_beliefs.shape[0]), p(self.leaf_beliefs), p(self.leaf_values),
                 p(sample_pass),
-                p(self.policy_sample), p(self.beliefs_last), p(self.start_policy_rows), _lib.stream_ptr(self.device))
+                p(self.policy_sample), p(self.beliefs_last), p(self.queue_order), p(self.start_policy_rows),
+                _lib.stream_ptr(self.device))
         self.launches += 1
 
     def solve(self, root_beliefs: torch.Tensor, scalars: np.ndarray, leaf_fn=None, *, cfr_plus: bool = False,
