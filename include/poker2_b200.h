@@ -98,7 +98,8 @@ int p2b_showdown_ev_sorted(const float* b_sorted, const int32_t* c1_sorted, cons
  *             p2b_cfr_solve_scratch_floats(max_internal, max_children, num_blocks, num_subgames, rows)
  *             floats the solve runs as
  *             three launches (start pass; iteration passes in a leaner kernel; final pass) with the same
- *             results, bit for bit; the extra floats carry the root rows between the launches
+ *             results, bit for bit; the extra floats carry the root rows between the launches (very
+ *             small batches stay in the one-launch form, see p2b_cfr_path_policy)
  *  scalars    [iterations] 32-byte records {float t^alpha, t^alpha+1, t^beta, t^beta+1,
  *             mix_old, mix_new, fl(mix_old+mix_new); int32 do_mix (bit 0; bits 1-2 see flags bit 4)}
  *  flags      bit 0: CFR+ (cumulative regrets clamped at zero after every update, cfr_evaluator.py:1366-1368);
