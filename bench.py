@@ -760,6 +760,74 @@ def run_street(args, rank: int, world: int, local_rank: int):
         dist.destroy_process_group()
 
 
+def run_production(args):
+    """What the production configuration of the upstream repository asks of the evaluator per call
+    (conf/config_rebel_cfr.yaml: 192 environments, bet sizes {0.5, 1.0}, depth 5, no raise cap, 200 iterations of
+    discounted_plus with a delay of 80 and exponent schedules, a warm start of type `model` over the first 15):
+    flop roots with deep stacks, so that the trees are the largest this configuration produces (up to 273
+    nodes), leaves valued by a random-init bf16 MLP called once per leaf, through `evaluator.SubgameEvaluator`
+    (initialize_subgame, evaluate_cfr with its leaf sampling and statistics, training_data)."""
+    from poker2_b200 import build, evaluator, leaf_eval, tree as ptree
+
+    build.build()
+    device = torch.device("cuda:0")
+    torch.cuda.set_device(device)
+    batch = args.batch if args.batch != 4096 else 192
+    iterations = args.iterations if args.iterations != 256 else 200
+    boards3, ranges, _, _ = make_street_inputs(batch, 3, 7, 1.0)
+    g = torch.Generator().manual_seed(8)
+    pot = torch.randint(20, 900, (batch,), generator=g).numpy()
+    stack = 1000 - pot // 2
+    boards = torch.full((batch, 5), -1, dtype=torch.int64)
+    boards[:, :3] = boards3
+    roots = ptree.root_states(pot, stack, min_raise=10, street=1)
+    env = evaluator.env_view(roots, boards.numpy())
+    model = leaf_eval.ValueMLP(1536, 4, dtype=torch.bfloat16, seed=0).to(device)
+    ws = min(15, max(iterations - 1, 0))
+    info = {}
+
+    def step():
+        ev = evaluator.SubgameEvaluator(
+            device, iterations=iterations, bet_bins=BET_BINS, max_depth=5, bb=10, cfr_type="discounted_plus", alpha=2.0,
+            alpha_final=4.0, beta=-1.0, beta_final=-2.0, gamma=5.0, gamma_final=0.0, dcfr_delay=min(80, iterations // 2),
+            warm_start_iterations=ws, warm_start_multiplier=10.0, enforce_zero_sum=True, model=model,
+            chance_average=False, generator=torch.Generator(device=device).manual_seed(1))
+        ev.initialize_subgame(env, torch.arange(batch), ranges)
+        ev.evaluate_cfr()
+        value_batch, _, policy_batch = ev.training_data()
+        info.update(nodes=ev.trees.total_nodes, largest=int(np.bincount(ev.trees.root_of).max()),
+                    leaves=ev.layout.num_model_leaves, launches=ev.solver.launches, rows=len(policy_batch),
+                    exploitability=ev.stats["local_exploitability"])
+        return float(value_batch.value_targets.float().sum().item())  # the read that ends the step
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    sampler.start()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    torch.cuda.synchronize()
+    ms_step = (time.perf_counter() - t0) * 1e3 / args.steps
+    clocks = sampler.stop()
+    passes = iterations - ws + 1 if ws else iterations
+    print(json.dumps({
+        "metric": "subgame-CFR-iterations/sec", "value": batch * passes / (ms_step / 1e3), "unit": "subgame-iterations/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32 solver state, bf16 leaf network", "data": "synthetic",
+        "config": {"workload": f"production-shaped evaluator call: {batch} flop roots (stack 1000, blinds 5/10), bet sizes "
+                               f"{{0.5, 1.0}}, depth 5, no raise cap, {iterations} iterations discounted_plus with schedules, "
+                               f"warm start {ws} x model ({passes} iteration passes), leaves valued by a random-init bf16 MLP "
+                               "(2707 -> 4 x 1536 GELU -> 2652) once per leaf; tree build, leaf sampling, statistics and "
+                               "training batches inside the timed region (host clock)",
+                   "batch": batch, "iterations": iterations, "nodes": info["nodes"], "largest_tree": info["largest"],
+                   "model_leaves": info["leaves"], "policy_rows": info["rows"],
+                   "local_exploitability": info["exploitability"]},
+        "clocks": clocks, "gpu_launches": info["launches"] * args.steps,
+    }))
+
+
 def main():
     global BATCH, ITERATIONS
     ap = argparse.ArgumentParser()
@@ -773,9 +841,10 @@ def main():
                     help="skip the micro, without_weight_sums and strong members (profiling runs)")
     ap.add_argument("--batch", type=int, default=BATCH, help="subgames per GPU (default: the headline 4096)")
     ap.add_argument("--iterations", type=int, default=ITERATIONS, help="DCFR iterations (default: 256)")
-    ap.add_argument("--workload", default="river", choices=["river", "micro", "turn", "flop"],
+    ap.add_argument("--workload", default="river", choices=["river", "micro", "turn", "flop", "production"],
                     help="river = the headline batched river solve; micro = rules/showdown micro-benchmark; "
-                         "turn / flop = subgames with network-valued leaves")
+                         "turn / flop = subgames with network-valued leaves; production = one evaluator call of the "
+                         "upstream production configuration (192 flop roots, depth 5, no raise cap)")
     ap.add_argument("--micro-log2-hands", type=int, default=26)
     ap.add_argument("--micro-board-factor", type=int, default=4, help="boards = 4096 x this")
     ap.add_argument("--leaf-chunk", type=int, default=2048, help="leaves per network batch (x ~48 samples)")
@@ -797,6 +866,10 @@ def main():
         return
     if args.workload in ("turn", "flop"):
         run_street(args, rank, world, local_rank)
+        return
+    if args.workload == "production":
+        if rank == 0:
+            run_production(args)
         return
     run_gpu_arm(args, rank, world, local_rank)
 
